@@ -1,0 +1,366 @@
+// C ABI of the library (include/dfdx_b200.h) and the host-side lowering of dfdx's kernel traits to
+// the canonical GemmProblem.  The lowering functions restate, call for call, the argument
+// computation of `impl MatMat*Kernel for Cuda` (dfdx-core/src/tensor_ops/matmul/cuda_kernel.rs)
+// — which strides are swapped for the transposed operands of the backward GEMMs, which batch
+// strides are zero — so a Rust caller can hand over `Tensor::strides` untouched.
+#include "common.cuh"
+#include <atomic>
+#include <mutex>
+#include <cstdio>
+#include <cstring>
+
+namespace b200 {
+
+size_t conv2d_workspace_bytes(int dtype, const b200_conv2d_op* o, int backward);
+int conv2d_forward(int dtype, const b200_conv2d_op* o, const void* img, const size_t is[4], const void* filters,
+                   void* out, void* ws, cudaStream_t stream);
+int conv2d_backward(int dtype, const b200_conv2d_op* o, const void* img, void* grad_img, const void* filters,
+                    const size_t fs[4], void* grad_filters, const void* grad_out, void* ws, cudaStream_t stream);
+void tc_set_xform_mode(int mode);
+
+namespace {
+
+constexpr int MAX_DEVICES = 64;
+DeviceState g_dev[MAX_DEVICES];
+std::mutex g_dev_mutex;
+std::atomic<int> g_path{B200_PATH_AUTO};
+std::atomic<uint64_t> g_launches{0}, g_tc_launches{0};
+thread_local char t_cuda_err[256] = "";
+
+bool valid_dtype(int d) { return d == B200_F32 || d == B200_F64 || d == B200_F16 || d == B200_AMP_F16; }
+
+// matmul/mod.rs:316-325: legal 2-D stride pairs have at least one unit stride.
+bool matrix_strides_ok(const size_t s[2]) { return s[0] == 1 || s[1] == 1; }
+
+}  // namespace
+
+DeviceState* device_state() {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) return nullptr;
+  return g_dev[dev].ready ? &g_dev[dev] : nullptr;
+}
+
+int note_cuda_error(cudaError_t e, const char* where) {
+  if (e == cudaSuccess) return B200_OK;
+  snprintf(t_cuda_err, sizeof(t_cuda_err), "%s: %s (%s)", where, cudaGetErrorName(e), cudaGetErrorString(e));
+  return B200_ERR_CUDA;
+}
+
+void count_launch(bool tensor) {
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  if (tensor) g_tc_launches.fetch_add(1, std::memory_order_relaxed);
+}
+
+// Batch folding: when rhs is shared by the whole batch and lhs / out are stacked with the row
+// stride, (B, M, K) x (K, N) is one (B*M, K) x (K, N) GEMM (no partial M tiles per batch item).
+static void fold_batch(GemmProblem& p) {
+  if (p.red != 1) return;
+  if (p.b1 > 1 && p.b_b1 == 0 && p.a_b1 == p.m * p.a_r && p.c_b1 == p.m * p.c_r && p.a_r != 0 && p.c_r != 0 &&
+      (p.b0 == 1)) {
+    p.m *= p.b1; p.b1 = 1; p.a_b1 = p.c_b1 = 0;
+  }
+}
+
+int run_gemm(const GemmProblem& p0, cudaStream_t stream) {
+  if (p0.m == 0 || p0.n == 0 || p0.b0 == 0 || p0.b1 == 0) return B200_OK;
+  if (!device_state()) return note_cuda_error(cudaErrorInitializationError, "b200_init not called on this device");
+  GemmProblem p = p0;
+  fold_batch(p);
+  const int path = g_path.load();
+  if (path == B200_PATH_SIMT || p.dtype == B200_F64 || p.k == 0) return launch_gemm_simt(p, stream);
+  if (path == B200_PATH_TENSOR) return launch_gemm_tc(p, stream);
+  // AUTO: tensor cores unless the problem is tiny (exact-FP32 SIMT keeps the reference's 1e-6
+  // absolute tolerance on its small known-answer tests) or not TMA-addressable.
+  const double work = (double)p.m * (double)p.n * (double)p.k * (double)p.red * (double)p.b0 * (double)p.b1;
+  if (work >= 262144.0 && p.m >= 8 && p.n >= 8 && p.k >= 8 && tc_eligible(p)) {
+    const int rc = launch_gemm_tc(p, stream);
+    if (rc != B200_ERR_UNSUPPORTED) return rc;
+  }
+  return launch_gemm_simt(p, stream);
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+// ------------------------------------------------------------------------------------------------
+extern "C" {
+
+int b200_init(int ordinal) {
+  if (ordinal < 0 || ordinal >= MAX_DEVICES) return B200_ERR_SHAPE;
+  int rc = note_cuda_error(cudaSetDevice(ordinal), "cudaSetDevice");
+  if (rc) return rc;
+  std::lock_guard<std::mutex> lock(g_dev_mutex);
+  DeviceState& d = g_dev[ordinal];
+  if (d.ready) return B200_OK;
+  cudaDeviceProp prop;
+  if ((rc = note_cuda_error(cudaGetDeviceProperties(&prop, ordinal), "cudaGetDeviceProperties"))) return rc;
+  if (prop.major != 10) {
+    snprintf(t_cuda_err, sizeof(t_cuda_err), "device %d is sm_%d%d; this library contains sm_100a code only",
+             ordinal, prop.major, prop.minor);
+    return B200_ERR_UNSUPPORTED;
+  }
+  d.sm_count = prop.multiProcessorCount;
+  if ((rc = note_cuda_error(cudaMalloc(&d.status, sizeof(int)), "cudaMalloc(status)"))) return rc;
+  if ((rc = note_cuda_error(cudaMemset(d.status, 0, sizeof(int)), "cudaMemset(status)"))) return rc;
+  if ((rc = tc_setup_device())) return rc;
+  d.ready = true;
+  return B200_OK;
+}
+
+const char* b200_strerror(int status) {
+  switch (status) {
+    case B200_OK: return "ok";
+    case B200_ERR_SHAPE: return "shape mismatch";
+    case B200_ERR_STRIDE: return "illegal strides (at least a single stride must be 1; output/batch stride must be non-zero)";
+    case B200_ERR_DTYPE: return "unknown dtype";
+    case B200_ERR_NULL: return "null pointer";
+    case B200_ERR_WORKSPACE: return "workspace too small";
+    case B200_ERR_CUDA: return "CUDA error (see b200_last_cuda_error)";
+    case B200_ERR_DEVICE_TIMEOUT: return "a bounded device-side wait expired";
+    case B200_ERR_UNSUPPORTED: return "unsupported on the requested path";
+    case B200_ERR_NOT_CONTIGUOUS: return "image & filter inputs to conv2d must be contiguous";
+    case B200_ERR_LIMIT: return "request exceeds a fixed capacity";
+    default: return "unknown status";
+  }
+}
+
+const char* b200_last_cuda_error(void) { return t_cuda_err; }
+
+int b200_device_status(void* stream) {
+  DeviceState* d = device_state();
+  if (!d) return B200_ERR_CUDA;
+  int rc = note_cuda_error(cudaStreamSynchronize((cudaStream_t)stream), "cudaStreamSynchronize");
+  if (rc) return rc;
+  int v = 0;
+  if ((rc = note_cuda_error(cudaMemcpy(&v, d->status, sizeof(int), cudaMemcpyDeviceToHost), "cudaMemcpy(status)"))) return rc;
+  if (v) cudaMemset(d->status, 0, sizeof(int));
+  return v;
+}
+
+int b200_set_path(int path) {
+  if (path < B200_PATH_AUTO || path > B200_PATH_TENSOR) return B200_ERR_UNSUPPORTED;
+  g_path.store(path);
+  return B200_OK;
+}
+
+/* Testing hook: 0 = split f32 into tf32_rn(big) + small (default), 1 = rely on the tensor core
+ * truncating raw f32 operands and only write the small copy. */
+int b200_set_tf32_split_mode(int mode) {
+  if (mode != 0 && mode != 1) return B200_ERR_UNSUPPORTED;
+  tc_set_xform_mode(mode);
+  return B200_OK;
+}
+
+uint64_t b200_launch_count(void) { return g_launches.load(); }
+uint64_t b200_tensor_launch_count(void) { return g_tc_launches.load(); }
+
+// ---- Cuda::gemm / Cuda::gemm_batch ---------------------------------------------------------------
+int b200_gemm(int dtype, size_t m, size_t k, size_t n, const void* lhs, const size_t ls[2], const void* rhs,
+              const size_t rs[2], double beta, void* out, const size_t os[2], void* stream) {
+  if (!valid_dtype(dtype)) return B200_ERR_DTYPE;
+  if (!ls || !rs || !os) return B200_ERR_NULL;
+  if (m && n && (!out || (k && (!lhs || !rhs)))) return B200_ERR_NULL;
+  if (!matrix_strides_ok(ls) || !matrix_strides_ok(rs) || !matrix_strides_ok(os)) return B200_ERR_STRIDE;
+  if (beta != 0.0 && beta != 1.0) return B200_ERR_UNSUPPORTED;
+  GemmProblem p;
+  p.dtype = dtype; p.beta = beta != 0.0; p.m = m; p.k = k; p.n = n;
+  p.a = lhs; p.a_r = ls[0]; p.a_c = ls[1];
+  p.b = rhs; p.b_r = rs[0]; p.b_c = rs[1];
+  p.c = out; p.c_r = os[0]; p.c_c = os[1];
+  return run_gemm(p, (cudaStream_t)stream);
+}
+
+int b200_gemm_batch(int dtype, size_t batch, size_t m, size_t k, size_t n, const void* lhs, const size_t ls[3],
+                    const void* rhs, const size_t rs[3], double beta, void* out, const size_t os[3], void* stream) {
+  if (!valid_dtype(dtype)) return B200_ERR_DTYPE;
+  if (!ls || !rs || !os) return B200_ERR_NULL;
+  if (batch && m && n && (!out || (k && (!lhs || !rhs)))) return B200_ERR_NULL;
+  if (os[0] == 0) return B200_ERR_STRIDE;  // assert_ne!(out_strides[0], 0), cuda_kernel.rs:208
+  if (!matrix_strides_ok(ls + 1) || !matrix_strides_ok(rs + 1) || !matrix_strides_ok(os + 1)) return B200_ERR_STRIDE;
+  if (beta != 0.0 && beta != 1.0) return B200_ERR_UNSUPPORTED;
+  GemmProblem p;
+  p.dtype = dtype; p.beta = beta != 0.0; p.b1 = batch; p.m = m; p.k = k; p.n = n;
+  p.a = lhs; p.a_b1 = ls[0]; p.a_r = ls[1]; p.a_c = ls[2];
+  p.b = rhs; p.b_b1 = rs[0]; p.b_r = rs[1]; p.b_c = rs[2];
+  p.c = out; p.c_b1 = os[0]; p.c_r = os[1]; p.c_c = os[2];
+  return run_gemm(p, (cudaStream_t)stream);
+}
+
+// ---- MatMatKernel (cuda_kernel.rs:244-312) -------------------------------------------------------
+int b200_matmat_forward(int dtype, size_t m, size_t k, size_t n, const void* lhs, const size_t ls[2],
+                        const void* rhs, const size_t rs[2], void* out, void* stream) {
+  const size_t os[2] = {n, 1};
+  return b200_gemm(dtype, m, k, n, lhs, ls, rhs, rs, 0.0, out, os, stream);
+}
+
+int b200_matmat_backward(int dtype, size_t m, size_t k, size_t n, const void* lhs, const size_t ls[2],
+                         void* grad_lhs, const void* rhs, const size_t rs[2], void* grad_rhs,
+                         const void* grad_out, void* stream, void* par_stream) {
+  (void)par_stream;
+  if (!ls || !rs) return B200_ERR_NULL;
+  const size_t os[2] = {n, 1};
+  int rc = B200_OK;
+  if (grad_lhs) {  // grad_lhs += grad_out * rhs^T
+    const size_t rs_t[2] = {rs[1], rs[0]};
+    if ((rc = b200_gemm(dtype, m, n, k, grad_out, os, rhs, rs_t, 1.0, grad_lhs, ls, stream))) return rc;
+  }
+  if (grad_rhs) {  // grad_rhs += lhs^T * grad_out
+    const size_t ls_t[2] = {ls[1], ls[0]};
+    rc = b200_gemm(dtype, k, m, n, lhs, ls_t, grad_out, os, 1.0, grad_rhs, rs, stream);
+  }
+  return rc;
+}
+
+// ---- MatMatBrKernel (cuda_kernel.rs:319-388) -----------------------------------------------------
+int b200_matmat_br_forward(int dtype, size_t batch, size_t m, size_t k, size_t n, const void* lhs,
+                           const size_t ls[3], const void* rhs, const size_t rs[2], void* out, void* stream) {
+  if (!ls || !rs) return B200_ERR_NULL;
+  const size_t rs3[3] = {0, rs[0], rs[1]};
+  const size_t os[3] = {m * n, n, 1};
+  return b200_gemm_batch(dtype, batch, m, k, n, lhs, ls, rhs, rs3, 0.0, out, os, stream);
+}
+
+int b200_matmat_br_backward(int dtype, size_t batch, size_t m, size_t k, size_t n, const void* lhs,
+                            const size_t ls[3], void* grad_lhs, const void* rhs, const size_t rs[2],
+                            void* grad_rhs, const void* grad_out, void* stream, void* par_stream) {
+  (void)par_stream;
+  if (!valid_dtype(dtype)) return B200_ERR_DTYPE;
+  if (!ls || !rs) return B200_ERR_NULL;
+  if (!matrix_strides_ok(ls + 1) || !matrix_strides_ok(rs)) return B200_ERR_STRIDE;
+  int rc = B200_OK;
+  if (grad_rhs && batch && k && n) {
+    // grad_rhs += sum_b lhs_b^T * grad_out_b : one launch, the batch is an outer reduction index.
+    if (!lhs || !grad_out) return B200_ERR_NULL;
+    GemmProblem p;
+    p.dtype = dtype; p.beta = 1; p.red = batch; p.m = k; p.k = m; p.n = n;
+    p.a = lhs; p.a_red = ls[0]; p.a_r = ls[2]; p.a_c = ls[1];
+    p.b = grad_out; p.b_red = m * n; p.b_r = n; p.b_c = 1;
+    p.c = grad_rhs; p.c_r = rs[0]; p.c_c = rs[1];
+    if ((rc = run_gemm(p, (cudaStream_t)stream))) return rc;
+  }
+  if (grad_lhs) {  // grad_lhs += grad_out * rhs^T, rhs broadcast over the batch
+    const size_t os[3] = {m * n, n, 1};
+    const size_t rs_t[3] = {0, rs[1], rs[0]};
+    rc = b200_gemm_batch(dtype, batch, m, n, k, grad_out, os, rhs, rs_t, 1.0, grad_lhs, ls, stream);
+  }
+  return rc;
+}
+
+// ---- MatMatBatch3Kernel (cuda_kernel.rs:395-462) -------------------------------------------------
+int b200_matmat_batch3_forward(int dtype, size_t batch, size_t m, size_t k, size_t n, const void* lhs,
+                               const size_t ls[3], const void* rhs, const size_t rs[3], void* out, void* stream) {
+  if (!ls || !rs) return B200_ERR_NULL;
+  if (ls[0] == 0 || rs[0] == 0) return B200_ERR_STRIDE;  // assert_ne!, cuda_kernel.rs:400-401
+  const size_t os[3] = {m * n, n, 1};
+  return b200_gemm_batch(dtype, batch, m, k, n, lhs, ls, rhs, rs, 0.0, out, os, stream);
+}
+
+int b200_matmat_batch3_backward(int dtype, size_t batch, size_t m, size_t k, size_t n, const void* lhs,
+                                const size_t ls[3], void* grad_lhs, const void* rhs, const size_t rs[3],
+                                void* grad_rhs, const void* grad_out, void* stream, void* par_stream) {
+  (void)par_stream;
+  if (!ls || !rs) return B200_ERR_NULL;
+  const size_t os[3] = {m * n, n, 1};
+  int rc = B200_OK;
+  if (grad_lhs) {
+    const size_t rs_t[3] = {rs[0], rs[2], rs[1]};
+    if ((rc = b200_gemm_batch(dtype, batch, m, n, k, grad_out, os, rhs, rs_t, 1.0, grad_lhs, ls, stream))) return rc;
+  }
+  if (grad_rhs) {
+    const size_t ls_t[3] = {ls[0], ls[2], ls[1]};
+    rc = b200_gemm_batch(dtype, batch, k, m, n, lhs, ls_t, grad_out, os, 1.0, grad_rhs, rs, stream);
+  }
+  return rc;
+}
+
+// ---- MatMatBatch4Kernel (cuda_kernel.rs:469-568) -------------------------------------------------
+static int gemm_batch2(int dtype, size_t b0, size_t b1, size_t m, size_t k, size_t n, const void* lhs,
+                       const size_t ls[4], const void* rhs, const size_t rs[4], int beta, void* out,
+                       const size_t os[4], void* stream) {
+  if (!valid_dtype(dtype)) return B200_ERR_DTYPE;
+  if (b0 && b1 && m && n && (!out || (k && (!lhs || !rhs)))) return B200_ERR_NULL;
+  if (!matrix_strides_ok(ls + 2) || !matrix_strides_ok(rs + 2) || !matrix_strides_ok(os + 2)) return B200_ERR_STRIDE;
+  if (os[0] == 0 || os[1] == 0) return B200_ERR_STRIDE;
+  GemmProblem p;
+  p.dtype = dtype; p.beta = beta; p.b0 = b0; p.b1 = b1; p.m = m; p.k = k; p.n = n;
+  p.a = lhs; p.a_b0 = ls[0]; p.a_b1 = ls[1]; p.a_r = ls[2]; p.a_c = ls[3];
+  p.b = rhs; p.b_b0 = rs[0]; p.b_b1 = rs[1]; p.b_r = rs[2]; p.b_c = rs[3];
+  p.c = out; p.c_b0 = os[0]; p.c_b1 = os[1]; p.c_r = os[2]; p.c_c = os[3];
+  return run_gemm(p, (cudaStream_t)stream);
+}
+
+int b200_matmat_batch4_forward(int dtype, size_t batch, size_t seq, size_t m, size_t k, size_t n,
+                               const void* lhs, const size_t ls[4], const void* rhs, const size_t rs[4],
+                               void* out, void* stream) {
+  if (!ls || !rs) return B200_ERR_NULL;
+  if (ls[0] == 0 || rs[0] == 0 || ls[1] == 0 || rs[1] == 0) return B200_ERR_STRIDE;  // cuda_kernel.rs:474-477
+  const size_t os[4] = {seq * m * n, m * n, n, 1};
+  return gemm_batch2(dtype, batch, seq, m, k, n, lhs, ls, rhs, rs, 0, out, os, stream);
+}
+
+int b200_matmat_batch4_backward(int dtype, size_t batch, size_t seq, size_t m, size_t k, size_t n,
+                                const void* lhs, const size_t ls[4], void* grad_lhs, const void* rhs,
+                                const size_t rs[4], void* grad_rhs, const void* grad_out, void* stream,
+                                void* par_stream) {
+  (void)par_stream;
+  if (!ls || !rs) return B200_ERR_NULL;
+  const size_t os[4] = {seq * m * n, m * n, n, 1};
+  int rc = B200_OK;
+  if (grad_lhs) {
+    const size_t rs_t[4] = {rs[0], rs[1], rs[3], rs[2]};
+    if ((rc = gemm_batch2(dtype, batch, seq, m, n, k, grad_out, os, rhs, rs_t, 1, grad_lhs, ls, stream))) return rc;
+  }
+  if (grad_rhs) {
+    const size_t ls_t[4] = {ls[0], ls[1], ls[3], ls[2]};
+    rc = gemm_batch2(dtype, batch, seq, k, m, n, lhs, ls_t, grad_out, os, 1, grad_rhs, rs, stream);
+  }
+  return rc;
+}
+
+// ---- conv2d ---------------------------------------------------------------------------------------
+static int check_conv_op(const b200_conv2d_op* op) {
+  if (!op) return B200_ERR_NULL;
+  if (!op->groups || !op->stride || !op->dilation || !op->kernel) return B200_ERR_SHAPE;
+  if (op->chan_in % op->groups || op->chan_out % op->groups) return B200_ERR_SHAPE;  // conv2d/mod.rs:281-286
+  return B200_OK;
+}
+
+size_t b200_conv2d_workspace_bytes(int dtype, const b200_conv2d_op* op, int backward) {
+  if (check_conv_op(op) || !valid_dtype(dtype)) return 0;
+  return conv2d_workspace_bytes(dtype, op, backward);
+}
+
+int b200_conv2d_forward(int dtype, const b200_conv2d_op* op, const void* img, const size_t img_strides[4],
+                        const void* filters, void* out, void* workspace, size_t workspace_bytes, void* stream) {
+  if (!valid_dtype(dtype)) return B200_ERR_DTYPE;
+  int rc = check_conv_op(op);
+  if (rc) return rc;
+  if (!img_strides) return B200_ERR_NULL;
+  const size_t need = conv2d_workspace_bytes(dtype, op, 0);
+  if (need == 0) return B200_OK;
+  if (!img || !filters || !out || !workspace) return B200_ERR_NULL;
+  if (workspace_bytes < need) return B200_ERR_WORKSPACE;
+  if (!device_state()) return note_cuda_error(cudaErrorInitializationError, "b200_init not called on this device");
+  return conv2d_forward(dtype, op, img, img_strides, filters, out, workspace, (cudaStream_t)stream);
+}
+
+int b200_conv2d_backward(int dtype, const b200_conv2d_op* op, const void* img, void* grad_img,
+                         const void* filters, const size_t filters_strides[4], void* grad_filters,
+                         const void* grad_out, void* workspace, size_t workspace_bytes, void* stream,
+                         void* par_stream) {
+  (void)par_stream;
+  if (!valid_dtype(dtype)) return B200_ERR_DTYPE;
+  int rc = check_conv_op(op);
+  if (rc) return rc;
+  if (!filters_strides) return B200_ERR_NULL;
+  const size_t need = conv2d_workspace_bytes(dtype, op, 1);
+  if (need == 0) return B200_OK;
+  if (!img || !filters || !grad_out || !workspace) return B200_ERR_NULL;
+  if (workspace_bytes < need) return B200_ERR_WORKSPACE;
+  if (!device_state()) return note_cuda_error(cudaErrorInitializationError, "b200_init not called on this device");
+  return conv2d_backward(dtype, op, img, grad_img, filters, filters_strides, grad_filters, grad_out, workspace,
+                         (cudaStream_t)stream);
+}
+
+}  // extern "C"

@@ -1,0 +1,59 @@
+// Shared definitions of the dfdx_b200 library: the canonical GEMM problem every entry point is
+// lowered to, status codes, and small helpers.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_fp16.h>
+#include <stdint.h>
+#include <stddef.h>
+#include "../../include/dfdx_b200.h"
+
+namespace b200 {
+
+// One (possibly batched, possibly batch-reduced) strided GEMM in row-major index terms:
+//   for (b0,b1) in batch:  C[b0,b1][i,j] = beta*C + sum_{r<red} sum_{p<k} A[b0,b1,r][i,p] * B[b0,b1,r][p,j]
+// Strides are in elements.  `red` > 1 is how the broadcast-rhs weight gradient
+// (matmul/cuda_kernel.rs:358-371 in dfdx: B serial beta=1 GEMMs) becomes a single launch.
+struct GemmProblem {
+  int dtype = B200_F32;
+  int beta = 0;
+  int64_t b0 = 1, b1 = 1, red = 1;
+  int64_t m = 0, k = 0, n = 0;
+  const void* a = nullptr;
+  int64_t a_b0 = 0, a_b1 = 0, a_red = 0, a_r = 0, a_c = 0;
+  const void* b = nullptr;
+  int64_t b_b0 = 0, b_b1 = 0, b_red = 0, b_r = 0, b_c = 0;
+  void* c = nullptr;
+  int64_t c_b0 = 0, c_b1 = 0, c_r = 0, c_c = 0;
+};
+
+static inline size_t dtype_size(int dtype) {
+  switch (dtype) {
+    case B200_F32: return 4;
+    case B200_F64: return 8;
+    case B200_F16:
+    case B200_AMP_F16: return 2;
+    default: return 0;
+  }
+}
+
+// Per-device state created by b200_init.
+struct DeviceState {
+  bool ready = false;
+  int sm_count = 0;
+  int* status = nullptr;  // device word: 0 or a B200_ERR_* written by a kernel that gave up on a wait
+};
+
+DeviceState* device_state();                 // state of the current device (nullptr before init)
+int note_cuda_error(cudaError_t e, const char* where);
+void count_launch(bool tensor);
+
+int launch_gemm_simt(const GemmProblem& p, cudaStream_t stream);
+// Returns B200_ERR_UNSUPPORTED (without launching) when the operands are not TMA-addressable.
+int launch_gemm_tc(const GemmProblem& p, cudaStream_t stream);
+bool tc_eligible(const GemmProblem& p);
+int tc_setup_device();                       // cudaFuncSetAttribute for every tensor-core kernel
+
+// Lowers one problem to a kernel family according to b200_set_path and eligibility.
+int run_gemm(const GemmProblem& p, cudaStream_t stream);
+
+}  // namespace b200

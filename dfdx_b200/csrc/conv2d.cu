@@ -1,0 +1,239 @@
+// conv2d lowered to unfold + GEMM: `Conv2DKernel for Cuda` of dfdx
+// (dfdx-core/src/tensor_ops/conv2d/cuda_kernel.rs:80-281) on top of this library's GEMM kernels.
+//
+// Workspace layout (caller-provided, see b200_conv2d_workspace_bytes):
+//   forward : patches (B, C, K, K, OH, OW)
+//   backward: patches (B, O, K, K, H, W) | filters_tr (G, C/G, O/G, K, K) | grad_filters_tr (B, G, C/G, O/G, K, K)
+// each region starts on a 256-byte boundary so the GEMM operands stay TMA-addressable.
+#include "common.cuh"
+
+namespace b200 {
+namespace {
+
+constexpr int NT = 256;
+
+struct Op {
+  int64_t kernel, stride, padding, dilation, groups, batch, chan_in, chan_out, h_in, h_out, w_in, w_out;
+};
+
+Op to_op(const b200_conv2d_op* o) {
+  Op r;
+  r.kernel = (int64_t)o->kernel; r.stride = (int64_t)o->stride; r.padding = (int64_t)o->padding;
+  r.dilation = (int64_t)o->dilation; r.groups = (int64_t)o->groups; r.batch = (int64_t)o->batch;
+  r.chan_in = (int64_t)o->chan_in; r.chan_out = (int64_t)o->chan_out; r.h_in = (int64_t)o->h_in;
+  r.h_out = (int64_t)o->h_out; r.w_in = (int64_t)o->w_in; r.w_out = (int64_t)o->w_out;
+  return r;
+}
+
+struct Strides4 { int64_t s[4]; };
+
+// im2col.  One thread per element of patches (b, c, k1, k2, oh, ow); consecutive threads walk ow, so
+// both the gather from the image row and the store are coalesced.  Zero where the tap falls in
+// the padding (conv2d.cu:18-52 of dfdx computes the same values, one thread per (b,c,oh,ow)).
+template <typename T>
+__global__ void __launch_bounds__(NT) unfold_input_kernel(const Op op, const T* __restrict__ img,
+                                                          const Strides4 st, T* __restrict__ patches,
+                                                          const int64_t total) {
+  for (int64_t i = (int64_t)blockIdx.x * NT + threadIdx.x; i < total; i += (int64_t)gridDim.x * NT) {
+    int64_t idx = i;
+    const int64_t ow = idx % op.w_out; idx /= op.w_out;
+    const int64_t oh = idx % op.h_out; idx /= op.h_out;
+    const int64_t k2 = idx % op.kernel; idx /= op.kernel;
+    const int64_t k1 = idx % op.kernel; idx /= op.kernel;
+    const int64_t c = idx % op.chan_in;
+    const int64_t b = idx / op.chan_in;
+    const int64_t y = oh * op.stride + op.dilation * k1 - op.padding;
+    const int64_t x = ow * op.stride + op.dilation * k2 - op.padding;
+    T v = T(0.0f);
+    if (y >= 0 && y < op.h_in && x >= 0 && x < op.w_in)
+      v = img[b * st.s[0] + c * st.s[1] + y * st.s[2] + x * st.s[3]];
+    patches[i] = v;
+  }
+}
+
+// Transposed-convolution gather: patches (b, o, k1, k2, y, x) = grad_out[b, o, oh, ow] where
+// (oh, ow) is the output pixel that input pixel (y, x) feeds through tap (k1, k2), if any
+// (conv2d.cu:54-94; conv2d/cpu_kernel.rs:9-40 `unfold_idx`).
+template <typename T>
+__global__ void __launch_bounds__(NT) unfold_output_kernel(const Op op, const T* __restrict__ gout,
+                                                           T* __restrict__ patches, const int64_t total) {
+  for (int64_t i = (int64_t)blockIdx.x * NT + threadIdx.x; i < total; i += (int64_t)gridDim.x * NT) {
+    int64_t idx = i;
+    const int64_t x = idx % op.w_in; idx /= op.w_in;
+    const int64_t y = idx % op.h_in; idx /= op.h_in;
+    const int64_t k2 = idx % op.kernel; idx /= op.kernel;
+    const int64_t k1 = idx % op.kernel; idx /= op.kernel;
+    const int64_t o = idx % op.chan_out;
+    const int64_t b = idx / op.chan_out;
+    T v = T(0.0f);
+    const int64_t ohs = y + op.padding - op.dilation * k1;
+    const int64_t ows = x + op.padding - op.dilation * k2;
+    if (ohs >= 0 && ows >= 0 && ohs % op.stride == 0 && ows % op.stride == 0) {
+      const int64_t oh = ohs / op.stride, ow = ows / op.stride;
+      if (oh < op.h_out && ow < op.w_out)
+        v = gout[((b * op.chan_out + o) * op.h_out + oh) * op.w_out + ow];
+    }
+    patches[i] = v;
+  }
+}
+
+// filters (O, C/G, K, K) through strides  ->  filters_tr (G, C/G, O/G, K, K) contiguous (conv2d.cu:96-127).
+template <typename T>
+__global__ void __launch_bounds__(NT) transpose_filters_kernel(const Op op, const T* __restrict__ f,
+                                                               const Strides4 st, T* __restrict__ ftr,
+                                                               const int64_t total) {
+  const int64_t cg = op.chan_in / op.groups, og = op.chan_out / op.groups;
+  for (int64_t i = (int64_t)blockIdx.x * NT + threadIdx.x; i < total; i += (int64_t)gridDim.x * NT) {
+    int64_t idx = i;
+    const int64_t k2 = idx % op.kernel; idx /= op.kernel;
+    const int64_t k1 = idx % op.kernel; idx /= op.kernel;
+    const int64_t o = idx % og; idx /= og;
+    const int64_t c = idx % cg;
+    const int64_t g = idx / cg;
+    ftr[i] = f[(g * og + o) * st.s[0] + c * st.s[1] + k1 * st.s[2] + k2 * st.s[3]];
+  }
+}
+
+// grad_filters[o, c, k1, k2] (through strides) += sum_b grad_filters_tr[b, g, c, o, k1, k2]
+// (conv2d.cu:129-168).  The sum runs in f32 (f64 for double) in batch order.
+template <typename T, typename A>
+__global__ void __launch_bounds__(NT) sum_transposed_filters_kernel(const Op op, const T* __restrict__ gftr,
+                                                                    T* __restrict__ gf, const Strides4 st,
+                                                                    const int64_t total) {
+  const int64_t cg = op.chan_in / op.groups, og = op.chan_out / op.groups;
+  for (int64_t i = (int64_t)blockIdx.x * NT + threadIdx.x; i < total; i += (int64_t)gridDim.x * NT) {
+    int64_t idx = i;
+    const int64_t k2 = idx % op.kernel; idx /= op.kernel;
+    const int64_t k1 = idx % op.kernel; idx /= op.kernel;
+    const int64_t o = idx % og; idx /= og;
+    const int64_t c = idx % cg;
+    const int64_t g = idx / cg;
+    A acc = A(0);
+    for (int64_t b = 0; b < op.batch; ++b) acc += (A)gftr[b * total + i];
+    T* dst = gf + (g * og + o) * st.s[0] + c * st.s[1] + k1 * st.s[2] + k2 * st.s[3];
+    *dst = (T)((A)*dst + acc);
+  }
+}
+
+unsigned grid_for(int64_t total, int sms) {
+  int64_t blocks = (total + NT - 1) / NT;
+  const int64_t cap = (int64_t)sms * 16;
+  if (blocks > cap) blocks = cap;
+  return (unsigned)(blocks < 1 ? 1 : blocks);
+}
+
+size_t align256(size_t x) { return (x + 255) & ~(size_t)255; }
+
+template <typename T, typename A>
+int forward_t(int dtype, const Op& op, const T* img, const size_t is[4], const T* filters, T* out,
+              void* ws, cudaStream_t stream) {
+  DeviceState* ds = device_state();
+  const int sms = ds ? ds->sm_count : 148;
+  T* patches = (T*)ws;
+  const int64_t total = op.batch * op.chan_in * op.kernel * op.kernel * op.h_out * op.w_out;
+  if (total == 0) return B200_OK;
+  Strides4 st{{(int64_t)is[0], (int64_t)is[1], (int64_t)is[2], (int64_t)is[3]}};
+  unfold_input_kernel<T><<<grid_for(total, sms), NT, 0, stream>>>(op, img, st, patches, total);
+  count_launch(false);
+  int rc = note_cuda_error(cudaGetLastError(), "unfold_input launch");
+  if (rc) return rc;
+
+  // filters (G, O/G, C/G*K*K) x patches (B, G, C/G*K*K, OH*OW) -> out (B, G, O/G, OH*OW)
+  const int64_t m = op.chan_out / op.groups, k = (op.chan_in / op.groups) * op.kernel * op.kernel,
+                n = op.h_out * op.w_out, G = op.groups;
+  GemmProblem p;
+  p.dtype = dtype; p.beta = 0; p.b0 = op.batch; p.b1 = G; p.m = m; p.k = k; p.n = n;
+  p.a = filters; p.a_b0 = 0; p.a_b1 = m * k; p.a_r = k; p.a_c = 1;
+  p.b = patches; p.b_b0 = G * k * n; p.b_b1 = k * n; p.b_r = n; p.b_c = 1;
+  p.c = out; p.c_b0 = G * m * n; p.c_b1 = m * n; p.c_r = n; p.c_c = 1;
+  return run_gemm(p, stream);
+}
+
+template <typename T, typename A>
+int backward_t(int dtype, const Op& op, const T* img, T* grad_img, const T* filters, const size_t fs[4],
+               T* grad_filters, const T* grad_out, void* ws, cudaStream_t stream) {
+  DeviceState* ds = device_state();
+  const int sms = ds ? ds->sm_count : 148;
+  const int64_t G = op.groups, cg = op.chan_in / G, og = op.chan_out / G, KK = op.kernel * op.kernel;
+  const int64_t hw = op.h_in * op.w_in;
+  const int64_t n_patches = op.batch * op.chan_out * KK * hw;
+  const int64_t n_filters = G * cg * og * KK;
+  if (n_patches == 0 || n_filters == 0) return B200_OK;
+  uint8_t* base = (uint8_t*)ws;
+  T* patches = (T*)base;
+  T* ftr = (T*)(base + align256((size_t)n_patches * sizeof(T)));
+  T* gftr = (T*)((uint8_t*)ftr + align256((size_t)n_filters * sizeof(T)));
+  Strides4 st{{(int64_t)fs[0], (int64_t)fs[1], (int64_t)fs[2], (int64_t)fs[3]}};
+  int rc;
+
+  unfold_output_kernel<T><<<grid_for(n_patches, sms), NT, 0, stream>>>(op, grad_out, patches, n_patches);
+  count_launch(false);
+  if ((rc = note_cuda_error(cudaGetLastError(), "unfold_output launch"))) return rc;
+
+  if (grad_img) {
+    transpose_filters_kernel<T><<<grid_for(n_filters, sms), NT, 0, stream>>>(op, filters, st, ftr, n_filters);
+    count_launch(false);
+    if ((rc = note_cuda_error(cudaGetLastError(), "transpose_filters launch"))) return rc;
+    // grad_img (B, G, C/G, H*W) += filters_tr (G, C/G, O/G*K*K) x patches (B, G, O/G*K*K, H*W)
+    const int64_t m = cg, k = og * KK, n = hw;
+    GemmProblem p;
+    p.dtype = dtype; p.beta = 1; p.b0 = op.batch; p.b1 = G; p.m = m; p.k = k; p.n = n;
+    p.a = ftr; p.a_b0 = 0; p.a_b1 = m * k; p.a_r = k; p.a_c = 1;
+    p.b = patches; p.b_b0 = G * k * n; p.b_b1 = k * n; p.b_r = n; p.b_c = 1;
+    p.c = grad_img; p.c_b0 = G * m * n; p.c_b1 = m * n; p.c_r = n; p.c_c = 1;
+    if ((rc = run_gemm(p, stream))) return rc;
+  }
+  if (grad_filters) {
+    // grad_filters_tr (B, G, C/G, O/G*K*K) = img (B, G, C/G, H*W) x patches^T (B, G, H*W, O/G*K*K)
+    const int64_t m = cg, k = hw, n = og * KK;
+    GemmProblem p;
+    p.dtype = dtype; p.beta = 0; p.b0 = op.batch; p.b1 = G; p.m = m; p.k = k; p.n = n;
+    p.a = img; p.a_b0 = G * m * k; p.a_b1 = m * k; p.a_r = k; p.a_c = 1;
+    p.b = patches; p.b_b0 = G * k * n; p.b_b1 = k * n; p.b_r = 1; p.b_c = k;
+    p.c = gftr; p.c_b0 = G * m * n; p.c_b1 = m * n; p.c_r = n; p.c_c = 1;
+    if ((rc = run_gemm(p, stream))) return rc;
+    sum_transposed_filters_kernel<T, A><<<grid_for(n_filters, sms), NT, 0, stream>>>(op, gftr, grad_filters, st,
+                                                                                      n_filters);
+    count_launch(false);
+    if ((rc = note_cuda_error(cudaGetLastError(), "sum_transposed_filters launch"))) return rc;
+  }
+  return B200_OK;
+}
+
+}  // namespace
+
+size_t conv2d_workspace_bytes(int dtype, const b200_conv2d_op* o, int backward) {
+  const size_t es = dtype_size(dtype);
+  if (!es || !o || !o->groups) return 0;
+  const size_t KK = o->kernel * o->kernel;
+  if (!backward) return align256(o->batch * o->chan_in * KK * o->h_out * o->w_out * es);
+  const size_t nf = o->groups * (o->chan_in / o->groups) * (o->chan_out / o->groups) * KK;
+  return align256(o->batch * o->chan_out * KK * o->h_in * o->w_in * es) + align256(nf * es) +
+         align256(o->batch * nf * es);
+}
+
+int conv2d_forward(int dtype, const b200_conv2d_op* o, const void* img, const size_t is[4], const void* filters,
+                   void* out, void* ws, cudaStream_t stream) {
+  const Op op = to_op(o);
+  switch (dtype) {
+    case B200_F32: return forward_t<float, float>(dtype, op, (const float*)img, is, (const float*)filters, (float*)out, ws, stream);
+    case B200_F64: return forward_t<double, double>(dtype, op, (const double*)img, is, (const double*)filters, (double*)out, ws, stream);
+    case B200_F16:
+    case B200_AMP_F16: return forward_t<__half, float>(dtype, op, (const __half*)img, is, (const __half*)filters, (__half*)out, ws, stream);
+    default: return B200_ERR_DTYPE;
+  }
+}
+
+int conv2d_backward(int dtype, const b200_conv2d_op* o, const void* img, void* grad_img, const void* filters,
+                    const size_t fs[4], void* grad_filters, const void* grad_out, void* ws, cudaStream_t stream) {
+  const Op op = to_op(o);
+  switch (dtype) {
+    case B200_F32: return backward_t<float, float>(dtype, op, (const float*)img, (float*)grad_img, (const float*)filters, fs, (float*)grad_filters, (const float*)grad_out, ws, stream);
+    case B200_F64: return backward_t<double, double>(dtype, op, (const double*)img, (double*)grad_img, (const double*)filters, fs, (double*)grad_filters, (const double*)grad_out, ws, stream);
+    case B200_F16:
+    case B200_AMP_F16: return backward_t<__half, float>(dtype, op, (const __half*)img, (__half*)grad_img, (const __half*)filters, fs, (__half*)grad_filters, (const __half*)grad_out, ws, stream);
+    default: return B200_ERR_DTYPE;
+  }
+}
+
+}  // namespace b200

@@ -1,0 +1,264 @@
+"""Host-side mirror of dfdx's `Cuda` device for the matmul / conv2d path.
+
+The names follow the reference (dfdx v0.13.0): `Cuda.gemm` / `Cuda.gemm_batch`
+(dfdx-core/src/tensor_ops/matmul/cuda_kernel.rs:153-237), the four kernel traits
+`MatMatKernel`, `MatMatBrKernel`, `MatMatBatch3Kernel`, `MatMatBatch4Kernel` (:240-569), the
+rank dispatch of `TryMatMul` (matmul/mod.rs:133-311) and `Conv2DKernel` / `TryConv2D`
+(conv2d/mod.rs:31-53,273-324).  Tensors are torch CUDA tensors used purely as device buffers: the
+element strides of a torch view are exactly dfdx's `Tensor::strides`, so `permute` / `expand` views
+reach the kernels without a copy, like dfdx's zero-copy `permute` / `broadcast`.
+
+Everything computes through the C ABI of libdfdx_b200.so; nothing here calls a torch math op.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+from ._lib import Conv2DOp, check, strides as _st
+
+_DTYPES = {torch.float32: _lib.F32, torch.float64: _lib.F64, torch.float16: _lib.F16}
+
+
+class ShapeMismatch(AssertionError):
+    """Raised where the reference panics with `assertion left == right failed` before any launch."""
+
+
+def _assert_eq(left, right):
+    if left != right:
+        raise ShapeMismatch(f"left: {left}\n right: {right}")
+
+
+def conv2d_out_dim(dim: int, kernel: int, stride: int, padding: int, dilation: int) -> int:
+    """conv2d/mod.rs:143-161."""
+    span = dilation * (kernel - 1) + 1
+    if dim + 2 * padding < span:
+        raise ShapeMismatch("called `Option::unwrap()` on a `None` value")
+    return (dim + 2 * padding - span) // stride + 1
+
+
+class Cuda:
+    """One device ordinal, like `Cuda::try_build(ordinal, seed)` (tensor/cuda/device.rs:72-91)."""
+
+    def __init__(self, ordinal: int = 0, amp: bool = False):
+        self.lib = _lib.load()
+        if not torch.cuda.is_available():
+            raise RuntimeError("dfdx_b200.Cuda needs a CUDA device (there is no CPU fallback)")
+        self.ordinal = ordinal
+        self.device = torch.device("cuda", ordinal)
+        self.amp = amp  # treat float16 as AMP<f16> (same arithmetic here: f32 accumulate either way)
+        torch.cuda.set_device(ordinal)
+        check(self.lib.b200_init(ordinal), "b200_init")
+        self._workspace = None  # grow-only byte workspace (tensor/cuda/device.rs:108-122)
+
+    # -- plumbing ---------------------------------------------------------------------------------
+    def _dtype(self, t: torch.Tensor) -> int:
+        try:
+            d = _DTYPES[t.dtype]
+        except KeyError:
+            raise TypeError(f"unsupported dtype {t.dtype}") from None
+        return _lib.AMP_F16 if (d == _lib.F16 and self.amp) else d
+
+    def _stream(self):
+        return torch.cuda.current_stream(self.device).cuda_stream
+
+    def get_workspace(self, nbytes: int) -> torch.Tensor:
+        if self._workspace is None or self._workspace.numel() < nbytes:
+            self._workspace = torch.empty(max(nbytes, 1), dtype=torch.uint8, device=self.device)
+        return self._workspace
+
+    def set_path(self, path: int) -> None:
+        check(self.lib.b200_set_path(path), "b200_set_path")
+
+    def device_status(self) -> int:
+        return self.lib.b200_device_status(self._stream())
+
+    def synchronize(self) -> None:
+        torch.cuda.synchronize(self.device)
+        check(self.device_status(), "device status")
+
+    def alloc_grad(self, t: torch.Tensor) -> torch.Tensor:
+        """Zeroed gradient buffer with the PHYSICAL length of t's storage
+        (tensor/cuda/device.rs:259-266): a permuted view's gradient lands in the base layout, a
+        broadcast view's gradient accumulates."""
+        n = t.untyped_storage().nbytes() // t.element_size()
+        return torch.zeros(n, dtype=t.dtype, device=t.device)
+
+    @staticmethod
+    def grad_view(grad: torch.Tensor, t: torch.Tensor) -> torch.Tensor:
+        return torch.as_strided(grad, t.shape, t.stride())
+
+    # -- Cuda::gemm / Cuda::gemm_batch --------------------------------------------------------------
+    def gemm(self, mkn, lhs, lhs_strides, rhs, rhs_strides, beta, out, out_strides) -> None:
+        m, k, n = mkn
+        check(self.lib.b200_gemm(self._dtype(out), m, k, n, lhs.data_ptr(), _st(lhs_strides), rhs.data_ptr(),
+                                 _st(rhs_strides), float(beta), out.data_ptr(), _st(out_strides), self._stream()),
+              "b200_gemm")
+
+    def gemm_batch(self, bmkn, lhs, lhs_strides, rhs, rhs_strides, beta, out, out_strides) -> None:
+        b, m, k, n = bmkn
+        check(self.lib.b200_gemm_batch(self._dtype(out), b, m, k, n, lhs.data_ptr(), _st(lhs_strides),
+                                       rhs.data_ptr(), _st(rhs_strides), float(beta), out.data_ptr(),
+                                       _st(out_strides), self._stream()), "b200_gemm_batch")
+
+    # -- kernel traits ------------------------------------------------------------------------------
+    def _empty(self, shape, like):
+        return torch.empty(shape, dtype=like.dtype, device=like.device)  # alloc_empty: uninitialised
+
+    def matmat_forward(self, lhs, rhs):
+        (m, k), n = lhs.shape, rhs.shape[1]
+        out = self._empty((m, n), lhs)
+        check(self.lib.b200_matmat_forward(self._dtype(lhs), m, k, n, lhs.data_ptr(), _st(lhs.stride()),
+                                           rhs.data_ptr(), _st(rhs.stride()), out.data_ptr(), self._stream()),
+              "b200_matmat_forward")
+        return out
+
+    def matmat_backward(self, lhs, grad_lhs, rhs, grad_rhs, grad_out) -> None:
+        (m, k), n = lhs.shape, rhs.shape[1]
+        check(self.lib.b200_matmat_backward(self._dtype(lhs), m, k, n, lhs.data_ptr(), _st(lhs.stride()),
+                                            _ptr(grad_lhs), rhs.data_ptr(), _st(rhs.stride()), _ptr(grad_rhs),
+                                            grad_out.data_ptr(), self._stream(), None), "b200_matmat_backward")
+
+    def matmat_br_forward(self, lhs, rhs):
+        (b, m, k), n = lhs.shape, rhs.shape[1]
+        out = self._empty((b, m, n), lhs)
+        check(self.lib.b200_matmat_br_forward(self._dtype(lhs), b, m, k, n, lhs.data_ptr(), _st(lhs.stride()),
+                                              rhs.data_ptr(), _st(rhs.stride()), out.data_ptr(), self._stream()),
+              "b200_matmat_br_forward")
+        return out
+
+    def matmat_br_backward(self, lhs, grad_lhs, rhs, grad_rhs, grad_out) -> None:
+        (b, m, k), n = lhs.shape, rhs.shape[1]
+        check(self.lib.b200_matmat_br_backward(self._dtype(lhs), b, m, k, n, lhs.data_ptr(), _st(lhs.stride()),
+                                               _ptr(grad_lhs), rhs.data_ptr(), _st(rhs.stride()), _ptr(grad_rhs),
+                                               grad_out.data_ptr(), self._stream(), None),
+              "b200_matmat_br_backward")
+
+    def matmat_batch3_forward(self, lhs, rhs):
+        (b, m, k), n = lhs.shape, rhs.shape[2]
+        out = self._empty((b, m, n), lhs)
+        check(self.lib.b200_matmat_batch3_forward(self._dtype(lhs), b, m, k, n, lhs.data_ptr(),
+                                                  _st(lhs.stride()), rhs.data_ptr(), _st(rhs.stride()),
+                                                  out.data_ptr(), self._stream()), "b200_matmat_batch3_forward")
+        return out
+
+    def matmat_batch3_backward(self, lhs, grad_lhs, rhs, grad_rhs, grad_out) -> None:
+        (b, m, k), n = lhs.shape, rhs.shape[2]
+        check(self.lib.b200_matmat_batch3_backward(self._dtype(lhs), b, m, k, n, lhs.data_ptr(),
+                                                   _st(lhs.stride()), _ptr(grad_lhs), rhs.data_ptr(),
+                                                   _st(rhs.stride()), _ptr(grad_rhs), grad_out.data_ptr(),
+                                                   self._stream(), None), "b200_matmat_batch3_backward")
+
+    def matmat_batch4_forward(self, lhs, rhs):
+        (b, s, m, k), n = lhs.shape, rhs.shape[3]
+        out = self._empty((b, s, m, n), lhs)
+        check(self.lib.b200_matmat_batch4_forward(self._dtype(lhs), b, s, m, k, n, lhs.data_ptr(),
+                                                  _st(lhs.stride()), rhs.data_ptr(), _st(rhs.stride()),
+                                                  out.data_ptr(), self._stream()), "b200_matmat_batch4_forward")
+        return out
+
+    def matmat_batch4_backward(self, lhs, grad_lhs, rhs, grad_rhs, grad_out) -> None:
+        (b, s, m, k), n = lhs.shape, rhs.shape[3]
+        check(self.lib.b200_matmat_batch4_backward(self._dtype(lhs), b, s, m, k, n, lhs.data_ptr(),
+                                                   _st(lhs.stride()), _ptr(grad_lhs), rhs.data_ptr(),
+                                                   _st(rhs.stride()), _ptr(grad_rhs), grad_out.data_ptr(),
+                                                   self._stream(), None), "b200_matmat_batch4_backward")
+
+    # -- TryMatMul (matmul/mod.rs:133-311) ---------------------------------------------------------
+    def matmul(self, lhs: torch.Tensor, rhs: torch.Tensor):
+        """Rank dispatch of `TryMatMul`.  Returns (out, backward) where
+        `backward(grad_out) -> (grad_lhs, grad_rhs)` runs the trait's backward into freshly zeroed
+        gradient buffers and returns them viewed through the operands' strides."""
+        ld, rd = lhs.dim(), rhs.dim()
+        if ld == 1 and rd == 1:       # outer product: (M,) x (N,) -> (M,1) x (1,N)   (mod.rs:139-158)
+            l2 = torch.as_strided(lhs, (lhs.shape[0], 1), (lhs.stride(0), 1))
+            r2 = torch.as_strided(rhs, (1, rhs.shape[0]), (rhs.shape[0], rhs.stride(0)))
+            return self._traced(self.matmat_forward, self.matmat_backward, l2, r2, lhs, rhs, None)
+        if ld == 1 and rd == 2:       # (K,) x (K,N) -> (N,)                            (mod.rs:160-174)
+            _assert_eq(lhs.shape[0], rhs.shape[0])
+            l2 = torch.as_strided(lhs, (1, lhs.shape[0]), (lhs.shape[0], lhs.stride(0)))
+            return self._traced(self.matmat_forward, self.matmat_backward, l2, rhs, lhs, rhs, (rhs.shape[1],))
+        if ld == 2 and rd == 1:       # (M,K) x (K,) -> (M,)                            (mod.rs:176-189)
+            _assert_eq(lhs.shape[1], rhs.shape[0])
+            r2 = torch.as_strided(rhs, (rhs.shape[0], 1), (rhs.stride(0), 1))
+            return self._traced(self.matmat_forward, self.matmat_backward, lhs, r2, lhs, rhs, (lhs.shape[0],))
+        if ld == 2 and rd == 2:
+            _assert_eq(lhs.shape[1], rhs.shape[0])
+            return self._traced(self.matmat_forward, self.matmat_backward, lhs, rhs, lhs, rhs, None)
+        if ld == 3 and rd == 2:
+            _assert_eq(lhs.shape[2], rhs.shape[0])
+            return self._traced(self.matmat_br_forward, self.matmat_br_backward, lhs, rhs, lhs, rhs, None)
+        if ld == 3 and rd == 3:
+            _assert_eq(lhs.shape[0], rhs.shape[0])
+            _assert_eq(lhs.shape[2], rhs.shape[1])
+            return self._traced(self.matmat_batch3_forward, self.matmat_batch3_backward, lhs, rhs, lhs, rhs, None)
+        if ld == 4 and rd == 4:
+            _assert_eq(lhs.shape[0], rhs.shape[0])
+            _assert_eq(lhs.shape[1], rhs.shape[1])
+            _assert_eq(lhs.shape[3], rhs.shape[2])
+            return self._traced(self.matmat_batch4_forward, self.matmat_batch4_backward, lhs, rhs, lhs, rhs, None)
+        raise TypeError(f"matmul is not defined for ranks {ld} x {rd}")
+
+    def _traced(self, fwd, bwd, l, r, l_orig, r_orig, out_shape):
+        out = fwd(l, r)
+        shaped = out if out_shape is None else out.reshape(out_shape)
+
+        def backward(grad_out: torch.Tensor):
+            go = grad_out.reshape(out.shape).contiguous()
+            gl, gr = self.alloc_grad(l_orig), self.alloc_grad(r_orig)
+            bwd(l, gl, r, gr, go)
+            return self.grad_view(gl, l_orig), self.grad_view(gr, r_orig)
+
+        return shaped, backward
+
+    # -- Conv2DKernel / TryConv2D (conv2d/mod.rs:273-324) -----------------------------------------
+    def conv2d_op(self, img, filters, stride, padding, dilation, groups) -> Conv2DOp:
+        b, c, h, w = img.shape
+        o, cg, k, k2 = filters.shape
+        _assert_eq(c, cg * groups)
+        _assert_eq(k, k2)
+        if o % groups:
+            raise ShapeMismatch("assertion failed: out_chan.size() % groups.size() == 0")
+        return Conv2DOp(kernel=k, stride=stride, padding=padding, dilation=dilation, groups=groups, batch=b,
+                        chan_in=c, chan_out=o, h_in=h, h_out=conv2d_out_dim(h, k, stride, padding, dilation),
+                        w_in=w, w_out=conv2d_out_dim(w, k, stride, padding, dilation))
+
+    def conv2d_forward(self, op: Conv2DOp, img, filters, out) -> None:
+        dt = self._dtype(img)
+        need = self.lib.b200_conv2d_workspace_bytes(dt, op, 0)
+        ws = self.get_workspace(need)
+        check(self.lib.b200_conv2d_forward(dt, op, img.data_ptr(), _st(img.stride()), filters.data_ptr(),
+                                           out.data_ptr(), ws.data_ptr(), ws.numel(), self._stream()),
+              "b200_conv2d_forward")
+
+    def conv2d_backward(self, op: Conv2DOp, img, grad_img, filters, grad_filters, grad_out) -> None:
+        dt = self._dtype(img)
+        need = self.lib.b200_conv2d_workspace_bytes(dt, op, 1)
+        ws = self.get_workspace(need)
+        check(self.lib.b200_conv2d_backward(dt, op, img.data_ptr(), _ptr(grad_img), filters.data_ptr(),
+                                            _st(filters.stride()), _ptr(grad_filters), grad_out.data_ptr(),
+                                            ws.data_ptr(), ws.numel(), self._stream(), None),
+              "b200_conv2d_backward")
+
+    def conv2d(self, img, filters, stride=1, padding=0, dilation=1, groups=1):
+        """`(img, filters).conv2d(stride, padding, dilation, groups)`; 3-D images are batch 1
+        (conv2d/mod.rs:216-222).  Returns (out, backward)."""
+        squeeze = img.dim() == 3
+        x = img.reshape((1,) + tuple(img.shape)) if squeeze else img
+        if not x.is_contiguous() or not filters.is_contiguous():
+            raise ShapeMismatch("Image & filter inputs to conv2d must be contiguous")
+        op = self.conv2d_op(x, filters, stride, padding, dilation, groups)
+        out = self._empty((op.batch, op.chan_out, op.h_out, op.w_out), x)
+        self.conv2d_forward(op, x, filters, out)
+
+        def backward(grad_out: torch.Tensor):
+            go = grad_out.reshape(out.shape).contiguous()
+            gx, gw = self.alloc_grad(x), self.alloc_grad(filters)
+            self.conv2d_backward(op, x, gx, filters, gw, go)
+            return self.grad_view(gx, x).reshape(img.shape), self.grad_view(gw, filters)
+
+        return (out[0] if squeeze else out), backward
+
+
+def _ptr(t):
+    return None if t is None else t.data_ptr()

@@ -1,0 +1,190 @@
+/*
+ * dfdx_b200 — C ABI of the B200 (sm_100a) matmul / conv2d hot path for dfdx's `Cuda` device.
+ *
+ * Every entry point is what dfdx's Rust side would bind (through cudarc-style raw device pointers
+ * and raw CUDA streams) in place of the cuBLAS calls and helper kernels it uses today.  All paths
+ * below are relative to the dfdx repository (v0.13.0).
+ *
+ * Conventions shared by all entry points
+ *   - Pointers are device pointers owned by the caller; nothing is retained after the call returns.
+ *   - Strides are ELEMENT strides exactly as stored in dfdx's `Tensor::strides`
+ *     (dfdx-core/src/tensor/tensor_impls.rs:32-39): any permutation / broadcast of a contiguous
+ *     layout.  A stride of 0 marks a broadcast dimension.
+ *   - `stream` / `par_stream` are `cudaStream_t` / `CUstream` handles passed as `void*`
+ *     (NULL = the legacy default stream).  Calls only enqueue work; ordering is stream order.
+ *   - Return value: 0 on success, a negative `b200_status` otherwise.  No entry point aborts,
+ *     throws or calls exit().  Shape / stride violations that the reference turns into a panic
+ *     before any launch are reported as B200_ERR_SHAPE / B200_ERR_STRIDE before any launch.
+ *   - The caller's CUDA context (device) must be current, as cudarc guarantees per call.
+ */
+#ifndef DFDX_B200_H
+#define DFDX_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Element types of the path: the `Dtype`s for which dfdx implements `Device<E>` on `Cuda`
+ * (dfdx-core/src/tensor_ops/utilities/device.rs:128-135). */
+typedef enum {
+  B200_F32 = 0,     /* f32: tensor cores via 3xTF32 (kind::tf32), exact-FP32 SIMT for small/unaligned */
+  B200_F64 = 1,     /* f64: SIMT only */
+  B200_F16 = 2,     /* half::f16 storage, f32 accumulate */
+  B200_AMP_F16 = 3  /* AMP<f16>: f16 storage, f32 compute (matmul/cuda_kernel.rs:62-135) */
+} b200_dtype;
+
+typedef enum {
+  B200_OK = 0,
+  B200_ERR_SHAPE = -1,        /* inner dimensions / batch dimensions disagree (matmul/mod.rs:192,229,267,306) */
+  B200_ERR_STRIDE = -2,       /* "At least a single stride must be 1" (matmul/mod.rs:323); zero out/batch stride
+                                 where the reference asserts non-zero (cuda_kernel.rs:208,400,474) */
+  B200_ERR_DTYPE = -3,
+  B200_ERR_NULL = -4,
+  B200_ERR_WORKSPACE = -5,    /* workspace smaller than b200_conv2d_workspace_bytes() */
+  B200_ERR_CUDA = -6,         /* a CUDA runtime/driver call failed; see b200_last_cuda_error() */
+  B200_ERR_DEVICE_TIMEOUT = -7, /* a bounded device-side wait expired (reported by b200_device_status) */
+  B200_ERR_UNSUPPORTED = -8,
+  B200_ERR_NOT_CONTIGUOUS = -9, /* conv2d: "Image & filter inputs to conv2d must be contiguous" (conv2d/mod.rs:287-289) */
+  B200_ERR_LIMIT = -10          /* request exceeds a documented fixed capacity */
+} b200_status;
+
+/* Mirrors `Conv2DOp` bit for bit: 12 x usize, #[repr(C)]
+ * (dfdx-core/src/tensor_ops/conv2d/mod.rs:14-29; device copy conv2d/conv2d.cu:3-16). */
+typedef struct {
+  size_t kernel, stride, padding, dilation, groups, batch;
+  size_t chan_in, chan_out, h_in, h_out, w_in, w_out;
+} b200_conv2d_op;
+
+/* Which kernel family serves the contraction.  AUTO is the product behaviour. */
+typedef enum {
+  B200_PATH_AUTO = 0,   /* tensor cores when operands are TMA-addressable and the problem is not tiny */
+  B200_PATH_SIMT = 1,   /* force the any-stride exact-FP32/FP64 SIMT kernels */
+  B200_PATH_TENSOR = 2  /* force tcgen05; returns B200_ERR_UNSUPPORTED if operands are not TMA-addressable */
+} b200_path;
+
+/* ---- library / device ------------------------------------------------------------------------- */
+
+/* Replaces `Cuda::try_build(ordinal, seed)`'s cuBLAS-handle creation
+ * (dfdx-core/src/tensor/cuda/device.rs:72-91): selects the device, resolves the driver entry
+ * point used to encode TMA descriptors, raises the kernels' dynamic shared-memory limits and
+ * allocates the per-device status word.  Idempotent; thread-safe. */
+int b200_init(int ordinal);
+
+const char* b200_strerror(int status);
+/* Text of the last CUDA error seen by this thread inside the library ("" if none). */
+const char* b200_last_cuda_error(void);
+/* Reads (and clears) the device-side status word of the current device after synchronising
+ * `stream`: 0, or B200_ERR_DEVICE_TIMEOUT if any kernel gave up on a bounded wait. */
+int b200_device_status(void* stream);
+/* Process-wide override of kernel-family selection (testing / profiling). */
+int b200_set_path(int path);
+/* f32 tensor-core operand split (testing / profiling): 0 (default) rewrites each staged f32 x as
+ * big = tf32_rn(x) and small = tf32_rn(x - big); 1 leaves x in place (the tensor core truncates it
+ * to tf32) and only writes small = tf32_rn(x - trunc(x)). */
+int b200_set_tf32_split_mode(int mode);
+/* Number of kernel launches this library has enqueued since load (all threads). */
+uint64_t b200_launch_count(void);
+/* Of those, launches of tcgen05 tensor-core kernels. */
+uint64_t b200_tensor_launch_count(void);
+
+/* ---- the two GEMM seams ---------------------------------------------------------------------- */
+
+/* Replaces the body of `Cuda::gemm` (dfdx-core/src/tensor_ops/matmul/cuda_kernel.rs:153-181,
+ * i.e. `gemm_cfg` :18-60 + cublas{S,D,H}gemm / cublasGemmEx):
+ *     out[i*os0 + j*os1] = beta*out[..] + sum_p lhs[i*ls0 + p*ls1] * rhs[p*rs0 + j*rs1]
+ * for i<m, j<n, p<k.  beta is 0 or 1; with beta == 0 `out` is never read (it comes from
+ * `alloc_empty`, cuda_kernel.rs:253).  Legal stride pairs are those `matrix_strides`
+ * accepts (matmul/mod.rs:316-325). */
+int b200_gemm(int dtype, size_t m, size_t k, size_t n,
+              const void* lhs, const size_t lhs_strides[2],
+              const void* rhs, const size_t rhs_strides[2],
+              double beta, void* out, const size_t out_strides[2], void* stream);
+
+/* Replaces the body of `Cuda::gemm_batch` (cuda_kernel.rs:184-237, cublas*gemmStridedBatched[Ex]).
+ * strides[0] is the batch stride; lhs/rhs batch stride may be 0, out batch stride must not be. */
+int b200_gemm_batch(int dtype, size_t batch, size_t m, size_t k, size_t n,
+                    const void* lhs, const size_t lhs_strides[3],
+                    const void* rhs, const size_t rhs_strides[3],
+                    double beta, void* out, const size_t out_strides[3], void* stream);
+
+/* ---- the kernel-trait seams (fused forward / backward) ---------------------------------------- */
+
+/* `MatMatKernel::forward/backward for Cuda` (cuda_kernel.rs:244-312): (M,K)x(K,N).
+ * forward writes a contiguous (M,N) `out`.  backward accumulates grad_lhs += grad_out * rhs^T
+ * through lhs_strides and grad_rhs += lhs^T * grad_out through rhs_strides; grad_out is a
+ * contiguous (M,N).  Either gradient pointer may be NULL to skip it.  The reference runs the two
+ * gradient GEMMs on `par_stream` and the default stream; here both are enqueued on `stream`
+ * (`par_stream` is accepted for signature compatibility and may be NULL). */
+int b200_matmat_forward(int dtype, size_t m, size_t k, size_t n,
+                        const void* lhs, const size_t lhs_strides[2],
+                        const void* rhs, const size_t rhs_strides[2],
+                        void* out, void* stream);
+int b200_matmat_backward(int dtype, size_t m, size_t k, size_t n,
+                         const void* lhs, const size_t lhs_strides[2], void* grad_lhs,
+                         const void* rhs, const size_t rhs_strides[2], void* grad_rhs,
+                         const void* grad_out, void* stream, void* par_stream);
+
+/* `MatMatBrKernel for Cuda` (cuda_kernel.rs:319-388): (B,M,K)x(K,N), rhs broadcast over B.
+ * backward: grad_rhs += sum_b lhs_b^T * grad_out_b is ONE launch that reduces over the batch
+ * inside the kernel (the reference issues B serial beta=1 GEMMs, :358-371). */
+int b200_matmat_br_forward(int dtype, size_t batch, size_t m, size_t k, size_t n,
+                           const void* lhs, const size_t lhs_strides[3],
+                           const void* rhs, const size_t rhs_strides[2],
+                           void* out, void* stream);
+int b200_matmat_br_backward(int dtype, size_t batch, size_t m, size_t k, size_t n,
+                            const void* lhs, const size_t lhs_strides[3], void* grad_lhs,
+                            const void* rhs, const size_t rhs_strides[2], void* grad_rhs,
+                            const void* grad_out, void* stream, void* par_stream);
+
+/* `MatMatBatch3Kernel for Cuda` (cuda_kernel.rs:395-462): (B,M,K)x(B,K,N); batch strides non-zero. */
+int b200_matmat_batch3_forward(int dtype, size_t batch, size_t m, size_t k, size_t n,
+                               const void* lhs, const size_t lhs_strides[3],
+                               const void* rhs, const size_t rhs_strides[3],
+                               void* out, void* stream);
+int b200_matmat_batch3_backward(int dtype, size_t batch, size_t m, size_t k, size_t n,
+                                const void* lhs, const size_t lhs_strides[3], void* grad_lhs,
+                                const void* rhs, const size_t rhs_strides[3], void* grad_rhs,
+                                const void* grad_out, void* stream, void* par_stream);
+
+/* `MatMatBatch4Kernel for Cuda` (cuda_kernel.rs:469-568): (B,S,M,K)x(B,S,K,N) in one launch per
+ * GEMM group (the reference loops over B on the host, :492-517, :538-564). */
+int b200_matmat_batch4_forward(int dtype, size_t batch, size_t seq, size_t m, size_t k, size_t n,
+                               const void* lhs, const size_t lhs_strides[4],
+                               const void* rhs, const size_t rhs_strides[4],
+                               void* out, void* stream);
+int b200_matmat_batch4_backward(int dtype, size_t batch, size_t seq, size_t m, size_t k, size_t n,
+                                const void* lhs, const size_t lhs_strides[4], void* grad_lhs,
+                                const void* rhs, const size_t rhs_strides[4], void* grad_rhs,
+                                const void* grad_out, void* stream, void* par_stream);
+
+/* ---- conv2d (unfold + GEMM lowering) ---------------------------------------------------------- */
+
+/* Bytes of caller-provided scratch the conv2d entry points need; `backward` != 0 selects the
+ * backward pass.  Plays the role of the sizes handed to `Cuda::get_workspace`
+ * (conv2d/cuda_kernel.rs:91-95,156-168; tensor/cuda/device.rs:108-122). */
+size_t b200_conv2d_workspace_bytes(int dtype, const b200_conv2d_op* op, int backward);
+
+/* `Conv2DKernel::forward for Cuda` (conv2d/cuda_kernel.rs:80-144 + conv2d.cu:18-52):
+ * out(B,O,OH,OW) = conv(img(B,C,H,W) with 4-D element strides, filters(O,C/G,K,K) contiguous).
+ * `out` is uninitialised on entry. */
+int b200_conv2d_forward(int dtype, const b200_conv2d_op* op,
+                        const void* img, const size_t img_strides[4],
+                        const void* filters, void* out,
+                        void* workspace, size_t workspace_bytes, void* stream);
+
+/* `Conv2DKernel::backward for Cuda` (conv2d/cuda_kernel.rs:146-281 + conv2d.cu:54-168):
+ * grad_img += conv_transpose(grad_out, filters); grad_filters (addressed through
+ * filters_strides) += sum_b img_b (x) grad_out_b.  img, grad_img contiguous (B,C,H,W). */
+int b200_conv2d_backward(int dtype, const b200_conv2d_op* op,
+                         const void* img, void* grad_img,
+                         const void* filters, const size_t filters_strides[4], void* grad_filters,
+                         const void* grad_out,
+                         void* workspace, size_t workspace_bytes, void* stream, void* par_stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DFDX_B200_H */

@@ -1,0 +1,235 @@
+"""TEST INFRASTRUCTURE — Python front-end of the CPU oracle (oracle.c) and the CPU baseline port.
+
+Only tests/, `__graft_entry__.smoke()` and bench.py's CPU-baseline / reference arm may import this.
+Tensors are torch CPU tensors (any dtype, any view); they are widened to f64 over their whole
+storage so that strides keep their meaning, and results come back as f64 torch tensors.
+The API mirrors `dfdx_b200.Cuda` (matmul / conv2d returning `(out, backward)`), which in turn
+mirrors dfdx's `TryMatMul` / `TryConv2D`.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import subprocess
+from pathlib import Path
+
+import numpy as np
+import torch
+
+HERE = Path(__file__).resolve().parent
+_sz = C.c_size_t
+_szp = C.POINTER(C.c_size_t)
+_dp = C.POINTER(C.c_double)
+_fp = C.POINTER(C.c_float)
+
+
+class Conv2DOp(C.Structure):
+    _fields_ = [(n, C.c_size_t) for n in (
+        "kernel", "stride", "padding", "dilation", "groups", "batch",
+        "chan_in", "chan_out", "h_in", "h_out", "w_in", "w_out")]
+
+
+def build() -> None:
+    """Compiles liboracle.so and libcpu_baseline.so next to their sources (idempotent)."""
+    res = subprocess.run(["make", "-C", str(HERE)], capture_output=True, text=True)
+    if res.returncode != 0:
+        raise RuntimeError(f"oracle build failed:\n{res.stdout}\n{res.stderr}")
+
+
+_oracle = None
+_baseline = None
+
+
+def lib() -> C.CDLL:
+    global _oracle
+    if _oracle is None:
+        if not (HERE / "liboracle.so").exists():
+            build()
+        L = C.CDLL(str(HERE / "liboracle.so"))
+        L.oracle_gemm.argtypes = [_sz, _sz, _sz, C.c_int, _dp, _szp, _dp, _szp, _dp, _szp]
+        L.oracle_matmat_forward.argtypes = [_sz, _sz, _sz, _dp, _szp, _dp, _szp, _dp]
+        L.oracle_matmat_backward.argtypes = [_sz, _sz, _sz, _dp, _szp, _dp, _dp, _szp, _dp, _dp]
+        L.oracle_matmat_br_forward.argtypes = [_sz] * 4 + [_dp, _szp, _dp, _szp, _dp]
+        L.oracle_matmat_br_backward.argtypes = [_sz] * 4 + [_dp, _szp, _dp, _dp, _szp, _dp, _dp]
+        L.oracle_matmat_batch3_forward.argtypes = [_sz] * 4 + [_dp, _szp, _dp, _szp, _dp]
+        L.oracle_matmat_batch3_backward.argtypes = [_sz] * 4 + [_dp, _szp, _dp, _dp, _szp, _dp, _dp]
+        L.oracle_matmat_batch4_forward.argtypes = [_sz] * 5 + [_dp, _szp, _dp, _szp, _dp]
+        L.oracle_matmat_batch4_backward.argtypes = [_sz] * 5 + [_dp, _szp, _dp, _dp, _szp, _dp, _dp]
+        L.oracle_conv2d_out_dim.argtypes = [_sz] * 5
+        L.oracle_conv2d_out_dim.restype = _sz
+        L.oracle_conv2d_forward.argtypes = [C.POINTER(Conv2DOp), _dp, _szp, _dp, _dp]
+        L.oracle_conv2d_forward.restype = C.c_int
+        L.oracle_conv2d_backward.argtypes = [C.POINTER(Conv2DOp), _dp, _dp, _dp, _szp, _dp, _dp]
+        L.oracle_conv2d_backward.restype = C.c_int
+        _oracle = L
+    return _oracle
+
+
+def baseline_lib() -> C.CDLL:
+    global _baseline
+    if _baseline is None:
+        if not (HERE / "libcpu_baseline.so").exists():
+            build()
+        L = C.CDLL(str(HERE / "libcpu_baseline.so"))
+        L.cpu_baseline_supported.restype = C.c_int
+        L.cpu_baseline_threads.restype = C.c_int
+        L.cpu_sgemm.argtypes = [_sz, _sz, _sz, C.c_int, _fp, _szp, _fp, _szp, _fp, _szp]
+        L.cpu_matmat_forward.argtypes = [_sz, _sz, _sz, _fp, _szp, _fp, _szp, _fp]
+        L.cpu_matmat_backward.argtypes = [_sz, _sz, _sz, _fp, _szp, _fp, _fp, _szp, _fp, _fp]
+        L.cpu_matmat_br_forward.argtypes = [_sz] * 4 + [_fp, _szp, _fp, _szp, _fp]
+        L.cpu_matmat_br_backward.argtypes = [_sz] * 4 + [_fp, _szp, _fp, _fp, _szp, _fp, _fp]
+        _baseline = L
+    return _baseline
+
+
+def _strides(seq):
+    return (C.c_size_t * len(seq))(*[int(s) for s in seq])
+
+
+class _Buf:
+    """A tensor's whole storage widened to f64, plus the view (offset, shape, strides) into it."""
+
+    def __init__(self, t: torch.Tensor):
+        t = t.detach().cpu()
+        n = t.untyped_storage().nbytes() // t.element_size()
+        flat = torch.empty(0, dtype=t.dtype).set_(t.untyped_storage(), 0, (n,), (1,))
+        self.data = flat.to(torch.float64).contiguous().numpy()
+        self.offset = t.storage_offset()
+        self.shape = tuple(t.shape)
+        self.strides = tuple(t.stride())
+
+    @property
+    def ptr(self):
+        return self.data[self.offset:].ctypes.data_as(_dp)
+
+    def zeros_like_storage(self) -> np.ndarray:
+        return np.zeros_like(self.data)
+
+    def view_of(self, flat: np.ndarray) -> torch.Tensor:
+        return torch.as_strided(torch.from_numpy(flat), self.shape, self.strides, self.offset)
+
+
+def _out(shape) -> np.ndarray:
+    return np.empty(int(np.prod(shape)) if len(shape) else 1, dtype=np.float64)
+
+
+def _p(a: np.ndarray):
+    return a.ctypes.data_as(_dp)
+
+
+def gemm(mkn, lhs: _Buf, lhs_strides, rhs: _Buf, rhs_strides, accum: bool, out: np.ndarray, out_strides):
+    m, k, n = mkn
+    lib().oracle_gemm(m, k, n, int(accum), lhs.ptr, _strides(lhs_strides), rhs.ptr, _strides(rhs_strides),
+                      _p(out), _strides(out_strides))
+
+
+class ShapeMismatch(AssertionError):
+    pass
+
+
+def _assert_eq(a, b):
+    if a != b:
+        raise ShapeMismatch(f"left: {a}\n right: {b}")
+
+
+_KINDS = {
+    (2, 2): ("oracle_matmat", 0), (3, 2): ("oracle_matmat_br", 1),
+    (3, 3): ("oracle_matmat_batch3", 1), (4, 4): ("oracle_matmat_batch4", 2),
+}
+
+
+def matmul(lhs: torch.Tensor, rhs: torch.Tensor):
+    """Rank dispatch of `TryMatMul` (matmul/mod.rs:133-311) on the oracle.  Returns (out, backward);
+    backward(grad_out) -> (grad_lhs, grad_rhs) as f64 views through the operands' strides."""
+    ld, rd = lhs.dim(), rhs.dim()
+    if ld == 1 and rd == 1:
+        l2 = torch.as_strided(lhs, (lhs.shape[0], 1), (lhs.stride(0), 1), lhs.storage_offset())
+        r2 = torch.as_strided(rhs, (1, rhs.shape[0]), (rhs.shape[0], rhs.stride(0)), rhs.storage_offset())
+        return _run(l2, r2, lhs, rhs, None)
+    if ld == 1 and rd == 2:
+        _assert_eq(lhs.shape[0], rhs.shape[0])
+        l2 = torch.as_strided(lhs, (1, lhs.shape[0]), (lhs.shape[0], lhs.stride(0)), lhs.storage_offset())
+        return _run(l2, rhs, lhs, rhs, (rhs.shape[1],))
+    if ld == 2 and rd == 1:
+        _assert_eq(lhs.shape[1], rhs.shape[0])
+        r2 = torch.as_strided(rhs, (rhs.shape[0], 1), (rhs.stride(0), 1), rhs.storage_offset())
+        return _run(lhs, r2, lhs, rhs, (lhs.shape[0],))
+    if (ld, rd) not in _KINDS:
+        raise TypeError(f"matmul is not defined for ranks {ld} x {rd}")
+    if ld == rd:
+        for i in range(ld - 2):
+            _assert_eq(lhs.shape[i], rhs.shape[i])
+    _assert_eq(lhs.shape[-1], rhs.shape[-2])
+    return _run(lhs, rhs, lhs, rhs, None)
+
+
+def _run(l, r, l_orig, r_orig, out_shape):
+    name, nbatch = _KINDS[(l.dim(), r.dim())]
+    L = lib()
+    lb, rb = _Buf(l), _Buf(r)
+    batch = tuple(l.shape[:nbatch])
+    m, k, n = l.shape[-2], l.shape[-1], r.shape[-1]
+    oshape = batch + (m, n)
+    out = _out(oshape)
+    getattr(L, name + "_forward")(*batch, m, k, n, lb.ptr, _strides(lb.strides), rb.ptr, _strides(rb.strides), _p(out))
+    out_t = torch.from_numpy(out).reshape(oshape)
+    shaped = out_t if out_shape is None else out_t.reshape(out_shape)
+
+    def backward(grad_out: torch.Tensor):
+        go = np.ascontiguousarray(grad_out.detach().cpu().to(torch.float64).reshape(oshape).numpy())
+        gl, gr = lb.zeros_like_storage(), rb.zeros_like_storage()
+        getattr(L, name + "_backward")(*batch, m, k, n, lb.ptr, _strides(lb.strides),
+                                       gl[lb.offset:].ctypes.data_as(_dp), rb.ptr, _strides(rb.strides),
+                                       gr[rb.offset:].ctypes.data_as(_dp), _p(go))
+        gl_v = torch.as_strided(torch.from_numpy(gl), l_orig.shape, l_orig.stride(), l_orig.storage_offset())
+        gr_v = torch.as_strided(torch.from_numpy(gr), r_orig.shape, r_orig.stride(), r_orig.storage_offset())
+        return gl_v, gr_v
+
+    return shaped, backward
+
+
+def conv2d_out_dim(dim, kernel, stride, padding, dilation) -> int:
+    v = lib().oracle_conv2d_out_dim(dim, kernel, stride, padding, dilation)
+    if v == (1 << 64) - 1:
+        raise ShapeMismatch("called `Option::unwrap()` on a `None` value")
+    return int(v)
+
+
+def conv2d(img: torch.Tensor, filters: torch.Tensor, stride=1, padding=0, dilation=1, groups=1):
+    """`TryConv2D` (conv2d/mod.rs:273-324) on the oracle.  Returns (out, backward)."""
+    squeeze = img.dim() == 3
+    x = img.reshape((1,) + tuple(img.shape)) if squeeze else img
+    if not x.is_contiguous() or not filters.is_contiguous():
+        raise ShapeMismatch("Image & filter inputs to conv2d must be contiguous")
+    b, c, h, w = x.shape
+    o, cg, k, k2 = filters.shape
+    _assert_eq(c, cg * groups)
+    _assert_eq(k, k2)
+    op = Conv2DOp(kernel=k, stride=stride, padding=padding, dilation=dilation, groups=groups, batch=b,
+                  chan_in=c, chan_out=o, h_in=h, h_out=conv2d_out_dim(h, k, stride, padding, dilation),
+                  w_in=w, w_out=conv2d_out_dim(w, k, stride, padding, dilation))
+    L = lib()
+    xb, fb = _Buf(x), _Buf(filters)
+    oshape = (b, o, op.h_out, op.w_out)
+    out = _out(oshape)
+    rc = L.oracle_conv2d_forward(C.byref(op), xb.ptr, _strides(xb.strides), fb.ptr, _p(out))
+    assert rc == 0
+    out_t = torch.from_numpy(out).reshape(oshape)
+
+    def backward(grad_out: torch.Tensor):
+        go = np.ascontiguousarray(grad_out.detach().cpu().to(torch.float64).reshape(oshape).numpy())
+        gx, gf = xb.zeros_like_storage(), fb.zeros_like_storage()
+        rc2 = L.oracle_conv2d_backward(C.byref(op), xb.ptr, gx[xb.offset:].ctypes.data_as(_dp), fb.ptr,
+                                       _strides(fb.strides), gf[fb.offset:].ctypes.data_as(_dp), _p(go))
+        assert rc2 == 0
+        return xb.view_of(gx).reshape(img.shape), fb.view_of(gf)
+
+    return (out_t[0] if squeeze else out_t), backward
+
+
+def rel_frobenius(got: torch.Tensor, want: torch.Tensor) -> float:
+    """||got - want||_F / ||want||_F in f64 (0/0 -> 0)."""
+    g = got.detach().cpu().to(torch.float64)
+    w = want.detach().cpu().to(torch.float64)
+    den = torch.linalg.vector_norm(w).item()
+    num = torch.linalg.vector_norm(g - w).item()
+    return num / den if den > 0 else num

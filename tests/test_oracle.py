@@ -1,0 +1,118 @@
+"""Pins the oracle beyond the literal vectors: against torch's CPU f64 matmul / conv2d on seeded
+random inputs (the reference's own goldens were produced with PyTorch, README.md:178-180), over the
+stride patterns the path meets (permuted, broadcast, batched), and the properties the reference tests
+(matmul/mod.rs:412-527; conv2d/tests.rs:218-250, :404-464)."""
+import pytest
+import torch
+import torch.nn.functional as F
+
+from helpers import OracleBackend, d_exp_mean, d_exp_sum, d_square_mean, d_sum
+
+TOL = 1e-11
+
+
+def gen(seed):
+    return torch.Generator().manual_seed(seed)
+
+
+def _grads(x, w, y_fn, dy_fn):
+    x = x.clone().requires_grad_(True)
+    w = w.clone().requires_grad_(True)
+    y = y_fn(x, w)
+    y.backward(dy_fn(y.detach()))
+    return y.detach(), x.grad, w.grad
+
+
+@pytest.mark.parametrize("shapes", [
+    ((4, 3), (3, 2)), ((5, 4, 3), (3, 2)), ((5, 3, 2), (5, 2, 4)), ((7, 5, 3, 2), (7, 5, 2, 4)),
+    ((3,), (3, 2)), ((5,), (3,)), ((4, 3), (3,)), ((33, 17), (17, 29)),
+])
+def test_matmul_matches_torch(oracle, shapes):
+    be = OracleBackend(oracle)
+    g = gen(1)
+    a, b = be.randn(*shapes[0], gen=g), be.randn(*shapes[1], gen=g)
+    out, bwd = be.matmul(a, b)
+    if a.dim() == 1 and b.dim() == 1:
+        fn = lambda x, w: torch.outer(x, w)
+    else:
+        fn = lambda x, w: torch.matmul(x, w)
+    y, ga_t, gb_t = _grads(a, b, fn, d_exp_mean)
+    assert (out - y).abs().max() < TOL
+    ga, gb = bwd(d_exp_mean(out))
+    assert (ga - ga_t).abs().max() < TOL and (gb - gb_t).abs().max() < TOL
+
+
+def test_matmul_transpose_property(oracle):
+    """matmul/mod.rs:412-426: (b^T a^T) yields the same gradients as (a b)."""
+    be = OracleBackend(oracle)
+    g = gen(2)
+    a, b = be.randn(4, 3, gen=g), be.randn(3, 2, gen=g)
+    c, bwd = be.matmul(a, b)
+    ga1, gb1 = bwd(d_exp_mean(c))
+    c2, bwd2 = be.matmul(b.permute(1, 0), a.permute(1, 0))
+    gb2_view, ga2_view = bwd2(d_exp_mean(c2))
+    assert (ga1 - ga2_view.permute(1, 0)).abs().max() < TOL
+    assert (gb1 - gb2_view.permute(1, 0)).abs().max() < TOL
+
+
+def test_matmul_broadcast_properties(oracle):
+    """matmul/mod.rs:428-473: broadcast-rhs equals per-item 2-D matmuls; rhs gradient sums over the batch.
+    Also :454-473: an expanded (stride-0) rhs through the batch-3 kernel accumulates into one buffer."""
+    be = OracleBackend(oracle)
+    g = gen(3)
+    a, b = be.randn(5, 4, 3, gen=g), be.randn(3, 2, gen=g)
+    r, bwd = be.matmul(a, b)
+    ga, gb = bwd(d_sum(r))
+    gb_sum = torch.zeros_like(gb)
+    for i in range(5):
+        ri, bwdi = be.matmul(a[i].contiguous(), b)
+        assert (ri - r[i]).abs().max() < TOL
+        gai, gbi = bwdi(d_sum(ri))
+        assert (gai - ga[i]).abs().max() < TOL
+        gb_sum += gbi
+    assert (gb_sum - gb).abs().max() < TOL
+
+
+@pytest.mark.parametrize("cfg", [
+    dict(x=(2, 3, 7, 6), w=(4, 3, 2, 2), stride=1, padding=0, dilation=1, groups=1),
+    dict(x=(1, 5, 7, 6), w=(3, 5, 2, 2), stride=4, padding=3, dilation=1, groups=1),
+    dict(x=(3, 3, 28, 28), w=(5, 3, 6, 6), stride=3, padding=2, dilation=1, groups=1),
+    dict(x=(2, 4, 9, 8), w=(6, 4, 3, 3), stride=2, padding=1, dilation=2, groups=1),
+    dict(x=(2, 9, 14, 14), w=(15, 3, 3, 3), stride=1, padding=0, dilation=1, groups=3),
+    dict(x=(2, 8, 10, 11), w=(4, 4, 3, 3), stride=2, padding=2, dilation=1, groups=2),
+])
+def test_conv2d_matches_torch(oracle, cfg):
+    be = OracleBackend(oracle)
+    g = gen(4)
+    x, w = be.randn(*cfg["x"], gen=g), be.randn(*cfg["w"], gen=g)
+    kw = {k: cfg[k] for k in ("stride", "padding", "dilation", "groups")}
+    y, bwd = be.conv2d(x, w, **kw)
+    yt, gxt, gwt = _grads(x, w, lambda a, b: F.conv2d(a, b, None, **kw), d_square_mean)
+    assert y.shape == yt.shape
+    assert (y - yt).abs().max() < TOL
+    gx, gw = bwd(d_square_mean(y))
+    assert (gx - gxt).abs().max() < TOL and (gw - gwt).abs().max() < TOL
+
+
+def test_conv2d_grouped_equals_slices(oracle):
+    """conv2d/tests.rs:404-464."""
+    be = OracleBackend(oracle)
+    g = gen(5)
+    x, w = be.randn(2, 9, 14, 14, gen=g), be.randn(15, 3, 3, 3, gen=g)
+    y, bwd = be.conv2d(x, w, groups=3)
+    gx, gw = bwd(d_exp_sum(y))
+    for i in range(3):
+        xg, wg = x[:, 3 * i:3 * i + 3].contiguous(), w[5 * i:5 * i + 5].contiguous()
+        yg, bwdg = be.conv2d(xg, wg)
+        assert (yg - y[:, 5 * i:5 * i + 5]).abs().max() < TOL
+        gxg, gwg = bwdg(d_exp_sum(yg))
+        assert (gxg - gx[:, 3 * i:3 * i + 3]).abs().max() < TOL
+        assert (gwg - gw[5 * i:5 * i + 5]).abs().max() < TOL
+
+
+def test_out_dim_formula(oracle):
+    assert oracle.conv2d_out_dim(56, 3, 1, 1, 1) == 56
+    assert oracle.conv2d_out_dim(28, 6, 3, 2, 1) == 9
+    assert oracle.conv2d_out_dim(7, 2, 4, 3, 1) == 3
+    with pytest.raises(AssertionError):
+        oracle.conv2d_out_dim(1, 5, 1, 0, 1)
