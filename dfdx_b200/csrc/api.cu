@@ -17,6 +17,7 @@ int conv2d_forward(int dtype, const b200_conv2d_op* o, const void* img, const si
 int conv2d_backward(int dtype, const b200_conv2d_op* o, const void* img, void* grad_img, const void* filters,
                     const size_t fs[4], void* grad_filters, const void* grad_out, void* ws, cudaStream_t stream);
 void tc_set_xform_mode(int mode);
+void tc_set_tile_n(int bn);
 
 namespace {
 
@@ -147,8 +148,15 @@ int b200_set_path(int path) {
 /* Testing hook: 0 = split f32 into tf32_rn(big) + small (default), 1 = rely on the tensor core
  * truncating raw f32 operands and only write the small copy. */
 int b200_set_tf32_split_mode(int mode) {
-  if (mode != 0 && mode != 1) return B200_ERR_UNSUPPORTED;
+  if (mode < 0 || mode > 7) return B200_ERR_UNSUPPORTED;   // bits 1, 2: timing experiments (wrong results)
   tc_set_xform_mode(mode);
+  return B200_OK;
+}
+
+/* Testing hook: force the N extent of the tensor-core tile (64, 128 or 256); 0 restores the heuristic. */
+int b200_set_tile_n(int bn) {
+  if (bn != 0 && bn != 64 && bn != 128 && bn != 256) return B200_ERR_UNSUPPORTED;
+  tc_set_tile_n(bn);
   return B200_OK;
 }
 

@@ -1,22 +1,29 @@
-// tcgen05 tensor-core GEMM for sm_100a: persistent, warp-specialised, TMA-fed.
+// tcgen05 tensor-core GEMMs for sm_100a: persistent, warp-specialised, TMA-fed.
 //
 //   C[b][128-row tile, BN-col tile] (beta) += sum_r sum_k A[b,r] * B[b,r]
 //
-// Data path per CTA (one CTA per SM, tiles assigned round-robin):
-//   warp 4      : TMA producer.  cp.async.bulk.tensor (tiled, 4-D maps [inner, outer, x, y]) brings a
-//                 128 x BK slice of A and a BN x BK slice of B into a STAGES-deep shared-memory ring,
-//                 128B-swizzled (f16, BK = 64) or 64B-swizzled (f32, BK = 16).  Operands are read in
-//                 place from dfdx's strides: K-major rows, or MN-major (the transposed views that
-//                 the backward GEMMs and `permute` produce) as 128/64-byte wide column chunks.
-//   warps 6..9  : (f32 only) 3xTF32 split.  Each raw f32 x in the stage is replaced by
-//                 big = tf32_rn(x) and a second copy small = tf32_rn(x - big) is written next to it.
-//   warp 5      : MMA issuer.  One thread issues tcgen05.mma (cta_group::1, M = 128, N = BN) from
-//                 shared-memory descriptors into a TMEM accumulator; f16: kind::f16 (K = 16 per
-//                 instruction); f32: kind::tf32 three times per k-step (small*big, big*small,
-//                 big*big; K = 8).  tcgen05.commit releases the stage / publishes the accumulator.
-//   warps 0..3  : epilogue.  tcgen05.ld the finished accumulator (double-buffered in TMEM so the
-//                 next tile's main loop overlaps), apply beta (0: never read C; 1: read-add), convert
-//                 and store through C's leading dimension.
+// Two kernels share the scaffolding (TMA producer warp -> shared-memory ring -> single-thread MMA
+// issuer -> TMEM accumulators -> epilogue warps; one CTA per SM, tiles assigned round-robin):
+//
+// gemm_f16_kernel   f16 operands, kind::f16, f32 accumulation in TMEM.  6 warps.  128B-swizzled stages
+//                   (BK = 64).  The accumulator is double-buffered in TMEM so the epilogue of tile i
+//                   overlaps the main loop of tile i+1.
+//
+// gemm_tf32x3_kernel  f32 operands as 3xTF32 (kind::tf32).  16 warps in four warpgroups:
+//                   WG3 = TMA producer warp + MMA warp, WG2 = operand split, WG0/WG1 = epilogue.
+//                   Each staged f32 x stays in place as the `big` operand (the tensor core reads its top
+//                   19 bits) and small = tf32_rn(x - trunc_tf32(x)) is written beside it; every k-step
+//                   issues small*big, big*small, big*big (K = 8).  The tensor core adds into its f32
+//                   accumulator with truncation, so the error of one long accumulation grows linearly
+//                   with K; therefore K is cut into chunks of 256: each chunk accumulates in one of two
+//                   TMEM buffers and the epilogue warpgroups add finished chunks into f32 registers
+//                   (round-to-nearest) while the next chunk runs.  setmaxnreg moves registers from the
+//                   producer / MMA / split warpgroups to the epilogue warpgroups.
+//
+// Operands are read in place from dfdx's strides: K-major rows, or MN-major (the transposed views that
+// the backward GEMMs and `permute` produce).  MN-major tiles are brought in as column chunks:
+// 64 x f16 under the 128B swizzle, 32 x f32 under the 128B swizzle with 32-byte atoms (the only
+// MN-major layout kind::tf32 accepts); K-major f32 tiles use the 64B swizzle (BK = 16).
 //
 // Every wait on an mbarrier is bounded: on expiry the CTA raises an abort flag in shared memory, all
 // roles drain, TMEM is freed, the kernel writes B200_ERR_DEVICE_TIMEOUT to the device status word and
@@ -145,31 +152,60 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_
   return d;
 }
 
+__device__ __forceinline__ void setmaxnreg_dec_40() { asm volatile("setmaxnreg.dec.sync.aligned.u32 40;"); }
+__device__ __forceinline__ void setmaxnreg_inc_216() { asm volatile("setmaxnreg.inc.sync.aligned.u32 216;"); }
+
 // ---------------------------------------------------------------------------------------------
 // Kernel configuration
 // ---------------------------------------------------------------------------------------------
 constexpr int BM = 128;
 
-template <int ESIZE, int BN>
-struct Cfg {
-  static constexpr int SWZ = (ESIZE == 2) ? 128 : 64;      // swizzle span = bytes per smem row
-  static constexpr int BK = SWZ / ESIZE;                    // k extent of a stage (elements)
-  static constexpr int CH = SWZ / ESIZE;                    // MN elements per MN-major chunk
-  static constexpr int KSTEPS = SWZ / 32;                   // 32 bytes of K per MMA instruction
-  static constexpr int A_BYTES = BM * SWZ;
-  static constexpr int B_BYTES = BN * SWZ;
-  static constexpr int RAW_BYTES = A_BYTES + B_BYTES;
-  static constexpr int STAGE_BYTES = RAW_BYTES * (ESIZE == 4 ? 2 : 1);   // f32: raw(big) + small copy
+// f16: every operand tile is made of 128-byte rows under the 128B swizzle.
+template <int BN>
+struct CfgH {
+  static constexpr int BK = 64;                             // k extent of a stage (elements)
+  static constexpr int CH = 64;                             // MN elements per MN-major chunk
+  static constexpr int KSTEPS = 4;                          // MMAs per stage (K = 16 each)
+  static constexpr int A_BYTES = BM * 128;
+  static constexpr int B_BYTES = BN * 128;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int STAGES_FIT = (192 * 1024) / STAGE_BYTES;
   static constexpr int STAGES = STAGES_FIT > 8 ? 8 : STAGES_FIT;
-  static constexpr int THREADS = (ESIZE == 4) ? 320 : 192;
+  static constexpr int THREADS = 192;
   static constexpr int TMEM_COLS = 2 * BN;
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024;          // + alignment slack
-  static constexpr uint32_t LAYOUT = (SWZ == 128) ? 2u : 4u;
-  static constexpr uint32_t SBO = 8 * SWZ;                  // 8 rows of one swizzle atom
-  static constexpr uint32_t MN_LBO = BK * SWZ;              // distance between MN-major chunks
-  static constexpr uint32_t MN_KADV = (ESIZE == 2 ? 2 : 1) * 8 * SWZ;  // k rows per MMA * row pitch
-  static constexpr uint32_t K_KADV = 32;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024;
+  static constexpr uint32_t LAYOUT = 2u;                    // SWIZZLE_128B
+  static constexpr uint32_t SBO = 1024;                     // 8 rows of 128 bytes
+  static constexpr uint32_t MN_LBO = BK * 128;              // distance between MN-major chunks
+  static constexpr uint32_t MN_KADV = 2 * 1024;             // 16 k rows per MMA
+  static constexpr uint32_t K_KADV = 32;                    // 16 elements of K per MMA
+};
+
+// f32 (3xTF32): K-major tiles are 64-byte rows under the 64B swizzle; MN-major tiles are chunks of
+// 32 columns x BK k-rows of 128 bytes under the 128B swizzle with 32-byte atoms.
+template <int BN>
+struct CfgS {
+  static constexpr int BK = 16;
+  static constexpr int CH = 32;
+  static constexpr int KSTEPS = 2;                          // k-steps per stage (K = 8 each), 3 MMAs per step
+  static constexpr int A_BYTES = BM * 64;
+  static constexpr int B_BYTES = BN * 64;
+  static constexpr int RAW_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGE_BYTES = 2 * RAW_BYTES;         // raw (big) + small copy
+  static constexpr int STAGES_FIT = (192 * 1024) / STAGE_BYTES;
+  static constexpr int STAGES = STAGES_FIT > 8 ? 8 : STAGES_FIT;
+  static constexpr int THREADS = 512;
+  static constexpr int TMEM_COLS = 2 * BN;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024;
+  static constexpr int CHUNK_KB = 16;                       // k-blocks per promotion chunk (K = 256)
+  static constexpr int HALF = BN / 2;                       // columns owned by one epilogue warpgroup
+  static constexpr uint32_t K_LAYOUT = 4u;                  // SWIZZLE_64B
+  static constexpr uint32_t K_SBO = 512;                    // 8 rows of 64 bytes
+  static constexpr uint32_t K_KADV = 32;                    // 8 elements of K per MMA
+  static constexpr uint32_t MN_LAYOUT = 1u;                 // SWIZZLE_128B_BASE32B
+  static constexpr uint32_t MN_SBO = 512;                   // 4 k-rows of 128 bytes
+  static constexpr uint32_t MN_LBO = BK * 128;              // distance between MN-major chunks
+  static constexpr uint32_t MN_KADV = 8 * 128;              // 8 k-rows per MMA
 };
 
 struct TcArgs {
@@ -184,21 +220,17 @@ struct TcArgs {
   void* c;
   long long c_b0, c_b1, ldc;      // element strides
   int beta;
-  int xform_mode;                 // f32: 0 = write big (tf32_rn) and small; 1 = small from truncation only
+  int xform_mode;                 // f32: 1 = big stays raw, write small only; 0 = also rewrite big = tf32_rn(x)
   long long wait_limit;           // clock cycles
   int* status;
 };
 
-template <typename OutT>
-__device__ __forceinline__ void store_chunk(OutT* dst, const uint32_t (&v)[32], int valid, int beta);
-
-template <>
-__device__ __forceinline__ void store_chunk<float>(float* dst, const uint32_t (&v)[32], int valid, int beta) {
+// 32 consecutive f32 accumulator columns of one output row -> global memory.
+__device__ __forceinline__ void store_chunk(float* dst, const float* v, int valid, int beta) {
   if (valid == 32) {
 #pragma unroll
     for (int q = 0; q < 8; ++q) {
-      float4 o = make_float4(__uint_as_float(v[4 * q]), __uint_as_float(v[4 * q + 1]),
-                             __uint_as_float(v[4 * q + 2]), __uint_as_float(v[4 * q + 3]));
+      float4 o = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
       if (beta) {
         const float4 old = *reinterpret_cast<const float4*>(dst + 4 * q);
         o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
@@ -209,21 +241,20 @@ __device__ __forceinline__ void store_chunk<float>(float* dst, const uint32_t (&
 #pragma unroll
     for (int q = 0; q < 32; ++q)
       if (q < valid) {
-        float o = __uint_as_float(v[q]);
+        float o = v[q];
         if (beta) o += dst[q];
         dst[q] = o;
       }
   }
 }
 
-template <>
-__device__ __forceinline__ void store_chunk<__half>(__half* dst, const uint32_t (&v)[32], int valid, int beta) {
+__device__ __forceinline__ void store_chunk(__half* dst, const float* v, int valid, int beta) {
   if (valid == 32) {
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
       float f[8];
 #pragma unroll
-      for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(v[8 * q + e]);
+      for (int e = 0; e < 8; ++e) f[e] = v[8 * q + e];
       if (beta) {
         const uint4 old = *reinterpret_cast<const uint4*>(dst + 8 * q);
         const __half2* oh = reinterpret_cast<const __half2*>(&old);
@@ -243,28 +274,60 @@ __device__ __forceinline__ void store_chunk<__half>(__half* dst, const uint32_t 
 #pragma unroll
     for (int q = 0; q < 32; ++q)
       if (q < valid) {
-        float o = __uint_as_float(v[q]);
+        float o = v[q];
         if (beta) o += __half2float(dst[q]);
         dst[q] = __float2half_rn(o);
       }
   }
 }
 
+struct TileCoord { int mt, nt, ib0, ib1; };
+__device__ __forceinline__ TileCoord decode_tile(const TcArgs& g, long long tile) {
+  const long long per_batch = (long long)g.m_tiles * g.n_tiles;
+  const long long bt = tile / per_batch;
+  const int rem = (int)(tile - bt * per_batch);
+  TileCoord t;
+  t.mt = rem % g.m_tiles; t.nt = rem / g.m_tiles;
+  t.ib1 = (int)(bt % g.nb1); t.ib0 = (int)(bt / g.nb1);
+  return t;
+}
+
+// Issues the TMA loads of one stage.  K-major operand: one box [BK, rows].  MN-major operand: one
+// box [CH, BK] per chunk of CH columns, chunks LBO bytes apart.
+template <int ROWS, int BK, int CH, uint32_t MN_LBO>
+__device__ __forceinline__ void load_operand(uint32_t dst, const CUtensorMap* map, uint32_t bar, bool mn_major,
+                                             int row0, int k0, int x, int y) {
+  if (!mn_major) {
+    tma_load_4d(dst, map, bar, k0, row0, x, y);
+  } else {
+#pragma unroll 1
+    for (int c = 0; c < ROWS / CH; ++c) tma_load_4d(dst + c * MN_LBO, map, bar, row0 + c * CH, k0, x, y);
+  }
+}
+
+__device__ __forceinline__ void teardown(int abort_flag, int* status) {
+  if (abort_flag) {
+    // Give copies that may still be in flight time to land before shared memory is released.
+    const long long t0 = clock64();
+    while (clock64() - t0 < 2000000) __nanosleep(1000);
+    if (threadIdx.x == 0) atomicExch(status, (int)B200_ERR_DEVICE_TIMEOUT);
+    __syncthreads();
+  }
+}
+
 // ---------------------------------------------------------------------------------------------
-// The kernel
+// f16 kernel
 // ---------------------------------------------------------------------------------------------
-template <int ESIZE, int BN>
-__global__ void __launch_bounds__(Cfg<ESIZE, BN>::THREADS, 1)
-gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
-               const TcArgs g) {
-  using C = Cfg<ESIZE, BN>;
-  using OutT = typename std::conditional<ESIZE == 2, __half, float>::type;
+template <int BN>
+__global__ void __launch_bounds__(CfgH<BN>::THREADS, 1)
+gemm_f16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+                const TcArgs g) {
+  using C = CfgH<BN>;
   constexpr int STAGES = C::STAGES;
 
   extern __shared__ uint8_t smem_dyn[];
   __shared__ __align__(8) uint64_t bar_full[STAGES];
   __shared__ __align__(8) uint64_t bar_empty[STAGES];
-  __shared__ __align__(8) uint64_t bar_xform[STAGES];
   __shared__ __align__(8) uint64_t bar_tfull[2];
   __shared__ __align__(8) uint64_t bar_tempty[2];
   __shared__ uint32_t tmem_slot;
@@ -278,7 +341,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(smem_u32(&bar_full[s]), 1);
       mbar_init(smem_u32(&bar_empty[s]), 1);
-      mbar_init(smem_u32(&bar_xform[s]), 128);
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(smem_u32(&bar_tfull[b]), 1);
@@ -299,9 +361,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = tmem_slot;
-
   const int total_kb = g.red * g.k_blocks;
-  const long long tiles_per_batch = (long long)g.m_tiles * g.n_tiles;
 
   if (warp == 4) {
     // ------------------------------------------------------------------ TMA producer
@@ -309,35 +369,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
       uint32_t it = 0;
       bool ok = true;
       for (long long tile = blockIdx.x; ok && tile < g.total_tiles; tile += gridDim.x) {
-        const long long bt = tile / tiles_per_batch;
-        const int rem = (int)(tile - bt * tiles_per_batch);
-        const int mt = rem % g.m_tiles, nt = rem / g.m_tiles;
-        const int ib1 = (int)(bt % g.nb1), ib0 = (int)(bt / g.nb1);
+        const TileCoord t = decode_tile(g, tile);
         for (int i = 0; i < total_kb; ++i, ++it) {
           const int r = i / g.k_blocks, kb = i - r * g.k_blocks;
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1u;
           if (!mbar_wait(smem_u32(&bar_empty[s]), ph ^ 1u, abortp, g.wait_limit)) { ok = false; break; }
           const uint32_t full = smem_u32(&bar_full[s]);
-          mbar_expect_tx(full, C::RAW_BYTES);
+          mbar_expect_tx(full, C::STAGE_BYTES);
           const uint32_t a_dst = smem_base + s * C::STAGE_BYTES;
-          const uint32_t b_dst = a_dst + C::A_BYTES;
-          const int ax = g.a_x1 * ib1 + g.a_xr * r, ay = g.a_y0 * ib0;
-          const int bx = g.b_x1 * ib1 + g.b_xr * r, by = g.b_y0 * ib0;
-          if (!g.a_mn) {
-            tma_load_4d(a_dst, &tma_a, full, kb * C::BK, mt * BM, ax, ay);
-          } else {
-#pragma unroll 1
-            for (int c = 0; c < BM / C::CH; ++c)
-              tma_load_4d(a_dst + c * C::MN_LBO, &tma_a, full, mt * BM + c * C::CH, kb * C::BK, ax, ay);
-          }
-          if (!g.b_mn) {
-            tma_load_4d(b_dst, &tma_b, full, kb * C::BK, nt * BN, bx, by);
-          } else {
-#pragma unroll 1
-            for (int c = 0; c < BN / C::CH; ++c)
-              tma_load_4d(b_dst + c * C::MN_LBO, &tma_b, full, nt * BN + c * C::CH, kb * C::BK, bx, by);
-          }
+          load_operand<BM, C::BK, C::CH, C::MN_LBO>(a_dst, &tma_a, full, g.a_mn, t.mt * BM, kb * C::BK,
+                                                     g.a_x1 * t.ib1 + g.a_xr * r, g.a_y0 * t.ib0);
+          load_operand<BN, C::BK, C::CH, C::MN_LBO>(a_dst + C::A_BYTES, &tma_b, full, g.b_mn, t.nt * BN, kb * C::BK,
+                                                     g.b_x1 * t.ib1 + g.b_xr * r, g.b_y0 * t.ib0);
         }
       }
     }
@@ -345,9 +389,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
   } else if (warp == 5) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      const uint32_t fmt = (ESIZE == 2) ? 0u : 2u;   // F16 / TF32 operand format
-      const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) |
-                             ((uint32_t)(g.a_mn ? 1 : 0) << 15) | ((uint32_t)(g.b_mn ? 1 : 0) << 16) |
+      // instruction descriptor: D = f32, A = B = f16, majors, N >> 3, M >> 4
+      const uint32_t idesc = (1u << 4) | ((uint32_t)(g.a_mn ? 1 : 0) << 15) | ((uint32_t)(g.b_mn ? 1 : 0) << 16) |
                              ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
       const uint32_t a_lbo = g.a_mn ? C::MN_LBO : 16u, b_lbo = g.b_mn ? C::MN_LBO : 16u;
       const uint32_t a_kadv = g.a_mn ? C::MN_KADV : C::K_KADV, b_kadv = g.b_mn ? C::MN_KADV : C::K_KADV;
@@ -361,8 +404,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
         for (int i = 0; i < total_kb; ++i, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1u;
-          const uint32_t ready = (ESIZE == 4) ? smem_u32(&bar_xform[s]) : smem_u32(&bar_full[s]);
-          if (!mbar_wait(ready, ph, abortp, g.wait_limit)) { ok = false; break; }
+          if (!mbar_wait(smem_u32(&bar_full[s]), ph, abortp, g.wait_limit)) { ok = false; break; }
           tc_fence_after();
           const uint32_t a_base = smem_base + s * C::STAGE_BYTES;
           const uint32_t b_base = a_base + C::A_BYTES;
@@ -370,16 +412,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
           for (int ks = 0; ks < C::KSTEPS; ++ks) {
             const uint64_t ad = make_smem_desc(a_base + ks * a_kadv, a_lbo, C::SBO, C::LAYOUT);
             const uint64_t bd = make_smem_desc(b_base + ks * b_kadv, b_lbo, C::SBO, C::LAYOUT);
-            const uint32_t acc = (i > 0 || ks > 0) ? 1u : 0u;
-            if constexpr (ESIZE == 2) {
-              umma<2>(d_tmem, ad, bd, idesc, acc);
-            } else {
-              const uint64_t ads = make_smem_desc(a_base + C::RAW_BYTES + ks * a_kadv, a_lbo, C::SBO, C::LAYOUT);
-              const uint64_t bds = make_smem_desc(b_base + C::RAW_BYTES + ks * b_kadv, b_lbo, C::SBO, C::LAYOUT);
-              umma<4>(d_tmem, ads, bd, idesc, acc);   // small * big
-              umma<4>(d_tmem, ad, bds, idesc, 1u);    // big * small
-              umma<4>(d_tmem, ad, bd, idesc, 1u);     // big * big
-            }
+            umma<2>(d_tmem, ad, bd, idesc, (i > 0 || ks > 0) ? 1u : 0u);
           }
           umma_commit(smem_u32(&bar_empty[s]));       // stage reusable once these MMAs retire
         }
@@ -387,89 +420,252 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
       }
     }
     __syncwarp();
-  } else if (warp < 4) {
-    // ------------------------------------------------------------------ epilogue
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 0..3)
     uint32_t tcount = 0;
     bool ok = true;
     for (long long tile = blockIdx.x; ok && tile < g.total_tiles; tile += gridDim.x, ++tcount) {
-      const long long bt = tile / tiles_per_batch;
-      const int rem = (int)(tile - bt * tiles_per_batch);
-      const int mt = rem % g.m_tiles, nt = rem / g.m_tiles;
-      const int ib1 = (int)(bt % g.nb1), ib0 = (int)(bt / g.nb1);
+      const TileCoord t = decode_tile(g, tile);
       const uint32_t buf = tcount & 1u, tph = (tcount >> 1) & 1u;
       if (!mbar_wait(smem_u32(&bar_tfull[buf]), tph, abortp, g.wait_limit)) { ok = false; break; }
       tc_fence_after();
-      const int row = mt * BM + warp * 32 + lane;
-      OutT* crow = (OutT*)g.c + ib0 * g.c_b0 + ib1 * g.c_b1 + (long long)row * g.ldc;
+      const int row = t.mt * BM + warp * 32 + lane;
+      __half* crow = (__half*)g.c + t.ib0 * g.c_b0 + t.ib1 * g.c_b1 + (long long)row * g.ldc;
       const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16) + buf * BN;
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
-        const int col0 = nt * BN + c * 32;
+        const int col0 = t.nt * BN + c * 32;
         if (col0 >= g.n) break;                      // warp-uniform
         uint32_t v[32];
         tmem_ld_32x32(taddr + c * 32, v);
         tmem_wait_ld();
         if (row < g.m) {
-          const int valid = (g.n - col0) < 32 ? (g.n - col0) : 32;
-          store_chunk<OutT>(crow + col0, v, valid, g.beta);
+          float f[32];
+#pragma unroll
+          for (int q = 0; q < 32; ++q) f[q] = __uint_as_float(v[q]);
+          store_chunk(crow + col0, f, (g.n - col0) < 32 ? (g.n - col0) : 32, g.beta);
         }
       }
       tc_fence_before();
       mbar_arrive(smem_u32(&bar_tempty[buf]));
     }
-  } else {
-    // ------------------------------------------------------------------ 3xTF32 split (f32 only)
-    if constexpr (ESIZE == 4) {
-      const int t = threadIdx.x - 192;
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  teardown(abort_flag, g.status);
+  if (warp == 5) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, C::TMEM_COLS);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// f32 kernel (3xTF32 with chunked promotion)
+// ---------------------------------------------------------------------------------------------
+template <int BN>
+__global__ void __launch_bounds__(CfgS<BN>::THREADS, 1)
+gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+                   const TcArgs g) {
+  using C = CfgS<BN>;
+  constexpr int STAGES = C::STAGES;
+  constexpr int PRODUCER_WARP = 12, MMA_WARP = 13;
+
+  extern __shared__ uint8_t smem_dyn[];
+  __shared__ __align__(8) uint64_t bar_full[STAGES];
+  __shared__ __align__(8) uint64_t bar_empty[STAGES];
+  __shared__ __align__(8) uint64_t bar_xform[STAGES];
+  __shared__ __align__(8) uint64_t bar_tfull[2];
+  __shared__ __align__(8) uint64_t bar_tempty[2];
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_flag;
+
+  const uint32_t smem_base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int wg = warp >> 2;
+  volatile int* abortp = &abort_flag;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(smem_u32(&bar_full[s]), 1);
+      mbar_init(smem_u32(&bar_empty[s]), 1);
+      mbar_init(smem_u32(&bar_xform[s]), 128);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(smem_u32(&bar_tfull[b]), 1);
+      mbar_init(smem_u32(&bar_tempty[b]), 256);
+    }
+    abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == MMA_WARP) {
+    tmem_alloc(smem_u32(&tmem_slot), C::TMEM_COLS);
+    tmem_relinquish();
+  }
+  if (warp == PRODUCER_WARP && lane == 0) {
+    tma_prefetch_desc(&tma_a);
+    tma_prefetch_desc(&tma_b);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_slot;
+  const int total_kb = g.red * g.k_blocks;
+
+  if (wg == 3) {
+    setmaxnreg_dec_40();
+    if (warp == PRODUCER_WARP && lane == 0) {
+      // ---------------------------------------------------------------- TMA producer
       uint32_t it = 0;
       bool ok = true;
       for (long long tile = blockIdx.x; ok && tile < g.total_tiles; tile += gridDim.x) {
+        const TileCoord t = decode_tile(g, tile);
         for (int i = 0; i < total_kb; ++i, ++it) {
+          const int r = i / g.k_blocks, kb = i - r * g.k_blocks;
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1u;
-          if (!mbar_wait(smem_u32(&bar_full[s]), ph, abortp, g.wait_limit)) { ok = false; break; }
-          const uint32_t raw = smem_base + s * C::STAGE_BYTES;
-#pragma unroll 4
-          for (int v = t; v < C::RAW_BYTES / 16; v += 128) {
-            uint32_t x[4], big[4], sm[4];
-            asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
-                         : "=r"(x[0]), "=r"(x[1]), "=r"(x[2]), "=r"(x[3]) : "r"(raw + v * 16));
+          if (!mbar_wait(smem_u32(&bar_empty[s]), ph ^ 1u, abortp, g.wait_limit)) { ok = false; break; }
+          const uint32_t full = smem_u32(&bar_full[s]);
+          mbar_expect_tx(full, C::RAW_BYTES);
+          const uint32_t a_dst = smem_base + s * C::STAGE_BYTES;
+          load_operand<BM, C::BK, C::CH, C::MN_LBO>(a_dst, &tma_a, full, g.a_mn, t.mt * BM, kb * C::BK,
+                                                     g.a_x1 * t.ib1 + g.a_xr * r, g.a_y0 * t.ib0);
+          load_operand<BN, C::BK, C::CH, C::MN_LBO>(a_dst + C::A_BYTES, &tma_b, full, g.b_mn, t.nt * BN, kb * C::BK,
+                                                     g.b_x1 * t.ib1 + g.b_xr * r, g.b_y0 * t.ib0);
+        }
+      }
+    } else if (warp == MMA_WARP && lane == 0) {
+      // ---------------------------------------------------------------- MMA issuer
+      // instruction descriptor: D = f32, A = B = tf32 (format 2), majors, N >> 3, M >> 4
+      const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(g.a_mn ? 1 : 0) << 15) |
+                             ((uint32_t)(g.b_mn ? 1 : 0) << 16) | ((uint32_t)(BN >> 3) << 17) |
+                             ((uint32_t)(BM >> 4) << 24);
+      const uint32_t a_lbo = g.a_mn ? C::MN_LBO : 16u, b_lbo = g.b_mn ? C::MN_LBO : 16u;
+      const uint32_t a_sbo = g.a_mn ? C::MN_SBO : C::K_SBO, b_sbo = g.b_mn ? C::MN_SBO : C::K_SBO;
+      const uint32_t a_lay = g.a_mn ? C::MN_LAYOUT : C::K_LAYOUT, b_lay = g.b_mn ? C::MN_LAYOUT : C::K_LAYOUT;
+      const uint32_t a_kadv = g.a_mn ? C::MN_KADV : C::K_KADV, b_kadv = g.b_mn ? C::MN_KADV : C::K_KADV;
+      uint32_t it = 0, ccount = 0;
+      bool ok = true;
+      for (long long tile = blockIdx.x; ok && tile < g.total_tiles; tile += gridDim.x) {
+        for (int kb0 = 0; ok && kb0 < total_kb; kb0 += C::CHUNK_KB, ++ccount) {
+          const uint32_t buf = ccount & 1u, cph = (ccount >> 1) & 1u;
+          if (!mbar_wait(smem_u32(&bar_tempty[buf]), cph ^ 1u, abortp, g.wait_limit)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t d_tmem = tmem_base + buf * BN;
+          const int nkb = (total_kb - kb0) < C::CHUNK_KB ? (total_kb - kb0) : C::CHUNK_KB;
+          for (int i = 0; i < nkb; ++i, ++it) {
+            const int s = it % STAGES;
+            const uint32_t ph = (it / STAGES) & 1u;
+            if (!mbar_wait(smem_u32(&bar_xform[s]), ph, abortp, g.wait_limit)) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t a_base = smem_base + s * C::STAGE_BYTES;
+            const uint32_t b_base = a_base + C::A_BYTES;
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const float xf = __uint_as_float(x[e]);
-              if (g.xform_mode == 0) {
-                asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(big[e]) : "f"(xf));
-              } else {
-                big[e] = x[e] & 0xffffe000u;         // what the tensor core keeps of a raw f32
+            for (int ks = 0; ks < C::KSTEPS; ++ks) {
+              const uint64_t ad = make_smem_desc(a_base + ks * a_kadv, a_lbo, a_sbo, a_lay);
+              const uint64_t bd = make_smem_desc(b_base + ks * b_kadv, b_lbo, b_sbo, b_lay);
+              const uint64_t ads = make_smem_desc(a_base + C::RAW_BYTES + ks * a_kadv, a_lbo, a_sbo, a_lay);
+              const uint64_t bds = make_smem_desc(b_base + C::RAW_BYTES + ks * b_kadv, b_lbo, b_sbo, b_lay);
+              if (g.xform_mode & 4) {                                         // bit 2: timing experiment
+                umma<4>(d_tmem, ad, bd, idesc, (i > 0 || ks > 0) ? 1u : 0u);
+                continue;
               }
-              float d = xf - __uint_as_float(big[e]);
-              if ((x[e] & 0x7f800000u) == 0x7f800000u) d = 0.f;   // inf / nan: keep them in `big` only
-              asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(sm[e]) : "f"(d));
+              umma<4>(d_tmem, ads, bd, idesc, (i > 0 || ks > 0) ? 1u : 0u);   // small * big
+              umma<4>(d_tmem, ad, bds, idesc, 1u);                            // big * small
+              umma<4>(d_tmem, ad, bd, idesc, 1u);                             // big * big
             }
-            if (g.xform_mode == 0)
-              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};"
-                           ::"r"(raw + v * 16), "r"(big[0]), "r"(big[1]), "r"(big[2]), "r"(big[3]) : "memory");
-            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};"
-                         ::"r"(raw + C::RAW_BYTES + v * 16), "r"(sm[0]), "r"(sm[1]), "r"(sm[2]), "r"(sm[3]) : "memory");
+            umma_commit(smem_u32(&bar_empty[s]));
           }
-          fence_proxy_async_smem();                   // generic-proxy writes -> visible to tcgen05.mma
-          mbar_arrive(smem_u32(&bar_xform[s]));
+          if (ok) umma_commit(smem_u32(&bar_tfull[buf]));
+        }
+      }
+    }
+    __syncwarp();
+  } else if (wg == 2) {
+    // ------------------------------------------------------------------ operand split (warps 8..11)
+    setmaxnreg_dec_40();
+    const int t = threadIdx.x - 256;
+    uint32_t it = 0;
+    bool ok = true;
+    for (long long tile = blockIdx.x; ok && tile < g.total_tiles; tile += gridDim.x) {
+      for (int i = 0; i < total_kb; ++i, ++it) {
+        const int s = it % STAGES;
+        const uint32_t ph = (it / STAGES) & 1u;
+        if (!mbar_wait(smem_u32(&bar_full[s]), ph, abortp, g.wait_limit)) { ok = false; break; }
+        const uint32_t raw = smem_base + s * C::STAGE_BYTES;
+        const int nvec = (g.xform_mode & 2) ? 0 : C::RAW_BYTES / 16;   // bit 1: timing experiment, no split
+#pragma unroll 2
+        for (int v = t; v < nvec; v += 128) {
+          uint32_t x[4], big[4], sm[4];
+          asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                       : "=r"(x[0]), "=r"(x[1]), "=r"(x[2]), "=r"(x[3]) : "r"(raw + v * 16));
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float xf = __uint_as_float(x[e]);
+            if (g.xform_mode == 0) {
+              asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(big[e]) : "f"(xf));
+            } else {
+              big[e] = x[e] & 0xffffe000u;           // what the tensor core keeps of a raw f32
+            }
+            float d = xf - __uint_as_float(big[e]);
+            if ((x[e] & 0x7f800000u) == 0x7f800000u) d = 0.f;   // inf / nan stay in `big` only
+            asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(sm[e]) : "f"(d));
+          }
+          if ((g.xform_mode & 1) == 0)
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};"
+                         ::"r"(raw + v * 16), "r"(big[0]), "r"(big[1]), "r"(big[2]), "r"(big[3]) : "memory");
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};"
+                       ::"r"(raw + C::RAW_BYTES + v * 16), "r"(sm[0]), "r"(sm[1]), "r"(sm[2]), "r"(sm[3]) : "memory");
+        }
+        fence_proxy_async_smem();                     // generic-proxy writes -> visible to tcgen05.mma
+        mbar_arrive(smem_u32(&bar_xform[s]));
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warpgroups 0 and 1)
+    setmaxnreg_inc_216();
+    const int quad = warp & 3;                        // TMEM lane quadrant this warp may read
+    const int col_base = wg * C::HALF;                // this warpgroup's half of the tile's columns
+    uint32_t ccount = 0;
+    bool ok = true;
+    for (long long tile = blockIdx.x; ok && tile < g.total_tiles; tile += gridDim.x) {
+      const TileCoord t = decode_tile(g, tile);
+      float acc[C::HALF];
+#pragma unroll
+      for (int q = 0; q < C::HALF; ++q) acc[q] = 0.f;
+      for (int kb0 = 0; kb0 < total_kb; kb0 += C::CHUNK_KB, ++ccount) {
+        const uint32_t buf = ccount & 1u, cph = (ccount >> 1) & 1u;
+        if (!mbar_wait(smem_u32(&bar_tfull[buf]), cph, abortp, g.wait_limit)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + buf * BN + col_base;
+#pragma unroll
+        for (int c = 0; c < C::HALF / 32; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32(taddr + c * 32, v);
+          tmem_wait_ld();
+#pragma unroll
+          for (int q = 0; q < 32; ++q) acc[c * 32 + q] += __uint_as_float(v[q]);   // round-to-nearest add
+        }
+        tc_fence_before();
+        mbar_arrive(smem_u32(&bar_tempty[buf]));
+      }
+      if (!ok) break;
+      const int row = t.mt * BM + quad * 32 + lane;
+      if (row < g.m) {
+        float* crow = (float*)g.c + t.ib0 * g.c_b0 + t.ib1 * g.c_b1 + (long long)row * g.ldc;
+#pragma unroll
+        for (int c = 0; c < C::HALF / 32; ++c) {
+          const int col0 = t.nt * BN + col_base + c * 32;
+          if (col0 < g.n) store_chunk(crow + col0, &acc[c * 32], (g.n - col0) < 32 ? (g.n - col0) : 32, g.beta);
         }
       }
     }
   }
 
-  // ---------------------------------------------------------------------- teardown
   tc_fence_before();
   __syncthreads();
-  if (abort_flag) {
-    // Give copies that may still be in flight time to land before shared memory is released.
-    const long long t0 = clock64();
-    while (clock64() - t0 < 2000000) __nanosleep(1000);
-    if (threadIdx.x == 0) atomicExch(g.status, (int)B200_ERR_DEVICE_TIMEOUT);
-    __syncthreads();
-  }
-  if (warp == 5) {
+  teardown(abort_flag, g.status);
+  if (warp == MMA_WARP) {
     tc_fence_after();
     tmem_dealloc(tmem_base, C::TMEM_COLS);
   }
@@ -578,7 +774,7 @@ Plan make_plan(const GemmProblem& p0) {
 // 4-D map [inner (unit stride), outer (ld), x, y]; box = [box_inner, box_outer, 1, 1].
 int encode_map(CUtensorMap* map, const void* base, size_t esize, int64_t inner, int64_t outer, int64_t ld,
                int64_t xn, int64_t xs, int64_t yn, int64_t ys, uint32_t box_inner, uint32_t box_outer,
-               uint32_t swz) {
+               CUtensorMapSwizzle sw) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return B200_ERR_CUDA;
   const cuuint64_t dims[4] = {(cuuint64_t)inner, (cuuint64_t)outer, (cuuint64_t)(xn > 0 ? xn : 1),
@@ -591,18 +787,18 @@ int encode_map(CUtensorMap* map, const void* base, size_t esize, int64_t inner, 
   const cuuint32_t box[4] = {box_inner, box_outer, 1, 1};
   const cuuint32_t estr[4] = {1, 1, 1, 1};
   const CUtensorMapDataType dt = (esize == 2) ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
-  const CUtensorMapSwizzle sw = (swz == 128) ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
   const CUresult r = fn(map, dt, 4, const_cast<void*>(base), dims, strides, box, estr,
                         CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? B200_OK : B200_ERR_UNSUPPORTED;
 }
 
-int g_xform_mode = 0;
+int g_xform_mode = 1;
+int g_force_bn = 0;   // 0 = choose by problem shape
 
-template <int ESIZE, int BN>
-int launch_cfg(const Plan& pl, cudaStream_t stream) {
-  using C = Cfg<ESIZE, BN>;
+// C: CfgH<BN> or CfgS<BN>; KERNEL: the matching kernel.
+template <typename C, int ESIZE, int BN, typename Kernel>
+int launch_cfg(const Plan& pl, cudaStream_t stream, Kernel kernel) {
   const GemmProblem& p = pl.p;
   DeviceState* ds = device_state();
   if (!ds || !ds->ready) return B200_ERR_CUDA;
@@ -612,17 +808,22 @@ int launch_cfg(const Plan& pl, cudaStream_t stream) {
   const bool b_mn = pl.lb.cols_contig;
   const bool reduce = p.red > 1;
   // x / y batch dimensions of each operand map and the coordinate multipliers the kernel applies.
-  const int64_t a_xn = reduce ? p.red : (p.a_b1 ? p.b1 : 1), a_xs = reduce ? p.a_red : p.a_b1;
-  const int64_t b_xn = reduce ? p.red : (p.b_b1 ? p.b1 : 1), b_xs = reduce ? p.b_red : p.b_b1;
+  const int64_t a_xn = reduce ? (p.a_red ? p.red : 1) : (p.a_b1 ? p.b1 : 1), a_xs = reduce ? p.a_red : p.a_b1;
+  const int64_t b_xn = reduce ? (p.b_red ? p.red : 1) : (p.b_b1 ? p.b1 : 1), b_xs = reduce ? p.b_red : p.b_b1;
   const int64_t a_yn = reduce ? 1 : (p.a_b0 ? p.b0 : 1), b_yn = reduce ? 1 : (p.b_b0 ? p.b0 : 1);
+
+  // Swizzle of the shared-memory tile: f16 128B everywhere; f32 64B for K-major rows, 128B with 32-byte
+  // atoms for MN-major chunks.
+  const CUtensorMapSwizzle sw_k = (ESIZE == 2) ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
+  const CUtensorMapSwizzle sw_mn = (ESIZE == 2) ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B;
 
   alignas(64) CUtensorMap ma, mb;
   int st;
-  if (!a_mn) st = encode_map(&ma, p.a, ESIZE, p.k, p.m, pl.la.ld, a_xn, a_xs, a_yn, p.a_b0, C::BK, BM, C::SWZ);
-  else       st = encode_map(&ma, p.a, ESIZE, p.m, p.k, pl.la.ld, a_xn, a_xs, a_yn, p.a_b0, C::CH, C::BK, C::SWZ);
+  if (!a_mn) st = encode_map(&ma, p.a, ESIZE, p.k, p.m, pl.la.ld, a_xn, a_xs, a_yn, p.a_b0, C::BK, BM, sw_k);
+  else       st = encode_map(&ma, p.a, ESIZE, p.m, p.k, pl.la.ld, a_xn, a_xs, a_yn, p.a_b0, C::CH, C::BK, sw_mn);
   if (st) return st;
-  if (!b_mn) st = encode_map(&mb, p.b, ESIZE, p.k, p.n, pl.lb.ld, b_xn, b_xs, b_yn, p.b_b0, C::BK, BN, C::SWZ);
-  else       st = encode_map(&mb, p.b, ESIZE, p.n, p.k, pl.lb.ld, b_xn, b_xs, b_yn, p.b_b0, C::CH, C::BK, C::SWZ);
+  if (!b_mn) st = encode_map(&mb, p.b, ESIZE, p.k, p.n, pl.lb.ld, b_xn, b_xs, b_yn, p.b_b0, C::BK, BN, sw_k);
+  else       st = encode_map(&mb, p.b, ESIZE, p.n, p.k, pl.lb.ld, b_xn, b_xs, b_yn, p.b_b0, C::CH, C::BK, sw_mn);
   if (st) return st;
 
   TcArgs g;
@@ -634,8 +835,8 @@ int launch_cfg(const Plan& pl, cudaStream_t stream) {
   g.red = (int)p.red;
   g.k_blocks = (int)((p.k + C::BK - 1) / C::BK);
   g.a_mn = a_mn; g.b_mn = b_mn;
-  g.a_x1 = (!reduce && a_xn > 1) ? 1 : 0; g.a_xr = (reduce && a_xn > 1 && p.a_red) ? 1 : 0; g.a_y0 = (a_yn > 1) ? 1 : 0;
-  g.b_x1 = (!reduce && b_xn > 1) ? 1 : 0; g.b_xr = (reduce && b_xn > 1 && p.b_red) ? 1 : 0; g.b_y0 = (b_yn > 1) ? 1 : 0;
+  g.a_x1 = (!reduce && a_xn > 1) ? 1 : 0; g.a_xr = (reduce && a_xn > 1) ? 1 : 0; g.a_y0 = (a_yn > 1) ? 1 : 0;
+  g.b_x1 = (!reduce && b_xn > 1) ? 1 : 0; g.b_xr = (reduce && b_xn > 1) ? 1 : 0; g.b_y0 = (b_yn > 1) ? 1 : 0;
   g.c = p.c; g.c_b0 = p.c_b0; g.c_b1 = p.c_b1; g.ldc = pl.ldc;
   g.beta = p.beta;
   g.xform_mode = g_xform_mode;
@@ -644,9 +845,15 @@ int launch_cfg(const Plan& pl, cudaStream_t stream) {
 
   const long long grid = g.total_tiles < ds->sm_count ? g.total_tiles : ds->sm_count;
   if (grid <= 0) return B200_OK;
-  gemm_tc_kernel<ESIZE, BN><<<(unsigned)grid, C::THREADS, C::SMEM_BYTES, stream>>>(ma, mb, g);
+  kernel<<<(unsigned)grid, C::THREADS, C::SMEM_BYTES, stream>>>(ma, mb, g);
   count_launch(true);
-  return note_cuda_error(cudaGetLastError(), "gemm_tc launch");
+  return note_cuda_error(cudaGetLastError(), "tensor-core gemm launch");
+}
+
+template <int ESIZE, int BN>
+int launch_bn(const Plan& pl, cudaStream_t stream) {
+  if constexpr (ESIZE == 2) return launch_cfg<CfgH<BN>, 2, BN>(pl, stream, gemm_f16_kernel<BN>);
+  else return launch_cfg<CfgS<BN>, 4, BN>(pl, stream, gemm_tf32x3_kernel<BN>);
 }
 
 template <int ESIZE>
@@ -658,21 +865,22 @@ int launch_es(const Plan& pl, cudaStream_t stream) {
     return ((p.m + BM - 1) / BM) * ((p.n + bn - 1) / bn) * p.b0 * p.b1;
   };
   // Widest N tile that still gives (nearly) every SM a tile; narrow tiles for narrow outputs.
+  const int64_t enough = ((int64_t)sms * 9) / 10;
   int bn = 64;
-  if (p.n > 128 && tiles(256) >= (sms * 9) / 10) bn = 256;
-  else if (p.n > 64 && tiles(128) >= (sms * 9) / 10) bn = 128;
-  else if (p.n > 64 && tiles(64) < sms / 2 && p.n > 128) bn = 64;
+  if (p.n > 128 && tiles(256) >= enough) bn = 256;
+  else if (p.n > 64 && tiles(128) >= enough) bn = 128;
+  if (g_force_bn) bn = g_force_bn;
   switch (bn) {
-    case 256: return launch_cfg<ESIZE, 256>(pl, stream);
-    case 128: return launch_cfg<ESIZE, 128>(pl, stream);
-    default: return launch_cfg<ESIZE, 64>(pl, stream);
+    case 256: return launch_bn<ESIZE, 256>(pl, stream);
+    case 128: return launch_bn<ESIZE, 128>(pl, stream);
+    default: return launch_bn<ESIZE, 64>(pl, stream);
   }
 }
 
-template <int ESIZE, int BN>
-int set_attr() {
-  return note_cuda_error(cudaFuncSetAttribute(gemm_tc_kernel<ESIZE, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                              Cfg<ESIZE, BN>::SMEM_BYTES), "cudaFuncSetAttribute");
+template <typename C, typename Kernel>
+int set_attr(Kernel kernel) {
+  return note_cuda_error(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES),
+                         "cudaFuncSetAttribute");
 }
 
 }  // namespace
@@ -681,12 +889,12 @@ bool tc_eligible(const GemmProblem& p) { return make_plan(p).ok; }
 
 int tc_setup_device() {
   int st = 0;
-  if ((st = set_attr<2, 64>())) return st;
-  if ((st = set_attr<2, 128>())) return st;
-  if ((st = set_attr<2, 256>())) return st;
-  if ((st = set_attr<4, 64>())) return st;
-  if ((st = set_attr<4, 128>())) return st;
-  if ((st = set_attr<4, 256>())) return st;
+  if ((st = set_attr<CfgH<64>>(gemm_f16_kernel<64>))) return st;
+  if ((st = set_attr<CfgH<128>>(gemm_f16_kernel<128>))) return st;
+  if ((st = set_attr<CfgH<256>>(gemm_f16_kernel<256>))) return st;
+  if ((st = set_attr<CfgS<64>>(gemm_tf32x3_kernel<64>))) return st;
+  if ((st = set_attr<CfgS<128>>(gemm_tf32x3_kernel<128>))) return st;
+  if ((st = set_attr<CfgS<256>>(gemm_tf32x3_kernel<256>))) return st;
   return encode_fn() ? B200_OK : B200_ERR_CUDA;
 }
 
@@ -698,5 +906,6 @@ int launch_gemm_tc(const GemmProblem& p, cudaStream_t stream) {
 }
 
 void tc_set_xform_mode(int mode) { g_xform_mode = mode; }
+void tc_set_tile_n(int bn) { g_force_bn = bn; }
 
 }  // namespace b200

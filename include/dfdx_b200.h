@@ -85,6 +85,9 @@ int b200_set_path(int path);
  * big = tf32_rn(x) and small = tf32_rn(x - big); 1 leaves x in place (the tensor core truncates it
  * to tf32) and only writes small = tf32_rn(x - trunc(x)). */
 int b200_set_tf32_split_mode(int mode);
+/* Tensor-core tile width override (testing / profiling): 64, 128 or 256 output columns per CTA tile;
+ * 0 (default) picks the widest tile that still gives every SM work. */
+int b200_set_tile_n(int bn);
 /* Number of kernel launches this library has enqueued since load (all threads). */
 uint64_t b200_launch_count(void);
 /* Of those, launches of tcgen05 tensor-core kernels. */

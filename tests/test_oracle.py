@@ -116,3 +116,28 @@ def test_out_dim_formula(oracle):
     assert oracle.conv2d_out_dim(7, 2, 4, 3, 1) == 3
     with pytest.raises(AssertionError):
         oracle.conv2d_out_dim(1, 5, 1, 0, 1)
+
+
+def test_cpu_baseline_port_matches_oracle(oracle):
+    """The timed CPU stand-in (oracle/cpu_baseline.c) computes the same MatMatBr forward / backward."""
+    import ctypes as C
+    import numpy as np
+    L = oracle.baseline_lib()
+    if not L.cpu_baseline_supported():
+        pytest.skip("host CPU lacks AVX2/FMA")
+    g = gen(9)
+    b, m, k, n = 3, 37, 70, 45
+    x = torch.randn(b, m, k, generator=g)
+    w = torch.randn(n, k, generator=g)
+    dy = torch.randn(b, m, n, generator=g)
+    want_y, bwd = oracle.matmul(x, w.permute(1, 0))
+    want_gx, want_gw = bwd(dy)
+    fp = lambda t: t.numpy().ctypes.data_as(C.POINTER(C.c_float))
+    st = lambda *v: (C.c_size_t * len(v))(*v)
+    y = torch.empty(b, m, n)
+    gx, gw = torch.zeros(b, m, k), torch.zeros(n, k)
+    L.cpu_matmat_br_forward(b, m, k, n, fp(x), st(m * k, k, 1), fp(w), st(1, k), fp(y))
+    L.cpu_matmat_br_backward(b, m, k, n, fp(x), st(m * k, k, 1), fp(gx), fp(w), st(1, k), fp(gw), fp(dy))
+    assert oracle.rel_frobenius(y, want_y) < 1e-6
+    assert oracle.rel_frobenius(gx, want_gx) < 1e-6
+    assert oracle.rel_frobenius(gw.permute(1, 0), want_gw) < 1e-6
