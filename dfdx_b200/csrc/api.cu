@@ -18,6 +18,7 @@ int conv2d_backward(int dtype, const b200_conv2d_op* o, const void* img, void* g
                     const size_t fs[4], void* grad_filters, const void* grad_out, void* ws, cudaStream_t stream);
 void tc_set_xform_mode(int mode);
 void tc_set_tile_n(int bn);
+void tc_set_mn_box5(int on);
 
 namespace {
 
@@ -157,6 +158,13 @@ int b200_set_tf32_split_mode(int mode) {
 int b200_set_tile_n(int bn) {
   if (bn != 0 && bn != 64 && bn != 128 && bn != 256) return B200_ERR_UNSUPPORTED;
   tc_set_tile_n(bn);
+  return B200_OK;
+}
+
+/* Testing hook: 1 (default) loads MN-major operands with one 5-D TMA box per stage where the extent is a
+ * whole number of column chunks; 0 always uses one 4-D box per chunk. */
+int b200_set_mn_single_box(int on) {
+  tc_set_mn_box5(on ? 1 : 0);
   return B200_OK;
 }
 

@@ -97,6 +97,22 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map
       " [%0], [%1, {%3, %4, %5, %6}], [%2];"
       ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
 }
+__device__ __forceinline__ void tma_load_5d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
+                                            int c0, int c1, int c2, int c3, int c4) {
+  asm volatile(
+      "cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4) : "memory");
+}
+// 32 lanes x 16 consecutive 32-bit columns.
+__device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, uint32_t (&v)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+        "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+      : "r"(taddr) : "memory");
+}
 __device__ __forceinline__ void tmem_alloc(uint32_t slot_smem, uint32_t cols) {
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot_smem), "r"(cols) : "memory");
 }
@@ -152,8 +168,8 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_
   return d;
 }
 
-__device__ __forceinline__ void setmaxnreg_dec_40() { asm volatile("setmaxnreg.dec.sync.aligned.u32 40;"); }
-__device__ __forceinline__ void setmaxnreg_inc_216() { asm volatile("setmaxnreg.inc.sync.aligned.u32 216;"); }
+__device__ __forceinline__ void setmaxnreg_dec_56() { asm volatile("setmaxnreg.dec.sync.aligned.u32 56;"); }
+__device__ __forceinline__ void setmaxnreg_inc_200() { asm volatile("setmaxnreg.inc.sync.aligned.u32 200;"); }
 
 // ---------------------------------------------------------------------------------------------
 // Kernel configuration
@@ -215,6 +231,7 @@ struct TcArgs {
   long long total_tiles;
   int red, k_blocks;              // k iterations per tile = red * k_blocks
   int a_mn, b_mn;                 // operand is MN-major (else K-major)
+  int a_ld, b_ld;                 // load_operand mode: 0 K-major, 1 MN-major per chunk, 2 MN-major one box
   int a_x1, a_xr, a_y0;           // TMA x = a_x1*ib1 + a_xr*r ; y = a_y0*ib0
   int b_x1, b_xr, b_y0;
   void* c;
@@ -292,13 +309,17 @@ __device__ __forceinline__ TileCoord decode_tile(const TcArgs& g, long long tile
   return t;
 }
 
-// Issues the TMA loads of one stage.  K-major operand: one box [BK, rows].  MN-major operand: one
-// box [CH, BK] per chunk of CH columns, chunks LBO bytes apart.
+// Issues the TMA loads of one stage.  mode 0, K-major operand: one 4-D box [BK, rows].  MN-major
+// operand: mode 2 = one 5-D box [CH, BK, rows/CH] over the view (CH, K, MN/CH, x, y) of the matrix
+// (needs MN % CH == 0); mode 1 = one 4-D box [CH, BK] per chunk of CH columns.  Either way chunk c of
+// the tile lands at dst + c * MN_LBO.
 template <int ROWS, int BK, int CH, uint32_t MN_LBO>
-__device__ __forceinline__ void load_operand(uint32_t dst, const CUtensorMap* map, uint32_t bar, bool mn_major,
+__device__ __forceinline__ void load_operand(uint32_t dst, const CUtensorMap* map, uint32_t bar, int mode,
                                              int row0, int k0, int x, int y) {
-  if (!mn_major) {
+  if (mode == 0) {
     tma_load_4d(dst, map, bar, k0, row0, x, y);
+  } else if (mode == 2) {
+    tma_load_5d(dst, map, bar, 0, k0, row0 / CH, x, y);
   } else {
 #pragma unroll 1
     for (int c = 0; c < ROWS / CH; ++c) tma_load_4d(dst + c * MN_LBO, map, bar, row0 + c * CH, k0, x, y);
@@ -378,9 +399,9 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
           const uint32_t full = smem_u32(&bar_full[s]);
           mbar_expect_tx(full, C::STAGE_BYTES);
           const uint32_t a_dst = smem_base + s * C::STAGE_BYTES;
-          load_operand<BM, C::BK, C::CH, C::MN_LBO>(a_dst, &tma_a, full, g.a_mn, t.mt * BM, kb * C::BK,
+          load_operand<BM, C::BK, C::CH, C::MN_LBO>(a_dst, &tma_a, full, g.a_ld, t.mt * BM, kb * C::BK,
                                                      g.a_x1 * t.ib1 + g.a_xr * r, g.a_y0 * t.ib0);
-          load_operand<BN, C::BK, C::CH, C::MN_LBO>(a_dst + C::A_BYTES, &tma_b, full, g.b_mn, t.nt * BN, kb * C::BK,
+          load_operand<BN, C::BK, C::CH, C::MN_LBO>(a_dst + C::A_BYTES, &tma_b, full, g.b_ld, t.nt * BN, kb * C::BK,
                                                      g.b_x1 * t.ib1 + g.b_xr * r, g.b_y0 * t.ib0);
         }
       }
@@ -460,6 +481,71 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
   }
 }
 
+// 3xTF32 operand split of the stages, run by SPLIT_THREADS threads (tt = 0 .. SPLIT_THREADS-1).
+// Each raw f32 x stays in place as the `big` operand (the tensor core reads its top 19 bits) and
+// small = tf32_rn(x - trunc_tf32(x)) is written RAW_BYTES further on.  Four 16-byte vectors are in
+// flight per thread to cover the shared-memory latency.
+constexpr int SPLIT_THREADS = 192;
+
+template <typename C>
+__device__ __forceinline__ void split_role(const TcArgs& g, uint32_t smem_base, uint64_t* bar_full,
+                                           uint64_t* bar_xform, volatile int* abortp, int total_kb, int tt) {
+  constexpr int STAGES = C::STAGES;
+  constexpr int NVEC = C::RAW_BYTES / 16;
+  uint32_t it = 0;
+  bool ok = true;
+  for (long long tile = blockIdx.x; ok && tile < g.total_tiles; tile += gridDim.x) {
+    for (int i = 0; i < total_kb; ++i, ++it) {
+      const int s = it % STAGES;
+      const uint32_t ph = (it / STAGES) & 1u;
+      if (!mbar_wait(smem_u32(&bar_full[s]), ph, abortp, g.wait_limit)) { ok = false; break; }
+      const uint32_t raw = smem_base + s * C::STAGE_BYTES;
+      const int nvec = (g.xform_mode & 2) ? 0 : NVEC;   // bit 1: timing experiment, no split
+#pragma unroll 1
+      for (int v0 = tt; v0 < nvec; v0 += 4 * SPLIT_THREADS) {
+        uint32_t x[4][4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int v = v0 + u * SPLIT_THREADS;
+          if (v < NVEC)
+            asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                         : "=r"(x[u][0]), "=r"(x[u][1]), "=r"(x[u][2]), "=r"(x[u][3]) : "r"(raw + v * 16));
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int v = v0 + u * SPLIT_THREADS;
+          if (v < NVEC) {
+            uint32_t sm[4];
+            if ((g.xform_mode & 1) == 0) {              // optional: rewrite big = tf32_rn(x) as well
+              uint32_t big[4];
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(big[e]) : "f"(__uint_as_float(x[u][e])));
+                float d = __uint_as_float(x[u][e]) - __uint_as_float(big[e]);
+                d = (d != d) ? 0.f : d;
+                asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(sm[e]) : "f"(d));
+              }
+              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};"
+                           ::"r"(raw + v * 16), "r"(big[0]), "r"(big[1]), "r"(big[2]), "r"(big[3]) : "memory");
+            } else {
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                float d = __uint_as_float(x[u][e]) - __uint_as_float(x[u][e] & 0xffffe000u);
+                d = (d != d) ? 0.f : d;                 // inf - inf: keep inf / nan in `big` only
+                asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(sm[e]) : "f"(d));
+              }
+            }
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};"
+                         ::"r"(raw + C::RAW_BYTES + v * 16), "r"(sm[0]), "r"(sm[1]), "r"(sm[2]), "r"(sm[3]) : "memory");
+          }
+        }
+      }
+      fence_proxy_async_smem();                         // generic-proxy writes -> visible to tcgen05.mma
+      mbar_arrive(smem_u32(&bar_xform[s]));
+    }
+  }
+}
+
 // ---------------------------------------------------------------------------------------------
 // f32 kernel (3xTF32 with chunked promotion)
 // ---------------------------------------------------------------------------------------------
@@ -489,7 +575,7 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_const
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(smem_u32(&bar_full[s]), 1);
       mbar_init(smem_u32(&bar_empty[s]), 1);
-      mbar_init(smem_u32(&bar_xform[s]), 128);
+      mbar_init(smem_u32(&bar_xform[s]), SPLIT_THREADS);
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(smem_u32(&bar_tfull[b]), 1);
@@ -513,7 +599,7 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_const
   const int total_kb = g.red * g.k_blocks;
 
   if (wg == 3) {
-    setmaxnreg_dec_40();
+    setmaxnreg_dec_56();
     if (warp == PRODUCER_WARP && lane == 0) {
       // ---------------------------------------------------------------- TMA producer
       uint32_t it = 0;
@@ -528,9 +614,9 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_const
           const uint32_t full = smem_u32(&bar_full[s]);
           mbar_expect_tx(full, C::RAW_BYTES);
           const uint32_t a_dst = smem_base + s * C::STAGE_BYTES;
-          load_operand<BM, C::BK, C::CH, C::MN_LBO>(a_dst, &tma_a, full, g.a_mn, t.mt * BM, kb * C::BK,
+          load_operand<BM, C::BK, C::CH, C::MN_LBO>(a_dst, &tma_a, full, g.a_ld, t.mt * BM, kb * C::BK,
                                                      g.a_x1 * t.ib1 + g.a_xr * r, g.a_y0 * t.ib0);
-          load_operand<BN, C::BK, C::CH, C::MN_LBO>(a_dst + C::A_BYTES, &tma_b, full, g.b_mn, t.nt * BN, kb * C::BK,
+          load_operand<BN, C::BK, C::CH, C::MN_LBO>(a_dst + C::A_BYTES, &tma_b, full, g.b_ld, t.nt * BN, kb * C::BK,
                                                      g.b_x1 * t.ib1 + g.b_xr * r, g.b_y0 * t.ib0);
         }
       }
@@ -580,50 +666,18 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_const
         }
       }
     }
+    else if (warp >= 14) {
+      // ---------------------------------------------------------------- operand split (warps 14, 15)
+      split_role<C>(g, smem_base, bar_full, bar_xform, abortp, total_kb, threadIdx.x - 448 + 128);
+    }
     __syncwarp();
   } else if (wg == 2) {
     // ------------------------------------------------------------------ operand split (warps 8..11)
-    setmaxnreg_dec_40();
-    const int t = threadIdx.x - 256;
-    uint32_t it = 0;
-    bool ok = true;
-    for (long long tile = blockIdx.x; ok && tile < g.total_tiles; tile += gridDim.x) {
-      for (int i = 0; i < total_kb; ++i, ++it) {
-        const int s = it % STAGES;
-        const uint32_t ph = (it / STAGES) & 1u;
-        if (!mbar_wait(smem_u32(&bar_full[s]), ph, abortp, g.wait_limit)) { ok = false; break; }
-        const uint32_t raw = smem_base + s * C::STAGE_BYTES;
-        const int nvec = (g.xform_mode & 2) ? 0 : C::RAW_BYTES / 16;   // bit 1: timing experiment, no split
-#pragma unroll 2
-        for (int v = t; v < nvec; v += 128) {
-          uint32_t x[4], big[4], sm[4];
-          asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
-                       : "=r"(x[0]), "=r"(x[1]), "=r"(x[2]), "=r"(x[3]) : "r"(raw + v * 16));
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const float xf = __uint_as_float(x[e]);
-            if (g.xform_mode == 0) {
-              asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(big[e]) : "f"(xf));
-            } else {
-              big[e] = x[e] & 0xffffe000u;           // what the tensor core keeps of a raw f32
-            }
-            float d = xf - __uint_as_float(big[e]);
-            if ((x[e] & 0x7f800000u) == 0x7f800000u) d = 0.f;   // inf / nan stay in `big` only
-            asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(sm[e]) : "f"(d));
-          }
-          if ((g.xform_mode & 1) == 0)
-            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};"
-                         ::"r"(raw + v * 16), "r"(big[0]), "r"(big[1]), "r"(big[2]), "r"(big[3]) : "memory");
-          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};"
-                       ::"r"(raw + C::RAW_BYTES + v * 16), "r"(sm[0]), "r"(sm[1]), "r"(sm[2]), "r"(sm[3]) : "memory");
-        }
-        fence_proxy_async_smem();                     // generic-proxy writes -> visible to tcgen05.mma
-        mbar_arrive(smem_u32(&bar_xform[s]));
-      }
-    }
+    setmaxnreg_dec_56();
+    split_role<C>(g, smem_base, bar_full, bar_xform, abortp, total_kb, threadIdx.x - 256);
   } else {
     // ------------------------------------------------------------------ epilogue (warpgroups 0 and 1)
-    setmaxnreg_inc_216();
+    setmaxnreg_inc_200();
     const int quad = warp & 3;                        // TMEM lane quadrant this warp may read
     const int col_base = wg * C::HALF;                // this warpgroup's half of the tile's columns
     uint32_t ccount = 0;
@@ -639,12 +693,12 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_const
         tc_fence_after();
         const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + buf * BN + col_base;
 #pragma unroll
-        for (int c = 0; c < C::HALF / 32; ++c) {
-          uint32_t v[32];
-          tmem_ld_32x32(taddr + c * 32, v);
+        for (int c = 0; c < C::HALF / 16; ++c) {
+          uint32_t v[16];
+          tmem_ld_32x16(taddr + c * 16, v);
           tmem_wait_ld();
 #pragma unroll
-          for (int q = 0; q < 32; ++q) acc[c * 32 + q] += __uint_as_float(v[q]);   // round-to-nearest add
+          for (int q = 0; q < 16; ++q) acc[c * 16 + q] += __uint_as_float(v[q]);   // round-to-nearest add
         }
         tc_fence_before();
         mbar_arrive(smem_u32(&bar_tempty[buf]));
@@ -771,6 +825,28 @@ Plan make_plan(const GemmProblem& p0) {
   return pl;
 }
 
+// 5-D map of an MN-major operand seen as (CH, K, MN/CH, x, y): element (e, k, c) sits at
+// (c*CH + e) + k*ld.  box = [CH, BK, chunks, 1, 1]: one TMA brings all column chunks of a tile.
+int encode_map_mn5(CUtensorMap* map, const void* base, size_t esize, int64_t mn, int64_t k, int64_t ld,
+                   int64_t xn, int64_t xs, int64_t yn, int64_t ys, uint32_t ch, uint32_t bk, uint32_t chunks,
+                   CUtensorMapSwizzle sw) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return B200_ERR_CUDA;
+  const cuuint64_t dims[5] = {ch, (cuuint64_t)k, (cuuint64_t)(mn / ch), (cuuint64_t)(xn > 0 ? xn : 1),
+                              (cuuint64_t)(yn > 0 ? yn : 1)};
+  const uint64_t ldb = (uint64_t)ld * esize;
+  const uint64_t xsb = (dims[3] > 1) ? (uint64_t)xs * esize : ldb;
+  const uint64_t ysb = (dims[4] > 1) ? (uint64_t)ys * esize : ldb;
+  const cuuint64_t strides[4] = {ldb, (cuuint64_t)ch * esize, xsb, ysb};
+  const cuuint32_t box[5] = {ch, bk, chunks, 1, 1};
+  const cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+  const CUtensorMapDataType dt = (esize == 2) ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+  const CUresult r = fn(map, dt, 5, const_cast<void*>(base), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? B200_OK : B200_ERR_UNSUPPORTED;
+}
+
 // 4-D map [inner (unit stride), outer (ld), x, y]; box = [box_inner, box_outer, 1, 1].
 int encode_map(CUtensorMap* map, const void* base, size_t esize, int64_t inner, int64_t outer, int64_t ld,
                int64_t xn, int64_t xs, int64_t yn, int64_t ys, uint32_t box_inner, uint32_t box_outer,
@@ -795,6 +871,7 @@ int encode_map(CUtensorMap* map, const void* base, size_t esize, int64_t inner, 
 
 int g_xform_mode = 1;
 int g_force_bn = 0;   // 0 = choose by problem shape
+int g_mn_box5 = 1;    // MN-major operands: one 5-D TMA box per stage where the extent allows
 
 // C: CfgH<BN> or CfgS<BN>; KERNEL: the matching kernel.
 template <typename C, int ESIZE, int BN, typename Kernel>
@@ -817,13 +894,21 @@ int launch_cfg(const Plan& pl, cudaStream_t stream, Kernel kernel) {
   const CUtensorMapSwizzle sw_k = (ESIZE == 2) ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
   const CUtensorMapSwizzle sw_mn = (ESIZE == 2) ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B;
 
+  // MN-major operands whose MN extent is a whole number of chunks come in with one 5-D box per stage
+  // (a partial last chunk would make that box read past the end of a row).
+  const int a_ld = !a_mn ? 0 : ((p.m % C::CH == 0 && g_mn_box5) ? 2 : 1);
+  const int b_ld = !b_mn ? 0 : ((p.n % C::CH == 0 && g_mn_box5) ? 2 : 1);
   alignas(64) CUtensorMap ma, mb;
   int st;
-  if (!a_mn) st = encode_map(&ma, p.a, ESIZE, p.k, p.m, pl.la.ld, a_xn, a_xs, a_yn, p.a_b0, C::BK, BM, sw_k);
-  else       st = encode_map(&ma, p.a, ESIZE, p.m, p.k, pl.la.ld, a_xn, a_xs, a_yn, p.a_b0, C::CH, C::BK, sw_mn);
+  if (a_ld == 0)      st = encode_map(&ma, p.a, ESIZE, p.k, p.m, pl.la.ld, a_xn, a_xs, a_yn, p.a_b0, C::BK, BM, sw_k);
+  else if (a_ld == 1) st = encode_map(&ma, p.a, ESIZE, p.m, p.k, pl.la.ld, a_xn, a_xs, a_yn, p.a_b0, C::CH, C::BK, sw_mn);
+  else                st = encode_map_mn5(&ma, p.a, ESIZE, p.m, p.k, pl.la.ld, a_xn, a_xs, a_yn, p.a_b0, C::CH, C::BK,
+                                          BM / C::CH, sw_mn);
   if (st) return st;
-  if (!b_mn) st = encode_map(&mb, p.b, ESIZE, p.k, p.n, pl.lb.ld, b_xn, b_xs, b_yn, p.b_b0, C::BK, BN, sw_k);
-  else       st = encode_map(&mb, p.b, ESIZE, p.n, p.k, pl.lb.ld, b_xn, b_xs, b_yn, p.b_b0, C::CH, C::BK, sw_mn);
+  if (b_ld == 0)      st = encode_map(&mb, p.b, ESIZE, p.k, p.n, pl.lb.ld, b_xn, b_xs, b_yn, p.b_b0, C::BK, BN, sw_k);
+  else if (b_ld == 1) st = encode_map(&mb, p.b, ESIZE, p.n, p.k, pl.lb.ld, b_xn, b_xs, b_yn, p.b_b0, C::CH, C::BK, sw_mn);
+  else                st = encode_map_mn5(&mb, p.b, ESIZE, p.n, p.k, pl.lb.ld, b_xn, b_xs, b_yn, p.b_b0, C::CH, C::BK,
+                                          BN / C::CH, sw_mn);
   if (st) return st;
 
   TcArgs g;
@@ -835,6 +920,7 @@ int launch_cfg(const Plan& pl, cudaStream_t stream, Kernel kernel) {
   g.red = (int)p.red;
   g.k_blocks = (int)((p.k + C::BK - 1) / C::BK);
   g.a_mn = a_mn; g.b_mn = b_mn;
+  g.a_ld = a_ld; g.b_ld = b_ld;
   g.a_x1 = (!reduce && a_xn > 1) ? 1 : 0; g.a_xr = (reduce && a_xn > 1) ? 1 : 0; g.a_y0 = (a_yn > 1) ? 1 : 0;
   g.b_x1 = (!reduce && b_xn > 1) ? 1 : 0; g.b_xr = (reduce && b_xn > 1) ? 1 : 0; g.b_y0 = (b_yn > 1) ? 1 : 0;
   g.c = p.c; g.c_b0 = p.c_b0; g.c_b1 = p.c_b1; g.ldc = pl.ldc;
@@ -864,11 +950,15 @@ int launch_es(const Plan& pl, cudaStream_t stream) {
   auto tiles = [&](int bn) {
     return ((p.m + BM - 1) / BM) * ((p.n + bn - 1) / bn) * p.b0 * p.b1;
   };
-  // Widest N tile that still gives (nearly) every SM a tile; narrow tiles for narrow outputs.
-  const int64_t enough = ((int64_t)sms * 9) / 10;
+  // Tile width by a wave model: time ~ ceil(tiles / SMs) * (cost of one tile of that width).  The
+  // relative per-tile costs are measured (a 128-wide tile takes about 3/4 of the time of a 256-wide
+  // one because its main loop is bound by shared-memory bandwidth, not by the tensor pipe).
+  const double w256 = 1.0, w128 = (ESIZE == 4) ? 0.75 : 0.87, w64 = (ESIZE == 4) ? 0.55 : 0.70;
+  auto waves = [&](int bn_) { return (double)((tiles(bn_) + sms - 1) / sms); };
   int bn = 64;
-  if (p.n > 128 && tiles(256) >= enough) bn = 256;
-  else if (p.n > 64 && tiles(128) >= enough) bn = 128;
+  double best = waves(64) * w64;
+  if (p.n > 64 && waves(128) * w128 <= best) { best = waves(128) * w128; bn = 128; }
+  if (p.n > 128 && waves(256) * w256 <= best) { best = waves(256) * w256; bn = 256; }
   if (g_force_bn) bn = g_force_bn;
   switch (bn) {
     case 256: return launch_bn<ESIZE, 256>(pl, stream);
@@ -907,5 +997,6 @@ int launch_gemm_tc(const GemmProblem& p, cudaStream_t stream) {
 
 void tc_set_xform_mode(int mode) { g_xform_mode = mode; }
 void tc_set_tile_n(int bn) { g_force_bn = bn; }
+void tc_set_mn_box5(int on) { g_mn_box5 = on; }
 
 }  // namespace b200

@@ -88,6 +88,9 @@ int b200_set_tf32_split_mode(int mode);
 /* Tensor-core tile width override (testing / profiling): 64, 128 or 256 output columns per CTA tile;
  * 0 (default) picks the widest tile that still gives every SM work. */
 int b200_set_tile_n(int bn);
+/* MN-major operand loading (testing / profiling): 1 (default) brings a tile's column chunks with one
+ * 5-D TMA box where the extent is a whole number of chunks; 0 always issues one 4-D box per chunk. */
+int b200_set_mn_single_box(int on);
 /* Number of kernel launches this library has enqueued since load (all threads). */
 uint64_t b200_launch_count(void);
 /* Of those, launches of tcgen05 tensor-core kernels. */
