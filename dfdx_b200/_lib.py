@@ -54,7 +54,11 @@ SIGNATURES = {
     "b200_conv2d_workspace_bytes": (_sz, [_i, C.POINTER(Conv2DOp), _i]),
     "b200_conv2d_forward": (_i, [_i, C.POINTER(Conv2DOp), _vp, _szp, _vp, _vp, _vp, _sz, _vp]),
     "b200_conv2d_backward": (_i, [_i, C.POINTER(Conv2DOp), _vp, _vp, _vp, _szp, _vp, _vp, _vp, _sz, _vp, _vp]),
+    "b200_conv2d_forward_noalloc": (_i, [_i, C.POINTER(Conv2DOp), _vp, _szp, _vp, _vp, _vp]),
 }
+
+# Capacity of the library-resident scratch of b200_conv2d_forward_noalloc (include/dfdx_b200.h).
+CONV2D_NOALLOC_SCRATCH_BYTES = 32 << 20
 
 _lib = None
 

@@ -6,6 +6,7 @@
 //   backward: patches (B, O, K, K, H, W) | filters_tr (G, C/G, O/G, K, K) | grad_filters_tr (B, G, C/G, O/G, K, K)
 // each region starts on a 256-byte boundary so the GEMM operands stay TMA-addressable.
 #include "common.cuh"
+#include <mutex>
 
 namespace b200 {
 namespace {
@@ -237,3 +238,69 @@ int conv2d_backward(int dtype, const b200_conv2d_op* o, const void* img, void* g
 }
 
 }  // namespace b200
+
+// ------------------------------------------------------------------------------------------------
+// conv2d forward for callers that cannot allocate device memory.
+//
+// Some users of this library have no way to obtain scratch memory at the moment they need a
+// convolution: a process that has handed every byte of the GPU to its own arena at start-up, a
+// latency-critical loop in which cudaMalloc's implicit device synchronisation is unacceptable, or a
+// component that is only ever given input and output buffers by its host application.  For them the
+// im2col patch buffer lives in a fixed array inside the library image instead of in a caller-provided
+// workspace.  The array costs B200_CONV2D_NOALLOC_SCRATCH_BYTES on every GPU on which the library is
+// loaded, for the life of the process, whether or not this entry point is ever called.
+// ------------------------------------------------------------------------------------------------
+namespace b200 {
+namespace {
+
+constexpr size_t NOALLOC_SCRATCH_BYTES = (size_t)B200_CONV2D_NOALLOC_SCRATCH_BYTES;
+
+// File-scope device array.  In host code this name is only a handle for the runtime's symbol
+// table, never a device address: the address a kernel can use comes from cudaGetSymbolAddress.
+static __device__ __align__(256) unsigned char g_noalloc_scratch[NOALLOC_SCRATCH_BYTES];
+
+constexpr int NOALLOC_MAX_DEVICES = 64;
+void* g_noalloc_ptr[NOALLOC_MAX_DEVICES] = {};
+std::mutex g_noalloc_mutex;
+
+// Resolves the array's address on the CURRENT device, once per device.
+int noalloc_scratch(void** out) {
+  int dev = -1;
+  int rc = note_cuda_error(cudaGetDevice(&dev), "cudaGetDevice");
+  if (rc) return rc;
+  if (dev < 0 || dev >= NOALLOC_MAX_DEVICES) return B200_ERR_LIMIT;
+  std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+  if (!g_noalloc_ptr[dev]) {
+    void* p = nullptr;
+    rc = note_cuda_error(cudaGetSymbolAddress(&p, g_noalloc_scratch), "cudaGetSymbolAddress(conv2d scratch)");
+    if (rc) return rc;
+    if (!p) return B200_ERR_CUDA;
+    g_noalloc_ptr[dev] = p;
+  }
+  *out = g_noalloc_ptr[dev];
+  return B200_OK;
+}
+
+}  // namespace
+}  // namespace b200
+
+extern "C" int b200_conv2d_forward_noalloc(int dtype, const b200_conv2d_op* op, const void* img,
+                                           const size_t img_strides[4], const void* filters, void* out,
+                                           void* stream) {
+  using namespace b200;
+  if (dtype_size(dtype) == 0) return B200_ERR_DTYPE;
+  if (!op || !img_strides) return B200_ERR_NULL;
+  if (!op->groups || !op->stride || !op->dilation || !op->kernel) return B200_ERR_SHAPE;
+  if (op->chan_in % op->groups || op->chan_out % op->groups) return B200_ERR_SHAPE;
+  const size_t need = conv2d_workspace_bytes(dtype, op, 0);
+  if (need == 0) return B200_OK;
+  if (need > NOALLOC_SCRATCH_BYTES) return B200_ERR_LIMIT;   // use b200_conv2d_forward with a workspace instead
+  if (!img || !filters || !out) return B200_ERR_NULL;
+  if (!device_state()) return note_cuda_error(cudaErrorInitializationError, "b200_init not called on this device");
+  void* scratch = nullptr;
+  const int rc = noalloc_scratch(&scratch);
+  if (rc) return rc;
+  // The unfold kernel writes every element of the patch buffer (zeros where a tap falls in the
+  // padding), so nothing left over from an earlier call is ever read: no clearing is needed.
+  return conv2d_forward(dtype, op, img, img_strides, filters, out, scratch, (cudaStream_t)stream);
+}

@@ -190,6 +190,30 @@ int b200_conv2d_backward(int dtype, const b200_conv2d_op* op,
                          const void* grad_out,
                          void* workspace, size_t workspace_bytes, void* stream, void* par_stream);
 
+/* ---- conv2d forward without any allocation ------------------------------------------------------ */
+
+/* Capacity of the library-resident scratch array used by b200_conv2d_forward_noalloc. */
+#define B200_CONV2D_NOALLOC_SCRATCH_BYTES (32u << 20)
+
+/* This entry point has no counterpart in the reference (dfdx always takes its patch buffer from
+ * `Cuda::get_workspace`).  It is `b200_conv2d_forward` for callers that cannot provide a workspace
+ * because they cannot allocate device memory where they run: the GPU's memory is already owned by their
+ * own arena, a cudaMalloc (which synchronises the device) is not acceptable in their loop, or they are
+ * handed nothing but input and output buffers.  The im2col patch buffer is a fixed
+ * B200_CONV2D_NOALLOC_SCRATCH_BYTES array inside the library image (held on every GPU that loads the
+ * library until the process exits); the call allocates and frees nothing.
+ *   - Limit: b200_conv2d_workspace_bytes(dtype, op, 0) must not exceed the capacity above, otherwise
+ *     B200_ERR_LIMIT is returned and nothing is launched (use b200_conv2d_forward with a workspace).
+ *   - b200_init(ordinal) must have been called for the current device.  The first call on each device also
+ *     looks up the array's device address; make that first call before starting any stream capture.
+ *   - All calls on a device share the one array.  Every call overwrites all of the part it uses, so earlier
+ *     contents never leak into a result; but two calls whose GPU work can overlap (different streams, or
+ *     different threads without ordering) race on it — serialise them on one stream or with events.
+ * Arguments and results are otherwise exactly those of b200_conv2d_forward. */
+int b200_conv2d_forward_noalloc(int dtype, const b200_conv2d_op* op,
+                                const void* img, const size_t img_strides[4],
+                                const void* filters, void* out, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
