@@ -19,6 +19,7 @@ int conv2d_backward(int dtype, const b200_conv2d_op* o, const void* img, void* g
 void tc_set_xform_mode(int mode);
 void tc_set_tile_n(int bn);
 void tc_set_mn_box5(int on);
+void tc_set_pair_mode(int mode);
 
 namespace {
 
@@ -149,7 +150,7 @@ int b200_set_path(int path) {
 /* Testing hook: 0 = split f32 into tf32_rn(big) + small (default), 1 = rely on the tensor core
  * truncating raw f32 operands and only write the small copy. */
 int b200_set_tf32_split_mode(int mode) {
-  if (mode < 0 || mode > 7) return B200_ERR_UNSUPPORTED;   // bits 1, 2: timing experiments (wrong results)
+  if (mode < 0 || mode > 15) return B200_ERR_UNSUPPORTED;   // bits 1, 2, 3: timing experiments (wrong results)
   tc_set_xform_mode(mode);
   return B200_OK;
 }
@@ -165,6 +166,14 @@ int b200_set_tile_n(int bn) {
  * whole number of column chunks; 0 always uses one 4-D box per chunk. */
 int b200_set_mn_single_box(int on) {
   tc_set_mn_box5(on ? 1 : 0);
+  return B200_OK;
+}
+
+/* Testing hook: 1 (default) single-CTA tensor-core kernels only, 0 planner's choice, 2 forces the CTA-pair
+ * kernels wherever the output is wider than 128 columns. */
+int b200_set_cta_pair_mode(int mode) {
+  if (mode < 0 || mode > 2) return B200_ERR_UNSUPPORTED;
+  tc_set_pair_mode(mode);
   return B200_OK;
 }
 

@@ -28,313 +28,22 @@
 // Every wait on an mbarrier is bounded: on expiry the CTA raises an abort flag in shared memory, all
 // roles drain, TMEM is freed, the kernel writes B200_ERR_DEVICE_TIMEOUT to the device status word and
 // returns normally.
-#include "common.cuh"
-#include <cuda.h>
+#include "tc_device.cuh"
 #include <mutex>
 
 namespace b200 {
+
+int pair_tile_m();
+int pair_tile_n();
+int pair_block_k(int esize);
+int pair_chunk(int esize);
+int pair_setup_device();
+int launch_pair(int esize, const CUtensorMap& ma, const CUtensorMap& mb, const tcx::TcArgs& g, int sm_count,
+                cudaStream_t stream);
+
 namespace {
 
-// ---------------------------------------------------------------------------------------------
-// PTX wrappers
-// ---------------------------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void* p) {
-  return (uint32_t)__cvta_generic_to_shared(p);
-}
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-  return ok;
-}
-// Bounded wait.  Returns false (and raises *abort_flag) if `limit` clock cycles pass, or as soon as
-// another role has raised the flag.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                          long long limit) {
-#pragma unroll 1
-  for (int i = 0; i < 64; ++i)
-    if (mbar_try_wait(bar, parity)) return true;
-  const long long t0 = clock64();
-#pragma unroll 1
-  for (;;) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if (*abort_flag) return false;
-    if (clock64() - t0 > limit) { *abort_flag = 1; return false; }
-  }
-}
-__device__ __forceinline__ void fence_mbar_init() {
-  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-}
-__device__ __forceinline__ void fence_proxy_async_smem() {
-  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-}
-__device__ __forceinline__ void tc_fence_before() {
-  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-}
-__device__ __forceinline__ void tc_fence_after() {
-  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-}
-__device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* m) {
-  asm volatile("prefetch.tensormap [%0];" ::"l"(m) : "memory");
-}
-// Tiled 4-D TMA load, completion counted in bytes on `bar`.  Coordinates innermost first.
-__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
-                                            int c0, int c1, int c2, int c3) {
-  asm volatile(
-      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes"
-      " [%0], [%1, {%3, %4, %5, %6}], [%2];"
-      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
-}
-__device__ __forceinline__ void tma_load_5d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
-                                            int c0, int c1, int c2, int c3, int c4) {
-  asm volatile(
-      "cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes"
-      " [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
-      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4) : "memory");
-}
-// 32 lanes x 16 consecutive 32-bit columns.
-__device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, uint32_t (&v)[16]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
-        "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
-      : "r"(taddr) : "memory");
-}
-__device__ __forceinline__ void tmem_alloc(uint32_t slot_smem, uint32_t cols) {
-  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot_smem), "r"(cols) : "memory");
-}
-__device__ __forceinline__ void tmem_relinquish() {
-  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
-  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-template <int ESIZE>
-__device__ __forceinline__ void umma(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
-                                     uint32_t accumulate) {
-  if constexpr (ESIZE == 2) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
-  } else {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
-  }
-}
-// 32 lanes x 32 consecutive 32-bit columns: thread i of the warp receives lane (base+i), columns c..c+31.
-__device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&v)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
-        "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
-        "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
-        "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-      : "r"(taddr) : "memory");
-}
-__device__ __forceinline__ void tmem_wait_ld() {
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
-
-// Shared-memory matrix descriptor (sm_100 format): start address, leading / stride byte offsets in
-// 16-byte units, descriptor version 1 at bit 46, swizzle mode at bits 61..63 (2 = 128B, 4 = 64B).
-__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes,
-                                                   uint32_t layout_type) {
-  uint64_t d = (uint64_t)((saddr & 0x3FFFFu) >> 4);
-  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16;
-  d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32;
-  d |= 1ull << 46;
-  d |= (uint64_t)layout_type << 61;
-  return d;
-}
-
-__device__ __forceinline__ void setmaxnreg_dec_56() { asm volatile("setmaxnreg.dec.sync.aligned.u32 56;"); }
-__device__ __forceinline__ void setmaxnreg_inc_200() { asm volatile("setmaxnreg.inc.sync.aligned.u32 200;"); }
-
-// ---------------------------------------------------------------------------------------------
-// Kernel configuration
-// ---------------------------------------------------------------------------------------------
-constexpr int BM = 128;
-
-// f16: every operand tile is made of 128-byte rows under the 128B swizzle.
-template <int BN>
-struct CfgH {
-  static constexpr int BK = 64;                             // k extent of a stage (elements)
-  static constexpr int CH = 64;                             // MN elements per MN-major chunk
-  static constexpr int KSTEPS = 4;                          // MMAs per stage (K = 16 each)
-  static constexpr int A_BYTES = BM * 128;
-  static constexpr int B_BYTES = BN * 128;
-  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int STAGES_FIT = (192 * 1024) / STAGE_BYTES;
-  static constexpr int STAGES = STAGES_FIT > 8 ? 8 : STAGES_FIT;
-  static constexpr int THREADS = 192;
-  static constexpr int TMEM_COLS = 2 * BN;
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024;
-  static constexpr uint32_t LAYOUT = 2u;                    // SWIZZLE_128B
-  static constexpr uint32_t SBO = 1024;                     // 8 rows of 128 bytes
-  static constexpr uint32_t MN_LBO = BK * 128;              // distance between MN-major chunks
-  static constexpr uint32_t MN_KADV = 2 * 1024;             // 16 k rows per MMA
-  static constexpr uint32_t K_KADV = 32;                    // 16 elements of K per MMA
-};
-
-// f32 (3xTF32): K-major tiles are 64-byte rows under the 64B swizzle; MN-major tiles are chunks of
-// 32 columns x BK k-rows of 128 bytes under the 128B swizzle with 32-byte atoms.
-template <int BN>
-struct CfgS {
-  static constexpr int BK = 16;
-  static constexpr int CH = 32;
-  static constexpr int KSTEPS = 2;                          // k-steps per stage (K = 8 each), 3 MMAs per step
-  static constexpr int A_BYTES = BM * 64;
-  static constexpr int B_BYTES = BN * 64;
-  static constexpr int RAW_BYTES = A_BYTES + B_BYTES;
-  static constexpr int STAGE_BYTES = 2 * RAW_BYTES;         // raw (big) + small copy
-  static constexpr int STAGES_FIT = (192 * 1024) / STAGE_BYTES;
-  static constexpr int STAGES = STAGES_FIT > 8 ? 8 : STAGES_FIT;
-  static constexpr int THREADS = 512;
-  static constexpr int TMEM_COLS = 2 * BN;
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024;
-  static constexpr int CHUNK_KB = 16;                       // k-blocks per promotion chunk (K = 256)
-  static constexpr int HALF = BN / 2;                       // columns owned by one epilogue warpgroup
-  static constexpr uint32_t K_LAYOUT = 4u;                  // SWIZZLE_64B
-  static constexpr uint32_t K_SBO = 512;                    // 8 rows of 64 bytes
-  static constexpr uint32_t K_KADV = 32;                    // 8 elements of K per MMA
-  static constexpr uint32_t MN_LAYOUT = 1u;                 // SWIZZLE_128B_BASE32B
-  static constexpr uint32_t MN_SBO = 512;                   // 4 k-rows of 128 bytes
-  static constexpr uint32_t MN_LBO = BK * 128;              // distance between MN-major chunks
-  static constexpr uint32_t MN_KADV = 8 * 128;              // 8 k-rows per MMA
-};
-
-struct TcArgs {
-  int m, n;                       // output extent of one batch item
-  int m_tiles, n_tiles;
-  int nb1;                        // inner batch count (tile id -> (b0, b1))
-  long long total_tiles;
-  int red, k_blocks;              // k iterations per tile = red * k_blocks
-  int a_mn, b_mn;                 // operand is MN-major (else K-major)
-  int a_ld, b_ld;                 // load_operand mode: 0 K-major, 1 MN-major per chunk, 2 MN-major one box
-  int a_x1, a_xr, a_y0;           // TMA x = a_x1*ib1 + a_xr*r ; y = a_y0*ib0
-  int b_x1, b_xr, b_y0;
-  void* c;
-  long long c_b0, c_b1, ldc;      // element strides
-  int beta;
-  int xform_mode;                 // f32: 1 = big stays raw, write small only; 0 = also rewrite big = tf32_rn(x)
-  long long wait_limit;           // clock cycles
-  int* status;
-};
-
-// 32 consecutive f32 accumulator columns of one output row -> global memory.
-__device__ __forceinline__ void store_chunk(float* dst, const float* v, int valid, int beta) {
-  if (valid == 32) {
-#pragma unroll
-    for (int q = 0; q < 8; ++q) {
-      float4 o = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
-      if (beta) {
-        const float4 old = *reinterpret_cast<const float4*>(dst + 4 * q);
-        o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
-      }
-      *reinterpret_cast<float4*>(dst + 4 * q) = o;
-    }
-  } else {
-#pragma unroll
-    for (int q = 0; q < 32; ++q)
-      if (q < valid) {
-        float o = v[q];
-        if (beta) o += dst[q];
-        dst[q] = o;
-      }
-  }
-}
-
-__device__ __forceinline__ void store_chunk(__half* dst, const float* v, int valid, int beta) {
-  if (valid == 32) {
-#pragma unroll
-    for (int q = 0; q < 4; ++q) {
-      float f[8];
-#pragma unroll
-      for (int e = 0; e < 8; ++e) f[e] = v[8 * q + e];
-      if (beta) {
-        const uint4 old = *reinterpret_cast<const uint4*>(dst + 8 * q);
-        const __half2* oh = reinterpret_cast<const __half2*>(&old);
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const float2 t = __half22float2(oh[e]);
-          f[2 * e] += t.x; f[2 * e + 1] += t.y;
-        }
-      }
-      uint4 pk;
-      __half2* ph = reinterpret_cast<__half2*>(&pk);
-#pragma unroll
-      for (int e = 0; e < 4; ++e) ph[e] = __floats2half2_rn(f[2 * e], f[2 * e + 1]);
-      *reinterpret_cast<uint4*>(dst + 8 * q) = pk;
-    }
-  } else {
-#pragma unroll
-    for (int q = 0; q < 32; ++q)
-      if (q < valid) {
-        float o = v[q];
-        if (beta) o += __half2float(dst[q]);
-        dst[q] = __float2half_rn(o);
-      }
-  }
-}
-
-struct TileCoord { int mt, nt, ib0, ib1; };
-__device__ __forceinline__ TileCoord decode_tile(const TcArgs& g, long long tile) {
-  const long long per_batch = (long long)g.m_tiles * g.n_tiles;
-  const long long bt = tile / per_batch;
-  const int rem = (int)(tile - bt * per_batch);
-  TileCoord t;
-  t.mt = rem % g.m_tiles; t.nt = rem / g.m_tiles;
-  t.ib1 = (int)(bt % g.nb1); t.ib0 = (int)(bt / g.nb1);
-  return t;
-}
-
-// Issues the TMA loads of one stage.  mode 0, K-major operand: one 4-D box [BK, rows].  MN-major
-// operand: mode 2 = one 5-D box [CH, BK, rows/CH] over the view (CH, K, MN/CH, x, y) of the matrix
-// (needs MN % CH == 0); mode 1 = one 4-D box [CH, BK] per chunk of CH columns.  Either way chunk c of
-// the tile lands at dst + c * MN_LBO.
-template <int ROWS, int BK, int CH, uint32_t MN_LBO>
-__device__ __forceinline__ void load_operand(uint32_t dst, const CUtensorMap* map, uint32_t bar, int mode,
-                                             int row0, int k0, int x, int y) {
-  if (mode == 0) {
-    tma_load_4d(dst, map, bar, k0, row0, x, y);
-  } else if (mode == 2) {
-    tma_load_5d(dst, map, bar, 0, k0, row0 / CH, x, y);
-  } else {
-#pragma unroll 1
-    for (int c = 0; c < ROWS / CH; ++c) tma_load_4d(dst + c * MN_LBO, map, bar, row0 + c * CH, k0, x, y);
-  }
-}
-
-__device__ __forceinline__ void teardown(int abort_flag, int* status) {
-  if (abort_flag) {
-    // Give copies that may still be in flight time to land before shared memory is released.
-    const long long t0 = clock64();
-    while (clock64() - t0 < 2000000) __nanosleep(1000);
-    if (threadIdx.x == 0) atomicExch(status, (int)B200_ERR_DEVICE_TIMEOUT);
-    __syncthreads();
-  }
-}
+using namespace tcx;
 
 // ---------------------------------------------------------------------------------------------
 // f16 kernel
@@ -397,6 +106,7 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
           const uint32_t ph = (it / STAGES) & 1u;
           if (!mbar_wait(smem_u32(&bar_empty[s]), ph ^ 1u, abortp, g.wait_limit)) { ok = false; break; }
           const uint32_t full = smem_u32(&bar_full[s]);
+          if (g.xform_mode & 8) { mbar_arrive(full); continue; }   // timing experiment: no loads
           mbar_expect_tx(full, C::STAGE_BYTES);
           const uint32_t a_dst = smem_base + s * C::STAGE_BYTES;
           load_operand<BM, C::BK, C::CH, C::MN_LBO>(a_dst, &tma_a, full, g.a_ld, t.mt * BM, kb * C::BK,
@@ -433,6 +143,7 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
           for (int ks = 0; ks < C::KSTEPS; ++ks) {
             const uint64_t ad = make_smem_desc(a_base + ks * a_kadv, a_lbo, C::SBO, C::LAYOUT);
             const uint64_t bd = make_smem_desc(b_base + ks * b_kadv, b_lbo, C::SBO, C::LAYOUT);
+            if ((g.xform_mode & 4) && ks > 0) continue;               // timing experiment: 1 MMA of 4
             umma<2>(d_tmem, ad, bd, idesc, (i > 0 || ks > 0) ? 1u : 0u);
           }
           umma_commit(smem_u32(&bar_empty[s]));       // stage reusable once these MMAs retire
@@ -483,15 +194,19 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
 
 // 3xTF32 operand split of the stages, run by SPLIT_THREADS threads (tt = 0 .. SPLIT_THREADS-1).
 // Each raw f32 x stays in place as the `big` operand (the tensor core reads its top 19 bits) and
-// small = tf32_rn(x - trunc_tf32(x)) is written RAW_BYTES further on.  Four 16-byte vectors are in
-// flight per thread to cover the shared-memory latency.
-constexpr int SPLIT_THREADS = 192;
+// small = x - trunc_tf32(x) (exact; the tensor core again keeps its top 19 bits) is written RAW_BYTES
+// further on.  A stage is a whole number of 16-byte vectors per thread; all of a thread's vectors are
+// loaded before any is stored, to cover the shared-memory latency.
+constexpr int SPLIT_WARPS = 8;
+constexpr int SPLIT_THREADS = SPLIT_WARPS * 32;
 
 template <typename C>
 __device__ __forceinline__ void split_role(const TcArgs& g, uint32_t smem_base, uint64_t* bar_full,
                                            uint64_t* bar_xform, volatile int* abortp, int total_kb, int tt) {
   constexpr int STAGES = C::STAGES;
   constexpr int NVEC = C::RAW_BYTES / 16;
+  static_assert(NVEC % SPLIT_THREADS == 0, "a stage must be a whole number of vectors per split thread");
+  constexpr int PER = NVEC / SPLIT_THREADS;             // 6 (BN = 256), 4 (128), 3 (64)
   uint32_t it = 0;
   bool ok = true;
   for (long long tile = blockIdx.x; ok && tile < g.total_tiles; tile += gridDim.x) {
@@ -499,45 +214,27 @@ __device__ __forceinline__ void split_role(const TcArgs& g, uint32_t smem_base, 
       const int s = it % STAGES;
       const uint32_t ph = (it / STAGES) & 1u;
       if (!mbar_wait(smem_u32(&bar_full[s]), ph, abortp, g.wait_limit)) { ok = false; break; }
-      const uint32_t raw = smem_base + s * C::STAGE_BYTES;
-      const int nvec = (g.xform_mode & 2) ? 0 : NVEC;   // bit 1: timing experiment, no split
-#pragma unroll 1
-      for (int v0 = tt; v0 < nvec; v0 += 4 * SPLIT_THREADS) {
-        uint32_t x[4][4];
+      const uint32_t raw = smem_base + s * C::STAGE_BYTES + tt * 16;
+      if (!(g.xform_mode & 2)) {                        // bit 1: timing experiment, no split
+        uint32_t x[PER][4];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          const int v = v0 + u * SPLIT_THREADS;
-          if (v < NVEC)
-            asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
-                         : "=r"(x[u][0]), "=r"(x[u][1]), "=r"(x[u][2]), "=r"(x[u][3]) : "r"(raw + v * 16));
-        }
+        for (int u = 0; u < PER; ++u)
+          asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                       : "=r"(x[u][0]), "=r"(x[u][1]), "=r"(x[u][2]), "=r"(x[u][3])
+                       : "r"(raw + u * (SPLIT_THREADS * 16)));
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          const int v = v0 + u * SPLIT_THREADS;
-          if (v < NVEC) {
-            uint32_t sm[4];
-            if ((g.xform_mode & 1) == 0) {              // optional: rewrite big = tf32_rn(x) as well
-              uint32_t big[4];
+        for (int u = 0; u < PER; ++u) {
+          uint32_t sm[4];
 #pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(big[e]) : "f"(__uint_as_float(x[u][e])));
-                float d = __uint_as_float(x[u][e]) - __uint_as_float(big[e]);
-                d = (d != d) ? 0.f : d;
-                asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(sm[e]) : "f"(d));
-              }
-              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};"
-                           ::"r"(raw + v * 16), "r"(big[0]), "r"(big[1]), "r"(big[2]), "r"(big[3]) : "memory");
-            } else {
-#pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                float d = __uint_as_float(x[u][e]) - __uint_as_float(x[u][e] & 0xffffe000u);
-                d = (d != d) ? 0.f : d;                 // inf - inf: keep inf / nan in `big` only
-                asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(sm[e]) : "f"(d));
-              }
-            }
-            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};"
-                         ::"r"(raw + C::RAW_BYTES + v * 16), "r"(sm[0]), "r"(sm[1]), "r"(sm[2]), "r"(sm[3]) : "memory");
+          for (int e = 0; e < 4; ++e) {
+            float d = __uint_as_float(x[u][e]) - __uint_as_float(x[u][e] & 0xffffe000u);
+            d = (d != d) ? 0.f : d;                     // inf - inf: keep inf / nan in `big` only
+            if ((g.xform_mode & 1) == 0) asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(sm[e]) : "f"(d));
+            else sm[e] = __float_as_uint(d);
           }
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};"
+                       ::"r"(raw + C::RAW_BYTES + u * (SPLIT_THREADS * 16)), "r"(sm[0]), "r"(sm[1]), "r"(sm[2]), "r"(sm[3])
+                       : "memory");
         }
       }
       fence_proxy_async_smem();                         // generic-proxy writes -> visible to tcgen05.mma
@@ -555,7 +252,7 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_const
                    const TcArgs g) {
   using C = CfgS<BN>;
   constexpr int STAGES = C::STAGES;
-  constexpr int PRODUCER_WARP = 12, MMA_WARP = 13;
+  constexpr int PRODUCER_WARP = 8, MMA_WARP = 9;      // warpgroup 2; warpgroups 3 and 4 split operands
 
   extern __shared__ uint8_t smem_dyn[];
   __shared__ __align__(8) uint64_t bar_full[STAGES];
@@ -598,8 +295,8 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_const
   const uint32_t tmem_base = tmem_slot;
   const int total_kb = g.red * g.k_blocks;
 
-  if (wg == 3) {
-    setmaxnreg_dec_56();
+  if (wg == 2) {
+    setmaxnreg_dec_low();
     if (warp == PRODUCER_WARP && lane == 0) {
       // ---------------------------------------------------------------- TMA producer
       uint32_t it = 0;
@@ -612,6 +309,7 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_const
           const uint32_t ph = (it / STAGES) & 1u;
           if (!mbar_wait(smem_u32(&bar_empty[s]), ph ^ 1u, abortp, g.wait_limit)) { ok = false; break; }
           const uint32_t full = smem_u32(&bar_full[s]);
+          if (g.xform_mode & 8) { mbar_arrive(full); continue; }   // timing experiment: no loads
           mbar_expect_tx(full, C::RAW_BYTES);
           const uint32_t a_dst = smem_base + s * C::STAGE_BYTES;
           load_operand<BM, C::BK, C::CH, C::MN_LBO>(a_dst, &tma_a, full, g.a_ld, t.mt * BM, kb * C::BK,
@@ -666,18 +364,14 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_const
         }
       }
     }
-    else if (warp >= 14) {
-      // ---------------------------------------------------------------- operand split (warps 14, 15)
-      split_role<C>(g, smem_base, bar_full, bar_xform, abortp, total_kb, threadIdx.x - 448 + 128);
-    }
     __syncwarp();
-  } else if (wg == 2) {
-    // ------------------------------------------------------------------ operand split (warps 8..11)
-    setmaxnreg_dec_56();
-    split_role<C>(g, smem_base, bar_full, bar_xform, abortp, total_kb, threadIdx.x - 256);
+  } else if (wg >= 3) {
+    // ------------------------------------------------------------------ operand split (warps 12..19)
+    setmaxnreg_dec_split();
+    split_role<C>(g, smem_base, bar_full, bar_xform, abortp, total_kb, threadIdx.x - 384);
   } else {
     // ------------------------------------------------------------------ epilogue (warpgroups 0 and 1)
-    setmaxnreg_inc_200();
+    setmaxnreg_inc_epi();
     const int quad = warp & 3;                        // TMEM lane quadrant this warp may read
     const int col_base = wg * C::HALF;                // this warpgroup's half of the tile's columns
     uint32_t ccount = 0;
@@ -872,10 +566,16 @@ int encode_map(CUtensorMap* map, const void* base, size_t esize, int64_t inner, 
 int g_xform_mode = 1;
 int g_force_bn = 0;   // 0 = choose by problem shape
 int g_mn_box5 = 1;    // MN-major operands: one 5-D TMA box per stage where the extent allows
+int g_pair_mode = 1;  // 0 = choose by problem shape, 1 = never use CTA pairs (default: not faster yet), 2 = always (n > 128)
 
-// C: CfgH<BN> or CfgS<BN>; KERNEL: the matching kernel.
-template <typename C, int ESIZE, int BN, typename Kernel>
-int launch_cfg(const Plan& pl, cudaStream_t stream, Kernel kernel) {
+// Tensor maps and kernel arguments for a tile grid of TM x TN outputs per scheduling unit, where one
+// CTA stages BMC rows of A and BNC columns of B per k-block of BK (MN-major operands in chunks of CH).
+struct Launch {
+  alignas(64) CUtensorMap ma, mb;
+  TcArgs g;
+};
+
+int build_launch(Launch& L, const Plan& pl, int esize, int tm, int tn, int bmc, int bnc, int bk, int ch) {
   const GemmProblem& p = pl.p;
   DeviceState* ds = device_state();
   if (!ds || !ds->ready) return B200_ERR_CUDA;
@@ -891,34 +591,33 @@ int launch_cfg(const Plan& pl, cudaStream_t stream, Kernel kernel) {
 
   // Swizzle of the shared-memory tile: f16 128B everywhere; f32 64B for K-major rows, 128B with 32-byte
   // atoms for MN-major chunks.
-  const CUtensorMapSwizzle sw_k = (ESIZE == 2) ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
-  const CUtensorMapSwizzle sw_mn = (ESIZE == 2) ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B;
+  const CUtensorMapSwizzle sw_k = (esize == 2) ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
+  const CUtensorMapSwizzle sw_mn = (esize == 2) ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B;
 
   // MN-major operands whose MN extent is a whole number of chunks come in with one 5-D box per stage
   // (a partial last chunk would make that box read past the end of a row).
-  const int a_ld = !a_mn ? 0 : ((p.m % C::CH == 0 && g_mn_box5) ? 2 : 1);
-  const int b_ld = !b_mn ? 0 : ((p.n % C::CH == 0 && g_mn_box5) ? 2 : 1);
-  alignas(64) CUtensorMap ma, mb;
+  const int a_ld = !a_mn ? 0 : ((p.m % ch == 0 && g_mn_box5) ? 2 : 1);
+  const int b_ld = !b_mn ? 0 : ((p.n % ch == 0 && g_mn_box5) ? 2 : 1);
   int st;
-  if (a_ld == 0)      st = encode_map(&ma, p.a, ESIZE, p.k, p.m, pl.la.ld, a_xn, a_xs, a_yn, p.a_b0, C::BK, BM, sw_k);
-  else if (a_ld == 1) st = encode_map(&ma, p.a, ESIZE, p.m, p.k, pl.la.ld, a_xn, a_xs, a_yn, p.a_b0, C::CH, C::BK, sw_mn);
-  else                st = encode_map_mn5(&ma, p.a, ESIZE, p.m, p.k, pl.la.ld, a_xn, a_xs, a_yn, p.a_b0, C::CH, C::BK,
-                                          BM / C::CH, sw_mn);
+  if (a_ld == 0)      st = encode_map(&L.ma, p.a, esize, p.k, p.m, pl.la.ld, a_xn, a_xs, a_yn, p.a_b0, bk, bmc, sw_k);
+  else if (a_ld == 1) st = encode_map(&L.ma, p.a, esize, p.m, p.k, pl.la.ld, a_xn, a_xs, a_yn, p.a_b0, ch, bk, sw_mn);
+  else                st = encode_map_mn5(&L.ma, p.a, esize, p.m, p.k, pl.la.ld, a_xn, a_xs, a_yn, p.a_b0, ch, bk,
+                                          bmc / ch, sw_mn);
   if (st) return st;
-  if (b_ld == 0)      st = encode_map(&mb, p.b, ESIZE, p.k, p.n, pl.lb.ld, b_xn, b_xs, b_yn, p.b_b0, C::BK, BN, sw_k);
-  else if (b_ld == 1) st = encode_map(&mb, p.b, ESIZE, p.n, p.k, pl.lb.ld, b_xn, b_xs, b_yn, p.b_b0, C::CH, C::BK, sw_mn);
-  else                st = encode_map_mn5(&mb, p.b, ESIZE, p.n, p.k, pl.lb.ld, b_xn, b_xs, b_yn, p.b_b0, C::CH, C::BK,
-                                          BN / C::CH, sw_mn);
+  if (b_ld == 0)      st = encode_map(&L.mb, p.b, esize, p.k, p.n, pl.lb.ld, b_xn, b_xs, b_yn, p.b_b0, bk, bnc, sw_k);
+  else if (b_ld == 1) st = encode_map(&L.mb, p.b, esize, p.n, p.k, pl.lb.ld, b_xn, b_xs, b_yn, p.b_b0, ch, bk, sw_mn);
+  else                st = encode_map_mn5(&L.mb, p.b, esize, p.n, p.k, pl.lb.ld, b_xn, b_xs, b_yn, p.b_b0, ch, bk,
+                                          bnc / ch, sw_mn);
   if (st) return st;
 
-  TcArgs g;
+  TcArgs& g = L.g;
   g.m = (int)p.m; g.n = (int)p.n;
-  g.m_tiles = (int)((p.m + BM - 1) / BM);
-  g.n_tiles = (int)((p.n + BN - 1) / BN);
+  g.m_tiles = (int)((p.m + tm - 1) / tm);
+  g.n_tiles = (int)((p.n + tn - 1) / tn);
   g.nb1 = (int)p.b1;
   g.total_tiles = (long long)g.m_tiles * g.n_tiles * p.b0 * p.b1;
   g.red = (int)p.red;
-  g.k_blocks = (int)((p.k + C::BK - 1) / C::BK);
+  g.k_blocks = (int)((p.k + bk - 1) / bk);
   g.a_mn = a_mn; g.b_mn = b_mn;
   g.a_ld = a_ld; g.b_ld = b_ld;
   g.a_x1 = (!reduce && a_xn > 1) ? 1 : 0; g.a_xr = (reduce && a_xn > 1) ? 1 : 0; g.a_y0 = (a_yn > 1) ? 1 : 0;
@@ -928,12 +627,30 @@ int launch_cfg(const Plan& pl, cudaStream_t stream, Kernel kernel) {
   g.xform_mode = g_xform_mode;
   g.wait_limit = 400000000LL + (long long)g.red * g.k_blocks * 40000LL;
   g.status = ds->status;
+  return B200_OK;
+}
 
-  const long long grid = g.total_tiles < ds->sm_count ? g.total_tiles : ds->sm_count;
+// C: CfgH<BN> or CfgS<BN>; KERNEL: the matching kernel.
+template <typename C, int ESIZE, int BN, typename Kernel>
+int launch_cfg(const Plan& pl, cudaStream_t stream, Kernel kernel) {
+  Launch L;
+  const int st = build_launch(L, pl, ESIZE, BM, BN, BM, BN, C::BK, C::CH);
+  if (st) return st;
+  DeviceState* ds = device_state();
+  const long long grid = L.g.total_tiles < ds->sm_count ? L.g.total_tiles : ds->sm_count;
   if (grid <= 0) return B200_OK;
-  kernel<<<(unsigned)grid, C::THREADS, C::SMEM_BYTES, stream>>>(ma, mb, g);
+  kernel<<<(unsigned)grid, C::THREADS, C::SMEM_BYTES, stream>>>(L.ma, L.mb, L.g);
   count_launch(true);
   return note_cuda_error(cudaGetLastError(), "tensor-core gemm launch");
+}
+
+// CTA-pair kernels (gemm_tc_pair.cu): 256 x 256 tiles, each CTA stages 128 rows of A and 128 columns of B.
+int launch_pair_plan(const Plan& pl, int esize, cudaStream_t stream) {
+  Launch L;
+  const int tm = pair_tile_m(), tn = pair_tile_n();
+  const int st = build_launch(L, pl, esize, tm, tn, tm / 2, tn / 2, pair_block_k(esize), pair_chunk(esize));
+  if (st) return st;
+  return launch_pair(esize, L.ma, L.mb, L.g, device_state()->sm_count, stream);
 }
 
 template <int ESIZE, int BN>
@@ -960,6 +677,13 @@ int launch_es(const Plan& pl, cudaStream_t stream) {
   if (p.n > 64 && waves(128) * w128 <= best) { best = waves(128) * w128; bn = 128; }
   if (p.n > 128 && waves(256) * w256 <= best) { best = waves(256) * w256; bn = 256; }
   if (g_force_bn) bn = g_force_bn;
+  // CTA pairs (256 x 256 tiles on two SMs) when the problem fills the machine with them.
+  if (!g_force_bn && g_pair_mode != 1 && p.n > 128) {
+    const int64_t tiles2 = ((p.m + 255) / 256) * ((p.n + 255) / 256) * p.b0 * p.b1;
+    const int64_t pairs = sms / 2;
+    const double cost2 = (double)((tiles2 + pairs - 1) / pairs) * 0.8;   // a pair wave of 256x256 tiles vs a wave of 128x256 tiles
+    if (g_pair_mode == 2 || (p.m > 128 && cost2 <= best)) return launch_pair_plan(pl, ESIZE, stream);
+  }
   switch (bn) {
     case 256: return launch_bn<ESIZE, 256>(pl, stream);
     case 128: return launch_bn<ESIZE, 128>(pl, stream);
@@ -985,6 +709,7 @@ int tc_setup_device() {
   if ((st = set_attr<CfgS<64>>(gemm_tf32x3_kernel<64>))) return st;
   if ((st = set_attr<CfgS<128>>(gemm_tf32x3_kernel<128>))) return st;
   if ((st = set_attr<CfgS<256>>(gemm_tf32x3_kernel<256>))) return st;
+  if ((st = pair_setup_device())) return st;
   return encode_fn() ? B200_OK : B200_ERR_CUDA;
 }
 
@@ -998,5 +723,6 @@ int launch_gemm_tc(const GemmProblem& p, cudaStream_t stream) {
 void tc_set_xform_mode(int mode) { g_xform_mode = mode; }
 void tc_set_tile_n(int bn) { g_force_bn = bn; }
 void tc_set_mn_box5(int on) { g_mn_box5 = on; }
+void tc_set_pair_mode(int mode) { g_pair_mode = mode; }
 
 }  // namespace b200

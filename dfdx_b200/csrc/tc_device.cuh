@@ -1,0 +1,323 @@
+// Device-side building blocks shared by the tensor-core GEMM kernels (gemm_tc.cu: one CTA per MMA;
+// gemm_tc_pair.cu: CTA pairs): PTX wrappers for mbarriers, TMA, tcgen05 and TMEM, the shared-memory
+// descriptor, tile configurations, kernel arguments and the epilogue store.
+#pragma once
+#include "common.cuh"
+#include <cuda.h>
+
+namespace b200 {
+namespace tcx {
+
+// ---------------------------------------------------------------------------------------------
+// PTX wrappers
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok;
+}
+// Bounded wait.  Returns false (and raises *abort_flag) if `limit` clock cycles pass, or as soon as
+// another role has raised the flag.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          long long limit) {
+#pragma unroll 1
+  for (int i = 0; i < 64; ++i)
+    if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+#pragma unroll 1
+  for (;;) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (*abort_flag) return false;
+    if (clock64() - t0 > limit) { *abort_flag = 1; return false; }
+  }
+}
+__device__ __forceinline__ void fence_mbar_init() {
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void fence_proxy_async_smem() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* m) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(m) : "memory");
+}
+// Tiled 4-D TMA load, completion counted in bytes on `bar`.  Coordinates innermost first.
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
+                                            int c0, int c1, int c2, int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
+}
+__device__ __forceinline__ void tma_load_5d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
+                                            int c0, int c1, int c2, int c3, int c4) {
+  asm volatile(
+      "cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4) : "memory");
+}
+// 32 lanes x 16 consecutive 32-bit columns.
+__device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, uint32_t (&v)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+        "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+      : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t slot_smem, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot_smem), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+template <int ESIZE>
+__device__ __forceinline__ void umma(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                     uint32_t accumulate) {
+  if constexpr (ESIZE == 2) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+  }
+}
+// 32 lanes x 32 consecutive 32-bit columns: thread i of the warp receives lane (base+i), columns c..c+31.
+__device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+        "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+        "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+        "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+      : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_wait_ld() {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor (sm_100 format): start address, leading / stride byte offsets in
+// 16-byte units, descriptor version 1 at bit 46, swizzle mode at bits 61..63 (2 = 128B, 4 = 64B).
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes,
+                                                   uint32_t layout_type) {
+  uint64_t d = (uint64_t)((saddr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16;
+  d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32;
+  d |= 1ull << 46;
+  d |= (uint64_t)layout_type << 61;
+  return d;
+}
+
+// Register split of the single-CTA f32 kernel.  setmaxnreg only redistributes what the CTA was given at
+// launch (640 threads x 96 registers = 61440): a request beyond that blocks forever, so the budget is
+// checked at compile time.
+constexpr int F32_REGS_LAUNCH = 96, F32_REGS_EPI = 192, F32_REGS_LOW = 32, F32_REGS_SPLIT = 32;
+static_assert(2 * 128 * F32_REGS_EPI + 128 * F32_REGS_LOW + 2 * 128 * F32_REGS_SPLIT <= 640 * F32_REGS_LAUNCH,
+              "setmaxnreg budget exceeds the CTA's launch allocation");
+__device__ __forceinline__ void setmaxnreg_dec_low() { asm volatile("setmaxnreg.dec.sync.aligned.u32 32;"); }
+__device__ __forceinline__ void setmaxnreg_dec_split() { asm volatile("setmaxnreg.dec.sync.aligned.u32 32;"); }
+__device__ __forceinline__ void setmaxnreg_inc_epi() { asm volatile("setmaxnreg.inc.sync.aligned.u32 192;"); }
+// Pair f32 kernel (512 threads x 128 registers = 65536): 2 x 128 x 200 + 2 x 128 x 56 = 65536.
+__device__ __forceinline__ void setmaxnreg_dec_56() { asm volatile("setmaxnreg.dec.sync.aligned.u32 56;"); }
+__device__ __forceinline__ void setmaxnreg_inc_200() { asm volatile("setmaxnreg.inc.sync.aligned.u32 200;"); }
+
+// ---------------------------------------------------------------------------------------------
+// Kernel configuration
+// ---------------------------------------------------------------------------------------------
+constexpr int BM = 128;
+
+// f16: every operand tile is made of 128-byte rows under the 128B swizzle.
+template <int BN>
+struct CfgH {
+  static constexpr int BK = 64;                             // k extent of a stage (elements)
+  static constexpr int CH = 64;                             // MN elements per MN-major chunk
+  static constexpr int KSTEPS = 4;                          // MMAs per stage (K = 16 each)
+  static constexpr int A_BYTES = BM * 128;
+  static constexpr int B_BYTES = BN * 128;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES_FIT = (192 * 1024) / STAGE_BYTES;
+  static constexpr int STAGES = STAGES_FIT > 8 ? 8 : STAGES_FIT;
+  static constexpr int THREADS = 192;
+  static constexpr int TMEM_COLS = 2 * BN;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024;
+  static constexpr uint32_t LAYOUT = 2u;                    // SWIZZLE_128B
+  static constexpr uint32_t SBO = 1024;                     // 8 rows of 128 bytes
+  static constexpr uint32_t MN_LBO = BK * 128;              // distance between MN-major chunks
+  static constexpr uint32_t MN_KADV = 2 * 1024;             // 16 k rows per MMA
+  static constexpr uint32_t K_KADV = 32;                    // 16 elements of K per MMA
+};
+
+// f32 (3xTF32): K-major tiles are 64-byte rows under the 64B swizzle; MN-major tiles are chunks of
+// 32 columns x BK k-rows of 128 bytes under the 128B swizzle with 32-byte atoms.
+template <int BN>
+struct CfgS {
+  static constexpr int BK = 16;
+  static constexpr int CH = 32;
+  static constexpr int KSTEPS = 2;                          // k-steps per stage (K = 8 each), 3 MMAs per step
+  static constexpr int A_BYTES = BM * 64;
+  static constexpr int B_BYTES = BN * 64;
+  static constexpr int RAW_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGE_BYTES = 2 * RAW_BYTES;         // raw (big) + small copy
+  static constexpr int STAGES_FIT = (192 * 1024) / STAGE_BYTES;
+  static constexpr int STAGES = STAGES_FIT > 8 ? 8 : STAGES_FIT;
+  static constexpr int THREADS = 640;                       // 5 warpgroups: 2 epilogue, 1 producer + MMA, 2 operand split
+  static constexpr int TMEM_COLS = 2 * BN;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024;
+  static constexpr int CHUNK_KB = 16;                       // k-blocks per promotion chunk (K = 256)
+  static constexpr int HALF = BN / 2;                       // columns owned by one epilogue warpgroup
+  static constexpr uint32_t K_LAYOUT = 4u;                  // SWIZZLE_64B
+  static constexpr uint32_t K_SBO = 512;                    // 8 rows of 64 bytes
+  static constexpr uint32_t K_KADV = 32;                    // 8 elements of K per MMA
+  static constexpr uint32_t MN_LAYOUT = 1u;                 // SWIZZLE_128B_BASE32B
+  static constexpr uint32_t MN_SBO = 512;                   // 4 k-rows of 128 bytes
+  static constexpr uint32_t MN_LBO = BK * 128;              // distance between MN-major chunks
+  static constexpr uint32_t MN_KADV = 8 * 128;              // 8 k-rows per MMA
+};
+
+struct TcArgs {
+  int m, n;                       // output extent of one batch item
+  int m_tiles, n_tiles;
+  int nb1;                        // inner batch count (tile id -> (b0, b1))
+  long long total_tiles;
+  int red, k_blocks;              // k iterations per tile = red * k_blocks
+  int a_mn, b_mn;                 // operand is MN-major (else K-major)
+  int a_ld, b_ld;                 // load_operand mode: 0 K-major, 1 MN-major per chunk, 2 MN-major one box
+  int a_x1, a_xr, a_y0;           // TMA x = a_x1*ib1 + a_xr*r ; y = a_y0*ib0
+  int b_x1, b_xr, b_y0;
+  void* c;
+  long long c_b0, c_b1, ldc;      // element strides
+  int beta;
+  int xform_mode;                 // f32: 1 = big stays raw, write small only; 0 = also rewrite big = tf32_rn(x)
+  long long wait_limit;           // clock cycles
+  int* status;
+};
+
+// 32 consecutive f32 accumulator columns of one output row -> global memory.
+__device__ __forceinline__ void store_chunk(float* dst, const float* v, int valid, int beta) {
+  if (valid == 32) {
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+      float4 o = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+      if (beta) {
+        const float4 old = *reinterpret_cast<const float4*>(dst + 4 * q);
+        o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+      }
+      *reinterpret_cast<float4*>(dst + 4 * q) = o;
+    }
+  } else {
+#pragma unroll
+    for (int q = 0; q < 32; ++q)
+      if (q < valid) {
+        float o = v[q];
+        if (beta) o += dst[q];
+        dst[q] = o;
+      }
+  }
+}
+
+__device__ __forceinline__ void store_chunk(__half* dst, const float* v, int valid, int beta) {
+  if (valid == 32) {
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      float f[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) f[e] = v[8 * q + e];
+      if (beta) {
+        const uint4 old = *reinterpret_cast<const uint4*>(dst + 8 * q);
+        const __half2* oh = reinterpret_cast<const __half2*>(&old);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 t = __half22float2(oh[e]);
+          f[2 * e] += t.x; f[2 * e + 1] += t.y;
+        }
+      }
+      uint4 pk;
+      __half2* ph = reinterpret_cast<__half2*>(&pk);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) ph[e] = __floats2half2_rn(f[2 * e], f[2 * e + 1]);
+      *reinterpret_cast<uint4*>(dst + 8 * q) = pk;
+    }
+  } else {
+#pragma unroll
+    for (int q = 0; q < 32; ++q)
+      if (q < valid) {
+        float o = v[q];
+        if (beta) o += __half2float(dst[q]);
+        dst[q] = __float2half_rn(o);
+      }
+  }
+}
+
+struct TileCoord { int mt, nt, ib0, ib1; };
+__device__ __forceinline__ TileCoord decode_tile(const TcArgs& g, long long tile) {
+  const long long per_batch = (long long)g.m_tiles * g.n_tiles;
+  const long long bt = tile / per_batch;
+  const int rem = (int)(tile - bt * per_batch);
+  TileCoord t;
+  t.mt = rem % g.m_tiles; t.nt = rem / g.m_tiles;
+  t.ib1 = (int)(bt % g.nb1); t.ib0 = (int)(bt / g.nb1);
+  return t;
+}
+
+// Issues the TMA loads of one stage.  mode 0, K-major operand: one 4-D box [BK, rows].  MN-major
+// operand: mode 2 = one 5-D box [CH, BK, rows/CH] over the view (CH, K, MN/CH, x, y) of the matrix
+// (needs MN % CH == 0); mode 1 = one 4-D box [CH, BK] per chunk of CH columns.  Either way chunk c of
+// the tile lands at dst + c * MN_LBO.
+template <int ROWS, int BK, int CH, uint32_t MN_LBO>
+__device__ __forceinline__ void load_operand(uint32_t dst, const CUtensorMap* map, uint32_t bar, int mode,
+                                             int row0, int k0, int x, int y) {
+  if (mode == 0) {
+    tma_load_4d(dst, map, bar, k0, row0, x, y);
+  } else if (mode == 2) {
+    tma_load_5d(dst, map, bar, 0, k0, row0 / CH, x, y);
+  } else {
+#pragma unroll 1
+    for (int c = 0; c < ROWS / CH; ++c) tma_load_4d(dst + c * MN_LBO, map, bar, row0 + c * CH, k0, x, y);
+  }
+}
+
+__device__ __forceinline__ void teardown(int abort_flag, int* status) {
+  if (abort_flag) {
+    // Give copies that may still be in flight time to land before shared memory is released.
+    const long long t0 = clock64();
+    while (clock64() - t0 < 2000000) __nanosleep(1000);
+    if (threadIdx.x == 0) atomicExch(status, (int)B200_ERR_DEVICE_TIMEOUT);
+    __syncthreads();
+  }
+}
+
+}  // namespace tcx
+}  // namespace b200

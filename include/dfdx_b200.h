@@ -91,6 +91,10 @@ int b200_set_tile_n(int bn);
 /* MN-major operand loading (testing / profiling): 1 (default) brings a tile's column chunks with one
  * 5-D TMA box where the extent is a whole number of chunks; 0 always issues one 4-D box per chunk. */
 int b200_set_mn_single_box(int on);
+/* CTA-pair kernels (testing / profiling): 1 (default) uses the single-CTA tensor-core kernels only, 0 lets the
+ * planner choose between them and the CTA-pair (cta_group::2, 256x256 tiles) kernels by a wave model, 2 forces
+ * the pair kernels wherever the output is wider than 128 columns. */
+int b200_set_cta_pair_mode(int mode);
 /* Number of kernel launches this library has enqueued since load (all threads). */
 uint64_t b200_launch_count(void);
 /* Of those, launches of tcgen05 tensor-core kernels. */

@@ -125,6 +125,24 @@ def test_tensor_core_layouts(cuda_dev, oracle, dtype, layout, tile_n):
 
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.float32])
+@pytest.mark.parametrize("layout", ["".join(p) for p in itertools.product("rc", repeat=3)])
+def test_cta_pair_kernels(cuda_dev, oracle, dtype, layout):
+    """The cta_group::2 kernels (two CTAs per 256x256 tile), forced: every layout, ragged shapes incl. one
+    where the second CTA of the pair has no rows, beta 0 and 1, long K."""
+    cuda_dev.set_path(dfdx_b200.PATH_TENSOR)
+    assert cuda_dev.lib.b200_set_cta_pair_mode(2) == 0
+    try:
+        before = cuda_dev.lib.b200_tensor_launch_count()
+        shapes = [(256, 256, 264), (520, 136, 776), (104, 264, 304), (384, 2056, 512)]
+        for i, (m, k, n) in enumerate(shapes):
+            check_gemm(cuda_dev, oracle, m, k, n, layout[0], layout[1], layout[2], i % 2, dtype, pad=8, seed=300 + i)
+        assert cuda_dev.lib.b200_tensor_launch_count() - before == len(shapes)
+    finally:
+        cuda_dev.lib.b200_set_cta_pair_mode(1)
+        cuda_dev.set_path(dfdx_b200.PATH_AUTO)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.float32])
 def test_tensor_core_long_k_accuracy(cuda_dev, oracle, dtype):
     """The stated bound must hold where accumulation is longest: K = 16384."""
     cuda_dev.set_path(dfdx_b200.PATH_TENSOR)
