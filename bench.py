@@ -161,6 +161,98 @@ def run_reference(args, rank: int):
     }))
 
 
+def run_other_workload(args, dev, rank, world):
+    """Forward + backward of configuration 1, 3 or 4 on device-resident synthetic inputs; one JSON line."""
+    import torch
+    import torch.distributed as dist
+    import dfdx_b200
+    device, lib = dev.device, dev.lib
+    g = torch.Generator(device="cpu").manual_seed(0xD0FD + int(args.workload[1]) + 1000 * rank)
+    mib = 1024.0 * 1024.0
+    if args.workload == "c1":
+        a = (torch.rand(1024, 1024, generator=g) * 2 - 1).to(device)
+        b = (torch.rand(1024, 1024, generator=g) * 2 - 1).to(device)
+        dc = torch.randn(1024, 1024, generator=g).to(device)
+        ga, gb = torch.zeros_like(a), torch.zeros_like(b)
+
+        def step():
+            dev.matmat_forward(a, b)
+            dev.matmat_backward(a, ga, b, gb, dc)
+        flops, algo_bytes, bound, dtype = 6 * 1024 ** 3, 44 * mib, "tensor", "f32"
+        name = "config[0]: MatMat f32 A[1024,1024] x B[1024,1024], fwd + grad_lhs + grad_rhs"
+        peak_div = 6.0
+    elif args.workload == "c3":
+        q, k, v = (torch.randn(16, 16, 512, 64, generator=g).half().to(device) for _ in range(3))
+        kt = k.permute(0, 1, 3, 2)
+        p = torch.softmax(torch.randn(16, 16, 512, 512, generator=g), -1).half().to(device)
+        do = torch.randn(16, 16, 512, 64, generator=g).half().to(device)
+        ds = torch.randn(16, 16, 512, 512, generator=g).half().to(device)
+        gq, gk, gv, gp = torch.zeros_like(q), torch.zeros_like(k), torch.zeros_like(v), torch.zeros_like(p)
+
+        def step():
+            dev.matmat_batch4_forward(q, kt)                 # scores = Q K^T
+            dev.matmat_batch4_forward(p, v)                  # out = P V   (softmax is not on the path)
+            dev.matmat_batch4_backward(p, gp, v, gv, do)     # dP, dV
+            dev.matmat_batch4_backward(q, gq, kt, gk, ds)    # dQ, dK
+        flops, algo_bytes, bound, dtype = 2 * 6 * 256 * 512 * 512 * 64, 1136 * mib, "hbm", "f16"
+        name = "config[2]: MatMatBatch4 f16 Q,K,V[16,16,512,64]: QK^T and PV, forward + backward (6 GEMM groups)"
+        peak_div = 1.0
+    else:
+        x = torch.randn(32, 64, 56, 56, generator=g).to(device)
+        w = ((torch.rand(128, 64, 3, 3, generator=g) * 2 - 1) / 24.0).to(device)
+        dy = torch.randn(32, 128, 56, 56, generator=g).to(device)
+        op = dev.conv2d_op(x, w, 1, 1, 1, 1)
+        y, gx, gw = torch.empty(32, 128, 56, 56, device=device), torch.zeros_like(x), torch.zeros_like(w)
+
+        def step():
+            dev.conv2d_forward(op, x, w, y)
+            dev.conv2d_backward(op, x, gx, w, gw, dy)
+        flops, algo_bytes, bound, dtype = 3 * 2 * 32 * 128 * 576 * 3136, 246 * mib, "tensor", "f32"
+        name = "config[3]: conv2d f32 x[32,64,56,56] * w[128,64,3,3], stride 1, padding 1, fwd + both gradients"
+        peak_div = 6.0
+
+    stream = torch.cuda.current_stream(device)
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize(device)
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=device)   # > L2: evicts between steps
+    e = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    l0, t0 = lib.b200_launch_count(), lib.b200_tensor_launch_count()
+    for i in range(args.steps):
+        flush.fill_(i & 1)
+        e[i][0].record(stream)
+        step()
+        e[i][1].record(stream)
+    torch.cuda.synchronize(device)
+    dfdx_b200._lib.check(dev.device_status(), "device status after the timed region")
+    ms = sum(a.elapsed_time(b) for a, b in e)
+    if world > 1:
+        t = torch.tensor([ms], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    if rank != 0:
+        return
+    peaks, which = measured_peaks()
+    per_step = ms / args.steps
+    tflops = world * flops / (per_step * 1e-3) / 1e12
+    if bound == "hbm":
+        achieved, peak, unit = algo_bytes / (per_step * 1e-3) / 1e9, peaks["hbm_gbs"], "GB/s"
+        basis = f"{which} hbm_gbs; algorithmic bytes 1136 MiB per step"
+    else:
+        achieved, peak, unit = tflops / world, peaks["bf16_tflops"] / peak_div, "TFLOP/s"
+        basis = f"{which} bf16_tflops (burst) / 2 (tf32) / 3 (3xTF32)"
+    print(json.dumps({
+        "metric": METRIC, "value": round(tflops, 3), "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": round(per_step, 4), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": dtype, "data": "synthetic",
+        "config": {"workload": name, "l2": "256 MiB flush buffer written between timed steps"},
+        "gpu_launches": int(lib.b200_launch_count() - l0),
+        "tensor_core_launches": int(lib.b200_tensor_launch_count() - t0), "e2e": None,
+        "roofline": {"bound": bound, "achieved": round(achieved, 2), "peak": round(peak, 2), "unit": unit,
+                     "frac": round(achieved / peak, 4), "traffic": None, "peak_basis": basis},
+    }))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -168,6 +260,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--workload", default="c2", choices=["c1", "c2", "c3", "c4"],
+                    help="c2 (default) is the benchmark; c1 / c3 / c4 time the other configurations of the "
+                         "path with the same harness (device-resident only; used for profiling)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -189,6 +284,12 @@ def main():
     dev = dfdx_b200.Cuda(local_rank)
     device = dev.device
     lib = dev.lib
+
+    if args.workload != "c2":
+        run_other_workload(args, dev, rank, world)
+        if world > 1:
+            dist.destroy_process_group()
+        return
 
     # Synthetic inputs of the configuration (seeded per rank): X ~ N(0,1), W ~ U(+-1/sqrt(K)), dY ~ N(0,1).
     g = torch.Generator(device="cpu").manual_seed(0xD0FD + 2 + 1000 * rank)

@@ -116,6 +116,115 @@ __global__ void __launch_bounds__(NT) sum_transposed_filters_kernel(const Op op,
   }
 }
 
+// ---- plane-staged unfold kernels (fast path) -----------------------------------------------------
+// One block per (batch, channel) plane: the plane is read from global memory once into shared
+// memory, then all K*K shifted copies of it are written with 16-byte stores.  Used when a plane fits
+// 48 KB of shared memory and the patch row length is a whole number of vectors; otherwise the
+// element-per-thread kernels above serve.
+template <typename T> struct VecOf;
+template <> struct VecOf<float> { static constexpr int N = 4; using type = float4; };
+template <> struct VecOf<double> { static constexpr int N = 2; using type = double2; };
+template <> struct VecOf<__half> { static constexpr int N = 8; using type = uint4; };
+
+struct Op32 {
+  int kernel, stride, padding, dilation, chan_in, chan_out, h_in, h_out, w_in, w_out;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(NT) unfold_input_plane_kernel(const Op32 op, const T* __restrict__ img,
+                                                                const Strides4 st, T* __restrict__ patches) {
+  constexpr int V = VecOf<T>::N;
+  using VT = typename VecOf<T>::type;
+  extern __shared__ __align__(16) unsigned char plane_raw[];
+  T* plane = reinterpret_cast<T*>(plane_raw);
+  const int id = blockIdx.x, b = id / op.chan_in, c = id - b * op.chan_in;
+  const T* src = img + (int64_t)b * st.s[0] + (int64_t)c * st.s[1];
+  const int hw = op.h_in * op.w_in;
+  for (int i = threadIdx.x; i < hw; i += NT) {
+    const int y = i / op.w_in, x = i - y * op.w_in;
+    plane[i] = src[(int64_t)y * st.s[2] + (int64_t)x * st.s[3]];
+  }
+  __syncthreads();
+  const int npos = op.h_out * op.w_out, vrow = op.w_out / V, nvec = op.h_out * vrow;
+  T* dst = patches + (int64_t)id * op.kernel * op.kernel * npos;
+  for (int v = threadIdx.x; v < nvec; v += NT) {
+    const int oh = v / vrow, ow0 = (v - oh * vrow) * V;
+    for (int k1 = 0; k1 < op.kernel; ++k1) {
+      const int y = oh * op.stride + op.dilation * k1 - op.padding;
+      const bool yok = y >= 0 && y < op.h_in;
+      for (int k2 = 0; k2 < op.kernel; ++k2) {
+        const int x0 = ow0 * op.stride + op.dilation * k2 - op.padding;
+        __align__(16) T vals[V];
+#pragma unroll
+        for (int e = 0; e < V; ++e) {
+          const int x = x0 + e * op.stride;
+          vals[e] = (yok && x >= 0 && x < op.w_in) ? plane[y * op.w_in + x] : T(0.0f);
+        }
+        *reinterpret_cast<VT*>(dst + (int64_t)(k1 * op.kernel + k2) * npos + oh * op.w_out + ow0) =
+            *reinterpret_cast<const VT*>(vals);
+      }
+    }
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(NT) unfold_output_plane_kernel(const Op32 op, const T* __restrict__ gout,
+                                                                 T* __restrict__ patches) {
+  constexpr int V = VecOf<T>::N;
+  using VT = typename VecOf<T>::type;
+  extern __shared__ __align__(16) unsigned char plane_raw[];
+  T* plane = reinterpret_cast<T*>(plane_raw);
+  const int id = blockIdx.x;                                   // b * chan_out + o
+  const int npos = op.h_out * op.w_out;
+  const T* src = gout + (int64_t)id * npos;
+  for (int i = threadIdx.x; i < npos; i += NT) plane[i] = src[i];
+  __syncthreads();
+  const int hw = op.h_in * op.w_in, vrow = op.w_in / V, nvec = op.h_in * vrow;
+  T* dst = patches + (int64_t)id * op.kernel * op.kernel * hw;
+  for (int v = threadIdx.x; v < nvec; v += NT) {
+    const int y = v / vrow, x0 = (v - y * vrow) * V;
+    for (int k1 = 0; k1 < op.kernel; ++k1) {
+      const int ohs = y + op.padding - op.dilation * k1;
+      const int oh = ohs / op.stride;
+      const bool yok = ohs >= 0 && ohs - oh * op.stride == 0 && oh < op.h_out;
+      for (int k2 = 0; k2 < op.kernel; ++k2) {
+        __align__(16) T vals[V];
+#pragma unroll
+        for (int e = 0; e < V; ++e) {
+          const int ows = x0 + e + op.padding - op.dilation * k2;
+          const int ow = ows / op.stride;
+          vals[e] = (yok && ows >= 0 && ows - ow * op.stride == 0 && ow < op.w_out) ? plane[oh * op.w_out + ow]
+                                                                                    : T(0.0f);
+        }
+        *reinterpret_cast<VT*>(dst + (int64_t)(k1 * op.kernel + k2) * hw + y * op.w_in + x0) =
+            *reinterpret_cast<const VT*>(vals);
+      }
+    }
+  }
+}
+
+Op32 to_op32(const Op& o) {
+  return Op32{(int)o.kernel, (int)o.stride, (int)o.padding, (int)o.dilation, (int)o.chan_in, (int)o.chan_out,
+              (int)o.h_in, (int)o.h_out, (int)o.w_in, (int)o.w_out};
+}
+
+bool fits_int(const Op& o) {
+  const int64_t lim = 1 << 30;
+  return o.batch * o.chan_in < lim && o.batch * o.chan_out < lim && o.h_in * o.w_in < lim &&
+         o.h_out * o.w_out < lim && o.kernel < 4096 && o.stride < lim && o.padding < lim && o.dilation < lim;
+}
+
+template <typename T>
+bool plane_path_input(const Op& o) {
+  return fits_int(o) && o.w_out % VecOf<T>::N == 0 && (size_t)(o.h_in * o.w_in) * sizeof(T) <= 48 * 1024 &&
+         o.h_out * o.w_out > 0;
+}
+template <typename T>
+bool plane_path_output(const Op& o) {
+  return fits_int(o) && o.w_in % VecOf<T>::N == 0 && (size_t)(o.h_out * o.w_out) * sizeof(T) <= 48 * 1024 &&
+         o.h_in * o.w_in > 0;
+}
+
 unsigned grid_for(int64_t total, int sms) {
   int64_t blocks = (total + NT - 1) / NT;
   const int64_t cap = (int64_t)sms * 16;
@@ -134,7 +243,11 @@ int forward_t(int dtype, const Op& op, const T* img, const size_t is[4], const T
   const int64_t total = op.batch * op.chan_in * op.kernel * op.kernel * op.h_out * op.w_out;
   if (total == 0) return B200_OK;
   Strides4 st{{(int64_t)is[0], (int64_t)is[1], (int64_t)is[2], (int64_t)is[3]}};
-  unfold_input_kernel<T><<<grid_for(total, sms), NT, 0, stream>>>(op, img, st, patches, total);
+  if (plane_path_input<T>(op))
+    unfold_input_plane_kernel<T><<<(unsigned)(op.batch * op.chan_in), NT, (size_t)(op.h_in * op.w_in) * sizeof(T),
+                                   stream>>>(to_op32(op), img, st, patches);
+  else
+    unfold_input_kernel<T><<<grid_for(total, sms), NT, 0, stream>>>(op, img, st, patches, total);
   count_launch(false);
   int rc = note_cuda_error(cudaGetLastError(), "unfold_input launch");
   if (rc) return rc;
@@ -167,7 +280,11 @@ int backward_t(int dtype, const Op& op, const T* img, T* grad_img, const T* filt
   Strides4 st{{(int64_t)fs[0], (int64_t)fs[1], (int64_t)fs[2], (int64_t)fs[3]}};
   int rc;
 
-  unfold_output_kernel<T><<<grid_for(n_patches, sms), NT, 0, stream>>>(op, grad_out, patches, n_patches);
+  if (plane_path_output<T>(op))
+    unfold_output_plane_kernel<T><<<(unsigned)(op.batch * op.chan_out), NT,
+                                    (size_t)(op.h_out * op.w_out) * sizeof(T), stream>>>(to_op32(op), grad_out, patches);
+  else
+    unfold_output_kernel<T><<<grid_for(n_patches, sms), NT, 0, stream>>>(op, grad_out, patches, n_patches);
   count_launch(false);
   if ((rc = note_cuda_error(cudaGetLastError(), "unfold_output launch"))) return rc;
 

@@ -615,6 +615,9 @@ int build_launch(Launch& L, const Plan& pl, int esize, int tm, int tn, int bmc, 
   g.m_tiles = (int)((p.m + tm - 1) / tm);
   g.n_tiles = (int)((p.n + tn - 1) / tn);
   g.nb1 = (int)p.b1;
+  // Walk the dimension with fewer tiles fastest: the CTAs of one wave then share as many operand panels as
+  // possible (an A panel is consumed by all its N tiles at once), which keeps DRAM reads near one pass.
+  g.n_fast = g.n_tiles < g.m_tiles ? 1 : 0;
   g.total_tiles = (long long)g.m_tiles * g.n_tiles * p.b0 * p.b1;
   g.red = (int)p.red;
   g.k_blocks = (int)((p.k + bk - 1) / bk);

@@ -211,6 +211,7 @@ struct TcArgs {
   int m, n;                       // output extent of one batch item
   int m_tiles, n_tiles;
   int nb1;                        // inner batch count (tile id -> (b0, b1))
+  int n_fast;                     // tile order inside a batch item: 1 = N tiles fastest, 0 = M tiles fastest
   long long total_tiles;
   int red, k_blocks;              // k iterations per tile = red * k_blocks
   int a_mn, b_mn;                 // operand is MN-major (else K-major)
@@ -287,7 +288,8 @@ __device__ __forceinline__ TileCoord decode_tile(const TcArgs& g, long long tile
   const long long bt = tile / per_batch;
   const int rem = (int)(tile - bt * per_batch);
   TileCoord t;
-  t.mt = rem % g.m_tiles; t.nt = rem / g.m_tiles;
+  if (g.n_fast) { t.nt = rem % g.n_tiles; t.mt = rem / g.n_tiles; }
+  else { t.mt = rem % g.m_tiles; t.nt = rem / g.m_tiles; }
   t.ib1 = (int)(bt % g.nb1); t.ib0 = (int)(bt / g.nb1);
   return t;
 }
