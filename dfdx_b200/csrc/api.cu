@@ -20,6 +20,7 @@ void tc_set_xform_mode(int mode);
 void tc_set_tile_n(int bn);
 void tc_set_mn_box5(int on);
 void tc_set_pair_mode(int mode);
+void tc_set_store_mode(int mode);
 
 namespace {
 
@@ -174,6 +175,14 @@ int b200_set_mn_single_box(int on) {
 int b200_set_cta_pair_mode(int mode) {
   if (mode < 0 || mode > 2) return B200_ERR_UNSUPPORTED;
   tc_set_pair_mode(mode);
+  return B200_OK;
+}
+
+/* Testing hook: epilogue store orientation of the tensor-core kernels: 0 (default) planner's choice,
+ * 1 row stores only, 2 column stores wherever the output allows. */
+int b200_set_store_mode(int mode) {
+  if (mode < 0 || mode > 2) return B200_ERR_UNSUPPORTED;
+  tc_set_store_mode(mode);
   return B200_OK;
 }
 

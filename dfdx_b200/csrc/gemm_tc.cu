@@ -159,23 +159,45 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
     for (long long tile = blockIdx.x; ok && tile < g.total_tiles; tile += gridDim.x, ++tcount) {
       const TileCoord t = decode_tile(g, tile);
       const uint32_t buf = tcount & 1u, tph = (tcount >> 1) & 1u;
+      const int row = t.mt * BM + warp * 32 + lane;
+      __half* cbase = (__half*)g.c + t.ib0 * g.c_b0 + t.ib1 * g.c_b1;
+      // beta = 1 with row stores: the values the row already holds do not depend on the accumulator, so
+      // they are fetched before waiting for it, four 32-column chunks ahead of their use.
+      constexpr int NCH = BN / 32, AHEAD = NCH < 4 ? NCH : 4;
+      const bool rmw = g.beta && !g.c_col && row < g.m;
+      const __half* orow = cbase + (long long)row * g.ldc + t.nt * BN;
+      uint32_t oldv[AHEAD][16];
+      if (rmw) {
+#pragma unroll
+        for (int pc = 0; pc < AHEAD; ++pc)
+          if (t.nt * BN + pc * 32 + 32 <= g.n) load_old_f16(orow + pc * 32, oldv[pc], g.c_wide);
+      }
       if (!mbar_wait(smem_u32(&bar_tfull[buf]), tph, abortp, g.wait_limit)) { ok = false; break; }
       tc_fence_after();
-      const int row = t.mt * BM + warp * 32 + lane;
-      __half* crow = (__half*)g.c + t.ib0 * g.c_b0 + t.ib1 * g.c_b1 + (long long)row * g.ldc;
       const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16) + buf * BN;
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        const int col0 = t.nt * BN + c * 32;
-        if (col0 >= g.n) break;                      // warp-uniform
-        uint32_t v[32];
-        tmem_ld_32x32(taddr + c * 32, v);
-        tmem_wait_ld();
-        if (row < g.m) {
-          float f[32];
 #pragma unroll
-          for (int q = 0; q < 32; ++q) f[q] = __uint_as_float(v[q]);
-          store_chunk(crow + col0, f, (g.n - col0) < 32 ? (g.n - col0) : 32, g.beta);
+      for (int c = 0; c < NCH; ++c) {
+        const int col0 = t.nt * BN + c * 32;
+        if (col0 < g.n) {                            // warp-uniform
+          uint32_t v[32];
+          tmem_ld_32x32(taddr + c * 32, v);
+          tmem_wait_ld();
+          const int valid = (g.n - col0) < 32 ? (g.n - col0) : 32;
+          if (row < g.m) {
+            float f[32];
+#pragma unroll
+            for (int q = 0; q < 32; ++q) f[q] = __uint_as_float(v[q]);
+            if (g.c_col) {
+              store_chunk_col(cbase + (long long)col0 * g.ldc + row, f, valid, g.ldc, g.beta);
+            } else if (rmw && valid == 32) {
+              add_old_f16(f, oldv[c % AHEAD]);
+              store_chunk(cbase + (long long)row * g.ldc + col0, f, 32, 0, g.c_wide);
+            } else {
+              store_chunk(cbase + (long long)row * g.ldc + col0, f, valid, g.beta, g.c_wide);
+            }
+          }
+          if (rmw && c + AHEAD < NCH && col0 + AHEAD * 32 + 32 <= g.n)
+            load_old_f16(orow + (c + AHEAD) * 32, oldv[c % AHEAD], g.c_wide);
         }
       }
       tc_fence_before();
@@ -400,11 +422,15 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_const
       if (!ok) break;
       const int row = t.mt * BM + quad * 32 + lane;
       if (row < g.m) {
-        float* crow = (float*)g.c + t.ib0 * g.c_b0 + t.ib1 * g.c_b1 + (long long)row * g.ldc;
+        float* cbase = (float*)g.c + t.ib0 * g.c_b0 + t.ib1 * g.c_b1;
 #pragma unroll
         for (int c = 0; c < C::HALF / 32; ++c) {
           const int col0 = t.nt * BN + col_base + c * 32;
-          if (col0 < g.n) store_chunk(crow + col0, &acc[c * 32], (g.n - col0) < 32 ? (g.n - col0) : 32, g.beta);
+          if (col0 < g.n) {
+            const int valid = (g.n - col0) < 32 ? (g.n - col0) : 32;
+            if (g.c_col) store_chunk_col(cbase + (long long)col0 * g.ldc + row, &acc[c * 32], valid, g.ldc, g.beta);
+            else store_chunk(cbase + (long long)row * g.ldc + col0, &acc[c * 32], valid, g.beta, g.c_wide);
+          }
         }
       }
     }
@@ -472,10 +498,8 @@ bool batch_stride_ok(int64_t count, int64_t stride, size_t esize) {
   return stride > 0 && (stride * (int64_t)esize) % 16 == 0;
 }
 
-// Output canonicalisation: a transposed C (unit row stride) is computed as C^T = B^T A^T.
-GemmProblem canonical(const GemmProblem& p) {
-  if (p.c_c == 1 || p.n == 1) return p;
-  if (p.c_r != 1 && p.m != 1) return p;  // not addressable either way; classification will reject it
+// The transposed problem C^T = B^T A^T (same memory, m <-> n, operands exchanged).
+GemmProblem transposed(const GemmProblem& p) {
   GemmProblem q = p;
   q.m = p.n; q.n = p.m;
   q.a = p.b; q.a_b0 = p.b_b0; q.a_b1 = p.b_b1; q.a_red = p.b_red; q.a_r = p.b_c; q.a_c = p.b_r;
@@ -489,13 +513,26 @@ struct Plan {
   GemmProblem p;
   Layout2D la, lb;
   int64_t ldc = 0;
+  int c_col = 0;     // 1: C element (i, j) of the kernel's problem sits at j*ldc + i (column store)
 };
 
-Plan make_plan(const GemmProblem& p0) {
+// Two ways to run a GEMM whose C has a unit stride along one dimension:
+//   row store    : the kernel's N runs along C's unit-stride dimension; each epilogue thread writes
+//                  16-byte vectors of its own row (needs ldc to be a multiple of 16 bytes);
+//   column store : the kernel's M runs along C's unit-stride dimension; for every output column the 32
+//                  lanes of a warp write 32 consecutive elements (fully coalesced, any ldc).
+// Whichever of the problem and its transpose has the required unit stride is used.
+Plan make_plan(const GemmProblem& p0, bool col_store) {
   Plan pl;
   if (p0.dtype == B200_F64) return pl;
   const size_t es = dtype_size(p0.dtype);
-  pl.p = canonical(p0);
+  const bool unit_n = (p0.c_c == 1 || p0.n == 1), unit_m = (p0.c_r == 1 || p0.m == 1);
+  if (!col_store) {
+    if (unit_n) pl.p = p0; else if (unit_m) pl.p = transposed(p0); else return pl;
+  } else {
+    if (unit_m) pl.p = p0; else if (unit_n) pl.p = transposed(p0); else return pl;
+  }
+  pl.c_col = col_store ? 1 : 0;
   const GemmProblem& p = pl.p;
   if (p.m < 1 || p.n < 1 || p.k < 1 || p.b0 < 1 || p.b1 < 1 || p.red < 1) return pl;
   if (p.red > 1 && (p.b0 != 1 || p.b1 != 1)) return pl;
@@ -505,16 +542,25 @@ Plan make_plan(const GemmProblem& p0) {
   pl.lb = classify(p.k, p.n, p.b_r, p.b_c, es);
   if (!pl.la.ok || !pl.lb.ok) return pl;
   const int64_t align = 16 / (int64_t)es;
-  // C: row-major with an aligned leading dimension (vector stores in the epilogue).
-  if (p.n == 1) pl.ldc = p.c_r; else if (p.c_c == 1) pl.ldc = p.c_r; else return pl;
-  if (p.m == 1 && pl.ldc <= 0) pl.ldc = (p.n + align - 1) / align * align;
-  if (pl.ldc <= 0 || pl.ldc % align) return pl;
-  if (((uintptr_t)p.a | (uintptr_t)p.b | (uintptr_t)p.c) & 15) return pl;
+  if (!col_store) {
+    // row-major C with an aligned leading dimension (vector stores in the epilogue)
+    pl.ldc = p.c_r;
+    if (p.m == 1 && pl.ldc <= 0) pl.ldc = (p.n + align - 1) / align * align;
+    if (pl.ldc <= 0 || pl.ldc % align) return pl;
+    if ((uintptr_t)p.c & 15) return pl;
+    if ((p.b0 > 1 && (p.c_b0 <= 0 || p.c_b0 % align)) || (p.b1 > 1 && (p.c_b1 <= 0 || p.c_b1 % align))) return pl;
+  } else {
+    // column-major C: scalar stores, only element alignment is needed
+    pl.ldc = p.c_c;
+    if (p.n == 1 && pl.ldc <= 0) pl.ldc = p.m;
+    if (pl.ldc <= 0) return pl;
+    if ((p.b0 > 1 && p.c_b0 <= 0) || (p.b1 > 1 && p.c_b1 <= 0)) return pl;
+  }
+  if (((uintptr_t)p.a | (uintptr_t)p.b) & 15) return pl;
   if (!batch_stride_ok(p.b0, p.a_b0, es) || !batch_stride_ok(p.b1, p.a_b1, es) ||
       !batch_stride_ok(p.red, p.a_red, es) || !batch_stride_ok(p.b0, p.b_b0, es) ||
       !batch_stride_ok(p.b1, p.b_b1, es) || !batch_stride_ok(p.red, p.b_red, es))
     return pl;
-  if ((p.b0 > 1 && (p.c_b0 <= 0 || p.c_b0 % align)) || (p.b1 > 1 && (p.c_b1 <= 0 || p.c_b1 % align))) return pl;
   pl.ok = true;
   return pl;
 }
@@ -566,6 +612,7 @@ int encode_map(CUtensorMap* map, const void* base, size_t esize, int64_t inner, 
 int g_xform_mode = 1;
 int g_force_bn = 0;   // 0 = choose by problem shape
 int g_mn_box5 = 1;    // MN-major operands: one 5-D TMA box per stage where the extent allows
+int g_store_mode = 0; // 0 = choose, 1 = row stores only, 2 = column stores where possible
 int g_pair_mode = 1;  // 0 = choose by problem shape, 1 = never use CTA pairs (default: not faster yet), 2 = always (n > 128)
 
 // Tensor maps and kernel arguments for a tile grid of TM x TN outputs per scheduling unit, where one
@@ -625,7 +672,13 @@ int build_launch(Launch& L, const Plan& pl, int esize, int tm, int tn, int bmc, 
   g.a_ld = a_ld; g.b_ld = b_ld;
   g.a_x1 = (!reduce && a_xn > 1) ? 1 : 0; g.a_xr = (reduce && a_xn > 1) ? 1 : 0; g.a_y0 = (a_yn > 1) ? 1 : 0;
   g.b_x1 = (!reduce && b_xn > 1) ? 1 : 0; g.b_xr = (reduce && b_xn > 1) ? 1 : 0; g.b_y0 = (b_yn > 1) ? 1 : 0;
-  g.c = p.c; g.c_b0 = p.c_b0; g.c_b1 = p.c_b1; g.ldc = pl.ldc;
+  g.c = p.c; g.c_b0 = p.c_b0; g.c_b1 = p.c_b1; g.ldc = pl.ldc; g.c_col = pl.c_col;
+  {
+    const uint64_t es = (uint64_t)esize;
+    const bool wide = !pl.c_col && ((uintptr_t)p.c % 32 == 0) && ((uint64_t)pl.ldc * es % 32 == 0) &&
+                      (p.b0 <= 1 || (uint64_t)p.c_b0 * es % 32 == 0) && (p.b1 <= 1 || (uint64_t)p.c_b1 * es % 32 == 0);
+    g.c_wide = wide ? 1 : 0;
+  }
   g.beta = p.beta;
   g.xform_mode = g_xform_mode;
   g.wait_limit = 400000000LL + (long long)g.red * g.k_blocks * 40000LL;
@@ -662,23 +715,31 @@ int launch_bn(const Plan& pl, cudaStream_t stream) {
   else return launch_cfg<CfgS<BN>, 4, BN>(pl, stream, gemm_tf32x3_kernel<BN>);
 }
 
-template <int ESIZE>
-int launch_es(const Plan& pl, cudaStream_t stream) {
+// Tile width by a wave model: time ~ ceil(tiles / SMs) * (cost of one tile of that width).  The relative
+// per-tile costs are measured (a 128-wide tile takes about 3/4 of the time of a 256-wide one because its
+// main loop is bound by shared-memory traffic, not by the tensor pipe).  Returns the modelled cost.
+double choose_tile(const Plan& pl, int esize, int* bn_out) {
   const GemmProblem& p = pl.p;
   DeviceState* ds = device_state();
   const int sms = ds ? ds->sm_count : 148;
-  auto tiles = [&](int bn) {
-    return ((p.m + BM - 1) / BM) * ((p.n + bn - 1) / bn) * p.b0 * p.b1;
-  };
-  // Tile width by a wave model: time ~ ceil(tiles / SMs) * (cost of one tile of that width).  The
-  // relative per-tile costs are measured (a 128-wide tile takes about 3/4 of the time of a 256-wide
-  // one because its main loop is bound by shared-memory bandwidth, not by the tensor pipe).
-  const double w256 = 1.0, w128 = (ESIZE == 4) ? 0.75 : 0.87, w64 = (ESIZE == 4) ? 0.55 : 0.70;
+  auto tiles = [&](int bn) { return ((p.m + BM - 1) / BM) * ((p.n + bn - 1) / bn) * p.b0 * p.b1; };
+  const double w256 = 1.0, w128 = (esize == 4) ? 0.75 : 0.87, w64 = (esize == 4) ? 0.55 : 0.70;
   auto waves = [&](int bn_) { return (double)((tiles(bn_) + sms - 1) / sms); };
   int bn = 64;
   double best = waves(64) * w64;
   if (p.n > 64 && waves(128) * w128 <= best) { best = waves(128) * w128; bn = 128; }
   if (p.n > 128 && waves(256) * w256 <= best) { best = waves(256) * w256; bn = 256; }
+  *bn_out = bn;
+  return best;
+}
+
+template <int ESIZE>
+int launch_es(const Plan& pl, cudaStream_t stream) {
+  const GemmProblem& p = pl.p;
+  DeviceState* ds = device_state();
+  const int sms = ds ? ds->sm_count : 148;
+  int bn = 64;
+  const double best = choose_tile(pl, ESIZE, &bn);
   if (g_force_bn) bn = g_force_bn;
   // CTA pairs (256 x 256 tiles on two SMs) when the problem fills the machine with them.
   if (!g_force_bn && g_pair_mode != 1 && p.n > 128) {
@@ -702,7 +763,7 @@ int set_attr(Kernel kernel) {
 
 }  // namespace
 
-bool tc_eligible(const GemmProblem& p) { return make_plan(p).ok; }
+bool tc_eligible(const GemmProblem& p) { return make_plan(p, false).ok || make_plan(p, true).ok; }
 
 int tc_setup_device() {
   int st = 0;
@@ -717,15 +778,35 @@ int tc_setup_device() {
 }
 
 int launch_gemm_tc(const GemmProblem& p, cudaStream_t stream) {
-  const Plan pl = make_plan(p);
-  if (!pl.ok) return B200_ERR_UNSUPPORTED;
-  if (p.dtype == B200_F32) return launch_es<4>(pl, stream);
-  return launch_es<2>(pl, stream);
+  const int es = (p.dtype == B200_F32) ? 4 : 2;
+  Plan row = make_plan(p, false), col = make_plan(p, true);
+  if (g_store_mode == 1) col.ok = false;
+  if (g_store_mode == 2 && col.ok) row.ok = false;
+  if (!row.ok && !col.ok) return B200_ERR_UNSUPPORTED;
+  const Plan* pl = &row;
+  if (!row.ok) {
+    pl = &col;
+  } else if (col.ok) {
+    // Both orientations are possible.  Row stores (vector accesses) are faster per tile; the column-store
+    // orientation is taken only for f32 outputs and only when it wastes clearly less of the machine (e.g. an
+    // output with 64 rows, which fills half of a 128-row tile but exactly one 64-column tile).
+    int bn;
+    const double cr = choose_tile(row, es, &bn), cc = choose_tile(col, es, &bn);
+    auto m_waste = [](const Plan& q) {
+      const double padded = (double)((q.p.m + BM - 1) / BM) * BM;
+      return 1.0 - (double)q.p.m / padded;
+    };
+    const bool rows_wasted = m_waste(row) >= 0.4 && m_waste(col) < 0.2;   // e.g. 64 output rows in 128-row tiles
+    if (g_store_mode == 2 || (es == 4 && (cc < 0.8 * cr || rows_wasted))) pl = &col;
+  }
+  if (p.dtype == B200_F32) return launch_es<4>(*pl, stream);
+  return launch_es<2>(*pl, stream);
 }
 
 void tc_set_xform_mode(int mode) { g_xform_mode = mode; }
 void tc_set_tile_n(int bn) { g_force_bn = bn; }
 void tc_set_mn_box5(int on) { g_mn_box5 = on; }
 void tc_set_pair_mode(int mode) { g_pair_mode = mode; }
+void tc_set_store_mode(int mode) { g_store_mode = mode; }
 
 }  // namespace b200

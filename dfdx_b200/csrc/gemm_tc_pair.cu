@@ -241,7 +241,7 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_con
       if (!mbar_wait(smem_u32(&bar_tfull[buf]), tph, abortp, g.wait_limit)) { ok = false; break; }
       tc_fence_after();
       const int row = t.mt * 2 * PBM + rank * PBM + warp * 32 + lane;
-      __half* crow = (__half*)g.c + t.ib0 * g.c_b0 + t.ib1 * g.c_b1 + (long long)row * g.ldc;
+      __half* cbase = (__half*)g.c + t.ib0 * g.c_b0 + t.ib1 * g.c_b1;
       const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16) + buf * PBN;
 #pragma unroll 1
       for (int c = 0; c < PBN / 32; ++c) {
@@ -254,7 +254,9 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_con
           float f[32];
 #pragma unroll
           for (int q = 0; q < 32; ++q) f[q] = __uint_as_float(v[q]);
-          store_chunk(crow + col0, f, (g.n - col0) < 32 ? (g.n - col0) : 32, g.beta);
+          const int valid = (g.n - col0) < 32 ? (g.n - col0) : 32;
+          if (g.c_col) store_chunk_col(cbase + (long long)col0 * g.ldc + row, f, valid, g.ldc, g.beta);
+          else store_chunk(cbase + (long long)row * g.ldc + col0, f, valid, g.beta, g.c_wide);
         }
       }
       tc_fence_before();
@@ -506,11 +508,15 @@ gemm_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_
       if (!ok) break;
       const int row = t.mt * 2 * PBM + rank * PBM + quad * 32 + lane;
       if (row < g.m) {
-        float* crow = (float*)g.c + t.ib0 * g.c_b0 + t.ib1 * g.c_b1 + (long long)row * g.ldc;
+        float* cbase = (float*)g.c + t.ib0 * g.c_b0 + t.ib1 * g.c_b1;
 #pragma unroll
         for (int c = 0; c < C::HALF / 32; ++c) {
           const int col0 = t.nt * PBN + col_base + c * 32;
-          if (col0 < g.n) store_chunk(crow + col0, &acc[c * 32], (g.n - col0) < 32 ? (g.n - col0) : 32, g.beta);
+          if (col0 < g.n) {
+            const int valid = (g.n - col0) < 32 ? (g.n - col0) : 32;
+            if (g.c_col) store_chunk_col(cbase + (long long)col0 * g.ldc + row, &acc[c * 32], valid, g.ldc, g.beta);
+            else store_chunk(cbase + (long long)row * g.ldc + col0, &acc[c * 32], valid, g.beta, g.c_wide);
+          }
         }
       }
     }

@@ -220,15 +220,45 @@ struct TcArgs {
   int b_x1, b_xr, b_y0;
   void* c;
   long long c_b0, c_b1, ldc;      // element strides
+  int c_col;                      // 0: C(i,j) at i*ldc + j (row store); 1: at j*ldc + i (column store)
+  int c_wide;                     // row store: every row start is 32-byte aligned (256-bit accesses)
   int beta;
   int xform_mode;                 // f32: 1 = big stays raw, write small only; 0 = also rewrite big = tf32_rn(x)
   long long wait_limit;           // clock cycles
   int* status;
 };
 
-// 32 consecutive f32 accumulator columns of one output row -> global memory.
-__device__ __forceinline__ void store_chunk(float* dst, const float* v, int valid, int beta) {
-  if (valid == 32) {
+// 256-bit global accesses (sm_100): one 32-byte sector per thread and instruction.
+__device__ __forceinline__ void ld_global_v8(const void* p, uint32_t (&r)[8]) {
+  asm volatile("ld.global.v8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+               : "l"(p));
+}
+__device__ __forceinline__ void st_global_v8(void* p, const uint32_t (&r)[8]) {
+  asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+               ::"l"(p), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+               : "memory");
+}
+
+// 32 consecutive f32 accumulator columns of one output row -> global memory.  `wide`: the row start is
+// 32-byte aligned, so whole sectors are written per thread; otherwise 16-byte pieces.
+__device__ __forceinline__ void store_chunk(float* dst, const float* v, int valid, int beta, int wide) {
+  if (valid == 32 && wide) {
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      uint32_t o[8];
+      if (beta) {
+        uint32_t old[8];
+        ld_global_v8(dst + 8 * q, old);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) o[e] = __float_as_uint(v[8 * q + e] + __uint_as_float(old[e]));
+      } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) o[e] = __float_as_uint(v[8 * q + e]);
+      }
+      st_global_v8(dst + 8 * q, o);
+    }
+  } else if (valid == 32) {
 #pragma unroll
     for (int q = 0; q < 8; ++q) {
       float4 o = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
@@ -249,27 +279,59 @@ __device__ __forceinline__ void store_chunk(float* dst, const float* v, int vali
   }
 }
 
-__device__ __forceinline__ void store_chunk(__half* dst, const float* v, int valid, int beta) {
-  if (valid == 32) {
+// The 32 f16 values (64 bytes) a row already holds at dst, as 16 packed registers.
+__device__ __forceinline__ void load_old_f16(const __half* src, uint32_t (&old)[16], int wide) {
+  if (wide) {
+    uint32_t a[8], b[8];
+    ld_global_v8(src, a);
+    ld_global_v8(src + 16, b);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) { old[e] = a[e]; old[8 + e] = b[e]; }
+  } else {
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
-      float f[8];
+      const uint4 t = *reinterpret_cast<const uint4*>(src + 8 * q);
+      old[4 * q] = t.x; old[4 * q + 1] = t.y; old[4 * q + 2] = t.z; old[4 * q + 3] = t.w;
+    }
+  }
+}
+__device__ __forceinline__ void add_old_f16(float* v, const uint32_t (&old)[16]) {
 #pragma unroll
-      for (int e = 0; e < 8; ++e) f[e] = v[8 * q + e];
-      if (beta) {
-        const uint4 old = *reinterpret_cast<const uint4*>(dst + 8 * q);
-        const __half2* oh = reinterpret_cast<const __half2*>(&old);
+  for (int e = 0; e < 16; ++e) {
+    const float2 t = __half22float2(*reinterpret_cast<const __half2*>(&old[e]));
+    v[2 * e] += t.x; v[2 * e + 1] += t.y;
+  }
+}
+
+__device__ __forceinline__ void store_chunk(__half* dst, const float* v, int valid, int beta, int wide) {
+  if (valid == 32) {
+    uint32_t pk[16];
+    if (beta) {
+      uint32_t old[16];
+      load_old_f16(dst, old, wide);
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const float2 t = __half22float2(oh[e]);
-          f[2 * e] += t.x; f[2 * e + 1] += t.y;
-        }
+      for (int e = 0; e < 16; ++e) {
+        const float2 t = __half22float2(*reinterpret_cast<const __half2*>(&old[e]));
+        const __half2 h = __floats2half2_rn(v[2 * e] + t.x, v[2 * e + 1] + t.y);
+        pk[e] = *reinterpret_cast<const uint32_t*>(&h);
       }
-      uint4 pk;
-      __half2* ph = reinterpret_cast<__half2*>(&pk);
+    } else {
 #pragma unroll
-      for (int e = 0; e < 4; ++e) ph[e] = __floats2half2_rn(f[2 * e], f[2 * e + 1]);
-      *reinterpret_cast<uint4*>(dst + 8 * q) = pk;
+      for (int e = 0; e < 16; ++e) {
+        const __half2 h = __floats2half2_rn(v[2 * e], v[2 * e + 1]);
+        pk[e] = *reinterpret_cast<const uint32_t*>(&h);
+      }
+    }
+    if (wide) {
+      uint32_t a[8], b[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) { a[e] = pk[e]; b[e] = pk[8 + e]; }
+      st_global_v8(dst, a);
+      st_global_v8(dst + 16, b);
+    } else {
+#pragma unroll
+      for (int q = 0; q < 4; ++q)
+        *reinterpret_cast<uint4*>(dst + 8 * q) = make_uint4(pk[4 * q], pk[4 * q + 1], pk[4 * q + 2], pk[4 * q + 3]);
     }
   } else {
 #pragma unroll
@@ -280,6 +342,24 @@ __device__ __forceinline__ void store_chunk(__half* dst, const float* v, int val
         dst[q] = __float2half_rn(o);
       }
   }
+}
+
+// Column store: the 32 lanes of a warp hold 32 consecutive rows, so for every column they write 32
+// consecutive elements.  dst points at (row, col0); v holds the row's 32 columns from col0 on.
+template <typename OutT>
+__device__ __forceinline__ void store_chunk_col(OutT* dst, const float* v, int valid, long long ldc, int beta) {
+#pragma unroll
+  for (int q = 0; q < 32; ++q)
+    if (q < valid) {
+      float o = v[q];
+      if constexpr (sizeof(OutT) == 2) {
+        if (beta) o += __half2float(dst[q * ldc]);
+        dst[q * ldc] = __float2half_rn(o);
+      } else {
+        if (beta) o += dst[q * ldc];
+        dst[q * ldc] = o;
+      }
+    }
 }
 
 struct TileCoord { int mt, nt, ib0, ib1; };

@@ -95,6 +95,10 @@ int b200_set_mn_single_box(int on);
  * planner choose between them and the CTA-pair (cta_group::2, 256x256 tiles) kernels by a wave model, 2 forces
  * the pair kernels wherever the output is wider than 128 columns. */
 int b200_set_cta_pair_mode(int mode);
+/* Epilogue store orientation of the tensor-core kernels (testing / profiling): 0 (default) planner's choice,
+ * 1 row stores only (each thread writes 16-byte pieces of its output row), 2 column stores wherever possible
+ * (the kernel's M runs along the output's unit-stride dimension; warp stores are contiguous). */
+int b200_set_store_mode(int mode);
 /* Number of kernel launches this library has enqueued since load (all threads). */
 uint64_t b200_launch_count(void);
 /* Of those, launches of tcgen05 tensor-core kernels. */

@@ -106,14 +106,17 @@ def test_simt_degenerate_stride_pairs(cuda_dev, oracle):
 TC_SHAPES = [(128, 64, 64), (128, 64, 256), (200, 136, 72), (264, 520, 104), (64, 1032, 136), (384, 40, 512)]
 
 
+@pytest.mark.parametrize("store", [pytest.param(1, id="rowstore"), pytest.param(2, id="colstore")])
 @pytest.mark.parametrize("tile_n", [64, 128, 256])
 @pytest.mark.parametrize("dtype", [torch.float16, torch.float32])
 @pytest.mark.parametrize("layout", ["".join(p) for p in itertools.product("rc", repeat=3)])
-def test_tensor_core_layouts(cuda_dev, oracle, dtype, layout, tile_n):
-    """tcgen05 path forced, every tile width: K-major / MN-major A and B, row-major / transposed C,
-    ragged M, N and K (TMA zero fill), padded leading dimensions, beta 0 and 1."""
+def test_tensor_core_layouts(cuda_dev, oracle, dtype, layout, tile_n, store):
+    """tcgen05 path forced, every tile width and both epilogue store orientations: K-major / MN-major A
+    and B, row-major / transposed C, ragged M, N and K (TMA zero fill), padded leading dimensions,
+    beta 0 and 1."""
     cuda_dev.set_path(dfdx_b200.PATH_TENSOR)
     assert cuda_dev.lib.b200_set_tile_n(tile_n) == 0
+    assert cuda_dev.lib.b200_set_store_mode(store) == 0
     try:
         before = cuda_dev.lib.b200_tensor_launch_count()
         for i, (m, k, n) in enumerate(TC_SHAPES):
@@ -121,6 +124,7 @@ def test_tensor_core_layouts(cuda_dev, oracle, dtype, layout, tile_n):
         assert cuda_dev.lib.b200_tensor_launch_count() - before == len(TC_SHAPES)
     finally:
         cuda_dev.lib.b200_set_tile_n(0)
+        cuda_dev.lib.b200_set_store_mode(0)
         cuda_dev.set_path(dfdx_b200.PATH_AUTO)
 
 
