@@ -34,6 +34,9 @@ FLOP_PER_ITEM = 6 * S * K * N              # fwd + two backward GEMMs for one ba
 FLOP_PER_STEP = B * FLOP_PER_ITEM          # 412.3 GFLOP
 FLOP_PER_LAUNCH = FLOP_PER_STEP / 3.0      # each of the three GEMMs: 137.4 GFLOP
 METRIC = "gemm_fwd_bwd_tflops"
+# dram__bytes_read.sum + dram__bytes_write.sum per launch from one ncu capture of this workload
+# (forward 306.6 MB, grad_rhs 359.8 MB, grad_lhs 442.9 MB).
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 369.8e6
 WORKLOAD = f"config[1]: MatMatBr f32 X[{B},{S},{K}] x W^T, W stored [{N},{K}], fwd + grad_lhs + grad_rhs"
 
 
@@ -391,7 +394,9 @@ def main():
                     "d2h_bytes_per_step": int(gw_h.numel() * 4),
                     "api": "dfdx_b200.Cuda.matmul + backward, pinned host inputs (X, dY) in, grad_rhs out"},
             "roofline": {"bound": "tensor", "achieved": round(achieved, 2), "peak": round(peak, 2), "unit": "TFLOP/s",
-                         "frac": round(achieved / peak, 4), "traffic": None,
+                         "frac": round(achieved / peak, 4), "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH,
+                         "traffic_note": "dram read+write bytes per launch, mean of the 3 launches of a step, one ncu "
+                                         "capture (profiles/gemm_tf32x3_config2.md); algorithmic mean 380 MB",
                          "kernel": "gemm_tf32x3_kernel<256> (logical f32 flops; 3 tf32 MMAs per logical MAC)",
                          "peak_basis": f"{which} bf16_tflops_sustained / 2 (tf32) / 3 (3xTF32)",
                          "avg_launch_ms": round(per_launch_ms, 4)},
