@@ -21,6 +21,7 @@ void tc_set_tile_n(int bn);
 void tc_set_mn_box5(int on);
 void tc_set_pair_mode(int mode);
 void tc_set_store_mode(int mode);
+void tc_set_split_mode(int mode);
 
 namespace {
 
@@ -183,6 +184,14 @@ int b200_set_cta_pair_mode(int mode) {
 int b200_set_store_mode(int mode) {
   if (mode < 0 || mode > 2) return B200_ERR_UNSUPPORTED;
   tc_set_store_mode(mode);
+  return B200_OK;
+}
+
+/* Testing hook: split-K of the f32 tensor-core kernel: 0 (default) planner's choice, 1 never, n in 2..64 forces
+ * n K-slices on single-batch problems. */
+int b200_set_split_k(int mode) {
+  if (mode < 0 || mode > 64) return B200_ERR_UNSUPPORTED;
+  tc_set_split_mode(mode);
   return B200_OK;
 }
 

@@ -275,10 +275,41 @@ int backward_t(int dtype, const Op& op, const T* img, T* grad_img, const T* filt
   if (n_patches == 0 || n_filters == 0) return B200_OK;
   uint8_t* base = (uint8_t*)ws;
   T* patches = (T*)base;
-  T* ftr = (T*)(base + align256((size_t)n_patches * sizeof(T)));
+  const int64_t n_fwd_patches = op.batch * op.chan_in * KK * op.h_out * op.w_out;
+  T* ftr = (T*)(base + align256((size_t)(n_patches > n_fwd_patches ? n_patches : n_fwd_patches) * sizeof(T)));
   T* gftr = (T*)((uint8_t*)ftr + align256((size_t)n_filters * sizeof(T)));
   Strides4 st{{(int64_t)fs[0], (int64_t)fs[1], (int64_t)fs[2], (int64_t)fs[3]}};
   int rc;
+
+  // grad_filters first, while the workspace is free: with contiguous filters,
+  //   grad_filters (G, O/G, C/G*K*K) += sum_b grad_out_b (G, O/G, OH*OW) x patches(img_b)^T (G, OH*OW, C/G*K*K)
+  // is one batch-reduced GEMM per group (O/G rows: full tiles) that accumulates straight into the filter
+  // layout, instead of per-image GEMMs into a B-fold temporary followed by a sum.
+  const bool filters_contig = (int64_t)fs[3] == 1 && (int64_t)fs[2] == op.kernel && (int64_t)fs[1] == KK &&
+                              (int64_t)fs[0] == cg * KK;
+  bool grad_filters_done = false;
+  // (f32 only: that kernel can cut the long reduction into K slices; the f16 kernel cannot yet.)
+  if (grad_filters && filters_contig && n_fwd_patches > 0 && dtype == B200_F32) {
+    const int64_t npos = op.h_out * op.w_out;
+    Strides4 ist{{op.chan_in * hw, hw, op.w_in, 1}};
+    if (plane_path_input<T>(op))
+      unfold_input_plane_kernel<T><<<(unsigned)(op.batch * op.chan_in), NT, (size_t)hw * sizeof(T), stream>>>(
+          to_op32(op), img, ist, patches);
+    else
+      unfold_input_kernel<T><<<grid_for(n_fwd_patches, sms), NT, 0, stream>>>(op, img, ist, patches, n_fwd_patches);
+    count_launch(false);
+    if ((rc = note_cuda_error(cudaGetLastError(), "unfold_input launch (backward)"))) return rc;
+    for (int64_t gi = 0; gi < G; ++gi) {
+      GemmProblem p;
+      p.dtype = dtype; p.beta = 1; p.red = op.batch; p.m = og; p.k = npos; p.n = cg * KK;
+      p.a = grad_out + gi * og * npos; p.a_red = op.chan_out * npos; p.a_r = npos; p.a_c = 1;
+      p.b = patches + gi * cg * KK * npos; p.b_red = op.chan_in * KK * npos; p.b_r = 1; p.b_c = npos;
+      p.c = grad_filters + gi * og * cg * KK; p.c_r = cg * KK; p.c_c = 1;
+      if ((rc = run_gemm(p, stream))) return rc;
+    }
+    grad_filters_done = true;
+    if (!grad_img) return B200_OK;
+  }
 
   if (plane_path_output<T>(op))
     unfold_output_plane_kernel<T><<<(unsigned)(op.batch * op.chan_out), NT,
@@ -301,7 +332,7 @@ int backward_t(int dtype, const Op& op, const T* img, T* grad_img, const T* filt
     p.c = grad_img; p.c_b0 = G * m * n; p.c_b1 = m * n; p.c_r = n; p.c_c = 1;
     if ((rc = run_gemm(p, stream))) return rc;
   }
-  if (grad_filters) {
+  if (grad_filters && !grad_filters_done) {
     // grad_filters_tr (B, G, C/G, O/G*K*K) = img (B, G, C/G, H*W) x patches^T (B, G, H*W, O/G*K*K)
     const int64_t m = cg, k = hw, n = og * KK;
     GemmProblem p;
@@ -326,8 +357,9 @@ size_t conv2d_workspace_bytes(int dtype, const b200_conv2d_op* o, int backward) 
   const size_t KK = o->kernel * o->kernel;
   if (!backward) return align256(o->batch * o->chan_in * KK * o->h_out * o->w_out * es);
   const size_t nf = o->groups * (o->chan_in / o->groups) * (o->chan_out / o->groups) * KK;
-  return align256(o->batch * o->chan_out * KK * o->h_in * o->w_in * es) + align256(nf * es) +
-         align256(o->batch * nf * es);
+  const size_t bwd_patches = o->batch * o->chan_out * KK * o->h_in * o->w_in * es;
+  const size_t fwd_patches = o->batch * o->chan_in * KK * o->h_out * o->w_out * es;
+  return align256(bwd_patches > fwd_patches ? bwd_patches : fwd_patches) + align256(nf * es) + align256(o->batch * nf * es);
 }
 
 int conv2d_forward(int dtype, const b200_conv2d_op* o, const void* img, const size_t is[4], const void* filters,

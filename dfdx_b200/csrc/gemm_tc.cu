@@ -231,8 +231,9 @@ __device__ __forceinline__ void split_role(const TcArgs& g, uint32_t smem_base, 
   constexpr int PER = NVEC / SPLIT_THREADS;             // 6 (BN = 256), 4 (128), 3 (64)
   uint32_t it = 0;
   bool ok = true;
-  for (long long tile = blockIdx.x; ok && tile < g.total_tiles; tile += gridDim.x) {
-    for (int i = 0; i < total_kb; ++i, ++it) {
+  for (long long unit = blockIdx.x; ok && unit < g.total_units; unit += gridDim.x) {
+    const Unit un = decode_unit(g, unit, total_kb);
+    for (int i = un.kb_lo; i < un.kb_hi; ++i, ++it) {
       const int s = it % STAGES;
       const uint32_t ph = (it / STAGES) & 1u;
       if (!mbar_wait(smem_u32(&bar_full[s]), ph, abortp, g.wait_limit)) { ok = false; break; }
@@ -323,9 +324,10 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_const
       // ---------------------------------------------------------------- TMA producer
       uint32_t it = 0;
       bool ok = true;
-      for (long long tile = blockIdx.x; ok && tile < g.total_tiles; tile += gridDim.x) {
-        const TileCoord t = decode_tile(g, tile);
-        for (int i = 0; i < total_kb; ++i, ++it) {
+      for (long long unit = blockIdx.x; ok && unit < g.total_units; unit += gridDim.x) {
+        const Unit un = decode_unit(g, unit, total_kb);
+        const TileCoord t = decode_tile(g, un.tile);
+        for (int i = un.kb_lo; i < un.kb_hi; ++i, ++it) {
           const int r = i / g.k_blocks, kb = i - r * g.k_blocks;
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1u;
@@ -352,13 +354,14 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_const
       const uint32_t a_kadv = g.a_mn ? C::MN_KADV : C::K_KADV, b_kadv = g.b_mn ? C::MN_KADV : C::K_KADV;
       uint32_t it = 0, ccount = 0;
       bool ok = true;
-      for (long long tile = blockIdx.x; ok && tile < g.total_tiles; tile += gridDim.x) {
-        for (int kb0 = 0; ok && kb0 < total_kb; kb0 += C::CHUNK_KB, ++ccount) {
+      for (long long unit = blockIdx.x; ok && unit < g.total_units; unit += gridDim.x) {
+        const Unit un = decode_unit(g, unit, total_kb);
+        for (int kb0 = un.kb_lo; ok && kb0 < un.kb_hi; kb0 += C::CHUNK_KB, ++ccount) {
           const uint32_t buf = ccount & 1u, cph = (ccount >> 1) & 1u;
           if (!mbar_wait(smem_u32(&bar_tempty[buf]), cph ^ 1u, abortp, g.wait_limit)) { ok = false; break; }
           tc_fence_after();
           const uint32_t d_tmem = tmem_base + buf * BN;
-          const int nkb = (total_kb - kb0) < C::CHUNK_KB ? (total_kb - kb0) : C::CHUNK_KB;
+          const int nkb = (un.kb_hi - kb0) < C::CHUNK_KB ? (un.kb_hi - kb0) : C::CHUNK_KB;
           for (int i = 0; i < nkb; ++i, ++it) {
             const int s = it % STAGES;
             const uint32_t ph = (it / STAGES) & 1u;
@@ -398,12 +401,13 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_const
     const int col_base = wg * C::HALF;                // this warpgroup's half of the tile's columns
     uint32_t ccount = 0;
     bool ok = true;
-    for (long long tile = blockIdx.x; ok && tile < g.total_tiles; tile += gridDim.x) {
-      const TileCoord t = decode_tile(g, tile);
+    for (long long unit = blockIdx.x; ok && unit < g.total_units; unit += gridDim.x) {
+      const Unit un = decode_unit(g, unit, total_kb);
+      const TileCoord t = decode_tile(g, un.tile);
       float acc[C::HALF];
 #pragma unroll
       for (int q = 0; q < C::HALF; ++q) acc[q] = 0.f;
-      for (int kb0 = 0; kb0 < total_kb; kb0 += C::CHUNK_KB, ++ccount) {
+      for (int kb0 = un.kb_lo; kb0 < un.kb_hi; kb0 += C::CHUNK_KB, ++ccount) {
         const uint32_t buf = ccount & 1u, cph = (ccount >> 1) & 1u;
         if (!mbar_wait(smem_u32(&bar_tfull[buf]), cph, abortp, g.wait_limit)) { ok = false; break; }
         tc_fence_after();
@@ -428,8 +432,14 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_const
           const int col0 = t.nt * BN + col_base + c * 32;
           if (col0 < g.n) {
             const int valid = (g.n - col0) < 32 ? (g.n - col0) : 32;
-            if (g.c_col) store_chunk_col(cbase + (long long)col0 * g.ldc + row, &acc[c * 32], valid, g.ldc, g.beta);
-            else store_chunk(cbase + (long long)row * g.ldc + col0, &acc[c * 32], valid, g.beta, g.c_wide);
+            if (g.ksplit > 1) {
+              if (g.c_col) add_chunk_atomic_col(cbase + (long long)col0 * g.ldc + row, &acc[c * 32], valid, g.ldc);
+              else add_chunk_atomic(cbase + (long long)row * g.ldc + col0, &acc[c * 32], valid);
+            } else if (g.c_col) {
+              store_chunk_col(cbase + (long long)col0 * g.ldc + row, &acc[c * 32], valid, g.ldc, g.beta);
+            } else {
+              store_chunk(cbase + (long long)row * g.ldc + col0, &acc[c * 32], valid, g.beta, g.c_wide);
+            }
           }
         }
       }
@@ -612,6 +622,7 @@ int encode_map(CUtensorMap* map, const void* base, size_t esize, int64_t inner, 
 int g_xform_mode = 1;
 int g_force_bn = 0;   // 0 = choose by problem shape
 int g_mn_box5 = 1;    // MN-major operands: one 5-D TMA box per stage where the extent allows
+int g_split_mode = 0; // split-K of the f32 kernel: 0 = choose, 1 = never, n >= 2 = force n slices (testing)
 int g_store_mode = 0; // 0 = choose, 1 = row stores only, 2 = column stores where possible
 int g_pair_mode = 1;  // 0 = choose by problem shape, 1 = never use CTA pairs (default: not faster yet), 2 = always (n > 128)
 
@@ -666,6 +677,7 @@ int build_launch(Launch& L, const Plan& pl, int esize, int tm, int tn, int bmc, 
   // possible (an A panel is consumed by all its N tiles at once), which keeps DRAM reads near one pass.
   g.n_fast = g.n_tiles < g.m_tiles ? 1 : 0;
   g.total_tiles = (long long)g.m_tiles * g.n_tiles * p.b0 * p.b1;
+  g.ksplit = 1; g.kb_per_slice = 0; g.total_units = g.total_tiles;   // launch_cfg fills the slice length
   g.red = (int)p.red;
   g.k_blocks = (int)((p.k + bk - 1) / bk);
   g.a_mn = a_mn; g.b_mn = b_mn;
@@ -686,14 +698,31 @@ int build_launch(Launch& L, const Plan& pl, int esize, int tm, int tn, int bmc, 
   return B200_OK;
 }
 
-// C: CfgH<BN> or CfgS<BN>; KERNEL: the matching kernel.
+// C: CfgH<BN> or CfgS<BN>; KERNEL: the matching kernel.  ksplit > 1 (f32 kernel only): K is cut into that many
+// slices, each (tile, slice) is a work unit and the slices' partial results are added into C atomically; for
+// beta = 0 the output is zeroed first.
 template <typename C, int ESIZE, int BN, typename Kernel>
-int launch_cfg(const Plan& pl, cudaStream_t stream, Kernel kernel) {
+int launch_cfg(const Plan& pl, cudaStream_t stream, Kernel kernel, int ksplit) {
   Launch L;
   const int st = build_launch(L, pl, ESIZE, BM, BN, BM, BN, C::BK, C::CH);
   if (st) return st;
   DeviceState* ds = device_state();
-  const long long grid = L.g.total_tiles < ds->sm_count ? L.g.total_tiles : ds->sm_count;
+  TcArgs& g = L.g;
+  const int total_kb = g.red * g.k_blocks;
+  g.kb_per_slice = total_kb;
+  if (ESIZE == 4 && ksplit > 1 && total_kb >= 2 * ksplit) {
+    g.kb_per_slice = (total_kb + ksplit - 1) / ksplit;
+    g.ksplit = (total_kb + g.kb_per_slice - 1) / g.kb_per_slice;
+    g.total_units = g.total_tiles * g.ksplit;
+    if (g.ksplit > 1 && !g.beta) {
+      const GemmProblem& p = pl.p;   // single batch item (checked by the caller)
+      const size_t width = (size_t)(pl.c_col ? p.m : p.n) * 4, height = (size_t)(pl.c_col ? p.n : p.m);
+      const int rc = note_cuda_error(cudaMemset2DAsync(p.c, (size_t)pl.ldc * 4, 0, width, height, stream),
+                                     "cudaMemset2DAsync(split-K output)");
+      if (rc) return rc;
+    }
+  }
+  const long long grid = g.total_units < ds->sm_count ? g.total_units : ds->sm_count;
   if (grid <= 0) return B200_OK;
   kernel<<<(unsigned)grid, C::THREADS, C::SMEM_BYTES, stream>>>(L.ma, L.mb, L.g);
   count_launch(true);
@@ -710,9 +739,9 @@ int launch_pair_plan(const Plan& pl, int esize, cudaStream_t stream) {
 }
 
 template <int ESIZE, int BN>
-int launch_bn(const Plan& pl, cudaStream_t stream) {
-  if constexpr (ESIZE == 2) return launch_cfg<CfgH<BN>, 2, BN>(pl, stream, gemm_f16_kernel<BN>);
-  else return launch_cfg<CfgS<BN>, 4, BN>(pl, stream, gemm_tf32x3_kernel<BN>);
+int launch_bn(const Plan& pl, cudaStream_t stream, int ksplit) {
+  if constexpr (ESIZE == 2) return launch_cfg<CfgH<BN>, 2, BN>(pl, stream, gemm_f16_kernel<BN>, 1);
+  else return launch_cfg<CfgS<BN>, 4, BN>(pl, stream, gemm_tf32x3_kernel<BN>, ksplit);
 }
 
 // Tile width by a wave model: time ~ ceil(tiles / SMs) * (cost of one tile of that width).  The relative
@@ -748,10 +777,34 @@ int launch_es(const Plan& pl, cudaStream_t stream) {
     const double cost2 = (double)((tiles2 + pairs - 1) / pairs) * 0.8;   // a pair wave of 256x256 tiles vs a wave of 128x256 tiles
     if (g_pair_mode == 2 || (p.m > 128 && cost2 <= best)) return launch_pair_plan(pl, ESIZE, stream);
   }
+  // Split-K (f32, one batch item): when the tiles alone leave most SMs idle, K slices become extra work
+  // units.  Model: time = waves * (k-blocks per unit * t_kb(tile width) + t_fixed), in microseconds.
+  int ksplit = 1;
+  if (ESIZE == 4 && g_split_mode != 1 && p.b0 == 1 && p.b1 == 1) {
+    const int64_t total_kb = p.red * ((p.k + 15) / 16);
+    auto model = [&](int bn_, int s_) {
+      const int64_t tiles = ((p.m + BM - 1) / BM) * ((p.n + bn_ - 1) / bn_);
+      const double t_kb = bn_ == 256 ? 0.65 : (bn_ == 128 ? 0.48 : 0.36);
+      const double waves = (double)((tiles * s_ + sms - 1) / sms);
+      return waves * ((double)((total_kb + s_ - 1) / s_) * t_kb + 4.0 + (s_ > 1 ? 2.0 : 0.0));
+    };
+    double best_t = model(bn, 1);
+    const int widths[3] = {256, 128, 64};
+    for (int wi = 0; wi < 3; ++wi) {
+      const int bn_ = widths[wi];
+      if ((bn_ == 256 && p.n <= 128) || (bn_ == 128 && p.n <= 64) || (g_force_bn && bn_ != g_force_bn)) continue;
+      for (int s_ = 2; s_ <= 64; ++s_) {
+        if (total_kb / s_ < 16) break;                      // at least one promotion chunk per slice
+        const double t = model(bn_, s_);
+        if (t < 0.85 * best_t) { best_t = t; bn = bn_; ksplit = s_; }
+      }
+    }
+    if (g_split_mode >= 2) ksplit = g_split_mode;           // testing: force this many slices
+  }
   switch (bn) {
-    case 256: return launch_bn<ESIZE, 256>(pl, stream);
-    case 128: return launch_bn<ESIZE, 128>(pl, stream);
-    default: return launch_bn<ESIZE, 64>(pl, stream);
+    case 256: return launch_bn<ESIZE, 256>(pl, stream, ksplit);
+    case 128: return launch_bn<ESIZE, 128>(pl, stream, ksplit);
+    default: return launch_bn<ESIZE, 64>(pl, stream, ksplit);
   }
 }
 
@@ -787,17 +840,12 @@ int launch_gemm_tc(const GemmProblem& p, cudaStream_t stream) {
   if (!row.ok) {
     pl = &col;
   } else if (col.ok) {
-    // Both orientations are possible.  Row stores (vector accesses) are faster per tile; the column-store
-    // orientation is taken only for f32 outputs and only when it wastes clearly less of the machine (e.g. an
-    // output with 64 rows, which fills half of a 128-row tile but exactly one 64-column tile).
+    // Both orientations are possible.  Row stores (vector accesses) are much faster per tile (measured: even an
+    // output with 64 rows, half of a 128-row tile, is faster with row stores), so the column-store orientation is
+    // taken only where the model says it halves the work.
     int bn;
     const double cr = choose_tile(row, es, &bn), cc = choose_tile(col, es, &bn);
-    auto m_waste = [](const Plan& q) {
-      const double padded = (double)((q.p.m + BM - 1) / BM) * BM;
-      return 1.0 - (double)q.p.m / padded;
-    };
-    const bool rows_wasted = m_waste(row) >= 0.4 && m_waste(col) < 0.2;   // e.g. 64 output rows in 128-row tiles
-    if (g_store_mode == 2 || (es == 4 && (cc < 0.8 * cr || rows_wasted))) pl = &col;
+    if (g_store_mode == 2 || (es == 4 && cc < 0.5 * cr)) pl = &col;
   }
   if (p.dtype == B200_F32) return launch_es<4>(*pl, stream);
   return launch_es<2>(*pl, stream);
@@ -808,5 +856,6 @@ void tc_set_tile_n(int bn) { g_force_bn = bn; }
 void tc_set_mn_box5(int on) { g_mn_box5 = on; }
 void tc_set_pair_mode(int mode) { g_pair_mode = mode; }
 void tc_set_store_mode(int mode) { g_store_mode = mode; }
+void tc_set_split_mode(int mode) { g_split_mode = mode; }
 
 }  // namespace b200

@@ -213,6 +213,8 @@ struct TcArgs {
   int nb1;                        // inner batch count (tile id -> (b0, b1))
   int n_fast;                     // tile order inside a batch item: 1 = N tiles fastest, 0 = M tiles fastest
   long long total_tiles;
+  int ksplit, kb_per_slice;       // f32 kernel: K is cut into ksplit slices of kb_per_slice k-blocks; a work unit is
+  long long total_units;          // (tile, slice); slices of one tile add their partial results atomically
   int red, k_blocks;              // k iterations per tile = red * k_blocks
   int a_mn, b_mn;                 // operand is MN-major (else K-major)
   int a_ld, b_ld;                 // load_operand mode: 0 K-major, 1 MN-major per chunk, 2 MN-major one box
@@ -362,7 +364,36 @@ __device__ __forceinline__ void store_chunk_col(OutT* dst, const float* v, int v
     }
 }
 
+// Split-K: partial results of a K slice are added into C (which holds beta*C_old, or zeros) with vector
+// reductions; the order of the additions is not fixed, so the last bits can differ between runs.
+__device__ __forceinline__ void add_chunk_atomic(float* dst, const float* v, int valid) {
+  if (valid == 32) {
+#pragma unroll
+    for (int q = 0; q < 8; ++q)
+      asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};"
+                   ::"l"(dst + 4 * q), "f"(v[4 * q]), "f"(v[4 * q + 1]), "f"(v[4 * q + 2]), "f"(v[4 * q + 3]) : "memory");
+  } else {
+#pragma unroll
+    for (int q = 0; q < 32; ++q)
+      if (q < valid) atomicAdd(dst + q, v[q]);
+  }
+}
+__device__ __forceinline__ void add_chunk_atomic_col(float* dst, const float* v, int valid, long long ldc) {
+#pragma unroll
+  for (int q = 0; q < 32; ++q)
+    if (q < valid) atomicAdd(dst + q * ldc, v[q]);
+}
+
 struct TileCoord { int mt, nt, ib0, ib1; };
+struct Unit { long long tile; int kb_lo, kb_hi; };
+__device__ __forceinline__ Unit decode_unit(const TcArgs& g, long long unit, int total_kb) {
+  Unit u;
+  u.tile = unit / g.ksplit;
+  const int slice = (int)(unit - u.tile * g.ksplit);
+  u.kb_lo = slice * g.kb_per_slice;
+  u.kb_hi = u.kb_lo + g.kb_per_slice < total_kb ? u.kb_lo + g.kb_per_slice : total_kb;
+  return u;
+}
 __device__ __forceinline__ TileCoord decode_tile(const TcArgs& g, long long tile) {
   const long long per_batch = (long long)g.m_tiles * g.n_tiles;
   const long long bt = tile / per_batch;

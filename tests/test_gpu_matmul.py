@@ -146,6 +146,25 @@ def test_cta_pair_kernels(cuda_dev, oracle, dtype, layout):
         cuda_dev.set_path(dfdx_b200.PATH_AUTO)
 
 
+@pytest.mark.parametrize("slices", [2, 3, 7])
+@pytest.mark.parametrize("layout", ["rcr", "crr", "rrc", "ccc"])
+def test_split_k_f32(cuda_dev, oracle, layout, slices):
+    """f32 split-K: K slices of one tile are separate work units whose partial results are added atomically;
+    beta 0 (output zeroed first, NaN-poisoned here) and beta 1, ragged shapes, both store orientations."""
+    cuda_dev.set_path(dfdx_b200.PATH_TENSOR)
+    assert cuda_dev.lib.b200_set_split_k(slices) == 0
+    try:
+        for store in (1, 2):
+            cuda_dev.lib.b200_set_store_mode(store)
+            for i, (m, k, n) in enumerate([(128, 1024, 256), (200, 1160, 136), (264, 4096, 520)]):
+                check_gemm(cuda_dev, oracle, m, k, n, layout[0], layout[1], layout[2], i % 2, torch.float32, pad=8,
+                           seed=400 + i)
+    finally:
+        cuda_dev.lib.b200_set_split_k(0)
+        cuda_dev.lib.b200_set_store_mode(0)
+        cuda_dev.set_path(dfdx_b200.PATH_AUTO)
+
+
 @pytest.mark.parametrize("dtype", [torch.float16, torch.float32])
 def test_tensor_core_long_k_accuracy(cuda_dev, oracle, dtype):
     """The stated bound must hold where accumulation is longest: K = 16384."""
