@@ -256,6 +256,82 @@ def run_other_workload(args, dev, rank, world):
     }))
 
 
+def run_transformer(args, dev, rank, world):
+    """Configuration 5: data-parallel training step of a 6-layer encoder (d_model 512, 8 heads, ffn 2048),
+    batch 64 per GPU, sequence 256, MSE loss, Adam; all matmuls on this library (dfdx_b200/encoder.py)."""
+    import torch
+    import torch.distributed as dist
+    import dfdx_b200
+    from dfdx_b200.encoder import Trainer
+    device, lib = dev.device, dev.lib
+    BATCH, SEQ, MODEL = 64, 256, 512
+    trainer = Trainer(dev, world, layers=6, model=MODEL, heads=8, ff=2048, seed=0)      # same init on every rank
+    g = torch.Generator(device="cpu").manual_seed(0xD0FD + 5 + 1000 * rank)             # different data per rank
+    x_h = torch.randn(BATCH, SEQ, MODEL, generator=g).half().pin_memory()
+    t_h = torch.randn(BATCH, SEQ, MODEL, generator=g).half().pin_memory()
+    x, t = x_h.to(device), t_h.to(device)
+    stream = torch.cuda.current_stream(device)
+    l_before = lib.b200_launch_count()
+    captured = trainer.capture(x, t)                            # 3 eager warm-up steps + 1 recorded step
+    launches_per_step = (lib.b200_launch_count() - l_before) // 4 if captured else None
+
+    def timed(fn, steps, warmup):
+        for _ in range(warmup):
+            fn()
+        torch.cuda.synchronize(device)
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(device)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        l0, t0 = lib.b200_launch_count(), lib.b200_tensor_launch_count()
+        e0.record(stream)
+        for _ in range(steps):
+            fn()
+        e1.record(stream)
+        torch.cuda.synchronize(device)
+        if world > 1:
+            dist.barrier()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            tt = torch.tensor([ms], device=device)
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+            ms = float(tt.item())
+        return ms, lib.b200_launch_count() - l0, lib.b200_tensor_launch_count() - t0
+
+    losses = []
+
+    def step_e2e():
+        xd, td = x_h.to(device, non_blocking=True), t_h.to(device, non_blocking=True)
+        losses.append(float(trainer.step(xd, td)))          # the loss crosses back to the host every step
+
+    ms, launches, tc = timed(lambda: trainer.step(x, t), args.steps, max(args.warmup, 3))
+    dfdx_b200._lib.check(dev.device_status(), "device status after the timed region")
+    e2e_steps = max(3, min(args.steps, 10))
+    ms_e2e, _, _ = timed(step_e2e, e2e_steps, 3)
+    if rank != 0:
+        return
+    gemm_flop = 2.010e12                                     # matmul flops per step per GPU (forward + backward)
+    sps, sps_e2e = args.steps / (ms * 1e-3), e2e_steps / (ms_e2e * 1e-3)
+    n_params = sum(p.numel() for p in trainer.model.parameters())
+    print(json.dumps({
+        "metric": "transformer_train_tokens_per_s", "value": round(world * BATCH * SEQ * sps, 1), "unit": "token/s",
+        "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(ms / args.steps, 3),
+        "steps_per_s": round(sps, 3), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f16 compute, f32 accumulate, f32 master weights", "data": "synthetic",
+        "config": {"workload": "config[4]: encoder 6 x (d_model 512, 8 heads, ffn 2048), batch 64/GPU, seq 256, MSE, Adam",
+                   "parameters": n_params, "parallelism": f"dp{world}: NCCL all-reduce of one flat f32 gradient buffer",
+                   "matmuls": "all on libdfdx_b200 (MatMatBr + MatMatBatch4, forward and backward); LayerNorm, softmax, "
+                              "ReLU, bias, loss and Adam are torch ops (separate non-matmul kernels in dfdx too)"},
+        "gpu_launches": int(launches_per_step * args.steps) if captured else int(launches),
+        "tensor_core_launches": int(launches_per_step * args.steps) if captured else int(tc),
+        "cuda_graph": bool(captured), "cuda_graph_error": getattr(trainer, "capture_error", None),
+        "gemm_tflops_per_gpu": round(gemm_flop * sps / 1e12, 2),
+        "e2e": {"value": round(world * BATCH * SEQ * sps_e2e, 1), "unit": "token/s", "steps": e2e_steps,
+                "h2d_bytes_per_step": int(2 * x_h.numel() * 2), "d2h_bytes_per_step": 4,
+                "last_loss": losses[-1] if losses else None},
+    }))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -263,7 +339,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--workload", default="c2", choices=["c1", "c2", "c3", "c4"],
+    ap.add_argument("--workload", default="c2", choices=["c1", "c2", "c3", "c4", "c5"],
                     help="c2 (default) is the benchmark; c1 / c3 / c4 time the other configurations of the "
                          "path with the same harness (device-resident only; used for profiling)")
     args = ap.parse_args()
@@ -288,6 +364,11 @@ def main():
     device = dev.device
     lib = dev.lib
 
+    if args.workload == "c5":
+        run_transformer(args, dev, rank, world)
+        if world > 1:
+            dist.destroy_process_group()
+        return
     if args.workload != "c2":
         run_other_workload(args, dev, rank, world)
         if world > 1:

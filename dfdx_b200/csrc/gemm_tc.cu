@@ -9,16 +9,18 @@
 //                   (BK = 64).  The accumulator is double-buffered in TMEM so the epilogue of tile i
 //                   overlaps the main loop of tile i+1.
 //
-// gemm_tf32x3_kernel  f32 operands as 3xTF32 (kind::tf32).  16 warps in four warpgroups:
-//                   WG3 = TMA producer warp + MMA warp, WG2 = operand split, WG0/WG1 = epilogue.
+// gemm_tf32x3_kernel  f32 operands as 3xTF32 (kind::tf32).  20 warps in five warpgroups: WG0/WG1 =
+//                   epilogue, WG2 = TMA producer warp + MMA warp, WG3/WG4 = operand split.
 //                   Each staged f32 x stays in place as the `big` operand (the tensor core reads its top
-//                   19 bits) and small = tf32_rn(x - trunc_tf32(x)) is written beside it; every k-step
-//                   issues small*big, big*small, big*big (K = 8).  The tensor core adds into its f32
+//                   19 bits) and small = x - trunc_tf32(x) is written beside it; every k-step issues
+//                   small*big, big*small, big*big (K = 8).  The tensor core adds into its f32
 //                   accumulator with truncation, so the error of one long accumulation grows linearly
 //                   with K; therefore K is cut into chunks of 256: each chunk accumulates in one of two
 //                   TMEM buffers and the epilogue warpgroups add finished chunks into f32 registers
 //                   (round-to-nearest) while the next chunk runs.  setmaxnreg moves registers from the
-//                   producer / MMA / split warpgroups to the epilogue warpgroups.
+//                   producer / MMA / split warpgroups to the epilogue warpgroups.  Problems with few
+//                   output tiles are cut along K as well (split-K): a work unit is (tile, K slice) and
+//                   the slices add their partial results into C with vector atomics.
 //
 // Operands are read in place from dfdx's strides: K-major rows, or MN-major (the transposed views that
 // the backward GEMMs and `permute` produce).  MN-major tiles are brought in as column chunks:

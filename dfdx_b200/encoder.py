@@ -1,0 +1,178 @@
+"""Transformer-encoder training step whose matrix multiplications all run on this library.
+
+This is measurement harness for BASELINE configuration 5, not a re-implementation of dfdx's nn
+stack: the block structure restates dfdx's `EncoderBlock` (dfdx/src/nn/layers/transformer.rs:24-47:
+ResidualAdd(MultiHeadAttention) -> LayerNorm1D -> ResidualAdd(Linear, ReLU, Linear) -> LayerNorm1D)
+and `MultiHeadAttention::try_forward` (multi_head_attention.rs:105-146: three Linear layers, the
+(b,s,h,d) buffers viewed as (b,h,s,d) / (b,h,d,s) without a copy, q.matmul(k) * 1/sqrt(d), softmax,
+.matmul(v), permute back, output Linear).  Every `matmul` goes through `dfdx_b200.Cuda.matmul`
+(`MatMatBrKernel` for the Linear layers, `MatMatBatch4Kernel` for the attention products, forward and
+backward); bias, residual, LayerNorm, softmax, ReLU, the MSE loss and Adam are plain torch ops, as
+they are separate (non-matmul) kernels in dfdx too.
+
+Parameters are f32 master weights; each step computes in f16 (`AMP<f16>`-like: f16 storage, f32
+accumulation inside the GEMMs) and Adam updates the f32 masters.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.nn.functional as F
+
+from .cuda import Cuda
+
+
+class _MatMul(torch.autograd.Function):
+    """`TryMatMul` with its tape entry: forward through the kernel trait's forward, backward through its
+    backward (gradients come back viewed through the operands' own strides, as dfdx stores them)."""
+
+    @staticmethod
+    def forward(ctx, dev: Cuda, lhs: torch.Tensor, rhs: torch.Tensor):
+        if lhs.storage_offset() or not _dense(lhs):
+            lhs = lhs.contiguous()
+        if rhs.storage_offset() or not _dense(rhs):
+            rhs = rhs.contiguous()
+        out, bwd = dev.matmul(lhs, rhs)
+        ctx.bwd = bwd
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        gl, gr = ctx.bwd(grad_out)
+        return None, gl, gr
+
+
+def _dense(t: torch.Tensor) -> bool:
+    """True when t is a permutation of a contiguous buffer that starts at its storage's origin."""
+    return t.numel() * t.element_size() == t.untyped_storage().nbytes()
+
+
+def matmul(dev: Cuda, lhs: torch.Tensor, rhs: torch.Tensor) -> torch.Tensor:
+    return _MatMul.apply(dev, lhs, rhs)
+
+
+class Linear(torch.nn.Module):
+    """dfdx `Linear`: weight stored (O, I), consumed as the permuted (I, O) view; uniform(+-1/sqrt(I)) init
+    (dfdx/src/nn/layers/linear.rs:65-89)."""
+
+    def __init__(self, dev: Cuda, i: int, o: int, gen: torch.Generator):
+        super().__init__()
+        self.dev = dev
+        b = 1.0 / math.sqrt(i)
+        self.weight = torch.nn.Parameter(((torch.rand(o, i, generator=gen) * 2 - 1) * b).to(dev.device))
+        self.bias = torch.nn.Parameter(((torch.rand(o, generator=gen) * 2 - 1) * b).to(dev.device))
+
+    def forward(self, x):
+        w = self.weight.half()                                     # f16 compute copy of the f32 master
+        return matmul(self.dev, x, w.permute(1, 0)) + self.bias.half()
+
+
+class MultiHeadAttention(torch.nn.Module):
+    def __init__(self, dev: Cuda, model: int, heads: int, gen: torch.Generator):
+        super().__init__()
+        self.dev, self.heads = dev, heads
+        self.w_q, self.w_k = Linear(dev, model, model, gen), Linear(dev, model, model, gen)
+        self.w_v, self.w_o = Linear(dev, model, model, gen), Linear(dev, model, model, gen)
+
+    def forward(self, x):
+        b, s, m = x.shape
+        h, d = self.heads, m // self.heads
+        v = self.w_v(x).reshape(b, s, h, d).permute(0, 2, 1, 3)
+        k = self.w_k(x).reshape(b, s, h, d).permute(0, 2, 3, 1)
+        q = self.w_q(x).reshape(b, s, h, d).permute(0, 2, 1, 3)
+        weights = torch.softmax(matmul(self.dev, q, k) * (1.0 / math.sqrt(d)), dim=-1)
+        tokens = matmul(self.dev, weights, v).permute(0, 2, 1, 3).reshape(b, s, m)
+        return self.w_o(tokens)
+
+
+class EncoderBlock(torch.nn.Module):
+    def __init__(self, dev: Cuda, model: int, heads: int, ff: int, gen: torch.Generator):
+        super().__init__()
+        self.attn = MultiHeadAttention(dev, model, heads, gen)
+        self.norm1 = torch.nn.LayerNorm(model, device=dev.device)
+        self.l1, self.l2 = Linear(dev, model, ff, gen), Linear(dev, ff, model, gen)
+        self.norm2 = torch.nn.LayerNorm(model, device=dev.device)
+
+    def _norm(self, ln, x):
+        return F.layer_norm(x, ln.normalized_shape, ln.weight.half(), ln.bias.half(), ln.eps)
+
+    def forward(self, x):
+        x = self._norm(self.norm1, x + self.attn(x))
+        return self._norm(self.norm2, x + self.l2(torch.relu(self.l1(x))))
+
+
+class Encoder(torch.nn.Module):
+    """`layers` encoder blocks (BASELINE configuration 5: 6 x (d_model 512, 8 heads, ffn 2048))."""
+
+    def __init__(self, dev: Cuda, layers=6, model=512, heads=8, ff=2048, seed=0):
+        super().__init__()
+        gen = torch.Generator().manual_seed(seed)
+        self.blocks = torch.nn.ModuleList(EncoderBlock(dev, model, heads, ff, gen) for _ in range(layers))
+
+    def forward(self, x):
+        for blk in self.blocks:
+            x = blk(x)
+        return x
+
+
+class Trainer:
+    """One data-parallel training step: forward, MSE loss, backward, gradient all-reduce, Adam.
+
+    The eager step is bound by host-side launch overhead (about 300 small launches), so `capture()` records
+    the whole step once into a CUDA graph and `step()` then replays it on static input buffers."""
+
+    def __init__(self, dev: Cuda, world: int = 1, **model_kw):
+        self.dev, self.world = dev, world
+        self.model = Encoder(dev, **model_kw)
+        params = list(self.model.parameters())
+        # one flat f32 gradient buffer: a single NCCL all-reduce per step
+        self.flat_grad = torch.zeros(sum(p.numel() for p in params), device=dev.device)
+        off = 0
+        for p in params:
+            p.grad = self.flat_grad[off:off + p.numel()].view_as(p)
+            off += p.numel()
+        self.opt = torch.optim.Adam(params, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, fused=True, capturable=True)
+        self.graph = None
+
+    def _step(self, x: torch.Tensor, target: torch.Tensor) -> torch.Tensor:
+        self.flat_grad.zero_()
+        loss = F.mse_loss(self.model(x).float(), target.float())
+        loss.backward()
+        if self.world > 1:
+            import torch.distributed as dist
+            dist.all_reduce(self.flat_grad)
+            self.flat_grad.div_(self.world)
+        self.opt.step()
+        return loss
+
+    def capture(self, x: torch.Tensor, target: torch.Tensor) -> bool:
+        """Records the step into a CUDA graph (after three eager steps on a side stream).  Returns False and
+        stays eager if the capture fails."""
+        self._x, self._t = x.clone(), target.clone()
+        try:
+            side = torch.cuda.Stream(self.dev.device)
+            side.wait_stream(torch.cuda.current_stream(self.dev.device))
+            with torch.cuda.stream(side):
+                for _ in range(3):
+                    self._step(self._x, self._t)
+            torch.cuda.current_stream(self.dev.device).wait_stream(side)
+            torch.cuda.synchronize(self.dev.device)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                self._loss = self._step(self._x, self._t)
+            self.graph = graph
+            return True
+        except Exception as exc:  # noqa: BLE001 - any capture failure means: stay eager
+            self.capture_error = repr(exc)
+            self.graph = None
+            torch.cuda.synchronize(self.dev.device)
+            return False
+
+    def step(self, x: torch.Tensor, target: torch.Tensor) -> torch.Tensor:
+        if self.graph is None:
+            return self._step(x, target)
+        self._x.copy_(x, non_blocking=True)
+        self._t.copy_(target, non_blocking=True)
+        self.graph.replay()
+        return self._loss

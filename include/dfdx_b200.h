@@ -81,9 +81,11 @@ const char* b200_last_cuda_error(void);
 int b200_device_status(void* stream);
 /* Process-wide override of kernel-family selection (testing / profiling). */
 int b200_set_path(int path);
-/* f32 tensor-core operand split (testing / profiling): 0 (default) rewrites each staged f32 x as
- * big = tf32_rn(x) and small = tf32_rn(x - big); 1 leaves x in place (the tensor core truncates it
- * to tf32) and only writes small = tf32_rn(x - trunc(x)). */
+/* f32 tensor-core operand split (testing / profiling).  Every staged f32 x is used in place as the `big`
+ * tf32 operand (the tensor core reads its top 19 bits) and small = x - trunc_tf32(x) is written beside it.
+ * Bit 0: 1 (default) stores small as computed, 0 rounds it to tf32 first (cvt.rna).  Bits 1..3 are timing
+ * experiments that give WRONG results: skip the split work (2), issue a third of the MMAs (4), skip the TMA
+ * loads (8). */
 int b200_set_tf32_split_mode(int mode);
 /* Tensor-core tile width override (testing / profiling): 64, 128 or 256 output columns per CTA tile;
  * 0 (default) picks the widest tile that still gives every SM work. */

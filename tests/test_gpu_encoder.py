@@ -1,0 +1,61 @@
+"""The encoder harness of configuration 5: its matmuls (forward and backward, through the C ABI) against
+torch's own f32 autograd on the same f16-rounded parameters and inputs."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def test_encoder_block_matches_torch_autograd(cuda_dev):
+    from dfdx_b200 import encoder as enc
+    dev = cuda_dev
+    gen = torch.Generator().manual_seed(1)
+    blk = enc.EncoderBlock(dev, 128, 4, 256, gen)
+    x = torch.randn(3, 40, 128, generator=gen).half().to(dev.device).requires_grad_(True)
+    t = torch.randn(3, 40, 128, generator=gen).to(dev.device)
+    before = dev.lib.b200_launch_count()
+    loss = torch.nn.functional.mse_loss(blk(x).float(), t)
+    loss.backward()
+    assert dev.lib.b200_launch_count() - before >= 3 * 8      # 6 Linear + 2 attention matmuls, forward + 2 grads
+    got = {n: p.grad.clone() for n, p in blk.named_parameters()}
+    gx = x.grad.float().clone()
+
+    # reference: same math with torch.matmul in f32 on the f16-rounded values
+    real = enc.matmul
+    enc.matmul = lambda d, a, b: torch.matmul(a.float(), b.float()).half()
+    try:
+        for p in blk.parameters():
+            p.grad = None
+        x2 = x.detach().clone().requires_grad_(True)
+        loss2 = torch.nn.functional.mse_loss(blk(x2).float(), t)
+        loss2.backward()
+    finally:
+        enc.matmul = real
+    assert abs(loss.item() - loss2.item()) <= 2e-3 * abs(loss2.item())
+    biggest = max(float(p.grad.norm()) for p in blk.parameters())
+    for n, p in blk.named_parameters():
+        ref = p.grad
+        # gradients that are mathematically zero (the key bias: softmax is shift-invariant) are pure rounding
+        # noise, so the error is measured against the larger of the reference norm and 1e-2 of the largest one
+        err = (got[n] - ref).norm() / max(float(ref.norm()), 1e-2 * biggest)
+        assert err <= 2e-2, f"{n}: relative error {float(err):.3e}"
+    err = (gx - x2.grad.float()).norm() / x2.grad.float().norm()
+    assert err <= 2e-2
+
+
+def test_trainer_graph_replay_matches_eager(cuda_dev):
+    """A captured step replays to the same loss trajectory as eager steps from the same initial state."""
+    from dfdx_b200.encoder import Trainer
+    gen = torch.Generator().manual_seed(2)
+    x = torch.randn(4, 32, 64, generator=gen).half().to(cuda_dev.device)
+    t = torch.randn(4, 32, 64, generator=gen).half().to(cuda_dev.device)
+    kw = dict(layers=2, model=64, heads=4, ff=128, seed=3)
+    eager = Trainer(cuda_dev, 1, **kw)
+    want = [eager.step(x, t).item() for _ in range(7)]
+    graphed = Trainer(cuda_dev, 1, **kw)
+    assert graphed.capture(x, t), getattr(graphed, "capture_error", "")
+    got = [graphed.step(x, t).item() for _ in range(4)]            # capture ran 3 warm-up steps + 1 recorded step
+    assert want[6] < want[0]                                        # it trains
+    for g_, w_ in zip(got, want[4:7] + [None]):
+        if w_ is not None:
+            assert abs(g_ - w_) <= 2e-2 * abs(w_)
