@@ -108,6 +108,9 @@ int b200_init(int ordinal) {
   d.sm_count = prop.multiProcessorCount;
   if ((rc = note_cuda_error(cudaMalloc(&d.status, sizeof(int)), "cudaMalloc(status)"))) return rc;
   if ((rc = note_cuda_error(cudaMemset(d.status, 0, sizeof(int)), "cudaMemset(status)"))) return rc;
+  if ((rc = note_cuda_error(cudaMalloc(&d.split_scratch, SPLIT_SCRATCH_BYTES), "cudaMalloc(split-K scratch)"))) return rc;
+  d.split_scratch_bytes = SPLIT_SCRATCH_BYTES;
+  if ((rc = note_cuda_error(cudaEventCreateWithFlags(&d.split_event, cudaEventDisableTiming), "cudaEventCreate"))) return rc;
   if ((rc = tc_setup_device())) return rc;
   d.ready = true;
   return B200_OK;

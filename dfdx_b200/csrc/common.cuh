@@ -41,7 +41,15 @@ struct DeviceState {
   bool ready = false;
   int sm_count = 0;
   int* status = nullptr;  // device word: 0 or a B200_ERR_* written by a kernel that gave up on a wait
+  // f32 scratch for split-K partial sums of f16 GEMMs (fixed size, allocated by b200_init).  Uses on
+  // different streams are ordered through `split_event`.
+  float* split_scratch = nullptr;
+  size_t split_scratch_bytes = 0;
+  cudaEvent_t split_event = nullptr;
+  cudaStream_t split_last_stream = nullptr;
+  bool split_used = false;
 };
+constexpr size_t SPLIT_SCRATCH_BYTES = 64u << 20;
 
 DeviceState* device_state();                 // state of the current device (nullptr before init)
 int note_cuda_error(cudaError_t e, const char* where);

@@ -288,8 +288,8 @@ int backward_t(int dtype, const Op& op, const T* img, T* grad_img, const T* filt
   const bool filters_contig = (int64_t)fs[3] == 1 && (int64_t)fs[2] == op.kernel && (int64_t)fs[1] == KK &&
                               (int64_t)fs[0] == cg * KK;
   bool grad_filters_done = false;
-  // (f32 only: that kernel can cut the long reduction into K slices; the f16 kernel cannot yet.)
-  if (grad_filters && filters_contig && n_fwd_patches > 0 && dtype == B200_F32) {
+  // (tensor-core dtypes only: their kernels cut the long reduction into K slices.)
+  if (grad_filters && filters_contig && n_fwd_patches > 0 && dtype != B200_F64) {
     const int64_t npos = op.h_out * op.w_out;
     Strides4 ist{{op.chan_in * hw, hw, op.w_in, 1}};
     if (plane_path_input<T>(op))

@@ -100,9 +100,10 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
-      for (long long tile = blockIdx.x; ok && tile < g.total_tiles; tile += gridDim.x) {
-        const TileCoord t = decode_tile(g, tile);
-        for (int i = 0; i < total_kb; ++i, ++it) {
+      for (long long unit = blockIdx.x; ok && unit < g.total_units; unit += gridDim.x) {
+        const Unit un = decode_unit(g, unit, total_kb);
+        const TileCoord t = decode_tile(g, un.tile);
+        for (int i = un.kb_lo; i < un.kb_hi; ++i, ++it) {
           const int r = i / g.k_blocks, kb = i - r * g.k_blocks;
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1u;
@@ -129,12 +130,13 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
       const uint32_t a_kadv = g.a_mn ? C::MN_KADV : C::K_KADV, b_kadv = g.b_mn ? C::MN_KADV : C::K_KADV;
       uint32_t it = 0, tcount = 0;
       bool ok = true;
-      for (long long tile = blockIdx.x; ok && tile < g.total_tiles; tile += gridDim.x, ++tcount) {
+      for (long long unit = blockIdx.x; ok && unit < g.total_units; unit += gridDim.x, ++tcount) {
+        const Unit un = decode_unit(g, unit, total_kb);
         const uint32_t buf = tcount & 1u, tph = (tcount >> 1) & 1u;
         if (!mbar_wait(smem_u32(&bar_tempty[buf]), tph ^ 1u, abortp, g.wait_limit)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + buf * BN;
-        for (int i = 0; i < total_kb; ++i, ++it) {
+        for (int i = un.kb_lo; i < un.kb_hi; ++i, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1u;
           if (!mbar_wait(smem_u32(&bar_full[s]), ph, abortp, g.wait_limit)) { ok = false; break; }
@@ -146,7 +148,7 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
             const uint64_t ad = make_smem_desc(a_base + ks * a_kadv, a_lbo, C::SBO, C::LAYOUT);
             const uint64_t bd = make_smem_desc(b_base + ks * b_kadv, b_lbo, C::SBO, C::LAYOUT);
             if ((g.xform_mode & 4) && ks > 0) continue;               // timing experiment: 1 MMA of 4
-            umma<2>(d_tmem, ad, bd, idesc, (i > 0 || ks > 0) ? 1u : 0u);
+            umma<2>(d_tmem, ad, bd, idesc, (i > un.kb_lo || ks > 0) ? 1u : 0u);
           }
           umma_commit(smem_u32(&bar_empty[s]));       // stage reusable once these MMAs retire
         }
@@ -158,15 +160,16 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
     // ------------------------------------------------------------------ epilogue (warps 0..3)
     uint32_t tcount = 0;
     bool ok = true;
-    for (long long tile = blockIdx.x; ok && tile < g.total_tiles; tile += gridDim.x, ++tcount) {
-      const TileCoord t = decode_tile(g, tile);
+    for (long long unit = blockIdx.x; ok && unit < g.total_units; unit += gridDim.x, ++tcount) {
+      const Unit un = decode_unit(g, unit, total_kb);
+      const TileCoord t = decode_tile(g, un.tile);
       const uint32_t buf = tcount & 1u, tph = (tcount >> 1) & 1u;
       const int row = t.mt * BM + warp * 32 + lane;
       __half* cbase = (__half*)g.c + t.ib0 * g.c_b0 + t.ib1 * g.c_b1;
       // beta = 1 with row stores: the values the row already holds do not depend on the accumulator, so
       // they are fetched before waiting for it, four 32-column chunks ahead of their use.
       constexpr int NCH = BN / 32, AHEAD = NCH < 4 ? NCH : 4;
-      const bool rmw = g.beta && !g.c_col && row < g.m;
+      const bool rmw = g.beta && !g.c_col && row < g.m && g.ksplit == 1;
       const __half* orow = cbase + (long long)row * g.ldc + t.nt * BN;
       uint32_t oldv[AHEAD][16];
       if (rmw) {
@@ -189,7 +192,9 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
             float f[32];
 #pragma unroll
             for (int q = 0; q < 32; ++q) f[q] = __uint_as_float(v[q]);
-            if (g.c_col) {
+            if (g.ksplit > 1) {                      // K slice: partial sums go to the f32 scratch
+              add_chunk_atomic(g.split_out + (long long)row * g.split_ld + col0, f, valid);
+            } else if (g.c_col) {
               store_chunk_col(cbase + (long long)col0 * g.ldc + row, f, valid, g.ldc, g.beta);
             } else if (rmw && valid == 32) {
               add_old_f16(f, oldv[c % AHEAD]);
@@ -457,6 +462,24 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_const
   }
 }
 
+// Split-K of an f16 GEMM: C = f16(beta * C + S) for the m x n f32 partial-sum matrix S (row-major, ld = lds).
+// C element (i, j) sits at i*c_r + j*c_c.
+__global__ void __launch_bounds__(256) splitk_finalize_f16_kernel(const float* __restrict__ S, long long lds,
+                                                                  __half* C, long long c_r, long long c_c, int m, int n,
+                                                                  int beta) {
+  const long long total = (long long)m * n;
+  for (long long idx = (long long)blockIdx.x * 256 + threadIdx.x; idx < total; idx += (long long)gridDim.x * 256) {
+    // walk C's unit-stride dimension fastest
+    int i, j;
+    if (c_c == 1) { i = (int)(idx / n); j = (int)(idx - (long long)i * n); }
+    else { j = (int)(idx / m); i = (int)(idx - (long long)j * m); }
+    float v = S[(long long)i * lds + j];
+    __half* dst = C + (long long)i * c_r + (long long)j * c_c;
+    if (beta) v += __half2float(*dst);
+    *dst = __float2half_rn(v);
+  }
+}
+
 // ---------------------------------------------------------------------------------------------
 // Host side: operand classification, tensor maps, launch
 // ---------------------------------------------------------------------------------------------
@@ -624,6 +647,7 @@ int encode_map(CUtensorMap* map, const void* base, size_t esize, int64_t inner, 
 int g_xform_mode = 1;
 int g_force_bn = 0;   // 0 = choose by problem shape
 int g_mn_box5 = 1;    // MN-major operands: one 5-D TMA box per stage where the extent allows
+std::mutex g_split_mutex;
 int g_split_mode = 0; // split-K of the f32 kernel: 0 = choose, 1 = never, n >= 2 = force n slices (testing)
 int g_store_mode = 0; // 0 = choose, 1 = row stores only, 2 = column stores where possible
 int g_pair_mode = 1;  // 0 = choose by problem shape, 1 = never use CTA pairs (default: not faster yet), 2 = always (n > 128)
@@ -712,16 +736,55 @@ int launch_cfg(const Plan& pl, cudaStream_t stream, Kernel kernel, int ksplit) {
   TcArgs& g = L.g;
   const int total_kb = g.red * g.k_blocks;
   g.kb_per_slice = total_kb;
-  if (ESIZE == 4 && ksplit > 1 && total_kb >= 2 * ksplit) {
-    g.kb_per_slice = (total_kb + ksplit - 1) / ksplit;
-    g.ksplit = (total_kb + g.kb_per_slice - 1) / g.kb_per_slice;
-    g.total_units = g.total_tiles * g.ksplit;
-    if (g.ksplit > 1 && !g.beta) {
-      const GemmProblem& p = pl.p;   // single batch item (checked by the caller)
-      const size_t width = (size_t)(pl.c_col ? p.m : p.n) * 4, height = (size_t)(pl.c_col ? p.n : p.m);
-      const int rc = note_cuda_error(cudaMemset2DAsync(p.c, (size_t)pl.ldc * 4, 0, width, height, stream),
-                                     "cudaMemset2DAsync(split-K output)");
-      if (rc) return rc;
+  g.split_out = nullptr; g.split_ld = 0;
+  if (ksplit > 1 && total_kb >= 2 * ksplit) {
+    const GemmProblem& p = pl.p;   // single batch item (checked by the caller)
+    const int kb_per = (total_kb + ksplit - 1) / ksplit, slices = (total_kb + kb_per - 1) / kb_per;
+    if (ESIZE == 4 && slices > 1) {
+      g.kb_per_slice = kb_per; g.ksplit = slices; g.total_units = g.total_tiles * slices;
+      if (!g.beta) {
+        const size_t width = (size_t)(pl.c_col ? p.m : p.n) * 4, height = (size_t)(pl.c_col ? p.n : p.m);
+        const int rc = note_cuda_error(cudaMemset2DAsync(p.c, (size_t)pl.ldc * 4, 0, width, height, stream),
+                                       "cudaMemset2DAsync(split-K output)");
+        if (rc) return rc;
+      }
+    } else if (ESIZE == 2 && slices > 1) {
+      // f16: partial sums are accumulated in the device's f32 scratch, then folded into C by a second kernel
+      const long long lds = (p.n + 3) / 4 * 4;
+      const size_t need = (size_t)p.m * (size_t)lds * sizeof(float);
+      if (need <= ds->split_scratch_bytes) {
+        std::lock_guard<std::mutex> lock(g_split_mutex);
+        int rc;
+        // Order this use after the previous one when that ran on another stream.  A capturing stream neither
+        // waits on nor records the shared event (the replayed graph is ordered by its launch stream).
+        cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+        cudaStreamIsCapturing(stream, &cap);
+        const bool capturing = cap != cudaStreamCaptureStatusNone;
+        if (!capturing && ds->split_used && ds->split_last_stream != stream &&
+            (rc = note_cuda_error(cudaStreamWaitEvent(stream, ds->split_event, 0), "cudaStreamWaitEvent(split-K)")))
+          return rc;
+        if ((rc = note_cuda_error(cudaMemsetAsync(ds->split_scratch, 0, need, stream), "cudaMemsetAsync(split-K)"))) return rc;
+        g.kb_per_slice = kb_per; g.ksplit = slices; g.total_units = g.total_tiles * slices;
+        g.split_out = ds->split_scratch; g.split_ld = lds;
+        const long long grid2 = g.total_units < ds->sm_count ? g.total_units : ds->sm_count;
+        kernel<<<(unsigned)grid2, C::THREADS, C::SMEM_BYTES, stream>>>(L.ma, L.mb, L.g);
+        count_launch(true);
+        if ((rc = note_cuda_error(cudaGetLastError(), "tensor-core gemm launch"))) return rc;
+        const long long total = (long long)p.m * p.n;
+        long long blocks = (total + 255) / 256;
+        if (blocks > (long long)ds->sm_count * 8) blocks = (long long)ds->sm_count * 8;
+        const long long c_r = pl.c_col ? 1 : pl.ldc, c_c = pl.c_col ? pl.ldc : 1;
+        splitk_finalize_f16_kernel<<<(unsigned)blocks, 256, 0, stream>>>(ds->split_scratch, lds, (__half*)p.c, c_r, c_c,
+                                                                         (int)p.m, (int)p.n, g.beta);
+        count_launch(false);
+        if ((rc = note_cuda_error(cudaGetLastError(), "split-K finalize launch"))) return rc;
+        if (!capturing) {
+          ds->split_used = true;
+          ds->split_last_stream = stream;
+          rc = note_cuda_error(cudaEventRecord(ds->split_event, stream), "cudaEventRecord(split-K)");
+        }
+        return rc;
+      }
     }
   }
   const long long grid = g.total_units < ds->sm_count ? g.total_units : ds->sm_count;
@@ -742,7 +805,7 @@ int launch_pair_plan(const Plan& pl, int esize, cudaStream_t stream) {
 
 template <int ESIZE, int BN>
 int launch_bn(const Plan& pl, cudaStream_t stream, int ksplit) {
-  if constexpr (ESIZE == 2) return launch_cfg<CfgH<BN>, 2, BN>(pl, stream, gemm_f16_kernel<BN>, 1);
+  if constexpr (ESIZE == 2) return launch_cfg<CfgH<BN>, 2, BN>(pl, stream, gemm_f16_kernel<BN>, ksplit);
   else return launch_cfg<CfgS<BN>, 4, BN>(pl, stream, gemm_tf32x3_kernel<BN>, ksplit);
 }
 
@@ -782,11 +845,13 @@ int launch_es(const Plan& pl, cudaStream_t stream) {
   // Split-K (f32, one batch item): when the tiles alone leave most SMs idle, K slices become extra work
   // units.  Model: time = waves * (k-blocks per unit * t_kb(tile width) + t_fixed), in microseconds.
   int ksplit = 1;
-  if (ESIZE == 4 && g_split_mode != 1 && p.b0 == 1 && p.b1 == 1) {
-    const int64_t total_kb = p.red * ((p.k + 15) / 16);
+  if (g_split_mode != 1 && p.b0 == 1 && p.b1 == 1) {
+    const int bk = (ESIZE == 4) ? 16 : 64;
+    const int64_t total_kb = p.red * ((p.k + bk - 1) / bk);
     auto model = [&](int bn_, int s_) {
       const int64_t tiles = ((p.m + BM - 1) / BM) * ((p.n + bn_ - 1) / bn_);
-      const double t_kb = bn_ == 256 ? 0.65 : (bn_ == 128 ? 0.48 : 0.36);
+      const double t_kb = (ESIZE == 4) ? (bn_ == 256 ? 0.65 : (bn_ == 128 ? 0.48 : 0.36))
+                                       : (bn_ == 256 ? 0.52 : (bn_ == 128 ? 0.42 : 0.36));
       const double waves = (double)((tiles * s_ + sms - 1) / sms);
       return waves * ((double)((total_kb + s_ - 1) / s_) * t_kb + 4.0 + (s_ > 1 ? 2.0 : 0.0));
     };
@@ -796,7 +861,7 @@ int launch_es(const Plan& pl, cudaStream_t stream) {
       const int bn_ = widths[wi];
       if ((bn_ == 256 && p.n <= 128) || (bn_ == 128 && p.n <= 64) || (g_force_bn && bn_ != g_force_bn)) continue;
       for (int s_ = 2; s_ <= 64; ++s_) {
-        if (total_kb / s_ < 16) break;                      // at least one promotion chunk per slice
+        if (total_kb / s_ < (ESIZE == 4 ? 16 : 8)) break;    // keep slices long enough to amortise their fixed cost
         const double t = model(bn_, s_);
         if (t < 0.85 * best_t) { best_t = t; bn = bn_; ksplit = s_; }
       }

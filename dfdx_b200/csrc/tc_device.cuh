@@ -215,6 +215,8 @@ struct TcArgs {
   long long total_tiles;
   int ksplit, kb_per_slice;       // f32 kernel: K is cut into ksplit slices of kb_per_slice k-blocks; a work unit is
   long long total_units;          // (tile, slice); slices of one tile add their partial results atomically
+  float* split_out;               // f16 kernel with ksplit > 1: f32 scratch (m x split_ld, zeroed) that takes the
+  long long split_ld;             // partial sums; a finalize kernel then writes C = f16(beta*C + scratch)
   int red, k_blocks;              // k iterations per tile = red * k_blocks
   int a_mn, b_mn;                 // operand is MN-major (else K-major)
   int a_ld, b_ld;                 // load_operand mode: 0 K-major, 1 MN-major per chunk, 2 MN-major one box

@@ -146,6 +146,25 @@ def test_cta_pair_kernels(cuda_dev, oracle, dtype, layout):
         cuda_dev.set_path(dfdx_b200.PATH_AUTO)
 
 
+@pytest.mark.parametrize("slices", [2, 5])
+@pytest.mark.parametrize("layout", ["rcr", "crr", "rrc", "ccc"])
+def test_split_k_f16(cuda_dev, oracle, layout, slices):
+    """f16 split-K: K slices accumulate f32 partial sums in the library's scratch, a finalize kernel folds them
+    into the f16 output (beta 0 with NaN-poisoned output, beta 1), both store orientations, ragged shapes."""
+    cuda_dev.set_path(dfdx_b200.PATH_TENSOR)
+    assert cuda_dev.lib.b200_set_split_k(slices) == 0
+    try:
+        for store in (1, 2):
+            cuda_dev.lib.b200_set_store_mode(store)
+            for i, (m, k, n) in enumerate([(128, 2048, 256), (200, 2312, 136), (264, 4104, 264)]):
+                check_gemm(cuda_dev, oracle, m, k, n, layout[0], layout[1], layout[2], i % 2, torch.float16, pad=8,
+                           seed=500 + i)
+    finally:
+        cuda_dev.lib.b200_set_split_k(0)
+        cuda_dev.lib.b200_set_store_mode(0)
+        cuda_dev.set_path(dfdx_b200.PATH_AUTO)
+
+
 @pytest.mark.parametrize("slices", [2, 3, 7])
 @pytest.mark.parametrize("layout", ["rcr", "crr", "rrc", "ccc"])
 def test_split_k_f32(cuda_dev, oracle, layout, slices):
@@ -156,7 +175,7 @@ def test_split_k_f32(cuda_dev, oracle, layout, slices):
     try:
         for store in (1, 2):
             cuda_dev.lib.b200_set_store_mode(store)
-            for i, (m, k, n) in enumerate([(128, 1024, 256), (200, 1160, 136), (264, 4096, 520)]):
+            for i, (m, k, n) in enumerate([(128, 1024, 256), (200, 1160, 136), (264, 2056, 264)]):
                 check_gemm(cuda_dev, oracle, m, k, n, layout[0], layout[1], layout[2], i % 2, torch.float32, pad=8,
                            seed=400 + i)
     finally:
