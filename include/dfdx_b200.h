@@ -70,7 +70,9 @@ typedef enum {
 /* Replaces `Cuda::try_build(ordinal, seed)`'s cuBLAS-handle creation
  * (dfdx-core/src/tensor/cuda/device.rs:72-91): selects the device, resolves the driver entry
  * point used to encode TMA descriptors, raises the kernels' dynamic shared-memory limits and
- * allocates the per-device status word.  Idempotent; thread-safe. */
+ * allocates the per-device status word, a 64 MiB f32 scratch for the split-K partial sums of f16
+ * GEMMs and the event that orders its uses across streams.  These are the library's only device
+ * allocations.  Idempotent; thread-safe. */
 int b200_init(int ordinal);
 
 const char* b200_strerror(int status);
