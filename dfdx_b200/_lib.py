@@ -19,6 +19,15 @@ ERR_SHAPE, ERR_STRIDE, ERR_DTYPE, ERR_NULL, ERR_WORKSPACE = -1, -2, -3, -4, -5
 ERR_CUDA, ERR_DEVICE_TIMEOUT, ERR_UNSUPPORTED, ERR_NOT_CONTIGUOUS, ERR_LIMIT = -6, -7, -8, -9, -10
 
 
+# b200_activation
+ACT_NONE, ACT_RELU = 0, 1
+
+
+class Epilogue(C.Structure):
+    """`b200_epilogue`: out = activation(alpha * sum + bias[j])."""
+    _fields_ = [("alpha", C.c_double), ("bias", C.c_void_p), ("activation", C.c_int)]
+
+
 class Conv2DOp(C.Structure):
     """Bit-identical to dfdx's `Conv2DOp` (dfdx-core/src/tensor_ops/conv2d/mod.rs:14-29)."""
     _fields_ = [(n, C.c_size_t) for n in (
@@ -54,6 +63,9 @@ SIGNATURES = {
     "b200_matmat_batch3_backward": (_i, [_i, _sz, _sz, _sz, _sz, _vp, _szp, _vp, _vp, _szp, _vp, _vp, _vp, _vp]),
     "b200_matmat_batch4_forward": (_i, [_i, _sz, _sz, _sz, _sz, _sz, _vp, _szp, _vp, _szp, _vp, _vp]),
     "b200_matmat_batch4_backward": (_i, [_i, _sz, _sz, _sz, _sz, _sz, _vp, _szp, _vp, _vp, _szp, _vp, _vp, _vp, _vp]),
+    "b200_gemm_batch_fused": (_i, [_i, _sz, _sz, _sz, _sz, _sz, _vp, _szp, _vp, _szp, C.POINTER(Epilogue), _vp, _szp, _vp]),
+    "b200_linear_forward": (_i, [_i, _sz, _sz, _sz, _sz, _vp, _szp, _vp, _szp, _vp, _i, _vp, _vp]),
+    "b200_matmat_batch4_forward_scaled": (_i, [_i, _sz, _sz, _sz, _sz, _sz, _vp, _szp, _vp, _szp, _d, _vp, _vp]),
     "b200_conv2d_workspace_bytes": (_sz, [_i, C.POINTER(Conv2DOp), _i]),
     "b200_conv2d_forward": (_i, [_i, C.POINTER(Conv2DOp), _vp, _szp, _vp, _vp, _vp, _sz, _vp]),
     "b200_conv2d_backward": (_i, [_i, C.POINTER(Conv2DOp), _vp, _vp, _vp, _szp, _vp, _vp, _vp, _sz, _vp, _vp]),

@@ -60,6 +60,7 @@ void count_launch(bool tensor) {
 // stride, (B, M, K) x (K, N) is one (B*M, K) x (K, N) GEMM (no partial M tiles per batch item).
 static void fold_batch(GemmProblem& p) {
   if (p.red != 1) return;
+  if (p.bias && p.bias_dim == 1) return;   // a per-row bias repeats per batch item
   if (p.b1 > 1 && p.b_b1 == 0 && p.a_b1 == p.m * p.a_r && p.c_b1 == p.m * p.c_r && p.a_r != 0 && p.c_r != 0 &&
       (p.b0 == 1)) {
     p.m *= p.b1; p.b1 = 1; p.a_b1 = p.c_b1 = 0;
@@ -112,6 +113,7 @@ int b200_init(int ordinal) {
   d.split_scratch_bytes = SPLIT_SCRATCH_BYTES;
   if ((rc = note_cuda_error(cudaEventCreateWithFlags(&d.split_event, cudaEventDisableTiming), "cudaEventCreate"))) return rc;
   if ((rc = tc_setup_device())) return rc;
+  if ((rc = attention_setup_device())) return rc;
   d.ready = true;
   return B200_OK;
 }
@@ -323,17 +325,63 @@ int b200_matmat_batch3_backward(int dtype, size_t batch, size_t m, size_t k, siz
 // ---- MatMatBatch4Kernel (cuda_kernel.rs:469-568) -------------------------------------------------
 static int gemm_batch2(int dtype, size_t b0, size_t b1, size_t m, size_t k, size_t n, const void* lhs,
                        const size_t ls[4], const void* rhs, const size_t rs[4], int beta, void* out,
-                       const size_t os[4], void* stream) {
+                       const size_t os[4], void* stream, const b200_epilogue* ep = nullptr) {
   if (!valid_dtype(dtype)) return B200_ERR_DTYPE;
+  if (ep && (ep->activation != B200_ACT_NONE && ep->activation != B200_ACT_RELU)) return B200_ERR_UNSUPPORTED;
+  if (ep && beta) return B200_ERR_UNSUPPORTED;
   if (b0 && b1 && m && n && (!out || (k && (!lhs || !rhs)))) return B200_ERR_NULL;
   if (!matrix_strides_ok(ls + 2) || !matrix_strides_ok(rs + 2) || !matrix_strides_ok(os + 2)) return B200_ERR_STRIDE;
-  if (os[0] == 0 || os[1] == 0) return B200_ERR_STRIDE;
+  if ((b0 > 1 && os[0] == 0) || (b1 > 1 && os[1] == 0)) return B200_ERR_STRIDE;
   GemmProblem p;
   p.dtype = dtype; p.beta = beta; p.b0 = b0; p.b1 = b1; p.m = m; p.k = k; p.n = n;
   p.a = lhs; p.a_b0 = ls[0]; p.a_b1 = ls[1]; p.a_r = ls[2]; p.a_c = ls[3];
   p.b = rhs; p.b_b0 = rs[0]; p.b_b1 = rs[1]; p.b_r = rs[2]; p.b_c = rs[3];
   p.c = out; p.c_b0 = os[0]; p.c_b1 = os[1]; p.c_r = os[2]; p.c_c = os[3];
+  if (ep) { p.alpha = ep->alpha; p.bias = ep->bias; p.bias_dim = 0; p.act = ep->activation; }
   return run_gemm(p, (cudaStream_t)stream);
+}
+
+// ---- fused epilogues ------------------------------------------------------------------------------
+int b200_gemm_batch_fused(int dtype, size_t batch0, size_t batch1, size_t m, size_t k, size_t n, const void* lhs,
+                          const size_t ls[4], const void* rhs, const size_t rs[4], const b200_epilogue* ep,
+                          void* out, const size_t os[4], void* stream) {
+  if (!ls || !rs || !os) return B200_ERR_NULL;
+  return gemm_batch2(dtype, batch0, batch1, m, k, n, lhs, ls, rhs, rs, 0, out, os, stream, ep);
+}
+
+int b200_linear_forward(int dtype, size_t batch, size_t m, size_t i, size_t o, const void* x, const size_t xs[3],
+                        const void* weight, const size_t ws[2], const void* bias, int activation, void* out,
+                        void* stream) {
+  if (!xs || !ws) return B200_ERR_NULL;
+  const size_t ls[4] = {0, xs[0], xs[1], xs[2]};
+  const size_t rs[4] = {0, 0, ws[0], ws[1]};
+  const size_t os[4] = {batch * m * o, m * o, o, 1};
+  b200_epilogue ep;
+  ep.alpha = 1.0; ep.bias = bias; ep.activation = activation;
+  return gemm_batch2(dtype, 1, batch, m, i, o, x, ls, weight, rs, 0, out, os, stream, &ep);
+}
+
+int b200_matmat_batch4_forward_scaled(int dtype, size_t batch, size_t seq, size_t m, size_t k, size_t n,
+                                      const void* lhs, const size_t ls[4], const void* rhs, const size_t rs[4],
+                                      double alpha, void* out, void* stream) {
+  if (!ls || !rs) return B200_ERR_NULL;
+  if (ls[0] == 0 || rs[0] == 0 || ls[1] == 0 || rs[1] == 0) return B200_ERR_STRIDE;
+  const size_t os[4] = {seq * m * n, m * n, n, 1};
+  b200_epilogue ep;
+  ep.alpha = alpha; ep.bias = nullptr; ep.activation = B200_ACT_NONE;
+  return gemm_batch2(dtype, batch, seq, m, k, n, lhs, ls, rhs, rs, 0, out, os, stream, &ep);
+}
+
+int b200_attention_forward(int dtype, size_t batch, size_t heads, size_t s1, size_t s2, size_t d, const void* q,
+                           const size_t qs[4], const void* k, const size_t ks[4], const void* v, const size_t vs[4],
+                           double alpha, void* out, const size_t os[4], float* lse, void* stream) {
+  if (!valid_dtype(dtype)) return B200_ERR_DTYPE;
+  if (!qs || !ks || !vs || !os) return B200_ERR_NULL;
+  if (batch && heads && s1 && (!q || !k || !v || !out)) return B200_ERR_NULL;
+  int64_t q4[4], k4[4], v4[4], o4[4];
+  for (int i = 0; i < 4; ++i) { q4[i] = (int64_t)qs[i]; k4[i] = (int64_t)ks[i]; v4[i] = (int64_t)vs[i]; o4[i] = (int64_t)os[i]; }
+  return attention_forward(dtype, (int64_t)batch, (int64_t)heads, (int64_t)s1, (int64_t)s2, (int64_t)d, q, q4, k, k4, v,
+                           v4, alpha, out, o4, lse, (cudaStream_t)stream);
 }
 
 int b200_matmat_batch4_forward(int dtype, size_t batch, size_t seq, size_t m, size_t k, size_t n,

@@ -24,6 +24,14 @@ struct GemmProblem {
   int64_t b_b0 = 0, b_b1 = 0, b_red = 0, b_r = 0, b_c = 0;
   void* c = nullptr;
   int64_t c_b0 = 0, c_b1 = 0, c_r = 0, c_c = 0;
+  // Optional fused epilogue (beta == 0 only):  C = act(alpha * (A.B) + bias), applied to the f32 (f64)
+  // accumulator before the single rounding to C's type.  `bias` has C's element type and is indexed by the
+  // output column j (bias_dim 0, e.g. Linear's bias over output features) or by the row i (bias_dim 1).
+  double alpha = 1.0;
+  const void* bias = nullptr;
+  int bias_dim = 0;
+  int act = B200_ACT_NONE;
+  bool fused() const { return alpha != 1.0 || bias != nullptr || act != B200_ACT_NONE; }
 };
 
 static inline size_t dtype_size(int dtype) {
@@ -60,6 +68,12 @@ int launch_gemm_simt(const GemmProblem& p, cudaStream_t stream);
 int launch_gemm_tc(const GemmProblem& p, cudaStream_t stream);
 bool tc_eligible(const GemmProblem& p);
 int tc_setup_device();                       // cudaFuncSetAttribute for every tensor-core kernel
+
+// Fused attention forward (attention.cu); strides in elements, see b200_attention_forward.
+int attention_setup_device();
+int attention_forward(int dtype, int64_t B, int64_t H, int64_t s1, int64_t s2, int64_t d, const void* q,
+                      const int64_t qs[4], const void* k, const int64_t ks[4], const void* v, const int64_t vs[4],
+                      double alpha, void* out, const int64_t os[4], float* lse, cudaStream_t stream);
 
 // Lowers one problem to a kernel family according to b200_set_path and eligibility.
 int run_gemm(const GemmProblem& p, cudaStream_t stream);

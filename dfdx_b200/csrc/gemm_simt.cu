@@ -27,6 +27,7 @@ struct SimtArgs {
   const void* b; int64_t b_b0, b_b1, b_red, b_r, b_c;
   void* c; int64_t c_b0, c_b1, c_r, c_c;
   int beta;
+  int fused; double alpha; const void* bias; int bias_dim, act;   // optional epilogue: act(alpha*acc + bias)
   int64_t tiles_m, tiles_n;
 };
 
@@ -98,6 +99,11 @@ __global__ void __launch_bounds__(NT) gemm_simt_kernel(const SimtArgs g) {
       T* dst = pc + gi * g.c_r + gj * g.c_c;
       A v = acc[i][j];
       if (g.beta) v += to_acc<T>(*dst);   // beta == 0 never reads the (uninitialised) output
+      if (g.fused) {
+        v *= (A)g.alpha;
+        if (g.bias) v += to_acc<T>(reinterpret_cast<const T*>(g.bias)[g.bias_dim ? gi : gj]);
+        if (g.act == B200_ACT_RELU) v = v > (A)0 ? v : (A)0;
+      }
       *dst = from_acc<T, A>(v);
     }
   }
@@ -111,6 +117,7 @@ int launch_t(const GemmProblem& p, cudaStream_t stream) {
   g.b = p.b; g.b_b0 = p.b_b0; g.b_b1 = p.b_b1; g.b_red = p.b_red; g.b_r = p.b_r; g.b_c = p.b_c;
   g.c = p.c; g.c_b0 = p.c_b0; g.c_b1 = p.c_b1; g.c_r = p.c_r; g.c_c = p.c_c;
   g.beta = p.beta;
+  g.fused = p.fused() ? 1 : 0; g.alpha = p.alpha; g.bias = p.bias; g.bias_dim = p.bias_dim; g.act = p.act;
   g.tiles_m = (p.m + TS - 1) / TS;
   g.tiles_n = (p.n + TS - 1) / TS;
   const int64_t blocks = g.tiles_m * g.tiles_n * p.b0 * p.b1;

@@ -192,6 +192,7 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
             float f[32];
 #pragma unroll
             for (int q = 0; q < 32; ++q) f[q] = __uint_as_float(v[q]);
+            if (g.fused) fused_epilogue<__half>(f, g, row, col0, valid);
             if (g.ksplit > 1) {                      // K slice: partial sums go to the f32 scratch
               add_chunk_atomic(g.split_out + (long long)row * g.split_ld + col0, f, valid);
             } else if (g.c_col) {
@@ -439,6 +440,7 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_const
           const int col0 = t.nt * BN + col_base + c * 32;
           if (col0 < g.n) {
             const int valid = (g.n - col0) < 32 ? (g.n - col0) : 32;
+            if (g.fused) fused_epilogue<float>(&acc[c * 32], g, row, col0, valid);
             if (g.ksplit > 1) {
               if (g.c_col) add_chunk_atomic_col(cbase + (long long)col0 * g.ldc + row, &acc[c * 32], valid, g.ldc);
               else add_chunk_atomic(cbase + (long long)row * g.ldc + col0, &acc[c * 32], valid);
@@ -540,6 +542,7 @@ GemmProblem transposed(const GemmProblem& p) {
   q.a = p.b; q.a_b0 = p.b_b0; q.a_b1 = p.b_b1; q.a_red = p.b_red; q.a_r = p.b_c; q.a_c = p.b_r;
   q.b = p.a; q.b_b0 = p.a_b0; q.b_b1 = p.a_b1; q.b_red = p.a_red; q.b_r = p.a_c; q.b_c = p.a_r;
   q.c_r = p.c_c; q.c_c = p.c_r;
+  q.bias_dim = p.bias_dim ? 0 : 1;
   return q;
 }
 
@@ -591,7 +594,7 @@ Plan make_plan(const GemmProblem& p0, bool col_store) {
     if (pl.ldc <= 0) return pl;
     if ((p.b0 > 1 && p.c_b0 <= 0) || (p.b1 > 1 && p.c_b1 <= 0)) return pl;
   }
-  if (((uintptr_t)p.a | (uintptr_t)p.b) & 15) return pl;
+  if (((uintptr_t)p.a | (uintptr_t)p.b | (uintptr_t)p.bias) & 15) return pl;
   if (!batch_stride_ok(p.b0, p.a_b0, es) || !batch_stride_ok(p.b1, p.a_b1, es) ||
       !batch_stride_ok(p.red, p.a_red, es) || !batch_stride_ok(p.b0, p.b_b0, es) ||
       !batch_stride_ok(p.b1, p.b_b1, es) || !batch_stride_ok(p.red, p.b_red, es))
@@ -718,6 +721,7 @@ int build_launch(Launch& L, const Plan& pl, int esize, int tm, int tn, int bmc, 
     g.c_wide = wide ? 1 : 0;
   }
   g.beta = p.beta;
+  g.fused = p.fused() ? 1 : 0; g.alpha = (float)p.alpha; g.bias = p.bias; g.bias_row = p.bias_dim ? 1 : 0; g.act = p.act;
   g.xform_mode = g_xform_mode;
   g.wait_limit = 400000000LL + (long long)g.red * g.k_blocks * 40000LL;
   g.status = ds->status;
@@ -836,7 +840,7 @@ int launch_es(const Plan& pl, cudaStream_t stream) {
   const double best = choose_tile(pl, ESIZE, &bn);
   if (g_force_bn) bn = g_force_bn;
   // CTA pairs (256 x 256 tiles on two SMs) when the problem fills the machine with them.
-  if (!g_force_bn && g_pair_mode != 1 && p.n > 128) {
+  if (!g_force_bn && g_pair_mode != 1 && p.n > 128 && !p.fused()) {   // the pair kernels have no fused epilogue
     const int64_t tiles2 = ((p.m + 255) / 256) * ((p.n + 255) / 256) * p.b0 * p.b1;
     const int64_t pairs = sms / 2;
     const double cost2 = (double)((tiles2 + pairs - 1) / pairs) * 0.8;   // a pair wave of 256x256 tiles vs a wave of 128x256 tiles
@@ -845,7 +849,7 @@ int launch_es(const Plan& pl, cudaStream_t stream) {
   // Split-K (f32, one batch item): when the tiles alone leave most SMs idle, K slices become extra work
   // units.  Model: time = waves * (k-blocks per unit * t_kb(tile width) + t_fixed), in microseconds.
   int ksplit = 1;
-  if (g_split_mode != 1 && p.b0 == 1 && p.b1 == 1) {
+  if (g_split_mode != 1 && p.b0 == 1 && p.b1 == 1 && !p.fused()) {   // a fused epilogue needs the whole sum in one unit
     const int bk = (ESIZE == 4) ? 16 : 64;
     const int64_t total_kb = p.red * ((p.k + bk - 1) / bk);
     auto model = [&](int bn_, int s_) {

@@ -230,7 +230,50 @@ struct TcArgs {
   int xform_mode;                 // f32: 1 = big stays raw, write small only; 0 = also rewrite big = tf32_rn(x)
   long long wait_limit;           // clock cycles
   int* status;
+  // optional epilogue (beta == 0, no split-K):  C = act(alpha * acc + bias)
+  int fused;                      // any of the three below is active
+  float alpha;
+  const void* bias;               // C's element type, 16-byte aligned; indexed by the kernel's column, or
+  int bias_row;                   // (bias_row) by the kernel's row
+  int act;                        // B200_ACT_*
 };
+
+// Fused epilogue on 32 consecutive accumulator columns [col0, col0+32) of output row `row` (row < m):
+// f = act(alpha * f + bias).  T is C's element type (the bias has the same type).
+__device__ __forceinline__ float bias_to_float(float x) { return x; }
+__device__ __forceinline__ float bias_to_float(__half x) { return __half2float(x); }
+
+template <typename T>
+__device__ __forceinline__ void fused_epilogue(float* f, const TcArgs& g, int row, int col0, int valid) {
+  const T* bias = reinterpret_cast<const T*>(g.bias);
+  const float alpha = g.alpha;
+  if (bias == nullptr) {
+#pragma unroll
+    for (int q = 0; q < 32; ++q) f[q] *= alpha;
+  } else if (g.bias_row) {
+    const float br = bias_to_float(__ldg(bias + row));
+#pragma unroll
+    for (int q = 0; q < 32; ++q) f[q] = fmaf(f[q], alpha, br);
+  } else if (valid == 32) {
+    // all lanes read the same 32 bias values: broadcast 16-byte loads
+    constexpr int PER = 16 / (int)sizeof(T);          // elements per 16-byte vector
+#pragma unroll
+    for (int v = 0; v < 32 / PER; ++v) {
+      const uint4 raw = __ldg(reinterpret_cast<const uint4*>(bias + col0) + v);
+      const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+      for (int q = 0; q < PER; ++q) f[v * PER + q] = fmaf(f[v * PER + q], alpha, bias_to_float(e[q]));
+    }
+  } else {
+#pragma unroll
+    for (int q = 0; q < 32; ++q)
+      if (q < valid) f[q] = fmaf(f[q], alpha, bias_to_float(__ldg(bias + col0 + q)));
+  }
+  if (g.act == B200_ACT_RELU) {
+#pragma unroll
+    for (int q = 0; q < 32; ++q) f[q] = fmaxf(f[q], 0.f);
+  }
+}
 
 // 256-bit global accesses (sm_100): one 32-byte sector per thread and instruction.
 __device__ __forceinline__ void ld_global_v8(const void* p, uint32_t (&r)[8]) {

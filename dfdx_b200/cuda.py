@@ -164,6 +164,42 @@ class Cuda:
                                                    _st(rhs.stride()), _ptr(grad_rhs), grad_out.data_ptr(),
                                                    self._stream(), None), "b200_matmat_batch4_backward")
 
+    # -- fused epilogues (API additions) -------------------------------------------------------------
+    def gemm_batch_fused(self, lhs, rhs, out, alpha=1.0, bias=None, relu=False) -> None:
+        """out[b0,b1] = act(alpha * lhs[b0,b1] @ rhs[b0,b1] + bias) for rank-4 views (batch strides of lhs / rhs
+        may be 0); one launch, `out` is only written."""
+        (b0, b1, m, k), n = lhs.shape, rhs.shape[3]
+        _assert_eq(tuple(rhs.shape[:3]), (b0, b1, k))
+        ep = _lib.Epilogue(float(alpha), _ptr(bias), _lib.ACT_RELU if relu else _lib.ACT_NONE)
+        check(self.lib.b200_gemm_batch_fused(self._dtype(lhs), b0, b1, m, k, n, lhs.data_ptr(), _st(lhs.stride()),
+                                             rhs.data_ptr(), _st(rhs.stride()), ep, out.data_ptr(),
+                                             _st(out.stride()), self._stream()), "b200_gemm_batch_fused")
+
+    def linear_forward(self, x, weight_view, bias=None, relu=False):
+        """`Linear::try_forward` (+ optional ReLU) in one launch: x (B, S, I), weight_view the (I, O) view of the
+        stored (O, I) weight, bias (O,) -> (B, S, O)."""
+        (b, m, i), o = x.shape, weight_view.shape[1]
+        _assert_eq(weight_view.shape[0], i)
+        if bias is not None:
+            _assert_eq(tuple(bias.shape), (o,))
+        out = self._empty((b, m, o), x)
+        check(self.lib.b200_linear_forward(self._dtype(x), b, m, i, o, x.data_ptr(), _st(x.stride()),
+                                           weight_view.data_ptr(), _st(weight_view.stride()), _ptr(bias),
+                                           _lib.ACT_RELU if relu else _lib.ACT_NONE, out.data_ptr(),
+                                           self._stream()), "b200_linear_forward")
+        return out
+
+    def matmat_batch4_forward_scaled(self, lhs, rhs, alpha: float):
+        """`q.matmul(k) * scalar` (multi_head_attention.rs:136-137) in one launch."""
+        (b, s, m, k), n = lhs.shape, rhs.shape[3]
+        _assert_eq(tuple(rhs.shape[:3]), (b, s, k))
+        out = self._empty((b, s, m, n), lhs)
+        check(self.lib.b200_matmat_batch4_forward_scaled(self._dtype(lhs), b, s, m, k, n, lhs.data_ptr(),
+                                                         _st(lhs.stride()), rhs.data_ptr(), _st(rhs.stride()),
+                                                         float(alpha), out.data_ptr(), self._stream()),
+              "b200_matmat_batch4_forward_scaled")
+        return out
+
     # -- TryMatMul (matmul/mod.rs:133-311) ---------------------------------------------------------
     def matmul(self, lhs: torch.Tensor, rhs: torch.Tensor):
         """Rank dispatch of `TryMatMul`.  Returns (out, backward) where

@@ -5,10 +5,13 @@ stack: the block structure restates dfdx's `EncoderBlock` (dfdx/src/nn/layers/tr
 ResidualAdd(MultiHeadAttention) -> LayerNorm1D -> ResidualAdd(Linear, ReLU, Linear) -> LayerNorm1D)
 and `MultiHeadAttention::try_forward` (multi_head_attention.rs:105-146: three Linear layers, the
 (b,s,h,d) buffers viewed as (b,h,s,d) / (b,h,d,s) without a copy, q.matmul(k) * 1/sqrt(d), softmax,
-.matmul(v), permute back, output Linear).  Every `matmul` goes through `dfdx_b200.Cuda.matmul`
+.matmul(v), permute back, output Linear).  Every `matmul` goes through `dfdx_b200.Cuda`
 (`MatMatBrKernel` for the Linear layers, `MatMatBatch4Kernel` for the attention products, forward and
-backward); bias, residual, LayerNorm, softmax, ReLU, the MSE loss and Adam are plain torch ops, as
-they are separate (non-matmul) kernels in dfdx too.
+backward).  With `fused=True` (default) the ops that directly follow a GEMM in the forward pass — Linear's
+bias add, the feed-forward ReLU, the 1/sqrt(d) scale of the scores — run in that GEMM's epilogue
+(`b200_linear_forward`, `b200_matmat_batch4_forward_scaled`); with `fused=False` they are separate torch
+ops, as they are separate kernels in dfdx.  Residual, LayerNorm, softmax, the MSE loss and Adam are plain
+torch ops either way.
 
 Parameters are f32 master weights; each step computes in f16 (`AMP<f16>`-like: f16 storage, f32
 accumulation inside the GEMMs) and Adam updates the f32 masters.
@@ -52,28 +55,83 @@ def matmul(dev: Cuda, lhs: torch.Tensor, rhs: torch.Tensor) -> torch.Tensor:
     return _MatMul.apply(dev, lhs, rhs)
 
 
+class _FusedLinear(torch.autograd.Function):
+    """`Linear` (+ optional ReLU) with the bias add and the activation done in the GEMM's epilogue
+    (`b200_linear_forward`): one launch and one pass over the output where the unfused path runs three.
+    Backward: ReLU's mask and the bias gradient (a column sum) are torch ops, the two GEMMs are
+    `MatMatBrKernel::backward`."""
+
+    @staticmethod
+    def forward(ctx, dev: Cuda, x, weight, bias, relu: bool):
+        if x.storage_offset() or not _dense(x):
+            x = x.contiguous()
+        w_view = weight.permute(1, 0)                              # (O, I) stored, (I, O) consumed
+        y = dev.linear_forward(x, w_view, bias, relu)
+        ctx.dev, ctx.relu = dev, relu
+        ctx.save_for_backward(x, weight, y if relu else None)
+        return y
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        x, weight, y = ctx.saved_tensors
+        dev, w_view = ctx.dev, weight.permute(1, 0)
+        g = grad_out.contiguous()
+        if ctx.relu:
+            g = torch.ops.aten.threshold_backward(g, y, 0.0)
+        gx, gw = dev.alloc_grad(x), dev.alloc_grad(w_view)
+        dev.matmat_br_backward(x, gx, w_view, gw, g)
+        grad_bias = g.sum(dim=(0, 1), dtype=torch.float32).to(g.dtype)
+        return None, dev.grad_view(gx, x), gw.view_as(weight), grad_bias, None
+
+
+class _ScaledMatMul(torch.autograd.Function):
+    """`q.matmul(k) * alpha` with the scale in the GEMM's epilogue (`b200_matmat_batch4_forward_scaled`)."""
+
+    @staticmethod
+    def forward(ctx, dev: Cuda, lhs, rhs, alpha: float):
+        if lhs.storage_offset() or not _dense(lhs):
+            lhs = lhs.contiguous()
+        if rhs.storage_offset() or not _dense(rhs):
+            rhs = rhs.contiguous()
+        ctx.dev, ctx.alpha = dev, alpha
+        ctx.save_for_backward(lhs, rhs)
+        return dev.matmat_batch4_forward_scaled(lhs, rhs, alpha)
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        lhs, rhs = ctx.saved_tensors
+        dev = ctx.dev
+        g = (grad_out * ctx.alpha).contiguous()
+        gl, gr = dev.alloc_grad(lhs), dev.alloc_grad(rhs)
+        dev.matmat_batch4_backward(lhs, gl, rhs, gr, g)
+        return None, dev.grad_view(gl, lhs), dev.grad_view(gr, rhs), None
+
+
 class Linear(torch.nn.Module):
     """dfdx `Linear`: weight stored (O, I), consumed as the permuted (I, O) view; uniform(+-1/sqrt(I)) init
     (dfdx/src/nn/layers/linear.rs:65-89)."""
 
-    def __init__(self, dev: Cuda, i: int, o: int, gen: torch.Generator):
+    def __init__(self, dev: Cuda, i: int, o: int, gen: torch.Generator, fused: bool = True):
         super().__init__()
-        self.dev = dev
+        self.dev, self.fused = dev, fused
         b = 1.0 / math.sqrt(i)
         self.weight = torch.nn.Parameter(((torch.rand(o, i, generator=gen) * 2 - 1) * b).to(dev.device))
         self.bias = torch.nn.Parameter(((torch.rand(o, generator=gen) * 2 - 1) * b).to(dev.device))
 
-    def forward(self, x):
+    def forward(self, x, relu: bool = False):
         w = self.weight.half()                                     # f16 compute copy of the f32 master
-        return matmul(self.dev, x, w.permute(1, 0)) + self.bias.half()
+        if self.fused:
+            return _FusedLinear.apply(self.dev, x, w, self.bias.half(), relu)
+        y = matmul(self.dev, x, w.permute(1, 0)) + self.bias.half()
+        return torch.relu(y) if relu else y
 
 
 class MultiHeadAttention(torch.nn.Module):
-    def __init__(self, dev: Cuda, model: int, heads: int, gen: torch.Generator):
+    def __init__(self, dev: Cuda, model: int, heads: int, gen: torch.Generator, fused: bool = True):
         super().__init__()
-        self.dev, self.heads = dev, heads
-        self.w_q, self.w_k = Linear(dev, model, model, gen), Linear(dev, model, model, gen)
-        self.w_v, self.w_o = Linear(dev, model, model, gen), Linear(dev, model, model, gen)
+        self.dev, self.heads, self.fused = dev, heads, fused
+        self.w_q, self.w_k = Linear(dev, model, model, gen, fused), Linear(dev, model, model, gen, fused)
+        self.w_v, self.w_o = Linear(dev, model, model, gen, fused), Linear(dev, model, model, gen, fused)
 
     def forward(self, x):
         b, s, m = x.shape
@@ -81,17 +139,21 @@ class MultiHeadAttention(torch.nn.Module):
         v = self.w_v(x).reshape(b, s, h, d).permute(0, 2, 1, 3)
         k = self.w_k(x).reshape(b, s, h, d).permute(0, 2, 3, 1)
         q = self.w_q(x).reshape(b, s, h, d).permute(0, 2, 1, 3)
-        weights = torch.softmax(matmul(self.dev, q, k) * (1.0 / math.sqrt(d)), dim=-1)
+        if self.fused:
+            scores = _ScaledMatMul.apply(self.dev, q, k, 1.0 / math.sqrt(d))
+        else:
+            scores = matmul(self.dev, q, k) * (1.0 / math.sqrt(d))
+        weights = torch.softmax(scores, dim=-1)
         tokens = matmul(self.dev, weights, v).permute(0, 2, 1, 3).reshape(b, s, m)
         return self.w_o(tokens)
 
 
 class EncoderBlock(torch.nn.Module):
-    def __init__(self, dev: Cuda, model: int, heads: int, ff: int, gen: torch.Generator):
+    def __init__(self, dev: Cuda, model: int, heads: int, ff: int, gen: torch.Generator, fused: bool = True):
         super().__init__()
-        self.attn = MultiHeadAttention(dev, model, heads, gen)
+        self.attn = MultiHeadAttention(dev, model, heads, gen, fused)
         self.norm1 = torch.nn.LayerNorm(model, device=dev.device)
-        self.l1, self.l2 = Linear(dev, model, ff, gen), Linear(dev, ff, model, gen)
+        self.l1, self.l2 = Linear(dev, model, ff, gen, fused), Linear(dev, ff, model, gen, fused)
         self.norm2 = torch.nn.LayerNorm(model, device=dev.device)
 
     def _norm(self, ln, x):
@@ -99,16 +161,16 @@ class EncoderBlock(torch.nn.Module):
 
     def forward(self, x):
         x = self._norm(self.norm1, x + self.attn(x))
-        return self._norm(self.norm2, x + self.l2(torch.relu(self.l1(x))))
+        return self._norm(self.norm2, x + self.l2(self.l1(x, relu=True)))
 
 
 class Encoder(torch.nn.Module):
     """`layers` encoder blocks (BASELINE configuration 5: 6 x (d_model 512, 8 heads, ffn 2048))."""
 
-    def __init__(self, dev: Cuda, layers=6, model=512, heads=8, ff=2048, seed=0):
+    def __init__(self, dev: Cuda, layers=6, model=512, heads=8, ff=2048, seed=0, fused=True):
         super().__init__()
         gen = torch.Generator().manual_seed(seed)
-        self.blocks = torch.nn.ModuleList(EncoderBlock(dev, model, heads, ff, gen) for _ in range(layers))
+        self.blocks = torch.nn.ModuleList(EncoderBlock(dev, model, heads, ff, gen, fused) for _ in range(layers))
 
     def forward(self, x):
         for blk in self.blocks:

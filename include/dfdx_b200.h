@@ -58,6 +58,22 @@ typedef struct {
   size_t chan_in, chan_out, h_in, h_out, w_in, w_out;
 } b200_conv2d_op;
 
+/* Activation applied by a fused epilogue. */
+typedef enum {
+  B200_ACT_NONE = 0,
+  B200_ACT_RELU = 1     /* max(x, 0), dfdx's `ReLU` (dfdx-core/src/tensor_ops/relu/mod.rs) */
+} b200_activation;
+
+/* Work done on each output element between the accumulator and the single store:
+ *     out = activation(alpha * sum + bias[j])            (j = output column)
+ * `bias` is NULL or `n` elements of the output's dtype, 16-byte aligned for the tensor-core kernels
+ * (otherwise the SIMT kernel serves the call). */
+typedef struct {
+  double alpha;         /* 1.0 = no scaling */
+  const void* bias;
+  int activation;       /* b200_activation */
+} b200_epilogue;
+
 /* Which kernel family serves the contraction.  AUTO is the product behaviour. */
 typedef enum {
   B200_PATH_AUTO = 0,   /* tensor cores when operands are TMA-addressable and the problem is not tiny */
@@ -181,6 +197,57 @@ int b200_matmat_batch4_backward(int dtype, size_t batch, size_t seq, size_t m, s
                                 const void* lhs, const size_t lhs_strides[4], void* grad_lhs,
                                 const void* rhs, const size_t rhs_strides[4], void* grad_rhs,
                                 const void* grad_out, void* stream, void* par_stream);
+
+/* ---- GEMMs with a fused epilogue (API additions: no single counterpart in the reference) -------- */
+
+/* A doubly batched strided GEMM (strides = [batch0, batch1, row, col] in elements; an lhs / rhs batch
+ * stride may be 0) whose epilogue applies `ep` before the store: one kernel and one pass over `out`
+ * where dfdx runs a GEMM and then one elementwise kernel per op, each re-reading and re-writing the GEMM's
+ * output.  beta is 0: `out` is only written.  `ep` NULL = plain GEMM. */
+int b200_gemm_batch_fused(int dtype, size_t batch0, size_t batch1, size_t m, size_t k, size_t n,
+                          const void* lhs, const size_t lhs_strides[4],
+                          const void* rhs, const size_t rhs_strides[4],
+                          const b200_epilogue* ep, void* out, const size_t out_strides[4], void* stream);
+
+/* `Linear::try_forward` in one launch (dfdx/src/nn/layers/linear.rs:82-89: `x.matmul(weight.permute())`,
+ * then `Bias1D::try_forward`, bias1d.rs:66-79: `bias.broadcast_like(&x) + x`), optionally followed by the
+ * `ReLU` of FeedForward (dfdx/src/nn/layers/transformer.rs:4-8):
+ *     out[b, s, o] = act(sum_i x[b, s, i] * weight[i, o] + bias[o])
+ * x: (batch, m, i) with strides `x_strides`; `weight` is the (i, o) VIEW with strides `w_strides`
+ * (for dfdx's stored (O, I) weight: [1, I]); bias: o elements or NULL; out: contiguous (batch, m, o). */
+int b200_linear_forward(int dtype, size_t batch, size_t m, size_t i, size_t o,
+                        const void* x, const size_t x_strides[3],
+                        const void* weight, const size_t w_strides[2],
+                        const void* bias, int activation, void* out, void* stream);
+
+/* `q.matmul(k) * scalar` of MultiHeadAttention in one launch
+ * (dfdx/src/nn/layers/multi_head_attention.rs:136-137): `b200_matmat_batch4_forward` with every output
+ * element multiplied by `alpha` before it is rounded and stored. */
+int b200_matmat_batch4_forward_scaled(int dtype, size_t batch, size_t seq, size_t m, size_t k, size_t n,
+                                      const void* lhs, const size_t lhs_strides[4],
+                                      const void* rhs, const size_t rhs_strides[4],
+                                      double alpha, void* out, void* stream);
+
+/* ---- fused attention (API addition) --------------------------------------------------------------- */
+
+/* The op sequence of `MultiHeadAttention::try_forward` between its projections
+ * (dfdx/src/nn/layers/multi_head_attention.rs:136-141):
+ *     weights = softmax(q.matmul(k) * alpha, last axis);   tokens = weights.matmul(v)
+ * in one kernel: the (batch, heads, S1, S2) score tensor lives in tensor memory / shared memory and never
+ * reaches HBM (the unfused path writes and re-reads it five times).  f16 / AMP f16 only; f32 accumulation
+ * and an f32 softmax inside.
+ *   q   : (batch, heads, S1, D) view      k : (batch, heads, D, S2) view — exactly what dfdx passes to matmul
+ *   v   : (batch, heads, S2, D) view      out: (batch, heads, S1, D) view (e.g. a permuted (batch, S1, heads, D)
+ *         buffer, which saves the copy `tokens.permute().reshape()` makes)
+ * all with unit stride along D and every other stride a multiple of 8 elements, 16-byte aligned bases, D a
+ * multiple of 8 and <= 128; anything else returns B200_ERR_UNSUPPORTED before any launch and the caller keeps
+ * the unfused sequence.  `lse` is NULL or batch*heads*S1 floats that receive log(sum_j exp(alpha * s_ij)),
+ * which b200_attention_backward needs. */
+int b200_attention_forward(int dtype, size_t batch, size_t heads, size_t s1, size_t s2, size_t d,
+                           const void* q, const size_t q_strides[4],
+                           const void* k, const size_t k_strides[4],
+                           const void* v, const size_t v_strides[4],
+                           double alpha, void* out, const size_t out_strides[4], float* lse, void* stream);
 
 /* ---- conv2d (unfold + GEMM lowering) ---------------------------------------------------------- */
 

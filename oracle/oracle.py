@@ -226,6 +226,20 @@ def conv2d(img: torch.Tensor, filters: torch.Tensor, stride=1, padding=0, dilati
     return (out_t[0] if squeeze else out_t), backward
 
 
+def fused_matmul(lhs: torch.Tensor, rhs: torch.Tensor, alpha: float = 1.0, bias: torch.Tensor = None,
+                 relu: bool = False) -> torch.Tensor:
+    """The op sequences the fused epilogues stand for, step by step in f64: `matmul`, then `* scalar`
+    (multi_head_attention.rs:136-137), then `Bias1D` = bias broadcast over the leading dims + add
+    (nn/layers/bias1d.rs:66-79, called from linear.rs:82-89), then `ReLU` = max(x, 0)."""
+    y, _ = matmul(lhs, rhs)
+    y = y * float(alpha)
+    if bias is not None:
+        y = y + bias.detach().cpu().to(torch.float64)
+    if relu:
+        y = torch.clamp_min(y, 0.0)
+    return y
+
+
 def rel_frobenius(got: torch.Tensor, want: torch.Tensor) -> float:
     """||got - want||_F / ||want||_F in f64 (0/0 -> 0)."""
     g = got.detach().cpu().to(torch.float64)

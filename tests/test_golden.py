@@ -138,6 +138,17 @@ def test_linear(be, name):
     _check(be, dy.reshape(-1, dy.shape[-1]).sum(0), a[2])
 
 
+@pytest.mark.parametrize("name", ["test_forward_1d", "test_forward_2d", "test_forward_3d"])
+def test_linear_fused_forward(be, name):
+    """The same known answers through the one-launch Linear forward (matmul + bias in the epilogue)."""
+    t, a = _split(golden("linear")[name])
+    weight, bias, x = be.tensor(t[0]), be.tensor(t[1]), be.tensor(t[2])
+    _check(be, be.linear(x, weight.permute(1, 0), bias), a[0])
+    y_relu = be.host(be.linear(x, weight.permute(1, 0), bias, relu=True))
+    want = torch.clamp_min(torch.tensor(a[0]["value"], dtype=torch.float64), 0.0)
+    _check(be, y_relu, dict(a[0], value=want.tolist()))
+
+
 # ------------------------------------------------------------------------------------------ conv2d
 CONV_BIAS_CASES = {
     "test_conv2d_default_stride_and_padding": dict(stride=1, padding=0),

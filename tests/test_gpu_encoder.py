@@ -6,11 +6,12 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-def test_encoder_block_matches_torch_autograd(cuda_dev):
+@pytest.mark.parametrize("fused", [False, True], ids=["unfused", "fused-epilogues"])
+def test_encoder_block_matches_torch_autograd(cuda_dev, fused):
     from dfdx_b200 import encoder as enc
     dev = cuda_dev
     gen = torch.Generator().manual_seed(1)
-    blk = enc.EncoderBlock(dev, 128, 4, 256, gen)
+    blk = enc.EncoderBlock(dev, 128, 4, 256, gen, fused=fused)
     x = torch.randn(3, 40, 128, generator=gen).half().to(dev.device).requires_grad_(True)
     t = torch.randn(3, 40, 128, generator=gen).to(dev.device)
     before = dev.lib.b200_launch_count()
@@ -23,6 +24,9 @@ def test_encoder_block_matches_torch_autograd(cuda_dev):
     # reference: same math with torch.matmul in f32 on the f16-rounded values
     real = enc.matmul
     enc.matmul = lambda d, a, b: torch.matmul(a.float(), b.float()).half()
+    for mod in blk.modules():                                      # the reference pass runs the unfused op sequence
+        if hasattr(mod, "fused"):
+            mod.fused = False
     try:
         for p in blk.parameters():
             p.grad = None
