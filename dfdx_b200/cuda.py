@@ -200,6 +200,24 @@ class Cuda:
               "b200_matmat_batch4_forward_scaled")
         return out
 
+    def attention_forward(self, q, k, v, alpha: float, out=None, want_lse: bool = False):
+        """softmax(q.matmul(k) * alpha).matmul(v) in one kernel (multi_head_attention.rs:136-141).
+        q (B,H,S1,D), k (B,H,D,S2), v (B,H,S2,D) views with unit stride along D.  `out` defaults to a
+        (B,S1,H,D) buffer viewed as (B,H,S1,D), i.e. already in the layout the output projection reads.
+        Returns (out, lse or None)."""
+        b, h, s1, d = q.shape
+        s2 = k.shape[3]
+        _assert_eq(tuple(k.shape), (b, h, d, s2))
+        _assert_eq(tuple(v.shape), (b, h, s2, d))
+        if out is None:
+            out = self._empty((b, s1, h, d), q).permute(0, 2, 1, 3)
+        lse = torch.empty((b, h, s1), dtype=torch.float32, device=q.device) if want_lse else None
+        check(self.lib.b200_attention_forward(self._dtype(q), b, h, s1, s2, d, q.data_ptr(), _st(q.stride()),
+                                              k.data_ptr(), _st(k.stride()), v.data_ptr(), _st(v.stride()),
+                                              float(alpha), out.data_ptr(), _st(out.stride()), _ptr(lse),
+                                              self._stream()), "b200_attention_forward")
+        return out, lse
+
     # -- TryMatMul (matmul/mod.rs:133-311) ---------------------------------------------------------
     def matmul(self, lhs: torch.Tensor, rhs: torch.Tensor):
         """Rank dispatch of `TryMatMul`.  Returns (out, backward) where

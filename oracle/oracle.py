@@ -240,6 +240,18 @@ def fused_matmul(lhs: torch.Tensor, rhs: torch.Tensor, alpha: float = 1.0, bias:
     return y
 
 
+def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, alpha: float):
+    """The middle of `MultiHeadAttention::try_forward` (dfdx/src/nn/layers/multi_head_attention.rs:136-141) in
+    f64: weights = softmax(q.matmul(k) * alpha) over the last axis (softmax.rs: exp(x - logsumexp(x))),
+    tokens = weights.matmul(v).  q (B,H,S1,D), k (B,H,D,S2), v (B,H,S2,D).  Returns (tokens, logsumexp)."""
+    scores, _ = matmul(q, k)
+    scores = scores * float(alpha)
+    lse = torch.logsumexp(scores, dim=-1)
+    weights = torch.exp(scores - lse.unsqueeze(-1))
+    tokens, _ = matmul(weights, v.detach().cpu().to(torch.float64))
+    return tokens, lse
+
+
 def rel_frobenius(got: torch.Tensor, want: torch.Tensor) -> float:
     """||got - want||_F / ||want||_F in f64 (0/0 -> 0)."""
     g = got.detach().cpu().to(torch.float64)

@@ -1,0 +1,92 @@
+"""GPU parity of the fused attention kernel against the f64 oracle's step-by-step op sequence
+(matmul, scale, softmax, matmul), through the C ABI.  Tolerance: relative Frobenius error <= 2e-3 (f16
+output), log-sum-exp within 2e-3 absolute."""
+import math
+
+import pytest
+import torch
+
+import dfdx_b200
+from dfdx_b200 import _lib
+from helpers import FROB_TOL
+
+pytestmark = pytest.mark.gpu
+
+
+def gen(seed):
+    return torch.Generator().manual_seed(seed)
+
+
+def mha_views(b, h, s1, s2, d, g, device, spread=1.0):
+    """q, k, v as MultiHeadAttention builds them: (B,S,H,D) buffers viewed through permutes, no copy."""
+    q = (torch.randn(b, s1, h, d, generator=g, dtype=torch.float64) * spread).half().to(device).permute(0, 2, 1, 3)
+    k = (torch.randn(b, s2, h, d, generator=g, dtype=torch.float64) * spread).half().to(device).permute(0, 2, 3, 1)
+    v = torch.randn(b, s2, h, d, generator=g, dtype=torch.float64).half().to(device).permute(0, 2, 1, 3)
+    return q, k, v
+
+
+SHAPES = [(1, 1, 128, 128, 64), (2, 3, 200, 136, 64), (1, 2, 384, 520, 32), (1, 1, 128, 256, 128),
+          (2, 2, 72, 72, 16), (1, 2, 8, 1000, 64), (1, 1, 300, 8, 40), (1, 2, 130, 257, 96)]
+
+
+@pytest.mark.parametrize("shape", SHAPES, ids=lambda s: "x".join(map(str, s)))
+def test_attention_forward(cuda_dev, oracle, shape):
+    b, h, s1, s2, d = shape
+    q, k, v = mha_views(b, h, s1, s2, d, gen(sum(shape)), cuda_dev.device)
+    alpha = 1.0 / math.sqrt(d)
+    before = cuda_dev.lib.b200_tensor_launch_count()
+    out, lse = cuda_dev.attention_forward(q, k, v, alpha, want_lse=True)
+    cuda_dev.synchronize()
+    assert cuda_dev.lib.b200_tensor_launch_count() - before == 1
+    assert out.shape == (b, h, s1, d) and out.permute(0, 2, 1, 3).is_contiguous()
+    want, want_lse = oracle.attention(q.cpu(), k.cpu(), v.cpu(), alpha)
+    err = oracle.rel_frobenius(out, want)
+    assert err <= FROB_TOL[torch.float16], f"rel frobenius {err:.3e}"
+    assert float((lse.cpu().double() - want_lse).abs().max()) <= 2e-3
+
+
+def test_attention_peaked_scores_and_negative_scale(cuda_dev, oracle):
+    """Large score spread (the running maximum moves by hundreds between key tiles) and a negative scale."""
+    q, k, v = mha_views(1, 2, 256, 640, 64, gen(5), cuda_dev.device, spread=4.0)
+    for alpha in (1.0, -0.5):
+        out, lse = cuda_dev.attention_forward(q, k, v, alpha, want_lse=True)
+        want, want_lse = oracle.attention(q.cpu(), k.cpu(), v.cpu(), alpha)
+        assert oracle.rel_frobenius(out, want) <= FROB_TOL[torch.float16]
+        assert float(((lse.cpu().double() - want_lse).abs() / want_lse.abs().clamp_min(1.0)).max()) <= 2e-3
+        assert bool(torch.isfinite(out).all())
+
+
+def test_attention_output_layouts(cuda_dev, oracle):
+    """A caller-provided contiguous (B,H,S1,D) output (what `weights.matmul(v)` allocates) gives the same values."""
+    q, k, v = mha_views(2, 4, 160, 160, 64, gen(6), cuda_dev.device)
+    a, _ = cuda_dev.attention_forward(q, k, v, 0.125)
+    out = torch.empty(2, 4, 160, 64, dtype=torch.float16, device=cuda_dev.device)
+    b_, _ = cuda_dev.attention_forward(q, k, v, 0.125, out=out)
+    assert torch.equal(a.contiguous(), b_)
+
+
+def test_attention_matches_unfused_sequence(cuda_dev):
+    """Against this library's own unfused path (two batched GEMMs + torch softmax), configuration 3's shape."""
+    q, k, v = mha_views(16, 16, 512, 512, 64, gen(7), cuda_dev.device)
+    out, _ = cuda_dev.attention_forward(q, k, v, 0.125)
+    scores = cuda_dev.matmat_batch4_forward_scaled(q, k, 0.125)
+    ref = cuda_dev.matmat_batch4_forward(torch.softmax(scores.float(), dim=-1).half(), v)
+    err = (out.float() - ref.float()).norm() / ref.float().norm()
+    assert float(err) <= 2e-3
+
+
+def test_attention_rejects_what_it_cannot_address(cuda_dev):
+    dev = cuda_dev
+    q, k, v = mha_views(1, 1, 64, 64, 64, gen(8), dev.device)
+    with pytest.raises(dfdx_b200.B200Error) as e:                     # unit stride must be along D
+        dev.attention_forward(q.permute(0, 1, 3, 2).contiguous().permute(0, 1, 3, 2), k, v, 1.0)
+    assert e.value.status == _lib.ERR_UNSUPPORTED
+    q32 = q.float()
+    with pytest.raises(dfdx_b200.B200Error) as e:                     # f16 only
+        dev.attention_forward(q32, k.float(), v.float(), 1.0)
+    assert e.value.status == _lib.ERR_UNSUPPORTED
+    qd, kd, vd = mha_views(1, 1, 64, 64, 12, gen(9), dev.device)      # D not a multiple of 8
+    with pytest.raises(dfdx_b200.B200Error) as e:
+        dev.attention_forward(qd, kd, vd, 1.0)
+    assert e.value.status == _lib.ERR_UNSUPPORTED
+    assert dev.device_status() == 0
