@@ -6,16 +6,19 @@
 // .matmul(v)), which on the unfused path costs two batched GEMMs plus three elementwise passes over the
 // (batch, heads, S1, S2) score tensor.
 //
-// One CTA per (batch, head, 128-query tile); key/value tiles of 128 rows stream through TMA rings.
-//   warp 4      TMA producer: Q once, then K_j and V_j
-//   warp 5      MMA issuer:   S_j = Q K_j^T (kind::f16, M=128, N=128) into one of two TMEM buffers;
-//                             PV_j = P_j V_j (M=128, N=DP) into one of two more.  QK of tile j+1 is issued
-//                             before PV of tile j, so the tensor pipe works while the softmax warps are busy.
-//   warps 0..3  softmax: thread r owns query row r.  Reads S_j from TMEM, keeps the running row maximum m and
-//               sum l (base-2 exponent domain), writes P_j = exp2(x - m) as f16 into shared memory in the
-//               128B-swizzled K-major layout the MMA reads, then adds the finished PV_{j-1} into its f32 output
-//               registers and rescales them to the new maximum.  After the last tile: O = acc / l, and the
-//               row's log-sum-exp for the backward pass.
+// One CTA per (batch, head, 256 queries): two query tiles of 128 rows, each owned by one softmax warpgroup,
+// share the key/value tiles (128 rows each) that stream through TMA rings.
+//   warpgroup 2  warp 8: TMA producer (both Q tiles once, then K_j and V_j); warps 9, 10, 11: MMA issuers (one
+//                thread each: all S_t = Q_t K_j^T (kind::f16, M=128, N=128); PV_0 = P_0 V_j; PV_1 = P_1 V_j with
+//                M=128, N=DP), results in TMEM.  QK of tile j+1 is issued as soon as the softmax warps have read S_t(j), so the
+//                tensor pipe works while they are busy.
+//   warpgroups 0, 1  softmax: thread r owns query row r of tile t.  Reads S_t(j) from TMEM, adds the finished
+//                PV_t(j-1) into its f32 output registers, keeps the running row maximum m and sum l (base-2
+//                exponent domain), rescales, writes P = exp2(s*scale - m) as f16 into shared memory in the
+//                128B-swizzled K-major layout the MMA reads.  After the last tile: O = acc / l, and the row's
+//                log-sum-exp for the backward pass.  Two warpgroups give every scheduler two independent
+//                softmax warps (the exponentials run on the 16-per-clock SFU pipe and bound the kernel).
+//   Registers are moved from warpgroup 2 to the softmax warpgroups with setmaxnreg.
 // Every wait is bounded; on expiry the CTA raises its abort flag, all roles drain and the kernel reports
 // B200_ERR_DEVICE_TIMEOUT through the device status word.
 #include "tc_device.cuh"
@@ -29,7 +32,7 @@ using namespace tcx;
 
 struct AttnArgs {
   int s1, s2, d;
-  int heads, q_tiles, kv_tiles;
+  int heads, q_pairs, kv_tiles;    // q_pairs: CTAs per (batch, head), each 256 queries
   float scale_log2;               // alpha * log2(e)
   __half* out;
   long long o_b, o_h, o_s;        // element strides of the (batch, head, query) axes; d has unit stride
@@ -40,18 +43,23 @@ struct AttnArgs {
 
 template <int DP>
 struct AttnCfg {
-  static constexpr int KV_STAGES = DP == 64 ? 3 : 2;
-  static constexpr int Q_BYTES = 128 * DP * 2;
+  static constexpr int KV_STAGES = DP == 64 ? 2 : 1;       // DP = 128: shared memory holds one K and one V tile
+  static constexpr int NB = DP == 64 ? 2 : 1;              // buffers per query tile for P (shared memory) and PV (TMEM)
+  static constexpr int Q_BYTES = 128 * DP * 2;             // one query tile
   static constexpr int KV_BYTES = 128 * DP * 2;            // one K or V tile
-  static constexpr int P_BYTES = 128 * 128 * 2;
-  static constexpr int OFF_K = Q_BYTES;
+  static constexpr int P_BYTES = 128 * 128 * 2;            // one probability tile
+  static constexpr int OFF_K = 2 * Q_BYTES;
   static constexpr int OFF_V = OFF_K + KV_STAGES * KV_BYTES;
   static constexpr int OFF_P = OFF_V + KV_STAGES * KV_BYTES;
-  static constexpr int SMEM_BYTES = OFF_P + 2 * P_BYTES + 1024;
-  static constexpr int THREADS = 192;
-  static constexpr int TMEM_COLS = 512;                    // S: 2 x 128, PV: 2 x DP
+  static constexpr int SMEM_BYTES = OFF_P + 2 * NB * P_BYTES + 1024;
+  static constexpr int THREADS = 384;
+  static constexpr int TMEM_COLS = 512;                    // per query tile: S 128 columns, PV DP columns
   static constexpr uint32_t TM_S = 0, TM_O = 256;
 };
+// setmaxnreg budget: 384 threads x 168 registers at launch; 2 x 128 x 232 + 128 x 40 = 64512.
+constexpr int ATT_REGS_LAUNCH = 168, ATT_REGS_SOFTMAX = 232, ATT_REGS_LOW = 40;
+static_assert(2 * 128 * ATT_REGS_SOFTMAX + 128 * ATT_REGS_LOW <= 384 * ATT_REGS_LAUNCH,
+              "setmaxnreg budget exceeds the CTA's launch allocation");
 
 __device__ __forceinline__ float ex2_approx(float x) {
   float y;
@@ -66,6 +74,29 @@ __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t
   asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
 
+// tcgen05.mma kind::f16 with the two shared-memory descriptors given as (low, high) words.  The high word
+// (stride offset, version, swizzle mode) never changes inside a kernel and the low word is base + constant,
+// so issuing an MMA costs the single thread two integer adds: at N = 64 an MMA runs for only 32 clocks, and a
+// descriptor rebuilt from scratch per MMA (about 20 dependent integer instructions) made the issuing thread,
+// not the tensor core, the bottleneck.
+__device__ __forceinline__ void umma_f16_lohi(uint32_t d_tmem, uint32_t alo, uint32_t ahi, uint32_t blo, uint32_t bhi,
+                                              uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+      "setp.ne.b32 p, %6, 0;\n\t"
+      "mov.b64 da, {%1, %2};\n\t"
+      "mov.b64 db, {%3, %4};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t}"
+      ::"r"(d_tmem), "r"(alo), "r"(ahi), "r"(blo), "r"(bhi), "r"(idesc), "r"(accumulate) : "memory");
+}
+
+// One mbarrier arrival for the whole warp, after every lane has reached this point (each lane has issued its
+// own fence before the call).  128 single arrivals per hand-off serialise on the barrier word.
+__device__ __forceinline__ void warp_arrive(uint32_t bar, int lane) {
+  __syncwarp();
+  if (lane == 0) mbar_arrive(bar);
+}
+
 template <int DP>
 __global__ void __launch_bounds__(AttnCfg<DP>::THREADS, 1)
 attention_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_constant__ CUtensorMap tma_k,
@@ -73,43 +104,54 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
   using C = AttnCfg<DP>;
   constexpr int ST = C::KV_STAGES;
   constexpr int DCH = DP / 64;                             // 64-element chunks of the head dimension
+  constexpr int NB = C::NB;
+  constexpr int P_STRIDE = NB * C::P_BYTES;                // per query tile
+  // DP = 128: the output accumulator takes 128 registers, so the score row is not kept in registers between
+  // the maximum and the exponentials but read from tensor memory twice.
+  constexpr bool TWO_PASS = DP == 128;
 
   extern __shared__ uint8_t smem_dyn[];
   __shared__ __align__(8) uint64_t bar_q;
   __shared__ __align__(8) uint64_t bar_k_full[ST], bar_k_empty[ST], bar_v_full[ST], bar_v_empty[ST];
-  __shared__ __align__(8) uint64_t bar_s_full[2], bar_s_empty[2], bar_p_full[2], bar_p_empty[2];
-  __shared__ __align__(8) uint64_t bar_o_full[2], bar_o_empty[2];
+  // per query tile, one completion per key tile
+  __shared__ __align__(8) uint64_t bar_s_full[2], bar_s_empty[2];
+  __shared__ __align__(8) uint64_t bar_p_full[2][NB], bar_p_empty[2][NB], bar_o_full[2][NB], bar_o_empty[2][NB];
+  __shared__ __align__(8) uint64_t bar_turn[2];           // ping-pong of the two softmax warpgroups' exponential phases
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
 
   const uint32_t smem_base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, wg = warp >> 2;
   volatile int* abortp = &abort_flag;
 
+  const int ntile0 = (((int)(blockIdx.x % g.q_pairs) * 2 + 1) * 128 < g.s1) ? 2 : 1;
   if (threadIdx.x == 0) {
     mbar_init(smem_u32(&bar_q), 1);
     for (int s = 0; s < ST; ++s) {
       mbar_init(smem_u32(&bar_k_full[s]), 1);
       mbar_init(smem_u32(&bar_k_empty[s]), 1);
       mbar_init(smem_u32(&bar_v_full[s]), 1);
-      mbar_init(smem_u32(&bar_v_empty[s]), 1);
+      mbar_init(smem_u32(&bar_v_empty[s]), ntile0);         // released by the PV issuer of every query tile
     }
-    for (int b = 0; b < 2; ++b) {
-      mbar_init(smem_u32(&bar_s_full[b]), 1);
-      mbar_init(smem_u32(&bar_s_empty[b]), 128);
-      mbar_init(smem_u32(&bar_p_full[b]), 128);
-      mbar_init(smem_u32(&bar_p_empty[b]), 1);
-      mbar_init(smem_u32(&bar_o_full[b]), 1);
-      mbar_init(smem_u32(&bar_o_empty[b]), 128);
+    for (int t = 0; t < 2; ++t) {
+      mbar_init(smem_u32(&bar_s_full[t]), 1);
+      mbar_init(smem_u32(&bar_s_empty[t]), 4);              // one arrival per softmax warp
+      for (int b = 0; b < NB; ++b) {
+        mbar_init(smem_u32(&bar_p_full[t][b]), 4);
+        mbar_init(smem_u32(&bar_p_empty[t][b]), 1);
+        mbar_init(smem_u32(&bar_o_full[t][b]), 1);
+        mbar_init(smem_u32(&bar_o_empty[t][b]), 4);
+      }
+      mbar_init(smem_u32(&bar_turn[t]), 4);
     }
     abort_flag = 0;
     fence_mbar_init();
   }
-  if (warp == 5) {
+  if (warp == 9) {
     tmem_alloc(smem_u32(&tmem_slot), C::TMEM_COLS);
     tmem_relinquish();
   }
-  if (warp == 4 && lane == 0) {
+  if (warp == 8 && lane == 0) {
     tma_prefetch_desc(&tma_q);
     tma_prefetch_desc(&tma_k);
     tma_prefetch_desc(&tma_v);
@@ -119,186 +161,270 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
   tc_fence_after();
   const uint32_t tmem_base = tmem_slot;
 
-  // tile -> (batch, head, query tile); query tiles of one head are neighbours so they share K / V in L2
-  const int qt = blockIdx.x % g.q_tiles;
-  const int bh = blockIdx.x / g.q_tiles;
+  // CTA -> (batch, head, pair of query tiles); the pairs of one head are neighbours so they share K / V in L2
+  const int qp = blockIdx.x % g.q_pairs;
+  const int bh = blockIdx.x / g.q_pairs;
   const int ih = bh % g.heads, ib = bh / g.heads;
   const int T = g.kv_tiles;
+  const int ntile = ntile0;                                 // query tiles of this CTA that hold rows
   const int ksteps_qk = (g.d + 15) / 16;                    // k-steps that hold data (the rest of DP is zero fill)
 
-  if (warp == 4) {
-    // ------------------------------------------------------------------ TMA producer
-    if (lane == 0) {
-      const uint32_t bq = smem_u32(&bar_q);
-      mbar_expect_tx(bq, C::Q_BYTES);
-      for (int c = 0; c < DCH; ++c) tma_load_4d(smem_base + c * 16384, &tma_q, bq, c * 64, qt * 128, ih, ib);
-      bool ok = true;
-      for (int j = 0; ok && j < T; ++j) {
-        const int s = j % ST;
-        const uint32_t ph = (j / ST) & 1u;
-        if (!mbar_wait(smem_u32(&bar_k_empty[s]), ph ^ 1u, abortp, g.wait_limit)) { ok = false; break; }
-        const uint32_t fk = smem_u32(&bar_k_full[s]);
-        mbar_expect_tx(fk, C::KV_BYTES);
-        for (int c = 0; c < DCH; ++c)
-          tma_load_4d(smem_base + C::OFF_K + s * C::KV_BYTES + c * 16384, &tma_k, fk, c * 64, j * 128, ih, ib);
-        if (!mbar_wait(smem_u32(&bar_v_empty[s]), ph ^ 1u, abortp, g.wait_limit)) { ok = false; break; }
-        const uint32_t fv = smem_u32(&bar_v_full[s]);
-        mbar_expect_tx(fv, C::KV_BYTES);
-        for (int c = 0; c < DCH; ++c)
-          tma_load_4d(smem_base + C::OFF_V + s * C::KV_BYTES + c * 16384, &tma_v, fv, c * 64, j * 128, ih, ib);
-      }
-    }
-    __syncwarp();
-  } else if (warp == 5) {
-    // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
-      // S = Q K^T: A and B K-major, N = 128.   PV = P V: A K-major, B MN-major (V rows are keys), N = DP.
-      const uint32_t idesc_qk = (1u << 4) | ((uint32_t)(128 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
-      const uint32_t idesc_pv = (1u << 4) | (1u << 16) | ((uint32_t)(DP >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
-      bool ok = mbar_wait(smem_u32(&bar_q), 0, abortp, g.wait_limit);
-      auto issue_qk = [&](int j) -> bool {
-        const int s = j % ST, buf = j & 1;
-        if (!mbar_wait(smem_u32(&bar_k_full[s]), (j / ST) & 1u, abortp, g.wait_limit)) return false;
-        if (!mbar_wait(smem_u32(&bar_s_empty[buf]), ((j >> 1) & 1u) ^ 1u, abortp, g.wait_limit)) return false;
-        tc_fence_after();
-        const uint32_t qb = smem_base, kb = smem_base + C::OFF_K + s * C::KV_BYTES;
-        for (int ks = 0; ks < ksteps_qk; ++ks) {
-          const uint32_t off = (ks >> 2) * 16384 + (ks & 3) * 32;
-          umma<2>(tmem_base + C::TM_S + buf * 128, make_smem_desc(qb + off, 16, 1024, 2),
-                  make_smem_desc(kb + off, 16, 1024, 2), idesc_qk, ks > 0 ? 1u : 0u);
+  if (wg == 2) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+    if (warp == 8) {
+      // ---------------------------------------------------------------- TMA producer
+      if (lane == 0) {
+        const uint32_t bq = smem_u32(&bar_q);
+        mbar_expect_tx(bq, ntile * C::Q_BYTES);
+        for (int t = 0; t < ntile; ++t)
+          for (int c = 0; c < DCH; ++c)
+            tma_load_4d(smem_base + t * C::Q_BYTES + c * 16384, &tma_q, bq, c * 64, (qp * 2 + t) * 128, ih, ib);
+        bool ok = true;
+        for (int j = 0; ok && j < T; ++j) {
+          const int s = j % ST;
+          const uint32_t ph = (j / ST) & 1u;
+          if (!mbar_wait(smem_u32(&bar_k_empty[s]), ph ^ 1u, abortp, g.wait_limit)) { ok = false; break; }
+          const uint32_t fk = smem_u32(&bar_k_full[s]);
+          mbar_expect_tx(fk, C::KV_BYTES);
+          for (int c = 0; c < DCH; ++c)
+            tma_load_4d(smem_base + C::OFF_K + s * C::KV_BYTES + c * 16384, &tma_k, fk, c * 64, j * 128, ih, ib);
+          if (!mbar_wait(smem_u32(&bar_v_empty[s]), ph ^ 1u, abortp, g.wait_limit)) { ok = false; break; }
+          const uint32_t fv = smem_u32(&bar_v_full[s]);
+          mbar_expect_tx(fv, C::KV_BYTES);
+          for (int c = 0; c < DCH; ++c)
+            tma_load_4d(smem_base + C::OFF_V + s * C::KV_BYTES + c * 16384, &tma_v, fv, c * 64, j * 128, ih, ib);
         }
-        umma_commit(smem_u32(&bar_k_empty[s]));
-        umma_commit(smem_u32(&bar_s_full[buf]));
+      }
+      __syncwarp();
+    } else {
+      // ---------------------------------------------------------------- MMA issuers
+      // Three single-thread issuers: warp 9 issues every S = Q K^T, warps 10 and 11 issue PV for query tile 0
+      // and 1.  One thread doing all of it was the kernel's critical path: each wait, descriptor update and
+      // commit is a short dependent instruction chain that competes with the softmax warps for issue slots.
+      if (lane == 0) {
+        // descriptor words: low = (address >> 4) | (leading offset >> 4) << 16, high = (stride offset >> 4) | version | swizzle
+        const uint64_t dk = make_smem_desc(smem_base, 16, 1024, 2);             // K-major tiles (Q, K, P)
+        const uint64_t dv = make_smem_desc(smem_base, 16384, 1024, 2);          // MN-major tile (V)
+        const uint32_t hi_k = (uint32_t)(dk >> 32), hi_v = (uint32_t)(dv >> 32);
+        if (warp == 9) {
+          // S = Q K^T: A and B K-major, N = 128
+          const uint32_t idesc_qk = (1u << 4) | ((uint32_t)(128 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+          const uint32_t q_lo = (uint32_t)dk, k_lo = (uint32_t)dk + (uint32_t)(C::OFF_K >> 4);
+          bool ok = mbar_wait(smem_u32(&bar_q), 0, abortp, g.wait_limit);
+          // S_t(j): needs K_j and, for j > 0, the softmax warps of tile t to have read S_t(j-1)
+          for (int j = 0; ok && j < T; ++j) {
+            const int s = j % ST;
+            if (!mbar_wait(smem_u32(&bar_k_full[s]), (j / ST) & 1u, abortp, g.wait_limit)) break;
+            const uint32_t klo = k_lo + (uint32_t)(s * (C::KV_BYTES >> 4));
+            for (int t = 0; t < ntile; ++t) {
+              if (j > 0 && !mbar_wait(smem_u32(&bar_s_empty[t]), (uint32_t)(j - 1) & 1u, abortp, g.wait_limit)) { ok = false; break; }
+              tc_fence_after();
+              const uint32_t alo = q_lo + (uint32_t)(t * C::Q_BYTES >> 4);
+              if (ksteps_qk == DP / 16) {
+#pragma unroll
+                for (int ks = 0; ks < DP / 16; ++ks) {
+                  const uint32_t off = (uint32_t)(((ks >> 2) * 16384 + (ks & 3) * 32) >> 4);
+                  umma_f16_lohi(tmem_base + C::TM_S + t * 128, alo + off, hi_k, klo + off, hi_k, idesc_qk, ks > 0 ? 1u : 0u);
+                }
+              } else {
+                for (int ks = 0; ks < ksteps_qk; ++ks) {
+                  const uint32_t off = (uint32_t)(((ks >> 2) * 16384 + (ks & 3) * 32) >> 4);
+                  umma_f16_lohi(tmem_base + C::TM_S + t * 128, alo + off, hi_k, klo + off, hi_k, idesc_qk, ks > 0 ? 1u : 0u);
+                }
+              }
+              umma_commit(smem_u32(&bar_s_full[t]));
+            }
+            if (ok) umma_commit(smem_u32(&bar_k_empty[s]));
+          }
+        } else if (warp - 10 < ntile) {
+          // PV = P V: A K-major, B MN-major (V rows are keys), N = DP
+          const int t = warp - 10;
+          const uint32_t idesc_pv = (1u << 4) | (1u << 16) | ((uint32_t)(DP >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+          const uint32_t p_lo = (uint32_t)dk + (uint32_t)((C::OFF_P + t * P_STRIDE) >> 4);
+          const uint32_t v_lo = (uint32_t)dv + (uint32_t)(C::OFF_V >> 4);
+          for (int j = 0; j < T; ++j) {
+            const int s = j % ST;
+            // PV_t(j): needs V_j, P_t(j) and the softmax warps to have taken PV_t(j-1) out of tensor memory
+            if (!mbar_wait(smem_u32(&bar_v_full[s]), (j / ST) & 1u, abortp, g.wait_limit)) break;
+            const int b = j % NB;
+            const uint32_t bph = (uint32_t)(j / NB) & 1u;
+            if (j >= NB && !mbar_wait(smem_u32(&bar_o_empty[t][b]), bph ^ 1u, abortp, g.wait_limit)) break;
+            if (!mbar_wait(smem_u32(&bar_p_full[t][b]), bph, abortp, g.wait_limit)) break;
+            const uint32_t plo = p_lo + (uint32_t)(b * (C::P_BYTES >> 4));
+            tc_fence_after();
+            const uint32_t vlo = v_lo + (uint32_t)(s * (C::KV_BYTES >> 4));
+#pragma unroll
+            for (int ks = 0; ks < 8; ++ks)                    // 128 keys, 16 per MMA
+              umma_f16_lohi(tmem_base + C::TM_O + (t * NB + b) * DP, plo + (uint32_t)(((ks >> 2) * 16384 + (ks & 3) * 32) >> 4), hi_k,
+                            vlo + (uint32_t)(ks * 2048 >> 4), hi_v, idesc_pv, ks > 0 ? 1u : 0u);
+            umma_commit(smem_u32(&bar_p_empty[t][b]));
+            umma_commit(smem_u32(&bar_o_full[t][b]));
+            umma_commit(smem_u32(&bar_v_empty[s]));           // one arrival per query tile
+          }
+        }
+      }
+      __syncwarp();
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax / output (warpgroups 0, 1)
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
+    const int t = wg;                                        // query tile of this warpgroup
+    if (t < ntile) {
+      const int r = (warp & 3) * 32 + lane;                  // query row inside the tile = TMEM lane
+      const uint32_t lane_addr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
+      const uint32_t p_row = (uint32_t)(r >> 3) * 1024 + (uint32_t)(r & 7) * 128;
+      const uint32_t sw = (uint32_t)(r & 7);
+      const uint32_t pb0 = smem_base + C::OFF_P + t * P_STRIDE + p_row;
+      const float scale = g.scale_log2;
+      const bool pos = scale >= 0.f;
+      float acc[DP];
+#pragma unroll
+      for (int q = 0; q < DP; ++q) acc[q] = 0.f;
+      float m = -INFINITY, l = 0.f;                          // m in the scaled base-2 domain
+      bool ok = true;
+
+      float corr = 1.f;                                      // factor that moves acc to the current maximum
+      auto add_pv = [&](int j) -> bool {                     // acc = acc * corr + PV_t(j)
+        const int b = j % NB;
+        if (!mbar_wait(smem_u32(&bar_o_full[t][b]), (uint32_t)(j / NB) & 1u, abortp, g.wait_limit)) return false;
+        tc_fence_after();
+#pragma unroll
+        for (int c = 0; c < DP / 32; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32(lane_addr + C::TM_O + (t * NB + b) * DP + c * 32, v);
+          tmem_wait_ld();
+#pragma unroll
+          for (int q = 0; q < 32; ++q) acc[c * 32 + q] = fmaf(acc[c * 32 + q], corr, __uint_as_float(v[q]));
+        }
+        tc_fence_before();
+        warp_arrive(smem_u32(&bar_o_empty[t][b]), lane);
         return true;
       };
-      if (ok) ok = issue_qk(0);
-      for (int j = 0; ok && j < T; ++j) {
-        if (j + 1 < T && !issue_qk(j + 1)) { ok = false; break; }
-        const int s = j % ST, buf = j & 1;
-        const uint32_t ph2 = (j >> 1) & 1u;
-        if (!mbar_wait(smem_u32(&bar_v_full[s]), (j / ST) & 1u, abortp, g.wait_limit)) { ok = false; break; }
-        if (!mbar_wait(smem_u32(&bar_o_empty[buf]), ph2 ^ 1u, abortp, g.wait_limit)) { ok = false; break; }
-        if (!mbar_wait(smem_u32(&bar_p_full[buf]), ph2, abortp, g.wait_limit)) { ok = false; break; }
+
+      for (int j = 0; j < T; ++j) {
+        if (!mbar_wait(smem_u32(&bar_s_full[t]), (uint32_t)j & 1u, abortp, g.wait_limit)) { ok = false; break; }
         tc_fence_after();
-        const uint32_t pb = smem_base + C::OFF_P + buf * C::P_BYTES, vb = smem_base + C::OFF_V + s * C::KV_BYTES;
+        const int valid = g.s2 - j * 128;                    // keys of this tile that exist
+        const float gone = pos ? -INFINITY : INFINITY;       // a masked score: scaled it is -inf, probability 0
+        constexpr int KEEP = TWO_PASS ? 32 : 128;
+        uint32_t xr[KEEP];                                   // raw scores of this row (f32 bits)
+        float ext;
+        const uint32_t s_addr = lane_addr + C::TM_S + t * 128;
+        if constexpr (!TWO_PASS) {
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {                    // 128 keys, 16 per MMA
-          const uint64_t ad = make_smem_desc(pb + (ks >> 2) * 16384 + (ks & 3) * 32, 16, 1024, 2);
-          const uint64_t bd = make_smem_desc(vb + ks * 2048, 16384, 1024, 2);
-          umma<2>(tmem_base + C::TM_O + buf * DP, ad, bd, idesc_pv, ks > 0 ? 1u : 0u);
+          for (int c = 0; c < 4; ++c) tmem_ld_32x32(s_addr + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&xr[c * 32]));
+          tmem_wait_ld();
+          tc_fence_before();
+          warp_arrive(smem_u32(&bar_s_empty[t]), lane);
+          if (valid < 128) {
+#pragma unroll
+            for (int q = 0; q < 128; ++q)
+              if (q >= valid) xr[q] = __float_as_uint(gone);
+          }
+          float e4[4] = {gone, gone, gone, gone};            // four independent chains
+          if (pos) {
+#pragma unroll
+            for (int q = 0; q < 128; ++q) e4[q & 3] = fmaxf(e4[q & 3], __uint_as_float(xr[q]));
+            ext = fmaxf(fmaxf(e4[0], e4[1]), fmaxf(e4[2], e4[3]));
+          } else {
+#pragma unroll
+            for (int q = 0; q < 128; ++q) e4[q & 3] = fminf(e4[q & 3], __uint_as_float(xr[q]));
+            ext = fminf(fminf(e4[0], e4[1]), fminf(e4[2], e4[3]));
+          }
+        } else {
+          float e4[4] = {gone, gone, gone, gone};
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            tmem_ld_32x32(s_addr + c * 32, xr);
+            tmem_wait_ld();
+#pragma unroll
+            for (int q = 0; q < 32; ++q) {
+              float sv = __uint_as_float(xr[q]);
+              if (c * 32 + q >= valid) sv = gone;
+              e4[q & 3] = pos ? fmaxf(e4[q & 3], sv) : fminf(e4[q & 3], sv);
+            }
+          }
+          ext = pos ? fmaxf(fmaxf(e4[0], e4[1]), fmaxf(e4[2], e4[3])) : fminf(fminf(e4[0], e4[1]), fminf(e4[2], e4[3]));
         }
-        umma_commit(smem_u32(&bar_v_empty[s]));
-        umma_commit(smem_u32(&bar_p_empty[buf]));
-        umma_commit(smem_u32(&bar_o_full[buf]));
-      }
-    }
-    __syncwarp();
-  } else {
-    // ------------------------------------------------------------------ softmax / output (warps 0..3)
-    const int r = warp * 32 + lane;                          // query row inside the tile = TMEM lane
-    const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
-    const uint32_t p_row = (uint32_t)(r >> 3) * 1024 + (uint32_t)(r & 7) * 128;
-    const uint32_t sw = (uint32_t)(r & 7);
-    float acc[DP];
-#pragma unroll
-    for (int q = 0; q < DP; ++q) acc[q] = 0.f;
-    float m = -INFINITY, l = 0.f;
-    bool ok = true;
-
-    auto add_pv = [&](int j) -> bool {                       // acc += PV_j
-      const int buf = j & 1;
-      if (!mbar_wait(smem_u32(&bar_o_full[buf]), (j >> 1) & 1u, abortp, g.wait_limit)) return false;
-      tc_fence_after();
-#pragma unroll
-      for (int c = 0; c < DP / 32; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32(lane_addr + C::TM_O + buf * DP + c * 32, v);
-        tmem_wait_ld();
-#pragma unroll
-        for (int q = 0; q < 32; ++q) acc[c * 32 + q] += __uint_as_float(v[q]);
-      }
-      tc_fence_before();
-      mbar_arrive(smem_u32(&bar_o_empty[buf]));
-      return true;
-    };
-
-    for (int j = 0; j < T; ++j) {
-      const int buf = j & 1;
-      const uint32_t ph2 = (j >> 1) & 1u;
-      if (!mbar_wait(smem_u32(&bar_s_full[buf]), ph2, abortp, g.wait_limit)) { ok = false; break; }
-      tc_fence_after();
-      float x[128];
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32(lane_addr + C::TM_S + buf * 128 + c * 32, v);
-        tmem_wait_ld();
-#pragma unroll
-        for (int q = 0; q < 32; ++q) x[c * 32 + q] = __uint_as_float(v[q]) * g.scale_log2;
-      }
-      tc_fence_before();
-      mbar_arrive(smem_u32(&bar_s_empty[buf]));
-      const int valid = g.s2 - j * 128;                      // keys of this tile that exist
-      if (valid < 128) {
-#pragma unroll
-        for (int q = 0; q < 128; ++q)
-          if (q >= valid) x[q] = -INFINITY;
-      }
-      float mx = x[0];
-#pragma unroll
-      for (int q = 1; q < 128; ++q) mx = fmaxf(mx, x[q]);
-      const float m_new = fmaxf(m, mx);
-      // the P buffer is free once PV_{j-2} has been read by the tensor core
-      if (!mbar_wait(smem_u32(&bar_p_empty[buf]), ph2 ^ 1u, abortp, g.wait_limit)) { ok = false; break; }
-      const uint32_t pb = smem_base + C::OFF_P + buf * C::P_BYTES + p_row;
-      float sum = 0.f;
-#pragma unroll
-      for (int c = 0; c < 16; ++c) {                         // 16-byte chunks of 8 probabilities
-        float p[8];
-#pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          p[e] = ex2_approx(x[c * 8 + e] - m_new);
-          sum += p[e];
+        const float m_new = fmaxf(m, ext * scale);
+        const float corr_new = ex2_approx(m - m_new);        // first tile: exp2(-inf) = 0, acc and l are 0
+        // the P tile is free once PV(j-1) has been read by the tensor core
+        const int pbuf = j % NB;
+        if (j >= NB && !mbar_wait(smem_u32(&bar_p_empty[t][pbuf]), ((uint32_t)(j / NB) & 1u) ^ 1u, abortp, g.wait_limit)) { ok = false; break; }
+        const uint32_t pb = pb0 + pbuf * C::P_BYTES;
+        // (With single P / PV buffers, DP = 128, the turns would add to the tensor-core round trip instead.)
+        // The two warpgroups take turns in the exponential phase: it saturates the SFU pipe, and in lockstep that
+        // pipe would idle while both read scores / fold PV in.  Tile 0 goes first; tile 1 follows in the same j.
+        if (NB == 2 && ntile == 2) {
+          const bool go = t == 0 ? (j == 0 || mbar_wait(smem_u32(&bar_turn[1]), (uint32_t)(j - 1) & 1u, abortp, g.wait_limit))
+                                 : mbar_wait(smem_u32(&bar_turn[0]), (uint32_t)j & 1u, abortp, g.wait_limit);
+          if (!go) { ok = false; break; }
         }
-        st_shared_v4(pb + (uint32_t)(c >> 3) * 16384 + ((((uint32_t)c & 7u) ^ sw) << 4),
-                     pack_half2(p[0], p[1]), pack_half2(p[2], p[3]), pack_half2(p[4], p[5]), pack_half2(p[6], p[7]));
-      }
-      fence_proxy_async_smem();                              // generic-proxy writes -> visible to the MMA
-      mbar_arrive(smem_u32(&bar_p_full[buf]));
-      // fold the previous tile's product in and move everything to the new maximum
-      if (j > 0 && !add_pv(j - 1)) { ok = false; break; }
-      const float corr = ex2_approx(m - m_new);              // first tile: exp2(-inf) = 0, acc and l are 0
-      l = l * corr + sum;
-      if (corr != 1.f) {
+        float s4[4] = {0.f, 0.f, 0.f, 0.f};
+        const float nm = -m_new;
 #pragma unroll
-        for (int q = 0; q < DP; ++q) acc[q] *= corr;
-      }
-      m = m_new;
-    }
-    if (ok && T > 0) ok = add_pv(T - 1);
-    const int row = qt * 128 + r;
-    if (ok && row < g.s1) {
-      const float inv = 1.f / l;
-      __half* dst = g.out + ib * g.o_b + ih * g.o_h + (long long)row * g.o_s;
+        for (int c4 = 0; c4 < 4; ++c4) {                     // 32 scores at a time
+          if constexpr (TWO_PASS) {
+            tmem_ld_32x32(s_addr + c4 * 32, xr);
+            tmem_wait_ld();
+            if (valid < 128) {
 #pragma unroll
-      for (int c = 0; c < DP / 8; ++c) {
-        if (c * 8 < g.d) {                                   // d is a multiple of 8
-          uint4 o;
-          o.x = pack_half2(acc[c * 8 + 0] * inv, acc[c * 8 + 1] * inv);
-          o.y = pack_half2(acc[c * 8 + 2] * inv, acc[c * 8 + 3] * inv);
-          o.z = pack_half2(acc[c * 8 + 4] * inv, acc[c * 8 + 5] * inv);
-          o.w = pack_half2(acc[c * 8 + 6] * inv, acc[c * 8 + 7] * inv);
-          *reinterpret_cast<uint4*>(dst + c * 8) = o;
+              for (int q = 0; q < 32; ++q)
+                if (c4 * 32 + q >= valid) xr[q] = __float_as_uint(gone);
+            }
+          }
+#pragma unroll
+          for (int cc = 0; cc < 4; ++cc) {                   // 16-byte chunks of 8 probabilities
+            const int c = c4 * 4 + cc;
+            float p[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+              p[e] = ex2_approx(fmaf(__uint_as_float(xr[(TWO_PASS ? cc * 8 : c * 8) + e]), scale, nm));
+              s4[e & 3] += p[e];
+            }
+            st_shared_v4(pb + (uint32_t)(c >> 3) * 16384 + ((((uint32_t)c & 7u) ^ sw) << 4),
+                         pack_half2(p[0], p[1]), pack_half2(p[2], p[3]), pack_half2(p[4], p[5]), pack_half2(p[6], p[7]));
+          }
         }
+        if (TWO_PASS) {
+          tc_fence_before();
+          warp_arrive(smem_u32(&bar_s_empty[t]), lane);
+        }
+        fence_proxy_async_smem();                            // generic-proxy writes -> visible to the MMA
+        warp_arrive(smem_u32(&bar_p_full[t][pbuf]), lane);
+        if (NB == 2 && ntile == 2) warp_arrive(smem_u32(&bar_turn[t]), lane);
+        l = l * corr_new + ((s4[0] + s4[1]) + (s4[2] + s4[3]));
+        m = m_new;
+        // PV(j-1) was issued a whole iteration ago: taking it out here (rather than before the exponentials)
+        // keeps the tensor core's latency off this warpgroup's critical path
+        if (j > 0 && !add_pv(j - 1)) { ok = false; break; }
+        corr = corr_new;
       }
-      if (g.lse) g.lse[((long long)ib * g.heads + ih) * g.s1 + row] = (m + log2f(l)) * 0.6931471805599453f;
+      if (ok && T > 0) ok = add_pv(T - 1);
+      const int row = (qp * 2 + t) * 128 + r;
+      if (ok && row < g.s1) {
+        const float inv = 1.f / l;
+        __half* dst = g.out + ib * g.o_b + ih * g.o_h + (long long)row * g.o_s;
+#pragma unroll
+        for (int c = 0; c < DP / 8; ++c) {
+          if (c * 8 < g.d) {                                 // d is a multiple of 8
+            uint4 o;
+            o.x = pack_half2(acc[c * 8 + 0] * inv, acc[c * 8 + 1] * inv);
+            o.y = pack_half2(acc[c * 8 + 2] * inv, acc[c * 8 + 3] * inv);
+            o.z = pack_half2(acc[c * 8 + 4] * inv, acc[c * 8 + 5] * inv);
+            o.w = pack_half2(acc[c * 8 + 6] * inv, acc[c * 8 + 7] * inv);
+            *reinterpret_cast<uint4*>(dst + c * 8) = o;
+          }
+        }
+        if (g.lse) g.lse[((long long)ib * g.heads + ih) * g.s1 + row] = (m + log2f(l)) * 0.6931471805599453f;
+      }
     }
   }
 
   tc_fence_before();
   __syncthreads();
   teardown(abort_flag, g.status);
-  if (warp == 5) {
+  if (warp == 9) {
     tc_fence_after();
     tmem_dealloc(tmem_base, C::TMEM_COLS);
   }
@@ -379,7 +505,7 @@ int attention_forward(int dtype, int64_t B, int64_t H, int64_t s1, int64_t s2, i
     return B200_ERR_UNSUPPORTED;
   if (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)out) & 15) return B200_ERR_UNSUPPORTED;
   if (s1 > 0x7fffff00LL || s2 > 0x7fffff00LL || B * H > 0x7fffffffLL) return B200_ERR_LIMIT;
-  const int64_t q_tiles = (s1 + 127) / 128, ctas = q_tiles * H * B;
+  const int64_t q_pairs = (s1 + 255) / 256, ctas = q_pairs * H * B;
   if (ctas > 0x7fffffffLL) return B200_ERR_LIMIT;
 
   alignas(64) CUtensorMap mq, mk, mv;
@@ -389,8 +515,9 @@ int attention_forward(int dtype, int64_t B, int64_t H, int64_t s1, int64_t s2, i
   if ((rc = encode_bhsd(&mv, v, d, s2, H, B, vs[2], vs[1], vs[0], 128))) return rc;
   AttnArgs g;
   g.s1 = (int)s1; g.s2 = (int)s2; g.d = (int)d;
-  g.heads = (int)H; g.q_tiles = (int)q_tiles; g.kv_tiles = (int)((s2 + 127) / 128);
+  g.heads = (int)H; g.q_pairs = (int)q_pairs; g.kv_tiles = (int)((s2 + 127) / 128);
   g.scale_log2 = (float)(alpha * 1.4426950408889634);
+  if (g.scale_log2 == 0.f) g.scale_log2 = 1e-30f;           // keeps (masked score = -inf) * scale = -inf
   g.out = (__half*)out; g.o_b = os[0]; g.o_h = os[1]; g.o_s = os[2];
   g.lse = lse;
   g.wait_limit = 400000000LL + (long long)g.kv_tiles * 400000LL;

@@ -128,7 +128,14 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
                              ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
       const uint32_t a_lbo = g.a_mn ? C::MN_LBO : 16u, b_lbo = g.b_mn ? C::MN_LBO : 16u;
       const uint32_t a_kadv = g.a_mn ? C::MN_KADV : C::K_KADV, b_kadv = g.b_mn ? C::MN_KADV : C::K_KADV;
-      uint32_t it = 0, tcount = 0;
+      // descriptor words of stage 0 (see umma_lohi): per stage and per k-step only the low word moves
+      const uint64_t da0 = make_smem_desc(smem_base, a_lbo, C::SBO, C::LAYOUT);
+      const uint64_t db0 = make_smem_desc(smem_base + C::A_BYTES, b_lbo, C::SBO, C::LAYOUT);
+      const uint32_t a_hi = (uint32_t)(da0 >> 32), b_hi = (uint32_t)(db0 >> 32);
+      const uint32_t a_lo0 = (uint32_t)da0, b_lo0 = (uint32_t)db0;
+      const uint32_t a_k16 = a_kadv >> 4, b_k16 = b_kadv >> 4;
+      constexpr uint32_t STAGE16 = C::STAGE_BYTES >> 4;
+      uint32_t ring_s = 0, ring_ph = 0, tcount = 0;        // stage ring position and its phase bit
       bool ok = true;
       for (long long unit = blockIdx.x; ok && unit < g.total_units; unit += gridDim.x, ++tcount) {
         const Unit un = decode_unit(g, unit, total_kb);
@@ -136,19 +143,16 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
         if (!mbar_wait(smem_u32(&bar_tempty[buf]), tph ^ 1u, abortp, g.wait_limit)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + buf * BN;
-        for (int i = un.kb_lo; i < un.kb_hi; ++i, ++it) {
-          const int s = it % STAGES;
-          const uint32_t ph = (it / STAGES) & 1u;
+        for (int i = un.kb_lo; i < un.kb_hi; ++i) {
+          const uint32_t s = ring_s, ph = ring_ph;
+          if (++ring_s == (uint32_t)STAGES) { ring_s = 0; ring_ph ^= 1u; }
           if (!mbar_wait(smem_u32(&bar_full[s]), ph, abortp, g.wait_limit)) { ok = false; break; }
           tc_fence_after();
-          const uint32_t a_base = smem_base + s * C::STAGE_BYTES;
-          const uint32_t b_base = a_base + C::A_BYTES;
+          const uint32_t a_lo = a_lo0 + (uint32_t)s * STAGE16, b_lo = b_lo0 + (uint32_t)s * STAGE16;
 #pragma unroll
           for (int ks = 0; ks < C::KSTEPS; ++ks) {
-            const uint64_t ad = make_smem_desc(a_base + ks * a_kadv, a_lbo, C::SBO, C::LAYOUT);
-            const uint64_t bd = make_smem_desc(b_base + ks * b_kadv, b_lbo, C::SBO, C::LAYOUT);
             if ((g.xform_mode & 4) && ks > 0) continue;               // timing experiment: 1 MMA of 4
-            umma<2>(d_tmem, ad, bd, idesc, (i > un.kb_lo || ks > 0) ? 1u : 0u);
+            umma_lohi<2>(d_tmem, a_lo + ks * a_k16, a_hi, b_lo + ks * b_k16, b_hi, idesc, (i > un.kb_lo || ks > 0) ? 1u : 0u);
           }
           umma_commit(smem_u32(&bar_empty[s]));       // stage reusable once these MMAs retire
         }
@@ -360,7 +364,14 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_const
       const uint32_t a_sbo = g.a_mn ? C::MN_SBO : C::K_SBO, b_sbo = g.b_mn ? C::MN_SBO : C::K_SBO;
       const uint32_t a_lay = g.a_mn ? C::MN_LAYOUT : C::K_LAYOUT, b_lay = g.b_mn ? C::MN_LAYOUT : C::K_LAYOUT;
       const uint32_t a_kadv = g.a_mn ? C::MN_KADV : C::K_KADV, b_kadv = g.b_mn ? C::MN_KADV : C::K_KADV;
-      uint32_t it = 0, ccount = 0;
+      // descriptor words of stage 0 (see umma_lohi): per stage, per operand copy and per k-step only the low word moves
+      const uint64_t da0 = make_smem_desc(smem_base, a_lbo, a_sbo, a_lay);
+      const uint64_t db0 = make_smem_desc(smem_base + C::A_BYTES, b_lbo, b_sbo, b_lay);
+      const uint32_t a_hi = (uint32_t)(da0 >> 32), b_hi = (uint32_t)(db0 >> 32);
+      const uint32_t a_lo0 = (uint32_t)da0, b_lo0 = (uint32_t)db0;
+      const uint32_t a_k16 = a_kadv >> 4, b_k16 = b_kadv >> 4;
+      constexpr uint32_t STAGE16 = C::STAGE_BYTES >> 4, SMALL16 = C::RAW_BYTES >> 4;
+      uint32_t ring_s = 0, ring_ph = 0, ccount = 0;        // stage ring position and its phase bit
       bool ok = true;
       for (long long unit = blockIdx.x; ok && unit < g.total_units; unit += gridDim.x) {
         const Unit un = decode_unit(g, unit, total_kb);
@@ -370,26 +381,22 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_const
           tc_fence_after();
           const uint32_t d_tmem = tmem_base + buf * BN;
           const int nkb = (un.kb_hi - kb0) < C::CHUNK_KB ? (un.kb_hi - kb0) : C::CHUNK_KB;
-          for (int i = 0; i < nkb; ++i, ++it) {
-            const int s = it % STAGES;
-            const uint32_t ph = (it / STAGES) & 1u;
+          for (int i = 0; i < nkb; ++i) {
+            const uint32_t s = ring_s, ph = ring_ph;
+            if (++ring_s == (uint32_t)STAGES) { ring_s = 0; ring_ph ^= 1u; }
             if (!mbar_wait(smem_u32(&bar_xform[s]), ph, abortp, g.wait_limit)) { ok = false; break; }
             tc_fence_after();
-            const uint32_t a_base = smem_base + s * C::STAGE_BYTES;
-            const uint32_t b_base = a_base + C::A_BYTES;
+            const uint32_t a_lo = a_lo0 + (uint32_t)s * STAGE16, b_lo = b_lo0 + (uint32_t)s * STAGE16;
 #pragma unroll
             for (int ks = 0; ks < C::KSTEPS; ++ks) {
-              const uint64_t ad = make_smem_desc(a_base + ks * a_kadv, a_lbo, a_sbo, a_lay);
-              const uint64_t bd = make_smem_desc(b_base + ks * b_kadv, b_lbo, b_sbo, b_lay);
-              const uint64_t ads = make_smem_desc(a_base + C::RAW_BYTES + ks * a_kadv, a_lbo, a_sbo, a_lay);
-              const uint64_t bds = make_smem_desc(b_base + C::RAW_BYTES + ks * b_kadv, b_lbo, b_sbo, b_lay);
+              const uint32_t al = a_lo + ks * a_k16, bl = b_lo + ks * b_k16;
               if (g.xform_mode & 4) {                                         // bit 2: timing experiment
-                umma<4>(d_tmem, ad, bd, idesc, (i > 0 || ks > 0) ? 1u : 0u);
+                umma_lohi<4>(d_tmem, al, a_hi, bl, b_hi, idesc, (i > 0 || ks > 0) ? 1u : 0u);
                 continue;
               }
-              umma<4>(d_tmem, ads, bd, idesc, (i > 0 || ks > 0) ? 1u : 0u);   // small * big
-              umma<4>(d_tmem, ad, bds, idesc, 1u);                            // big * small
-              umma<4>(d_tmem, ad, bd, idesc, 1u);                             // big * big
+              umma_lohi<4>(d_tmem, al + SMALL16, a_hi, bl, b_hi, idesc, (i > 0 || ks > 0) ? 1u : 0u);   // small * big
+              umma_lohi<4>(d_tmem, al, a_hi, bl + SMALL16, b_hi, idesc, 1u);                            // big * small
+              umma_lohi<4>(d_tmem, al, a_hi, bl, b_hi, idesc, 1u);                                      // big * big
             }
             umma_commit(smem_u32(&bar_empty[s]));
           }
