@@ -67,6 +67,9 @@ SIGNATURES = {
     "b200_linear_forward": (_i, [_i, _sz, _sz, _sz, _sz, _vp, _szp, _vp, _szp, _vp, _i, _vp, _vp]),
     "b200_matmat_batch4_forward_scaled": (_i, [_i, _sz, _sz, _sz, _sz, _sz, _vp, _szp, _vp, _szp, _d, _vp, _vp]),
     "b200_attention_forward": (_i, [_i, _sz, _sz, _sz, _sz, _sz, _vp, _szp, _vp, _szp, _vp, _szp, _d, _vp, _szp, _vp, _vp]),
+    "b200_attention_backward_workspace_bytes": (_sz, [_sz, _sz, _sz]),
+    "b200_attention_backward": (_i, [_i, _sz, _sz, _sz, _sz, _sz, _vp, _szp, _vp, _szp, _vp, _szp, _d, _vp, _szp, _vp,
+                                     _vp, _szp, _vp, _szp, _vp, _szp, _vp, _szp, _i, _vp, _sz, _vp]),
     "b200_conv2d_workspace_bytes": (_sz, [_i, C.POINTER(Conv2DOp), _i]),
     "b200_conv2d_forward": (_i, [_i, C.POINTER(Conv2DOp), _vp, _szp, _vp, _vp, _vp, _sz, _vp]),
     "b200_conv2d_backward": (_i, [_i, C.POINTER(Conv2DOp), _vp, _vp, _vp, _szp, _vp, _vp, _vp, _sz, _vp, _vp]),

@@ -114,6 +114,7 @@ int b200_init(int ordinal) {
   if ((rc = note_cuda_error(cudaEventCreateWithFlags(&d.split_event, cudaEventDisableTiming), "cudaEventCreate"))) return rc;
   if ((rc = tc_setup_device())) return rc;
   if ((rc = attention_setup_device())) return rc;
+  if ((rc = attention_bwd_setup_device())) return rc;
   d.ready = true;
   return B200_OK;
 }
@@ -382,6 +383,28 @@ int b200_attention_forward(int dtype, size_t batch, size_t heads, size_t s1, siz
   for (int i = 0; i < 4; ++i) { q4[i] = (int64_t)qs[i]; k4[i] = (int64_t)ks[i]; v4[i] = (int64_t)vs[i]; o4[i] = (int64_t)os[i]; }
   return attention_forward(dtype, (int64_t)batch, (int64_t)heads, (int64_t)s1, (int64_t)s2, (int64_t)d, q, q4, k, k4, v,
                            v4, alpha, out, o4, lse, (cudaStream_t)stream);
+}
+
+size_t b200_attention_backward_workspace_bytes(size_t batch, size_t heads, size_t s1) {
+  return attention_backward_workspace_bytes((int64_t)batch, (int64_t)heads, (int64_t)s1);
+}
+
+int b200_attention_backward(int dtype, size_t batch, size_t heads, size_t s1, size_t s2, size_t d, const void* q,
+                            const size_t qs[4], const void* k, const size_t ks[4], const void* v, const size_t vs[4],
+                            double alpha, const void* out, const size_t os[4], const float* lse, const void* grad_out,
+                            const size_t gs[4], void* grad_q, const size_t gqs[4], void* grad_k, const size_t gks[4],
+                            void* grad_v, const size_t gvs[4], int accumulate, void* workspace, size_t workspace_bytes,
+                            void* stream) {
+  if (!valid_dtype(dtype)) return B200_ERR_DTYPE;
+  if (!qs || !ks || !vs || !os || !gs || !gqs || !gks || !gvs) return B200_ERR_NULL;
+  if (batch && heads && s1 && s2 && d && (!q || !k || !v || !out || !lse || !grad_out || !workspace)) return B200_ERR_NULL;
+  int64_t a[8][4];
+  const size_t* src[8] = {qs, ks, vs, os, gs, gqs, gks, gvs};
+  for (int t = 0; t < 8; ++t)
+    for (int i = 0; i < 4; ++i) a[t][i] = (int64_t)src[t][i];
+  return attention_backward(dtype, (int64_t)batch, (int64_t)heads, (int64_t)s1, (int64_t)s2, (int64_t)d, q, a[0], k, a[1], v,
+                            a[2], alpha, out, a[3], lse, grad_out, a[4], grad_q, a[5], grad_k, a[6], grad_v, a[7],
+                            accumulate, workspace, workspace_bytes, (cudaStream_t)stream);
 }
 
 int b200_matmat_batch4_forward(int dtype, size_t batch, size_t seq, size_t m, size_t k, size_t n,

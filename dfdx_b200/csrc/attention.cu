@@ -21,14 +21,14 @@
 //   Registers are moved from warpgroup 2 to the softmax warpgroups with setmaxnreg.
 // Every wait is bounded; on expiry the CTA raises its abort flag, all roles drain and the kernel reports
 // B200_ERR_DEVICE_TIMEOUT through the device status word.
-#include "tc_device.cuh"
-#include <mutex>
+#include "attention_common.cuh"
 
 namespace b200 {
 
 namespace {
 
 using namespace tcx;
+using namespace attn;
 
 struct AttnArgs {
   int s1, s2, d;
@@ -60,42 +60,6 @@ struct AttnCfg {
 constexpr int ATT_REGS_LAUNCH = 168, ATT_REGS_SOFTMAX = 232, ATT_REGS_LOW = 40;
 static_assert(2 * 128 * ATT_REGS_SOFTMAX + 128 * ATT_REGS_LOW <= 384 * ATT_REGS_LAUNCH,
               "setmaxnreg budget exceeds the CTA's launch allocation");
-
-__device__ __forceinline__ float ex2_approx(float x) {
-  float y;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
-__device__ __forceinline__ uint32_t pack_half2(float a, float b) {
-  const __half2 h = __floats2half2_rn(a, b);
-  return *reinterpret_cast<const uint32_t*>(&h);
-}
-__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
-  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
-}
-
-// tcgen05.mma kind::f16 with the two shared-memory descriptors given as (low, high) words.  The high word
-// (stride offset, version, swizzle mode) never changes inside a kernel and the low word is base + constant,
-// so issuing an MMA costs the single thread two integer adds: at N = 64 an MMA runs for only 32 clocks, and a
-// descriptor rebuilt from scratch per MMA (about 20 dependent integer instructions) made the issuing thread,
-// not the tensor core, the bottleneck.
-__device__ __forceinline__ void umma_f16_lohi(uint32_t d_tmem, uint32_t alo, uint32_t ahi, uint32_t blo, uint32_t bhi,
-                                              uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
-      "setp.ne.b32 p, %6, 0;\n\t"
-      "mov.b64 da, {%1, %2};\n\t"
-      "mov.b64 db, {%3, %4};\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t}"
-      ::"r"(d_tmem), "r"(alo), "r"(ahi), "r"(blo), "r"(bhi), "r"(idesc), "r"(accumulate) : "memory");
-}
-
-// One mbarrier arrival for the whole warp, after every lane has reached this point (each lane has issued its
-// own fence before the call).  128 single arrivals per hand-off serialise on the barrier word.
-__device__ __forceinline__ void warp_arrive(uint32_t bar, int lane) {
-  __syncwarp();
-  if (lane == 0) mbar_arrive(bar);
-}
 
 template <int DP>
 __global__ void __launch_bounds__(AttnCfg<DP>::THREADS, 1)
@@ -224,12 +188,12 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
 #pragma unroll
                 for (int ks = 0; ks < DP / 16; ++ks) {
                   const uint32_t off = (uint32_t)(((ks >> 2) * 16384 + (ks & 3) * 32) >> 4);
-                  umma_f16_lohi(tmem_base + C::TM_S + t * 128, alo + off, hi_k, klo + off, hi_k, idesc_qk, ks > 0 ? 1u : 0u);
+                  umma_lohi<2>(tmem_base + C::TM_S + t * 128, alo + off, hi_k, klo + off, hi_k, idesc_qk, ks > 0 ? 1u : 0u);
                 }
               } else {
                 for (int ks = 0; ks < ksteps_qk; ++ks) {
                   const uint32_t off = (uint32_t)(((ks >> 2) * 16384 + (ks & 3) * 32) >> 4);
-                  umma_f16_lohi(tmem_base + C::TM_S + t * 128, alo + off, hi_k, klo + off, hi_k, idesc_qk, ks > 0 ? 1u : 0u);
+                  umma_lohi<2>(tmem_base + C::TM_S + t * 128, alo + off, hi_k, klo + off, hi_k, idesc_qk, ks > 0 ? 1u : 0u);
                 }
               }
               umma_commit(smem_u32(&bar_s_full[t]));
@@ -255,7 +219,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
             const uint32_t vlo = v_lo + (uint32_t)(s * (C::KV_BYTES >> 4));
 #pragma unroll
             for (int ks = 0; ks < 8; ++ks)                    // 128 keys, 16 per MMA
-              umma_f16_lohi(tmem_base + C::TM_O + (t * NB + b) * DP, plo + (uint32_t)(((ks >> 2) * 16384 + (ks & 3) * 32) >> 4), hi_k,
+              umma_lohi<2>(tmem_base + C::TM_O + (t * NB + b) * DP, plo + (uint32_t)(((ks >> 2) * 16384 + (ks & 3) * 32) >> 4), hi_k,
                             vlo + (uint32_t)(ks * 2048 >> 4), hi_v, idesc_pv, ks > 0 ? 1u : 0u);
             umma_commit(smem_u32(&bar_p_empty[t][b]));
             umma_commit(smem_u32(&bar_o_full[t][b]));
@@ -286,7 +250,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
       float corr = 1.f;                                      // factor that moves acc to the current maximum
       auto add_pv = [&](int j) -> bool {                     // acc = acc * corr + PV_t(j)
         const int b = j % NB;
-        if (!mbar_wait(smem_u32(&bar_o_full[t][b]), (uint32_t)(j / NB) & 1u, abortp, g.wait_limit)) return false;
+        if (!mbar_wait_warp(smem_u32(&bar_o_full[t][b]), (uint32_t)(j / NB) & 1u, abortp, g.wait_limit)) return false;
         tc_fence_after();
 #pragma unroll
         for (int c = 0; c < DP / 32; ++c) {
@@ -302,7 +266,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
       };
 
       for (int j = 0; j < T; ++j) {
-        if (!mbar_wait(smem_u32(&bar_s_full[t]), (uint32_t)j & 1u, abortp, g.wait_limit)) { ok = false; break; }
+        if (!mbar_wait_warp(smem_u32(&bar_s_full[t]), (uint32_t)j & 1u, abortp, g.wait_limit)) { ok = false; break; }
         tc_fence_after();
         const int valid = g.s2 - j * 128;                    // keys of this tile that exist
         const float gone = pos ? -INFINITY : INFINITY;       // a masked score: scaled it is -inf, probability 0
@@ -350,14 +314,14 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
         const float corr_new = ex2_approx(m - m_new);        // first tile: exp2(-inf) = 0, acc and l are 0
         // the P tile is free once PV(j-1) has been read by the tensor core
         const int pbuf = j % NB;
-        if (j >= NB && !mbar_wait(smem_u32(&bar_p_empty[t][pbuf]), ((uint32_t)(j / NB) & 1u) ^ 1u, abortp, g.wait_limit)) { ok = false; break; }
+        if (j >= NB && !mbar_wait_warp(smem_u32(&bar_p_empty[t][pbuf]), ((uint32_t)(j / NB) & 1u) ^ 1u, abortp, g.wait_limit)) { ok = false; break; }
         const uint32_t pb = pb0 + pbuf * C::P_BYTES;
         // (With single P / PV buffers, DP = 128, the turns would add to the tensor-core round trip instead.)
         // The two warpgroups take turns in the exponential phase: it saturates the SFU pipe, and in lockstep that
         // pipe would idle while both read scores / fold PV in.  Tile 0 goes first; tile 1 follows in the same j.
         if (NB == 2 && ntile == 2) {
-          const bool go = t == 0 ? (j == 0 || mbar_wait(smem_u32(&bar_turn[1]), (uint32_t)(j - 1) & 1u, abortp, g.wait_limit))
-                                 : mbar_wait(smem_u32(&bar_turn[0]), (uint32_t)j & 1u, abortp, g.wait_limit);
+          const bool go = t == 0 ? (j == 0 || mbar_wait_warp(smem_u32(&bar_turn[1]), (uint32_t)(j - 1) & 1u, abortp, g.wait_limit))
+                                 : mbar_wait_warp(smem_u32(&bar_turn[0]), (uint32_t)j & 1u, abortp, g.wait_limit);
           if (!go) { ok = false; break; }
         }
         float s4[4] = {0.f, 0.f, 0.f, 0.f};
@@ -433,42 +397,6 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
 // ---------------------------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
-                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
-                                  CUtensorMapFloatOOBfill);
-
-EncodeTiledFn attn_encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  static std::once_flag once;
-  std::call_once(once, [] {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-        q == cudaDriverEntryPointSuccess)
-      fn = (EncodeTiledFn)p;
-  });
-  return fn;
-}
-
-// f16 tensor (d, s, h, b) with unit stride along d; box = [64, rows, 1, 1] under the 128B swizzle.
-int encode_bhsd(CUtensorMap* map, const void* base, int64_t d, int64_t s, int64_t h, int64_t b, int64_t ss,
-                int64_t hs, int64_t bs, uint32_t rows) {
-  EncodeTiledFn fn = attn_encode_fn();
-  if (!fn) return B200_ERR_CUDA;
-  const cuuint64_t dims[4] = {(cuuint64_t)d, (cuuint64_t)s, (cuuint64_t)h, (cuuint64_t)b};
-  const uint64_t row = (uint64_t)(s > 1 ? ss : d) * 2;
-  const cuuint64_t strides[3] = {row, h > 1 ? (cuuint64_t)hs * 2 : row, b > 1 ? (cuuint64_t)bs * 2 : row};
-  const cuuint32_t box[4] = {64, rows, 1, 1};
-  const cuuint32_t estr[4] = {1, 1, 1, 1};
-  const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
-                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? B200_OK : B200_ERR_UNSUPPORTED;
-}
-
-bool stride_ok(int64_t extent, int64_t stride) { return extent <= 1 || (stride > 0 && stride % 8 == 0); }
-
 template <int DP>
 int launch_fwd(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const AttnArgs& g, int64_t ctas,
                cudaStream_t stream) {

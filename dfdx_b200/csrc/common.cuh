@@ -75,6 +75,15 @@ int attention_forward(int dtype, int64_t B, int64_t H, int64_t s1, int64_t s2, i
                       const int64_t qs[4], const void* k, const int64_t ks[4], const void* v, const int64_t vs[4],
                       double alpha, void* out, const int64_t os[4], float* lse, cudaStream_t stream);
 
+// Fused attention backward (attention_bwd.cu); see b200_attention_backward.
+int attention_bwd_setup_device();
+size_t attention_backward_workspace_bytes(int64_t B, int64_t H, int64_t s1);
+int attention_backward(int dtype, int64_t B, int64_t H, int64_t s1, int64_t s2, int64_t d, const void* q,
+                       const int64_t qs[4], const void* k, const int64_t ks[4], const void* v, const int64_t vs[4],
+                       double alpha, const void* out, const int64_t os[4], const float* lse, const void* go,
+                       const int64_t gs[4], void* gq, const int64_t gqs[4], void* gk, const int64_t gks[4], void* gv,
+                       const int64_t gvs[4], int accumulate, void* workspace, size_t workspace_bytes, cudaStream_t stream);
+
 // Lowers one problem to a kernel family according to b200_set_path and eligibility.
 int run_gemm(const GemmProblem& p, cudaStream_t stream);
 

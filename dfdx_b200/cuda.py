@@ -218,6 +218,26 @@ class Cuda:
                                               self._stream()), "b200_attention_forward")
         return out, lse
 
+    def attention_backward(self, q, k, v, alpha: float, out, lse, grad_out, accumulate_into=None):
+        """Gradients of `attention_forward`.  Returns (grad_q, grad_k, grad_v) viewed through q's, k's and v's
+        strides (zeroed buffers of the storages' physical length, as `Gradients::try_alloc_for` makes them), or
+        accumulates into the three given flat buffers."""
+        b, h, s1, d = q.shape
+        s2 = k.shape[3]
+        if accumulate_into is None:
+            gq, gk, gv = self.alloc_grad(q), self.alloc_grad(k), self.alloc_grad(v)
+        else:
+            gq, gk, gv = accumulate_into
+        go = grad_out if grad_out.stride(3) == 1 else grad_out.contiguous()
+        need = self.lib.b200_attention_backward_workspace_bytes(b, h, s1)
+        ws = self.get_workspace(need)
+        check(self.lib.b200_attention_backward(
+            self._dtype(q), b, h, s1, s2, d, q.data_ptr(), _st(q.stride()), k.data_ptr(), _st(k.stride()),
+            v.data_ptr(), _st(v.stride()), float(alpha), out.data_ptr(), _st(out.stride()), lse.data_ptr(),
+            go.data_ptr(), _st(go.stride()), gq.data_ptr(), _st(q.stride()), gk.data_ptr(), _st(k.stride()),
+            gv.data_ptr(), _st(v.stride()), 1, ws.data_ptr(), ws.numel(), self._stream()), "b200_attention_backward")
+        return self.grad_view(gq, q), self.grad_view(gk, k), self.grad_view(gv, v)
+
     # -- TryMatMul (matmul/mod.rs:133-311) ---------------------------------------------------------
     def matmul(self, lhs: torch.Tensor, rhs: torch.Tensor):
         """Rank dispatch of `TryMatMul`.  Returns (out, backward) where

@@ -249,6 +249,26 @@ int b200_attention_forward(int dtype, size_t batch, size_t heads, size_t s1, siz
                            const void* v, const size_t v_strides[4],
                            double alpha, void* out, const size_t out_strides[4], float* lse, void* stream);
 
+/* Backward of b200_attention_forward: the tape entries of the same four ops (matmul, scalar mul, softmax,
+ * matmul) in three launches, again without a score-sized tensor in HBM (P is recomputed from `lse`).
+ *   out, lse      : what the forward returned          grad_out : gradient of `out`, a (batch, heads, S1, D) view
+ *   grad_q / grad_v: views shaped and strided like q / v;  grad_k: a (batch, heads, D, S2) view like k
+ *   accumulate    : 0 = the gradients are written; 1 = added to what the buffers hold, as dfdx's backward ops do
+ *                   into `Gradients` buffers.  grad_q may be NULL (only dK, dV) or grad_k and grad_v both NULL.
+ *   workspace     : b200_attention_backward_workspace_bytes(batch, heads, S1) bytes of device scratch, 16-byte aligned
+ * Same layout limits as the forward (B200_ERR_UNSUPPORTED before any launch otherwise). */
+size_t b200_attention_backward_workspace_bytes(size_t batch, size_t heads, size_t s1);
+int b200_attention_backward(int dtype, size_t batch, size_t heads, size_t s1, size_t s2, size_t d,
+                            const void* q, const size_t q_strides[4],
+                            const void* k, const size_t k_strides[4],
+                            const void* v, const size_t v_strides[4],
+                            double alpha, const void* out, const size_t out_strides[4], const float* lse,
+                            const void* grad_out, const size_t grad_out_strides[4],
+                            void* grad_q, const size_t grad_q_strides[4],
+                            void* grad_k, const size_t grad_k_strides[4],
+                            void* grad_v, const size_t grad_v_strides[4],
+                            int accumulate, void* workspace, size_t workspace_bytes, void* stream);
+
 /* ---- conv2d (unfold + GEMM lowering) ---------------------------------------------------------- */
 
 /* Bytes of caller-provided scratch the conv2d entry points need; `backward` != 0 selects the

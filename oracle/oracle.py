@@ -252,6 +252,20 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, alpha: float):
     return tokens, lse
 
 
+def attention_backward(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, alpha: float, grad_out: torch.Tensor):
+    """Backward of `attention` as dfdx's tape runs it, op by op in f64: matmul backward (matmul/cpu_kernel.rs via
+    `matmul`'s backward), softmax backward (softmax.rs: y * (g - sum(g * y))), scalar-mul backward, matmul backward.
+    Returns (grad_q, grad_k, grad_v) viewed through the operands' strides."""
+    scores, bwd_qk = matmul(q, k)
+    scores = scores * float(alpha)
+    weights = torch.softmax(scores, dim=-1)
+    _, bwd_wv = matmul(weights, v.detach().cpu().to(torch.float64))
+    g_w, g_v = bwd_wv(grad_out.detach().cpu().to(torch.float64))
+    g_scores = weights * (g_w - (g_w * weights).sum(dim=-1, keepdim=True)) * float(alpha)
+    g_q, g_k = bwd_qk(g_scores)
+    return g_q, g_k, g_v
+
+
 def rel_frobenius(got: torch.Tensor, want: torch.Tensor) -> float:
     """||got - want||_F / ||want||_F in f64 (0/0 -> 0)."""
     g = got.detach().cpu().to(torch.float64)

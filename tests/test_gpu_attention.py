@@ -90,3 +90,61 @@ def test_attention_rejects_what_it_cannot_address(cuda_dev):
         dev.attention_forward(qd, kd, vd, 1.0)
     assert e.value.status == _lib.ERR_UNSUPPORTED
     assert dev.device_status() == 0
+
+
+# ----------------------------------------------------------------------------------------------- backward
+BWD_SHAPES = [(1, 1, 128, 128, 64), (2, 3, 200, 136, 64), (1, 2, 384, 520, 32), (1, 1, 128, 256, 128),
+              (2, 2, 72, 72, 16), (1, 2, 8, 300, 64), (1, 1, 300, 8, 40), (1, 2, 130, 257, 96)]
+
+
+@pytest.mark.parametrize("shape", BWD_SHAPES, ids=lambda s: "x".join(map(str, s)))
+def test_attention_backward(cuda_dev, oracle, shape):
+    """dQ, dK, dV against the oracle's op-by-op backward; gradients land in the operands' base layouts
+    ((B,S,H,D) buffers) through the views' strides, as dfdx stores them."""
+    b, h, s1, s2, d = shape
+    g = gen(1000 + sum(shape))
+    q, k, v = mha_views(b, h, s1, s2, d, g, cuda_dev.device)
+    alpha = 1.0 / math.sqrt(d)
+    out, lse = cuda_dev.attention_forward(q, k, v, alpha, want_lse=True)
+    go = torch.randn(b, s1, h, d, generator=g, dtype=torch.float64).half().to(cuda_dev.device).permute(0, 2, 1, 3)
+    before = cuda_dev.lib.b200_tensor_launch_count()
+    gq, gk, gv = cuda_dev.attention_backward(q, k, v, alpha, out, lse, go)
+    cuda_dev.synchronize()
+    assert cuda_dev.lib.b200_tensor_launch_count() - before == 2
+    assert gq.stride() == q.stride() and gk.stride() == k.stride() and gv.stride() == v.stride()
+    wq, wk, wv = oracle.attention_backward(q.cpu(), k.cpu(), v.cpu(), alpha, go.cpu())
+    for name, got, want in (("dQ", gq, wq), ("dK", gk, wk), ("dV", gv, wv)):
+        err = oracle.rel_frobenius(got, want)
+        assert err <= 2 * FROB_TOL[torch.float16], f"{name}: rel frobenius {err:.3e}"
+    assert cuda_dev.device_status() == 0
+
+
+def test_attention_backward_accumulates(cuda_dev, oracle):
+    """accumulate = 1 adds to what the gradient buffers hold (two calls give twice the gradient)."""
+    g = gen(77)
+    q, k, v = mha_views(1, 2, 192, 160, 64, g, cuda_dev.device)
+    out, lse = cuda_dev.attention_forward(q, k, v, 0.125, want_lse=True)
+    go = torch.randn(1, 192, 2, 64, generator=g).half().to(cuda_dev.device).permute(0, 2, 1, 3)
+    once = cuda_dev.attention_backward(q, k, v, 0.125, out, lse, go)
+    bufs = (cuda_dev.alloc_grad(q), cuda_dev.alloc_grad(k), cuda_dev.alloc_grad(v))
+    cuda_dev.attention_backward(q, k, v, 0.125, out, lse, go, accumulate_into=bufs)
+    twice = cuda_dev.attention_backward(q, k, v, 0.125, out, lse, go, accumulate_into=bufs)
+    for a, b2 in zip(once, twice):
+        assert oracle.rel_frobenius(b2, 2.0 * a.double()) <= 1e-3
+
+
+def test_attention_backward_workspace_is_checked(cuda_dev):
+    g = gen(78)
+    q, k, v = mha_views(1, 1, 64, 64, 64, g, cuda_dev.device)
+    out, lse = cuda_dev.attention_forward(q, k, v, 0.125, want_lse=True)
+    lib = cuda_dev.lib
+    need = lib.b200_attention_backward_workspace_bytes(1, 1, 64)
+    assert need == 64 * 8
+    ws = torch.empty(need, dtype=torch.uint8, device=cuda_dev.device)
+    gq, gk, gv = cuda_dev.alloc_grad(q), cuda_dev.alloc_grad(k), cuda_dev.alloc_grad(v)
+    st = _lib.strides
+    rc = lib.b200_attention_backward(_lib.F16, 1, 1, 64, 64, 64, q.data_ptr(), st(q.stride()), k.data_ptr(), st(k.stride()),
+                                     v.data_ptr(), st(v.stride()), 0.125, out.data_ptr(), st(out.stride()), lse.data_ptr(),
+                                     out.data_ptr(), st(out.stride()), gq.data_ptr(), st(q.stride()), gk.data_ptr(),
+                                     st(k.stride()), gv.data_ptr(), st(v.stride()), 0, ws.data_ptr(), need - 1, None)
+    assert rc == _lib.ERR_WORKSPACE
