@@ -266,7 +266,7 @@ def run_transformer(args, dev, rank, world):
     device, lib = dev.device, dev.lib
     BATCH, SEQ, MODEL = 64, 256, 512
     trainer = Trainer(dev, world, layers=6, model=MODEL, heads=8, ff=2048, seed=0,       # same init on every rank
-                      fused=not args.unfused_epilogues)
+                      fused=False if args.unfused_epilogues else (True if args.unfused_attention else "attention"))
     g = torch.Generator(device="cpu").manual_seed(0xD0FD + 5 + 1000 * rank)             # different data per rank
     x_h = torch.randn(BATCH, SEQ, MODEL, generator=g).half().pin_memory()
     t_h = torch.randn(BATCH, SEQ, MODEL, generator=g).half().pin_memory()
@@ -324,7 +324,9 @@ def run_transformer(args, dev, rank, world):
                    "matmuls": "all on libdfdx_b200 (MatMatBr + MatMatBatch4, forward and backward); LayerNorm, softmax, "
                               "loss and Adam are torch ops (separate non-matmul kernels in dfdx too)",
                    "epilogues": "bias, ReLU and score scale as separate torch ops" if args.unfused_epilogues else
-                                "Linear bias, feed-forward ReLU and the 1/sqrt(d) score scale fused into the forward GEMMs"},
+                                "Linear bias, feed-forward ReLU and the 1/sqrt(d) score scale fused into the forward GEMMs",
+                   "attention": "two batched GEMMs + torch softmax" if (args.unfused_epilogues or args.unfused_attention)
+                                else "fused attention kernels (b200_attention_forward / _backward)"},
         "gpu_launches": int(launches_per_step * args.steps) if captured else int(launches),
         "tensor_core_launches": int(launches_per_step * args.steps) if captured else int(tc),
         "cuda_graph": bool(captured), "cuda_graph_error": getattr(trainer, "capture_error", None),
@@ -342,6 +344,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--unfused-attention", action="store_true",
+                    help="workload c5: scores / softmax / weighted sum as two batched GEMMs and a torch softmax instead of "
+                         "the fused attention kernels")
     ap.add_argument("--unfused-epilogues", action="store_true",
                     help="workload c5: bias / ReLU / score scale as separate ops after the GEMMs (the reference's op sequence)")
     ap.add_argument("--workload", default="c2", choices=["c1", "c2", "c3", "c4", "c5"],

@@ -7,7 +7,8 @@ and `MultiHeadAttention::try_forward` (multi_head_attention.rs:105-146: three Li
 (b,s,h,d) buffers viewed as (b,h,s,d) / (b,h,d,s) without a copy, q.matmul(k) * 1/sqrt(d), softmax,
 .matmul(v), permute back, output Linear).  Every `matmul` goes through `dfdx_b200.Cuda`
 (`MatMatBrKernel` for the Linear layers, `MatMatBatch4Kernel` for the attention products, forward and
-backward).  With `fused=True` (default) the ops that directly follow a GEMM in the forward pass — Linear's
+backward).  With `fused="attention"` the whole scores / softmax / weighted-sum sequence additionally runs as the
+fused attention kernels.  With `fused=True` (default) the ops that directly follow a GEMM in the forward pass — Linear's
 bias add, the feed-forward ReLU, the 1/sqrt(d) scale of the scores — run in that GEMM's epilogue
 (`b200_linear_forward`, `b200_matmat_batch4_forward_scaled`); with `fused=False` they are separate torch
 ops, as they are separate kernels in dfdx.  Residual, LayerNorm, softmax, the MSE loss and Adam are plain
@@ -107,6 +108,25 @@ class _ScaledMatMul(torch.autograd.Function):
         return None, dev.grad_view(gl, lhs), dev.grad_view(gr, rhs), None
 
 
+class _FusedAttention(torch.autograd.Function):
+    """softmax(q.matmul(k) * alpha).matmul(v) as one forward kernel and three backward launches
+    (`b200_attention_forward` / `b200_attention_backward`): the (batch, heads, S, S) score tensor never reaches
+    HBM, and the output is written straight in the (batch, S, heads * d) layout the output projection reads."""
+
+    @staticmethod
+    def forward(ctx, dev: Cuda, q, k, v, alpha: float):
+        out, lse = dev.attention_forward(q, k, v, alpha, want_lse=True)
+        ctx.dev, ctx.alpha = dev, alpha
+        ctx.save_for_backward(q, k, v, out, lse)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        q, k, v, out, lse = ctx.saved_tensors
+        gq, gk, gv = ctx.dev.attention_backward(q, k, v, ctx.alpha, out, lse, grad_out)
+        return None, gq, gk, gv, None
+
+
 class Linear(torch.nn.Module):
     """dfdx `Linear`: weight stored (O, I), consumed as the permuted (I, O) view; uniform(+-1/sqrt(I)) init
     (dfdx/src/nn/layers/linear.rs:65-89)."""
@@ -139,6 +159,9 @@ class MultiHeadAttention(torch.nn.Module):
         v = self.w_v(x).reshape(b, s, h, d).permute(0, 2, 1, 3)
         k = self.w_k(x).reshape(b, s, h, d).permute(0, 2, 3, 1)
         q = self.w_q(x).reshape(b, s, h, d).permute(0, 2, 1, 3)
+        if self.fused == "attention" and x.dtype == torch.float16 and d % 8 == 0 and d <= 128:
+            tokens = _FusedAttention.apply(self.dev, q, k, v, 1.0 / math.sqrt(d))
+            return self.w_o(tokens.permute(0, 2, 1, 3).reshape(b, s, m))
         if self.fused:
             scores = _ScaledMatMul.apply(self.dev, q, k, 1.0 / math.sqrt(d))
         else:
