@@ -15,9 +15,9 @@
 // ring: C1, C2):
 //   mode 0: R1 = Q, R2 = dO, C1 = K_j, C2 = V_j      S' = R1 C1^T = S,    dP' = R2 C2^T = dP
 //   mode 1: R1 = K, R2 = V,  C1 = Q_i, C2 = dO_i     S' = R1 C1^T = S^T,  dP' = R2 C2^T = dP^T
-// Warp 4 = TMA producer, warp 5 = MMA issuer (S', dP' into double-buffered TMEM; accumulators acc1 += dS' C1 and,
-// mode 1, acc2 += P' C2 stay in TMEM over the whole loop), warps 0..3 = one thread per row: read S' and dP' from
-// TMEM, P' = exp2(s * scale - L), dS' = P' (dP' - Dl), write dS' (and P') as f16 MMA operands into shared memory.
+// Warp 8 = TMA producer, warps 9 and 10 = MMA issuers (S', dP' into double-buffered TMEM; accumulators acc1 += dS' C1
+// and, mode 1, acc2 += P' C2 stay in TMEM over the whole loop), warps 0..7 = two threads per row (each takes half of
+// a step's 64 columns; no reduction across a row is needed in the backward pass): read S' and dP' from TMEM, P' = exp2(s * scale - L), dS' = P' (dP' - Dl), write dS' (and P') as f16 MMA operands into shared memory.
 // The same shared-memory image of a column tile serves as the K-major B operand of S' / dP' and as the MN-major
 // B operand of the accumulator MMAs.  Every wait is bounded (abort flag, device status word).
 #include "attention_common.cuh"
@@ -51,7 +51,7 @@ struct BwdCfg {
   static constexpr int OFF_C = 2 * R_BYTES;
   static constexpr int OFF_A = OFF_C + ST * 2 * C_BYTES;   // dS'[0], dS'[1], then (mode 1) P'[0], P'[1]
   static constexpr int SMEM_BYTES = OFF_A + (MODE == 1 ? 4 : 2) * A_BYTES + 1024;
-  static constexpr int THREADS = 192;
+  static constexpr int THREADS = 384;                      // 8 row warps, TMA warp, two MMA issuers, one idle warp
   static constexpr int TMEM_COLS = 512;
   static constexpr uint32_t TM_S = 0, TM_DP = 128, TM_ACC1 = 256, TM_ACC2 = 256 + DP;
 };
@@ -119,18 +119,18 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tma_r1, const __grid_co
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(smem_u32(&bar_sdp_full[b]), 1);
-      mbar_init(smem_u32(&bar_sdp_empty[b]), 4);
-      mbar_init(smem_u32(&bar_a_full[b]), 4);
+      mbar_init(smem_u32(&bar_sdp_empty[b]), 8);            // one arrival per row warp
+      mbar_init(smem_u32(&bar_a_full[b]), 8);
       mbar_init(smem_u32(&bar_a_empty[b]), 1);
     }
     abort_flag = 0;
     fence_mbar_init();
   }
-  if (warp == 5) {
+  if (warp == 9) {
     tmem_alloc(smem_u32(&tmem_slot), C::TMEM_COLS);
     tmem_relinquish();
   }
-  if (warp == 4 && lane == 0) {
+  if (warp == 8 && lane == 0) {
     tma_prefetch_desc(&tma_r1);
     tma_prefetch_desc(&tma_r2);
     tma_prefetch_desc(&tma_c1);
@@ -147,7 +147,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tma_r1, const __grid_co
   const int T = g.col_tiles;
   const int ksteps = (g.d + 15) / 16;                       // k-steps of S' / dP' that hold data
 
-  if (warp == 4) {
+  if (warp == 8) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
       const uint32_t br = smem_u32(&bar_r);
@@ -169,8 +169,11 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tma_r1, const __grid_co
       }
     }
     __syncwarp();
-  } else if (warp == 5) {
-    // ------------------------------------------------------------------ MMA issuer
+  } else if (warp == 9 || warp == 10) {
+    // ------------------------------------------------------------------ MMA issuers
+    // warp 9 issues S' and dP', warp 10 the accumulator MMAs: two short instruction streams instead of one long
+    // one (the issuing thread's waits, descriptor updates and commits are a serial chain that competes with the
+    // row warps for issue slots).
     if (lane == 0) {
       const uint32_t idesc_s = (1u << 4) | ((uint32_t)(64 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);             // N = 64
       const uint32_t idesc_acc = (1u << 4) | (1u << 16) | ((uint32_t)(DP >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);  // B MN-major
@@ -178,56 +181,60 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tma_r1, const __grid_co
       const uint64_t dm = make_smem_desc(smem_base, 8192, 1024, 2);            // MN-major column tile (d-chunk stride 8192)
       const uint32_t hi_k = (uint32_t)(dk >> 32), hi_m = (uint32_t)(dm >> 32);
       const uint32_t lo_k = (uint32_t)dk, lo_m = (uint32_t)dm;
-      bool ok = mbar_wait(smem_u32(&bar_r), 0, abortp, g.wait_limit);
-      // S'(j) and dP'(j): need column tile j and, for j >= 2, the row threads to have read buffer j & 1
-      auto issue_sdp = [&](int j) -> bool {
-        const int s = j % ST, b = j & 1;
-        if (!mbar_wait(smem_u32(&bar_c_full[s]), ((uint32_t)(j / ST)) & 1u, abortp, g.wait_limit)) return false;
-        if (j >= 2 && !mbar_wait(smem_u32(&bar_sdp_empty[b]), (((uint32_t)(j >> 1)) & 1u) ^ 1u, abortp, g.wait_limit)) return false;
-        tc_fence_after();
-        const uint32_t c_lo = lo_k + (uint32_t)((C::OFF_C + s * 2 * C::C_BYTES) >> 4);
-        for (int ks = 0; ks < ksteps; ++ks) {
-          const uint32_t ro = (uint32_t)(((ks >> 2) * 16384 + (ks & 3) * 32) >> 4);
-          const uint32_t co = (uint32_t)(((ks >> 2) * 8192 + (ks & 3) * 32) >> 4);
-          umma_lohi<2>(tmem_base + C::TM_S + b * 64, lo_k + ro, hi_k, c_lo + co, hi_k, idesc_s, ks > 0 ? 1u : 0u);
+      if (warp == 9) {
+        bool ok = mbar_wait(smem_u32(&bar_r), 0, abortp, g.wait_limit);
+        // S'(j) and dP'(j): need column tile j and, for j >= 2, the row threads to have read buffer j & 1
+        for (int j = 0; ok && j < T; ++j) {
+          const int s = j % ST, b = j & 1;
+          if (!mbar_wait(smem_u32(&bar_c_full[s]), ((uint32_t)(j / ST)) & 1u, abortp, g.wait_limit)) break;
+          if (j >= 2 && !mbar_wait(smem_u32(&bar_sdp_empty[b]), (((uint32_t)(j >> 1)) & 1u) ^ 1u, abortp, g.wait_limit)) break;
+          tc_fence_after();
+          const uint32_t c_lo = lo_k + (uint32_t)((C::OFF_C + s * 2 * C::C_BYTES) >> 4);
+          for (int ks = 0; ks < ksteps; ++ks) {
+            const uint32_t ro = (uint32_t)(((ks >> 2) * 16384 + (ks & 3) * 32) >> 4);
+            const uint32_t co = (uint32_t)(((ks >> 2) * 8192 + (ks & 3) * 32) >> 4);
+            umma_lohi<2>(tmem_base + C::TM_S + b * 64, lo_k + ro, hi_k, c_lo + co, hi_k, idesc_s, ks > 0 ? 1u : 0u);
+          }
+          for (int ks = 0; ks < ksteps; ++ks) {
+            const uint32_t ro = (uint32_t)((C::R_BYTES + (ks >> 2) * 16384 + (ks & 3) * 32) >> 4);
+            const uint32_t co = (uint32_t)((C::C_BYTES + (ks >> 2) * 8192 + (ks & 3) * 32) >> 4);
+            umma_lohi<2>(tmem_base + C::TM_DP + b * 64, lo_k + ro, hi_k, c_lo + co, hi_k, idesc_s, ks > 0 ? 1u : 0u);
+          }
+          umma_commit(smem_u32(&bar_sdp_full[b]));
         }
-        for (int ks = 0; ks < ksteps; ++ks) {
-          const uint32_t ro = (uint32_t)((C::R_BYTES + (ks >> 2) * 16384 + (ks & 3) * 32) >> 4);
-          const uint32_t co = (uint32_t)((C::C_BYTES + (ks >> 2) * 8192 + (ks & 3) * 32) >> 4);
-          umma_lohi<2>(tmem_base + C::TM_DP + b * 64, lo_k + ro, hi_k, c_lo + co, hi_k, idesc_s, ks > 0 ? 1u : 0u);
-        }
-        umma_commit(smem_u32(&bar_sdp_full[b]));
-        return true;
-      };
-      if (ok && T > 0) ok = issue_sdp(0);
-      for (int j = 0; ok && j < T; ++j) {
-        if (j + 1 < T && !issue_sdp(j + 1)) { ok = false; break; }
-        const int s = j % ST, b = j & 1;
-        if (!mbar_wait(smem_u32(&bar_a_full[b]), ((uint32_t)(j >> 1)) & 1u, abortp, g.wait_limit)) { ok = false; break; }
-        tc_fence_after();
-        const uint32_t a_lo = lo_k + (uint32_t)((C::OFF_A + b * C::A_BYTES) >> 4);
-        const uint32_t c_lo = lo_m + (uint32_t)((C::OFF_C + s * 2 * C::C_BYTES) >> 4);
+      } else {
+        bool ok = true;
+        for (int j = 0; j < T; ++j) {
+          const int s = j % ST, b = j & 1;
+          if (!mbar_wait(smem_u32(&bar_c_full[s]), ((uint32_t)(j / ST)) & 1u, abortp, g.wait_limit)) { ok = false; break; }
+          if (!mbar_wait(smem_u32(&bar_a_full[b]), ((uint32_t)(j >> 1)) & 1u, abortp, g.wait_limit)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_lo = lo_k + (uint32_t)((C::OFF_A + b * C::A_BYTES) >> 4);
+          const uint32_t c_lo = lo_m + (uint32_t)((C::OFF_C + s * 2 * C::C_BYTES) >> 4);
 #pragma unroll
-        for (int ks = 0; ks < 4; ++ks)                        // 64 columns of S', 16 per MMA
-          umma_lohi<2>(tmem_base + C::TM_ACC1, a_lo + (uint32_t)(ks * 32 >> 4), hi_k, c_lo + (uint32_t)(ks * 2048 >> 4), hi_m,
-                       idesc_acc, (j > 0 || ks > 0) ? 1u : 0u);
-        if (MODE == 1) {
+          for (int ks = 0; ks < 4; ++ks)                      // 64 columns of S', 16 per MMA
+            umma_lohi<2>(tmem_base + C::TM_ACC1, a_lo + (uint32_t)(ks * 32 >> 4), hi_k, c_lo + (uint32_t)(ks * 2048 >> 4), hi_m,
+                         idesc_acc, (j > 0 || ks > 0) ? 1u : 0u);
+          if (MODE == 1) {
 #pragma unroll
-          for (int ks = 0; ks < 4; ++ks)
-            umma_lohi<2>(tmem_base + C::TM_ACC2, a_lo + (uint32_t)((2 * C::A_BYTES + ks * 32) >> 4), hi_k,
-                         c_lo + (uint32_t)((C::C_BYTES + ks * 2048) >> 4), hi_m, idesc_acc, (j > 0 || ks > 0) ? 1u : 0u);
+            for (int ks = 0; ks < 4; ++ks)
+              umma_lohi<2>(tmem_base + C::TM_ACC2, a_lo + (uint32_t)((2 * C::A_BYTES + ks * 32) >> 4), hi_k,
+                           c_lo + (uint32_t)((C::C_BYTES + ks * 2048) >> 4), hi_m, idesc_acc, (j > 0 || ks > 0) ? 1u : 0u);
+          }
+          umma_commit(smem_u32(&bar_a_empty[b]));
+          umma_commit(smem_u32(&bar_c_empty[s]));
         }
-        umma_commit(smem_u32(&bar_a_empty[b]));
-        umma_commit(smem_u32(&bar_c_empty[s]));
+        if (ok) umma_commit(smem_u32(&bar_acc));
       }
-      if (ok) umma_commit(smem_u32(&bar_acc));
     }
     __syncwarp();
-  } else {
-    // ------------------------------------------------------------------ row threads (warps 0..3)
-    const int r = warp * 32 + lane;                          // row inside the tile = TMEM lane
+  } else if (warp < 8) {
+    // ------------------------------------------------------------------ row threads (warps 0..7)
+    // warps w and w + 4 share the rows of TMEM lane quadrant w & 3 and split each step's 64 columns in halves
+    const int quad = warp & 3, half = warp >> 2;
+    const int r = quad * 32 + lane;                          // row inside the tile = TMEM lane
     const int row = rt * 128 + r;
-    const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
     const uint32_t a_row = (uint32_t)(r >> 3) * 1024 + (uint32_t)(r & 7) * 128;
     const uint32_t sw = (uint32_t)(r & 7);
     const float scale = g.scale_log2;
@@ -243,21 +250,19 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tma_r1, const __grid_co
       const uint32_t ph = ((uint32_t)(j >> 1)) & 1u;
       if (!mbar_wait_warp(smem_u32(&bar_sdp_full[b]), ph, abortp, g.wait_limit)) { ok = false; break; }
       tc_fence_after();
-      uint32_t sv[64], dv[64];
-      tmem_ld_32x32(lane_addr + C::TM_S + b * 64, *reinterpret_cast<uint32_t(*)[32]>(&sv[0]));
-      tmem_ld_32x32(lane_addr + C::TM_S + b * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&sv[32]));
-      tmem_ld_32x32(lane_addr + C::TM_DP + b * 64, *reinterpret_cast<uint32_t(*)[32]>(&dv[0]));
-      tmem_ld_32x32(lane_addr + C::TM_DP + b * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&dv[32]));
+      uint32_t sv[32], dv[32];
+      tmem_ld_32x32(lane_addr + C::TM_S + b * 64 + half * 32, sv);
+      tmem_ld_32x32(lane_addr + C::TM_DP + b * 64 + half * 32, dv);
       tmem_wait_ld();
       tc_fence_before();
       warp_arrive(smem_u32(&bar_sdp_empty[b]), lane);
       // the operand buffers of this parity are free once the accumulator MMAs of step j-2 have read them
       if (j >= 2 && !mbar_wait_warp(smem_u32(&bar_a_empty[b]), ph ^ 1u, abortp, g.wait_limit)) { ok = false; break; }
       const uint32_t ds_dst = smem_base + C::OFF_A + b * C::A_BYTES + a_row;
-      const int valid = g.n_cols - j * 64;                   // columns of this step that exist
-      const float2* caux = aux + j * 64;                     // mode 1: per-column constants (padded to 64)
+      const int valid = g.n_cols - j * 64 - half * 32;       // columns of this thread's half that exist
+      const float2* caux = aux + j * 64 + half * 32;         // mode 1: per-column constants (padded to 64)
 #pragma unroll
-      for (int c = 0; c < 8; ++c) {                          // 16-byte chunks of 8 columns
+      for (int c = 0; c < 4; ++c) {                          // 16-byte chunks of 8 columns
         float pv[8], dsv[8];
 #pragma unroll
         for (int e = 0; e < 8; e += 2) {
@@ -278,7 +283,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tma_r1, const __grid_co
           dsv[e] = p0 * (__uint_as_float(dv[c * 8 + e]) - d0);
           dsv[e + 1] = p1 * (__uint_as_float(dv[c * 8 + e + 1]) - d1);
         }
-        const uint32_t off = (((uint32_t)c ^ sw) << 4);
+        const uint32_t off = (((uint32_t)(half * 4 + c) ^ sw) << 4);
         st_shared_v4(ds_dst + off, pack_half2(dsv[0], dsv[1]), pack_half2(dsv[2], dsv[3]), pack_half2(dsv[4], dsv[5]),
                      pack_half2(dsv[6], dsv[7]));
         if (MODE == 1)
@@ -299,10 +304,21 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tma_r1, const __grid_co
                                  : g.out2 + ib * g.o2_b + ih * g.o2_h + (long long)row * g.o2_r;
         const float mul = which == 0 ? g.alpha : 1.f;         // dQ and dK carry the score scale, dV does not
         const uint32_t tm = which == 0 ? C::TM_ACC1 : C::TM_ACC2;
+        constexpr int CPH = DP / 64;                          // 32-column chunks per half
 #pragma unroll
-        for (int c = 0; c < DP / 32; ++c) {
+        for (int cc = 0; cc < CPH; ++cc) {                    // each half stores half of the columns
+          const int c = half * CPH + cc;
           uint32_t v[32];
           tmem_ld_32x32(lane_addr + tm + c * 32, v);
+          // what the gradient buffer holds: all four 16-byte pieces are requested before any is used, so the
+          // row-strided (uncoalesced) reads overlap instead of costing one memory round trip each
+          uint4 old[4];
+          if (g.accumulate) {
+#pragma unroll
+            for (int q8 = 0; q8 < 4; ++q8)
+              old[q8] = (store && c * 32 + q8 * 8 < g.d) ? *reinterpret_cast<const uint4*>(dst + c * 32 + q8 * 8)
+                                                         : make_uint4(0u, 0u, 0u, 0u);
+          }
           tmem_wait_ld();
 #pragma unroll
           for (int q8 = 0; q8 < 4; ++q8) {
@@ -312,8 +328,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tma_r1, const __grid_co
 #pragma unroll
               for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(v[q8 * 8 + e]) * mul;
               if (g.accumulate) {
-                const uint4 old = *reinterpret_cast<const uint4*>(dst + col);
-                const __half2* ho = reinterpret_cast<const __half2*>(&old);
+                const __half2* ho = reinterpret_cast<const __half2*>(&old[q8]);
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                   const float2 fo = __half22float2(ho[e]);
@@ -334,7 +349,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tma_r1, const __grid_co
   tc_fence_before();
   __syncthreads();
   teardown(abort_flag, g.status);
-  if (warp == 5) {
+  if (warp == 9) {
     tc_fence_after();
     tmem_dealloc(tmem_base, C::TMEM_COLS);
   }

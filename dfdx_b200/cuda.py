@@ -228,6 +228,9 @@ class Cuda:
             gq, gk, gv = self.alloc_grad(q), self.alloc_grad(k), self.alloc_grad(v)
         else:
             gq, gk, gv = accumulate_into
+        # Fresh zeroed buffers need no read-modify-write, unless several elements of a view alias one storage
+        # element (a broadcast), where writes would overwrite each other's sums.
+        acc = 0 if (accumulate_into is None and all(st != 0 for t in (q, k, v) for st in t.stride())) else 1
         go = grad_out if grad_out.stride(3) == 1 else grad_out.contiguous()
         need = self.lib.b200_attention_backward_workspace_bytes(b, h, s1)
         ws = self.get_workspace(need)
@@ -235,7 +238,7 @@ class Cuda:
             self._dtype(q), b, h, s1, s2, d, q.data_ptr(), _st(q.stride()), k.data_ptr(), _st(k.stride()),
             v.data_ptr(), _st(v.stride()), float(alpha), out.data_ptr(), _st(out.stride()), lse.data_ptr(),
             go.data_ptr(), _st(go.stride()), gq.data_ptr(), _st(q.stride()), gk.data_ptr(), _st(k.stride()),
-            gv.data_ptr(), _st(v.stride()), 1, ws.data_ptr(), ws.numel(), self._stream()), "b200_attention_backward")
+            gv.data_ptr(), _st(v.stride()), acc, ws.data_ptr(), ws.numel(), self._stream()), "b200_attention_backward")
         return self.grad_view(gq, q), self.grad_view(gk, k), self.grad_view(gv, v)
 
     # -- TryMatMul (matmul/mod.rs:133-311) ---------------------------------------------------------
