@@ -170,7 +170,7 @@ def run_other_workload(args, dev, rank, world):
     import torch.distributed as dist
     import dfdx_b200
     device, lib = dev.device, dev.lib
-    g = torch.Generator(device="cpu").manual_seed(0xD0FD + int(args.workload[1]) + 1000 * rank)
+    g = torch.Generator(device="cpu").manual_seed(0xD0FD + (int(args.workload[1]) if args.workload[1].isdigit() else 9) + 1000 * rank)
     mib = 1024.0 * 1024.0
     if args.workload == "c1":
         a = (torch.rand(1024, 1024, generator=g) * 2 - 1).to(device)
@@ -199,6 +199,22 @@ def run_other_workload(args, dev, rank, world):
             dev.matmat_batch4_backward(q, gq, kt, gk, ds)    # dQ, dK
         flops, algo_bytes, bound, dtype = 2 * 6 * 256 * 512 * 512 * 64, 1136 * mib, "hbm", "f16"
         name = "config[2]: MatMatBatch4 f16 Q,K,V[16,16,512,64]: QK^T and PV, forward + backward (6 GEMM groups)"
+        peak_div = 1.0
+    elif args.workload == "attn":
+        # configuration 3's tensors through the fused kernels: softmax(Q K^T / sqrt(d)) V, forward + backward
+        # (the flop count is that of the same six GEMM groups; the recomputation inside the backward is not counted)
+        q = torch.randn(16, 512, 16, 64, generator=g).half().to(device).permute(0, 2, 1, 3)
+        k = torch.randn(16, 512, 16, 64, generator=g).half().to(device).permute(0, 2, 3, 1)
+        v = torch.randn(16, 512, 16, 64, generator=g).half().to(device).permute(0, 2, 1, 3)
+        do = torch.randn(16, 512, 16, 64, generator=g).half().to(device).permute(0, 2, 1, 3)
+        bufs = (dev.alloc_grad(q), dev.alloc_grad(k), dev.alloc_grad(v))
+
+        def step():
+            out, lse = dev.attention_forward(q, k, v, 0.125, want_lse=True)
+            dev.attention_backward(q, k, v, 0.125, out, lse, do, accumulate_into=bufs)
+        flops, algo_bytes, bound, dtype = 2 * 6 * 256 * 512 * 512 * 64, 9 * 16 * mib, "tensor", "f16"
+        name = ("config[2] shapes, fused: softmax(Q K^T / 8) V for f16 Q,K,V[16,16,512,64], forward + backward "
+                "(b200_attention_forward / _backward; flops of the six GEMM groups)")
         peak_div = 1.0
     else:
         x = torch.randn(32, 64, 56, 56, generator=g).to(device)
@@ -243,7 +259,7 @@ def run_other_workload(args, dev, rank, world):
         basis = f"{which} hbm_gbs; algorithmic bytes 1136 MiB per step"
     else:
         achieved, peak, unit = tflops / world, peaks["bf16_tflops"] / peak_div, "TFLOP/s"
-        basis = f"{which} bf16_tflops (burst) / 2 (tf32) / 3 (3xTF32)"
+        basis = (f"{which} bf16_tflops (burst) / 2 (tf32) / 3 (3xTF32)" if peak_div > 1 else f"{which} bf16_tflops (burst), f16 tensor rate")
     print(json.dumps({
         "metric": METRIC, "value": round(tflops, 3), "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": round(per_step, 4), "higher_is_better": True, "scaling": "weak",
@@ -349,7 +365,7 @@ def main():
                          "the fused attention kernels")
     ap.add_argument("--unfused-epilogues", action="store_true",
                     help="workload c5: bias / ReLU / score scale as separate ops after the GEMMs (the reference's op sequence)")
-    ap.add_argument("--workload", default="c2", choices=["c1", "c2", "c3", "c4", "c5"],
+    ap.add_argument("--workload", default="c2", choices=["c1", "c2", "c3", "c4", "c5", "attn"],
                     help="c2 (default) is the benchmark; c1 / c3 / c4 time the other configurations of the "
                          "path with the same harness (device-resident only; used for profiling)")
     args = ap.parse_args()
