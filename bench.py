@@ -337,8 +337,10 @@ def run_transformer(args, dev, rank, world):
         "dtype": "f16 compute, f32 accumulate, f32 master weights", "data": "synthetic",
         "config": {"workload": "config[4]: encoder 6 x (d_model 512, 8 heads, ffn 2048), batch 64/GPU, seq 256, MSE, Adam",
                    "parameters": n_params, "parallelism": f"dp{world}: NCCL all-reduce of one flat f32 gradient buffer",
-                   "matmuls": "all on libdfdx_b200 (MatMatBr + MatMatBatch4, forward and backward); LayerNorm, softmax, "
+                   "matmuls": "all on libdfdx_b200 (MatMatBr + MatMatBatch4, forward and backward); residual adds, casts, "
                               "loss and Adam are torch ops (separate non-matmul kernels in dfdx too)",
+                   "rowwise": "torch LayerNorm / sum" if args.unfused_epilogues else
+                              "LayerNorm forward + backward and the bias gradients on libdfdx_b200 (b200_layer_norm_*, b200_bias_grad)",
                    "epilogues": "bias, ReLU and score scale as separate torch ops" if args.unfused_epilogues else
                                 "Linear bias, feed-forward ReLU and the 1/sqrt(d) score scale fused into the forward GEMMs",
                    "attention": "two batched GEMMs + torch softmax" if (args.unfused_epilogues or args.unfused_attention)

@@ -67,6 +67,9 @@ SIGNATURES = {
     "b200_linear_forward": (_i, [_i, _sz, _sz, _sz, _sz, _vp, _szp, _vp, _szp, _vp, _i, _vp, _vp]),
     "b200_matmat_batch4_forward_scaled": (_i, [_i, _sz, _sz, _sz, _sz, _sz, _vp, _szp, _vp, _szp, _d, _vp, _vp]),
     "b200_attention_forward": (_i, [_i, _sz, _sz, _sz, _sz, _sz, _vp, _szp, _vp, _szp, _vp, _szp, _d, _vp, _szp, _vp, _vp]),
+    "b200_layer_norm_forward": (_i, [_i, _sz, _sz, _vp, _sz, _vp, _vp, _d, _vp, _sz, _vp, _vp]),
+    "b200_layer_norm_backward": (_i, [_i, _sz, _sz, _vp, _sz, _vp, _vp, _vp, _sz, _vp, _sz, _i, _vp, _vp, _vp]),
+    "b200_bias_grad": (_i, [_i, _sz, _sz, _vp, _sz, _vp, _vp]),
     "b200_attention_backward_workspace_bytes": (_sz, [_sz, _sz, _sz]),
     "b200_attention_backward": (_i, [_i, _sz, _sz, _sz, _sz, _sz, _vp, _szp, _vp, _szp, _vp, _szp, _d, _vp, _szp, _vp,
                                      _vp, _szp, _vp, _szp, _vp, _szp, _vp, _szp, _i, _vp, _sz, _vp]),

@@ -21,7 +21,7 @@ CSRC = PKG / "csrc"
 LIBDIR = PKG / "lib"
 OBJDIR = LIBDIR / "obj"
 LIB = LIBDIR / "libdfdx_b200.so"
-SOURCES = ["api.cu", "gemm_simt.cu", "gemm_tc.cu", "gemm_tc_pair.cu", "conv2d.cu", "attention.cu", "attention_bwd.cu"]
+SOURCES = ["api.cu", "gemm_simt.cu", "gemm_tc.cu", "gemm_tc_pair.cu", "conv2d.cu", "attention.cu", "attention_bwd.cu", "rowwise.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-lineinfo", "-O3", "-std=c++17",

@@ -385,6 +385,32 @@ int b200_attention_forward(int dtype, size_t batch, size_t heads, size_t s1, siz
                            v4, alpha, out, o4, lse, (cudaStream_t)stream);
 }
 
+int b200_layer_norm_forward(int dtype, size_t rows, size_t cols, const void* x, size_t x_ld, const void* gamma, const void* beta,
+                            double epsilon, void* y, size_t y_ld, float* stats, void* stream) {
+  if (!valid_dtype(dtype)) return B200_ERR_DTYPE;
+  if (rows && cols && (!x || !y)) return B200_ERR_NULL;
+  if (rows > 1 && (x_ld < cols || y_ld < cols)) return B200_ERR_STRIDE;
+  return layer_norm_forward(dtype, (int64_t)rows, (int64_t)cols, x, (int64_t)x_ld, gamma, beta, epsilon, y, (int64_t)y_ld, stats,
+                            (cudaStream_t)stream);
+}
+
+int b200_layer_norm_backward(int dtype, size_t rows, size_t cols, const void* x, size_t x_ld, const void* gamma,
+                             const float* stats, const void* grad_out, size_t grad_out_ld, void* grad_x, size_t grad_x_ld,
+                             int accumulate_x, float* grad_gamma, float* grad_beta, void* stream) {
+  if (!valid_dtype(dtype)) return B200_ERR_DTYPE;
+  if (rows && cols && (!x || !grad_out || !stats)) return B200_ERR_NULL;
+  if (rows > 1 && (x_ld < cols || grad_out_ld < cols || (grad_x && grad_x_ld < cols))) return B200_ERR_STRIDE;
+  return layer_norm_backward(dtype, (int64_t)rows, (int64_t)cols, x, (int64_t)x_ld, gamma, stats, grad_out, (int64_t)grad_out_ld,
+                             grad_x, (int64_t)grad_x_ld, accumulate_x, grad_gamma, grad_beta, (cudaStream_t)stream);
+}
+
+int b200_bias_grad(int dtype, size_t rows, size_t cols, const void* grad_out, size_t grad_out_ld, float* grad_bias, void* stream) {
+  if (!valid_dtype(dtype)) return B200_ERR_DTYPE;
+  if (rows && cols && (!grad_out || !grad_bias)) return B200_ERR_NULL;
+  if (rows > 1 && grad_out_ld < cols) return B200_ERR_STRIDE;
+  return column_sum(dtype, (int64_t)rows, (int64_t)cols, grad_out, (int64_t)grad_out_ld, grad_bias, (cudaStream_t)stream);
+}
+
 size_t b200_attention_backward_workspace_bytes(size_t batch, size_t heads, size_t s1) {
   return attention_backward_workspace_bytes((int64_t)batch, (int64_t)heads, (int64_t)s1);
 }

@@ -84,6 +84,14 @@ int attention_backward(int dtype, int64_t B, int64_t H, int64_t s1, int64_t s2, 
                        const int64_t gs[4], void* gq, const int64_t gqs[4], void* gk, const int64_t gks[4], void* gv,
                        const int64_t gvs[4], int accumulate, void* workspace, size_t workspace_bytes, cudaStream_t stream);
 
+// Row-wise kernels (rowwise.cu); leading dimensions in elements.
+int layer_norm_forward(int dtype, int64_t rows, int64_t cols, const void* x, int64_t x_ld, const void* gamma, const void* beta,
+                       double eps, void* y, int64_t y_ld, float* stats, cudaStream_t stream);
+int layer_norm_backward(int dtype, int64_t rows, int64_t cols, const void* x, int64_t x_ld, const void* gamma, const float* stats,
+                        const void* g, int64_t g_ld, void* gx, int64_t gx_ld, int accumulate_x, float* ggamma, float* gbeta,
+                        cudaStream_t stream);
+int column_sum(int dtype, int64_t rows, int64_t cols, const void* g, int64_t ld, float* out, cudaStream_t stream);
+
 // Lowers one problem to a kernel family according to b200_set_path and eligibility.
 int run_gemm(const GemmProblem& p, cudaStream_t stream);
 

@@ -1,0 +1,344 @@
+// Row-wise kernels that sit next to the GEMMs in a Transformer training step: LayerNorm forward / backward and the
+// bias gradient (a column sum).  All are HBM-bound: every tensor is read from DRAM once (re-reads of a row hit
+// L1 / L2) and written once; statistics and reductions are f32.
+//
+//   layer_norm_fwd_kernel   y = (x - mean) / sqrt(var + eps) * gamma + beta over the last axis
+//                           (dfdx-core/src/tensor_ops/normalize.rs:33-50 as used by dfdx/src/nn/layers/layer_norm1d.rs:87-91:
+//                           mean, centred, mean of squares + epsilon, sqrt, divide; then * gamma + beta: nine kernels and
+//                           as many passes over the tensor in the reference, one here)
+//   layer_norm_bwd_kernel   dx = rstd * (g*gamma - mean(g*gamma) - xhat * mean(g*gamma*xhat)),
+//                           dgamma += sum_rows g * xhat,  dbeta += sum_rows g   (the tape entries of the same ops)
+//   column_sum_kernel       out[j] += sum_i g[i, j]   (backward of `bias.broadcast_like(&x) + x`, bias1d.rs:66-79)
+// One warp per row; lanes walk the row in 16-byte vectors when the layout allows, element-wise otherwise.
+#include "common.cuh"
+
+namespace b200 {
+
+namespace {
+
+template <typename T> struct Vec;
+template <> struct Vec<float> { static constexpr int N = 4; };
+template <> struct Vec<__half> { static constexpr int N = 8; };
+
+__device__ __forceinline__ float to_f(float x) { return x; }
+__device__ __forceinline__ float to_f(__half x) { return __half2float(x); }
+template <typename T> __device__ __forceinline__ T from_f(float x);
+template <> __device__ __forceinline__ float from_f<float>(float x) { return x; }
+template <> __device__ __forceinline__ __half from_f<__half>(float x) { return __float2half_rn(x); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// Loads the n (= Vec<T>::N) elements that start at column c of a row into f[]; vec: 16-byte access is legal.
+template <typename T>
+__device__ __forceinline__ void load_vec(const T* row, int c, int cols, bool vec, float* f) {
+  constexpr int N = Vec<T>::N;
+  if (vec) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(row + c);
+    const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+    for (int q = 0; q < N; ++q) f[q] = to_f(e[q]);
+  } else {
+#pragma unroll
+    for (int q = 0; q < N; ++q) f[q] = (c + q < cols) ? to_f(row[c + q]) : 0.f;
+  }
+}
+template <typename T>
+__device__ __forceinline__ void store_vec(T* row, int c, int cols, bool vec, const float* f) {
+  constexpr int N = Vec<T>::N;
+  if (vec) {
+    uint4 raw;
+    T* e = reinterpret_cast<T*>(&raw);
+#pragma unroll
+    for (int q = 0; q < N; ++q) e[q] = from_f<T>(f[q]);
+    *reinterpret_cast<uint4*>(row + c) = raw;
+  } else {
+#pragma unroll
+    for (int q = 0; q < N; ++q)
+      if (c + q < cols) row[c + q] = from_f<T>(f[q]);
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) layer_norm_fwd_kernel(const T* __restrict__ x, long long x_ld, const T* __restrict__ gamma,
+                                                             const T* __restrict__ beta, float eps, T* __restrict__ y,
+                                                             long long y_ld, float* __restrict__ stats, long long rows, int cols,
+                                                             int vec) {
+  constexpr int N = Vec<T>::N;
+  const int lane = threadIdx.x & 31;
+  const long long warp0 = (long long)blockIdx.x * 8 + (threadIdx.x >> 5), nwarps = (long long)gridDim.x * 8;
+  const float inv_n = 1.f / (float)cols;
+  for (long long r = warp0; r < rows; r += nwarps) {
+    const T* xr = x + r * x_ld;
+    float s = 0.f;
+    for (int c = lane * N; c < cols; c += 32 * N) {
+      float f[N];
+      load_vec(xr, c, cols, vec, f);
+#pragma unroll
+      for (int q = 0; q < N; ++q) s += f[q];
+    }
+    const float mean = warp_sum(s) * inv_n;
+    float sq = 0.f;
+    for (int c = lane * N; c < cols; c += 32 * N) {
+      float f[N];
+      load_vec(xr, c, cols, vec, f);
+#pragma unroll
+      for (int q = 0; q < N; ++q) {
+        const float d = (c + q < cols) ? f[q] - mean : 0.f;
+        sq = fmaf(d, d, sq);
+      }
+    }
+    const float rstd = 1.f / sqrtf(warp_sum(sq) * inv_n + eps);
+    T* yr = y + r * y_ld;
+    for (int c = lane * N; c < cols; c += 32 * N) {
+      float f[N], gm[N], bt[N];
+      load_vec(xr, c, cols, vec, f);
+      if (gamma) load_vec(gamma, c, cols, vec, gm);
+      if (beta) load_vec(beta, c, cols, vec, bt);
+#pragma unroll
+      for (int q = 0; q < N; ++q) {
+        float v = (f[q] - mean) * rstd;
+        if (gamma) v *= gm[q];
+        if (beta) v += bt[q];
+        f[q] = v;
+      }
+      store_vec(yr, c, cols, vec, f);
+    }
+    if (stats && lane == 0) { stats[2 * r] = mean; stats[2 * r + 1] = rstd; }
+  }
+}
+
+// MAXV vectors per lane: cols <= 32 * N * MAXV.  Per-lane partial sums of dgamma / dbeta live in registers over all
+// rows of the warp, are combined across the block's warps in shared memory and added to global memory once per block.
+template <typename T, int MAXV>
+__global__ void __launch_bounds__(256) layer_norm_bwd_kernel(const T* __restrict__ x, long long x_ld, const T* __restrict__ gamma,
+                                                             const float* __restrict__ stats, const T* __restrict__ g,
+                                                             long long g_ld, T* __restrict__ gx, long long gx_ld, int accumulate_x,
+                                                             float* __restrict__ ggamma, float* __restrict__ gbeta, long long rows,
+                                                             int cols, int vec) {
+  constexpr int N = Vec<T>::N;
+  __shared__ float red[8][32 * N + 1];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const long long warp0 = (long long)blockIdx.x * 8 + warp, nwarps = (long long)gridDim.x * 8;
+  const float inv_n = 1.f / (float)cols;
+  float dg[MAXV][N], db[MAXV][N];
+#pragma unroll
+  for (int v = 0; v < MAXV; ++v)
+#pragma unroll
+    for (int q = 0; q < N; ++q) dg[v][q] = db[v][q] = 0.f;
+
+  for (long long r = warp0; r < rows; r += nwarps) {
+    const T* xr = x + r * x_ld;
+    const T* gr = g + r * g_ld;
+    const float mean = stats[2 * r], rstd = stats[2 * r + 1];
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int v = 0; v < MAXV; ++v) {
+      const int c = (v * 32 + lane) * N;
+      if (c < cols) {
+        float fx[N], fg[N], gm[N];
+        load_vec(xr, c, cols, vec, fx);
+        load_vec(gr, c, cols, vec, fg);
+        if (gamma) load_vec(gamma, c, cols, vec, gm);
+#pragma unroll
+        for (int q = 0; q < N; ++q) {
+          const float xh = (c + q < cols) ? (fx[q] - mean) * rstd : 0.f;
+          const float gg = gamma ? fg[q] * gm[q] : fg[q];
+          s1 += gg;
+          s2 = fmaf(gg, xh, s2);
+          dg[v][q] = fmaf(fg[q], xh, dg[v][q]);
+          db[v][q] += fg[q];
+        }
+      }
+    }
+    const float c1 = warp_sum(s1) * inv_n, c2 = warp_sum(s2) * inv_n;
+    if (gx) {
+      T* or_ = gx + r * gx_ld;
+#pragma unroll
+      for (int v = 0; v < MAXV; ++v) {
+        const int c = (v * 32 + lane) * N;
+        if (c < cols) {
+          float fx[N], fg[N], gm[N], old[N];
+          load_vec(xr, c, cols, vec, fx);
+          load_vec(gr, c, cols, vec, fg);
+          if (gamma) load_vec(gamma, c, cols, vec, gm);
+          if (accumulate_x) load_vec(or_, c, cols, vec, old);
+#pragma unroll
+          for (int q = 0; q < N; ++q) {
+            const float xh = (fx[q] - mean) * rstd;
+            const float gg = gamma ? fg[q] * gm[q] : fg[q];
+            float d = rstd * (gg - c1 - xh * c2);
+            if (accumulate_x) d += old[q];
+            fx[q] = d;
+          }
+          store_vec(or_, c, cols, vec, fx);
+        }
+      }
+    }
+  }
+  // block reduction of the column sums, one 32*N-column slab at a time
+#pragma unroll
+  for (int v = 0; v < MAXV; ++v) {
+    if (v * 32 * N >= cols) break;
+#pragma unroll
+    for (int pass = 0; pass < 2; ++pass) {
+      float* out = pass == 0 ? ggamma : gbeta;
+      __syncthreads();
+#pragma unroll
+      for (int q = 0; q < N; ++q) red[warp][lane * N + q] = pass == 0 ? dg[v][q] : db[v][q];
+      __syncthreads();
+      if (out) {
+        for (int i = threadIdx.x; i < 32 * N; i += 256) {
+          const int col = v * 32 * N + i;
+          if (col < cols) {
+            float t = 0.f;
+#pragma unroll
+            for (int w = 0; w < 8; ++w) t += red[w][i];
+            atomicAdd(out + col, t);
+          }
+        }
+      }
+    }
+  }
+}
+
+// out[j] += sum_i g[i, j].  grid.x walks column slabs of 32*N, grid.y row slabs; one atomic per column and block.
+template <typename T>
+__global__ void __launch_bounds__(256) column_sum_kernel(const T* __restrict__ g, long long ld, float* __restrict__ out,
+                                                         long long rows, int cols, int vec) {
+  constexpr int N = Vec<T>::N;
+  __shared__ float red[8][32 * N + 1];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int c = (blockIdx.x * 32 + lane) * N;
+  float acc[N];
+#pragma unroll
+  for (int q = 0; q < N; ++q) acc[q] = 0.f;
+  if (c < cols) {
+    for (long long r = (long long)blockIdx.y * 8 + warp; r < rows; r += (long long)gridDim.y * 8) {
+      float f[N];
+      load_vec(g + r * ld, c, cols, vec, f);
+#pragma unroll
+      for (int q = 0; q < N; ++q) acc[q] += f[q];
+    }
+  }
+#pragma unroll
+  for (int q = 0; q < N; ++q) red[warp][lane * N + q] = acc[q];
+  __syncthreads();
+  for (int i = threadIdx.x; i < 32 * N; i += 256) {
+    const int col = blockIdx.x * 32 * N + i;
+    if (col < cols) {
+      float t = 0.f;
+#pragma unroll
+      for (int w = 0; w < 8; ++w) t += red[w][i];
+      atomicAdd(out + col, t);
+    }
+  }
+}
+
+bool vec_ok(size_t es, int64_t cols, std::initializer_list<int64_t> lds, std::initializer_list<const void*> ptrs) {
+  const int64_t n = 16 / (int64_t)es;
+  if (cols % n) return false;
+  for (int64_t ld : lds)
+    if (ld % n) return false;
+  for (const void* p : ptrs)
+    if ((uintptr_t)p & 15) return false;
+  return true;
+}
+
+template <typename T>
+int ln_forward_t(int64_t rows, int64_t cols, const void* x, int64_t x_ld, const void* gamma, const void* beta, double eps,
+                 void* y, int64_t y_ld, float* stats, cudaStream_t stream) {
+  DeviceState* ds = device_state();
+  const int vec = vec_ok(sizeof(T), cols, {x_ld, y_ld}, {x, y, gamma, beta}) ? 1 : 0;
+  long long blocks = (rows + 7) / 8;
+  const long long cap = (long long)ds->sm_count * 16;
+  if (blocks > cap) blocks = cap;
+  layer_norm_fwd_kernel<T><<<(unsigned)blocks, 256, 0, stream>>>((const T*)x, x_ld, (const T*)gamma, (const T*)beta, (float)eps,
+                                                                 (T*)y, y_ld, stats, rows, (int)cols, vec);
+  count_launch(false);
+  return note_cuda_error(cudaGetLastError(), "layer_norm forward launch");
+}
+
+template <typename T>
+int ln_backward_t(int64_t rows, int64_t cols, const void* x, int64_t x_ld, const void* gamma, const float* stats, const void* g,
+                  int64_t g_ld, void* gx, int64_t gx_ld, int accumulate_x, float* ggamma, float* gbeta, cudaStream_t stream) {
+  DeviceState* ds = device_state();
+  constexpr int N = Vec<T>::N;
+  const int vec = vec_ok(sizeof(T), cols, {x_ld, g_ld, gx ? gx_ld : 0}, {x, g, gx, gamma}) ? 1 : 0;
+  long long blocks = (rows + 7) / 8;
+  const long long cap = (long long)ds->sm_count * 4;        // few blocks: each ends with `cols` atomics per output
+  if (blocks > cap) blocks = cap;
+  const int64_t vecs = (cols + 32 * N - 1) / (32 * N);
+  auto launch = [&](auto kernel) {
+    kernel<<<(unsigned)blocks, 256, 0, stream>>>((const T*)x, x_ld, (const T*)gamma, stats, (const T*)g, g_ld, (T*)gx, gx_ld,
+                                                 accumulate_x, ggamma, gbeta, rows, (int)cols, vec);
+  };
+  if (vecs <= 2) launch(layer_norm_bwd_kernel<T, 2>);
+  else if (vecs <= 4) launch(layer_norm_bwd_kernel<T, 4>);
+  else if (vecs <= 8) launch(layer_norm_bwd_kernel<T, 8>);
+  else return B200_ERR_LIMIT;
+  count_launch(false);
+  return note_cuda_error(cudaGetLastError(), "layer_norm backward launch");
+}
+
+template <typename T>
+int column_sum_t(int64_t rows, int64_t cols, const void* g, int64_t ld, float* out, cudaStream_t stream) {
+  DeviceState* ds = device_state();
+  constexpr int N = Vec<T>::N;
+  const int vec = vec_ok(sizeof(T), cols, {ld}, {g}) ? 1 : 0;
+  const long long gx = (cols + 32 * N - 1) / (32 * N);
+  long long gy = (rows + 63) / 64;                           // at least 8 rows per warp
+  const long long cap = ((long long)ds->sm_count * 8 + gx - 1) / gx;
+  if (gy > cap) gy = cap;
+  if (gy < 1) gy = 1;
+  if (gx > 0x7fffffffLL || gy > 65535) return B200_ERR_LIMIT;
+  column_sum_kernel<T><<<dim3((unsigned)gx, (unsigned)gy), 256, 0, stream>>>((const T*)g, ld, out, rows, (int)cols, vec);
+  count_launch(false);
+  return note_cuda_error(cudaGetLastError(), "column sum launch");
+}
+
+}  // namespace
+
+int layer_norm_forward(int dtype, int64_t rows, int64_t cols, const void* x, int64_t x_ld, const void* gamma, const void* beta,
+                       double eps, void* y, int64_t y_ld, float* stats, cudaStream_t stream) {
+  if (rows == 0 || cols == 0) return B200_OK;
+  if (!device_state()) return note_cuda_error(cudaErrorInitializationError, "b200_init not called on this device");
+  if (cols > 0x7fffffffLL) return B200_ERR_LIMIT;
+  switch (dtype) {
+    case B200_F32: return ln_forward_t<float>(rows, cols, x, x_ld, gamma, beta, eps, y, y_ld, stats, stream);
+    case B200_F16:
+    case B200_AMP_F16: return ln_forward_t<__half>(rows, cols, x, x_ld, gamma, beta, eps, y, y_ld, stats, stream);
+    default: return B200_ERR_UNSUPPORTED;
+  }
+}
+
+int layer_norm_backward(int dtype, int64_t rows, int64_t cols, const void* x, int64_t x_ld, const void* gamma, const float* stats,
+                        const void* g, int64_t g_ld, void* gx, int64_t gx_ld, int accumulate_x, float* ggamma, float* gbeta,
+                        cudaStream_t stream) {
+  if (rows == 0 || cols == 0) return B200_OK;
+  if (!device_state()) return note_cuda_error(cudaErrorInitializationError, "b200_init not called on this device");
+  switch (dtype) {
+    case B200_F32: return ln_backward_t<float>(rows, cols, x, x_ld, gamma, stats, g, g_ld, gx, gx_ld, accumulate_x, ggamma, gbeta, stream);
+    case B200_F16:
+    case B200_AMP_F16:
+      return ln_backward_t<__half>(rows, cols, x, x_ld, gamma, stats, g, g_ld, gx, gx_ld, accumulate_x, ggamma, gbeta, stream);
+    default: return B200_ERR_UNSUPPORTED;
+  }
+}
+
+int column_sum(int dtype, int64_t rows, int64_t cols, const void* g, int64_t ld, float* out, cudaStream_t stream) {
+  if (rows == 0 || cols == 0) return B200_OK;
+  if (!device_state()) return note_cuda_error(cudaErrorInitializationError, "b200_init not called on this device");
+  if (cols > 0x7fffffffLL) return B200_ERR_LIMIT;
+  switch (dtype) {
+    case B200_F32: return column_sum_t<float>(rows, cols, g, ld, out, stream);
+    case B200_F16:
+    case B200_AMP_F16: return column_sum_t<__half>(rows, cols, g, ld, out, stream);
+    default: return B200_ERR_UNSUPPORTED;
+  }
+}
+
+}  // namespace b200

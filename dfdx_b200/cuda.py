@@ -241,6 +241,36 @@ class Cuda:
             gv.data_ptr(), _st(v.stride()), acc, ws.data_ptr(), ws.numel(), self._stream()), "b200_attention_backward")
         return self.grad_view(gq, q), self.grad_view(gk, k), self.grad_view(gv, v)
 
+    # -- row-wise neighbours of the GEMMs ---------------------------------------------------------------
+    def layer_norm_forward(self, x, gamma=None, beta=None, eps: float = 1e-5, want_stats: bool = False):
+        """`LayerNorm1D::try_forward` over the last axis of a contiguous tensor.  Returns (y, stats or None)."""
+        cols = x.shape[-1]
+        rows = x.numel() // max(cols, 1)
+        y = self._empty(tuple(x.shape), x)
+        stats = torch.empty((rows, 2), dtype=torch.float32, device=x.device) if want_stats else None
+        check(self.lib.b200_layer_norm_forward(self._dtype(x), rows, cols, x.data_ptr(), cols, _ptr(gamma), _ptr(beta),
+                                               float(eps), y.data_ptr(), cols, _ptr(stats), self._stream()),
+              "b200_layer_norm_forward")
+        return y, stats
+
+    def layer_norm_backward(self, x, gamma, stats, grad_out, grad_gamma=None, grad_beta=None):
+        """Returns grad_x; adds the f32 column sums into grad_gamma / grad_beta (f32 tensors of `cols` elements)."""
+        cols = x.shape[-1]
+        rows = x.numel() // max(cols, 1)
+        gx = self._empty(tuple(x.shape), x)
+        check(self.lib.b200_layer_norm_backward(self._dtype(x), rows, cols, x.data_ptr(), cols, _ptr(gamma),
+                                                stats.data_ptr(), grad_out.data_ptr(), cols, gx.data_ptr(), cols, 0,
+                                                _ptr(grad_gamma), _ptr(grad_beta), self._stream()),
+              "b200_layer_norm_backward")
+        return gx
+
+    def bias_grad(self, grad_out, grad_bias) -> None:
+        """grad_bias (f32, `cols` elements) += column sums of the contiguous (..., cols) tensor grad_out."""
+        cols = grad_out.shape[-1]
+        rows = grad_out.numel() // max(cols, 1)
+        check(self.lib.b200_bias_grad(self._dtype(grad_out), rows, cols, grad_out.data_ptr(), cols, grad_bias.data_ptr(),
+                                      self._stream()), "b200_bias_grad")
+
     # -- TryMatMul (matmul/mod.rs:133-311) ---------------------------------------------------------
     def matmul(self, lhs: torch.Tensor, rhs: torch.Tensor):
         """Rank dispatch of `TryMatMul`.  Returns (out, backward) where

@@ -1,6 +1,6 @@
 """Transformer-encoder training step whose matrix multiplications all run on this library.
 
-This is measurement harness for BASELINE configuration 5, not a re-implementation of dfdx's nn
+This is a measurement harness for benchmark configuration 5, not a re-implementation of dfdx's nn
 stack: the block structure restates dfdx's `EncoderBlock` (dfdx/src/nn/layers/transformer.rs:24-47:
 ResidualAdd(MultiHeadAttention) -> LayerNorm1D -> ResidualAdd(Linear, ReLU, Linear) -> LayerNorm1D)
 and `MultiHeadAttention::try_forward` (multi_head_attention.rs:105-146: three Linear layers, the
@@ -11,8 +11,9 @@ backward).  With `fused="attention"` the whole scores / softmax / weighted-sum s
 fused attention kernels.  With `fused=True` (default) the ops that directly follow a GEMM in the forward pass — Linear's
 bias add, the feed-forward ReLU, the 1/sqrt(d) scale of the scores — run in that GEMM's epilogue
 (`b200_linear_forward`, `b200_matmat_batch4_forward_scaled`); with `fused=False` they are separate torch
-ops, as they are separate kernels in dfdx.  Residual, LayerNorm, softmax, the MSE loss and Adam are plain
-torch ops either way.
+ops, as they are separate kernels in dfdx; any fused mode also runs LayerNorm (forward and backward) and the bias
+gradient on this library's row-wise kernels.  Residual adds, softmax (unfused attention), the MSE loss and Adam are
+plain torch ops either way.
 
 Parameters are f32 master weights; each step computes in f16 (`AMP<f16>`-like: f16 storage, f32
 accumulation inside the GEMMs) and Adam updates the f32 masters.
@@ -81,7 +82,9 @@ class _FusedLinear(torch.autograd.Function):
             g = torch.ops.aten.threshold_backward(g, y, 0.0)
         gx, gw = dev.alloc_grad(x), dev.alloc_grad(w_view)
         dev.matmat_br_backward(x, gx, w_view, gw, g)
-        grad_bias = g.sum(dim=(0, 1), dtype=torch.float32).to(g.dtype)
+        grad_bias = torch.zeros(g.shape[-1], dtype=torch.float32, device=g.device)
+        dev.bias_grad(g, grad_bias)                                # f32 column sums, one pass over g
+        grad_bias = grad_bias.to(g.dtype)
         return None, dev.grad_view(gx, x), gw.view_as(weight), grad_bias, None
 
 
@@ -125,6 +128,27 @@ class _FusedAttention(torch.autograd.Function):
         q, k, v, out, lse = ctx.saved_tensors
         gq, gk, gv = ctx.dev.attention_backward(q, k, v, ctx.alpha, out, lse, grad_out)
         return None, gq, gk, gv, None
+
+
+class _LayerNorm(torch.autograd.Function):
+    """`LayerNorm1D` as one forward and one backward kernel (`b200_layer_norm_forward` / `_backward`); gamma and beta
+    are the f16 compute copies, their gradients come back as f32 column sums."""
+
+    @staticmethod
+    def forward(ctx, dev: Cuda, x, gamma, beta, eps: float):
+        x = x.contiguous()
+        y, stats = dev.layer_norm_forward(x, gamma, beta, eps, want_stats=True)
+        ctx.dev = dev
+        ctx.save_for_backward(x, gamma, stats)
+        return y
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        x, gamma, stats = ctx.saved_tensors
+        gg = torch.zeros(gamma.shape, dtype=torch.float32, device=x.device)
+        gb = torch.zeros(gamma.shape, dtype=torch.float32, device=x.device)
+        gx = ctx.dev.layer_norm_backward(x, gamma, stats, grad_out.contiguous(), gg, gb)
+        return None, gx, gg.to(gamma.dtype), gb.to(gamma.dtype), None
 
 
 class Linear(torch.nn.Module):
@@ -180,6 +204,8 @@ class EncoderBlock(torch.nn.Module):
         self.norm2 = torch.nn.LayerNorm(model, device=dev.device)
 
     def _norm(self, ln, x):
+        if self.attn.fused:
+            return _LayerNorm.apply(self.attn.dev, x, ln.weight.half(), ln.bias.half(), ln.eps)
         return F.layer_norm(x, ln.normalized_shape, ln.weight.half(), ln.bias.half(), ln.eps)
 
     def forward(self, x):

@@ -269,6 +269,33 @@ int b200_attention_backward(int dtype, size_t batch, size_t heads, size_t s1, si
                             void* grad_v, const size_t grad_v_strides[4],
                             int accumulate, void* workspace, size_t workspace_bytes, void* stream);
 
+/* ---- row-wise neighbours of the GEMMs (API additions) --------------------------------------------- */
+
+/* `LayerNorm1D::try_forward` (dfdx/src/nn/layers/layer_norm1d.rs:87-91) in one kernel:
+ *     y[r, :] = (x[r, :] - mean_r) / sqrt(mean((x[r, :] - mean_r)^2) + epsilon) * gamma + beta
+ * i.e. `normalize::<last axis>(epsilon)` (dfdx-core/src/tensor_ops/normalize.rs:33-50: mean, subtract, square,
+ * mean, add epsilon, sqrt, divide) followed by the broadcast multiply and add.  x, y: rows x cols with unit
+ * column stride and row strides x_ld / y_ld (elements); gamma, beta: cols elements of the same dtype or NULL
+ * (NULL, NULL = plain normalize).  `stats` is NULL or 2*rows floats that receive (mean, 1/std) per row for the
+ * backward.  f32 and f16 (f32 statistics); f64 returns B200_ERR_UNSUPPORTED. */
+int b200_layer_norm_forward(int dtype, size_t rows, size_t cols, const void* x, size_t x_ld,
+                            const void* gamma, const void* beta, double epsilon,
+                            void* y, size_t y_ld, float* stats, void* stream);
+
+/* The tape entries of the same ops in one kernel: grad_x (NULL = not wanted; written, or added to when
+ * accumulate_x != 0) and the f32 sums grad_gamma[j] += sum_r g[r,j] * xhat[r,j], grad_beta[j] += sum_r g[r,j]
+ * (either may be NULL; they are ADDED to, so zero them or pass f32 gradient buffers).  cols <= 1024 (f32) /
+ * 2048 (f16), else B200_ERR_LIMIT. */
+int b200_layer_norm_backward(int dtype, size_t rows, size_t cols, const void* x, size_t x_ld, const void* gamma,
+                             const float* stats, const void* grad_out, size_t grad_out_ld,
+                             void* grad_x, size_t grad_x_ld, int accumulate_x,
+                             float* grad_gamma, float* grad_beta, void* stream);
+
+/* Backward of `bias.broadcast_like(&x) + x` (dfdx/src/nn/layers/bias1d.rs:66-79; the `sum` over the
+ * broadcast axes): grad_bias[j] += sum_r grad_out[r, j] in f32, one pass over grad_out. */
+int b200_bias_grad(int dtype, size_t rows, size_t cols, const void* grad_out, size_t grad_out_ld,
+                   float* grad_bias, void* stream);
+
 /* ---- conv2d (unfold + GEMM lowering) ---------------------------------------------------------- */
 
 /* Bytes of caller-provided scratch the conv2d entry points need; `backward` != 0 selects the

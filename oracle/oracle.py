@@ -266,6 +266,30 @@ def attention_backward(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, alpha:
     return g_q, g_k, g_v
 
 
+def layer_norm(x: torch.Tensor, gamma: torch.Tensor = None, beta: torch.Tensor = None, eps: float = 1e-5):
+    """`normalize::<last axis>(epsilon)` step by step as dfdx-core/src/tensor_ops/normalize.rs:33-50 writes it (mean,
+    subtract, square, mean, + epsilon, sqrt, divide), then `* gamma + beta` (dfdx/src/nn/layers/layer_norm1d.rs:87-91),
+    in f64.  Returns (y, backward); backward(grad_out) -> (grad_x, grad_gamma, grad_beta)."""
+    x64 = x.detach().cpu().to(torch.float64)
+    mean = x64.mean(dim=-1, keepdim=True)
+    centered = x64 - mean
+    std = (centered.square().mean(dim=-1, keepdim=True) + float(eps)).sqrt()
+    xhat = centered / std
+    g64 = None if gamma is None else gamma.detach().cpu().to(torch.float64)
+    y = xhat if g64 is None else xhat * g64
+    if beta is not None:
+        y = y + beta.detach().cpu().to(torch.float64)
+
+    def backward(grad_out: torch.Tensor):
+        go = grad_out.detach().cpu().to(torch.float64)
+        gg = go if g64 is None else go * g64
+        gx = (gg - gg.mean(dim=-1, keepdim=True) - xhat * (gg * xhat).mean(dim=-1, keepdim=True)) / std
+        flat = go.reshape(-1, go.shape[-1])
+        return gx, (flat * xhat.reshape(flat.shape)).sum(0), flat.sum(0)
+
+    return y, backward
+
+
 def rel_frobenius(got: torch.Tensor, want: torch.Tensor) -> float:
     """||got - want||_F / ||want||_F in f64 (0/0 -> 0)."""
     g = got.detach().cpu().to(torch.float64)

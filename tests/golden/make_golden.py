@@ -11,6 +11,7 @@ Sources (dfdx v0.13.0):
     dfdx-core/src/tensor_ops/matmul/mod.rs      (tests at :327-768)
     dfdx-core/src/tensor_ops/conv2d/tests.rs
     dfdx/src/nn/layers/linear.rs                (tests at :97-204)
+    dfdx-core/src/tensor_ops/normalize.rs       (tests at :52-127; the normalisation inside LayerNorm1D)
 """
 from __future__ import annotations
 
@@ -26,6 +27,7 @@ FILES = {
     "matmul": "dfdx-core/src/tensor_ops/matmul/mod.rs",
     "conv2d": "dfdx-core/src/tensor_ops/conv2d/tests.rs",
     "linear": "dfdx/src/nn/layers/linear.rs",
+    "normalize": "dfdx-core/src/tensor_ops/normalize.rs",
 }
 
 

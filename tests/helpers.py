@@ -39,6 +39,10 @@ class OracleBackend:
     def conv2d(self, x, w, **kw):
         return self.o.conv2d(x, w, **kw)
 
+    def normalize(self, x, eps):
+        y, bwd = self.o.layer_norm(x, None, None, eps)
+        return y, lambda go: bwd(go)[0]
+
     def linear(self, x, weight_view, bias, relu=False):
         return self.o.fused_matmul(x, weight_view, 1.0, bias, relu)
 
@@ -71,6 +75,11 @@ class CudaBackend:
         """`Linear::try_forward` through the fused entry point (x of rank 1..3 is viewed as rank 3)."""
         x3 = x.reshape((1,) * (3 - x.dim()) + tuple(x.shape))
         return self.dev.linear_forward(x3, weight_view, bias, relu).reshape(tuple(x.shape[:-1]) + (weight_view.shape[1],))
+
+    def normalize(self, x, eps):
+        """`normalize` over the last axis through the LayerNorm kernels (gamma = beta = NULL)."""
+        y, stats = self.dev.layer_norm_forward(x, None, None, eps, want_stats=True)
+        return y, lambda go: self.dev.layer_norm_backward(x, None, stats, go.to(self.dtype).to(self.dev.device).contiguous())
 
     def conv2d(self, x, w, **kw):
         out, bwd = self.dev.conv2d(x, w, **kw)

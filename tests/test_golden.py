@@ -149,6 +149,19 @@ def test_linear_fused_forward(be, name):
     _check(be, y_relu, dict(a[0], value=want.tolist()))
 
 
+# ------------------------------------------------------------------------------------------ normalize
+@pytest.mark.parametrize("name", ["test_1d_normalize_axis_last", "test_2d_normalize_axis_last"])
+def test_normalize_last_axis(be, name):
+    """dfdx-core/src/tensor_ops/normalize.rs:52-96: r = a.normalize(1e-5); g = r.exp().mean().backward()."""
+    if be.dtype == torch.float64 and be.name == "cuda":
+        pytest.skip("the row-wise kernels serve f32 and f16")
+    t, a = _split(golden("normalize")[name])
+    x = be.tensor(t[0])
+    r, bwd = be.normalize(x, 1e-5)
+    _check(be, r, a[0])
+    _check(be, bwd(d_exp_mean(be.host(r))), a[1])
+
+
 # ------------------------------------------------------------------------------------------ conv2d
 CONV_BIAS_CASES = {
     "test_conv2d_default_stride_and_padding": dict(stride=1, padding=0),
