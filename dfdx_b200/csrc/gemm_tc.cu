@@ -53,7 +53,7 @@ using namespace tcx;
 template <int BN>
 __global__ void __launch_bounds__(CfgH<BN>::THREADS, 1)
 gemm_f16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
-                const TcArgs g) {
+                const __grid_constant__ CUtensorMap tma_c, const TcArgs g) {
   using C = CfgH<BN>;
   constexpr int STAGES = C::STAGES;
 
@@ -162,7 +162,7 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
     __syncwarp();
   } else {
     // ------------------------------------------------------------------ epilogue (warps 0..3)
-    uint32_t tcount = 0;
+    uint32_t tcount = 0, store_count = 0;
     bool ok = true;
     for (long long unit = blockIdx.x; ok && unit < g.total_units; unit += gridDim.x, ++tcount) {
       const Unit un = decode_unit(g, unit, total_kb);
@@ -181,9 +181,62 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
         for (int pc = 0; pc < AHEAD; ++pc)
           if (t.nt * BN + pc * 32 + 32 <= g.n) load_old_f16(orow + pc * 32, oldv[pc], g.c_wide);
       }
-      if (!mbar_wait(smem_u32(&bar_tfull[buf]), tph, abortp, g.wait_limit)) { ok = false; break; }
+      bool got = mbar_wait(smem_u32(&bar_tfull[buf]), tph, abortp, g.wait_limit);
+      // the staged epilogue below synchronises the four epilogue warps with named barriers, which have no
+      // time-out: all of them take this tile or none does
+      got = g.c_tma ? named_barrier_and(1, 128, got) : __all_sync(0xffffffffu, got);
+      if (!got) { ok = false; break; }
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16) + buf * BN;
+      if (g.c_tma) {
+        // Output through shared memory and TMA: per-thread row stores hand the memory system 32 separate
+        // 32-byte pieces per instruction (rows are ldc apart), which bounds GEMMs with a short K and a wide
+        // output; a staged 128 x 64 group leaves as one bulk tensor store of whole 128-byte lines.
+        const int r_in = warp * 32 + lane;
+        const uint32_t sw = (uint32_t)(r_in & 7);
+#pragma unroll
+        for (int c2 = 0; c2 < BN / 64; ++c2) {
+          const int col0 = t.nt * BN + c2 * 64;
+          if (col0 < g.n) {                          // block-uniform
+            const uint32_t stage = smem_base + C::OFF_OUT + (store_count & 1u) * C::OUT_BYTES;
+            if (threadIdx.x == 0) bulk_wait_group_read<1>();   // the store that last used this buffer has read it
+            named_barrier_sync(1, 128);
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              uint32_t v[32];
+              tmem_ld_32x32(taddr + c2 * 64 + h * 32, v);
+              tmem_wait_ld();
+              float f[32];
+#pragma unroll
+              for (int q = 0; q < 32; ++q) f[q] = __uint_as_float(v[q]);
+              if (g.fused && row < g.m) {
+                const int valid = (g.n - col0 - h * 32) < 32 ? (g.n - col0 - h * 32) : 32;
+                if (valid > 0) fused_epilogue<__half>(f, g, row, col0 + h * 32, valid);
+              }
+#pragma unroll
+              for (int q4 = 0; q4 < 4; ++q4) {
+                uint32_t w[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  const __half2 hh = __floats2half2_rn(f[q4 * 8 + 2 * e], f[q4 * 8 + 2 * e + 1]);
+                  w[e] = *reinterpret_cast<const uint32_t*>(&hh);
+                }
+                st_shared_v4_u32(stage + (uint32_t)r_in * 128u + ((((uint32_t)(h * 4 + q4)) ^ sw) << 4), w[0], w[1], w[2], w[3]);
+              }
+            }
+            fence_proxy_async_smem();
+            named_barrier_sync(1, 128);
+            if (threadIdx.x == 0) {
+              tma_store_4d(&tma_c, stage, col0, t.mt * BM, t.ib1, t.ib0);
+              bulk_commit_group();
+            }
+            ++store_count;
+          }
+        }
+        tc_fence_before();
+        mbar_arrive(smem_u32(&bar_tempty[buf]));
+        continue;
+      }
 #pragma unroll
       for (int c = 0; c < NCH; ++c) {
         const int col0 = t.nt * BN + c * 32;
@@ -215,6 +268,7 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
       tc_fence_before();
       mbar_arrive(smem_u32(&bar_tempty[buf]));
     }
+    if (threadIdx.x == 0) bulk_wait_group_read<0>();     // shared memory must outlive the last bulk stores' reads
   }
 
   tc_fence_before();
@@ -284,7 +338,7 @@ __device__ __forceinline__ void split_role(const TcArgs& g, uint32_t smem_base, 
 template <int BN>
 __global__ void __launch_bounds__(CfgS<BN>::THREADS, 1)
 gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
-                   const TcArgs g) {
+                   const __grid_constant__ CUtensorMap /* output map: used by the f16 kernel only */, const TcArgs g) {
   using C = CfgS<BN>;
   constexpr int STAGES = C::STAGES;
   constexpr int PRODUCER_WARP = 8, MMA_WARP = 9;      // warpgroup 2; warpgroups 3 and 4 split operands
@@ -665,7 +719,7 @@ int g_pair_mode = 1;  // 0 = choose by problem shape, 1 = never use CTA pairs (d
 // Tensor maps and kernel arguments for a tile grid of TM x TN outputs per scheduling unit, where one
 // CTA stages BMC rows of A and BNC columns of B per k-block of BK (MN-major operands in chunks of CH).
 struct Launch {
-  alignas(64) CUtensorMap ma, mb;
+  alignas(64) CUtensorMap ma, mb, mc;
   TcArgs g;
 };
 
@@ -727,6 +781,13 @@ int build_launch(Launch& L, const Plan& pl, int esize, int tm, int tn, int bmc, 
                       (p.b0 <= 1 || (uint64_t)p.c_b0 * es % 32 == 0) && (p.b1 <= 1 || (uint64_t)p.c_b1 * es % 32 == 0);
     g.c_wide = wide ? 1 : 0;
   }
+  g.c_tma = 0;
+  L.mc = L.ma;                                               // a valid descriptor even when it is not used
+  if (esize == 2 && !pl.c_col && !p.beta && g_store_mode != 1 && tm == BM) {
+    // output map (n, m, b1, b0), box 64 x 128, 128B swizzle: the epilogue stages groups of 64 columns
+    if (encode_map(&L.mc, p.c, 2, p.n, p.m, pl.ldc, p.b1, p.c_b1, p.b0, p.c_b0, 64, 128, CU_TENSOR_MAP_SWIZZLE_128B) == B200_OK)
+      g.c_tma = 1;
+  }
   g.beta = p.beta;
   g.fused = p.fused() ? 1 : 0; g.alpha = (float)p.alpha; g.bias = p.bias; g.bias_row = p.bias_dim ? 1 : 0; g.act = p.act;
   g.xform_mode = g_xform_mode;
@@ -778,7 +839,8 @@ int launch_cfg(const Plan& pl, cudaStream_t stream, Kernel kernel, int ksplit) {
         g.kb_per_slice = kb_per; g.ksplit = slices; g.total_units = g.total_tiles * slices;
         g.split_out = ds->split_scratch; g.split_ld = lds;
         const long long grid2 = g.total_units < ds->sm_count ? g.total_units : ds->sm_count;
-        kernel<<<(unsigned)grid2, C::THREADS, C::SMEM_BYTES, stream>>>(L.ma, L.mb, L.g);
+        L.g.c_tma = 0;                                       // partial sums go to the scratch, not to C
+        kernel<<<(unsigned)grid2, C::THREADS, C::SMEM_BYTES, stream>>>(L.ma, L.mb, L.mc, L.g);
         count_launch(true);
         if ((rc = note_cuda_error(cudaGetLastError(), "tensor-core gemm launch"))) return rc;
         const long long total = (long long)p.m * p.n;
@@ -800,7 +862,7 @@ int launch_cfg(const Plan& pl, cudaStream_t stream, Kernel kernel, int ksplit) {
   }
   const long long grid = g.total_units < ds->sm_count ? g.total_units : ds->sm_count;
   if (grid <= 0) return B200_OK;
-  kernel<<<(unsigned)grid, C::THREADS, C::SMEM_BYTES, stream>>>(L.ma, L.mb, L.g);
+  kernel<<<(unsigned)grid, C::THREADS, C::SMEM_BYTES, stream>>>(L.ma, L.mb, L.mc, L.g);
   count_launch(true);
   return note_cuda_error(cudaGetLastError(), "tensor-core gemm launch");
 }

@@ -77,6 +77,35 @@ __device__ __forceinline__ void tma_load_5d(uint32_t dst, const CUtensorMap* map
       " [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
       ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4) : "memory");
 }
+// Tiled 4-D TMA store shared -> global (bulk async-group completion).  Rows / columns of the box that fall outside
+// the tensor are not written.
+__device__ __forceinline__ void tma_store_4d(const CUtensorMap* map, uint32_t src, int c0, int c1, int c2, int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+      ::"l"(map), "r"(src), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
+}
+__device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// Waits until at most N of this thread's bulk groups still have to READ their shared-memory source.
+template <int N>
+__device__ __forceinline__ void bulk_wait_group_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+// Named barrier over `count` threads (id 0 is __syncthreads).
+__device__ __forceinline__ void named_barrier_sync(int id, int count) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
+}
+// The same barrier carrying a vote: returns true iff `pred` holds in every participating thread.
+__device__ __forceinline__ bool named_barrier_and(int id, int count, bool pred) {
+  uint32_t out;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\tsetp.ne.b32 q, %3, 0;\n\t"
+      "barrier.cta.red.and.pred p, %1, %2, q;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(out) : "r"(id), "r"(count), "r"((uint32_t)pred) : "memory");
+  return out != 0;
+}
+__device__ __forceinline__ void st_shared_v4_u32(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
 // 32 lanes x 16 consecutive 32-bit columns.
 __device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, uint32_t (&v)[16]) {
   asm volatile(
@@ -194,7 +223,9 @@ struct CfgH {
   static constexpr int STAGES = STAGES_FIT > 8 ? 8 : STAGES_FIT;
   static constexpr int THREADS = 192;
   static constexpr int TMEM_COLS = 2 * BN;
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024;
+  static constexpr int OUT_BYTES = 128 * 128;               // one staged output group: 128 rows x 64 f16 (TMA-store epilogue)
+  static constexpr int OFF_OUT = STAGES * STAGE_BYTES;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 2 * OUT_BYTES + 1024;
   static constexpr uint32_t LAYOUT = 2u;                    // SWIZZLE_128B
   static constexpr uint32_t SBO = 1024;                     // 8 rows of 128 bytes
   static constexpr uint32_t MN_LBO = BK * 128;              // distance between MN-major chunks
@@ -248,6 +279,8 @@ struct TcArgs {
   long long c_b0, c_b1, ldc;      // element strides
   int c_col;                      // 0: C(i,j) at i*ldc + j (row store); 1: at j*ldc + i (column store)
   int c_wide;                     // row store: every row start is 32-byte aligned (256-bit accesses)
+  int c_tma;                      // f16 kernel, row store, beta = 0: groups of 64 columns are staged in shared memory
+                                  // and written by TMA (tensor map `tma_c`) instead of per-thread row stores
   int beta;
   int xform_mode;                 // f32: 1 = big stays raw, write small only; 0 = also rewrite big = tf32_rn(x)
   long long wait_limit;           // clock cycles

@@ -115,9 +115,11 @@ int b200_set_mn_single_box(int on);
  * planner choose between them and the CTA-pair (cta_group::2, 256x256 tiles) kernels by a wave model, 2 forces
  * the pair kernels wherever the output is wider than 128 columns. */
 int b200_set_cta_pair_mode(int mode);
-/* Epilogue store orientation of the tensor-core kernels (testing / profiling): 0 (default) planner's choice,
- * 1 row stores only (each thread writes 16-byte pieces of its output row), 2 column stores wherever possible
- * (the kernel's M runs along the output's unit-stride dimension; warp stores are contiguous). */
+/* Epilogue store path of the tensor-core kernels (testing / profiling): 0 (default) planner's choice (f16 outputs
+ * with beta = 0 leave through shared memory and TMA bulk stores; otherwise row stores, or column stores where
+ * the model says so), 1 per-thread row stores only (each thread writes 16- / 32-byte pieces of its output row),
+ * 2 column stores wherever possible (the kernel's M runs along the output's unit-stride dimension; warp stores
+ * are contiguous). */
 int b200_set_store_mode(int mode);
 /* Split-K of the f32 tensor-core kernel (testing / profiling): 0 (default) the planner cuts K into slices when
  * the output tiles alone would leave most SMs idle (partial results are then added atomically, so the last

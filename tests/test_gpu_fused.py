@@ -61,7 +61,7 @@ def test_fused_simt(cuda_dev, oracle, dtype):
         cuda_dev.set_path(dfdx_b200.PATH_AUTO)
 
 
-@pytest.mark.parametrize("store", [pytest.param(1, id="rowstore"), pytest.param(2, id="colstore")])
+@pytest.mark.parametrize("store", [pytest.param(0, id="auto"), pytest.param(1, id="rowstore"), pytest.param(2, id="colstore")])
 @pytest.mark.parametrize("tile_n", [64, 128, 256])
 @pytest.mark.parametrize("dtype", [torch.float16, torch.float32])
 def test_fused_tensor_core(cuda_dev, oracle, dtype, tile_n, store):

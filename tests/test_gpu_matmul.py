@@ -106,7 +106,7 @@ def test_simt_degenerate_stride_pairs(cuda_dev, oracle):
 TC_SHAPES = [(128, 64, 64), (128, 64, 256), (200, 136, 72), (264, 520, 104), (64, 1032, 136), (384, 40, 512)]
 
 
-@pytest.mark.parametrize("store", [pytest.param(1, id="rowstore"), pytest.param(2, id="colstore")])
+@pytest.mark.parametrize("store", [pytest.param(0, id="auto"), pytest.param(1, id="rowstore"), pytest.param(2, id="colstore")])
 @pytest.mark.parametrize("tile_n", [64, 128, 256])
 @pytest.mark.parametrize("dtype", [torch.float16, torch.float32])
 @pytest.mark.parametrize("layout", ["".join(p) for p in itertools.product("rc", repeat=3)])
