@@ -57,23 +57,24 @@ struct BwdCfg {
 };
 
 // aux[(b*H + h) * pad + i] = (lse * log2 e, sum_d dO * O) for i < s1, (+inf, 0) for the padding rows.
+// Eight lanes share a row (16 bytes of O and of dO each per step), so a warp reads four rows as whole 128-byte lines.
 __global__ void __launch_bounds__(256) attention_bwd_prep_kernel(const __half* __restrict__ o, long long o_b, long long o_h,
                                                                  long long o_s, const __half* __restrict__ go, long long g_b,
                                                                  long long g_h, long long g_s, const float* __restrict__ lse,
                                                                  float2* __restrict__ aux, int heads, int s1, int pad, int d,
                                                                  long long total) {
-  const long long idx = (long long)blockIdx.x * 256 + threadIdx.x;
-  if (idx >= total) return;
-  const int i = (int)(idx % pad);
-  const long long bh = idx / pad;
-  float2 r = make_float2(INFINITY, 0.f);
-  if (i < s1) {
+  const long long idx = ((long long)blockIdx.x * 256 + threadIdx.x) >> 3;   // row of aux
+  const int sub = threadIdx.x & 7;
+  const bool live = idx < total;                             // whole 8-lane groups are live or not
+  const int i = live ? (int)(idx % pad) : 0;
+  const long long bh = live ? idx / pad : 0;
+  float acc = 0.f;
+  if (live && i < s1) {
     const int h = (int)(bh % heads);
     const long long b = bh / heads;
     const __half* po = o + b * o_b + h * o_h + (long long)i * o_s;
     const __half* pg = go + b * g_b + h * g_h + (long long)i * g_s;
-    float acc = 0.f;
-    for (int c = 0; c < d; c += 8) {                         // d is a multiple of 8, rows are 16-byte aligned
+    for (int c = sub * 8; c < d; c += 64) {                  // d is a multiple of 8, rows are 16-byte aligned
       const uint4 a = *reinterpret_cast<const uint4*>(po + c);
       const uint4 g = *reinterpret_cast<const uint4*>(pg + c);
       const __half2* ha = reinterpret_cast<const __half2*>(&a);
@@ -85,9 +86,12 @@ __global__ void __launch_bounds__(256) attention_bwd_prep_kernel(const __half* _
         acc = fmaf(fa.y, fg.y, acc);
       }
     }
-    r = make_float2(lse[bh * s1 + i] * 1.4426950408889634f, acc);
   }
-  aux[idx] = r;
+  acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+  acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+  acc += __shfl_xor_sync(0xffffffffu, acc, 4);
+  if (live && sub == 0)
+    aux[idx] = i < s1 ? make_float2(lse[bh * s1 + i] * 1.4426950408889634f, acc) : make_float2(INFINITY, 0.f);
 }
 
 template <int DP, int MODE>
@@ -416,7 +420,7 @@ int attention_backward(int dtype, int64_t B, int64_t H, int64_t s1, int64_t s2, 
   // 1. aux = (lse * log2 e, rowsum(dO o O))
   {
     const long long total = (long long)B * H * pad;
-    attention_bwd_prep_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(
+    attention_bwd_prep_kernel<<<(unsigned)((total * 8 + 255) / 256), 256, 0, stream>>>(
         (const __half*)out, os[0], os[1], os[2], (const __half*)go, gs[0], gs[1], gs[2], lse, (float2*)workspace, (int)H,
         (int)s1, (int)pad, (int)d, total);
     count_launch(false);

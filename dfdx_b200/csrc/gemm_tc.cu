@@ -173,7 +173,7 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
       // beta = 1 with row stores: the values the row already holds do not depend on the accumulator, so
       // they are fetched before waiting for it, four 32-column chunks ahead of their use.
       constexpr int NCH = BN / 32, AHEAD = NCH < 4 ? NCH : 4;
-      const bool rmw = g.beta && !g.c_col && row < g.m && g.ksplit == 1;
+      const bool rmw = g.beta && !g.c_col && row < g.m && g.ksplit == 1 && !g.c_tma;
       const __half* orow = cbase + (long long)row * g.ldc + t.nt * BN;
       uint32_t oldv[AHEAD][16];
       if (rmw) {
@@ -227,7 +227,8 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
             fence_proxy_async_smem();
             named_barrier_sync(1, 128);
             if (threadIdx.x == 0) {
-              tma_store_4d(&tma_c, stage, col0, t.mt * BM, t.ib1, t.ib0);
+              if (g.c_tma == 2) tma_reduce_add_4d(&tma_c, stage, col0, t.mt * BM, t.ib1, t.ib0);
+              else tma_store_4d(&tma_c, stage, col0, t.mt * BM, t.ib1, t.ib0);
               bulk_commit_group();
             }
             ++store_count;
@@ -783,10 +784,10 @@ int build_launch(Launch& L, const Plan& pl, int esize, int tm, int tn, int bmc, 
   }
   g.c_tma = 0;
   L.mc = L.ma;                                               // a valid descriptor even when it is not used
-  if (esize == 2 && !pl.c_col && !p.beta && g_store_mode != 1 && tm == BM) {
+  if (esize == 2 && !pl.c_col && g_store_mode != 1 && tm == BM) {
     // output map (n, m, b1, b0), box 64 x 128, 128B swizzle: the epilogue stages groups of 64 columns
     if (encode_map(&L.mc, p.c, 2, p.n, p.m, pl.ldc, p.b1, p.c_b1, p.b0, p.c_b0, 64, 128, CU_TENSOR_MAP_SWIZZLE_128B) == B200_OK)
-      g.c_tma = 1;
+      g.c_tma = p.beta ? 2 : 1;
   }
   g.beta = p.beta;
   g.fused = p.fused() ? 1 : 0; g.alpha = (float)p.alpha; g.bias = p.bias; g.bias_row = p.bias_dim ? 1 : 0; g.act = p.act;

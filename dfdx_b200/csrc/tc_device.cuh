@@ -84,6 +84,12 @@ __device__ __forceinline__ void tma_store_4d(const CUtensorMap* map, uint32_t sr
       "cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
       ::"l"(map), "r"(src), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
 }
+// The same box added element-wise into global memory (f16 add performed by the memory system).
+__device__ __forceinline__ void tma_reduce_add_4d(const CUtensorMap* map, uint32_t src, int c0, int c1, int c2, int c3) {
+  asm volatile(
+      "cp.reduce.async.bulk.tensor.4d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+      ::"l"(map), "r"(src), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
+}
 __device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 // Waits until at most N of this thread's bulk groups still have to READ their shared-memory source.
 template <int N>
@@ -279,8 +285,9 @@ struct TcArgs {
   long long c_b0, c_b1, ldc;      // element strides
   int c_col;                      // 0: C(i,j) at i*ldc + j (row store); 1: at j*ldc + i (column store)
   int c_wide;                     // row store: every row start is 32-byte aligned (256-bit accesses)
-  int c_tma;                      // f16 kernel, row store, beta = 0: groups of 64 columns are staged in shared memory
-                                  // and written by TMA (tensor map `tma_c`) instead of per-thread row stores
+  int c_tma;                      // f16 kernel, row store: groups of 64 columns are staged in shared memory and leave by
+                                  // TMA (tensor map `tma_c`) instead of per-thread row accesses: 1 = store (beta = 0),
+                                  // 2 = element-wise add into C (beta = 1: C += f16(acc), two roundings instead of one)
   int beta;
   int xform_mode;                 // f32: 1 = big stays raw, write small only; 0 = also rewrite big = tf32_rn(x)
   long long wait_limit;           // clock cycles

@@ -136,7 +136,10 @@ uint64_t b200_tensor_launch_count(void);
  * i.e. `gemm_cfg` :18-60 + cublas{S,D,H}gemm / cublasGemmEx):
  *     out[i*os0 + j*os1] = beta*out[..] + sum_p lhs[i*ls0 + p*ls1] * rhs[p*rs0 + j*rs1]
  * for i<m, j<n, p<k.  beta is 0 or 1; with beta == 0 `out` is never read (it comes from
- * `alloc_empty`, cuda_kernel.rs:253).  Legal stride pairs are those `matrix_strides`
+ * `alloc_empty`, cuda_kernel.rs:253).  With beta == 1 and f16 storage the tensor-core path adds the
+ * f16-rounded product into `out` (C += f16(acc), an element-wise add performed by the memory system on staged
+ * tiles): two roundings where cuBLAS rounds f32(acc + C) once; both stay within one f16 ulp of the exact sum, and
+ * accumulation into the zeroed buffers of `Gradients::try_alloc_for` is exact.  Legal stride pairs are those `matrix_strides`
  * accepts (matmul/mod.rs:316-325). */
 int b200_gemm(int dtype, size_t m, size_t k, size_t n,
               const void* lhs, const size_t lhs_strides[2],
