@@ -35,6 +35,12 @@ class Conv2DOp(C.Structure):
         "chan_in", "chan_out", "h_in", "h_out", "w_in", "w_out")]
 
 
+class Conv1DOp(C.Structure):
+    """Bit-identical to dfdx's `Conv1DOp` (dfdx-core/src/tensor_ops/conv1d/mod.rs:12-23)."""
+    _fields_ = [(n, C.c_size_t) for n in (
+        "kernel", "stride", "padding", "dilation", "groups", "batch", "chan_in", "chan_out", "l_in", "l_out")]
+
+
 _sz, _vp, _i, _d = C.c_size_t, C.c_void_p, C.c_int, C.c_double
 _szp = C.POINTER(C.c_size_t)
 
@@ -76,6 +82,9 @@ SIGNATURES = {
     "b200_conv2d_workspace_bytes": (_sz, [_i, C.POINTER(Conv2DOp), _i]),
     "b200_conv2d_forward": (_i, [_i, C.POINTER(Conv2DOp), _vp, _szp, _vp, _vp, _vp, _sz, _vp]),
     "b200_conv2d_backward": (_i, [_i, C.POINTER(Conv2DOp), _vp, _vp, _vp, _szp, _vp, _vp, _vp, _sz, _vp, _vp]),
+    "b200_conv1d_workspace_bytes": (_sz, [_i, C.POINTER(Conv1DOp), _i]),
+    "b200_conv1d_forward": (_i, [_i, C.POINTER(Conv1DOp), _vp, _szp, _vp, _vp, _vp, _sz, _vp]),
+    "b200_conv1d_backward": (_i, [_i, C.POINTER(Conv1DOp), _vp, _vp, _vp, _szp, _vp, _vp, _vp, _sz, _vp, _vp]),
     "b200_conv2d_forward_noalloc": (_i, [_i, C.POINTER(Conv2DOp), _vp, _szp, _vp, _vp, _vp]),
 }
 

@@ -13,13 +13,15 @@ namespace {
 
 constexpr int NT = 256;
 
+// Geometry of one convolution.  Kernel extent and padding are per axis so that the same kernels serve conv2d
+// (kh = kw, ph = pw) and conv1d (an image of height 1: kh = 1, ph = 0); stride and dilation are shared.
 struct Op {
-  int64_t kernel, stride, padding, dilation, groups, batch, chan_in, chan_out, h_in, h_out, w_in, w_out;
+  int64_t kh, kw, stride, ph, pw, dilation, groups, batch, chan_in, chan_out, h_in, h_out, w_in, w_out;
 };
 
 Op to_op(const b200_conv2d_op* o) {
   Op r;
-  r.kernel = (int64_t)o->kernel; r.stride = (int64_t)o->stride; r.padding = (int64_t)o->padding;
+  r.kh = r.kw = (int64_t)o->kernel; r.stride = (int64_t)o->stride; r.ph = r.pw = (int64_t)o->padding;
   r.dilation = (int64_t)o->dilation; r.groups = (int64_t)o->groups; r.batch = (int64_t)o->batch;
   r.chan_in = (int64_t)o->chan_in; r.chan_out = (int64_t)o->chan_out; r.h_in = (int64_t)o->h_in;
   r.h_out = (int64_t)o->h_out; r.w_in = (int64_t)o->w_in; r.w_out = (int64_t)o->w_out;
@@ -39,12 +41,12 @@ __global__ void __launch_bounds__(NT) unfold_input_kernel(const Op op, const T* 
     int64_t idx = i;
     const int64_t ow = idx % op.w_out; idx /= op.w_out;
     const int64_t oh = idx % op.h_out; idx /= op.h_out;
-    const int64_t k2 = idx % op.kernel; idx /= op.kernel;
-    const int64_t k1 = idx % op.kernel; idx /= op.kernel;
+    const int64_t k2 = idx % op.kw; idx /= op.kw;
+    const int64_t k1 = idx % op.kh; idx /= op.kh;
     const int64_t c = idx % op.chan_in;
     const int64_t b = idx / op.chan_in;
-    const int64_t y = oh * op.stride + op.dilation * k1 - op.padding;
-    const int64_t x = ow * op.stride + op.dilation * k2 - op.padding;
+    const int64_t y = oh * op.stride + op.dilation * k1 - op.ph;
+    const int64_t x = ow * op.stride + op.dilation * k2 - op.pw;
     T v = T(0.0f);
     if (y >= 0 && y < op.h_in && x >= 0 && x < op.w_in)
       v = img[b * st.s[0] + c * st.s[1] + y * st.s[2] + x * st.s[3]];
@@ -62,13 +64,13 @@ __global__ void __launch_bounds__(NT) unfold_output_kernel(const Op op, const T*
     int64_t idx = i;
     const int64_t x = idx % op.w_in; idx /= op.w_in;
     const int64_t y = idx % op.h_in; idx /= op.h_in;
-    const int64_t k2 = idx % op.kernel; idx /= op.kernel;
-    const int64_t k1 = idx % op.kernel; idx /= op.kernel;
+    const int64_t k2 = idx % op.kw; idx /= op.kw;
+    const int64_t k1 = idx % op.kh; idx /= op.kh;
     const int64_t o = idx % op.chan_out;
     const int64_t b = idx / op.chan_out;
     T v = T(0.0f);
-    const int64_t ohs = y + op.padding - op.dilation * k1;
-    const int64_t ows = x + op.padding - op.dilation * k2;
+    const int64_t ohs = y + op.ph - op.dilation * k1;
+    const int64_t ows = x + op.pw - op.dilation * k2;
     if (ohs >= 0 && ows >= 0 && ohs % op.stride == 0 && ows % op.stride == 0) {
       const int64_t oh = ohs / op.stride, ow = ows / op.stride;
       if (oh < op.h_out && ow < op.w_out)
@@ -86,8 +88,8 @@ __global__ void __launch_bounds__(NT) transpose_filters_kernel(const Op op, cons
   const int64_t cg = op.chan_in / op.groups, og = op.chan_out / op.groups;
   for (int64_t i = (int64_t)blockIdx.x * NT + threadIdx.x; i < total; i += (int64_t)gridDim.x * NT) {
     int64_t idx = i;
-    const int64_t k2 = idx % op.kernel; idx /= op.kernel;
-    const int64_t k1 = idx % op.kernel; idx /= op.kernel;
+    const int64_t k2 = idx % op.kw; idx /= op.kw;
+    const int64_t k1 = idx % op.kh; idx /= op.kh;
     const int64_t o = idx % og; idx /= og;
     const int64_t c = idx % cg;
     const int64_t g = idx / cg;
@@ -104,8 +106,8 @@ __global__ void __launch_bounds__(NT) sum_transposed_filters_kernel(const Op op,
   const int64_t cg = op.chan_in / op.groups, og = op.chan_out / op.groups;
   for (int64_t i = (int64_t)blockIdx.x * NT + threadIdx.x; i < total; i += (int64_t)gridDim.x * NT) {
     int64_t idx = i;
-    const int64_t k2 = idx % op.kernel; idx /= op.kernel;
-    const int64_t k1 = idx % op.kernel; idx /= op.kernel;
+    const int64_t k2 = idx % op.kw; idx /= op.kw;
+    const int64_t k1 = idx % op.kh; idx /= op.kh;
     const int64_t o = idx % og; idx /= og;
     const int64_t c = idx % cg;
     const int64_t g = idx / cg;
@@ -127,7 +129,7 @@ template <> struct VecOf<double> { static constexpr int N = 2; using type = doub
 template <> struct VecOf<__half> { static constexpr int N = 8; using type = uint4; };
 
 struct Op32 {
-  int kernel, stride, padding, dilation, chan_in, chan_out, h_in, h_out, w_in, w_out;
+  int kh, kw, stride, ph, pw, dilation, chan_in, chan_out, h_in, h_out, w_in, w_out;
 };
 
 template <typename T>
@@ -146,21 +148,21 @@ __global__ void __launch_bounds__(NT) unfold_input_plane_kernel(const Op32 op, c
   }
   __syncthreads();
   const int npos = op.h_out * op.w_out, vrow = op.w_out / V, nvec = op.h_out * vrow;
-  T* dst = patches + (int64_t)id * op.kernel * op.kernel * npos;
+  T* dst = patches + (int64_t)id * op.kh * op.kw * npos;
   for (int v = threadIdx.x; v < nvec; v += NT) {
     const int oh = v / vrow, ow0 = (v - oh * vrow) * V;
-    for (int k1 = 0; k1 < op.kernel; ++k1) {
-      const int y = oh * op.stride + op.dilation * k1 - op.padding;
+    for (int k1 = 0; k1 < op.kh; ++k1) {
+      const int y = oh * op.stride + op.dilation * k1 - op.ph;
       const bool yok = y >= 0 && y < op.h_in;
-      for (int k2 = 0; k2 < op.kernel; ++k2) {
-        const int x0 = ow0 * op.stride + op.dilation * k2 - op.padding;
+      for (int k2 = 0; k2 < op.kw; ++k2) {
+        const int x0 = ow0 * op.stride + op.dilation * k2 - op.pw;
         __align__(16) T vals[V];
 #pragma unroll
         for (int e = 0; e < V; ++e) {
           const int x = x0 + e * op.stride;
           vals[e] = (yok && x >= 0 && x < op.w_in) ? plane[y * op.w_in + x] : T(0.0f);
         }
-        *reinterpret_cast<VT*>(dst + (int64_t)(k1 * op.kernel + k2) * npos + oh * op.w_out + ow0) =
+        *reinterpret_cast<VT*>(dst + (int64_t)(k1 * op.kw + k2) * npos + oh * op.w_out + ow0) =
             *reinterpret_cast<const VT*>(vals);
       }
     }
@@ -180,23 +182,23 @@ __global__ void __launch_bounds__(NT) unfold_output_plane_kernel(const Op32 op, 
   for (int i = threadIdx.x; i < npos; i += NT) plane[i] = src[i];
   __syncthreads();
   const int hw = op.h_in * op.w_in, vrow = op.w_in / V, nvec = op.h_in * vrow;
-  T* dst = patches + (int64_t)id * op.kernel * op.kernel * hw;
+  T* dst = patches + (int64_t)id * op.kh * op.kw * hw;
   for (int v = threadIdx.x; v < nvec; v += NT) {
     const int y = v / vrow, x0 = (v - y * vrow) * V;
-    for (int k1 = 0; k1 < op.kernel; ++k1) {
-      const int ohs = y + op.padding - op.dilation * k1;
+    for (int k1 = 0; k1 < op.kh; ++k1) {
+      const int ohs = y + op.ph - op.dilation * k1;
       const int oh = ohs / op.stride;
       const bool yok = ohs >= 0 && ohs - oh * op.stride == 0 && oh < op.h_out;
-      for (int k2 = 0; k2 < op.kernel; ++k2) {
+      for (int k2 = 0; k2 < op.kw; ++k2) {
         __align__(16) T vals[V];
 #pragma unroll
         for (int e = 0; e < V; ++e) {
-          const int ows = x0 + e + op.padding - op.dilation * k2;
+          const int ows = x0 + e + op.pw - op.dilation * k2;
           const int ow = ows / op.stride;
           vals[e] = (yok && ows >= 0 && ows - ow * op.stride == 0 && ow < op.w_out) ? plane[oh * op.w_out + ow]
                                                                                     : T(0.0f);
         }
-        *reinterpret_cast<VT*>(dst + (int64_t)(k1 * op.kernel + k2) * hw + y * op.w_in + x0) =
+        *reinterpret_cast<VT*>(dst + (int64_t)(k1 * op.kw + k2) * hw + y * op.w_in + x0) =
             *reinterpret_cast<const VT*>(vals);
       }
     }
@@ -204,14 +206,14 @@ __global__ void __launch_bounds__(NT) unfold_output_plane_kernel(const Op32 op, 
 }
 
 Op32 to_op32(const Op& o) {
-  return Op32{(int)o.kernel, (int)o.stride, (int)o.padding, (int)o.dilation, (int)o.chan_in, (int)o.chan_out,
+  return Op32{(int)o.kh, (int)o.kw, (int)o.stride, (int)o.ph, (int)o.pw, (int)o.dilation, (int)o.chan_in, (int)o.chan_out,
               (int)o.h_in, (int)o.h_out, (int)o.w_in, (int)o.w_out};
 }
 
 bool fits_int(const Op& o) {
   const int64_t lim = 1 << 30;
   return o.batch * o.chan_in < lim && o.batch * o.chan_out < lim && o.h_in * o.w_in < lim &&
-         o.h_out * o.w_out < lim && o.kernel < 4096 && o.stride < lim && o.padding < lim && o.dilation < lim;
+         o.h_out * o.w_out < lim && o.kh < 4096 && o.kw < 4096 && o.stride < lim && o.ph < lim && o.pw < lim && o.dilation < lim;
 }
 
 template <typename T>
@@ -240,7 +242,7 @@ int forward_t(int dtype, const Op& op, const T* img, const size_t is[4], const T
   DeviceState* ds = device_state();
   const int sms = ds ? ds->sm_count : 148;
   T* patches = (T*)ws;
-  const int64_t total = op.batch * op.chan_in * op.kernel * op.kernel * op.h_out * op.w_out;
+  const int64_t total = op.batch * op.chan_in * op.kh * op.kw * op.h_out * op.w_out;
   if (total == 0) return B200_OK;
   Strides4 st{{(int64_t)is[0], (int64_t)is[1], (int64_t)is[2], (int64_t)is[3]}};
   if (plane_path_input<T>(op))
@@ -253,7 +255,7 @@ int forward_t(int dtype, const Op& op, const T* img, const size_t is[4], const T
   if (rc) return rc;
 
   // filters (G, O/G, C/G*K*K) x patches (B, G, C/G*K*K, OH*OW) -> out (B, G, O/G, OH*OW)
-  const int64_t m = op.chan_out / op.groups, k = (op.chan_in / op.groups) * op.kernel * op.kernel,
+  const int64_t m = op.chan_out / op.groups, k = (op.chan_in / op.groups) * op.kh * op.kw,
                 n = op.h_out * op.w_out, G = op.groups;
   GemmProblem p;
   p.dtype = dtype; p.beta = 0; p.b0 = op.batch; p.b1 = G; p.m = m; p.k = k; p.n = n;
@@ -268,7 +270,7 @@ int backward_t(int dtype, const Op& op, const T* img, T* grad_img, const T* filt
                T* grad_filters, const T* grad_out, void* ws, cudaStream_t stream) {
   DeviceState* ds = device_state();
   const int sms = ds ? ds->sm_count : 148;
-  const int64_t G = op.groups, cg = op.chan_in / G, og = op.chan_out / G, KK = op.kernel * op.kernel;
+  const int64_t G = op.groups, cg = op.chan_in / G, og = op.chan_out / G, KK = op.kh * op.kw;
   const int64_t hw = op.h_in * op.w_in;
   const int64_t n_patches = op.batch * op.chan_out * KK * hw;
   const int64_t n_filters = G * cg * og * KK;
@@ -285,7 +287,7 @@ int backward_t(int dtype, const Op& op, const T* img, T* grad_img, const T* filt
   //   grad_filters (G, O/G, C/G*K*K) += sum_b grad_out_b (G, O/G, OH*OW) x patches(img_b)^T (G, OH*OW, C/G*K*K)
   // is one batch-reduced GEMM per group (O/G rows: full tiles) that accumulates straight into the filter
   // layout, instead of per-image GEMMs into a B-fold temporary followed by a sum.
-  const bool filters_contig = (int64_t)fs[3] == 1 && (int64_t)fs[2] == op.kernel && (int64_t)fs[1] == KK &&
+  const bool filters_contig = (int64_t)fs[3] == 1 && (int64_t)fs[2] == op.kw && (int64_t)fs[1] == KK &&
                               (int64_t)fs[0] == cg * KK;
   bool grad_filters_done = false;
   // (tensor-core dtypes only: their kernels cut the long reduction into K slices.)
@@ -351,20 +353,20 @@ int backward_t(int dtype, const Op& op, const T* img, T* grad_img, const T* filt
 
 }  // namespace
 
-size_t conv2d_workspace_bytes(int dtype, const b200_conv2d_op* o, int backward) {
+namespace {
+size_t workspace_bytes_op(int dtype, const Op& o, int backward) {
   const size_t es = dtype_size(dtype);
-  if (!es || !o || !o->groups) return 0;
-  const size_t KK = o->kernel * o->kernel;
-  if (!backward) return align256(o->batch * o->chan_in * KK * o->h_out * o->w_out * es);
-  const size_t nf = o->groups * (o->chan_in / o->groups) * (o->chan_out / o->groups) * KK;
-  const size_t bwd_patches = o->batch * o->chan_out * KK * o->h_in * o->w_in * es;
-  const size_t fwd_patches = o->batch * o->chan_in * KK * o->h_out * o->w_out * es;
-  return align256(bwd_patches > fwd_patches ? bwd_patches : fwd_patches) + align256(nf * es) + align256(o->batch * nf * es);
+  if (!es || !o.groups) return 0;
+  const size_t KK = (size_t)(o.kh * o.kw);
+  const size_t fwd_patches = (size_t)o.batch * o.chan_in * KK * o.h_out * o.w_out * es;
+  if (!backward) return align256(fwd_patches);
+  const size_t nf = (size_t)o.groups * (o.chan_in / o.groups) * (o.chan_out / o.groups) * KK;
+  const size_t bwd_patches = (size_t)o.batch * o.chan_out * KK * o.h_in * o.w_in * es;
+  return align256(bwd_patches > fwd_patches ? bwd_patches : fwd_patches) + align256(nf * es) + align256(o.batch * nf * es);
 }
 
-int conv2d_forward(int dtype, const b200_conv2d_op* o, const void* img, const size_t is[4], const void* filters,
-                   void* out, void* ws, cudaStream_t stream) {
-  const Op op = to_op(o);
+int forward_any(int dtype, const Op& op, const void* img, const size_t is[4], const void* filters, void* out, void* ws,
+                cudaStream_t stream) {
   switch (dtype) {
     case B200_F32: return forward_t<float, float>(dtype, op, (const float*)img, is, (const float*)filters, (float*)out, ws, stream);
     case B200_F64: return forward_t<double, double>(dtype, op, (const double*)img, is, (const double*)filters, (double*)out, ws, stream);
@@ -374,9 +376,8 @@ int conv2d_forward(int dtype, const b200_conv2d_op* o, const void* img, const si
   }
 }
 
-int conv2d_backward(int dtype, const b200_conv2d_op* o, const void* img, void* grad_img, const void* filters,
-                    const size_t fs[4], void* grad_filters, const void* grad_out, void* ws, cudaStream_t stream) {
-  const Op op = to_op(o);
+int backward_any(int dtype, const Op& op, const void* img, void* grad_img, const void* filters, const size_t fs[4],
+                 void* grad_filters, const void* grad_out, void* ws, cudaStream_t stream) {
   switch (dtype) {
     case B200_F32: return backward_t<float, float>(dtype, op, (const float*)img, (float*)grad_img, (const float*)filters, fs, (float*)grad_filters, (const float*)grad_out, ws, stream);
     case B200_F64: return backward_t<double, double>(dtype, op, (const double*)img, (double*)grad_img, (const double*)filters, fs, (double*)grad_filters, (const double*)grad_out, ws, stream);
@@ -384,6 +385,45 @@ int conv2d_backward(int dtype, const b200_conv2d_op* o, const void* img, void* g
     case B200_AMP_F16: return backward_t<__half, float>(dtype, op, (const __half*)img, (__half*)grad_img, (const __half*)filters, fs, (__half*)grad_filters, (const __half*)grad_out, ws, stream);
     default: return B200_ERR_DTYPE;
   }
+}
+
+// conv1d (dfdx-core/src/tensor_ops/conv1d/mod.rs:12-23) as a convolution over an image of height 1.
+Op to_op(const b200_conv1d_op* o) {
+  Op r;
+  r.kh = 1; r.kw = (int64_t)o->kernel; r.stride = (int64_t)o->stride; r.ph = 0; r.pw = (int64_t)o->padding;
+  r.dilation = (int64_t)o->dilation; r.groups = (int64_t)o->groups; r.batch = (int64_t)o->batch;
+  r.chan_in = (int64_t)o->chan_in; r.chan_out = (int64_t)o->chan_out; r.h_in = 1; r.h_out = 1;
+  r.w_in = (int64_t)o->l_in; r.w_out = (int64_t)o->l_out;
+  return r;
+}
+}  // namespace
+
+size_t conv2d_workspace_bytes(int dtype, const b200_conv2d_op* o, int backward) {
+  return o ? workspace_bytes_op(dtype, to_op(o), backward) : 0;
+}
+size_t conv1d_workspace_bytes(int dtype, const b200_conv1d_op* o, int backward) {
+  return o ? workspace_bytes_op(dtype, to_op(o), backward) : 0;
+}
+// (B, C, L) and (O, C/G, K) strides are widened to the 4-D form the kernels index with (height stride unused).
+int conv1d_forward(int dtype, const b200_conv1d_op* o, const void* img, const size_t is[3], const void* filters, void* out,
+                   void* ws, cudaStream_t stream) {
+  const size_t is4[4] = {is[0], is[1], 0, is[2]};
+  return forward_any(dtype, to_op(o), img, is4, filters, out, ws, stream);
+}
+int conv1d_backward(int dtype, const b200_conv1d_op* o, const void* img, void* grad_img, const void* filters,
+                    const size_t fs[3], void* grad_filters, const void* grad_out, void* ws, cudaStream_t stream) {
+  const size_t fs4[4] = {fs[0], fs[1], fs[2] * (size_t)o->kernel, fs[2]};
+  return backward_any(dtype, to_op(o), img, grad_img, filters, fs4, grad_filters, grad_out, ws, stream);
+}
+
+int conv2d_forward(int dtype, const b200_conv2d_op* o, const void* img, const size_t is[4], const void* filters,
+                   void* out, void* ws, cudaStream_t stream) {
+  return forward_any(dtype, to_op(o), img, is, filters, out, ws, stream);
+}
+
+int conv2d_backward(int dtype, const b200_conv2d_op* o, const void* img, void* grad_img, const void* filters,
+                    const size_t fs[4], void* grad_filters, const void* grad_out, void* ws, cudaStream_t stream) {
+  return backward_any(dtype, to_op(o), img, grad_img, filters, fs, grad_filters, grad_out, ws, stream);
 }
 
 }  // namespace b200

@@ -15,7 +15,7 @@ from __future__ import annotations
 import torch
 
 from . import _lib
-from ._lib import Conv2DOp, check, strides as _st
+from ._lib import Conv1DOp, Conv2DOp, check, strides as _st
 
 _DTYPES = {torch.float32: _lib.F32, torch.float64: _lib.F64, torch.float16: _lib.F16}
 
@@ -369,3 +369,38 @@ class Cuda:
 
 def _ptr(t):
     return None if t is None else t.data_ptr()
+
+
+def _conv1d(self, img, filters, stride=1, padding=0, dilation=1, groups=1):
+    """`(img, filters).conv1d(stride, padding, dilation, groups)` (conv1d/mod.rs:160-286); 2-D images are batch 1.
+    Returns (out, backward)."""
+    squeeze = img.dim() == 2
+    x = img.reshape((1,) + tuple(img.shape)) if squeeze else img
+    if not x.is_contiguous() or not filters.is_contiguous():
+        raise ShapeMismatch("Image & filter inputs to conv1d must be contiguous")
+    b, c, l = x.shape
+    o, cg, k = filters.shape
+    _assert_eq(c, cg * groups)
+    if o % groups:
+        raise ShapeMismatch("assertion failed: out_chan.size() % groups.size() == 0")
+    op = Conv1DOp(kernel=k, stride=stride, padding=padding, dilation=dilation, groups=groups, batch=b, chan_in=c,
+                  chan_out=o, l_in=l, l_out=conv2d_out_dim(l, k, stride, padding, dilation))
+    dt = self._dtype(x)
+    out = self._empty((b, o, op.l_out), x)
+    ws = self.get_workspace(self.lib.b200_conv1d_workspace_bytes(dt, op, 0))
+    check(self.lib.b200_conv1d_forward(dt, op, x.data_ptr(), _st(x.stride()), filters.data_ptr(), out.data_ptr(),
+                                       ws.data_ptr(), ws.numel(), self._stream()), "b200_conv1d_forward")
+
+    def backward(grad_out: torch.Tensor):
+        go = grad_out.reshape(out.shape).contiguous()
+        gx, gw = self.alloc_grad(x), self.alloc_grad(filters)
+        wsb = self.get_workspace(self.lib.b200_conv1d_workspace_bytes(dt, op, 1))
+        check(self.lib.b200_conv1d_backward(dt, op, x.data_ptr(), gx.data_ptr(), filters.data_ptr(),
+                                            _st(filters.stride()), gw.data_ptr(), go.data_ptr(), wsb.data_ptr(),
+                                            wsb.numel(), self._stream(), None), "b200_conv1d_backward")
+        return self.grad_view(gx, x).reshape(img.shape), self.grad_view(gw, filters)
+
+    return (out[0] if squeeze else out), backward
+
+
+Cuda.conv1d = _conv1d

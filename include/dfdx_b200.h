@@ -58,6 +58,12 @@ typedef struct {
   size_t chan_in, chan_out, h_in, h_out, w_in, w_out;
 } b200_conv2d_op;
 
+/* Mirrors `Conv1DOp`: 10 x usize, #[repr(C)] (dfdx-core/src/tensor_ops/conv1d/mod.rs:12-23). */
+typedef struct {
+  size_t kernel, stride, padding, dilation, groups, batch;
+  size_t chan_in, chan_out, l_in, l_out;
+} b200_conv1d_op;
+
 /* Activation applied by a fused epilogue. */
 typedef enum {
   B200_ACT_NONE = 0,
@@ -322,6 +328,24 @@ int b200_conv2d_forward(int dtype, const b200_conv2d_op* op,
 int b200_conv2d_backward(int dtype, const b200_conv2d_op* op,
                          const void* img, void* grad_img,
                          const void* filters, const size_t filters_strides[4], void* grad_filters,
+                         const void* grad_out,
+                         void* workspace, size_t workspace_bytes, void* stream, void* par_stream);
+
+/* ---- conv1d (the same lowering over an image of height 1) ---------------------------------------- */
+
+/* `Conv1DKernel for Cuda` (dfdx-core/src/tensor_ops/conv1d/cuda_kernel.rs:80-277 + conv1d.cu): unfold into patches
+ * (B, C*K, L_out), one batched GEMM, and for the backward pass the transposed gather of grad_out, the transposed
+ * filters and the batch sum of the filter gradient.  Same contracts as the conv2d entry points with 3-D strides:
+ * img (B, C, L) through `img_strides`, filters (O, C/G, K) contiguous in forward and through `filters_strides` in
+ * backward, out / grad_out (B, O, L_out) contiguous, img / grad_img contiguous in backward. */
+size_t b200_conv1d_workspace_bytes(int dtype, const b200_conv1d_op* op, int backward);
+int b200_conv1d_forward(int dtype, const b200_conv1d_op* op,
+                        const void* img, const size_t img_strides[3],
+                        const void* filters, void* out,
+                        void* workspace, size_t workspace_bytes, void* stream);
+int b200_conv1d_backward(int dtype, const b200_conv1d_op* op,
+                         const void* img, void* grad_img,
+                         const void* filters, const size_t filters_strides[3], void* grad_filters,
                          const void* grad_out,
                          void* workspace, size_t workspace_bytes, void* stream, void* par_stream);
 

@@ -226,6 +226,61 @@ def conv2d(img: torch.Tensor, filters: torch.Tensor, stride=1, padding=0, dilati
     return (out_t[0] if squeeze else out_t), backward
 
 
+def conv1d(img: torch.Tensor, filters: torch.Tensor, stride=1, padding=0, dilation=1, groups=1):
+    """`TryConv1D` on the oracle (dfdx-core/src/tensor_ops/conv1d/mod.rs:160-286; arithmetic of
+    conv1d/cpu_kernel.rs:20-250: patches[c, k, l] = img[c, l*stride + k*dilation - padding] or 0 outside, then one
+    matmul per image and group; backward = the transposed gather of grad_out times the transposed filters for the
+    image, and img x patches(grad_out)^T summed over the batch for the filters), in f64.  Returns (out, backward)."""
+    squeeze = img.dim() == 2
+    x = img.reshape((1,) + tuple(img.shape)) if squeeze else img
+    if not x.is_contiguous() or not filters.is_contiguous():
+        raise ShapeMismatch("Image & filter inputs to conv1d must be contiguous")
+    b, c, l = x.shape
+    o, cg, k = filters.shape
+    _assert_eq(c, cg * groups)
+    og = o // groups
+    l_out = conv2d_out_dim(l, k, stride, padding, dilation)
+    x64 = x.detach().cpu().to(torch.float64)
+    w64 = filters.detach().cpu().to(torch.float64)
+
+    def patches_of(t):                      # (B, C, L) -> (B, C, K, L_out) with zero padding
+        p = torch.zeros(t.shape[0], t.shape[1], k, l_out, dtype=torch.float64)
+        for kk in range(k):
+            for lo in range(l_out):
+                pos = lo * stride + kk * dilation - padding
+                if 0 <= pos < l:
+                    p[:, :, kk, lo] = t[:, :, pos]
+        return p
+
+    pat = patches_of(x64)
+    out = torch.zeros(b, o, l_out, dtype=torch.float64)
+    for g in range(groups):
+        wg = w64[g * og:(g + 1) * og].reshape(og, cg * k)
+        pg = pat[:, g * cg:(g + 1) * cg].reshape(b, cg * k, l_out)
+        for i in range(b):
+            out[i, g * og:(g + 1) * og], _ = matmul(wg, pg[i])
+
+    def backward(grad_out: torch.Tensor):
+        go = grad_out.detach().cpu().to(torch.float64).reshape(b, o, l_out)
+        gx = torch.zeros(b, c, l, dtype=torch.float64)
+        gw = torch.zeros(o, cg, k, dtype=torch.float64)
+        for g in range(groups):
+            wg = w64[g * og:(g + 1) * og].reshape(og, cg * k)
+            for i in range(b):
+                gp, _ = matmul(wg.t().contiguous(), go[i, g * og:(g + 1) * og])          # (cg*k, l_out)
+                gp = gp.reshape(cg, k, l_out)
+                for kk in range(k):
+                    for lo in range(l_out):
+                        pos = lo * stride + kk * dilation - padding
+                        if 0 <= pos < l:
+                            gx[i, g * cg:(g + 1) * cg, pos] += gp[:, kk, lo]
+                d, _ = matmul(go[i, g * og:(g + 1) * og], pat[i, g * cg:(g + 1) * cg].reshape(cg * k, l_out).t().contiguous())
+                gw[g * og:(g + 1) * og] += d.reshape(og, cg, k)
+        return gx.reshape(img.shape), gw
+
+    return (out[0] if squeeze else out), backward
+
+
 def fused_matmul(lhs: torch.Tensor, rhs: torch.Tensor, alpha: float = 1.0, bias: torch.Tensor = None,
                  relu: bool = False) -> torch.Tensor:
     """The op sequences the fused epilogues stand for, step by step in f64: `matmul`, then `* scalar`

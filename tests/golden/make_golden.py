@@ -12,6 +12,7 @@ Sources (dfdx v0.13.0):
     dfdx-core/src/tensor_ops/conv2d/tests.rs
     dfdx/src/nn/layers/linear.rs                (tests at :97-204)
     dfdx-core/src/tensor_ops/normalize.rs       (tests at :52-127; the normalisation inside LayerNorm1D)
+    dfdx-core/src/tensor_ops/conv1d/tests.rs
 """
 from __future__ import annotations
 
@@ -28,6 +29,7 @@ FILES = {
     "conv2d": "dfdx-core/src/tensor_ops/conv2d/tests.rs",
     "linear": "dfdx/src/nn/layers/linear.rs",
     "normalize": "dfdx-core/src/tensor_ops/normalize.rs",
+    "conv1d": "dfdx-core/src/tensor_ops/conv1d/tests.rs",
 }
 
 

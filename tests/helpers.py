@@ -39,6 +39,9 @@ class OracleBackend:
     def conv2d(self, x, w, **kw):
         return self.o.conv2d(x, w, **kw)
 
+    def conv1d(self, x, w, **kw):
+        return self.o.conv1d(x, w, **kw)
+
     def normalize(self, x, eps):
         y, bwd = self.o.layer_norm(x, None, None, eps)
         return y, lambda go: bwd(go)[0]
@@ -75,6 +78,13 @@ class CudaBackend:
         """`Linear::try_forward` through the fused entry point (x of rank 1..3 is viewed as rank 3)."""
         x3 = x.reshape((1,) * (3 - x.dim()) + tuple(x.shape))
         return self.dev.linear_forward(x3, weight_view, bias, relu).reshape(tuple(x.shape[:-1]) + (weight_view.shape[1],))
+
+    def conv1d(self, x, w, **kw):
+        out, bwd = self.dev.conv1d(x, w, **kw)
+
+        def backward(go):
+            return bwd(go.to(self.dtype).to(self.dev.device))
+        return out, backward
 
     def normalize(self, x, eps):
         """`normalize` over the last axis through the LayerNorm kernels (gamma = beta = NULL)."""

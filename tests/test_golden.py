@@ -149,6 +149,27 @@ def test_linear_fused_forward(be, name):
     _check(be, y_relu, dict(a[0], value=want.tolist()))
 
 
+# ------------------------------------------------------------------------------------------ conv1d
+CONV1D_CASES = {
+    "test_conv1d_default_stride_and_padding": dict(stride=1, padding=0, dilation=1, groups=1),
+    "test_conv1d_all": dict(stride=2, padding=1, dilation=2, groups=1),
+    "test_conv1d_all_grouped": dict(stride=2, padding=1, dilation=2, groups=2),
+}
+
+
+@pytest.mark.parametrize("name", list(CONV1D_CASES))
+def test_conv1d(be, name):
+    """dfdx-core/src/tensor_ops/conv1d/tests.rs:4-131: result, then g = result.exp().mean().backward()."""
+    t, a = _split(golden("conv1d")[name])
+    order = (1, 0) if name == "test_conv1d_all_grouped" else (0, 1)       # that test builds x before w
+    weight, x = be.tensor(t[order[0]]), be.tensor(t[order[1]])
+    y, bwd = be.conv1d(x, weight, **CONV1D_CASES[name])
+    _check(be, y, a[0])
+    gx, gw = bwd(d_exp_mean(be.host(y)))
+    _check(be, gx, a[1])
+    _check(be, gw, a[2])
+
+
 # ------------------------------------------------------------------------------------------ normalize
 @pytest.mark.parametrize("name", ["test_1d_normalize_axis_last", "test_2d_normalize_axis_last"])
 def test_normalize_last_axis(be, name):
