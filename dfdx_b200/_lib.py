@@ -82,6 +82,9 @@ SIGNATURES = {
     "b200_conv2d_workspace_bytes": (_sz, [_i, C.POINTER(Conv2DOp), _i]),
     "b200_conv2d_forward": (_i, [_i, C.POINTER(Conv2DOp), _vp, _szp, _vp, _vp, _vp, _sz, _vp]),
     "b200_conv2d_backward": (_i, [_i, C.POINTER(Conv2DOp), _vp, _vp, _vp, _szp, _vp, _vp, _vp, _sz, _vp, _vp]),
+    "b200_convtrans2d_workspace_bytes": (_sz, [_i, C.POINTER(Conv2DOp), _i]),
+    "b200_convtrans2d_forward": (_i, [_i, C.POINTER(Conv2DOp), _vp, _vp, _szp, _vp, _vp, _sz, _vp]),
+    "b200_convtrans2d_backward": (_i, [_i, C.POINTER(Conv2DOp), _vp, _vp, _vp, _szp, _vp, _vp, _vp, _sz, _vp, _vp]),
     "b200_conv1d_workspace_bytes": (_sz, [_i, C.POINTER(Conv1DOp), _i]),
     "b200_conv1d_forward": (_i, [_i, C.POINTER(Conv1DOp), _vp, _szp, _vp, _vp, _vp, _sz, _vp]),
     "b200_conv1d_backward": (_i, [_i, C.POINTER(Conv1DOp), _vp, _vp, _vp, _szp, _vp, _vp, _vp, _sz, _vp, _vp]),

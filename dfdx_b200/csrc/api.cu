@@ -14,6 +14,11 @@ namespace b200 {
 size_t conv2d_workspace_bytes(int dtype, const b200_conv2d_op* o, int backward);
 int conv2d_forward(int dtype, const b200_conv2d_op* o, const void* img, const size_t is[4], const void* filters,
                    void* out, void* ws, cudaStream_t stream);
+size_t convtrans2d_workspace_bytes(int dtype, const b200_convtrans2d_op* o, int backward);
+int convtrans2d_forward(int dtype, const b200_convtrans2d_op* o, const void* img, const void* filters, const size_t fs[4],
+                        void* out, void* ws, cudaStream_t stream);
+int convtrans2d_backward(int dtype, const b200_convtrans2d_op* o, const void* img, void* grad_img, const void* filters,
+                         const size_t fs[4], void* grad_filters, const void* grad_out, void* ws, cudaStream_t stream);
 size_t conv1d_workspace_bytes(int dtype, const b200_conv1d_op* o, int backward);
 int conv1d_forward(int dtype, const b200_conv1d_op* o, const void* img, const size_t is[3], const void* filters, void* out,
                    void* ws, cudaStream_t stream);
@@ -509,6 +514,51 @@ int b200_conv2d_backward(int dtype, const b200_conv2d_op* op, const void* img, v
   if (!device_state()) return note_cuda_error(cudaErrorInitializationError, "b200_init not called on this device");
   return conv2d_backward(dtype, op, img, grad_img, filters, filters_strides, grad_filters, grad_out, workspace,
                          (cudaStream_t)stream);
+}
+
+// ---- convtrans2d -----------------------------------------------------------------------------------
+size_t b200_convtrans2d_workspace_bytes(int dtype, const b200_convtrans2d_op* op, int backward) {
+  if (check_conv_op(op) || !valid_dtype(dtype)) return 0;
+  return convtrans2d_workspace_bytes(dtype, op, backward);
+}
+
+int b200_convtrans2d_forward(int dtype, const b200_convtrans2d_op* op, const void* img, const void* filters,
+                             const size_t filters_strides[4], void* out, void* workspace, size_t workspace_bytes,
+                             void* stream) {
+  if (!valid_dtype(dtype)) return B200_ERR_DTYPE;
+  int rc = check_conv_op(op);
+  if (rc) return rc;
+  if (!filters_strides) return B200_ERR_NULL;
+  const size_t need = convtrans2d_workspace_bytes(dtype, op, 0);
+  if (need == 0 || op->batch * op->chan_out * op->h_out * op->w_out == 0) return B200_OK;
+  if (!img || !filters || !out || !workspace) return B200_ERR_NULL;
+  if (workspace_bytes < need) return B200_ERR_WORKSPACE;
+  if (!device_state()) return note_cuda_error(cudaErrorInitializationError, "b200_init not called on this device");
+  return convtrans2d_forward(dtype, op, img, filters, filters_strides, out, workspace, (cudaStream_t)stream);
+}
+
+int b200_convtrans2d_backward(int dtype, const b200_convtrans2d_op* op, const void* img, void* grad_img,
+                              const void* filters, const size_t filters_strides[4], void* grad_filters,
+                              const void* grad_out, void* workspace, size_t workspace_bytes, void* stream,
+                              void* par_stream) {
+  (void)par_stream;
+  if (!valid_dtype(dtype)) return B200_ERR_DTYPE;
+  int rc = check_conv_op(op);
+  if (rc) return rc;
+  if (!filters_strides) return B200_ERR_NULL;
+  const size_t need = convtrans2d_workspace_bytes(dtype, op, 1);
+  if (need == 0) return B200_OK;
+  if (!img || !filters || !grad_out || !workspace) return B200_ERR_NULL;
+  if (workspace_bytes < need) return B200_ERR_WORKSPACE;
+  if (grad_img) {                       // the convolution that produces grad_img reads the filters as one dense block
+    const size_t kk = op->kernel * op->kernel, og = op->chan_out / op->groups;
+    if (filters_strides[3] != 1 || filters_strides[2] != op->kernel || filters_strides[1] != kk ||
+        filters_strides[0] != og * kk)
+      return B200_ERR_NOT_CONTIGUOUS;
+  }
+  if (!device_state()) return note_cuda_error(cudaErrorInitializationError, "b200_init not called on this device");
+  return convtrans2d_backward(dtype, op, img, grad_img, filters, filters_strides, grad_filters, grad_out, workspace,
+                              (cudaStream_t)stream);
 }
 
 // ---- conv1d ---------------------------------------------------------------------------------------

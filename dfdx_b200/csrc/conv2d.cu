@@ -238,7 +238,7 @@ size_t align256(size_t x) { return (x + 255) & ~(size_t)255; }
 
 template <typename T, typename A>
 int forward_t(int dtype, const Op& op, const T* img, const size_t is[4], const T* filters, T* out,
-              void* ws, cudaStream_t stream) {
+              void* ws, cudaStream_t stream, int beta = 0) {
   DeviceState* ds = device_state();
   const int sms = ds ? ds->sm_count : 148;
   T* patches = (T*)ws;
@@ -258,7 +258,7 @@ int forward_t(int dtype, const Op& op, const T* img, const size_t is[4], const T
   const int64_t m = op.chan_out / op.groups, k = (op.chan_in / op.groups) * op.kh * op.kw,
                 n = op.h_out * op.w_out, G = op.groups;
   GemmProblem p;
-  p.dtype = dtype; p.beta = 0; p.b0 = op.batch; p.b1 = G; p.m = m; p.k = k; p.n = n;
+  p.dtype = dtype; p.beta = beta; p.b0 = op.batch; p.b1 = G; p.m = m; p.k = k; p.n = n;
   p.a = filters; p.a_b0 = 0; p.a_b1 = m * k; p.a_r = k; p.a_c = 1;
   p.b = patches; p.b_b0 = G * k * n; p.b_b1 = k * n; p.b_r = n; p.b_c = 1;
   p.c = out; p.c_b0 = G * m * n; p.c_b1 = m * n; p.c_r = n; p.c_c = 1;
@@ -366,12 +366,12 @@ size_t workspace_bytes_op(int dtype, const Op& o, int backward) {
 }
 
 int forward_any(int dtype, const Op& op, const void* img, const size_t is[4], const void* filters, void* out, void* ws,
-                cudaStream_t stream) {
+                cudaStream_t stream, int beta = 0) {
   switch (dtype) {
-    case B200_F32: return forward_t<float, float>(dtype, op, (const float*)img, is, (const float*)filters, (float*)out, ws, stream);
-    case B200_F64: return forward_t<double, double>(dtype, op, (const double*)img, is, (const double*)filters, (double*)out, ws, stream);
+    case B200_F32: return forward_t<float, float>(dtype, op, (const float*)img, is, (const float*)filters, (float*)out, ws, stream, beta);
+    case B200_F64: return forward_t<double, double>(dtype, op, (const double*)img, is, (const double*)filters, (double*)out, ws, stream, beta);
     case B200_F16:
-    case B200_AMP_F16: return forward_t<__half, float>(dtype, op, (const __half*)img, is, (const __half*)filters, (__half*)out, ws, stream);
+    case B200_AMP_F16: return forward_t<__half, float>(dtype, op, (const __half*)img, is, (const __half*)filters, (__half*)out, ws, stream, beta);
     default: return B200_ERR_DTYPE;
   }
 }
@@ -396,7 +396,49 @@ Op to_op(const b200_conv1d_op* o) {
   r.w_in = (int64_t)o->l_in; r.w_out = (int64_t)o->l_out;
   return r;
 }
+// A transposed convolution is the data gradient of a convolution: convtrans2d(img, w) with img (B, C, H, W) and
+// w (C, O/G, K, K) equals the grad_img of the conv2d that maps (B, O, H_out, W_out) to (B, C, H, W) with the same
+// filters, fed with img as its grad_out.  `to_op_ct` is that conv2d (dfdx lowers it the same way:
+// convtrans2d/cuda_kernel.rs:77-148 gathers patches over the output positions and multiplies by transposed filters).
+Op to_op_ct(const b200_convtrans2d_op* o) {
+  Op r;
+  r.kh = r.kw = (int64_t)o->kernel; r.stride = (int64_t)o->stride; r.ph = r.pw = (int64_t)o->padding;
+  r.dilation = (int64_t)o->dilation; r.groups = (int64_t)o->groups; r.batch = (int64_t)o->batch;
+  r.chan_in = (int64_t)o->chan_out; r.chan_out = (int64_t)o->chan_in;
+  r.h_in = (int64_t)o->h_out; r.w_in = (int64_t)o->w_out; r.h_out = (int64_t)o->h_in; r.w_out = (int64_t)o->w_in;
+  return r;
+}
 }  // namespace
+
+size_t convtrans2d_workspace_bytes(int dtype, const b200_convtrans2d_op* o, int backward) {
+  (void)backward;                                            // both passes use the conv2d-backward layout
+  return o ? workspace_bytes_op(dtype, to_op_ct(o), 1) : 0;
+}
+
+// out (B, O, H_out, W_out) = convtrans2d(img (B, C, H, W) contiguous, filters (C, O/G, K, K) through `fs`).
+int convtrans2d_forward(int dtype, const b200_convtrans2d_op* o, const void* img, const void* filters, const size_t fs[4],
+                        void* out, void* ws, cudaStream_t stream) {
+  const Op op = to_op_ct(o);
+  const size_t out_bytes = (size_t)(op.batch * op.chan_in * op.h_in * op.w_in) * dtype_size(dtype);
+  if (out_bytes == 0) return B200_OK;
+  const int rc = note_cuda_error(cudaMemsetAsync(out, 0, out_bytes, stream), "cudaMemsetAsync(convtrans2d out)");
+  if (rc) return rc;                                         // the data-gradient path accumulates
+  return backward_any(dtype, op, nullptr, out, filters, fs, nullptr, img, ws, stream);
+}
+
+// grad_img += conv2d(grad_out, filters);  grad_filters (through `fs`) += the filter gradient of that conv2d with
+// grad_out as its image and img as its output gradient (convtrans2d/cuda_kernel.rs:150-265).
+int convtrans2d_backward(int dtype, const b200_convtrans2d_op* o, const void* img, void* grad_img, const void* filters,
+                         const size_t fs[4], void* grad_filters, const void* grad_out, void* ws, cudaStream_t stream) {
+  const Op op = to_op_ct(o);
+  int rc = B200_OK;
+  if (grad_img) {
+    const size_t gs[4] = {(size_t)(op.chan_in * op.h_in * op.w_in), (size_t)(op.h_in * op.w_in), (size_t)op.w_in, 1};
+    if ((rc = forward_any(dtype, op, grad_out, gs, filters, grad_img, ws, stream, 1))) return rc;
+  }
+  if (grad_filters) rc = backward_any(dtype, op, grad_out, nullptr, filters, fs, grad_filters, img, ws, stream);
+  return rc;
+}
 
 size_t conv2d_workspace_bytes(int dtype, const b200_conv2d_op* o, int backward) {
   return o ? workspace_bytes_op(dtype, to_op(o), backward) : 0;

@@ -403,4 +403,46 @@ def _conv1d(self, img, filters, stride=1, padding=0, dilation=1, groups=1):
     return (out[0] if squeeze else out), backward
 
 
+def convtrans2d_out_dim(dim: int, kernel: int, stride: int, padding: int, dilation: int) -> int:
+    """convtrans2d/mod.rs:108-121."""
+    full = (dim - 1) * stride + dilation * (kernel - 1) + 1
+    if full < 2 * padding:
+        raise ShapeMismatch("called `Option::unwrap()` on a `None` value")
+    return full - 2 * padding
+
+
+def _convtrans2d(self, img, filters, stride=1, padding=0, dilation=1, groups=1):
+    """`(img, filters).convtrans2d(stride, padding, dilation, groups)` (convtrans2d/mod.rs:124-280): img (B,C,H,W) or
+    (C,H,W), filters (C, O/G, K, K).  Returns (out, backward)."""
+    squeeze = img.dim() == 3
+    x = img.reshape((1,) + tuple(img.shape)) if squeeze else img
+    if not x.is_contiguous() or not filters.is_contiguous():
+        raise ShapeMismatch("Image & filter inputs to conv2d must be contiguous")
+    b, c, h, w = x.shape
+    c2, og, k, k2 = filters.shape
+    _assert_eq(c, c2)
+    _assert_eq(k, k2)
+    op = Conv2DOp(kernel=k, stride=stride, padding=padding, dilation=dilation, groups=groups, batch=b, chan_in=c,
+                  chan_out=og * groups, h_in=h, h_out=convtrans2d_out_dim(h, k, stride, padding, dilation), w_in=w,
+                  w_out=convtrans2d_out_dim(w, k, stride, padding, dilation))
+    dt = self._dtype(x)
+    out = self._empty((b, op.chan_out, op.h_out, op.w_out), x)
+    ws = self.get_workspace(self.lib.b200_convtrans2d_workspace_bytes(dt, op, 0))
+    check(self.lib.b200_convtrans2d_forward(dt, op, x.data_ptr(), filters.data_ptr(), _st(filters.stride()),
+                                            out.data_ptr(), ws.data_ptr(), ws.numel(), self._stream()),
+          "b200_convtrans2d_forward")
+
+    def backward(grad_out: torch.Tensor):
+        go = grad_out.reshape(out.shape).contiguous()
+        gx, gw = self.alloc_grad(x), self.alloc_grad(filters)
+        wsb = self.get_workspace(self.lib.b200_convtrans2d_workspace_bytes(dt, op, 1))
+        check(self.lib.b200_convtrans2d_backward(dt, op, x.data_ptr(), gx.data_ptr(), filters.data_ptr(),
+                                                 _st(filters.stride()), gw.data_ptr(), go.data_ptr(), wsb.data_ptr(),
+                                                 wsb.numel(), self._stream(), None), "b200_convtrans2d_backward")
+        return self.grad_view(gx, x).reshape(img.shape), self.grad_view(gw, filters)
+
+    return (out[0] if squeeze else out), backward
+
+
 Cuda.conv1d = _conv1d
+Cuda.convtrans2d = _convtrans2d

@@ -58,6 +58,10 @@ typedef struct {
   size_t chan_in, chan_out, h_in, h_out, w_in, w_out;
 } b200_conv2d_op;
 
+/* Mirrors `ConvTrans2DOp`: the same 12 x usize as `Conv2DOp`
+ * (dfdx-core/src/tensor_ops/convtrans2d/mod.rs:12-28). */
+typedef b200_conv2d_op b200_convtrans2d_op;
+
 /* Mirrors `Conv1DOp`: 10 x usize, #[repr(C)] (dfdx-core/src/tensor_ops/conv1d/mod.rs:12-23). */
 typedef struct {
   size_t kernel, stride, padding, dilation, groups, batch;
@@ -348,6 +352,23 @@ int b200_conv1d_backward(int dtype, const b200_conv1d_op* op,
                          const void* filters, const size_t filters_strides[3], void* grad_filters,
                          const void* grad_out,
                          void* workspace, size_t workspace_bytes, void* stream, void* par_stream);
+
+/* ---- convtrans2d (the data gradient of a conv2d, run forward) ------------------------------------- */
+
+/* `ConvTrans2DKernel for Cuda` (dfdx-core/src/tensor_ops/convtrans2d/cuda_kernel.rs:77-265 + convtrans2d.cu):
+ * out (B, O, H_out, W_out) = convtrans2d(img (B, C, H, W), filters (C, O/G, K, K)); `out` is uninitialised on entry.
+ * img, out, grad_out, grad_img contiguous (the reference panics otherwise, convtrans2d/mod.rs:242-244); filters and
+ * grad_filters are addressed through `filters_strides`, and the backward pass needs them contiguous for grad_img
+ * (B200_ERR_NOT_CONTIGUOUS otherwise).  backward: grad_img += ..., grad_filters += ...; either may be NULL. */
+size_t b200_convtrans2d_workspace_bytes(int dtype, const b200_convtrans2d_op* op, int backward);
+int b200_convtrans2d_forward(int dtype, const b200_convtrans2d_op* op,
+                             const void* img, const void* filters, const size_t filters_strides[4], void* out,
+                             void* workspace, size_t workspace_bytes, void* stream);
+int b200_convtrans2d_backward(int dtype, const b200_convtrans2d_op* op,
+                              const void* img, void* grad_img,
+                              const void* filters, const size_t filters_strides[4], void* grad_filters,
+                              const void* grad_out,
+                              void* workspace, size_t workspace_bytes, void* stream, void* par_stream);
 
 /* ---- conv2d forward without any allocation ------------------------------------------------------ */
 

@@ -281,6 +281,58 @@ def conv1d(img: torch.Tensor, filters: torch.Tensor, stride=1, padding=0, dilati
     return (out[0] if squeeze else out), backward
 
 
+def convtrans2d(img: torch.Tensor, filters: torch.Tensor, stride=1, padding=0, dilation=1, groups=1):
+    """`TryConvTrans2D` on the oracle (dfdx-core/src/tensor_ops/convtrans2d/mod.rs:124-280; arithmetic of
+    convtrans2d/cpu_kernel.rs:9-271): input pixel (y, x) feeds output pixel (y*stride + k1*dilation - padding,
+    x*stride + k2*dilation - padding) through tap (k1, k2) when that lies inside the output (`unfold_idx`, :10-17);
+    filters are (C, O/G, K, K).  f64.  Returns (out, backward)."""
+    squeeze = img.dim() == 3
+    x = img.reshape((1,) + tuple(img.shape)) if squeeze else img
+    if not x.is_contiguous() or not filters.is_contiguous():
+        raise ShapeMismatch("Image & filter inputs to conv2d must be contiguous")
+    b, c, h, w = x.shape
+    c2, og, k, k2 = filters.shape
+    _assert_eq(c, c2)
+    _assert_eq(k, k2)
+    o, cg = og * groups, c // groups
+    h_out = (h - 1) * stride + dilation * (k - 1) + 1 - 2 * padding
+    w_out = (w - 1) * stride + dilation * (k - 1) + 1 - 2 * padding
+    x64 = x.detach().cpu().to(torch.float64)
+    w64 = filters.detach().cpu().to(torch.float64)
+
+    def taps():
+        for k1 in range(k):
+            for kk2 in range(k):
+                for y in range(h):
+                    oh = y * stride + k1 * dilation - padding
+                    if not 0 <= oh < h_out:
+                        continue
+                    for xx in range(w):
+                        ow = xx * stride + kk2 * dilation - padding
+                        if 0 <= ow < w_out:
+                            yield k1, kk2, y, xx, oh, ow
+
+    out = torch.zeros(b, o, h_out, w_out, dtype=torch.float64)
+    for g in range(groups):
+        xs, ws = x64[:, g * cg:(g + 1) * cg], w64[g * cg:(g + 1) * cg]              # (B, cg, H, W), (cg, og, K, K)
+        for k1, kk2, y, xx, oh, ow in taps():
+            out[:, g * og:(g + 1) * og, oh, ow] += xs[:, :, y, xx] @ ws[:, :, k1, kk2]
+
+    def backward(grad_out: torch.Tensor):
+        go = grad_out.detach().cpu().to(torch.float64).reshape(b, o, h_out, w_out)
+        gx = torch.zeros(b, c, h, w, dtype=torch.float64)
+        gw = torch.zeros(c, og, k, k, dtype=torch.float64)
+        for g in range(groups):
+            xs, ws = x64[:, g * cg:(g + 1) * cg], w64[g * cg:(g + 1) * cg]
+            gs = go[:, g * og:(g + 1) * og]
+            for k1, kk2, y, xx, oh, ow in taps():
+                gx[:, g * cg:(g + 1) * cg, y, xx] += gs[:, :, oh, ow] @ ws[:, :, k1, kk2].t()
+                gw[g * cg:(g + 1) * cg, :, k1, kk2] += xs[:, :, y, xx].t() @ gs[:, :, oh, ow]
+        return gx.reshape(img.shape), gw
+
+    return (out[0] if squeeze else out), backward
+
+
 def fused_matmul(lhs: torch.Tensor, rhs: torch.Tensor, alpha: float = 1.0, bias: torch.Tensor = None,
                  relu: bool = False) -> torch.Tensor:
     """The op sequences the fused epilogues stand for, step by step in f64: `matmul`, then `* scalar`

@@ -13,6 +13,7 @@ Sources (dfdx v0.13.0):
     dfdx/src/nn/layers/linear.rs                (tests at :97-204)
     dfdx-core/src/tensor_ops/normalize.rs       (tests at :52-127; the normalisation inside LayerNorm1D)
     dfdx-core/src/tensor_ops/conv1d/tests.rs
+    dfdx-core/src/tensor_ops/convtrans2d/tests.rs
 """
 from __future__ import annotations
 
@@ -30,6 +31,7 @@ FILES = {
     "linear": "dfdx/src/nn/layers/linear.rs",
     "normalize": "dfdx-core/src/tensor_ops/normalize.rs",
     "conv1d": "dfdx-core/src/tensor_ops/conv1d/tests.rs",
+    "convtrans2d": "dfdx-core/src/tensor_ops/convtrans2d/tests.rs",
 }
 
 
@@ -98,7 +100,7 @@ def extract(src: str) -> dict:
         body_start = fn.end() - 1
         body = src[body_start:_balanced(src, body_start, "{", "}")]
         events = []
-        for ev in re.finditer(r"(dev\s*\.\s*tensor\s*\(|assert_close_to_literal!\s*\()", body):
+        for ev in re.finditer(r"(dev(?:ice)?\s*\.\s*tensor\s*\(|assert_close_to_literal!\s*\()", body):
             open_idx = ev.end() - 1
             close_idx = _balanced(body, open_idx, "(", ")")
             args = _split_args(body[open_idx + 1:close_idx - 1])

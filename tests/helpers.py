@@ -42,6 +42,9 @@ class OracleBackend:
     def conv1d(self, x, w, **kw):
         return self.o.conv1d(x, w, **kw)
 
+    def convtrans2d(self, x, w, **kw):
+        return self.o.convtrans2d(x, w, **kw)
+
     def normalize(self, x, eps):
         y, bwd = self.o.layer_norm(x, None, None, eps)
         return y, lambda go: bwd(go)[0]
@@ -78,6 +81,13 @@ class CudaBackend:
         """`Linear::try_forward` through the fused entry point (x of rank 1..3 is viewed as rank 3)."""
         x3 = x.reshape((1,) * (3 - x.dim()) + tuple(x.shape))
         return self.dev.linear_forward(x3, weight_view, bias, relu).reshape(tuple(x.shape[:-1]) + (weight_view.shape[1],))
+
+    def convtrans2d(self, x, w, **kw):
+        out, bwd = self.dev.convtrans2d(x, w, **kw)
+
+        def backward(go):
+            return bwd(go.to(self.dtype).to(self.dev.device))
+        return out, backward
 
     def conv1d(self, x, w, **kw):
         out, bwd = self.dev.conv1d(x, w, **kw)

@@ -170,6 +170,28 @@ def test_conv1d(be, name):
     _check(be, gw, a[2])
 
 
+# ------------------------------------------------------------------------------------------ convtrans2d
+CONVTRANS2D_CASES = {
+    "test_convtrans2d_default": dict(stride=1, padding=0, dilation=1, groups=1),
+    "test_convtrans2d_stride_2": dict(stride=2, padding=0, dilation=1, groups=1),
+    "test_convtrans2d_padded": dict(stride=1, padding=1, dilation=1, groups=1),
+    "test_convtrans2d_grouped": dict(stride=1, padding=0, dilation=1, groups=2),
+    "test_convtrans2d_dilated": dict(stride=1, padding=0, dilation=2, groups=1),
+}
+
+
+@pytest.mark.parametrize("name", list(CONVTRANS2D_CASES))
+def test_convtrans2d(be, name):
+    """dfdx-core/src/tensor_ops/convtrans2d/tests.rs:4-516: y, then g = y.exp().mean().backward()."""
+    t, a = _split(golden("convtrans2d")[name])
+    x, w = be.tensor(t[0]), be.tensor(t[1])
+    y, bwd = be.convtrans2d(x, w, **CONVTRANS2D_CASES[name])
+    _check(be, y, a[0])
+    gx, gw = bwd(d_exp_mean(be.host(y)))
+    _check(be, gx, a[1])
+    _check(be, gw, a[2])
+
+
 # ------------------------------------------------------------------------------------------ normalize
 @pytest.mark.parametrize("name", ["test_1d_normalize_axis_last", "test_2d_normalize_axis_last"])
 def test_normalize_last_axis(be, name):
