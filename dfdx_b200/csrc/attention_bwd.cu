@@ -122,7 +122,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tma_r1, const __grid_co
       mbar_init(smem_u32(&bar_c_empty[s]), 1);
     }
     for (int b = 0; b < 2; ++b) {
-      mbar_init(smem_u32(&bar_sdp_full[b]), 1);
+      mbar_init(smem_u32(&bar_sdp_full[b]), 2);             // S' and dP' are committed by different issuers
       mbar_init(smem_u32(&bar_sdp_empty[b]), 8);            // one arrival per row warp
       mbar_init(smem_u32(&bar_a_full[b]), 8);
       mbar_init(smem_u32(&bar_a_empty[b]), 1);
@@ -173,11 +173,10 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tma_r1, const __grid_co
       }
     }
     __syncwarp();
-  } else if (warp == 9 || warp == 10) {
+  } else if (warp >= 9) {
     // ------------------------------------------------------------------ MMA issuers
-    // warp 9 issues S' and dP', warp 10 the accumulator MMAs: two short instruction streams instead of one long
-    // one (the issuing thread's waits, descriptor updates and commits are a serial chain that competes with the
-    // row warps for issue slots).
+    // warp 9 issues S', warp 11 dP', warp 10 the accumulator MMAs: three short instruction streams instead of one
+    // long one (each wait, MMA and commit of the issuing thread is a serial, long-latency step).
     if (lane == 0) {
       const uint32_t idesc_s = (1u << 4) | ((uint32_t)(64 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);             // N = 64
       const uint32_t idesc_acc = (1u << 4) | (1u << 16) | ((uint32_t)(DP >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);  // B MN-major
@@ -185,9 +184,12 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tma_r1, const __grid_co
       const uint64_t dm = make_smem_desc(smem_base, 8192, 1024, 2);            // MN-major column tile (d-chunk stride 8192)
       const uint32_t hi_k = (uint32_t)(dk >> 32), hi_m = (uint32_t)(dm >> 32);
       const uint32_t lo_k = (uint32_t)dk, lo_m = (uint32_t)dm;
-      if (warp == 9) {
+      if (warp == 9 || warp == 11) {
+        const bool second = warp == 11;                      // false: S' = R1 C1^T, true: dP' = R2 C2^T
+        const uint32_t r_off = second ? (uint32_t)C::R_BYTES : 0u, c_off = second ? (uint32_t)C::C_BYTES : 0u;
+        const uint32_t d_off = second ? C::TM_DP : C::TM_S;
         bool ok = mbar_wait(smem_u32(&bar_r), 0, abortp, g.wait_limit);
-        // S'(j) and dP'(j): need column tile j and, for j >= 2, the row threads to have read buffer j & 1
+        // (j): needs column tile j and, for j >= 2, the row threads to have read buffer j & 1
         for (int j = 0; ok && j < T; ++j) {
           const int s = j % ST, b = j & 1;
           if (!mbar_wait(smem_u32(&bar_c_full[s]), ((uint32_t)(j / ST)) & 1u, abortp, g.wait_limit)) break;
@@ -195,14 +197,9 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tma_r1, const __grid_co
           tc_fence_after();
           const uint32_t c_lo = lo_k + (uint32_t)((C::OFF_C + s * 2 * C::C_BYTES) >> 4);
           for (int ks = 0; ks < ksteps; ++ks) {
-            const uint32_t ro = (uint32_t)(((ks >> 2) * 16384 + (ks & 3) * 32) >> 4);
-            const uint32_t co = (uint32_t)(((ks >> 2) * 8192 + (ks & 3) * 32) >> 4);
-            umma_lohi<2>(tmem_base + C::TM_S + b * 64, lo_k + ro, hi_k, c_lo + co, hi_k, idesc_s, ks > 0 ? 1u : 0u);
-          }
-          for (int ks = 0; ks < ksteps; ++ks) {
-            const uint32_t ro = (uint32_t)((C::R_BYTES + (ks >> 2) * 16384 + (ks & 3) * 32) >> 4);
-            const uint32_t co = (uint32_t)((C::C_BYTES + (ks >> 2) * 8192 + (ks & 3) * 32) >> 4);
-            umma_lohi<2>(tmem_base + C::TM_DP + b * 64, lo_k + ro, hi_k, c_lo + co, hi_k, idesc_s, ks > 0 ? 1u : 0u);
+            const uint32_t ro = (uint32_t)((r_off + (ks >> 2) * 16384 + (ks & 3) * 32) >> 4);
+            const uint32_t co = (uint32_t)((c_off + (ks >> 2) * 8192 + (ks & 3) * 32) >> 4);
+            umma_lohi<2>(tmem_base + d_off + b * 64, lo_k + ro, hi_k, c_lo + co, hi_k, idesc_s, ks > 0 ? 1u : 0u);
           }
           umma_commit(smem_u32(&bar_sdp_full[b]));
         }
