@@ -133,7 +133,7 @@ def cpu_baseline_run(items: int, repeats: int):
 
 
 def cpu_baseline_block():
-    """Bounded (~10-20 s) CPU sample: one item first, then as many items as fit the budget."""
+    """Bounded (~10-20 s) CPU sample: one item first, then as many items as fit that time."""
     t1, threads = cpu_baseline_run(1, 1)
     items = max(1, min(B, int(12.0 / max(t1[0], 1e-3))))
     t, threads = cpu_baseline_run(items, 1)

@@ -214,7 +214,7 @@ class EncoderBlock(torch.nn.Module):
 
 
 class Encoder(torch.nn.Module):
-    """`layers` encoder blocks (BASELINE configuration 5: 6 x (d_model 512, 8 heads, ffn 2048))."""
+    """`layers` encoder blocks (benchmark configuration 5: 6 x (d_model 512, 8 heads, ffn 2048))."""
 
     def __init__(self, dev: Cuda, layers=6, model=512, heads=8, ff=2048, seed=0, fused=True):
         super().__init__()

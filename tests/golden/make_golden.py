@@ -130,7 +130,9 @@ def extract(src: str) -> dict:
 
 
 def main() -> None:
-    root = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: make_golden.py /path/to/dfdx")
+    root = Path(sys.argv[1])
     for name, rel in FILES.items():
         tests = extract((root / rel).read_text())
         out = {"source": rel, "tests": tests}

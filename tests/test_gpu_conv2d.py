@@ -1,7 +1,7 @@
 """GPU parity of conv2d (unfold + GEMM lowering) against the CPU oracle, through the C ABI.
 
 Cases follow dfdx-core/src/tensor_ops/conv2d/tests.rs: stride / padding / dilation / groups
-variants, batched vs single image (:218-250), grouped vs sliced (:404-464), plus BASELINE config 4 at
+variants, batched vs single image (:218-250), grouped vs sliced (:404-464), plus benchmark configuration 4 at
 full size on sampled output channels / pixels.
 """
 import pytest

@@ -2,7 +2,7 @@
 
 Covers: the two GEMM seams (`Cuda::gemm` / `gemm_batch`) over every operand layout dfdx can hand
 over, forced through each kernel family; the four kernel traits forward + backward; the reference's
-property tests (matmul/mod.rs:412-527); and the BASELINE configurations at full size through
+property tests (matmul/mod.rs:412-527); and the benchmark configurations at full size through
 sampled rows of the oracle plus size-independent properties.
 
 Tolerances: relative Frobenius error vs the f64 oracle <= 1e-5 (f32), <= 2e-3 (f16), 1e-12 (f64).
@@ -348,7 +348,7 @@ def test_shape_mismatch_panics(cuda_dev):
             dev.matmul(a, b)
 
 
-# --------------------------------------------------------------------------------- BASELINE configs, full size
+# --------------------------------------------------------------------------------- benchmark configurations, full size
 def _rows_check(oracle, got_rows, a_rows, b, tol):
     want, _ = oracle.matmul(a_rows, b)
     err = oracle.rel_frobenius(got_rows, want)
