@@ -206,7 +206,7 @@ int b200_set_store_mode(int mode) {
 /* Testing hook: split-K of the f32 tensor-core kernel: 0 (default) planner's choice, 1 never, n in 2..64 forces
  * n K-slices on single-batch problems. */
 int b200_set_split_k(int mode) {
-  if (mode < 0 || mode > 64) return B200_ERR_UNSUPPORTED;
+  if (mode < -1 || mode > 64) return B200_ERR_UNSUPPORTED;
   tc_set_split_mode(mode);
   return B200_OK;
 }

@@ -274,6 +274,8 @@ struct TcArgs {
   long long total_tiles;
   int ksplit, kb_per_slice;       // f32 kernel: K is cut into ksplit slices of kb_per_slice k-blocks; a work unit is
   long long total_units;          // (tile, slice); slices of one tile add their partial results atomically
+  int streamk;                    // f32 kernel: the (tile, k-block) space is cut into one contiguous range per CTA
+  long long sk_per_cta;           // k-blocks per CTA; a unit is the part of one tile inside the CTA's range (may be empty)
   float* split_out;               // f16 kernel with ksplit > 1: f32 scratch (m x split_ld, zeroed) that takes the
   long long split_ld;             // partial sums; a finalize kernel then writes C = f16(beta*C + scratch)
   int red, k_blocks;              // k iterations per tile = red * k_blocks
@@ -495,6 +497,20 @@ struct TileCoord { int mt, nt, ib0, ib1; };
 struct Unit { long long tile; int kb_lo, kb_hi; };
 __device__ __forceinline__ Unit decode_unit(const TcArgs& g, long long unit, int total_kb) {
   Unit u;
+  if (g.streamk) {
+    // unit = blockIdx.x + i * gridDim.x is the i-th tile that CTA blockIdx.x's k-block range touches
+    const long long cta = unit % gridDim.x, i = unit / gridDim.x;
+    const long long start = cta * g.sk_per_cta;
+    long long end = start + g.sk_per_cta;
+    const long long all = g.total_tiles * (long long)total_kb;
+    if (end > all) end = all;
+    u.tile = start / total_kb + i;
+    const long long t0 = u.tile * (long long)total_kb;
+    const long long lo = start > t0 ? start : t0, hi = end < t0 + total_kb ? end : t0 + total_kb;
+    if (hi <= lo || u.tile >= g.total_tiles) { u.tile = 0; u.kb_lo = u.kb_hi = 0; }   // nothing of that tile in the range
+    else { u.kb_lo = (int)(lo - t0); u.kb_hi = (int)(hi - t0); }
+    return u;
+  }
   u.tile = unit / g.ksplit;
   const int slice = (int)(unit - u.tile * g.ksplit);
   u.kb_lo = slice * g.kb_per_slice;

@@ -131,9 +131,11 @@ int b200_set_cta_pair_mode(int mode);
  * 2 column stores wherever possible (the kernel's M runs along the output's unit-stride dimension; warp stores
  * are contiguous). */
 int b200_set_store_mode(int mode);
-/* Split-K of the f32 tensor-core kernel (testing / profiling): 0 (default) the planner cuts K into slices when
- * the output tiles alone would leave most SMs idle (partial results are then added atomically, so the last
- * bits of such results can differ between runs), 1 never splits, n in 2..64 forces n slices. */
+/* K decomposition of the tensor-core kernels (testing / profiling): 0 (default) the planner cuts K into slices when
+ * the output tiles alone would leave most SMs idle (partial results are then added atomically, so the last bits of
+ * such results can differ between runs); 1 never splits; n in 2..64 forces n slices; -1 forces, for f32, the
+ * stream-K decomposition (the (tile, k-block) space cut into one equal contiguous range per SM; tiles cut by a
+ * range boundary are summed atomically), which the planner never picks on its own. */
 int b200_set_split_k(int mode);
 /* Number of kernel launches this library has enqueued since load (all threads). */
 uint64_t b200_launch_count(void);

@@ -184,6 +184,29 @@ def test_split_k_f32(cuda_dev, oracle, layout, slices):
         cuda_dev.set_path(dfdx_b200.PATH_AUTO)
 
 
+@pytest.mark.parametrize("tile_n", [0, 64, 128])
+@pytest.mark.parametrize("layout", ["rcr", "crr", "rrc", "ccc"])
+def test_stream_k_f32(cuda_dev, oracle, layout, tile_n):
+    """f32 stream-K forced: every CTA takes one contiguous range of the (tile, k-block) space; ranges that cut a
+    tile add their partial sums atomically.  Few tiles (ranges shorter than a tile), many tiles (several whole tiles
+    per range plus two cut ones), ragged shapes, beta 0 (NaN-poisoned output) and beta 1, both store orientations."""
+    cuda_dev.set_path(dfdx_b200.PATH_TENSOR)
+    assert cuda_dev.lib.b200_set_split_k(-1) == 0
+    assert cuda_dev.lib.b200_set_tile_n(tile_n) == 0
+    try:
+        for store in (1, 2):
+            cuda_dev.lib.b200_set_store_mode(store)
+            shapes = [(128, 1024, 256), (200, 1160, 136), (1160, 264, 2056), (4104, 520, 1032)]
+            for i, (m, k, n) in enumerate(shapes):
+                check_gemm(cuda_dev, oracle, m, k, n, layout[0], layout[1], layout[2], i % 2, torch.float32, pad=8,
+                           seed=450 + i)
+    finally:
+        cuda_dev.lib.b200_set_split_k(0)
+        cuda_dev.lib.b200_set_tile_n(0)
+        cuda_dev.lib.b200_set_store_mode(0)
+        cuda_dev.set_path(dfdx_b200.PATH_AUTO)
+
+
 @pytest.mark.parametrize("dtype", [torch.float16, torch.float32])
 def test_tensor_core_long_k_accuracy(cuda_dev, oracle, dtype):
     """The stated bound must hold where accumulation is longest: K = 16384."""
