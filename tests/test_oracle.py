@@ -141,3 +141,66 @@ def test_cpu_baseline_port_matches_oracle(oracle):
     assert oracle.rel_frobenius(y, want_y) < 1e-6
     assert oracle.rel_frobenius(gx, want_gx) < 1e-6
     assert oracle.rel_frobenius(gw.permute(1, 0), want_gw) < 1e-6
+
+
+# ---- restatements added for the fused / neighbouring ops: each against torch's own f64 implementation ----------
+def test_attention_oracle_matches_torch_autograd(oracle):
+    g = torch.Generator().manual_seed(11)
+    q = torch.randn(2, 20, 3, 16, generator=g, dtype=torch.float64).permute(0, 2, 1, 3).requires_grad_(True)
+    k = torch.randn(2, 24, 3, 16, generator=g, dtype=torch.float64).permute(0, 2, 3, 1).requires_grad_(True)
+    v = torch.randn(2, 24, 3, 16, generator=g, dtype=torch.float64).permute(0, 2, 1, 3).requires_grad_(True)
+    go = torch.randn(2, 3, 20, 16, generator=g, dtype=torch.float64)
+    ref = torch.softmax(q @ k * 0.25, -1) @ v
+    ref.backward(go)
+    out, lse = oracle.attention(q.detach(), k.detach(), v.detach(), 0.25)
+    assert torch.allclose(out, ref.detach(), atol=1e-12)
+    assert torch.allclose(lse, torch.logsumexp(q.detach() @ k.detach() * 0.25, -1), atol=1e-12)
+    gq, gk, gv = oracle.attention_backward(q.detach(), k.detach(), v.detach(), 0.25, go)
+    assert torch.allclose(gq, q.grad, atol=1e-12) and torch.allclose(gk, k.grad, atol=1e-12)
+    assert torch.allclose(gv, v.grad, atol=1e-12)
+
+
+def test_layer_norm_oracle_matches_torch(oracle):
+    g = torch.Generator().manual_seed(12)
+    x = torch.randn(7, 5, 33, generator=g, dtype=torch.float64, requires_grad=True)
+    gamma = torch.randn(33, generator=g, dtype=torch.float64, requires_grad=True)
+    beta = torch.randn(33, generator=g, dtype=torch.float64, requires_grad=True)
+    go = torch.randn(7, 5, 33, generator=g, dtype=torch.float64)
+    ref = torch.nn.functional.layer_norm(x, (33,), gamma, beta, 1e-5)
+    ref.backward(go)
+    y, bwd = oracle.layer_norm(x.detach(), gamma.detach(), beta.detach(), 1e-5)
+    gx, gg, gb = bwd(go)
+    assert torch.allclose(y, ref.detach(), atol=1e-12)
+    assert torch.allclose(gx, x.grad, atol=1e-12)
+    assert torch.allclose(gg, gamma.grad, atol=1e-12) and torch.allclose(gb, beta.grad, atol=1e-12)
+
+
+@pytest.mark.parametrize("case", [(2, 4, 6, 19, 3, 2, 1, 2, 2), (1, 3, 5, 28, 6, 1, 0, 1, 1), (3, 6, 6, 17, 4, 3, 2, 1, 3)])
+def test_conv1d_oracle_matches_torch(oracle, case):
+    b, c, o, l, k, stride, pad, dil, groups = case
+    g = torch.Generator().manual_seed(sum(case))
+    x = torch.randn(b, c, l, generator=g, dtype=torch.float64, requires_grad=True)
+    w = torch.randn(o, c // groups, k, generator=g, dtype=torch.float64, requires_grad=True)
+    ref = torch.nn.functional.conv1d(x, w, None, stride, pad, dil, groups)
+    go = torch.randn(*ref.shape, generator=g, dtype=torch.float64)
+    ref.backward(go)
+    y, bwd = oracle.conv1d(x.detach(), w.detach(), stride=stride, padding=pad, dilation=dil, groups=groups)
+    gx, gw = bwd(go)
+    assert torch.allclose(y, ref.detach(), atol=1e-12)
+    assert torch.allclose(gx, x.grad, atol=1e-12) and torch.allclose(gw, w.grad, atol=1e-12)
+
+
+@pytest.mark.parametrize("case", [(2, 4, 6, 5, 6, 3, 2, 1, 1, 2), (1, 3, 2, 4, 4, 2, 1, 0, 2, 1), (2, 6, 3, 5, 5, 3, 3, 2, 1, 3)])
+def test_convtrans2d_oracle_matches_torch(oracle, case):
+    b, c, o, h, w_, k, stride, pad, dil, groups = case
+    g = torch.Generator().manual_seed(sum(case))
+    x = torch.randn(b, c, h, w_, generator=g, dtype=torch.float64, requires_grad=True)
+    w = torch.randn(c, o // groups, k, k, generator=g, dtype=torch.float64, requires_grad=True)
+    ref = torch.nn.functional.conv_transpose2d(x, w, None, stride, pad, 0, groups, dil)
+    go = torch.randn(*ref.shape, generator=g, dtype=torch.float64)
+    ref.backward(go)
+    y, bwd = oracle.convtrans2d(x.detach(), w.detach(), stride=stride, padding=pad, dilation=dil, groups=groups)
+    gx, gw = bwd(go)
+    assert y.shape == ref.shape
+    assert torch.allclose(y, ref.detach(), atol=1e-12)
+    assert torch.allclose(gx, x.grad, atol=1e-12) and torch.allclose(gw, w.grad, atol=1e-12)
