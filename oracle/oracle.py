@@ -5,6 +5,13 @@ Tensors are torch CPU tensors (any dtype, any view); they are widened to f64 ove
 storage so that strides keep their meaning, and results come back as f64 torch tensors.
 The API mirrors `dfdx_b200.Cuda` (matmul / conv2d returning `(out, backward)`), which in turn
 mirrors dfdx's `TryMatMul` / `TryConv2D`.
+
+Restatements written directly in this file (f64, torch CPU ops + the C matmul): `fused_matmul`, `attention`,
+`attention_backward`, `layer_norm`, `conv1d`, `convtrans2d`; each docstring names the reference lines it follows.
+Parity is pinned: matmul, linear, conv2d, conv1d, convtrans2d and normalize reproduce every literal known answer
+the reference's tests hold for them (tests/golden/*.json, tests/test_golden.py); the attention restatement is the
+composition of pinned pieces (matmul, and softmax = exp(x - logsumexp)) and is checked against torch f64 autograd
+(tests/test_oracle.py), because the reference's MultiHeadAttention tests draw their inputs from Rust's seeded RNG.
 """
 from __future__ import annotations
 
