@@ -191,13 +191,24 @@ __global__ void __launch_bounds__(256) layer_norm_bwd_kernel(const T* __restrict
       for (int q = 0; q < N; ++q) red[warp][lane * N + q] = pass == 0 ? dg[v][q] : db[v][q];
       __syncthreads();
       if (out) {
-        for (int i = threadIdx.x; i < 32 * N; i += 256) {
+        // four columns per thread and one vector atomic (red.global.add.v4.f32) where the output allows it
+        for (int i = threadIdx.x * 4; i < 32 * N; i += 256 * 4) {
           const int col = v * 32 * N + i;
           if (col < cols) {
-            float t = 0.f;
+            float t[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-            for (int w = 0; w < 8; ++w) t += red[w][i];
-            atomicAdd(out + col, t);
+            for (int w = 0; w < 8; ++w) {
+#pragma unroll
+              for (int e = 0; e < 4; ++e) t[e] += red[w][i + e];
+            }
+            if (col + 3 < cols && ((uintptr_t)(out + col) & 15) == 0) {
+              asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(out + col), "f"(t[0]), "f"(t[1]), "f"(t[2]),
+                           "f"(t[3]) : "memory");
+            } else {
+#pragma unroll
+              for (int e = 0; e < 4; ++e)
+                if (col + e < cols) atomicAdd(out + col + e, t[e]);
+            }
           }
         }
       }
@@ -227,13 +238,23 @@ __global__ void __launch_bounds__(256) column_sum_kernel(const T* __restrict__ g
 #pragma unroll
   for (int q = 0; q < N; ++q) red[warp][lane * N + q] = acc[q];
   __syncthreads();
-  for (int i = threadIdx.x; i < 32 * N; i += 256) {
+  for (int i = threadIdx.x * 4; i < 32 * N; i += 256 * 4) {
     const int col = blockIdx.x * 32 * N + i;
     if (col < cols) {
-      float t = 0.f;
+      float t[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int w = 0; w < 8; ++w) t += red[w][i];
-      atomicAdd(out + col, t);
+      for (int w = 0; w < 8; ++w) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) t[e] += red[w][i + e];
+      }
+      if (col + 3 < cols && ((uintptr_t)(out + col) & 15) == 0) {
+        asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(out + col), "f"(t[0]), "f"(t[1]), "f"(t[2]),
+                     "f"(t[3]) : "memory");
+      } else {
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+          if (col + e < cols) atomicAdd(out + col + e, t[e]);
+      }
     }
   }
 }

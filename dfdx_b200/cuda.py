@@ -224,13 +224,19 @@ class Cuda:
         accumulates into the three given flat buffers."""
         b, h, s1, d = q.shape
         s2 = k.shape[3]
-        if accumulate_into is None:
-            gq, gk, gv = self.alloc_grad(q), self.alloc_grad(k), self.alloc_grad(v)
-        else:
+        # Fresh buffers are simply written (no zero fill, no read-modify-write) when every element of q, k and v
+        # owns its storage element and the views cover their storages; a broadcast view (several elements aliasing
+        # one storage element) or a partial view keeps dfdx's zero-then-accumulate.
+        dense = all(st != 0 for t in (q, k, v) for st in t.stride()) and \
+            all(t.numel() * t.element_size() == t.untyped_storage().nbytes() for t in (q, k, v))
+        acc = 0 if (accumulate_into is None and dense) else 1
+        if accumulate_into is not None:
             gq, gk, gv = accumulate_into
-        # Fresh zeroed buffers need no read-modify-write, unless several elements of a view alias one storage
-        # element (a broadcast), where writes would overwrite each other's sums.
-        acc = 0 if (accumulate_into is None and all(st != 0 for t in (q, k, v) for st in t.stride())) else 1
+        elif acc == 0:
+            gq, gk, gv = (torch.empty(t.untyped_storage().nbytes() // t.element_size(), dtype=t.dtype, device=t.device)
+                          for t in (q, k, v))
+        else:
+            gq, gk, gv = self.alloc_grad(q), self.alloc_grad(k), self.alloc_grad(v)
         go = grad_out if grad_out.stride(3) == 1 else grad_out.contiguous()
         need = self.lib.b200_attention_backward_workspace_bytes(b, h, s1)
         ws = self.get_workspace(need)
