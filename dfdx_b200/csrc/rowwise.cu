@@ -111,6 +111,66 @@ __global__ void __launch_bounds__(256) layer_norm_fwd_kernel(const T* __restrict
   }
 }
 
+// The same forward with the row kept in registers (cols <= 32 * N * MAXV): one global read per element, all of a
+// lane's loads issued before the first use.
+template <typename T, int MAXV>
+__global__ void __launch_bounds__(256) layer_norm_fwd_reg_kernel(const T* __restrict__ x, long long x_ld,
+                                                                 const T* __restrict__ gamma, const T* __restrict__ beta,
+                                                                 float eps, T* __restrict__ y, long long y_ld,
+                                                                 float* __restrict__ stats, long long rows, int cols, int vec) {
+  constexpr int N = Vec<T>::N;
+  const int lane = threadIdx.x & 31;
+  const long long warp0 = (long long)blockIdx.x * 8 + (threadIdx.x >> 5), nwarps = (long long)gridDim.x * 8;
+  const float inv_n = 1.f / (float)cols;
+  for (long long r = warp0; r < rows; r += nwarps) {
+    const T* xr = x + r * x_ld;
+    float f[MAXV][N];
+#pragma unroll
+    for (int v = 0; v < MAXV; ++v) {
+      const int c = (v * 32 + lane) * N;
+      if (c < cols) load_vec(xr, c, cols, vec, f[v]);
+      else {
+#pragma unroll
+        for (int q = 0; q < N; ++q) f[v][q] = 0.f;
+      }
+    }
+    float s = 0.f;
+#pragma unroll
+    for (int v = 0; v < MAXV; ++v)
+#pragma unroll
+      for (int q = 0; q < N; ++q) s += f[v][q];                // columns beyond `cols` hold zeros
+    const float mean = warp_sum(s) * inv_n;
+    float sq = 0.f;
+#pragma unroll
+    for (int v = 0; v < MAXV; ++v)
+#pragma unroll
+      for (int q = 0; q < N; ++q) {
+        const float d = ((v * 32 + lane) * N + q < cols) ? f[v][q] - mean : 0.f;
+        sq = fmaf(d, d, sq);
+      }
+    const float rstd = 1.f / sqrtf(warp_sum(sq) * inv_n + eps);
+    T* yr = y + r * y_ld;
+#pragma unroll
+    for (int v = 0; v < MAXV; ++v) {
+      const int c = (v * 32 + lane) * N;
+      if (c < cols) {
+        float gm[N], bt[N];
+        if (gamma) load_vec(gamma, c, cols, vec, gm);
+        if (beta) load_vec(beta, c, cols, vec, bt);
+#pragma unroll
+        for (int q = 0; q < N; ++q) {
+          float o = (f[v][q] - mean) * rstd;
+          if (gamma) o *= gm[q];
+          if (beta) o += bt[q];
+          f[v][q] = o;
+        }
+        store_vec(yr, c, cols, vec, f[v]);
+      }
+    }
+    if (stats && lane == 0) { stats[2 * r] = mean; stats[2 * r + 1] = rstd; }
+  }
+}
+
 // MAXV vectors per lane: cols <= 32 * N * MAXV.  Per-lane partial sums of dgamma / dbeta live in registers over all
 // rows of the warp, are combined across the block's warps in shared memory and added to global memory once per block.
 template <typename T, int MAXV>
@@ -135,6 +195,7 @@ __global__ void __launch_bounds__(256) layer_norm_bwd_kernel(const T* __restrict
     const T* gr = g + r * g_ld;
     const float mean = stats[2 * r], rstd = stats[2 * r + 1];
     float s1 = 0.f, s2 = 0.f;
+    float xh[MAXV][N], gg[MAXV][N];                            // x-hat and g * gamma of this lane's columns
 #pragma unroll
     for (int v = 0; v < MAXV; ++v) {
       const int c = (v * 32 + lane) * N;
@@ -145,13 +206,16 @@ __global__ void __launch_bounds__(256) layer_norm_bwd_kernel(const T* __restrict
         if (gamma) load_vec(gamma, c, cols, vec, gm);
 #pragma unroll
         for (int q = 0; q < N; ++q) {
-          const float xh = (c + q < cols) ? (fx[q] - mean) * rstd : 0.f;
-          const float gg = gamma ? fg[q] * gm[q] : fg[q];
-          s1 += gg;
-          s2 = fmaf(gg, xh, s2);
-          dg[v][q] = fmaf(fg[q], xh, dg[v][q]);
+          xh[v][q] = (c + q < cols) ? (fx[q] - mean) * rstd : 0.f;
+          gg[v][q] = gamma ? fg[q] * gm[q] : fg[q];
+          s1 += gg[v][q];
+          s2 = fmaf(gg[v][q], xh[v][q], s2);
+          dg[v][q] = fmaf(fg[q], xh[v][q], dg[v][q]);
           db[v][q] += fg[q];
         }
+      } else {
+#pragma unroll
+        for (int q = 0; q < N; ++q) xh[v][q] = gg[v][q] = 0.f;
       }
     }
     const float c1 = warp_sum(s1) * inv_n, c2 = warp_sum(s2) * inv_n;
@@ -161,20 +225,14 @@ __global__ void __launch_bounds__(256) layer_norm_bwd_kernel(const T* __restrict
       for (int v = 0; v < MAXV; ++v) {
         const int c = (v * 32 + lane) * N;
         if (c < cols) {
-          float fx[N], fg[N], gm[N], old[N];
-          load_vec(xr, c, cols, vec, fx);
-          load_vec(gr, c, cols, vec, fg);
-          if (gamma) load_vec(gamma, c, cols, vec, gm);
+          float d[N], old[N];
           if (accumulate_x) load_vec(or_, c, cols, vec, old);
 #pragma unroll
           for (int q = 0; q < N; ++q) {
-            const float xh = (fx[q] - mean) * rstd;
-            const float gg = gamma ? fg[q] * gm[q] : fg[q];
-            float d = rstd * (gg - c1 - xh * c2);
-            if (accumulate_x) d += old[q];
-            fx[q] = d;
+            d[q] = rstd * (gg[v][q] - c1 - xh[v][q] * c2);
+            if (accumulate_x) d[q] += old[q];
           }
-          store_vec(or_, c, cols, vec, fx);
+          store_vec(or_, c, cols, vec, d);
         }
       }
     }
@@ -277,8 +335,15 @@ int ln_forward_t(int64_t rows, int64_t cols, const void* x, int64_t x_ld, const 
   long long blocks = (rows + 7) / 8;
   const long long cap = (long long)ds->sm_count * 16;
   if (blocks > cap) blocks = cap;
-  layer_norm_fwd_kernel<T><<<(unsigned)blocks, 256, 0, stream>>>((const T*)x, x_ld, (const T*)gamma, (const T*)beta, (float)eps,
-                                                                 (T*)y, y_ld, stats, rows, (int)cols, vec);
+  const int64_t vecs = (cols + 32 * Vec<T>::N - 1) / (32 * Vec<T>::N);
+  auto launch = [&](auto kernel) {
+    kernel<<<(unsigned)blocks, 256, 0, stream>>>((const T*)x, x_ld, (const T*)gamma, (const T*)beta, (float)eps, (T*)y, y_ld,
+                                                 stats, rows, (int)cols, vec);
+  };
+  if (vecs <= 2) launch(layer_norm_fwd_reg_kernel<T, 2>);
+  else if (vecs <= 4) launch(layer_norm_fwd_reg_kernel<T, 4>);
+  else if (vecs <= 8) launch(layer_norm_fwd_reg_kernel<T, 8>);
+  else launch(layer_norm_fwd_kernel<T>);                     // long rows: three passes, re-reads hit L1 / L2
   count_launch(false);
   return note_cuda_error(cudaGetLastError(), "layer_norm forward launch");
 }
