@@ -280,30 +280,45 @@ int b200_matmat_br_forward(int dtype, size_t batch, size_t m, size_t k, size_t n
   return b200_gemm_batch(dtype, batch, m, k, n, lhs, ls, rhs, rs3, 0.0, out, os, stream);
 }
 
-int b200_matmat_br_backward(int dtype, size_t batch, size_t m, size_t k, size_t n, const void* lhs,
-                            const size_t ls[3], void* grad_lhs, const void* rhs, const size_t rs[2],
-                            void* grad_rhs, const void* grad_out, void* stream, void* par_stream) {
-  (void)par_stream;
+static int matmat_br_backward_beta(int dtype, size_t batch, size_t m, size_t k, size_t n, const void* lhs,
+                                   const size_t ls[3], void* grad_lhs, const void* rhs, const size_t rs[2],
+                                   void* grad_rhs, const void* grad_out, void* stream, int beta) {
   if (!valid_dtype(dtype)) return B200_ERR_DTYPE;
   if (!ls || !rs) return B200_ERR_NULL;
   if (!matrix_strides_ok(ls + 1) || !matrix_strides_ok(rs)) return B200_ERR_STRIDE;
   int rc = B200_OK;
   if (grad_rhs && batch && k && n) {
-    // grad_rhs += sum_b lhs_b^T * grad_out_b : one launch, the batch is an outer reduction index.
+    // grad_rhs (+)= sum_b lhs_b^T * grad_out_b : one launch, the batch is an outer reduction index.
     if (!lhs || !grad_out) return B200_ERR_NULL;
     GemmProblem p;
-    p.dtype = dtype; p.beta = 1; p.red = batch; p.m = k; p.k = m; p.n = n;
+    p.dtype = dtype; p.beta = beta; p.red = batch; p.m = k; p.k = m; p.n = n;
     p.a = lhs; p.a_red = ls[0]; p.a_r = ls[2]; p.a_c = ls[1];
     p.b = grad_out; p.b_red = m * n; p.b_r = n; p.b_c = 1;
     p.c = grad_rhs; p.c_r = rs[0]; p.c_c = rs[1];
     if ((rc = run_gemm(p, (cudaStream_t)stream))) return rc;
   }
-  if (grad_lhs) {  // grad_lhs += grad_out * rhs^T, rhs broadcast over the batch
+  if (grad_lhs) {  // grad_lhs (+)= grad_out * rhs^T, rhs broadcast over the batch
     const size_t os[3] = {m * n, n, 1};
     const size_t rs_t[3] = {0, rs[1], rs[0]};
-    rc = b200_gemm_batch(dtype, batch, m, n, k, grad_out, os, rhs, rs_t, 1.0, grad_lhs, ls, stream);
+    rc = b200_gemm_batch(dtype, batch, m, n, k, grad_out, os, rhs, rs_t, beta ? 1.0 : 0.0, grad_lhs, ls, stream);
   }
   return rc;
+}
+
+int b200_matmat_br_backward(int dtype, size_t batch, size_t m, size_t k, size_t n, const void* lhs,
+                            const size_t ls[3], void* grad_lhs, const void* rhs, const size_t rs[2],
+                            void* grad_rhs, const void* grad_out, void* stream, void* par_stream) {
+  (void)par_stream;
+  return matmat_br_backward_beta(dtype, batch, m, k, n, lhs, ls, grad_lhs, rhs, rs, grad_rhs, grad_out, stream, 1);
+}
+
+int b200_matmat_br_backward_overwrite(int dtype, size_t batch, size_t m, size_t k, size_t n, const void* lhs,
+                                      const size_t ls[3], void* grad_lhs, const void* rhs, const size_t rs[2],
+                                      void* grad_rhs, const void* grad_out, void* stream) {
+  // writing instead of accumulating is only the same thing when no two elements of a view share storage
+  if (ls && grad_lhs && ((batch > 1 && ls[0] == 0) || (m > 1 && ls[1] == 0) || (k > 1 && ls[2] == 0))) return B200_ERR_STRIDE;
+  if (rs && grad_rhs && ((k > 1 && rs[0] == 0) || (n > 1 && rs[1] == 0))) return B200_ERR_STRIDE;
+  return matmat_br_backward_beta(dtype, batch, m, k, n, lhs, ls, grad_lhs, rhs, rs, grad_rhs, grad_out, stream, 0);
 }
 
 // ---- MatMatBatch3Kernel (cuda_kernel.rs:395-462) -------------------------------------------------

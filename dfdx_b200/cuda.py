@@ -134,6 +134,14 @@ class Cuda:
                                                grad_out.data_ptr(), self._stream(), None),
               "b200_matmat_br_backward")
 
+    def matmat_br_backward_overwrite(self, lhs, grad_lhs, rhs, grad_rhs, grad_out) -> None:
+        """The first accumulation into fresh gradient buffers: they are written, need no zero fill and are not read."""
+        (b, m, k), n = lhs.shape, rhs.shape[1]
+        check(self.lib.b200_matmat_br_backward_overwrite(self._dtype(lhs), b, m, k, n, lhs.data_ptr(),
+                                                         _st(lhs.stride()), _ptr(grad_lhs), rhs.data_ptr(),
+                                                         _st(rhs.stride()), _ptr(grad_rhs), grad_out.data_ptr(),
+                                                         self._stream()), "b200_matmat_br_backward_overwrite")
+
     def matmat_batch3_forward(self, lhs, rhs):
         (b, m, k), n = lhs.shape, rhs.shape[2]
         out = self._empty((b, m, n), lhs)

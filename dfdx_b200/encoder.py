@@ -80,8 +80,10 @@ class _FusedLinear(torch.autograd.Function):
         g = grad_out.contiguous()
         if ctx.relu:
             g = torch.ops.aten.threshold_backward(g, y, 0.0)
-        gx, gw = dev.alloc_grad(x), dev.alloc_grad(w_view)
-        dev.matmat_br_backward(x, gx, w_view, gw, g)
+        # fresh gradient buffers: written by the first (and here only) backward op, no zero fill needed
+        gx = torch.empty(x.untyped_storage().nbytes() // x.element_size(), dtype=x.dtype, device=x.device)
+        gw = torch.empty(weight.numel(), dtype=weight.dtype, device=weight.device)
+        dev.matmat_br_backward_overwrite(x, gx, w_view, gw, g)
         grad_bias = torch.zeros(g.shape[-1], dtype=torch.float32, device=g.device)
         dev.bias_grad(g, grad_bias)                                # f32 column sums, one pass over g
         grad_bias = grad_bias.to(g.dtype)

@@ -217,6 +217,16 @@ int b200_matmat_batch4_backward(int dtype, size_t batch, size_t seq, size_t m, s
 
 /* ---- GEMMs with a fused epilogue (API additions: no single counterpart in the reference) -------- */
 
+/* `b200_matmat_br_backward` for the FIRST accumulation into freshly allocated gradient buffers: grad_lhs and grad_rhs
+ * are written, not added to, so they need not be zero-filled and are not read (dfdx zero-fills every gradient buffer
+ * in `Gradients::try_alloc_for` and the first backward op then adds into the zeros: two extra passes over each
+ * buffer).  A view in which several elements share storage (a stride of 0 over an extent > 1) is rejected with
+ * B200_ERR_STRIDE: there the sum over the aliased elements is the accumulation. */
+int b200_matmat_br_backward_overwrite(int dtype, size_t batch, size_t m, size_t k, size_t n,
+                                      const void* lhs, const size_t lhs_strides[3], void* grad_lhs,
+                                      const void* rhs, const size_t rhs_strides[2], void* grad_rhs,
+                                      const void* grad_out, void* stream);
+
 /* A doubly batched strided GEMM (strides = [batch0, batch1, row, col] in elements; an lhs / rhs batch
  * stride may be 0) whose epilogue applies `ep` before the store: one kernel and one pass over `out`
  * where dfdx runs a GEMM and then one elementwise kernel per op, each re-reading and re-writing the GEMM's

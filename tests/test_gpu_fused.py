@@ -143,3 +143,25 @@ def test_attention_scores_scaled(cuda_dev, oracle):
     got = cuda_dev.matmat_batch4_forward_scaled(q, k, 1.0 / math.sqrt(d))
     want = oracle.fused_matmul(q.cpu(), k.cpu(), 1.0 / math.sqrt(d))
     assert oracle.rel_frobenius(got, want) <= FROB_TOL[torch.float16]
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.float32, torch.float64])
+def test_matmat_br_backward_overwrite(cuda_dev, oracle, dtype):
+    """The first-accumulation variant writes what the accumulating one adds into zeros; the buffers are never read
+    (NaN-poisoned here); views with aliased elements are rejected."""
+    g = gen(41)
+    b, m, k, n = 3, 136, 72, 200
+    x = rand((b, m, k), dtype, g, cuda_dev.device)
+    w = rand((n, k), dtype, g, cuda_dev.device).permute(1, 0)              # (k, n) view of a stored (n, k) weight
+    go = rand((b, m, n), dtype, g, cuda_dev.device)
+    gx = torch.full((b * m * k,), float("nan"), dtype=dtype, device=cuda_dev.device)
+    gw = torch.full((n * k,), float("nan"), dtype=dtype, device=cuda_dev.device)
+    cuda_dev.matmat_br_backward_overwrite(x, gx, w, gw, go)
+    _, bwd = oracle.matmul(x.cpu(), w.cpu())
+    want_x, want_w = bwd(go.cpu())
+    assert oracle.rel_frobenius(cuda_dev.grad_view(gx, x), want_x) <= FROB_TOL[dtype]
+    assert oracle.rel_frobenius(cuda_dev.grad_view(gw, w), want_w) <= FROB_TOL[dtype]
+    xb = x[:1].expand(b, m, k)                                              # broadcast lhs: its gradient is a sum
+    with pytest.raises(dfdx_b200.B200Error) as e:
+        cuda_dev.matmat_br_backward_overwrite(xb, gx, w, gw, go)
+    assert e.value.status == _lib.ERR_STRIDE
