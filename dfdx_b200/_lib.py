@@ -56,6 +56,7 @@ SIGNATURES = {
     "b200_set_mn_single_box": (_i, [_i]),
     "b200_set_cta_pair_mode": (_i, [_i]),
     "b200_set_store_mode": (_i, [_i]),
+    "b200_set_conv_lowering": (_i, [_i, _sz]),
     "b200_set_split_k": (_i, [_i]),
     "b200_launch_count": (C.c_uint64, []),
     "b200_tensor_launch_count": (C.c_uint64, []),

@@ -31,6 +31,7 @@ void tc_set_tile_n(int bn);
 void tc_set_mn_box5(int on);
 void tc_set_pair_mode(int mode);
 void tc_set_store_mode(int mode);
+void conv_set_lowering(int grad_img_mode, size_t group_bytes);
 void tc_set_split_mode(int mode);
 
 namespace {
@@ -197,6 +198,11 @@ int b200_set_cta_pair_mode(int mode) {
 
 /* Testing hook: epilogue store orientation of the tensor-core kernels: 0 (default) planner's choice,
  * 1 row stores only, 2 column stores wherever the output allows. */
+int b200_set_conv_lowering(int grad_img_mode, size_t group_bytes) {
+  if (grad_img_mode < 0 || grad_img_mode > 1) return B200_ERR_UNSUPPORTED;
+  conv_set_lowering(grad_img_mode, group_bytes);
+  return B200_OK;
+}
 int b200_set_store_mode(int mode) {
   if (mode < 0 || mode > 2) return B200_ERR_UNSUPPORTED;
   tc_set_store_mode(mode);

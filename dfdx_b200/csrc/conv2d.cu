@@ -205,6 +205,116 @@ __global__ void __launch_bounds__(NT) unfold_output_plane_kernel(const Op32 op, 
   }
 }
 
+Op32 to_op32(const Op& o);
+
+// Division of a non-negative 31-bit integer by a launch constant as a multiply and a shift:
+// n / d = umulhi(n, ceil(2^p / d)) >> (p - 32) with p = 31 + ceil(log2 d), exact for 0 <= n < 2^31.
+struct FastDiv {
+  uint32_t mul, shr, d;
+  __device__ __forceinline__ int div(int n) const { return d == 1 ? n : (int)(__umulhi((uint32_t)n, mul) >> shr); }
+};
+FastDiv fast_div(int64_t d) {
+  FastDiv f{0u, 0u, (uint32_t)d};
+  if (d > 1) {
+    uint32_t l = 0;
+    while (((int64_t)1 << l) < d) ++l;
+    f.mul = (uint32_t)((((uint64_t)1 << (31 + l)) + (uint64_t)d - 1) / (uint64_t)d);
+    f.shr = l - 1;
+  }
+  return f;
+}
+
+// col2im: grad_img[b, c, y, x] += sum over the taps (k1, k2) that reach an output pixel of
+// cols[b, c, k1, k2, oh, ow], the per-tap data gradients produced by filters^T x grad_out.
+//
+// The kernel is issue-bound long before it is bandwidth-bound (a tap costs a few dozen instructions of index
+// work against one 4-byte load), so the index work is shared: a thread owns FOLD_P runs of V consecutive
+// pixels of a row (V = 4 when the row length allows, else 1), works out the row and the validity of a filter
+// row once per run, and with unit stride (UNIT) reaches the V pixels of a tap from one base address; launch
+// constants divide by multiply-and-shift.  Loads of two taps for all runs are issued before the adds.  A block
+// covers FOLD_P * NT consecutive runs of one (b, c) plane.  The sum runs in tap order in A (f32 for half); the
+// image element is read and written once.
+constexpr int FOLD_P = 2;
+template <typename T, typename A, int V, bool UNIT>
+__global__ void __launch_bounds__(NT) fold_cols_kernel(const Op32 op, const FastDiv by_vrow, const FastDiv by_stride,
+                                                       const unsigned blocks_per_plane, const T* __restrict__ cols,
+                                                       T* __restrict__ grad_img) {
+  constexpr int P = FOLD_P;
+  const unsigned plane = blockIdx.x / blocks_per_plane, chunk = blockIdx.x - plane * blocks_per_plane;
+  const int vrow = op.w_in / V, nvec = op.h_in * vrow, npos = op.h_out * op.w_out;
+  const T* src = cols + (int64_t)plane * op.kh * op.kw * npos;
+  T* dst = grad_img + (int64_t)plane * op.h_in * op.w_in;
+  int vi[P], ys[P], xs[P];
+  A acc[P][V];
+#pragma unroll
+  for (int p = 0; p < P; ++p) {
+    vi[p] = (int)(chunk * (NT * P) + p * NT + threadIdx.x);
+    const int vv = vi[p] < nvec ? vi[p] : 0;
+    const int y = by_vrow.div(vv);
+    ys[p] = y + op.ph; xs[p] = (vv - y * vrow) * V + op.pw;
+#pragma unroll
+    for (int e = 0; e < V; ++e) acc[p][e] = A(0);
+  }
+  for (int k1 = 0; k1 < op.kh; ++k1) {
+    int rowoff[P];                                           // offset of row oh inside a tap plane, -1 if the tap misses
+#pragma unroll
+    for (int p = 0; p < P; ++p) {
+      const int ohs = ys[p] - op.dilation * k1;
+      const int oh = UNIT ? ohs : by_stride.div(ohs < 0 ? 0 : ohs);
+      rowoff[p] = (vi[p] < nvec && ohs >= 0 && oh * op.stride == ohs && oh < op.h_out) ? oh * op.w_out : -1;
+    }
+    const T* tap = src + (int64_t)k1 * op.kw * npos;
+    for (int k2 = 0; k2 < op.kw; k2 += 2) {
+      T v[2][P][V];
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+#pragma unroll
+        for (int p = 0; p < P; ++p) {
+          const bool ok = k2 + j < op.kw && rowoff[p] >= 0;
+          const int ows0 = xs[p] - op.dilation * (k2 + j);
+          const T* q = tap + (int64_t)(k2 + j) * npos + (ok ? rowoff[p] : 0);
+#pragma unroll
+          for (int e = 0; e < V; ++e) {
+            const int ows = ows0 + e;
+            const int ow = UNIT ? ows : by_stride.div(ows < 0 ? 0 : ows);
+            const bool hit = ok && ows >= 0 && ow < op.w_out && (UNIT || ow * op.stride == ows);
+            v[j][p][e] = T(0.0f);
+            if (hit) v[j][p][e] = q[ow];
+          }
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 2; ++j)
+#pragma unroll
+        for (int p = 0; p < P; ++p)
+#pragma unroll
+          for (int e = 0; e < V; ++e) acc[p][e] += (A)v[j][p][e];
+    }
+  }
+#pragma unroll
+  for (int p = 0; p < P; ++p) {
+    if (vi[p] >= nvec) continue;
+    T* d = dst + (int64_t)vi[p] * V;
+#pragma unroll
+    for (int e = 0; e < V; ++e) d[e] = (T)((A)d[e] + acc[p][e]);
+  }
+}
+
+template <typename T, typename A>
+void launch_fold(const Op& op, int64_t planes, const T* cols, T* grad_img, cudaStream_t stream) {
+  const int v = op.w_in % 4 == 0 ? 4 : 1;
+  const int64_t nvec = op.h_in * (op.w_in / v);
+  const unsigned bpp = (unsigned)((nvec + NT * FOLD_P - 1) / (NT * FOLD_P));
+  const unsigned grid = (unsigned)(planes * bpp);
+  const Op32 o = to_op32(op);
+  const FastDiv by_vrow = fast_div(op.w_in / v), by_stride = fast_div(op.stride);
+  const bool unit = op.stride == 1;
+  if (v == 4 && unit) fold_cols_kernel<T, A, 4, true><<<grid, NT, 0, stream>>>(o, by_vrow, by_stride, bpp, cols, grad_img);
+  else if (v == 4) fold_cols_kernel<T, A, 4, false><<<grid, NT, 0, stream>>>(o, by_vrow, by_stride, bpp, cols, grad_img);
+  else if (unit) fold_cols_kernel<T, A, 1, true><<<grid, NT, 0, stream>>>(o, by_vrow, by_stride, bpp, cols, grad_img);
+  else fold_cols_kernel<T, A, 1, false><<<grid, NT, 0, stream>>>(o, by_vrow, by_stride, bpp, cols, grad_img);
+}
+
 Op32 to_op32(const Op& o) {
   return Op32{(int)o.kh, (int)o.kw, (int)o.stride, (int)o.ph, (int)o.pw, (int)o.dilation, (int)o.chan_in, (int)o.chan_out,
               (int)o.h_in, (int)o.h_out, (int)o.w_in, (int)o.w_out};
@@ -235,6 +345,11 @@ unsigned grid_for(int64_t total, int sms) {
 }
 
 size_t align256(size_t x) { return (x + 255) & ~(size_t)255; }
+
+// Tuning knobs (b200_set_conv_lowering): 0 = choose, 1 = data gradient by gather + GEMM only; bytes of cols per group of images.
+constexpr size_t CONV_GROUP_BYTES_DEFAULT = ~(size_t)0;
+int g_conv_grad_img_mode = 0;
+size_t g_conv_group_bytes = CONV_GROUP_BYTES_DEFAULT;
 
 template <typename T, typename A>
 int forward_t(int dtype, const Op& op, const T* img, const size_t is[4], const T* filters, T* out,
@@ -313,6 +428,40 @@ int backward_t(int dtype, const Op& op, const T* img, T* grad_img, const T* filt
     if (!grad_img) return B200_OK;
   }
 
+  // grad_img with contiguous filters: the transposed filters times grad_out give the per-tap data gradients
+  //   cols (B, G, C/G*K*K, OH*OW) = filters^T (G, C/G*K*K, O/G) x grad_out (B, G, O/G, OH*OW)
+  // and a gather (col2im) folds them into the image.  Against the gather-then-GEMM lowering below this
+  // moves B*C*K*K*OH*OW elements through the workspace instead of B*O*K*K*H*W, and the GEMM has C/G*K*K rows
+  // (full MMA tiles) instead of C/G.  Images go through in groups whose cols stay resident in L2 between the
+  // GEMM that writes them and the fold that reads them.
+  bool grad_img_done = !grad_img;
+  const int64_t blocks_per_plane = (hw + NT * FOLD_P - 1) / (NT * FOLD_P);   // upper bound of the fold's grid
+  if (grad_img && filters_contig && n_fwd_patches > 0 && g_conv_grad_img_mode != 1 && fits_int(op) &&
+      op.batch * op.chan_in * blocks_per_plane < ((int64_t)1 << 31) &&
+      op.dilation * (op.kw + 4) + op.w_in + op.pw < ((int64_t)1 << 31) && op.dilation * op.kh + op.h_in + op.ph < ((int64_t)1 << 31)) {
+    const int64_t npos = op.h_out * op.w_out, per_image = op.chan_in * KK * npos;
+    int64_t group = op.batch;
+    if (g_conv_group_bytes > 0) {
+      group = (int64_t)(g_conv_group_bytes / ((size_t)per_image * sizeof(T)));
+      group = group < 1 ? 1 : (group > op.batch ? op.batch : group);
+    }
+    for (int64_t b0 = 0; b0 < op.batch; b0 += group) {
+      const int64_t nb = op.batch - b0 < group ? op.batch - b0 : group;
+      GemmProblem p;
+      p.dtype = dtype; p.beta = 0; p.b0 = nb; p.b1 = G; p.m = cg * KK; p.k = og; p.n = npos;
+      p.a = filters; p.a_b0 = 0; p.a_b1 = og * cg * KK; p.a_r = 1; p.a_c = cg * KK;
+      p.b = grad_out + b0 * op.chan_out * npos; p.b_b0 = op.chan_out * npos; p.b_b1 = og * npos; p.b_r = npos; p.b_c = 1;
+      p.c = patches; p.c_b0 = per_image; p.c_b1 = cg * KK * npos; p.c_r = npos; p.c_c = 1;
+      if ((rc = run_gemm(p, stream))) return rc;
+      T* dst = grad_img + b0 * op.chan_in * hw;
+      launch_fold<T, A>(op, nb * op.chan_in, patches, dst, stream);
+      count_launch(false);
+      if ((rc = note_cuda_error(cudaGetLastError(), "fold_cols launch"))) return rc;
+    }
+    grad_img_done = true;
+  }
+  if (grad_img_done && (grad_filters_done || !grad_filters)) return B200_OK;
+
   if (plane_path_output<T>(op))
     unfold_output_plane_kernel<T><<<(unsigned)(op.batch * op.chan_out), NT,
                                     (size_t)(op.h_out * op.w_out) * sizeof(T), stream>>>(to_op32(op), grad_out, patches);
@@ -321,7 +470,7 @@ int backward_t(int dtype, const Op& op, const T* img, T* grad_img, const T* filt
   count_launch(false);
   if ((rc = note_cuda_error(cudaGetLastError(), "unfold_output launch"))) return rc;
 
-  if (grad_img) {
+  if (!grad_img_done) {
     transpose_filters_kernel<T><<<grid_for(n_filters, sms), NT, 0, stream>>>(op, filters, st, ftr, n_filters);
     count_launch(false);
     if ((rc = note_cuda_error(cudaGetLastError(), "transpose_filters launch"))) return rc;
@@ -438,6 +587,11 @@ int convtrans2d_backward(int dtype, const b200_convtrans2d_op* o, const void* im
   }
   if (grad_filters) rc = backward_any(dtype, op, grad_out, nullptr, filters, fs, grad_filters, img, ws, stream);
   return rc;
+}
+
+void conv_set_lowering(int grad_img_mode, size_t group_bytes) {
+  g_conv_grad_img_mode = grad_img_mode;
+  g_conv_group_bytes = group_bytes ? group_bytes : CONV_GROUP_BYTES_DEFAULT;
 }
 
 size_t conv2d_workspace_bytes(int dtype, const b200_conv2d_op* o, int backward) {

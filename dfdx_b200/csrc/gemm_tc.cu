@@ -339,7 +339,7 @@ __device__ __forceinline__ void split_role(const TcArgs& g, uint32_t smem_base, 
 template <int BN>
 __global__ void __launch_bounds__(CfgS<BN>::THREADS, 1)
 gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
-                   const __grid_constant__ CUtensorMap /* output map: used by the f16 kernel only */, const TcArgs g) {
+                   const __grid_constant__ CUtensorMap tma_c, const TcArgs g) {
   using C = CfgS<BN>;
   constexpr int STAGES = C::STAGES;
   constexpr int PRODUCER_WARP = 8, MMA_WARP = 9;      // warpgroup 2; warpgroups 3 and 4 split operands
@@ -493,12 +493,49 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_const
         tc_fence_before();
         mbar_arrive(smem_u32(&bar_tempty[buf]));
       }
+      // the staged stores below synchronise a warpgroup with a named barrier, which has no time-out: all of its
+      // threads take this unit's output or none does
+      if (g.c_tma) ok = named_barrier_and(1 + wg, 128, ok);
       if (!ok) break;
       if (un.kb_lo >= un.kb_hi) continue;               // an empty unit of the stream-K decomposition
       // partial sums (a K slice, or a stream-K range that does not span the tile's whole K) are added atomically
       const bool partial = g.ksplit > 1 || (g.streamk && !(un.kb_lo == 0 && un.kb_hi == total_kb));
       const int row = t.mt * BM + quad * 32 + lane;
-      if (row < g.m) {
+      if (g.c_tma && !partial) {
+        // Output through shared memory and TMA, as in the f16 kernel: per-thread row stores hand the memory
+        // system 32 separate 16- or 32-byte pieces per instruction, which bounds GEMMs with a short K and a
+        // wide output; a staged group of 128 rows x 32 columns leaves as one bulk tensor store (beta = 0) or
+        // reduce-add (beta = 1) of whole 128-byte lines.  Rows and columns past the output's extent are clipped
+        // by the tensor map.
+        const uint32_t stage = smem_base + C::OFF_OUT + (uint32_t)wg * C::OUT_BYTES;
+        const int r_in = quad * 32 + lane;
+        const uint32_t sw = (uint32_t)(r_in & 7);
+        const bool leader = (threadIdx.x & 127) == 0;
+#pragma unroll
+        for (int c = 0; c < C::HALF / 32; ++c) {
+          const int col0 = t.nt * BN + col_base + c * 32;
+          if (col0 < g.n) {                              // warpgroup-uniform
+            if (g.fused && row < g.m) {
+              const int valid = (g.n - col0) < 32 ? (g.n - col0) : 32;
+              fused_epilogue<float>(&acc[c * 32], g, row, col0, valid);
+            }
+            if (leader) bulk_wait_group_read<0>();       // the store that last used this buffer has read it
+            named_barrier_sync(1 + wg, 128);
+#pragma unroll
+            for (int q = 0; q < 8; ++q)
+              st_shared_v4_u32(stage + (uint32_t)r_in * 128u + ((((uint32_t)q) ^ sw) << 4),
+                               __float_as_uint(acc[c * 32 + q * 4]), __float_as_uint(acc[c * 32 + q * 4 + 1]),
+                               __float_as_uint(acc[c * 32 + q * 4 + 2]), __float_as_uint(acc[c * 32 + q * 4 + 3]));
+            fence_proxy_async_smem();
+            named_barrier_sync(1 + wg, 128);
+            if (leader) {
+              if (g.c_tma == 2) tma_reduce_add_4d(&tma_c, stage, col0, t.mt * BM, t.ib1, t.ib0);
+              else tma_store_4d(&tma_c, stage, col0, t.mt * BM, t.ib1, t.ib0);
+              bulk_commit_group();
+            }
+          }
+        }
+      } else if (row < g.m) {
         float* cbase = (float*)g.c + t.ib0 * g.c_b0 + t.ib1 * g.c_b1;
 #pragma unroll
         for (int c = 0; c < C::HALF / 32; ++c) {
@@ -518,6 +555,7 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_const
         }
       }
     }
+    if ((threadIdx.x & 127) == 0) bulk_wait_group_read<0>();   // shared memory must outlive the last bulk stores' reads
   }
 
   tc_fence_before();
@@ -788,9 +826,11 @@ int build_launch(Launch& L, const Plan& pl, int esize, int tm, int tn, int bmc, 
   }
   g.c_tma = 0;
   L.mc = L.ma;                                               // a valid descriptor even when it is not used
-  if (esize == 2 && !pl.c_col && g_store_mode != 1 && tm == BM) {
-    // output map (n, m, b1, b0), box 64 x 128, 128B swizzle: the epilogue stages groups of 64 columns
-    if (encode_map(&L.mc, p.c, 2, p.n, p.m, pl.ldc, p.b1, p.c_b1, p.b0, p.c_b0, 64, 128, CU_TENSOR_MAP_SWIZZLE_128B) == B200_OK)
+  if (!pl.c_col && g_store_mode != 1 && tm == BM) {
+    // output map (n, m, b1, b0), box 128 bytes x 128 rows, 128B swizzle: the epilogue stages groups of 64 f16 or
+    // 32 f32 columns
+    if (encode_map(&L.mc, p.c, esize, p.n, p.m, pl.ldc, p.b1, p.c_b1, p.b0, p.c_b0, 128 / esize, 128,
+                   CU_TENSOR_MAP_SWIZZLE_128B) == B200_OK)
       g.c_tma = p.beta ? 2 : 1;
   }
   g.beta = p.beta;

@@ -254,7 +254,9 @@ struct CfgS {
   static constexpr int STAGES = STAGES_FIT > 8 ? 8 : STAGES_FIT;
   static constexpr int THREADS = 640;                       // 5 warpgroups: 2 epilogue, 1 producer + MMA, 2 operand split
   static constexpr int TMEM_COLS = 2 * BN;
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024;
+  static constexpr int OUT_BYTES = 128 * 128;               // one staged output group per epilogue warpgroup: 128 rows x 32 f32
+  static constexpr int OFF_OUT = STAGES * STAGE_BYTES;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 2 * OUT_BYTES + 1024;
   static constexpr int CHUNK_KB = 16;                       // k-blocks per promotion chunk (K = 256)
   static constexpr int HALF = BN / 2;                       // columns owned by one epilogue warpgroup
   static constexpr uint32_t K_LAYOUT = 4u;                  // SWIZZLE_64B

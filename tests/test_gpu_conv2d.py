@@ -130,3 +130,31 @@ def test_config4_conv2d_f32_full_size(cuda_dev, oracle):
     _, gwb = bwd_b(dyd[16:].contiguous())
     dev.synchronize()
     assert oracle.rel_frobenius(gwa + gwb, gw.double()) <= 1e-5
+
+
+@pytest.mark.parametrize("lowering", [pytest.param((0, 0), id="fold"), pytest.param((0, 1), id="fold-per-image"),
+                                      pytest.param((1, 0), id="gather")])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+def test_grad_img_lowerings_agree_with_oracle(cuda_dev, oracle, dtype, lowering):
+    """The data gradient by filters^T x grad_out + fold (all images at once, and one image per pass) and by the
+    reference's gather + GEMM, every geometry of CASES, accumulating into a non-zero grad_img."""
+    mode, group = lowering
+    assert cuda_dev.lib.b200_set_conv_lowering(mode, group) == 0
+    try:
+        for case, cfg in enumerate(CASES):
+            kw = {k: cfg[k] for k in ("stride", "padding", "dilation", "groups")}
+            g = gen(90 + case)
+            x = (torch.randn(*cfg["x"], generator=g, dtype=torch.float64) * 0.5).to(dtype)
+            w = (torch.randn(*cfg["w"], generator=g, dtype=torch.float64) * 0.2).to(dtype)
+            want, obwd = OracleBackend(oracle, dtype).conv2d(x, w, **kw)
+            go = torch.randn(*want.shape, generator=g, dtype=torch.float64).to(dtype)
+            wgx, wgw = obwd(go)
+            xd, wd = x.to(cuda_dev.device), w.to(cuda_dev.device)
+            op = cuda_dev.conv2d_op(xd, wd, **kw)
+            gx, gw = torch.ones_like(xd), torch.zeros_like(wd)
+            cuda_dev.conv2d_backward(op, xd, gx, wd, gw, go.to(cuda_dev.device))
+            assert oracle.rel_frobenius(gx, wgx.to(torch.float64) + 1.0) <= FROB_TOL[dtype], (case, lowering)
+            assert oracle.rel_frobenius(gw, wgw) <= FROB_TOL[dtype], (case, lowering)
+    finally:
+        cuda_dev.lib.b200_set_conv_lowering(0, 0)
+    assert cuda_dev.lib.b200_set_conv_lowering(2, 0) == dfdx_b200._lib.ERR_UNSUPPORTED
