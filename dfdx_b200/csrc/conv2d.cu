@@ -135,35 +135,34 @@ struct Op32 {
 template <typename T>
 __global__ void __launch_bounds__(NT) unfold_input_plane_kernel(const Op32 op, const T* __restrict__ img,
                                                                 const Strides4 st, T* __restrict__ patches) {
+  // The plane is staged with its zero padding, so the copy loop below has no bounds checks: the kernel is
+  // bound by instruction issue, not by the 16-byte stores.
   constexpr int V = VecOf<T>::N;
   using VT = typename VecOf<T>::type;
   extern __shared__ __align__(16) unsigned char plane_raw[];
   T* plane = reinterpret_cast<T*>(plane_raw);
   const int id = blockIdx.x, b = id / op.chan_in, c = id - b * op.chan_in;
   const T* src = img + (int64_t)b * st.s[0] + (int64_t)c * st.s[1];
-  const int hw = op.h_in * op.w_in;
-  for (int i = threadIdx.x; i < hw; i += NT) {
-    const int y = i / op.w_in, x = i - y * op.w_in;
-    plane[i] = src[(int64_t)y * st.s[2] + (int64_t)x * st.s[3]];
+  const int pw_in = op.w_in + 2 * op.pw, ph_in = op.h_in + 2 * op.ph;
+  for (int i = threadIdx.x; i < ph_in * pw_in; i += NT) {
+    const int yy = i / pw_in, y = yy - op.ph, x = i - yy * pw_in - op.pw;
+    plane[i] = (y >= 0 && y < op.h_in && x >= 0 && x < op.w_in) ? src[(int64_t)y * st.s[2] + (int64_t)x * st.s[3]]
+                                                                : T(0.0f);
   }
   __syncthreads();
   const int npos = op.h_out * op.w_out, vrow = op.w_out / V, nvec = op.h_out * vrow;
   T* dst = patches + (int64_t)id * op.kh * op.kw * npos;
   for (int v = threadIdx.x; v < nvec; v += NT) {
     const int oh = v / vrow, ow0 = (v - oh * vrow) * V;
+    const T* corner = plane + oh * op.stride * pw_in + ow0 * op.stride;
+    T* out = dst + oh * op.w_out + ow0;
     for (int k1 = 0; k1 < op.kh; ++k1) {
-      const int y = oh * op.stride + op.dilation * k1 - op.ph;
-      const bool yok = y >= 0 && y < op.h_in;
-      for (int k2 = 0; k2 < op.kw; ++k2) {
-        const int x0 = ow0 * op.stride + op.dilation * k2 - op.pw;
+      const T* row = corner + op.dilation * k1 * pw_in;
+      for (int k2 = 0; k2 < op.kw; ++k2, row += op.dilation, out += npos) {
         __align__(16) T vals[V];
 #pragma unroll
-        for (int e = 0; e < V; ++e) {
-          const int x = x0 + e * op.stride;
-          vals[e] = (yok && x >= 0 && x < op.w_in) ? plane[y * op.w_in + x] : T(0.0f);
-        }
-        *reinterpret_cast<VT*>(dst + (int64_t)(k1 * op.kw + k2) * npos + oh * op.w_out + ow0) =
-            *reinterpret_cast<const VT*>(vals);
+        for (int e = 0; e < V; ++e) vals[e] = row[e * op.stride];
+        *reinterpret_cast<VT*>(out) = *reinterpret_cast<const VT*>(vals);
       }
     }
   }
@@ -326,10 +325,14 @@ bool fits_int(const Op& o) {
          o.h_out * o.w_out < lim && o.kh < 4096 && o.kw < 4096 && o.stride < lim && o.ph < lim && o.pw < lim && o.dilation < lim;
 }
 
+size_t padded_plane_bytes(const Op& o, size_t es) { return (size_t)((o.h_in + 2 * o.ph) * (o.w_in + 2 * o.pw)) * es; }
 template <typename T>
 bool plane_path_input(const Op& o) {
-  return fits_int(o) && o.w_out % VecOf<T>::N == 0 && (size_t)(o.h_in * o.w_in) * sizeof(T) <= 48 * 1024 &&
-         o.h_out * o.w_out > 0;
+  // every tap of every output pixel must fall inside the padded plane (true for consistent geometries)
+  return fits_int(o) && o.w_out % VecOf<T>::N == 0 && o.h_out * o.w_out > 0 &&
+         (o.h_in + 2 * o.ph) * (o.w_in + 2 * o.pw) < ((int64_t)1 << 24) && padded_plane_bytes(o, sizeof(T)) <= 48 * 1024 &&
+         (o.h_out - 1) * o.stride + o.dilation * (o.kh - 1) < o.h_in + 2 * o.ph &&
+         (o.w_out - 1) * o.stride + o.dilation * (o.kw - 1) < o.w_in + 2 * o.pw;
 }
 template <typename T>
 bool plane_path_output(const Op& o) {
@@ -361,7 +364,7 @@ int forward_t(int dtype, const Op& op, const T* img, const size_t is[4], const T
   if (total == 0) return B200_OK;
   Strides4 st{{(int64_t)is[0], (int64_t)is[1], (int64_t)is[2], (int64_t)is[3]}};
   if (plane_path_input<T>(op))
-    unfold_input_plane_kernel<T><<<(unsigned)(op.batch * op.chan_in), NT, (size_t)(op.h_in * op.w_in) * sizeof(T),
+    unfold_input_plane_kernel<T><<<(unsigned)(op.batch * op.chan_in), NT, padded_plane_bytes(op, sizeof(T)),
                                    stream>>>(to_op32(op), img, st, patches);
   else
     unfold_input_kernel<T><<<grid_for(total, sms), NT, 0, stream>>>(op, img, st, patches, total);
@@ -410,7 +413,7 @@ int backward_t(int dtype, const Op& op, const T* img, T* grad_img, const T* filt
     const int64_t npos = op.h_out * op.w_out;
     Strides4 ist{{op.chan_in * hw, hw, op.w_in, 1}};
     if (plane_path_input<T>(op))
-      unfold_input_plane_kernel<T><<<(unsigned)(op.batch * op.chan_in), NT, (size_t)hw * sizeof(T), stream>>>(
+      unfold_input_plane_kernel<T><<<(unsigned)(op.batch * op.chan_in), NT, padded_plane_bytes(op, sizeof(T)), stream>>>(
           to_op32(op), img, ist, patches);
     else
       unfold_input_kernel<T><<<grid_for(n_fwd_patches, sms), NT, 0, stream>>>(op, img, ist, patches, n_fwd_patches);
