@@ -16,7 +16,10 @@ gradient on this library's row-wise kernels.  Residual adds, softmax (unfused at
 plain torch ops either way.
 
 Parameters are f32 master weights; each step computes in f16 (`AMP<f16>`-like: f16 storage, f32
-accumulation inside the GEMMs) and Adam updates the f32 masters.
+accumulation inside the GEMMs) and Adam updates the f32 masters.  A `Trainer` keeps masters, f16 compute copies
+and gradients in flat buffers and, in the fused modes, has the backward ops write parameter gradients straight
+into them (dfdx's tape writes into `Gradients` storage the same way); modules used on their own take torch
+autograd's route.
 """
 from __future__ import annotations
 
@@ -153,6 +156,67 @@ class _LayerNorm(torch.autograd.Function):
         return None, gx, gg.to(gamma.dtype), gb.to(gamma.dtype), None
 
 
+class _DirectLinear(torch.autograd.Function):
+    """`_FusedLinear` for parameters held in a trainer's flat buffers, with the gradients written the way dfdx's tape
+    does it: straight into the parameter's gradient storage (`Gradients::get_or_alloc_mut`), not returned to
+    an autograd engine that would copy, cast and add them.  `slot` = (f16 weight, f16 bias, f16 weight-gradient
+    buffer, f32 bias-gradient buffer); the weight gradient is overwritten (each parameter is used once per
+    step), the bias gradient is added into its zeroed f32 slot."""
+
+    @staticmethod
+    def forward(ctx, dev: Cuda, x, slot, relu: bool):
+        if x.storage_offset() or not _dense(x):
+            x = x.contiguous()
+        y = dev.linear_forward(x, slot[0].permute(1, 0), slot[1], relu)
+        ctx.dev, ctx.relu, ctx.slot = dev, relu, slot
+        ctx.save_for_backward(x, y if relu else None)
+        return y
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        x, y = ctx.saved_tensors
+        dev, (w16, _, gw16, gb32) = ctx.dev, ctx.slot
+        g = grad_out.contiguous()
+        if ctx.relu:
+            g = torch.ops.aten.threshold_backward(g, y, 0.0)
+        gx = torch.empty(x.untyped_storage().nbytes() // x.element_size(), dtype=x.dtype, device=x.device)
+        dev.matmat_br_backward_overwrite(x, gx, w16.permute(1, 0), gw16, g)
+        dev.bias_grad(g, gb32)
+        return None, dev.grad_view(gx, x), None, None
+
+
+class _DirectLayerNorm(torch.autograd.Function):
+    """`_LayerNorm` with gamma's and beta's gradients added straight into their f32 gradient slots.
+    `slot` = (f16 gamma, f16 beta, f32 gamma-gradient buffer, f32 beta-gradient buffer)."""
+
+    @staticmethod
+    def forward(ctx, dev: Cuda, x, slot, eps: float):
+        x = x.contiguous()
+        y, stats = dev.layer_norm_forward(x, slot[0], slot[1], eps, want_stats=True)
+        ctx.dev, ctx.slot = dev, slot
+        ctx.save_for_backward(x, stats)
+        return y
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        x, stats = ctx.saved_tensors
+        g16, _, gg32, gb32 = ctx.slot
+        return None, ctx.dev.layer_norm_backward(x, g16, stats, grad_out.contiguous(), gg32, gb32), None, None
+
+
+class _Attach(torch.autograd.Function):
+    """Puts a tensor that needs no gradient on the tape (the ops above take their parameters outside autograd, so
+    the first layer's input is what makes their backward run); nothing flows back through it."""
+
+    @staticmethod
+    def forward(ctx, x, anchor):
+        return x.view_as(x)
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        return None, None
+
+
 class Linear(torch.nn.Module):
     """dfdx `Linear`: weight stored (O, I), consumed as the permuted (I, O) view; uniform(+-1/sqrt(I)) init
     (dfdx/src/nn/layers/linear.rs:65-89)."""
@@ -160,11 +224,14 @@ class Linear(torch.nn.Module):
     def __init__(self, dev: Cuda, i: int, o: int, gen: torch.Generator, fused: bool = True):
         super().__init__()
         self.dev, self.fused = dev, fused
+        self.slot = None                                           # set by a Trainer that owns the parameters' storage
         b = 1.0 / math.sqrt(i)
         self.weight = torch.nn.Parameter(((torch.rand(o, i, generator=gen) * 2 - 1) * b).to(dev.device))
         self.bias = torch.nn.Parameter(((torch.rand(o, generator=gen) * 2 - 1) * b).to(dev.device))
 
     def forward(self, x, relu: bool = False):
+        if self.slot is not None and self.fused:
+            return _DirectLinear.apply(self.dev, x, self.slot, relu)
         w = self.weight.half()                                     # f16 compute copy of the f32 master
         if self.fused:
             return _FusedLinear.apply(self.dev, x, w, self.bias.half(), relu)
@@ -206,6 +273,8 @@ class EncoderBlock(torch.nn.Module):
         self.norm2 = torch.nn.LayerNorm(model, device=dev.device)
 
     def _norm(self, ln, x):
+        if self.attn.fused and getattr(ln, "slot", None) is not None:
+            return _DirectLayerNorm.apply(self.attn.dev, x, ln.slot, ln.eps)
         if self.attn.fused:
             return _LayerNorm.apply(self.attn.dev, x, ln.weight.half(), ln.bias.half(), ln.eps)
         return F.layer_norm(x, ln.normalized_shape, ln.weight.half(), ln.bias.half(), ln.eps)
@@ -222,8 +291,12 @@ class Encoder(torch.nn.Module):
         super().__init__()
         gen = torch.Generator().manual_seed(seed)
         self.blocks = torch.nn.ModuleList(EncoderBlock(dev, model, heads, ff, gen, fused) for _ in range(layers))
+        self.attach = False                                        # set by a Trainer in direct-gradient mode
 
     def forward(self, x):
+        if self.attach and not x.requires_grad:
+            # a fresh leaf every step: a long-lived one would tie the backward pass to the stream it was made on
+            x = _Attach.apply(x, torch.zeros(1, device=x.device, requires_grad=True))
         for blk in self.blocks:
             x = blk(x)
         return x
@@ -235,23 +308,57 @@ class Trainer:
     The eager step is bound by host-side launch overhead (about 300 small launches), so `capture()` records
     the whole step once into a CUDA graph and `step()` then replays it on static input buffers."""
 
-    def __init__(self, dev: Cuda, world: int = 1, **model_kw):
+    def __init__(self, dev: Cuda, world: int = 1, direct: bool = True, **model_kw):
         self.dev, self.world = dev, world
         self.model = Encoder(dev, **model_kw)
-        params = list(self.model.parameters())
-        # one flat f32 gradient buffer: a single NCCL all-reduce per step
-        self.flat_grad = torch.zeros(sum(p.numel() for p in params), device=dev.device)
-        off = 0
+        linears = [m for m in self.model.modules() if isinstance(m, Linear)]
+        weights = [m.weight for m in linears]
+        seen = {id(p) for p in weights}
+        params = weights + [p for p in self.model.parameters() if id(p) not in seen]
+        total = sum(p.numel() for p in params)
+        # one flat f32 master buffer and one flat f32 gradient buffer (a single NCCL all-reduce per step), the
+        # Linear weights first
+        self.flat_param = torch.empty(total, device=dev.device)
+        self.flat_grad = torch.zeros(total, device=dev.device)
+        spans, off = {}, 0
         for p in params:
+            spans[id(p)] = (off, off + p.numel())
+            self.flat_param[off:off + p.numel()].copy_(p.data.reshape(-1))
+            p.data = self.flat_param[off:off + p.numel()].view_as(p)
             p.grad = self.flat_grad[off:off + p.numel()].view_as(p)
             off += p.numel()
+        # Direct-gradient mode (fused modes only): the f16 compute copies of all parameters are one flat buffer
+        # refreshed by one cast per step; the GEMMs write the f16 weight gradients into one flat buffer that one
+        # cast folds into the f32 gradients; bias / LayerNorm gradients (f32 column sums) are added straight into
+        # their f32 slots.  Otherwise every parameter takes torch's route: a cast per use, and per gradient a
+        # cast and an add.
+        self.direct = bool(direct and model_kw.get("fused", True))
+        if self.direct:
+            self.n_weights = sum(p.numel() for p in weights)
+            self.flat16 = torch.empty(total, dtype=torch.float16, device=dev.device)
+            self.flat_gw16 = torch.zeros(self.n_weights, dtype=torch.float16, device=dev.device)
+
+            def v16(p):
+                lo, hi = spans[id(p)]
+                return self.flat16[lo:hi].view_as(p)
+            for m in linears:
+                lo, hi = spans[id(m.weight)]
+                m.slot = (v16(m.weight), v16(m.bias), self.flat_gw16[lo:hi].view_as(m.weight), m.bias.grad)
+            for blk in self.model.blocks:
+                for ln in (blk.norm1, blk.norm2):
+                    ln.slot = (v16(ln.weight), v16(ln.bias), ln.weight.grad, ln.bias.grad)
+            self.model.attach = True
         self.opt = torch.optim.Adam(params, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, fused=True, capturable=True)
         self.graph = None
 
     def _step(self, x: torch.Tensor, target: torch.Tensor) -> torch.Tensor:
         self.flat_grad.zero_()
+        if self.direct:
+            self.flat16.copy_(self.flat_param)
         loss = F.mse_loss(self.model(x).float(), target.float())
         loss.backward()
+        if self.direct:
+            self.flat_grad[:self.n_weights].copy_(self.flat_gw16)
         if self.world > 1:
             import torch.distributed as dist
             dist.all_reduce(self.flat_grad)

@@ -64,3 +64,26 @@ def test_trainer_graph_replay_matches_eager(cuda_dev):
     for g_, w_ in zip(got, want[4:7] + [None]):
         if w_ is not None:
             assert abs(g_ - w_) <= 2e-2 * abs(w_)
+
+
+def test_trainer_direct_gradients_match_autograd_route(cuda_dev):
+    """Gradients written straight into the trainer's flat buffers equal the ones torch's autograd collects
+    (cast, add per parameter) for the same step; bias / LayerNorm gradients differ only by the f16 rounding the
+    autograd route puts on the f32 column sums."""
+    from dfdx_b200.encoder import Trainer
+    gen = torch.Generator().manual_seed(5)
+    x = torch.randn(4, 32, 64, generator=gen).half().to(cuda_dev.device)
+    t = torch.randn(4, 32, 64, generator=gen).half().to(cuda_dev.device)
+    kw = dict(layers=2, model=64, heads=4, ff=128, seed=3, fused="attention")
+    a, b = Trainer(cuda_dev, 1, direct=True, **kw), Trainer(cuda_dev, 1, direct=False, **kw)
+    assert a.direct and not b.direct
+    assert torch.equal(a.flat_param, b.flat_param)
+    la, lb = a._step(x, t), b._step(x, t)
+    assert abs(la.item() - lb.item()) <= 1e-6 * abs(lb.item())
+    for pa, pb, (name, _) in zip(a.opt.param_groups[0]["params"], b.opt.param_groups[0]["params"],
+                                 [(n, 0) for n in range(10 ** 6)]):
+        ref = pb.grad.float()
+        err = (pa.grad.float() - ref).norm() / max(float(ref.norm()), 1e-2 * float(b.flat_grad.norm()))
+        assert err <= 2e-3, f"parameter {name}: {float(err):.3e}"
+    # the step trained both the same way
+    assert (a.flat_param - b.flat_param).abs().max() <= 2.1e-3    # one Adam step moves a weight by at most lr
