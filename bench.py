@@ -35,7 +35,7 @@ FLOP_PER_STEP = B * FLOP_PER_ITEM          # 412.3 GFLOP
 FLOP_PER_LAUNCH = FLOP_PER_STEP / 3.0      # each of the three GEMMs: 137.4 GFLOP
 METRIC = "gemm_fwd_bwd_tflops"
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from one ncu capture of this workload
-# (forward 306.6 MB, grad_rhs 359.8 MB, grad_lhs 442.9 MB).
+# (forward 303.2 MB, grad_rhs 357.4 MB, grad_lhs 438.5 MB).
 NCU_TRAFFIC_BYTES_PER_LAUNCH = 366.4e6
 WORKLOAD = f"config[1]: MatMatBr f32 X[{B},{S},{K}] x W^T, W stored [{N},{K}], fwd + grad_lhs + grad_rhs"
 
