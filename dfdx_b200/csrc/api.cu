@@ -26,6 +26,7 @@ int conv1d_backward(int dtype, const b200_conv1d_op* o, const void* img, void* g
                     const size_t fs[3], void* grad_filters, const void* grad_out, void* ws, cudaStream_t stream);
 int conv2d_backward(int dtype, const b200_conv2d_op* o, const void* img, void* grad_img, const void* filters,
                     const size_t fs[4], void* grad_filters, const void* grad_out, void* ws, cudaStream_t stream);
+int conv_noalloc_setup_device();
 void tc_set_xform_mode(int mode);
 void tc_set_tile_n(int bn);
 void tc_set_mn_box5(int on);
@@ -33,6 +34,8 @@ void tc_set_pair_mode(int mode);
 void tc_set_store_mode(int mode);
 void conv_set_lowering(int grad_img_mode, size_t group_bytes);
 void tc_set_split_mode(int mode);
+void tc_set_capture_split(int on);
+void tc_set_wait_limit(long long cycles);
 
 namespace {
 
@@ -126,6 +129,7 @@ int b200_init(int ordinal) {
   if ((rc = tc_setup_device())) return rc;
   if ((rc = attention_setup_device())) return rc;
   if ((rc = attention_bwd_setup_device())) return rc;
+  if ((rc = conv_noalloc_setup_device())) return rc;
   d.ready = true;
   return B200_OK;
 }
@@ -166,10 +170,10 @@ int b200_set_path(int path) {
   return B200_OK;
 }
 
-/* Testing hook: 0 = split f32 into tf32_rn(big) + small (default), 1 = rely on the tensor core
- * truncating raw f32 operands and only write the small copy. */
+/* Testing hook: how the `small` half of the 3xTF32 operand split is stored: 1 (default) as computed (the tensor
+ * core keeps its top 19 bits), 0 rounded to tf32 first.  Both give results inside the f32 tolerance. */
 int b200_set_tf32_split_mode(int mode) {
-  if (mode < 0 || mode > 15) return B200_ERR_UNSUPPORTED;   // bits 1, 2, 3: timing experiments (wrong results)
+  if (mode != 0 && mode != 1) return B200_ERR_UNSUPPORTED;
   tc_set_xform_mode(mode);
   return B200_OK;
 }
@@ -196,13 +200,14 @@ int b200_set_cta_pair_mode(int mode) {
   return B200_OK;
 }
 
-/* Testing hook: epilogue store orientation of the tensor-core kernels: 0 (default) planner's choice,
- * 1 row stores only, 2 column stores wherever the output allows. */
+/* Testing hook: lowering of the convolution data gradient (see the header). */
 int b200_set_conv_lowering(int grad_img_mode, size_t group_bytes) {
   if (grad_img_mode < 0 || grad_img_mode > 1) return B200_ERR_UNSUPPORTED;
   conv_set_lowering(grad_img_mode, group_bytes);
   return B200_OK;
 }
+/* Testing hook: epilogue store orientation of the tensor-core kernels: 0 (default) planner's choice,
+ * 1 row stores only, 2 column stores wherever the output allows. */
 int b200_set_store_mode(int mode) {
   if (mode < 0 || mode > 2) return B200_ERR_UNSUPPORTED;
   tc_set_store_mode(mode);
@@ -214,6 +219,20 @@ int b200_set_store_mode(int mode) {
 int b200_set_split_k(int mode) {
   if (mode < -1 || mode > 64) return B200_ERR_UNSUPPORTED;
   tc_set_split_mode(mode);
+  return B200_OK;
+}
+
+/* f16 split-K inside stream captures: 0 (default) a GEMM enqueued on a capturing stream runs unsplit, 1 it may
+ * use the device's split-K scratch (the caller orders graph replays against all other use of the library). */
+int b200_set_capture_split_k(int on) {
+  tc_set_capture_split(on);
+  return B200_OK;
+}
+
+/* Testing hook: clock budget of the device-side waits of the tensor-core GEMM kernels (0 = by problem size). */
+int b200_set_wait_limit(long long cycles) {
+  if (cycles < 0) return B200_ERR_UNSUPPORTED;
+  tc_set_wait_limit(cycles);
   return B200_OK;
 }
 
@@ -252,6 +271,12 @@ int b200_gemm_batch(int dtype, size_t batch, size_t m, size_t k, size_t n, const
   return run_gemm(p, (cudaStream_t)stream);
 }
 
+// The stream that takes the grad_lhs GEMM of a backward pass.  dfdx enqueues it on the device's `par_stream`
+// and the grad_rhs GEMM on the default stream (cuda_kernel.rs:282-310, :354-386, :432-460, :535-566), joining the two
+// streams itself before (`par_stream.wait_for_default()`) and after (`dev.wait_for(par_stream)`).  A NULL
+// par_stream means the caller has no second stream: both GEMMs then go to `stream`.
+static void* lhs_stream_of(void* stream, void* par_stream) { return par_stream ? par_stream : stream; }
+
 // ---- MatMatKernel (cuda_kernel.rs:244-312) -------------------------------------------------------
 int b200_matmat_forward(int dtype, size_t m, size_t k, size_t n, const void* lhs, const size_t ls[2],
                         const void* rhs, const size_t rs[2], void* out, void* stream) {
@@ -262,13 +287,12 @@ int b200_matmat_forward(int dtype, size_t m, size_t k, size_t n, const void* lhs
 int b200_matmat_backward(int dtype, size_t m, size_t k, size_t n, const void* lhs, const size_t ls[2],
                          void* grad_lhs, const void* rhs, const size_t rs[2], void* grad_rhs,
                          const void* grad_out, void* stream, void* par_stream) {
-  (void)par_stream;
   if (!ls || !rs) return B200_ERR_NULL;
   const size_t os[2] = {n, 1};
   int rc = B200_OK;
   if (grad_lhs) {  // grad_lhs += grad_out * rhs^T
     const size_t rs_t[2] = {rs[1], rs[0]};
-    if ((rc = b200_gemm(dtype, m, n, k, grad_out, os, rhs, rs_t, 1.0, grad_lhs, ls, stream))) return rc;
+    if ((rc = b200_gemm(dtype, m, n, k, grad_out, os, rhs, rs_t, 1.0, grad_lhs, ls, lhs_stream_of(stream, par_stream)))) return rc;
   }
   if (grad_rhs) {  // grad_rhs += lhs^T * grad_out
     const size_t ls_t[2] = {ls[1], ls[0]};
@@ -288,7 +312,7 @@ int b200_matmat_br_forward(int dtype, size_t batch, size_t m, size_t k, size_t n
 
 static int matmat_br_backward_beta(int dtype, size_t batch, size_t m, size_t k, size_t n, const void* lhs,
                                    const size_t ls[3], void* grad_lhs, const void* rhs, const size_t rs[2],
-                                   void* grad_rhs, const void* grad_out, void* stream, int beta) {
+                                   void* grad_rhs, const void* grad_out, void* stream, void* lhs_stream, int beta) {
   if (!valid_dtype(dtype)) return B200_ERR_DTYPE;
   if (!ls || !rs) return B200_ERR_NULL;
   if (!matrix_strides_ok(ls + 1) || !matrix_strides_ok(rs)) return B200_ERR_STRIDE;
@@ -306,7 +330,7 @@ static int matmat_br_backward_beta(int dtype, size_t batch, size_t m, size_t k, 
   if (grad_lhs) {  // grad_lhs (+)= grad_out * rhs^T, rhs broadcast over the batch
     const size_t os[3] = {m * n, n, 1};
     const size_t rs_t[3] = {0, rs[1], rs[0]};
-    rc = b200_gemm_batch(dtype, batch, m, n, k, grad_out, os, rhs, rs_t, beta ? 1.0 : 0.0, grad_lhs, ls, stream);
+    rc = b200_gemm_batch(dtype, batch, m, n, k, grad_out, os, rhs, rs_t, beta ? 1.0 : 0.0, grad_lhs, ls, lhs_stream);
   }
   return rc;
 }
@@ -314,8 +338,8 @@ static int matmat_br_backward_beta(int dtype, size_t batch, size_t m, size_t k, 
 int b200_matmat_br_backward(int dtype, size_t batch, size_t m, size_t k, size_t n, const void* lhs,
                             const size_t ls[3], void* grad_lhs, const void* rhs, const size_t rs[2],
                             void* grad_rhs, const void* grad_out, void* stream, void* par_stream) {
-  (void)par_stream;
-  return matmat_br_backward_beta(dtype, batch, m, k, n, lhs, ls, grad_lhs, rhs, rs, grad_rhs, grad_out, stream, 1);
+  return matmat_br_backward_beta(dtype, batch, m, k, n, lhs, ls, grad_lhs, rhs, rs, grad_rhs, grad_out, stream,
+                                 lhs_stream_of(stream, par_stream), 1);
 }
 
 int b200_matmat_br_backward_overwrite(int dtype, size_t batch, size_t m, size_t k, size_t n, const void* lhs,
@@ -324,7 +348,7 @@ int b200_matmat_br_backward_overwrite(int dtype, size_t batch, size_t m, size_t 
   // writing instead of accumulating is only the same thing when no two elements of a view share storage
   if (ls && grad_lhs && ((batch > 1 && ls[0] == 0) || (m > 1 && ls[1] == 0) || (k > 1 && ls[2] == 0))) return B200_ERR_STRIDE;
   if (rs && grad_rhs && ((k > 1 && rs[0] == 0) || (n > 1 && rs[1] == 0))) return B200_ERR_STRIDE;
-  return matmat_br_backward_beta(dtype, batch, m, k, n, lhs, ls, grad_lhs, rhs, rs, grad_rhs, grad_out, stream, 0);
+  return matmat_br_backward_beta(dtype, batch, m, k, n, lhs, ls, grad_lhs, rhs, rs, grad_rhs, grad_out, stream, stream, 0);
 }
 
 // ---- MatMatBatch3Kernel (cuda_kernel.rs:395-462) -------------------------------------------------
@@ -339,13 +363,13 @@ int b200_matmat_batch3_forward(int dtype, size_t batch, size_t m, size_t k, size
 int b200_matmat_batch3_backward(int dtype, size_t batch, size_t m, size_t k, size_t n, const void* lhs,
                                 const size_t ls[3], void* grad_lhs, const void* rhs, const size_t rs[3],
                                 void* grad_rhs, const void* grad_out, void* stream, void* par_stream) {
-  (void)par_stream;
   if (!ls || !rs) return B200_ERR_NULL;
   const size_t os[3] = {m * n, n, 1};
   int rc = B200_OK;
   if (grad_lhs) {
     const size_t rs_t[3] = {rs[0], rs[2], rs[1]};
-    if ((rc = b200_gemm_batch(dtype, batch, m, n, k, grad_out, os, rhs, rs_t, 1.0, grad_lhs, ls, stream))) return rc;
+    if ((rc = b200_gemm_batch(dtype, batch, m, n, k, grad_out, os, rhs, rs_t, 1.0, grad_lhs, ls,
+                              lhs_stream_of(stream, par_stream)))) return rc;
   }
   if (grad_rhs) {
     const size_t ls_t[3] = {ls[0], ls[2], ls[1]};
@@ -477,13 +501,13 @@ int b200_matmat_batch4_backward(int dtype, size_t batch, size_t seq, size_t m, s
                                 const void* lhs, const size_t ls[4], void* grad_lhs, const void* rhs,
                                 const size_t rs[4], void* grad_rhs, const void* grad_out, void* stream,
                                 void* par_stream) {
-  (void)par_stream;
   if (!ls || !rs) return B200_ERR_NULL;
   const size_t os[4] = {seq * m * n, m * n, n, 1};
   int rc = B200_OK;
   if (grad_lhs) {
     const size_t rs_t[4] = {rs[0], rs[1], rs[3], rs[2]};
-    if ((rc = gemm_batch2(dtype, batch, seq, m, n, k, grad_out, os, rhs, rs_t, 1, grad_lhs, ls, stream))) return rc;
+    if ((rc = gemm_batch2(dtype, batch, seq, m, n, k, grad_out, os, rhs, rs_t, 1, grad_lhs, ls,
+                          lhs_stream_of(stream, par_stream)))) return rc;
   }
   if (grad_rhs) {
     const size_t ls_t[4] = {ls[0], ls[1], ls[3], ls[2]};
@@ -512,6 +536,7 @@ int b200_conv2d_forward(int dtype, const b200_conv2d_op* op, const void* img, co
   if (rc) return rc;
   if (!img_strides) return B200_ERR_NULL;
   const size_t need = conv2d_workspace_bytes(dtype, op, 0);
+  if (need == ~(size_t)0) return B200_ERR_LIMIT;             // the geometry's element counts overflow
   if (need == 0) return B200_OK;
   if (!img || !filters || !out || !workspace) return B200_ERR_NULL;
   if (workspace_bytes < need) return B200_ERR_WORKSPACE;
@@ -529,6 +554,7 @@ int b200_conv2d_backward(int dtype, const b200_conv2d_op* op, const void* img, v
   if (rc) return rc;
   if (!filters_strides) return B200_ERR_NULL;
   const size_t need = conv2d_workspace_bytes(dtype, op, 1);
+  if (need == ~(size_t)0) return B200_ERR_LIMIT;             // the geometry's element counts overflow
   if (need == 0) return B200_OK;
   if (!img || !filters || !grad_out || !workspace) return B200_ERR_NULL;
   if (workspace_bytes < need) return B200_ERR_WORKSPACE;
@@ -551,6 +577,7 @@ int b200_convtrans2d_forward(int dtype, const b200_convtrans2d_op* op, const voi
   if (rc) return rc;
   if (!filters_strides) return B200_ERR_NULL;
   const size_t need = convtrans2d_workspace_bytes(dtype, op, 0);
+  if (need == ~(size_t)0) return B200_ERR_LIMIT;             // the geometry's element counts overflow
   if (need == 0 || op->batch * op->chan_out * op->h_out * op->w_out == 0) return B200_OK;
   if (!img || !filters || !out || !workspace) return B200_ERR_NULL;
   if (workspace_bytes < need) return B200_ERR_WORKSPACE;
@@ -568,6 +595,7 @@ int b200_convtrans2d_backward(int dtype, const b200_convtrans2d_op* op, const vo
   if (rc) return rc;
   if (!filters_strides) return B200_ERR_NULL;
   const size_t need = convtrans2d_workspace_bytes(dtype, op, 1);
+  if (need == ~(size_t)0) return B200_ERR_LIMIT;             // the geometry's element counts overflow
   if (need == 0) return B200_OK;
   if (!img || !filters || !grad_out || !workspace) return B200_ERR_NULL;
   if (workspace_bytes < need) return B200_ERR_WORKSPACE;
@@ -602,6 +630,7 @@ int b200_conv1d_forward(int dtype, const b200_conv1d_op* op, const void* img, co
   if (rc) return rc;
   if (!img_strides) return B200_ERR_NULL;
   const size_t need = conv1d_workspace_bytes(dtype, op, 0);
+  if (need == ~(size_t)0) return B200_ERR_LIMIT;             // the geometry's element counts overflow
   if (need == 0) return B200_OK;
   if (!img || !filters || !out || !workspace) return B200_ERR_NULL;
   if (workspace_bytes < need) return B200_ERR_WORKSPACE;
@@ -618,6 +647,7 @@ int b200_conv1d_backward(int dtype, const b200_conv1d_op* op, const void* img, v
   if (rc) return rc;
   if (!filters_strides) return B200_ERR_NULL;
   const size_t need = conv1d_workspace_bytes(dtype, op, 1);
+  if (need == ~(size_t)0) return B200_ERR_LIMIT;             // the geometry's element counts overflow
   if (need == 0) return B200_OK;
   if (!img || !filters || !grad_out || !workspace) return B200_ERR_NULL;
   if (workspace_bytes < need) return B200_ERR_WORKSPACE;

@@ -6,7 +6,9 @@
 //   backward: patches (B, O, K, K, H, W) | filters_tr (G, C/G, O/G, K, K) | grad_filters_tr (B, G, C/G, O/G, K, K)
 // each region starts on a 256-byte boundary so the GEMM operands stay TMA-addressable.
 #include "common.cuh"
+#include <atomic>
 #include <mutex>
+#include <initializer_list>
 
 namespace b200 {
 namespace {
@@ -350,9 +352,10 @@ unsigned grid_for(int64_t total, int sms) {
 size_t align256(size_t x) { return (x + 255) & ~(size_t)255; }
 
 // Tuning knobs (b200_set_conv_lowering): 0 = choose, 1 = data gradient by gather + GEMM only; bytes of cols per group of images.
+// Atomics: a thread may change a knob while another thread launches.
 constexpr size_t CONV_GROUP_BYTES_DEFAULT = ~(size_t)0;
-int g_conv_grad_img_mode = 0;
-size_t g_conv_group_bytes = CONV_GROUP_BYTES_DEFAULT;
+std::atomic<int> g_conv_grad_img_mode{0};
+std::atomic<size_t> g_conv_group_bytes{CONV_GROUP_BYTES_DEFAULT};
 
 template <typename T, typename A>
 int forward_t(int dtype, const Op& op, const T* img, const size_t is[4], const T* filters, T* out,
@@ -444,8 +447,9 @@ int backward_t(int dtype, const Op& op, const T* img, T* grad_img, const T* filt
       op.dilation * (op.kw + 4) + op.w_in + op.pw < ((int64_t)1 << 31) && op.dilation * op.kh + op.h_in + op.ph < ((int64_t)1 << 31)) {
     const int64_t npos = op.h_out * op.w_out, per_image = op.chan_in * KK * npos;
     int64_t group = op.batch;
-    if (g_conv_group_bytes > 0) {
-      group = (int64_t)(g_conv_group_bytes / ((size_t)per_image * sizeof(T)));
+    const size_t group_bytes = g_conv_group_bytes.load();
+    if (group_bytes > 0) {
+      group = (int64_t)(group_bytes / ((size_t)per_image * sizeof(T)));
       group = group < 1 ? 1 : (group > op.batch ? op.batch : group);
     }
     for (int64_t b0 = 0; b0 < op.batch; b0 += group) {
@@ -506,15 +510,37 @@ int backward_t(int dtype, const Op& op, const T* img, T* grad_img, const T* filt
 }  // namespace
 
 namespace {
+// Overflow-checked products of caller-supplied extents: false when the product does not fit a size_t.
+bool mul_ok(size_t* acc, int64_t f) {
+  if (f < 0) return false;
+  return !__builtin_mul_overflow(*acc, (size_t)f, acc);
+}
+bool product(size_t* out, std::initializer_list<int64_t> factors) {
+  size_t acc = 1;
+  for (int64_t f : factors)
+    if (!mul_ok(&acc, f)) return false;
+  *out = acc;
+  return true;
+}
+constexpr size_t WS_OVERFLOW = ~(size_t)0;
+
+// Bytes of workspace one pass needs; WS_OVERFLOW when the geometry's element counts do not fit a size_t (or the
+// 31-bit index arithmetic of the kernels), 0 when there is nothing to compute.
 size_t workspace_bytes_op(int dtype, const Op& o, int backward) {
   const size_t es = dtype_size(dtype);
   if (!es || !o.groups) return 0;
-  const size_t KK = (size_t)(o.kh * o.kw);
-  const size_t fwd_patches = (size_t)o.batch * o.chan_in * KK * o.h_out * o.w_out * es;
+  size_t fwd_patches, bwd_patches, nf, bnf, img_elems, out_elems;
+  if (!product(&fwd_patches, {o.batch, o.chan_in, o.kh, o.kw, o.h_out, o.w_out, (int64_t)es}) ||
+      !product(&bwd_patches, {o.batch, o.chan_out, o.kh, o.kw, o.h_in, o.w_in, (int64_t)es}) ||
+      !product(&nf, {o.groups, o.chan_in / o.groups, o.chan_out / o.groups, o.kh, o.kw, (int64_t)es}) ||
+      !product(&bnf, {o.batch, (int64_t)nf}) ||
+      !product(&img_elems, {o.batch, o.chan_in, o.h_in, o.w_in, (int64_t)es}) ||
+      !product(&out_elems, {o.batch, o.chan_out, o.h_out, o.w_out, (int64_t)es}))
+    return WS_OVERFLOW;
+  const size_t big = (size_t)1 << 62;
+  if (fwd_patches > big || bwd_patches > big || bnf > big) return WS_OVERFLOW;
   if (!backward) return align256(fwd_patches);
-  const size_t nf = (size_t)o.groups * (o.chan_in / o.groups) * (o.chan_out / o.groups) * KK;
-  const size_t bwd_patches = (size_t)o.batch * o.chan_out * KK * o.h_in * o.w_in * es;
-  return align256(bwd_patches > fwd_patches ? bwd_patches : fwd_patches) + align256(nf * es) + align256(o.batch * nf * es);
+  return align256(bwd_patches > fwd_patches ? bwd_patches : fwd_patches) + align256(nf) + align256(bnf);
 }
 
 int forward_any(int dtype, const Op& op, const void* img, const size_t is[4], const void* filters, void* out, void* ws,
@@ -593,8 +619,8 @@ int convtrans2d_backward(int dtype, const b200_convtrans2d_op* o, const void* im
 }
 
 void conv_set_lowering(int grad_img_mode, size_t group_bytes) {
-  g_conv_grad_img_mode = grad_img_mode;
-  g_conv_group_bytes = group_bytes ? group_bytes : CONV_GROUP_BYTES_DEFAULT;
+  g_conv_grad_img_mode.store(grad_img_mode);
+  g_conv_group_bytes.store(group_bytes ? group_bytes : CONV_GROUP_BYTES_DEFAULT);
 }
 
 size_t conv2d_workspace_bytes(int dtype, const b200_conv2d_op* o, int backward) {
@@ -635,8 +661,8 @@ int conv2d_backward(int dtype, const b200_conv2d_op* o, const void* img, void* g
 // latency-critical loop in which cudaMalloc's implicit device synchronisation is unacceptable, or a
 // component that is only ever given input and output buffers by its host application.  For them the
 // im2col patch buffer lives in a fixed array inside the library image instead of in a caller-provided
-// workspace.  The array costs B200_CONV2D_NOALLOC_SCRATCH_BYTES on every GPU on which the library is
-// loaded, for the life of the process, whether or not this entry point is ever called.
+// workspace.  The array costs B200_CONV2D_NOALLOC_SCRATCH_BYTES on every GPU for which b200_init has run,
+// for the life of the process, whether or not this entry point is ever called.
 // ------------------------------------------------------------------------------------------------
 namespace b200 {
 namespace {
@@ -651,7 +677,9 @@ constexpr int NOALLOC_MAX_DEVICES = 64;
 void* g_noalloc_ptr[NOALLOC_MAX_DEVICES] = {};
 std::mutex g_noalloc_mutex;
 
-// Resolves the array's address on the CURRENT device, once per device.
+// Resolves the array's address on the CURRENT device, once per device.  Under CUDA's lazy module loading this
+// lookup is also what makes the array resident, so it runs inside b200_init: a caller that gives the rest of the
+// GPU to its own arena afterwards can no longer be surprised by the array's 32 MiB.
 int noalloc_scratch(void** out) {
   int dev = -1;
   int rc = note_cuda_error(cudaGetDevice(&dev), "cudaGetDevice");
@@ -665,11 +693,15 @@ int noalloc_scratch(void** out) {
     if (!p) return B200_ERR_CUDA;
     g_noalloc_ptr[dev] = p;
   }
-  *out = g_noalloc_ptr[dev];
+  if (out) *out = g_noalloc_ptr[dev];
   return B200_OK;
 }
 
 }  // namespace
+
+// Called by b200_init with the device current.
+int conv_noalloc_setup_device() { return noalloc_scratch(nullptr); }
+
 }  // namespace b200
 
 extern "C" int b200_conv2d_forward_noalloc(int dtype, const b200_conv2d_op* op, const void* img,
@@ -680,7 +712,7 @@ extern "C" int b200_conv2d_forward_noalloc(int dtype, const b200_conv2d_op* op, 
   if (!op || !img_strides) return B200_ERR_NULL;
   if (!op->groups || !op->stride || !op->dilation || !op->kernel) return B200_ERR_SHAPE;
   if (op->chan_in % op->groups || op->chan_out % op->groups) return B200_ERR_SHAPE;
-  const size_t need = conv2d_workspace_bytes(dtype, op, 0);
+  const size_t need = conv2d_workspace_bytes(dtype, op, 0);   // overflow-checked: SIZE_MAX when the extents wrap
   if (need == 0) return B200_OK;
   if (need > NOALLOC_SCRATCH_BYTES) return B200_ERR_LIMIT;   // use b200_conv2d_forward with a workspace instead
   if (!img || !filters || !out) return B200_ERR_NULL;

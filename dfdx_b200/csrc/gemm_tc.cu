@@ -31,6 +31,7 @@
 // roles drain, TMEM is freed, the kernel writes B200_ERR_DEVICE_TIMEOUT to the device status word and
 // returns normally.
 #include "tc_device.cuh"
+#include <atomic>
 #include <mutex>
 
 namespace b200 {
@@ -109,7 +110,6 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
           const uint32_t ph = (it / STAGES) & 1u;
           if (!mbar_wait(smem_u32(&bar_empty[s]), ph ^ 1u, abortp, g.wait_limit)) { ok = false; break; }
           const uint32_t full = smem_u32(&bar_full[s]);
-          if (g.xform_mode & 8) { mbar_arrive(full); continue; }   // timing experiment: no loads
           mbar_expect_tx(full, C::STAGE_BYTES);
           const uint32_t a_dst = smem_base + s * C::STAGE_BYTES;
           load_operand<BM, C::BK, C::CH, C::MN_LBO>(a_dst, &tma_a, full, g.a_ld, t.mt * BM, kb * C::BK,
@@ -151,7 +151,6 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
           const uint32_t a_lo = a_lo0 + (uint32_t)s * STAGE16, b_lo = b_lo0 + (uint32_t)s * STAGE16;
 #pragma unroll
           for (int ks = 0; ks < C::KSTEPS; ++ks) {
-            if ((g.xform_mode & 4) && ks > 0) continue;               // timing experiment: 1 MMA of 4
             umma_lohi<2>(d_tmem, a_lo + ks * a_k16, a_hi, b_lo + ks * b_k16, b_hi, idesc, (i > un.kb_lo || ks > 0) ? 1u : 0u);
           }
           umma_commit(smem_u32(&bar_empty[s]));       // stage reusable once these MMAs retire
@@ -305,7 +304,7 @@ __device__ __forceinline__ void split_role(const TcArgs& g, uint32_t smem_base, 
       const uint32_t ph = (it / STAGES) & 1u;
       if (!mbar_wait(smem_u32(&bar_full[s]), ph, abortp, g.wait_limit)) { ok = false; break; }
       const uint32_t raw = smem_base + s * C::STAGE_BYTES + tt * 16;
-      if (!(g.xform_mode & 2)) {                        // bit 1: timing experiment, no split
+      {
         uint32_t x[PER][4];
 #pragma unroll
         for (int u = 0; u < PER; ++u)
@@ -400,7 +399,6 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_const
           const uint32_t ph = (it / STAGES) & 1u;
           if (!mbar_wait(smem_u32(&bar_empty[s]), ph ^ 1u, abortp, g.wait_limit)) { ok = false; break; }
           const uint32_t full = smem_u32(&bar_full[s]);
-          if (g.xform_mode & 8) { mbar_arrive(full); continue; }   // timing experiment: no loads
           mbar_expect_tx(full, C::RAW_BYTES);
           const uint32_t a_dst = smem_base + s * C::STAGE_BYTES;
           load_operand<BM, C::BK, C::CH, C::MN_LBO>(a_dst, &tma_a, full, g.a_ld, t.mt * BM, kb * C::BK,
@@ -445,10 +443,6 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_const
 #pragma unroll
             for (int ks = 0; ks < C::KSTEPS; ++ks) {
               const uint32_t al = a_lo + ks * a_k16, bl = b_lo + ks * b_k16;
-              if (g.xform_mode & 4) {                                         // bit 2: timing experiment
-                umma_lohi<4>(d_tmem, al, a_hi, bl, b_hi, idesc, (i > 0 || ks > 0) ? 1u : 0u);
-                continue;
-              }
               umma_lohi<4>(d_tmem, al + SMALL16, a_hi, bl, b_hi, idesc, (i > 0 || ks > 0) ? 1u : 0u);   // small * big
               umma_lohi<4>(d_tmem, al, a_hi, bl + SMALL16, b_hi, idesc, 1u);                            // big * small
               umma_lohi<4>(d_tmem, al, a_hi, bl, b_hi, idesc, 1u);                                      // big * big
@@ -750,13 +744,16 @@ int encode_map(CUtensorMap* map, const void* base, size_t esize, int64_t inner, 
   return r == CUDA_SUCCESS ? B200_OK : B200_ERR_UNSUPPORTED;
 }
 
-int g_xform_mode = 1;
-int g_force_bn = 0;   // 0 = choose by problem shape
-int g_mn_box5 = 1;    // MN-major operands: one 5-D TMA box per stage where the extent allows
+// Process-wide testing / profiling knobs.  Atomics: a thread may change one while another thread launches.
+std::atomic<int> g_xform_mode{1};
+std::atomic<int> g_force_bn{0};   // 0 = choose by problem shape
+std::atomic<int> g_mn_box5{1};    // MN-major operands: one 5-D TMA box per stage where the extent allows
 std::mutex g_split_mutex;
-int g_split_mode = 0; // split-K of the f32 kernel: 0 = choose, 1 = never, n >= 2 = force n slices (testing)
-int g_store_mode = 0; // 0 = choose, 1 = row stores only, 2 = column stores where possible
-int g_pair_mode = 1;  // 0 = choose by problem shape, 1 = never use CTA pairs (default: not faster yet), 2 = always (n > 128)
+std::atomic<int> g_split_mode{0}; // split-K of the f32 kernel: 0 = choose, 1 = never, n >= 2 = force n slices (testing)
+std::atomic<int> g_store_mode{0}; // 0 = choose, 1 = row stores only, 2 = column stores where possible
+std::atomic<int> g_capture_split{0}; // 1 = f16 split-K also on capturing streams (the caller orders graph replays)
+std::atomic<long long> g_wait_limit{0}; // clock budget of every device-side wait; 0 = by problem size (testing)
+std::atomic<int> g_pair_mode{1};  // 0 = choose by problem shape, 1 = never use CTA pairs (default: not faster yet), 2 = always (n > 128)
 
 // Tensor maps and kernel arguments for a tile grid of TM x TN outputs per scheduling unit, where one
 // CTA stages BMC rows of A and BNC columns of B per k-block of BK (MN-major operands in chunks of CH).
@@ -836,7 +833,8 @@ int build_launch(Launch& L, const Plan& pl, int esize, int tm, int tn, int bmc, 
   g.beta = p.beta;
   g.fused = p.fused() ? 1 : 0; g.alpha = (float)p.alpha; g.bias = p.bias; g.bias_row = p.bias_dim ? 1 : 0; g.act = p.act;
   g.xform_mode = g_xform_mode;
-  g.wait_limit = 400000000LL + (long long)g.red * g.k_blocks * 40000LL;
+  const long long forced_limit = g_wait_limit.load();
+  g.wait_limit = forced_limit > 0 ? forced_limit : 400000000LL + (long long)g.red * g.k_blocks * 40000LL;
   g.status = ds->status;
   return B200_OK;
 }
@@ -886,14 +884,17 @@ int launch_cfg(const Plan& pl, cudaStream_t stream, Kernel kernel, int ksplit) {
       // f16: partial sums are accumulated in the device's f32 scratch, then folded into C by a second kernel
       const long long lds = (p.n + 3) / 4 * 4;
       const size_t need = (size_t)p.m * (size_t)lds * sizeof(float);
-      if (need <= ds->split_scratch_bytes) {
+      // A GEMM enqueued on a capturing stream runs unsplit: the one scratch per device is ordered across streams
+      // by an event that is recorded eagerly, and a replayed graph would neither wait on it nor record it.  A
+      // caller that orders every replay of its graphs against all other work of the library on the device (one
+      // stream, say) may ask for split-K inside captures (b200_set_capture_split_k); the event is then left alone.
+      cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+      if (cudaStreamIsCapturing(stream, &cap) != cudaSuccess) cap = cudaStreamCaptureStatusActive;
+      const bool capturing = cap != cudaStreamCaptureStatusNone;
+      if (need <= ds->split_scratch_bytes && (!capturing || g_capture_split.load())) {
         std::lock_guard<std::mutex> lock(g_split_mutex);
         int rc;
-        // Order this use after the previous one when that ran on another stream.  A capturing stream neither
-        // waits on nor records the shared event (the replayed graph is ordered by its launch stream).
-        cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
-        cudaStreamIsCapturing(stream, &cap);
-        const bool capturing = cap != cudaStreamCaptureStatusNone;
+        // Order this use after the previous one when that ran on another stream.
         if (!capturing && ds->split_used && ds->split_last_stream != stream &&
             (rc = note_cuda_error(cudaStreamWaitEvent(stream, ds->split_event, 0), "cudaStreamWaitEvent(split-K)")))
           return rc;
@@ -913,12 +914,10 @@ int launch_cfg(const Plan& pl, cudaStream_t stream, Kernel kernel, int ksplit) {
                                                                          (int)p.m, (int)p.n, g.beta);
         count_launch(false);
         if ((rc = note_cuda_error(cudaGetLastError(), "split-K finalize launch"))) return rc;
-        if (!capturing) {
-          ds->split_used = true;
-          ds->split_last_stream = stream;
-          rc = note_cuda_error(cudaEventRecord(ds->split_event, stream), "cudaEventRecord(split-K)");
-        }
-        return rc;
+        if (capturing) return B200_OK;
+        ds->split_used = true;
+        ds->split_last_stream = stream;
+        return note_cuda_error(cudaEventRecord(ds->split_event, stream), "cudaEventRecord(split-K)");
       }
     }
   }
@@ -969,6 +968,8 @@ int launch_es(const Plan& pl, cudaStream_t stream) {
   const int sms = ds ? ds->sm_count : 148;
   int bn = 64;
   const double best = choose_tile(pl, ESIZE, &bn);
+  const int g_force_bn = b200::g_force_bn.load(), g_pair_mode = b200::g_pair_mode.load(),
+            g_split_mode = b200::g_split_mode.load();     // one read per launch
   if (g_force_bn) bn = g_force_bn;
   // CTA pairs (256 x 256 tiles on two SMs) when the problem fills the machine with them.
   if (!g_force_bn && g_pair_mode != 1 && p.n > 128 && !p.fused()) {   // the pair kernels have no fused epilogue
@@ -1039,6 +1040,7 @@ int tc_setup_device() {
 int launch_gemm_tc(const GemmProblem& p, cudaStream_t stream) {
   const int es = (p.dtype == B200_F32) ? 4 : 2;
   Plan row = make_plan(p, false), col = make_plan(p, true);
+  const int g_store_mode = b200::g_store_mode.load();
   if (g_store_mode == 1) col.ok = false;
   if (g_store_mode == 2 && col.ok) row.ok = false;
   if (!row.ok && !col.ok) return B200_ERR_UNSUPPORTED;
@@ -1063,5 +1065,7 @@ void tc_set_mn_box5(int on) { g_mn_box5 = on; }
 void tc_set_pair_mode(int mode) { g_pair_mode = mode; }
 void tc_set_store_mode(int mode) { g_store_mode = mode; }
 void tc_set_split_mode(int mode) { g_split_mode = mode; }
+void tc_set_wait_limit(long long cycles) { g_wait_limit = cycles; }
+void tc_set_capture_split(int on) { g_capture_split = on ? 1 : 0; }
 
 }  // namespace b200

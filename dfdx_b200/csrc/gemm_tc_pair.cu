@@ -178,7 +178,6 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_con
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1u;
           if (!mbar_wait(smem_u32(&bar_empty[s]), ph ^ 1u, abortp, g.wait_limit)) { ok = false; break; }
-          if (g.xform_mode & 8) { if (rank == 0) mbar_arrive(smem_u32(&bar_full[s])); continue; }   // timing experiment
           if (rank == 0) mbar_expect_tx(smem_u32(&bar_full[s]), 2 * C::STAGE_BYTES);   // both CTAs' bytes
           const uint32_t full = mapa(smem_u32(&bar_full[s]), 0);
           const uint32_t a_dst = smem_base + s * C::STAGE_BYTES;
@@ -218,7 +217,6 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_con
           for (int ks = 0; ks < C::KSTEPS; ++ks) {
             const uint64_t ad = make_smem_desc(a_base + ks * a_kadv, a_lbo, C::SBO, C::LAYOUT);
             const uint64_t bd = make_smem_desc(b_base + ks * b_kadv, b_lbo, C::SBO, C::LAYOUT);
-            if ((g.xform_mode & 4) && ks > 0) continue;               // timing experiment: 1 MMA of 4
             umma2<2>(d_tmem, ad, bd, idesc, (i > 0 || ks > 0) ? 1u : 0u);
           }
           umma_commit2(mapa(smem_u32(&bar_empty[s]), 0));   // stage reusable in both CTAs
@@ -311,7 +309,7 @@ __device__ __forceinline__ void split_role_pair(const TcArgs& g, uint32_t smem_b
       const uint32_t ph = (it / STAGES) & 1u;
       if (!mbar_wait(smem_u32(&bar_full[s]), ph, abortp, g.wait_limit)) { ok = false; break; }
       const uint32_t raw = smem_base + s * C::STAGE_BYTES;
-      const int nvec = (g.xform_mode & 2) ? 0 : NVEC;
+      constexpr int nvec = NVEC;
 #pragma unroll 1
       for (int v0 = tt; v0 < nvec; v0 += 4 * NT) {
         uint32_t x[4][4];
@@ -410,7 +408,6 @@ gemm_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_
           const uint32_t ph = (it / STAGES) & 1u;
           if (!mbar_wait(smem_u32(&bar_empty[s]), ph ^ 1u, abortp, g.wait_limit)) { ok = false; break; }
           const uint32_t full = smem_u32(&bar_full[s]);
-          if (g.xform_mode & 8) { mbar_arrive(full); continue; }   // timing experiment: no loads
           mbar_expect_tx(full, C::RAW_BYTES);
           const uint32_t a_dst = smem_base + s * C::STAGE_BYTES;
           load_operand<PBM, C::BK, C::CH, C::MN_LBO>(a_dst, &tma_a, full, g.a_ld, t.mt * 2 * PBM + rank * PBM,
@@ -451,10 +448,6 @@ gemm_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_
               const uint64_t bd = make_smem_desc(b_base + ks * b_kadv, b_lbo, b_sbo, b_lay);
               const uint64_t ads = make_smem_desc(a_base + C::RAW_BYTES + ks * a_kadv, a_lbo, a_sbo, a_lay);
               const uint64_t bds = make_smem_desc(b_base + C::RAW_BYTES + ks * b_kadv, b_lbo, b_sbo, b_lay);
-              if (g.xform_mode & 4) {                                          // timing experiment
-                umma2<4>(d_tmem, ad, bd, idesc, (i > 0 || ks > 0) ? 1u : 0u);
-                continue;
-              }
               umma2<4>(d_tmem, ads, bd, idesc, (i > 0 || ks > 0) ? 1u : 0u);   // small * big
               umma2<4>(d_tmem, ad, bds, idesc, 1u);                            // big * small
               umma2<4>(d_tmem, ad, bd, idesc, 1u);                             // big * big

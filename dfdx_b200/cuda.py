@@ -40,7 +40,7 @@ def conv2d_out_dim(dim: int, kernel: int, stride: int, padding: int, dilation: i
 class Cuda:
     """One device ordinal, like `Cuda::try_build(ordinal, seed)` (tensor/cuda/device.rs:72-91)."""
 
-    def __init__(self, ordinal: int = 0, amp: bool = False):
+    def __init__(self, ordinal: int = 0, amp: bool = False, par_stream: bool = False):
         self.lib = _lib.load()
         if not torch.cuda.is_available():
             raise RuntimeError("dfdx_b200.Cuda needs a CUDA device (there is no CPU fallback)")
@@ -50,6 +50,9 @@ class Cuda:
         torch.cuda.set_device(ordinal)
         check(self.lib.b200_init(ordinal), "b200_init")
         self._workspace = None  # grow-only byte workspace (tensor/cuda/device.rs:108-122)
+        # dfdx's second stream, forked from the default one (tensor/cuda/device.rs:30,84): when present, the
+        # grad_lhs GEMM of every matmul backward runs on it beside the grad_rhs GEMM (matmul/cuda_kernel.rs:282-310)
+        self.par_stream = torch.cuda.Stream(self.device) if par_stream else None
 
     # -- plumbing ---------------------------------------------------------------------------------
     def _dtype(self, t: torch.Tensor) -> int:
@@ -61,6 +64,18 @@ class Cuda:
 
     def _stream(self):
         return torch.cuda.current_stream(self.device).cuda_stream
+
+    def _fork(self):
+        """`par_stream.wait_for_default()`: returns the handle to pass as `par_stream` (None without one)."""
+        if self.par_stream is None:
+            return None
+        self.par_stream.wait_stream(torch.cuda.current_stream(self.device))
+        return self.par_stream.cuda_stream
+
+    def _join(self) -> None:
+        """`dev.wait_for(par_stream)`."""
+        if self.par_stream is not None:
+            torch.cuda.current_stream(self.device).wait_stream(self.par_stream)
 
     def get_workspace(self, nbytes: int) -> torch.Tensor:
         if self._workspace is None or self._workspace.numel() < nbytes:
@@ -115,9 +130,11 @@ class Cuda:
 
     def matmat_backward(self, lhs, grad_lhs, rhs, grad_rhs, grad_out) -> None:
         (m, k), n = lhs.shape, rhs.shape[1]
+        par = self._fork()
         check(self.lib.b200_matmat_backward(self._dtype(lhs), m, k, n, lhs.data_ptr(), _st(lhs.stride()),
                                             _ptr(grad_lhs), rhs.data_ptr(), _st(rhs.stride()), _ptr(grad_rhs),
-                                            grad_out.data_ptr(), self._stream(), None), "b200_matmat_backward")
+                                            grad_out.data_ptr(), self._stream(), par), "b200_matmat_backward")
+        self._join()
 
     def matmat_br_forward(self, lhs, rhs):
         (b, m, k), n = lhs.shape, rhs.shape[1]
@@ -129,10 +146,12 @@ class Cuda:
 
     def matmat_br_backward(self, lhs, grad_lhs, rhs, grad_rhs, grad_out) -> None:
         (b, m, k), n = lhs.shape, rhs.shape[1]
+        par = self._fork()
         check(self.lib.b200_matmat_br_backward(self._dtype(lhs), b, m, k, n, lhs.data_ptr(), _st(lhs.stride()),
                                                _ptr(grad_lhs), rhs.data_ptr(), _st(rhs.stride()), _ptr(grad_rhs),
-                                               grad_out.data_ptr(), self._stream(), None),
+                                               grad_out.data_ptr(), self._stream(), par),
               "b200_matmat_br_backward")
+        self._join()
 
     def matmat_br_backward_overwrite(self, lhs, grad_lhs, rhs, grad_rhs, grad_out) -> None:
         """The first accumulation into fresh gradient buffers: they are written, need no zero fill and are not read."""
@@ -152,10 +171,12 @@ class Cuda:
 
     def matmat_batch3_backward(self, lhs, grad_lhs, rhs, grad_rhs, grad_out) -> None:
         (b, m, k), n = lhs.shape, rhs.shape[2]
+        par = self._fork()
         check(self.lib.b200_matmat_batch3_backward(self._dtype(lhs), b, m, k, n, lhs.data_ptr(),
                                                    _st(lhs.stride()), _ptr(grad_lhs), rhs.data_ptr(),
                                                    _st(rhs.stride()), _ptr(grad_rhs), grad_out.data_ptr(),
-                                                   self._stream(), None), "b200_matmat_batch3_backward")
+                                                   self._stream(), par), "b200_matmat_batch3_backward")
+        self._join()
 
     def matmat_batch4_forward(self, lhs, rhs):
         (b, s, m, k), n = lhs.shape, rhs.shape[3]
@@ -167,12 +188,15 @@ class Cuda:
 
     def matmat_batch4_backward(self, lhs, grad_lhs, rhs, grad_rhs, grad_out) -> None:
         (b, s, m, k), n = lhs.shape, rhs.shape[3]
+        par = self._fork()
         check(self.lib.b200_matmat_batch4_backward(self._dtype(lhs), b, s, m, k, n, lhs.data_ptr(),
                                                    _st(lhs.stride()), _ptr(grad_lhs), rhs.data_ptr(),
                                                    _st(rhs.stride()), _ptr(grad_rhs), grad_out.data_ptr(),
-                                                   self._stream(), None), "b200_matmat_batch4_backward")
+                                                   self._stream(), par), "b200_matmat_batch4_backward")
 
     # -- fused epilogues (API additions) -------------------------------------------------------------
+        self._join()
+
     def gemm_batch_fused(self, lhs, rhs, out, alpha=1.0, bias=None, relu=False) -> None:
         """out[b0,b1] = act(alpha * lhs[b0,b1] @ rhs[b0,b1] + bias) for rank-4 views (batch strides of lhs / rhs
         may be 0); one launch, `out` is only written."""

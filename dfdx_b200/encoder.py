@@ -379,8 +379,14 @@ class Trainer:
             torch.cuda.current_stream(self.dev.device).wait_stream(side)
             torch.cuda.synchronize(self.dev.device)
             graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph):
-                self._loss = self._step(self._x, self._t)
+            # The trainer replays its graph on the one stream that carries all of its other work on this library, so
+            # the f16 GEMMs inside the capture may keep their split-K (see b200_set_capture_split_k).
+            self.dev.lib.b200_set_capture_split_k(1)
+            try:
+                with torch.cuda.graph(graph):
+                    self._loss = self._step(self._x, self._t)
+            finally:
+                self.dev.lib.b200_set_capture_split_k(0)
             self.graph = graph
             return True
         except Exception as exc:  # noqa: BLE001 - any capture failure means: stay eager

@@ -111,9 +111,8 @@ int b200_device_status(void* stream);
 int b200_set_path(int path);
 /* f32 tensor-core operand split (testing / profiling).  Every staged f32 x is used in place as the `big`
  * tf32 operand (the tensor core reads its top 19 bits) and small = x - trunc_tf32(x) is written beside it.
- * Bit 0: 1 (default) stores small as computed, 0 rounds it to tf32 first (cvt.rna).  Bits 1..3 are timing
- * experiments that give WRONG results: skip the split work (2), issue a third of the MMAs (4), skip the TMA
- * loads (8). */
+ * mode 1 (default) stores small as computed, 0 rounds it to tf32 first (cvt.rna).  Both stay inside the f32
+ * tolerance; any other value returns B200_ERR_UNSUPPORTED. */
 int b200_set_tf32_split_mode(int mode);
 /* Tensor-core tile width override (testing / profiling): 64, 128 or 256 output columns per CTA tile;
  * 0 (default) picks the widest tile that still gives every SM work. */
@@ -143,6 +142,19 @@ int b200_set_conv_lowering(int grad_img_mode, size_t group_bytes);
  * stream-K decomposition (the (tile, k-block) space cut into one equal contiguous range per SM; tiles cut by a
  * range boundary are summed atomically), which the planner never picks on its own. */
 int b200_set_split_k(int mode);
+/* The split-K of an f16 GEMM keeps its partial sums in the one f32 scratch the device owns; uses on different
+ * streams are ordered by an event recorded when the GEMM is enqueued.  A stream capture cannot take part in that
+ * ordering (a replay neither waits on nor records the event), so by default (0) a GEMM enqueued on a capturing
+ * stream runs unsplit.  1: such GEMMs may split; the caller then guarantees that every replay of its graphs is
+ * ordered against all other work this library does on the device (one stream for everything is enough). */
+int b200_set_capture_split_k(int on);
+/* Clock budget of the bounded device-side waits of the tensor-core GEMM kernels (testing).  Every wait on a
+ * shared-memory barrier inside those kernels gives up after a budget of SM clock cycles; the kernel then drains,
+ * frees its tensor memory, writes B200_ERR_DEVICE_TIMEOUT to the device status word (b200_device_status) and
+ * returns, leaving the context usable; its output is undefined.  0 (default) sizes the budget by the problem
+ * (hundreds of milliseconds); a small positive value makes a healthy kernel give up, which is how the tests
+ * exercise that path.  Negative values return B200_ERR_UNSUPPORTED. */
+int b200_set_wait_limit(long long cycles);
 /* Number of kernel launches this library has enqueued since load (all threads). */
 uint64_t b200_launch_count(void);
 /* Of those, launches of tcgen05 tensor-core kernels. */
@@ -176,9 +188,11 @@ int b200_gemm_batch(int dtype, size_t batch, size_t m, size_t k, size_t n,
 /* `MatMatKernel::forward/backward for Cuda` (cuda_kernel.rs:244-312): (M,K)x(K,N).
  * forward writes a contiguous (M,N) `out`.  backward accumulates grad_lhs += grad_out * rhs^T
  * through lhs_strides and grad_rhs += lhs^T * grad_out through rhs_strides; grad_out is a
- * contiguous (M,N).  Either gradient pointer may be NULL to skip it.  The reference runs the two
- * gradient GEMMs on `par_stream` and the default stream; here both are enqueued on `stream`
- * (`par_stream` is accepted for signature compatibility and may be NULL). */
+ * contiguous (M,N).  Either gradient pointer may be NULL to skip it.  As in the reference
+ * (cuda_kernel.rs:282-310) the grad_lhs GEMM is enqueued on `par_stream` and the grad_rhs GEMM on `stream`, and the
+ * caller joins the two streams before and after the call, as dfdx does with `par_stream.wait_for_default()` and
+ * `dev.wait_for(par_stream)`.  A NULL `par_stream` means there is no second stream: both GEMMs go to `stream`.
+ * The same holds for the other three `*_backward` matmul entry points below. */
 int b200_matmat_forward(int dtype, size_t m, size_t k, size_t n,
                         const void* lhs, const size_t lhs_strides[2],
                         const void* rhs, const size_t rhs_strides[2],
@@ -333,7 +347,9 @@ int b200_bias_grad(int dtype, size_t rows, size_t cols, const void* grad_out, si
 
 /* Bytes of caller-provided scratch the conv2d entry points need; `backward` != 0 selects the
  * backward pass.  Plays the role of the sizes handed to `Cuda::get_workspace`
- * (conv2d/cuda_kernel.rs:91-95,156-168; tensor/cuda/device.rs:108-122). */
+ * (conv2d/cuda_kernel.rs:91-95,156-168; tensor/cuda/device.rs:108-122).  Returns SIZE_MAX when the element
+ * counts of the geometry do not fit a size_t; the forward / backward entry points then return B200_ERR_LIMIT
+ * (the same holds for the conv1d and convtrans2d variants). */
 size_t b200_conv2d_workspace_bytes(int dtype, const b200_conv2d_op* op, int backward);
 
 /* `Conv2DKernel::forward for Cuda` (conv2d/cuda_kernel.rs:80-144 + conv2d.cu:18-52):
@@ -346,7 +362,10 @@ int b200_conv2d_forward(int dtype, const b200_conv2d_op* op,
 
 /* `Conv2DKernel::backward for Cuda` (conv2d/cuda_kernel.rs:146-281 + conv2d.cu:54-168):
  * grad_img += conv_transpose(grad_out, filters); grad_filters (addressed through
- * filters_strides) += sum_b img_b (x) grad_out_b.  img, grad_img contiguous (B,C,H,W). */
+ * filters_strides) += sum_b img_b (x) grad_out_b.  img, grad_img contiguous (B,C,H,W).  Both gradients share the
+ * one workspace, so all of the pass is enqueued on `stream`; `par_stream` (on which the reference runs its grad_img
+ * half, :171-227) is accepted for signature compatibility and unused, here and in the conv1d / convtrans2d
+ * backward entry points. */
 int b200_conv2d_backward(int dtype, const b200_conv2d_op* op,
                          const void* img, void* grad_img,
                          const void* filters, const size_t filters_strides[4], void* grad_filters,
@@ -398,12 +417,15 @@ int b200_convtrans2d_backward(int dtype, const b200_convtrans2d_op* op,
  * because they cannot allocate device memory where they run: the GPU's memory is already owned by their
  * own arena, a cudaMalloc (which synchronises the device) is not acceptable in their loop, or they are
  * handed nothing but input and output buffers.  The im2col patch buffer is a fixed
- * B200_CONV2D_NOALLOC_SCRATCH_BYTES array inside the library image (held on every GPU that loads the
- * library until the process exits); the call allocates and frees nothing.
+ * B200_CONV2D_NOALLOC_SCRATCH_BYTES array inside the library image; it becomes resident on a GPU when b200_init
+ * runs for that GPU (which looks up the array's device address and thereby loads the module that holds it) and
+ * stays until the process exits.  The call itself allocates and frees nothing, explicitly or implicitly: free
+ * device memory is the same before and after it.
  *   - Limit: b200_conv2d_workspace_bytes(dtype, op, 0) must not exceed the capacity above, otherwise
  *     B200_ERR_LIMIT is returned and nothing is launched (use b200_conv2d_forward with a workspace).
- *   - b200_init(ordinal) must have been called for the current device.  The first call on each device also
- *     looks up the array's device address; make that first call before starting any stream capture.
+ *   - b200_init(ordinal) must have been called for the current device; it performs the one-time set-up (the
+ *     address lookup above), so call it before starting any stream capture and before handing the remaining
+ *     device memory to an arena.
  *   - All calls on a device share the one array.  Every call overwrites all of the part it uses, so earlier
  *     contents never leak into a result; but two calls whose GPU work can overlap (different streams, or
  *     different threads without ordering) race on it — serialise them on one stream or with events.

@@ -98,3 +98,29 @@ def test_path_selector_and_counters(lib):
     assert lib.b200_set_path(_lib.PATH_AUTO) == 0
     assert lib.b200_set_path(7) == _lib.ERR_UNSUPPORTED
     assert lib.b200_launch_count() >= lib.b200_tensor_launch_count()
+
+
+def test_conv_workspace_overflow_is_reported(lib):
+    # extents whose product wraps a size_t: SIZE_MAX from the size query, ERR_LIMIT from the entry points
+    big = 1 << 31
+    op = _lib.Conv2DOp(kernel=3, stride=1, padding=1, dilation=1, groups=1, batch=big, chan_in=big, chan_out=1,
+                       h_in=4, h_out=4, w_in=4, w_out=4)
+    size_max = (1 << (8 * C.sizeof(C.c_size_t))) - 1
+    assert lib.b200_conv2d_workspace_bytes(_lib.F32, C.byref(op), 0) == size_max
+    assert lib.b200_conv2d_workspace_bytes(_lib.F32, C.byref(op), 1) == size_max
+    p = 0x1000
+    one = _lib.strides([1, 1, 1, 1])
+    assert lib.b200_conv2d_forward(_lib.F32, C.byref(op), p, one, p, p, p, size_max, None) == _lib.ERR_LIMIT
+    assert lib.b200_conv2d_forward_noalloc(_lib.F32, C.byref(op), p, one, p, p, None) == _lib.ERR_LIMIT
+    assert lib.b200_conv2d_backward(_lib.F32, C.byref(op), p, p, p, one, p, p, p, size_max, None, None) == _lib.ERR_LIMIT
+
+
+def test_testing_hooks_reject_unknown_modes(lib):
+    # the f32 operand-split hook has two modes, both correct; nothing else is accepted
+    for mode in range(2, 16):
+        assert lib.b200_set_tf32_split_mode(mode) == _lib.ERR_UNSUPPORTED
+    assert lib.b200_set_tf32_split_mode(-1) == _lib.ERR_UNSUPPORTED
+    assert lib.b200_set_tf32_split_mode(0) == 0
+    assert lib.b200_set_tf32_split_mode(1) == 0
+    assert lib.b200_set_capture_split_k(1) == 0
+    assert lib.b200_set_capture_split_k(0) == 0

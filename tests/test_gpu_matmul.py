@@ -460,3 +460,92 @@ def test_config3_attention_matmuls_f16(cuda_dev, oracle):
     s2, _ = dev.matmul(q2, k2)
     dev.synchronize()
     assert torch.equal(s2, s)
+
+
+# --------------------------------------------------------------------------------- streams, capture, bounded waits
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+def test_backward_on_two_streams(cuda_dev, oracle, dtype):
+    """The backward entry points with a second stream, as dfdx drives them (matmul/cuda_kernel.rs:282-310):
+    grad_lhs on `par_stream`, grad_rhs on the default stream, joins on the caller's side."""
+    cuda_dev.par_stream = torch.cuda.Stream(cuda_dev.device)
+    try:
+        _trait_case(cuda_dev, oracle, dtype, (264, 520), (520, 392), seed=21, scale=0.3)                    # MatMat
+        _trait_case(cuda_dev, oracle, dtype, (6, 48, 64), (136, 64), b_perm=(1, 0), seed=22, scale=0.3)     # MatMatBr
+        _trait_case(cuda_dev, oracle, dtype, (5, 40, 72), (5, 72, 136), seed=23, scale=0.3)                 # Batch3
+        _trait_case(cuda_dev, oracle, dtype, (2, 40, 3, 64), (2, 48, 3, 64), a_perm=(0, 2, 1, 3), b_perm=(0, 2, 3, 1),
+                    seed=24, scale=0.3)                                                                     # Batch4
+        # long K, few tiles: both gradient GEMMs of the f16 case take split-K and so share the device's scratch
+        _trait_case(cuda_dev, oracle, dtype, (128, 4096), (4096, 256), seed=25, scale=0.1)
+    finally:
+        cuda_dev.par_stream = None
+
+
+def test_bounded_wait_runs_out_and_kernel_returns(cuda_dev, oracle):
+    """A device-side wait that runs out: with a clock budget far below what a long-K tile needs, the kernel gives
+    up, drains, frees its tensor memory and returns; the status word reports it once, and the next launch on the
+    same device is healthy."""
+    dev = cuda_dev
+    g = gen(31)
+    a = torch.randn(128, 16384, generator=g).to(dev.device)
+    b = torch.randn(16384, 256, generator=g).to(dev.device)
+    c = torch.zeros(128, 256, device=dev.device)
+    dev.set_path(dfdx_b200.PATH_TENSOR)
+    assert dev.lib.b200_set_split_k(1) == 0                 # one unit walks the whole K: far longer than the budget
+    try:
+        assert dev.lib.b200_set_wait_limit(2000) == 0
+        dev.gemm((128, 16384, 256), a, a.stride(), b, b.stride(), 0.0, c, c.stride())
+        torch.cuda.synchronize(dev.device)                  # the kernel came back
+        assert dev.device_status() == dfdx_b200._lib.ERR_DEVICE_TIMEOUT
+        assert dev.device_status() == 0                     # reading the status clears it
+    finally:
+        dev.lib.b200_set_wait_limit(0)
+        dev.lib.b200_set_split_k(0)
+    try:
+        check_gemm(dev, oracle, 128, 16384, 256, "r", "r", "r", 0, torch.float32, pad=0, seed=32)
+        check_gemm(dev, oracle, 200, 264, 136, "r", "c", "r", 1, torch.float16, pad=8, seed=33)
+    finally:
+        dev.set_path(dfdx_b200.PATH_AUTO)
+    assert dev.device_status() == 0
+
+
+def test_captured_split_k_f16_next_to_an_eager_one(cuda_dev, oracle):
+    """An f16 GEMM that takes split-K when run eagerly is recorded into a CUDA graph (where it runs unsplit, because
+    a replay cannot take part in the event ordering of the device's one split-K scratch) and replayed on one stream
+    while an eager split-K GEMM runs on another; both must match the oracle."""
+    dev = cuda_dev
+    g = gen(41)
+    m, k, n = 128, 8192, 256
+    a1 = (torch.randn(m, k, generator=g) * 0.1).half().to(dev.device)
+    b1 = (torch.randn(k, n, generator=g) * 0.1).half().to(dev.device)
+    a2 = (torch.randn(m, k, generator=g) * 0.1).half().to(dev.device)
+    b2 = (torch.randn(k, n, generator=g) * 0.1).half().to(dev.device)
+    c1 = torch.zeros(m, n, dtype=torch.float16, device=dev.device)
+    c2 = torch.zeros(m, n, dtype=torch.float16, device=dev.device)
+    want1, _ = oracle.matmul(a1.cpu(), b1.cpu())
+    want2, _ = oracle.matmul(a2.cpu(), b2.cpu())
+    dev.set_path(dfdx_b200.PATH_TENSOR)
+    try:
+        l0 = dev.lib.b200_launch_count()
+        dev.gemm((m, k, n), a1, a1.stride(), b1, b1.stride(), 0.0, c1, c1.stride())        # eager warm-up: split-K
+        assert dev.lib.b200_launch_count() - l0 == 2, "expected the split-K pair of launches (GEMM + finalize)"
+        torch.cuda.synchronize(dev.device)
+        sa, sb = torch.cuda.Stream(dev.device), torch.cuda.Stream(dev.device)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(sa):
+            l0 = dev.lib.b200_launch_count()
+            with torch.cuda.graph(graph, stream=sa):
+                dev.gemm((m, k, n), a1, a1.stride(), b1, b1.stride(), 0.0, c1, c1.stride())
+            assert dev.lib.b200_launch_count() - l0 == 1, "a captured GEMM must run unsplit"
+        c1.fill_(float("nan"))
+        torch.cuda.synchronize(dev.device)
+        for _ in range(4):
+            with torch.cuda.stream(sa):
+                graph.replay()
+            with torch.cuda.stream(sb):
+                dev.gemm((m, k, n), a2, a2.stride(), b2, b2.stride(), 0.0, c2, c2.stride())
+        torch.cuda.synchronize(dev.device)
+    finally:
+        dev.set_path(dfdx_b200.PATH_AUTO)
+    assert frob(oracle, c1, want1) <= FROB_TOL[torch.float16]
+    assert frob(oracle, c2, want2) <= FROB_TOL[torch.float16]
+    assert dev.device_status() == 0
