@@ -36,6 +36,8 @@ void conv_set_lowering(int grad_img_mode, size_t group_bytes);
 void tc_set_split_mode(int mode);
 void tc_set_capture_split(int on);
 void tc_set_wait_limit(long long cycles);
+void tc_set_max_ctas(int n);
+int tc_wait_selftest(long long limit, long long* cycles, cudaStream_t stream);
 
 namespace {
 
@@ -229,11 +231,24 @@ int b200_set_capture_split_k(int on) {
   return B200_OK;
 }
 
+/* Upper bound on the grids of the persistent tensor-core GEMM kernels (0 = one CTA per SM). */
+int b200_set_max_ctas(int n) {
+  if (n < 0) return B200_ERR_UNSUPPORTED;
+  tc_set_max_ctas(n);
+  return B200_OK;
+}
+
 /* Testing hook: clock budget of the device-side waits of the tensor-core GEMM kernels (0 = by problem size). */
 int b200_set_wait_limit(long long cycles) {
   if (cycles < 0) return B200_ERR_UNSUPPORTED;
   tc_set_wait_limit(cycles);
   return B200_OK;
+}
+
+/* Testing hook: a one-CTA kernel whose only wait can never be satisfied (see the header). */
+int b200_selftest_bounded_wait(long long limit_cycles, long long* waited_cycles, void* stream) {
+  if (limit_cycles < 0) return B200_ERR_UNSUPPORTED;
+  return tc_wait_selftest(limit_cycles, waited_cycles, (cudaStream_t)stream);
 }
 
 uint64_t b200_launch_count(void) { return g_launches.load(); }

@@ -579,6 +579,29 @@ __global__ void __launch_bounds__(256) splitk_finalize_f16_kernel(const float* _
   }
 }
 
+// Self-test of the bounded wait: one thread waits on a barrier that nothing ever completes.  The wait must give up
+// after its clock budget, raise the abort flag and let the CTA run the same teardown as the GEMM kernels (status
+// word = B200_ERR_DEVICE_TIMEOUT).  The cycles the wait took are left in g_selftest_cycles; with a budget of 0 that
+// is the time the polls themselves take (a failed try_wait suspends the thread for a hardware-defined while).
+__device__ long long g_selftest_cycles;
+__global__ void __launch_bounds__(128) wait_selftest_kernel(long long limit, int* status) {
+  __shared__ __align__(8) uint64_t bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    mbar_init(smem_u32(&bar), 1);
+    abort_flag = 0;
+    fence_mbar_init();
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const long long t0 = clock64();
+    mbar_wait(smem_u32(&bar), 0u, &abort_flag, limit);
+    g_selftest_cycles = clock64() - t0;
+  }
+  __syncthreads();
+  teardown(abort_flag, status);
+}
+
 // ---------------------------------------------------------------------------------------------
 // Host side: operand classification, tensor maps, launch
 // ---------------------------------------------------------------------------------------------
@@ -752,6 +775,7 @@ std::mutex g_split_mutex;
 std::atomic<int> g_split_mode{0}; // split-K of the f32 kernel: 0 = choose, 1 = never, n >= 2 = force n slices (testing)
 std::atomic<int> g_store_mode{0}; // 0 = choose, 1 = row stores only, 2 = column stores where possible
 std::atomic<int> g_capture_split{0}; // 1 = f16 split-K also on capturing streams (the caller orders graph replays)
+std::atomic<int> g_max_ctas{0};   // upper bound on the persistent grids; 0 = one CTA per SM (b200_set_max_ctas)
 std::atomic<long long> g_wait_limit{0}; // clock budget of every device-side wait; 0 = by problem size (testing)
 std::atomic<int> g_pair_mode{1};  // 0 = choose by problem shape, 1 = never use CTA pairs (default: not faster yet), 2 = always (n > 128)
 
@@ -761,6 +785,13 @@ struct Launch {
   alignas(64) CUtensorMap ma, mb, mc;
   TcArgs g;
 };
+
+// SMs the persistent grids may occupy: all of them, unless the caller keeps some free for kernels that have to
+// run beside a GEMM (a collective on another stream).
+int grid_sms(const DeviceState* ds) {
+  const int all = ds ? ds->sm_count : 148, cap = g_max_ctas.load();
+  return (cap > 0 && cap < all) ? cap : all;
+}
 
 int build_launch(Launch& L, const Plan& pl, int esize, int tm, int tn, int bmc, int bnc, int bk, int ch) {
   const GemmProblem& p = pl.p;
@@ -858,7 +889,7 @@ int launch_cfg(const Plan& pl, cudaStream_t stream, Kernel kernel, int ksplit) {
     // atomically (beta = 0 outputs are zeroed first)
     const GemmProblem& p = pl.p;
     const long long all = g.total_tiles * (long long)total_kb;
-    const long long grid = ds->sm_count;
+    const long long grid = grid_sms(ds);
     g.streamk = 1;
     g.sk_per_cta = (all + grid - 1) / grid;
     const long long per_cta_tiles = (g.sk_per_cta + total_kb - 1) / total_kb + 1;      // tiles a range can touch
@@ -901,7 +932,7 @@ int launch_cfg(const Plan& pl, cudaStream_t stream, Kernel kernel, int ksplit) {
         if ((rc = note_cuda_error(cudaMemsetAsync(ds->split_scratch, 0, need, stream), "cudaMemsetAsync(split-K)"))) return rc;
         g.kb_per_slice = kb_per; g.ksplit = slices; g.total_units = g.total_tiles * slices;
         g.split_out = ds->split_scratch; g.split_ld = lds;
-        const long long grid2 = g.total_units < ds->sm_count ? g.total_units : ds->sm_count;
+        const long long grid2 = g.total_units < grid_sms(ds) ? g.total_units : grid_sms(ds);
         L.g.c_tma = 0;                                       // partial sums go to the scratch, not to C
         kernel<<<(unsigned)grid2, C::THREADS, C::SMEM_BYTES, stream>>>(L.ma, L.mb, L.mc, L.g);
         count_launch(true);
@@ -921,7 +952,7 @@ int launch_cfg(const Plan& pl, cudaStream_t stream, Kernel kernel, int ksplit) {
       }
     }
   }
-  const long long grid = g.total_units < ds->sm_count ? g.total_units : ds->sm_count;
+  const long long grid = g.total_units < grid_sms(ds) ? g.total_units : grid_sms(ds);
   if (grid <= 0) return B200_OK;
   kernel<<<(unsigned)grid, C::THREADS, C::SMEM_BYTES, stream>>>(L.ma, L.mb, L.mc, L.g);
   count_launch(true);
@@ -934,7 +965,7 @@ int launch_pair_plan(const Plan& pl, int esize, cudaStream_t stream) {
   const int tm = pair_tile_m(), tn = pair_tile_n();
   const int st = build_launch(L, pl, esize, tm, tn, tm / 2, tn / 2, pair_block_k(esize), pair_chunk(esize));
   if (st) return st;
-  return launch_pair(esize, L.ma, L.mb, L.g, device_state()->sm_count, stream);
+  return launch_pair(esize, L.ma, L.mb, L.g, grid_sms(device_state()), stream);
 }
 
 template <int ESIZE, int BN>
@@ -949,7 +980,7 @@ int launch_bn(const Plan& pl, cudaStream_t stream, int ksplit) {
 double choose_tile(const Plan& pl, int esize, int* bn_out) {
   const GemmProblem& p = pl.p;
   DeviceState* ds = device_state();
-  const int sms = ds ? ds->sm_count : 148;
+  const int sms = grid_sms(ds);
   auto tiles = [&](int bn) { return ((p.m + BM - 1) / BM) * ((p.n + bn - 1) / bn) * p.b0 * p.b1; };
   const double w256 = 1.0, w128 = (esize == 4) ? 0.75 : 0.87, w64 = (esize == 4) ? 0.55 : 0.70;
   auto waves = [&](int bn_) { return (double)((tiles(bn_) + sms - 1) / sms); };
@@ -965,7 +996,7 @@ template <int ESIZE>
 int launch_es(const Plan& pl, cudaStream_t stream) {
   const GemmProblem& p = pl.p;
   DeviceState* ds = device_state();
-  const int sms = ds ? ds->sm_count : 148;
+  const int sms = grid_sms(ds);
   int bn = 64;
   const double best = choose_tile(pl, ESIZE, &bn);
   const int g_force_bn = b200::g_force_bn.load(), g_pair_mode = b200::g_pair_mode.load(),
@@ -1059,12 +1090,27 @@ int launch_gemm_tc(const GemmProblem& p, cudaStream_t stream) {
   return launch_es<2>(*pl, stream);
 }
 
+int tc_wait_selftest(long long limit, long long* cycles, cudaStream_t stream) {
+  DeviceState* ds = device_state();
+  if (!ds) return note_cuda_error(cudaErrorInitializationError, "b200_init not called on this device");
+  wait_selftest_kernel<<<1, 128, 0, stream>>>(limit, ds->status);
+  count_launch(false);
+  int rc = note_cuda_error(cudaGetLastError(), "wait self-test launch");
+  if (rc) return rc;
+  if ((rc = note_cuda_error(cudaStreamSynchronize(stream), "cudaStreamSynchronize(wait self-test)"))) return rc;
+  long long v = 0;
+  if ((rc = note_cuda_error(cudaMemcpyFromSymbol(&v, g_selftest_cycles, sizeof(v)), "cudaMemcpyFromSymbol"))) return rc;
+  if (cycles) *cycles = v;
+  return B200_OK;
+}
+
 void tc_set_xform_mode(int mode) { g_xform_mode = mode; }
 void tc_set_tile_n(int bn) { g_force_bn = bn; }
 void tc_set_mn_box5(int on) { g_mn_box5 = on; }
 void tc_set_pair_mode(int mode) { g_pair_mode = mode; }
 void tc_set_store_mode(int mode) { g_store_mode = mode; }
 void tc_set_split_mode(int mode) { g_split_mode = mode; }
+void tc_set_max_ctas(int n) { g_max_ctas = n; }
 void tc_set_wait_limit(long long cycles) { g_wait_limit = cycles; }
 void tc_set_capture_split(int on) { g_capture_split = on ? 1 : 0; }
 

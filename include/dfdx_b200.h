@@ -148,6 +148,12 @@ int b200_set_split_k(int mode);
  * stream runs unsplit.  1: such GEMMs may split; the caller then guarantees that every replay of its graphs is
  * ordered against all other work this library does on the device (one stream for everything is enough). */
 int b200_set_capture_split_k(int on);
+/* The tensor-core GEMM kernels are persistent: their grid is one CTA per SM (or one per work unit when there are
+ * fewer), and each CTA takes nearly all of an SM's shared memory, so a kernel enqueued on another stream while a
+ * GEMM runs finds no SM to start on until the GEMM ends.  n > 0 caps the grids at n CTAs, leaving the other SMs
+ * to such kernels (a NCCL all-reduce of one gradient while the GEMM of the next runs); 0 (default) restores one
+ * CTA per SM.  Process-wide; takes effect from the next launch.  Negative values return B200_ERR_UNSUPPORTED. */
+int b200_set_max_ctas(int n);
 /* Clock budget of the bounded device-side waits of the tensor-core GEMM kernels (testing).  Every wait on a
  * shared-memory barrier inside those kernels gives up after a budget of SM clock cycles; the kernel then drains,
  * frees its tensor memory, writes B200_ERR_DEVICE_TIMEOUT to the device status word (b200_device_status) and
@@ -155,6 +161,13 @@ int b200_set_capture_split_k(int on);
  * (hundreds of milliseconds); a small positive value makes a healthy kernel give up, which is how the tests
  * exercise that path.  Negative values return B200_ERR_UNSUPPORTED. */
 int b200_set_wait_limit(long long cycles);
+/* Self-test of that mechanism (testing): launches one small CTA in which a thread waits, with the kernels' own
+ * bounded wait and a budget of `limit_cycles`, on a barrier that nothing ever completes; the wait gives up, the CTA
+ * runs the kernels' teardown and sets the status word, so b200_device_status then reports
+ * B200_ERR_DEVICE_TIMEOUT once.  Synchronises `stream`.  `waited_cycles` (host pointer, may be NULL) receives the SM
+ * clock cycles the wait lasted: a failed poll suspends the thread for a hardware-defined time, so this exceeds the
+ * budget by up to 64 such polls. */
+int b200_selftest_bounded_wait(long long limit_cycles, long long* waited_cycles, void* stream);
 /* Number of kernel launches this library has enqueued since load (all threads). */
 uint64_t b200_launch_count(void);
 /* Of those, launches of tcgen05 tensor-core kernels. */

@@ -50,6 +50,29 @@ def _worker(rank, world, port, out):
     ok = torch.allclose(gw, gw_full, atol=1e-12)
     ok &= torch.allclose(gather_batch(y), y_full, atol=1e-12)
     ok &= torch.allclose(gather_batch(gx), gx_full, atol=1e-12)
+    # one large matmul cut along the rows of its left operand (strong scaling of `MatMatKernel`): the shared
+    # rhs's gradient is the all-reduced sum, through the overlapped reducer and a flat bucket of two gradients
+    from dfdx_b200.parallel import FlatBucket, OverlappedReducer, shard_rows
+    a = torch.randn(10, 4, generator=g, dtype=torch.float64)
+    b = torch.randn(4, 3, generator=g, dtype=torch.float64)
+    dc = torch.randn(10, 3, generator=g, dtype=torch.float64)
+    c_full, bwd2 = oracle.matmul(a, b)
+    ga_full, gb_full = bwd2(dc)
+    a_r, dc_r = shard_rows(a, world, rank, align=4), shard_rows(dc, world, rank, align=4)
+    c_r, bwd_r = oracle.matmul(a_r.contiguous(), b)
+    ga_r, gb_r = bwd_r(dc_r.contiguous())
+    bucket = FlatBucket([gb_r.shape, gw.shape], torch.float64, "cpu")
+    bucket.views[0].copy_(gb_r)
+    bucket.views[1].copy_(gw / world)             # already summed above: every rank holds the same values
+    red = OverlappedReducer(None)
+    red.start([bucket.flat])
+    red.finish()
+    ok &= torch.allclose(bucket.views[0], gb_full, atol=1e-12)
+    ok &= torch.allclose(bucket.views[1], gw_full, atol=1e-12)
+    rows = [shard_rows(torch.arange(10).view(10, 1), world, r, align=4).numel() for r in range(world)]
+    ok &= sum(rows) == 10 and rows[0] % 4 == 0
+    ok &= torch.allclose(c_r, shard_rows(c_full, world, rank, align=4), atol=1e-12)
+    ok &= torch.allclose(ga_r, shard_rows(ga_full, world, rank, align=4), atol=1e-12)
     out[rank] = bool(ok)
     dist.destroy_process_group()
 
