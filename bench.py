@@ -484,7 +484,7 @@ def run_other(h, name, steps, warmup):
         "workload": desc, "dtype": kind, "tflops": round(h.world * flops / (per_step * 1e-3) / 1e12, 3),
         "ms_per_step": round(per_step, 4), "steps": steps, "gpu_launches": r["launches"],
         "tensor_core_launches": r["tc_launches"], "l2": "256 MiB flush buffer written between timed steps",
-        "roofline": h.roofline(bound, kind, flops, algo_bytes, per_step, per_step * 1e-3),
+        "roofline": h.roofline(bound, kind, flops, algo_bytes, per_step, r["ms"] * 1e-3),
     }
 
 
@@ -508,7 +508,7 @@ def run_transformer(h, args, steps, warmup):
 
     def step_e2e():
         xd, td = x_h.to(device, non_blocking=True), t_h.to(device, non_blocking=True)
-        losses.append(float(trainer.step(xd, td)))          # the loss crosses back to the host every step
+        losses.append(float(trainer.step(xd, td).detach()))          # the loss crosses back to the host every step
 
     r = h.region(lambda: trainer.step(x, t), steps, max(warmup, 3))
     h.check_status("the encoder step")

@@ -67,6 +67,8 @@ int note_cuda_error(cudaError_t e, const char* where) {
   return B200_ERR_CUDA;
 }
 
+int current_path() { return g_path.load(); }
+
 void count_launch(bool tensor) {
   g_launches.fetch_add(1, std::memory_order_relaxed);
   if (tensor) g_tc_launches.fetch_add(1, std::memory_order_relaxed);
@@ -204,7 +206,7 @@ int b200_set_cta_pair_mode(int mode) {
 
 /* Testing hook: lowering of the convolution data gradient (see the header). */
 int b200_set_conv_lowering(int grad_img_mode, size_t group_bytes) {
-  if (grad_img_mode < 0 || grad_img_mode > 1) return B200_ERR_UNSUPPORTED;
+  if (grad_img_mode < 0 || grad_img_mode > 2) return B200_ERR_UNSUPPORTED;
   conv_set_lowering(grad_img_mode, group_bytes);
   return B200_OK;
 }

@@ -94,5 +94,40 @@ int column_sum(int dtype, int64_t rows, int64_t cols, const void* g, int64_t ld,
 
 // Lowers one problem to a kernel family according to b200_set_path and eligibility.
 int run_gemm(const GemmProblem& p, cudaStream_t stream);
+int current_path();                          // b200_path in force
+
+// Implicit-GEMM convolution on the f32 (3xTF32) tensor-core kernel (gemm_tc.cu): the im2col gather is done by the
+// TMA loads from a channels-last copy of the image, no patch buffer exists.  Unit stride only.
+//
+// ConvImplicit: out[b, g*m + i, y, x] (beta) += sum_{tap=(k1,k2)} sum_c filt[g][i][tap][c] *
+//                                              img_cl[b, y + h0 + k1*dh, x + w0 + k2*dw, g*cpad + c]
+// with zeros outside the image.  The forward pass uses (h0, dh, w0, dw) = (-pad, dil, -pad, dil) on the input image;
+// the data gradient is the same sum over grad_out with (pad, -dil, pad, -dil) and the filters' roles exchanged.
+struct ConvImplicit {
+  const float* img_cl = nullptr;             // (batch, h_img, w_img, groups * cpad), channels padded with zeros
+  int64_t batch = 0, h_img = 0, w_img = 0, groups = 1, cpad = 0;   // cpad % 16 == 0
+  const float* filt = nullptr;               // (groups, m, kh*kw, cpad)
+  int64_t m = 0;                             // output channels per group
+  int kh = 1, kw = 1, h0 = 0, dh = 1, w0 = 0, dw = 1;
+  float* out = nullptr;                      // (batch, groups * m, h_out, w_out) contiguous
+  int64_t h_out = 0, w_out = 0;              // w_out <= 256
+  int beta = 0;
+};
+bool conv_implicit_ok(const ConvImplicit& c);
+int launch_conv_implicit(const ConvImplicit& c, cudaStream_t stream);
+
+// Filter gradient of the same convolution for one group:
+//   out[i][tap][c] += sum_b sum_{y,x} gout[b, i, y, x] * img_cl[b, y + h0 + k1*dh, x + w0 + k2*dw, c]
+// `out` (m, kh*kw, cpad) must hold zeros (or a running sum): the K slices of the reduction add into it atomically.
+struct ConvImplicitWgrad {
+  const float* gout = nullptr;               // this group's (m, h_out, w_out) planes; image stride gout_bs elements
+  int64_t gout_bs = 0, m = 0, h_out = 0, w_out = 0;   // w_out % 4 == 0
+  const float* img_cl = nullptr;             // this group's first channel of (batch, h_img, w_img, c_total)
+  int64_t batch = 0, h_img = 0, w_img = 0, c_total = 0, cpad = 0;   // cpad % 32 == 0
+  int kh = 1, kw = 1, h0 = 0, dh = 1, w0 = 0, dw = 1;
+  float* out = nullptr;
+};
+bool conv_implicit_wgrad_ok(const ConvImplicitWgrad& c);
+int launch_conv_implicit_wgrad(const ConvImplicitWgrad& c, cudaStream_t stream);
 
 }  // namespace b200

@@ -9,6 +9,7 @@
 #include <atomic>
 #include <mutex>
 #include <initializer_list>
+#include <type_traits>
 
 namespace b200 {
 namespace {
@@ -357,6 +358,199 @@ constexpr size_t CONV_GROUP_BYTES_DEFAULT = ~(size_t)0;
 std::atomic<int> g_conv_grad_img_mode{0};
 std::atomic<size_t> g_conv_group_bytes{CONV_GROUP_BYTES_DEFAULT};
 
+// ---- implicit-GEMM path (f32, unit stride): no patch buffer ------------------------------------------
+// The tensor-core kernel gathers the patches itself, by TMA, from a channels-last copy of the image (a TMA box
+// must start on a 16-byte boundary, which a one-pixel shift along the rows of an NCHW image is not; with the
+// channels innermost every shift is a whole number of pixels = whole vectors).  What is left of the lowering is
+// this layout change (one read and one write of the image instead of K*K writes and reads of it) and a re-layout
+// of the filters.
+
+// (B, C, H, W) through strides -> (B, H, W, G*cpad); channel c = g*cg + ci goes to g*cpad + ci, the rest is zero.
+__global__ void __launch_bounds__(256) to_channels_last_kernel(const float* __restrict__ in, const Strides4 st,
+                                                               float* __restrict__ out, const int cg, const int cpad,
+                                                               const int ctot, const int hw, const int w) {
+  __shared__ float tile[32][33];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int64_t b = blockIdx.z;
+  const int p0 = blockIdx.x * 32, c0 = blockIdx.y * 32;
+  const int p = p0 + tx, y = p / w, x = p - y * w;
+#pragma unroll
+  for (int j = ty; j < 32; j += 8) {
+    const int cp = c0 + j, g = cp / cpad, ci = cp - g * cpad;
+    float v = 0.f;
+    if (cp < ctot && ci < cg && p < hw)
+      v = in[b * st.s[0] + (int64_t)(g * cg + ci) * st.s[1] + (int64_t)y * st.s[2] + (int64_t)x * st.s[3]];
+    tile[j][tx] = v;
+  }
+  __syncthreads();
+#pragma unroll
+  for (int j = ty; j < 32; j += 8) {
+    const int pp = p0 + j, cp = c0 + tx;
+    if (pp < hw && cp < ctot) out[(b * hw + pp) * ctot + cp] = tile[tx][j];
+  }
+}
+
+// filters (O, C/G, kh, kw) through strides -> rows[g][i][tap][cp] with zero padding:
+//   transpose 0: i = output channel in the group, cp = input channel      (forward: M = O/G, K = taps x C/G)
+//   transpose 1: i = input channel, cp = output channel in the group      (data gradient: M = C/G, K = taps x O/G)
+__global__ void __launch_bounds__(NT) filters_to_rows_kernel(const float* __restrict__ f, const Strides4 st,
+                                                             float* __restrict__ rows, const int og, const int cg,
+                                                             const int kk, const int kw, const int cpad,
+                                                             const int transpose, const int64_t total) {
+  const int m = transpose ? cg : og, inner = transpose ? og : cg;
+  for (int64_t i = (int64_t)blockIdx.x * NT + threadIdx.x; i < total; i += (int64_t)gridDim.x * NT) {
+    int64_t idx = i;
+    const int cp = (int)(idx % cpad); idx /= cpad;
+    const int tap = (int)(idx % kk); idx /= kk;
+    const int mi = (int)(idx % m);
+    const int64_t g = idx / m;
+    const int k1 = tap / kw, k2 = tap - k1 * kw;
+    float v = 0.f;
+    if (cp < inner) {
+      const int64_t o = g * og + (transpose ? cp : mi), ci = transpose ? mi : cp;
+      v = f[o * st.s[0] + ci * st.s[1] + (int64_t)k1 * st.s[2] + (int64_t)k2 * st.s[3]];
+    }
+    rows[i] = v;
+  }
+}
+
+// grad_filters[g*og + o, c, k1, k2] (through strides) += rows[g][o][tap][c]
+__global__ void __launch_bounds__(NT) add_filter_rows_kernel(const float* __restrict__ rows, float* __restrict__ gf,
+                                                             const Strides4 st, const int og, const int cg, const int kk,
+                                                             const int kw, const int cpad, const int64_t total) {
+  for (int64_t i = (int64_t)blockIdx.x * NT + threadIdx.x; i < total; i += (int64_t)gridDim.x * NT) {
+    int64_t idx = i;
+    const int c = (int)(idx % cg); idx /= cg;
+    const int tap = (int)(idx % kk); idx /= kk;
+    const int64_t o = idx;                                     // g*og + o
+    const int k1 = tap / kw, k2 = tap - k1 * kw;
+    gf[o * st.s[0] + (int64_t)c * st.s[1] + (int64_t)k1 * st.s[2] + (int64_t)k2 * st.s[3]] +=
+        rows[(o * kk + tap) * cpad + c];
+  }
+}
+
+int64_t round_up(int64_t x, int64_t to) { return (x + to - 1) / to * to; }
+
+int launch_to_channels_last(const float* in, const Strides4& st, float* out, int64_t batch, int64_t groups, int64_t cg,
+                            int64_t cpad, int64_t h, int64_t w, cudaStream_t stream) {
+  const int64_t ctot = groups * cpad, hw = h * w;
+  dim3 grid((unsigned)((hw + 31) / 32), (unsigned)((ctot + 31) / 32), (unsigned)batch);
+  to_channels_last_kernel<<<grid, 256, 0, stream>>>(in, st, out, (int)cg, (int)cpad, (int)ctot, (int)hw, (int)w);
+  count_launch(false);
+  return note_cuda_error(cudaGetLastError(), "to_channels_last launch");
+}
+
+// Which passes of a geometry the implicit path serves (f32, unit stride, a tensor-core sized problem whose padded
+// channel counts at most double the work).
+struct ImplicitPlan {
+  bool fwd = false, wgrad = false, dgrad = false;
+  int64_t cpad16 = 0, cpad32 = 0, opad16 = 0;
+};
+ImplicitPlan implicit_plan(int dtype, const Op& o) {
+  ImplicitPlan pl;
+  if (dtype != B200_F32 || o.stride != 1 || current_path() == B200_PATH_SIMT || !fits_int(o)) return pl;
+  if (o.groups < 1 || o.batch < 1 || o.batch > 65535) return pl;
+  const int64_t cg = o.chan_in / o.groups, og = o.chan_out / o.groups, kk = o.kh * o.kw;
+  const int64_t npos = o.h_out * o.w_out, hw = o.h_in * o.w_in;
+  if (cg < 8 || og < 8 || npos < 8 || hw < 8) return pl;
+  const double work = (double)o.batch * (double)o.chan_out * (double)cg * (double)kk * (double)npos;
+  if (work < 4194304.0) return pl;
+  pl.cpad16 = round_up(cg, 16); pl.cpad32 = round_up(cg, 32); pl.opad16 = round_up(og, 16);
+  if (o.groups * pl.cpad32 > (1 << 30) || o.groups * pl.opad16 > (1 << 30)) return pl;
+  pl.fwd = pl.cpad16 <= 2 * cg && o.w_out <= 256 && npos % 4 == 0;
+  pl.wgrad = pl.cpad32 <= 2 * cg && o.w_out % 4 == 0 && (o.groups * pl.cpad32) % 4 == 0;
+  // the data gradient's GEMM has C/G rows: below half an MMA tile the materialising lowering (full tiles) wins
+  pl.dgrad = pl.opad16 <= 2 * og && o.w_in <= 256 && hw % 4 == 0 && cg >= 64;
+  return pl;
+}
+
+// out (beta) += conv(img, filters) without a patch buffer.  Workspace: channels-last image | filter rows.
+int forward_implicit(const Op& op, const ImplicitPlan& pl, const float* img, const Strides4& ist, const float* filters,
+                     const Strides4& fst, float* out, void* ws, cudaStream_t stream, int beta) {
+  DeviceState* ds = device_state();
+  const int sms = ds ? ds->sm_count : 148;
+  const int64_t G = op.groups, cg = op.chan_in / G, og = op.chan_out / G, kk = op.kh * op.kw, cpad = pl.cpad16;
+  float* img_cl = (float*)ws;
+  float* rows = (float*)((uint8_t*)ws + align256((size_t)(op.batch * op.h_in * op.w_in * G * cpad) * 4));
+  ConvImplicit c;
+  c.img_cl = img_cl; c.batch = op.batch; c.h_img = op.h_in; c.w_img = op.w_in; c.groups = G; c.cpad = cpad;
+  c.filt = rows; c.m = og; c.kh = (int)op.kh; c.kw = (int)op.kw;
+  c.h0 = -(int)op.ph; c.dh = (int)op.dilation; c.w0 = -(int)op.pw; c.dw = (int)op.dilation;
+  c.out = out; c.h_out = op.h_out; c.w_out = op.w_out; c.beta = beta;
+  if (!conv_implicit_ok(c)) return B200_ERR_UNSUPPORTED;
+  int rc = launch_to_channels_last(img, ist, img_cl, op.batch, G, cg, cpad, op.h_in, op.w_in, stream);
+  if (rc) return rc;
+  const int64_t n_rows = G * og * kk * cpad;
+  filters_to_rows_kernel<<<grid_for(n_rows, sms), NT, 0, stream>>>(filters, fst, rows, (int)og, (int)cg, (int)kk,
+                                                                    (int)op.kw, (int)cpad, 0, n_rows);
+  count_launch(false);
+  if ((rc = note_cuda_error(cudaGetLastError(), "filters_to_rows launch"))) return rc;
+  return launch_conv_implicit(c, stream);
+}
+
+// grad_filters (through strides) += the filter gradient, without a patch buffer.
+// Workspace: channels-last image | gradient rows (G, O/G, taps, cpad).
+int wgrad_implicit(const Op& op, const ImplicitPlan& pl, const float* img, const Strides4& fst, float* grad_filters,
+                   const float* grad_out, void* ws, cudaStream_t stream) {
+  DeviceState* ds = device_state();
+  const int sms = ds ? ds->sm_count : 148;
+  const int64_t G = op.groups, cg = op.chan_in / G, og = op.chan_out / G, kk = op.kh * op.kw, cpad = pl.cpad32;
+  const int64_t npos = op.h_out * op.w_out, hw = op.h_in * op.w_in;
+  float* img_cl = (float*)ws;
+  float* rows = (float*)((uint8_t*)ws + align256((size_t)(op.batch * hw * G * cpad) * 4));
+  ConvImplicitWgrad c;
+  c.gout = grad_out; c.gout_bs = op.chan_out * npos; c.m = og; c.h_out = op.h_out; c.w_out = op.w_out;
+  c.img_cl = img_cl; c.batch = op.batch; c.h_img = op.h_in; c.w_img = op.w_in; c.c_total = G * cpad; c.cpad = cpad;
+  c.kh = (int)op.kh; c.kw = (int)op.kw;
+  c.h0 = -(int)op.ph; c.dh = (int)op.dilation; c.w0 = -(int)op.pw; c.dw = (int)op.dilation;
+  c.out = rows;
+  if (!conv_implicit_wgrad_ok(c)) return B200_ERR_UNSUPPORTED;
+  const Strides4 ist{{op.chan_in * hw, hw, op.w_in, 1}};
+  int rc = launch_to_channels_last(img, ist, img_cl, op.batch, G, cg, cpad, op.h_in, op.w_in, stream);
+  if (rc) return rc;
+  const int64_t n_rows = G * og * kk * cpad;
+  if ((rc = note_cuda_error(cudaMemsetAsync(rows, 0, (size_t)n_rows * 4, stream), "cudaMemsetAsync(filter gradient rows)")))
+    return rc;
+  for (int64_t g = 0; g < G; ++g) {
+    c.gout = grad_out + g * og * npos;
+    c.img_cl = img_cl + g * cpad;
+    c.out = rows + g * og * kk * cpad;
+    if ((rc = launch_conv_implicit_wgrad(c, stream))) return rc;
+  }
+  const int64_t total = op.chan_out * kk * cg;
+  add_filter_rows_kernel<<<grid_for(total, sms), NT, 0, stream>>>(rows, grad_filters, fst, (int)og, (int)cg, (int)kk,
+                                                                  (int)op.kw, (int)cpad, total);
+  count_launch(false);
+  return note_cuda_error(cudaGetLastError(), "add_filter_rows launch");
+}
+
+// grad_img += the data gradient, as a convolution of grad_out with the filters' roles exchanged, without a patch
+// buffer.  Workspace: channels-last grad_out | filter rows (G, C/G, taps, opad).
+int dgrad_implicit(const Op& op, const ImplicitPlan& pl, float* grad_img, const float* filters, const Strides4& fst,
+                   const float* grad_out, void* ws, cudaStream_t stream) {
+  DeviceState* ds = device_state();
+  const int sms = ds ? ds->sm_count : 148;
+  const int64_t G = op.groups, cg = op.chan_in / G, og = op.chan_out / G, kk = op.kh * op.kw, opad = pl.opad16;
+  const int64_t npos = op.h_out * op.w_out;
+  float* gout_cl = (float*)ws;
+  float* rows = (float*)((uint8_t*)ws + align256((size_t)(op.batch * npos * G * opad) * 4));
+  ConvImplicit c;
+  c.img_cl = gout_cl; c.batch = op.batch; c.h_img = op.h_out; c.w_img = op.w_out; c.groups = G; c.cpad = opad;
+  c.filt = rows; c.m = cg; c.kh = (int)op.kh; c.kw = (int)op.kw;
+  c.h0 = (int)op.ph; c.dh = -(int)op.dilation; c.w0 = (int)op.pw; c.dw = -(int)op.dilation;
+  c.out = grad_img; c.h_out = op.h_in; c.w_out = op.w_in; c.beta = 1;
+  if (!conv_implicit_ok(c)) return B200_ERR_UNSUPPORTED;
+  const Strides4 gst{{op.chan_out * npos, npos, op.w_out, 1}};
+  int rc = launch_to_channels_last(grad_out, gst, gout_cl, op.batch, G, og, opad, op.h_out, op.w_out, stream);
+  if (rc) return rc;
+  const int64_t n_rows = G * cg * kk * opad;
+  filters_to_rows_kernel<<<grid_for(n_rows, sms), NT, 0, stream>>>(filters, fst, rows, (int)og, (int)cg, (int)kk,
+                                                                    (int)op.kw, (int)opad, 1, n_rows);
+  count_launch(false);
+  if ((rc = note_cuda_error(cudaGetLastError(), "filters_to_rows launch (data gradient)"))) return rc;
+  return launch_conv_implicit(c, stream);
+}
+
 template <typename T, typename A>
 int forward_t(int dtype, const Op& op, const T* img, const size_t is[4], const T* filters, T* out,
               void* ws, cudaStream_t stream, int beta = 0) {
@@ -366,6 +560,15 @@ int forward_t(int dtype, const Op& op, const T* img, const size_t is[4], const T
   const int64_t total = op.batch * op.chan_in * op.kh * op.kw * op.h_out * op.w_out;
   if (total == 0) return B200_OK;
   Strides4 st{{(int64_t)is[0], (int64_t)is[1], (int64_t)is[2], (int64_t)is[3]}};
+  if constexpr (std::is_same<T, float>::value) {
+    const ImplicitPlan ip = implicit_plan(dtype, op);
+    if (ip.fwd && g_conv_grad_img_mode.load() == 0) {
+      const int64_t cgk = (op.chan_in / op.groups) * op.kh * op.kw;
+      const Strides4 fst{{cgk, op.kh * op.kw, op.kw, 1}};     // the forward pass takes contiguous filters
+      const int rc = forward_implicit(op, ip, img, st, filters, fst, out, ws, stream, beta);
+      if (rc != B200_ERR_UNSUPPORTED) return rc;
+    }
+  }
   if (plane_path_input<T>(op))
     unfold_input_plane_kernel<T><<<(unsigned)(op.batch * op.chan_in), NT, padded_plane_bytes(op, sizeof(T)),
                                    stream>>>(to_op32(op), img, st, patches);
@@ -403,6 +606,25 @@ int backward_t(int dtype, const Op& op, const T* img, T* grad_img, const T* filt
   T* gftr = (T*)((uint8_t*)ftr + align256((size_t)n_filters * sizeof(T)));
   Strides4 st{{(int64_t)fs[0], (int64_t)fs[1], (int64_t)fs[2], (int64_t)fs[3]}};
   int rc;
+
+  // The implicit-GEMM lowerings (no patch buffer) where they apply; each pass uses the workspace from its start,
+  // one after the other on the stream.
+  if constexpr (std::is_same<T, float>::value) {
+    const ImplicitPlan ip = implicit_plan(dtype, op);
+    if (g_conv_grad_img_mode.load() == 0) {
+      if (grad_filters && img && ip.wgrad) {
+        rc = wgrad_implicit(op, ip, img, st, grad_filters, grad_out, ws, stream);
+        if (rc == B200_OK) grad_filters = nullptr;
+        else if (rc != B200_ERR_UNSUPPORTED) return rc;
+      }
+      if (grad_img && ip.dgrad) {
+        rc = dgrad_implicit(op, ip, grad_img, filters, st, grad_out, ws, stream);
+        if (rc == B200_OK) grad_img = nullptr;
+        else if (rc != B200_ERR_UNSUPPORTED) return rc;
+      }
+      if (!grad_filters && !grad_img) return B200_OK;
+    }
+  }
 
   // grad_filters first, while the workspace is free: with contiguous filters,
   //   grad_filters (G, O/G, C/G*K*K) += sum_b grad_out_b (G, O/G, OH*OW) x patches(img_b)^T (G, OH*OW, C/G*K*K)
@@ -539,8 +761,25 @@ size_t workspace_bytes_op(int dtype, const Op& o, int backward) {
     return WS_OVERFLOW;
   const size_t big = (size_t)1 << 62;
   if (fwd_patches > big || bwd_patches > big || bnf > big) return WS_OVERFLOW;
-  if (!backward) return align256(fwd_patches);
-  return align256(bwd_patches > fwd_patches ? bwd_patches : fwd_patches) + align256(nf) + align256(bnf);
+  // the implicit-GEMM lowerings keep a channels-last copy of the image (or of grad_out) with padded channels and
+  // the re-laid-out filters instead of patches; with a 1x1 filter that can be more than the patches take
+  size_t impl_fwd = 0, impl_bwd = 0;
+  if (dtype == B200_F32 && o.stride == 1) {
+    const int64_t cg = o.chan_in / o.groups, og = o.chan_out / o.groups;
+    const int64_t c16 = round_up(cg, 16), c32 = round_up(cg, 32), o16 = round_up(og, 16);
+    size_t a, b, c, d, e, f;
+    if (!product(&a, {o.batch, o.h_in, o.w_in, o.groups, c16, 4}) || !product(&b, {o.groups, og, o.kh, o.kw, c16, 4}) ||
+        !product(&c, {o.batch, o.h_in, o.w_in, o.groups, c32, 4}) || !product(&d, {o.groups, og, o.kh, o.kw, c32, 4}) ||
+        !product(&e, {o.batch, o.h_out, o.w_out, o.groups, o16, 4}) || !product(&f, {o.groups, cg, o.kh, o.kw, o16, 4}) ||
+        a > big || c > big || e > big)
+      return WS_OVERFLOW;
+    impl_fwd = align256(a) + align256(b);
+    const size_t w = align256(c) + align256(d), g = align256(e) + align256(f);
+    impl_bwd = w > g ? w : g;
+  }
+  if (!backward) return align256(fwd_patches) > impl_fwd ? align256(fwd_patches) : impl_fwd;
+  const size_t old_bwd = align256(bwd_patches > fwd_patches ? bwd_patches : fwd_patches) + align256(nf) + align256(bnf);
+  return old_bwd > impl_bwd ? old_bwd : impl_bwd;
 }
 
 int forward_any(int dtype, const Op& op, const void* img, const size_t is[4], const void* filters, void* out, void* ws,

@@ -335,7 +335,9 @@ __device__ __forceinline__ void split_role(const TcArgs& g, uint32_t smem_base, 
 // ---------------------------------------------------------------------------------------------
 // f32 kernel (3xTF32 with chunked promotion)
 // ---------------------------------------------------------------------------------------------
-template <int BN>
+// CV: 0 = GEMM over strided matrices; 1, 2 = implicit convolution (see TcArgs): only the producer's TMA
+// coordinates, the MMA's N and the epilogue's column range differ.
+template <int BN, int CV = 0>
 __global__ void __launch_bounds__(CfgS<BN>::THREADS, 1)
 gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                    const __grid_constant__ CUtensorMap tma_c, const TcArgs g) {
@@ -351,6 +353,7 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_const
   __shared__ __align__(8) uint64_t bar_tempty[2];
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
+  __shared__ int cv_tab[CV == 2 ? 3 * (BN / 32) : 1];      // CV 2: per 32-column chunk of the tile, its image box
 
   const uint32_t smem_base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -393,14 +396,44 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_const
       for (long long unit = blockIdx.x; ok && unit < g.total_units; unit += gridDim.x) {
         const Unit un = decode_unit(g, unit, total_kb);
         const TileCoord t = decode_tile(g, un.tile);
+        if constexpr (CV == 2) {
+          // the image box each 32-column chunk of this tile reads: (channel, column shift, row shift) of its tap
+          for (int j = 0; j < g.tile_cols / 32; ++j) {
+            const int n = t.nt * g.tile_cols + j * 32, tap = n / g.cv_cpad, k1 = tap / g.cv_kw;
+            cv_tab[3 * j] = n - tap * g.cv_cpad;
+            cv_tab[3 * j + 1] = g.cv_w0 + (tap - k1 * g.cv_kw) * g.cv_dw;
+            cv_tab[3 * j + 2] = tap < g.cv_taps ? g.cv_h0 + k1 * g.cv_dh : (1 << 28);   // past the last tap: zero fill
+          }
+        }
         for (int i = un.kb_lo; i < un.kb_hi; ++i, ++it) {
           const int r = i / g.k_blocks, kb = i - r * g.k_blocks;
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1u;
           if (!mbar_wait(smem_u32(&bar_empty[s]), ph ^ 1u, abortp, g.wait_limit)) { ok = false; break; }
           const uint32_t full = smem_u32(&bar_full[s]);
-          mbar_expect_tx(full, C::RAW_BYTES);
           const uint32_t a_dst = smem_base + s * C::STAGE_BYTES;
+          if constexpr (CV == 1) {
+            // k-block = (tap, block of 16 channels): A = the re-laid-out filters (k = tap * channels + channel), B = one
+            // box of the channels-last image shifted by the tap; pixels outside the image arrive as zeros
+            mbar_expect_tx(full, C::A_BYTES + g.b_tx_bytes);
+            const int tap = kb / g.cv_cblocks, cb = kb - tap * g.cv_cblocks, k1 = tap / g.cv_kw, k2 = tap - k1 * g.cv_kw;
+            tma_load_4d(a_dst, &tma_a, full, kb * C::BK, t.mt * BM, t.ib1, 0);
+            tma_load_4d(a_dst + C::A_BYTES, &tma_b, full, t.ib1 * g.cv_cpad + cb * C::BK, g.cv_w0 + k2 * g.cv_dw,
+                        t.nt * g.cv_rows + g.cv_h0 + k1 * g.cv_dh, t.ib0);
+            continue;
+          }
+          if constexpr (CV == 2) {
+            // k-block = 16 pixels of output row `oh` of image r: A = that box of grad_out for 128 output channels,
+            // B = for each 32-column chunk the same pixels of the image, shifted by the chunk's tap
+            mbar_expect_tx(full, C::A_BYTES + g.b_tx_bytes);
+            const int oh = kb / g.cv_wblocks, w = (kb - oh * g.cv_wblocks) * C::BK;
+            tma_load_4d(a_dst, &tma_a, full, w, oh, t.mt * BM, r);
+            for (int j = 0; j < g.tile_cols / 32; ++j)
+              tma_load_4d(a_dst + C::A_BYTES + j * C::MN_LBO, &tma_b, full, cv_tab[3 * j], w + cv_tab[3 * j + 1],
+                          oh + cv_tab[3 * j + 2], r);
+            continue;
+          }
+          mbar_expect_tx(full, C::RAW_BYTES);
           load_operand<BM, C::BK, C::CH, C::MN_LBO>(a_dst, &tma_a, full, g.a_ld, t.mt * BM, kb * C::BK,
                                                      g.a_x1 * t.ib1 + g.a_xr * r, g.a_y0 * t.ib0);
           load_operand<BN, C::BK, C::CH, C::MN_LBO>(a_dst + C::A_BYTES, &tma_b, full, g.b_ld, t.nt * BN, kb * C::BK,
@@ -410,9 +443,9 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_const
     } else if (warp == MMA_WARP && lane == 0) {
       // ---------------------------------------------------------------- MMA issuer
       // instruction descriptor: D = f32, A = B = tf32 (format 2), majors, N >> 3, M >> 4
+      const uint32_t mma_n = CV ? (uint32_t)g.mma_n : (uint32_t)BN;
       const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(g.a_mn ? 1 : 0) << 15) |
-                             ((uint32_t)(g.b_mn ? 1 : 0) << 16) | ((uint32_t)(BN >> 3) << 17) |
-                             ((uint32_t)(BM >> 4) << 24);
+                             ((uint32_t)(g.b_mn ? 1 : 0) << 16) | ((mma_n >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
       const uint32_t a_lbo = g.a_mn ? C::MN_LBO : 16u, b_lbo = g.b_mn ? C::MN_LBO : 16u;
       const uint32_t a_sbo = g.a_mn ? C::MN_SBO : C::K_SBO, b_sbo = g.b_mn ? C::MN_SBO : C::K_SBO;
       const uint32_t a_lay = g.a_mn ? C::MN_LAYOUT : C::K_LAYOUT, b_lay = g.b_mn ? C::MN_LAYOUT : C::K_LAYOUT;
@@ -495,6 +528,11 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_const
       // partial sums (a K slice, or a stream-K range that does not span the tile's whole K) are added atomically
       const bool partial = g.ksplit > 1 || (g.streamk && !(un.kb_lo == 0 && un.kb_hi == total_kb));
       const int row = t.mt * BM + quad * 32 + lane;
+      // columns of this tile: [tile_col0, n_end).  An implicit-convolution tile holds tile_valid columns (whole image
+      // rows) and the next tile starts tile_cols further on.
+      const int tile_col0 = CV ? t.nt * g.tile_cols : t.nt * BN;
+      const int n_end = (CV && tile_col0 + g.tile_valid < g.n) ? tile_col0 + g.tile_valid : g.n;
+      float* cbase = (float*)g.c + t.ib0 * g.c_b0 + t.ib1 * g.c_b1;
       if (g.c_tma && !partial) {
         // Output through shared memory and TMA, as in the f16 kernel: per-thread row stores hand the memory
         // system 32 separate 16- or 32-byte pieces per instruction, which bounds GEMMs with a short K and a
@@ -507,11 +545,14 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_const
         const bool leader = (threadIdx.x & 127) == 0;
 #pragma unroll
         for (int c = 0; c < C::HALF / 32; ++c) {
-          const int col0 = t.nt * BN + col_base + c * 32;
-          if (col0 < g.n) {                              // warpgroup-uniform
-            if (g.fused && row < g.m) {
-              const int valid = (g.n - col0) < 32 ? (g.n - col0) : 32;
-              fused_epilogue<float>(&acc[c * 32], g, row, col0, valid);
+          const int col0 = tile_col0 + col_base + c * 32;
+          if (col0 < n_end) {                            // warpgroup-uniform
+            const int valid = (n_end - col0) < 32 ? (n_end - col0) : 32;
+            if (g.fused && row < g.m) fused_epilogue<float>(&acc[c * 32], g, row, col0, valid);
+            if (CV && valid < 32 && n_end < g.n) {
+              // the group's other columns belong to the next tile (the map clips only at the output's end)
+              if (row < g.m) store_chunk(cbase + (long long)row * g.ldc + col0, &acc[c * 32], valid, g.beta, 0);
+              continue;
             }
             if (leader) bulk_wait_group_read<0>();       // the store that last used this buffer has read it
             named_barrier_sync(1 + wg, 128);
@@ -530,12 +571,11 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_const
           }
         }
       } else if (row < g.m) {
-        float* cbase = (float*)g.c + t.ib0 * g.c_b0 + t.ib1 * g.c_b1;
 #pragma unroll
         for (int c = 0; c < C::HALF / 32; ++c) {
-          const int col0 = t.nt * BN + col_base + c * 32;
-          if (col0 < g.n) {
-            const int valid = (g.n - col0) < 32 ? (g.n - col0) : 32;
+          const int col0 = tile_col0 + col_base + c * 32;
+          if (col0 < n_end) {
+            const int valid = (n_end - col0) < 32 ? (n_end - col0) : 32;
             if (g.fused) fused_epilogue<float>(&acc[c * 32], g, row, col0, valid);
             if (partial) {
               if (g.c_col) add_chunk_atomic_col(cbase + (long long)col0 * g.ldc + row, &acc[c * 32], valid, g.ldc);
@@ -864,6 +904,9 @@ int build_launch(Launch& L, const Plan& pl, int esize, int tm, int tn, int bmc, 
   g.beta = p.beta;
   g.fused = p.fused() ? 1 : 0; g.alpha = (float)p.alpha; g.bias = p.bias; g.bias_row = p.bias_dim ? 1 : 0; g.act = p.act;
   g.xform_mode = g_xform_mode;
+  g.tile_cols = tn; g.tile_valid = tn; g.mma_n = tn; g.b_tx_bytes = 0;
+  g.cv_cblocks = 1; g.cv_cpad = 16; g.cv_kw = 1; g.cv_taps = 1; g.cv_w0 = g.cv_dw = g.cv_h0 = g.cv_dh = 0;
+  g.cv_rows = 1; g.cv_wout = 1; g.cv_wblocks = 1;
   const long long forced_limit = g_wait_limit.load();
   g.wait_limit = forced_limit > 0 ? forced_limit : 400000000LL + (long long)g.red * g.k_blocks * 40000LL;
   g.status = ds->status;
@@ -1054,6 +1097,222 @@ int set_attr(Kernel kernel) {
 
 }  // namespace
 
+// ---------------------------------------------------------------------------------------------
+// Implicit-GEMM convolution: tensor maps and launch (kernels: gemm_tf32x3_kernel<256, 1> and <256, 2>)
+// ---------------------------------------------------------------------------------------------
+namespace {
+
+// 4-D f32 map with explicit extents, byte strides of dimensions 1..3 and box.
+int encode_map_f32(CUtensorMap* map, const void* base, const uint64_t dims[4], const uint64_t strides_b[3],
+                   const uint32_t box[4], CUtensorMapSwizzle sw) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return B200_ERR_CUDA;
+  cuuint64_t d[4], st[3];
+  cuuint32_t bx[4], es[4] = {1, 1, 1, 1};
+  for (int i = 0; i < 4; ++i) { d[i] = dims[i] ? dims[i] : 1; bx[i] = box[i]; }
+  for (int i = 0; i < 3; ++i) st[i] = strides_b[i];
+  // size-1 dimensions still need a legal (multiple-of-16, non-zero) stride
+  for (int i = 0; i < 3; ++i)
+    if (d[i + 1] == 1 && (st[i] == 0 || st[i] % 16)) st[i] = i ? st[i - 1] : 16;
+  const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<void*>(base), d, st, bx, es,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? B200_OK : B200_ERR_UNSUPPORTED;
+}
+
+constexpr int CV_BN = 256;
+using CvCfg = CfgS<CV_BN>;
+
+// Image rows per N tile of the forward / data-gradient kernel: whole rows, at most 256 positions, a multiple of
+// four positions (16-byte output accesses); among those the count that minimises waves x (per-tile cost).
+int conv_rows_per_tile(const ConvImplicit& c, int sms) {
+  const int64_t m_tiles = (c.m + BM - 1) / BM;
+  int best = 0;
+  double best_cost = 0;
+  for (int r = 1; r * c.w_out <= CV_BN && r <= c.h_out; ++r) {
+    if ((r * c.w_out) % 4) continue;
+    const int64_t tiles = c.batch * c.groups * m_tiles * ((c.h_out + r - 1) / r);
+    const double cost = (double)((tiles + sms - 1) / sms) * (64.0 + (double)(r * c.w_out));
+    if (!best || cost < best_cost) { best = r; best_cost = cost; }
+  }
+  return best;
+}
+
+void cv_common_args(TcArgs& g, DeviceState* ds) {
+  g.nb1 = 1; g.n_fast = 0;
+  g.ksplit = 1; g.streamk = 0; g.sk_per_cta = 0; g.split_out = nullptr; g.split_ld = 0;
+  g.red = 1;
+  g.a_mn = 0; g.b_mn = 0; g.a_ld = 0; g.b_ld = 0;
+  g.a_x1 = g.a_xr = g.a_y0 = g.b_x1 = g.b_xr = g.b_y0 = 0;
+  g.c_b0 = g.c_b1 = 0; g.c_col = 0; g.c_wide = 0; g.c_tma = 0; g.beta = 0;
+  g.xform_mode = g_xform_mode.load();
+  g.status = ds->status;
+  g.fused = 0; g.alpha = 1.f; g.bias = nullptr; g.bias_row = 0; g.act = B200_ACT_NONE;
+  g.cv_cblocks = 1; g.cv_cpad = 16; g.cv_kw = 1; g.cv_taps = 1; g.cv_w0 = g.cv_dw = g.cv_h0 = g.cv_dh = 0;
+  g.cv_rows = 1; g.cv_wout = 1; g.cv_wblocks = 1;
+}
+
+}  // namespace
+
+bool conv_implicit_ok(const ConvImplicit& c) {
+  DeviceState* ds = device_state();
+  if (!ds || !encode_fn()) return false;
+  if (c.batch < 1 || c.groups < 1 || c.m < 1 || c.h_out < 1 || c.w_out < 1 || c.w_out > CV_BN) return false;
+  if (c.cpad < 16 || c.cpad % 16 || c.kh < 1 || c.kw < 1) return false;
+  const int64_t lim = 0x7fffff00LL;
+  if (c.batch > lim || c.groups * c.cpad > lim || c.h_img > lim || c.w_img > lim || c.h_out * c.w_out > lim ||
+      (int64_t)c.kh * c.kw * c.cpad > lim || c.m > lim || c.batch * c.groups > lim)
+    return false;
+  if (((uintptr_t)c.img_cl | (uintptr_t)c.filt | (uintptr_t)c.out) & 15) return false;
+  if ((c.h_out * c.w_out) % 4) return false;                 // batch / channel strides of the output: 16 bytes
+  return conv_rows_per_tile(c, grid_sms(ds)) > 0;
+}
+
+int launch_conv_implicit(const ConvImplicit& c, cudaStream_t stream) {
+  DeviceState* ds = device_state();
+  if (!ds || !ds->ready) return B200_ERR_CUDA;
+  if (!conv_implicit_ok(c)) return B200_ERR_UNSUPPORTED;
+  const int sms = grid_sms(ds);
+  const int rows = conv_rows_per_tile(c, sms);
+  const int64_t taps = (int64_t)c.kh * c.kw, kr = taps * c.cpad, npos = c.h_out * c.w_out, ct = c.groups * c.cpad;
+  Launch L;
+  // A: filters (groups, m, taps*cpad), K-major rows
+  {
+    const uint64_t dims[4] = {(uint64_t)kr, (uint64_t)c.m, (uint64_t)c.groups, 1};
+    const uint64_t st[3] = {(uint64_t)kr * 4, (uint64_t)c.m * kr * 4, (uint64_t)c.groups * c.m * kr * 4};
+    const uint32_t box[4] = {(uint32_t)CvCfg::BK, (uint32_t)BM, 1, 1};
+    const int rc = encode_map_f32(&L.ma, c.filt, dims, st, box, CU_TENSOR_MAP_SWIZZLE_64B);
+    if (rc) return rc;
+  }
+  // B: channels-last image (channel, x, y, image); one box = 16 channels x w_out pixels x `rows` image rows
+  {
+    const uint64_t dims[4] = {(uint64_t)ct, (uint64_t)c.w_img, (uint64_t)c.h_img, (uint64_t)c.batch};
+    const uint64_t st[3] = {(uint64_t)ct * 4, (uint64_t)c.w_img * ct * 4, (uint64_t)c.h_img * c.w_img * ct * 4};
+    const uint32_t box[4] = {(uint32_t)CvCfg::BK, (uint32_t)c.w_out, (uint32_t)rows, 1};
+    const int rc = encode_map_f32(&L.mb, c.img_cl, dims, st, box, CU_TENSOR_MAP_SWIZZLE_64B);
+    if (rc) return rc;
+  }
+  TcArgs& g = L.g;
+  cv_common_args(g, ds);
+  g.m = (int)c.m; g.n = (int)npos;
+  g.m_tiles = (int)((c.m + BM - 1) / BM);
+  g.n_tiles = (int)((c.h_out + rows - 1) / rows);
+  g.nb1 = (int)c.groups;
+  g.total_tiles = (long long)g.m_tiles * g.n_tiles * c.batch * c.groups;
+  g.total_units = g.total_tiles;
+  g.k_blocks = (int)(taps * (c.cpad / CvCfg::BK));
+  g.kb_per_slice = g.k_blocks;
+  g.c = c.out; g.c_b0 = c.groups * c.m * npos; g.c_b1 = c.m * npos; g.ldc = npos;
+  g.tile_cols = rows * (int)c.w_out; g.tile_valid = g.tile_cols;
+  g.mma_n = (g.tile_cols + 15) / 16 * 16;
+  g.b_tx_bytes = CvCfg::BK * 4 * g.tile_cols;
+  g.c_wide = (g.tile_cols % 8 == 0 && npos % 8 == 0 && ((uintptr_t)c.out % 32 == 0)) ? 1 : 0;
+  g.beta = c.beta ? 1 : 0;
+  L.mc = L.ma;
+  if (g_store_mode.load() != 1 &&
+      encode_map(&L.mc, c.out, 4, npos, c.m, npos, c.groups, c.m * npos, c.batch, c.groups * c.m * npos, 32, 128,
+                 CU_TENSOR_MAP_SWIZZLE_128B) == B200_OK)
+    g.c_tma = g.beta ? 2 : 1;
+  g.cv_cblocks = (int)(c.cpad / CvCfg::BK); g.cv_cpad = (int)c.cpad; g.cv_kw = c.kw; g.cv_taps = (int)taps;
+  g.cv_w0 = c.w0; g.cv_dw = c.dw; g.cv_h0 = c.h0; g.cv_dh = c.dh;
+  g.cv_rows = rows; g.cv_wout = (int)c.w_out;
+  const long long forced_limit = g_wait_limit.load();
+  g.wait_limit = forced_limit > 0 ? forced_limit : 400000000LL + (long long)g.k_blocks * 40000LL;
+  const long long grid = g.total_units < sms ? g.total_units : sms;
+  if (grid <= 0) return B200_OK;
+  gemm_tf32x3_kernel<CV_BN, 1><<<(unsigned)grid, CvCfg::THREADS, CvCfg::SMEM_BYTES, stream>>>(L.ma, L.mb, L.mc, L.g);
+  count_launch(true);
+  return note_cuda_error(cudaGetLastError(), "implicit convolution launch");
+}
+
+namespace {
+// Width of the N tiles of the filter-gradient kernel: a multiple of 32 columns (one chunk = 32 channels of one tap),
+// the one that covers taps*cpad columns with the least padding, then the widest.
+int wgrad_tile_cols(int64_t kr) {
+  int best = 32;
+  int64_t best_pad = -1;
+  for (int tc = CV_BN; tc >= 32; tc -= 32) {
+    const int64_t padded = (kr + tc - 1) / tc * tc;
+    if (best_pad < 0 || padded < best_pad) { best = tc; best_pad = padded; }
+  }
+  return best;
+}
+}  // namespace
+
+bool conv_implicit_wgrad_ok(const ConvImplicitWgrad& c) {
+  DeviceState* ds = device_state();
+  if (!ds || !encode_fn()) return false;
+  if (c.batch < 1 || c.m < 1 || c.h_out < 1 || c.w_out < 1 || c.w_out % 4) return false;
+  if (c.cpad < 32 || c.cpad % 32 || c.c_total % 4 || c.kh < 1 || c.kw < 1 || c.gout_bs % 4) return false;
+  const int64_t lim = 0x7fffff00LL;
+  if (c.batch > lim || c.c_total > lim || c.h_img > lim || c.w_img > lim || c.h_out * c.w_out > lim ||
+      (int64_t)c.kh * c.kw * c.cpad > lim || c.m > lim || c.h_out * ((c.w_out + 15) / 16) > lim / (c.batch > 0 ? c.batch : 1))
+    return false;
+  if (((uintptr_t)c.img_cl | (uintptr_t)c.gout | (uintptr_t)c.out) & 15) return false;
+  return true;
+}
+
+int launch_conv_implicit_wgrad(const ConvImplicitWgrad& c, cudaStream_t stream) {
+  DeviceState* ds = device_state();
+  if (!ds || !ds->ready) return B200_ERR_CUDA;
+  if (!conv_implicit_wgrad_ok(c)) return B200_ERR_UNSUPPORTED;
+  const int sms = grid_sms(ds);
+  const int64_t taps = (int64_t)c.kh * c.kw, kr = taps * c.cpad, npos = c.h_out * c.w_out;
+  const int tile_cols = wgrad_tile_cols(kr);
+  Launch L;
+  // A: grad_out of this group as (x, y, channel, image); one box = 16 pixels of one row x 128 channels
+  {
+    const uint64_t dims[4] = {(uint64_t)c.w_out, (uint64_t)c.h_out, (uint64_t)c.m, (uint64_t)c.batch};
+    const uint64_t st[3] = {(uint64_t)c.w_out * 4, (uint64_t)npos * 4, (uint64_t)c.gout_bs * 4};
+    const uint32_t box[4] = {(uint32_t)CvCfg::BK, 1, (uint32_t)BM, 1};
+    const int rc = encode_map_f32(&L.ma, c.gout, dims, st, box, CU_TENSOR_MAP_SWIZZLE_64B);
+    if (rc) return rc;
+  }
+  // B: this group's channels of the channels-last image; one box = 32 channels x 16 pixels of one row
+  {
+    const uint64_t dims[4] = {(uint64_t)c.cpad, (uint64_t)c.w_img, (uint64_t)c.h_img, (uint64_t)c.batch};
+    const uint64_t st[3] = {(uint64_t)c.c_total * 4, (uint64_t)c.w_img * c.c_total * 4,
+                            (uint64_t)c.h_img * c.w_img * c.c_total * 4};
+    const uint32_t box[4] = {(uint32_t)CvCfg::CH, (uint32_t)CvCfg::BK, 1, 1};
+    const int rc = encode_map_f32(&L.mb, c.img_cl, dims, st, box, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
+    if (rc) return rc;
+  }
+  L.mc = L.ma;
+  TcArgs& g = L.g;
+  cv_common_args(g, ds);
+  g.m = (int)c.m; g.n = (int)kr;
+  g.m_tiles = (int)((c.m + BM - 1) / BM);
+  g.n_tiles = (int)((kr + tile_cols - 1) / tile_cols);
+  g.total_tiles = (long long)g.m_tiles * g.n_tiles;
+  g.red = (int)c.batch;
+  g.cv_wblocks = (int)((c.w_out + CvCfg::BK - 1) / CvCfg::BK);
+  g.k_blocks = (int)(c.h_out * g.cv_wblocks);
+  const long long total_kb = (long long)g.red * g.k_blocks;
+  // K slices: as many work units as SMs; the slices add into `out` atomically
+  long long slices = sms / g.total_tiles;
+  if (slices < 1) slices = 1;
+  if (slices > total_kb) slices = total_kb;
+  const long long kb_per = (total_kb + slices - 1) / slices;
+  slices = (total_kb + kb_per - 1) / kb_per;
+  g.kb_per_slice = (int)kb_per; g.ksplit = (int)slices;
+  // a single slice still adds into `out` (which holds zeros or a running sum): ksplit > 1 selects the atomic path
+  if (g.ksplit == 1) { g.beta = 1; }
+  g.total_units = g.total_tiles * slices;
+  g.b_mn = 1;
+  g.c = c.out; g.ldc = kr;
+  g.tile_cols = tile_cols; g.tile_valid = tile_cols; g.mma_n = tile_cols;
+  g.b_tx_bytes = tile_cols * CvCfg::BK * 4;
+  g.cv_cpad = (int)c.cpad; g.cv_kw = c.kw; g.cv_taps = (int)taps;
+  g.cv_w0 = c.w0; g.cv_dw = c.dw; g.cv_h0 = c.h0; g.cv_dh = c.dh;
+  const long long forced_limit = g_wait_limit.load();
+  g.wait_limit = forced_limit > 0 ? forced_limit : 400000000LL + kb_per * 40000LL;
+  const long long grid = g.total_units < sms ? g.total_units : sms;
+  if (grid <= 0) return B200_OK;
+  gemm_tf32x3_kernel<CV_BN, 2><<<(unsigned)grid, CvCfg::THREADS, CvCfg::SMEM_BYTES, stream>>>(L.ma, L.mb, L.mc, L.g);
+  count_launch(true);
+  return note_cuda_error(cudaGetLastError(), "implicit filter-gradient launch");
+}
+
 bool tc_eligible(const GemmProblem& p) { return make_plan(p, false).ok || make_plan(p, true).ok; }
 
 int tc_setup_device() {
@@ -1064,6 +1323,8 @@ int tc_setup_device() {
   if ((st = set_attr<CfgS<64>>(gemm_tf32x3_kernel<64>))) return st;
   if ((st = set_attr<CfgS<128>>(gemm_tf32x3_kernel<128>))) return st;
   if ((st = set_attr<CfgS<256>>(gemm_tf32x3_kernel<256>))) return st;
+  if ((st = set_attr<CfgS<256>>(gemm_tf32x3_kernel<256, 1>))) return st;
+  if ((st = set_attr<CfgS<256>>(gemm_tf32x3_kernel<256, 2>))) return st;
   if ((st = pair_setup_device())) return st;
   return encode_fn() ? B200_OK : B200_ERR_CUDA;
 }

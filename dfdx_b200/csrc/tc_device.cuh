@@ -302,6 +302,23 @@ struct TcArgs {
   const void* bias;               // C's element type, 16-byte aligned; indexed by the kernel's column, or
   int bias_row;                   // (bias_row) by the kernel's row
   int act;                        // B200_ACT_*
+  // Implicit convolution (f32 kernel, template parameter CV != 0): the im2col happens in the TMA loads.
+  //   CV 1 (forward / data gradient): the B tile of k-block (tap, channel block) is ONE box of a channels-last
+  //        image, `cv_rows` image rows x `cv_wout` pixels x 16 channels, shifted by the tap; an N tile is those
+  //        cv_rows x cv_wout output positions of one image (ib0), group ib1.
+  //   CV 2 (filter gradient): the reduction runs over output positions, 16 pixels of one image row per k-block
+  //        (red = images); A is a box of grad_out, B tile chunk j is a box of the channels-last image for the tap
+  //        and channel range that columns 32 j .. 32 j + 31 of the tile stand for.
+  int tile_cols;                  // output columns from one N tile to the next (BN for a plain GEMM)
+  int tile_valid;                 // columns of a tile that exist (<= tile_cols)
+  int mma_n;                      // N of the MMA instruction (multiple of 16, >= tile_valid)
+  int b_tx_bytes;                 // bytes the B loads of one stage deliver
+  int cv_cblocks;                 // CV 1: k-blocks per tap (padded channels per group / 16)
+  int cv_cpad;                    // padded channels per group in the channels-last image
+  int cv_kw, cv_taps;             // filter taps per row, taps in all
+  int cv_w0, cv_dw, cv_h0, cv_dh; // tap (k1, k2) reads the image at (row + cv_h0 + k1 * cv_dh, col + cv_w0 + k2 * cv_dw)
+  int cv_rows, cv_wout;           // CV 1: image rows and pixels per row of one N tile
+  int cv_wblocks;                 // CV 2: k-blocks per image row (ceil(w_out / 16))
 };
 
 // Fused epilogue on 32 consecutive accumulator columns [col0, col0+32) of output row `row` (row < m):

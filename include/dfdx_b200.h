@@ -130,11 +130,16 @@ int b200_set_cta_pair_mode(int mode);
  * 2 column stores wherever possible (the kernel's M runs along the output's unit-stride dimension; warp stores
  * are contiguous). */
 int b200_set_store_mode(int mode);
-/* Lowering of the convolution data gradient (testing / profiling).  grad_img_mode 0 (default): with contiguous
- * filters, filters^T x grad_out followed by a fold (col2im) of the per-tap gradients into the image; 1: always the
- * reference's lowering (gather grad_out into patches, then GEMM with the transposed filters).  group_bytes: the
- * GEMM + fold pass runs over groups of images whose per-tap gradients take at most this many bytes (0 = the
- * default, sized to stay in L2; SIZE_MAX = all images at once).  Returns 0, or B200_ERR_UNSUPPORTED. */
+/* Lowering of the convolutions (testing / profiling).  mode 0 (default): the planner's choice.  For f32 with unit
+ * stride and tensor-core sized problems that is the implicit GEMM: the kernel's TMA loads gather the patches from a
+ * channels-last copy of the image, no patch buffer exists (forward, filter gradient, and the data gradient when the
+ * image has at least 64 channels per group); everything else takes the materialising lowerings of mode 2.
+ * mode 2: always materialise: unfold + GEMM forward, one batch-reduced GEMM over the unfolded image for the filter
+ * gradient, and for the data gradient (contiguous filters) filters^T x grad_out followed by a fold (col2im) of the
+ * per-tap gradients into the image.  mode 1: as mode 2, but the data gradient always takes the reference's lowering
+ * (gather grad_out into patches, then GEMM with the transposed filters).  group_bytes: the GEMM + fold pass runs over
+ * groups of images whose per-tap gradients take at most this many bytes (0 = the default, all images at once).
+ * Returns 0, or B200_ERR_UNSUPPORTED. */
 int b200_set_conv_lowering(int grad_img_mode, size_t group_bytes);
 /* K decomposition of the tensor-core kernels (testing / profiling): 0 (default) the planner cuts K into slices when
  * the output tiles alone would leave most SMs idle (partial results are then added atomically, so the last bits of

@@ -132,12 +132,12 @@ def test_config4_conv2d_f32_full_size(cuda_dev, oracle):
     assert oracle.rel_frobenius(gwa + gwb, gw.double()) <= 1e-5
 
 
-@pytest.mark.parametrize("lowering", [pytest.param((0, 0), id="fold"), pytest.param((0, 1), id="fold-per-image"),
-                                      pytest.param((1, 0), id="gather")])
+@pytest.mark.parametrize("lowering", [pytest.param((0, 0), id="auto"), pytest.param((2, 0), id="fold"),
+                                      pytest.param((2, 1), id="fold-per-image"), pytest.param((1, 0), id="gather")])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
 def test_grad_img_lowerings_agree_with_oracle(cuda_dev, oracle, dtype, lowering):
-    """The data gradient by filters^T x grad_out + fold (all images at once, and one image per pass) and by the
-    reference's gather + GEMM, every geometry of CASES, accumulating into a non-zero grad_img."""
+    """The data gradient by the planner's choice, by filters^T x grad_out + fold (all images at once, and one image
+    per pass) and by the reference's gather + GEMM, every geometry of CASES, accumulating into a non-zero grad_img."""
     mode, group = lowering
     assert cuda_dev.lib.b200_set_conv_lowering(mode, group) == 0
     try:
@@ -157,4 +157,70 @@ def test_grad_img_lowerings_agree_with_oracle(cuda_dev, oracle, dtype, lowering)
             assert oracle.rel_frobenius(gw, wgw) <= FROB_TOL[dtype], (case, lowering)
     finally:
         cuda_dev.lib.b200_set_conv_lowering(0, 0)
-    assert cuda_dev.lib.b200_set_conv_lowering(2, 0) == dfdx_b200._lib.ERR_UNSUPPORTED
+    assert cuda_dev.lib.b200_set_conv_lowering(3, 0) == dfdx_b200._lib.ERR_UNSUPPORTED
+
+
+# Geometries the implicit-GEMM lowering serves (f32, unit stride, tensor-core sized): padding 0 / 1 / 2, dilation,
+# groups, 1x1 and 5x5 filters, channel counts that need zero padding (24 -> 32), output rows that do not fill a
+# tile (20 pixels per row: 12 rows = 240 positions per tile, the last tile of an image ragged), more than one tile
+# of output channels with a ragged last one (200), data gradients with 64 and 128 channels per group.
+IMPLICIT_CASES = [
+    dict(x=(2, 16, 24, 24), w=(32, 16, 3, 3), padding=1, dilation=1, groups=1, dgrad=False),
+    dict(x=(2, 64, 14, 20), w=(48, 64, 3, 3), padding=1, dilation=1, groups=1, dgrad=True),
+    dict(x=(3, 24, 12, 12), w=(40, 24, 5, 5), padding=2, dilation=1, groups=1, dgrad=False),
+    dict(x=(2, 32, 16, 16), w=(64, 32, 3, 3), padding=2, dilation=2, groups=1, dgrad=False),
+    dict(x=(2, 64, 12, 12), w=(64, 32, 3, 3), padding=1, dilation=1, groups=2, dgrad=False),
+    dict(x=(2, 128, 12, 12), w=(128, 64, 3, 3), padding=1, dilation=1, groups=2, dgrad=True),
+    dict(x=(2, 64, 16, 16), w=(128, 64, 1, 1), padding=0, dilation=1, groups=1, dgrad=True),
+    dict(x=(2, 16, 16, 16), w=(200, 16, 3, 3), padding=1, dilation=1, groups=1, dgrad=False),
+    dict(x=(2, 128, 10, 12), w=(24, 128, 3, 3), padding=1, dilation=1, groups=1, dgrad=True),
+    dict(x=(6, 64, 9, 10), w=(32, 64, 3, 3), padding=0, dilation=1, groups=1, dgrad=False),  # 7 x 8 outputs: one 56-wide tile
+]
+
+
+@pytest.mark.parametrize("case", range(len(IMPLICIT_CASES)))
+def test_implicit_gemm_lowering(cuda_dev, oracle, case):
+    """Forward, filter gradient and data gradient through the implicit GEMM (no patch buffer): against the oracle, and
+    against the materialising lowering of the same library; the launch counts show which lowering ran."""
+    dev, lib = cuda_dev, cuda_dev.lib
+    cfg = IMPLICIT_CASES[case]
+    kw = dict(stride=1, padding=cfg["padding"], dilation=cfg["dilation"], groups=cfg["groups"])
+    g = gen(300 + case)
+    x = (torch.randn(*cfg["x"], generator=g, dtype=torch.float64) * 0.5).float()
+    w = (torch.randn(*cfg["w"], generator=g, dtype=torch.float64) * 0.2).float()
+    want, obwd = OracleBackend(oracle, torch.float32).conv2d(x, w, **kw)
+    go = torch.randn(*want.shape, generator=g, dtype=torch.float64).float()
+    wgx, wgw = obwd(go)
+    xd, wd, god = x.to(dev.device), w.to(dev.device), go.to(dev.device)
+    op = dev.conv2d_op(xd, wd, **kw)
+    res = {}
+    for mode in (0, 2):
+        assert lib.b200_set_conv_lowering(mode, 0) == 0
+        try:
+            y = torch.full(want.shape, float("nan"), device=dev.device)
+            l0, t0 = lib.b200_launch_count(), lib.b200_tensor_launch_count()
+            dev.conv2d_forward(op, xd, wd, y)
+            fwd_launches = (lib.b200_launch_count() - l0, lib.b200_tensor_launch_count() - t0)
+            gx, gw = torch.ones_like(xd), torch.full_like(wd, 0.5)
+            l0, t0 = lib.b200_launch_count(), lib.b200_tensor_launch_count()
+            dev.conv2d_backward(op, xd, gx, wd, gw, god)
+            bwd_launches = (lib.b200_launch_count() - l0, lib.b200_tensor_launch_count() - t0)
+            dev.synchronize()
+        finally:
+            lib.b200_set_conv_lowering(0, 0)
+        res[mode] = (y, gx, gw)
+        assert oracle.rel_frobenius(y, want) <= 1e-5, (case, mode)
+        assert oracle.rel_frobenius(gx, wgx.double() + 1.0) <= 1e-5, (case, mode)
+        assert oracle.rel_frobenius(gw, wgw.double() + 0.5) <= 1e-5, (case, mode)
+        if mode == 0:
+            # implicit forward: layout change + filter rows + one tensor-core launch
+            assert fwd_launches == (3, 1), fwd_launches
+            # filter gradient: layout change + one launch per group + add; data gradient: 3 launches when implicit,
+            # else one GEMM + one fold
+            groups = cfg["groups"]
+            expect = 2 + groups + (3 if cfg["dgrad"] else 2)
+            assert bwd_launches[0] == expect, (bwd_launches, expect)
+        else:
+            assert fwd_launches == (2, 1), fwd_launches
+    for a, b in zip(res[0], res[2]):
+        assert oracle.rel_frobenius(a, b.double()) <= 2e-5
