@@ -82,6 +82,8 @@ SIGNATURES = {
     "b200_layer_norm_forward": (_i, [_i, _sz, _sz, _vp, _sz, _vp, _vp, _d, _vp, _sz, _vp, _vp]),
     "b200_layer_norm_backward": (_i, [_i, _sz, _sz, _vp, _sz, _vp, _vp, _vp, _sz, _vp, _sz, _i, _vp, _vp, _vp]),
     "b200_bias_grad": (_i, [_i, _sz, _sz, _vp, _sz, _vp, _vp]),
+    "b200_softmax_forward": (_i, [_i, _sz, _sz, _vp, _sz, _d, _vp, _sz, _vp]),
+    "b200_softmax_backward": (_i, [_i, _sz, _sz, _vp, _sz, _vp, _sz, _d, _vp, _sz, _i, _vp]),
     "b200_attention_backward_workspace_bytes": (_sz, [_sz, _sz, _sz]),
     "b200_attention_backward": (_i, [_i, _sz, _sz, _sz, _sz, _sz, _vp, _szp, _vp, _szp, _vp, _szp, _d, _vp, _szp, _vp,
                                      _vp, _szp, _vp, _szp, _vp, _szp, _vp, _szp, _i, _vp, _sz, _vp]),

@@ -483,6 +483,23 @@ int b200_bias_grad(int dtype, size_t rows, size_t cols, const void* grad_out, si
   return column_sum(dtype, (int64_t)rows, (int64_t)cols, grad_out, (int64_t)grad_out_ld, grad_bias, (cudaStream_t)stream);
 }
 
+int b200_softmax_forward(int dtype, size_t rows, size_t cols, const void* x, size_t x_ld, double alpha, void* y, size_t y_ld,
+                         void* stream) {
+  if (!valid_dtype(dtype)) return B200_ERR_DTYPE;
+  if (rows && cols && (!x || !y)) return B200_ERR_NULL;
+  if (rows > 1 && (x_ld < cols || y_ld < cols)) return B200_ERR_STRIDE;
+  return softmax_forward(dtype, (int64_t)rows, (int64_t)cols, x, (int64_t)x_ld, alpha, y, (int64_t)y_ld, (cudaStream_t)stream);
+}
+
+int b200_softmax_backward(int dtype, size_t rows, size_t cols, const void* y, size_t y_ld, const void* grad_out,
+                          size_t grad_out_ld, double alpha, void* grad_x, size_t grad_x_ld, int accumulate, void* stream) {
+  if (!valid_dtype(dtype)) return B200_ERR_DTYPE;
+  if (rows && cols && (!y || !grad_out || !grad_x)) return B200_ERR_NULL;
+  if (rows > 1 && (y_ld < cols || grad_out_ld < cols || grad_x_ld < cols)) return B200_ERR_STRIDE;
+  return softmax_backward(dtype, (int64_t)rows, (int64_t)cols, y, (int64_t)y_ld, grad_out, (int64_t)grad_out_ld, alpha, grad_x,
+                          (int64_t)grad_x_ld, accumulate, (cudaStream_t)stream);
+}
+
 size_t b200_attention_backward_workspace_bytes(size_t batch, size_t heads, size_t s1) {
   return attention_backward_workspace_bytes((int64_t)batch, (int64_t)heads, (int64_t)s1);
 }

@@ -90,6 +90,10 @@ int layer_norm_forward(int dtype, int64_t rows, int64_t cols, const void* x, int
 int layer_norm_backward(int dtype, int64_t rows, int64_t cols, const void* x, int64_t x_ld, const void* gamma, const float* stats,
                         const void* g, int64_t g_ld, void* gx, int64_t gx_ld, int accumulate_x, float* ggamma, float* gbeta,
                         cudaStream_t stream);
+int softmax_forward(int dtype, int64_t rows, int64_t cols, const void* x, int64_t x_ld, double alpha, void* y, int64_t y_ld,
+                    cudaStream_t stream);
+int softmax_backward(int dtype, int64_t rows, int64_t cols, const void* y, int64_t y_ld, const void* g, int64_t g_ld,
+                     double alpha, void* gx, int64_t gx_ld, int accumulate, cudaStream_t stream);
 int column_sum(int dtype, int64_t rows, int64_t cols, const void* g, int64_t ld, float* out, cudaStream_t stream);
 
 // Lowers one problem to a kernel family according to b200_set_path and eligibility.

@@ -9,6 +9,9 @@
 //   layer_norm_bwd_kernel   dx = rstd * (g*gamma - mean(g*gamma) - xhat * mean(g*gamma*xhat)),
 //                           dgamma += sum_rows g * xhat,  dbeta += sum_rows g   (the tape entries of the same ops)
 //   column_sum_kernel       out[j] += sum_i g[i, j]   (backward of `bias.broadcast_like(&x) + x`, bias1d.rs:66-79)
+//   softmax_fwd_kernel      y = softmax(alpha * x) over the last axis = exp(alpha*x - max) / sum exp(alpha*x - max)
+//                           (dfdx-core/src/tensor_ops/softmax.rs:36-84: max, subtract, exp, sum, divide: five kernels there)
+//   softmax_bwd_kernel      dx (+)= alpha * y * (g - sum_j g_j y_j)   (the tape entries of div, sum, exp and the scalar mul)
 // One warp per row; lanes walk the row in 16-byte vectors when the layout allows, element-wise otherwise.
 #include "common.cuh"
 
@@ -317,6 +320,148 @@ __global__ void __launch_bounds__(256) column_sum_kernel(const T* __restrict__ g
   }
 }
 
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// One warp per row, the row kept in registers (cols <= 32 * N * MAXV) or re-read from L1 / L2 (MAXV == 0).
+template <typename T, int MAXV>
+__global__ void __launch_bounds__(256) softmax_fwd_kernel(const T* __restrict__ x, long long x_ld, float alpha,
+                                                          T* __restrict__ y, long long y_ld, long long rows, int cols, int vec) {
+  constexpr int N = Vec<T>::N;
+  constexpr float LOG2E = 1.4426950408889634f;
+  const int lane = threadIdx.x & 31;
+  const long long warp0 = (long long)blockIdx.x * 8 + (threadIdx.x >> 5), nwarps = (long long)gridDim.x * 8;
+  const float a2 = alpha * LOG2E;                            // exp(alpha*x - m) = exp2(a2*x - m*log2e)
+  for (long long r = warp0; r < rows; r += nwarps) {
+    const T* xr = x + r * x_ld;
+    T* yr = y + r * y_ld;
+    if constexpr (MAXV > 0) {
+      float f[MAXV][N];
+      float mx = -INFINITY;
+#pragma unroll
+      for (int v = 0; v < MAXV; ++v) {
+        const int c = (v * 32 + lane) * N;
+        if (c < cols) load_vec(xr, c, cols, vec, f[v]);
+#pragma unroll
+        for (int q = 0; q < N; ++q) {
+          f[v][q] = (c + q < cols) ? f[v][q] * a2 : -INFINITY;
+          mx = fmaxf(mx, f[v][q]);
+        }
+      }
+      mx = warp_max(mx);
+      if (mx == -INFINITY) mx = 0.f;                         // a row of -inf: exp2(-inf - 0) = 0, 0/0 -> NaN as the reference
+      float s = 0.f;
+#pragma unroll
+      for (int v = 0; v < MAXV; ++v)
+#pragma unroll
+        for (int q = 0; q < N; ++q) { f[v][q] = exp2f(f[v][q] - mx); s += f[v][q]; }
+      const float inv = 1.f / warp_sum(s);
+#pragma unroll
+      for (int v = 0; v < MAXV; ++v) {
+        const int c = (v * 32 + lane) * N;
+#pragma unroll
+        for (int q = 0; q < N; ++q) f[v][q] *= inv;
+        if (c < cols) store_vec(yr, c, cols, vec, f[v]);
+      }
+    } else {
+      float mx = -INFINITY;
+      for (int c = lane * N; c < cols; c += 32 * N) {
+        float f[N];
+        load_vec(xr, c, cols, vec, f);
+#pragma unroll
+        for (int q = 0; q < N; ++q)
+          if (c + q < cols) mx = fmaxf(mx, f[q] * a2);
+      }
+      mx = warp_max(mx);
+      if (mx == -INFINITY) mx = 0.f;
+      float s = 0.f;
+      for (int c = lane * N; c < cols; c += 32 * N) {
+        float f[N];
+        load_vec(xr, c, cols, vec, f);
+#pragma unroll
+        for (int q = 0; q < N; ++q)
+          if (c + q < cols) s += exp2f(f[q] * a2 - mx);
+      }
+      const float inv = 1.f / warp_sum(s);
+      for (int c = lane * N; c < cols; c += 32 * N) {
+        float f[N];
+        load_vec(xr, c, cols, vec, f);
+#pragma unroll
+        for (int q = 0; q < N; ++q) f[q] = exp2f(f[q] * a2 - mx) * inv;
+        store_vec(yr, c, cols, vec, f);
+      }
+    }
+  }
+}
+
+template <typename T, int MAXV>
+__global__ void __launch_bounds__(256) softmax_bwd_kernel(const T* __restrict__ y, long long y_ld, const T* __restrict__ g,
+                                                          long long g_ld, float alpha, T* __restrict__ gx, long long gx_ld,
+                                                          int accumulate, long long rows, int cols, int vec) {
+  constexpr int N = Vec<T>::N;
+  const int lane = threadIdx.x & 31;
+  const long long warp0 = (long long)blockIdx.x * 8 + (threadIdx.x >> 5), nwarps = (long long)gridDim.x * 8;
+  for (long long r = warp0; r < rows; r += nwarps) {
+    const T* yr = y + r * y_ld;
+    const T* gr = g + r * g_ld;
+    T* dr = gx + r * gx_ld;
+    if constexpr (MAXV > 0) {
+      float yv[MAXV][N], gv[MAXV][N];
+      float dot = 0.f;
+#pragma unroll
+      for (int v = 0; v < MAXV; ++v) {
+        const int c = (v * 32 + lane) * N;
+        if (c < cols) { load_vec(yr, c, cols, vec, yv[v]); load_vec(gr, c, cols, vec, gv[v]); }
+#pragma unroll
+        for (int q = 0; q < N; ++q) {
+          if (c + q >= cols) { yv[v][q] = 0.f; gv[v][q] = 0.f; }
+          dot = fmaf(yv[v][q], gv[v][q], dot);
+        }
+      }
+      dot = warp_sum(dot);
+#pragma unroll
+      for (int v = 0; v < MAXV; ++v) {
+        const int c = (v * 32 + lane) * N;
+        if (c >= cols) continue;
+        float o[N];
+        if (accumulate) load_vec(dr, c, cols, vec, o);
+#pragma unroll
+        for (int q = 0; q < N; ++q) {
+          const float d = alpha * yv[v][q] * (gv[v][q] - dot);
+          o[q] = accumulate ? o[q] + d : d;
+        }
+        store_vec(dr, c, cols, vec, o);
+      }
+    } else {
+      float dot = 0.f;
+      for (int c = lane * N; c < cols; c += 32 * N) {
+        float a[N], b[N];
+        load_vec(yr, c, cols, vec, a);
+        load_vec(gr, c, cols, vec, b);
+#pragma unroll
+        for (int q = 0; q < N; ++q)
+          if (c + q < cols) dot = fmaf(a[q], b[q], dot);
+      }
+      dot = warp_sum(dot);
+      for (int c = lane * N; c < cols; c += 32 * N) {
+        float a[N], b[N], o[N];
+        load_vec(yr, c, cols, vec, a);
+        load_vec(gr, c, cols, vec, b);
+        if (accumulate) load_vec(dr, c, cols, vec, o);
+#pragma unroll
+        for (int q = 0; q < N; ++q) {
+          const float d = alpha * a[q] * (b[q] - dot);
+          o[q] = accumulate ? o[q] + d : d;
+        }
+        store_vec(dr, c, cols, vec, o);
+      }
+    }
+  }
+}
+
 bool vec_ok(size_t es, int64_t cols, std::initializer_list<int64_t> lds, std::initializer_list<const void*> ptrs) {
   const int64_t n = 16 / (int64_t)es;
   if (cols % n) return false;
@@ -386,6 +531,46 @@ int column_sum_t(int64_t rows, int64_t cols, const void* g, int64_t ld, float* o
   return note_cuda_error(cudaGetLastError(), "column sum launch");
 }
 
+template <typename T>
+int softmax_forward_t(int64_t rows, int64_t cols, const void* x, int64_t x_ld, double alpha, void* y, int64_t y_ld,
+                      cudaStream_t stream) {
+  DeviceState* ds = device_state();
+  const int vec = vec_ok(sizeof(T), cols, {x_ld, y_ld}, {x, y}) ? 1 : 0;
+  long long blocks = (rows + 7) / 8;
+  const long long cap = (long long)ds->sm_count * 16;
+  if (blocks > cap) blocks = cap;
+  const int64_t vecs = (cols + 32 * Vec<T>::N - 1) / (32 * Vec<T>::N);
+  auto launch = [&](auto kernel) {
+    kernel<<<(unsigned)blocks, 256, 0, stream>>>((const T*)x, x_ld, (float)alpha, (T*)y, y_ld, rows, (int)cols, vec);
+  };
+  if (vecs <= 2) launch(softmax_fwd_kernel<T, 2>);
+  else if (vecs <= 4) launch(softmax_fwd_kernel<T, 4>);
+  else if (vecs <= 8) launch(softmax_fwd_kernel<T, 8>);
+  else launch(softmax_fwd_kernel<T, 0>);
+  count_launch(false);
+  return note_cuda_error(cudaGetLastError(), "softmax forward launch");
+}
+
+template <typename T>
+int softmax_backward_t(int64_t rows, int64_t cols, const void* y, int64_t y_ld, const void* g, int64_t g_ld, double alpha,
+                       void* gx, int64_t gx_ld, int accumulate, cudaStream_t stream) {
+  DeviceState* ds = device_state();
+  const int vec = vec_ok(sizeof(T), cols, {y_ld, g_ld, gx_ld}, {y, g, gx}) ? 1 : 0;
+  long long blocks = (rows + 7) / 8;
+  const long long cap = (long long)ds->sm_count * 16;
+  if (blocks > cap) blocks = cap;
+  const int64_t vecs = (cols + 32 * Vec<T>::N - 1) / (32 * Vec<T>::N);
+  auto launch = [&](auto kernel) {
+    kernel<<<(unsigned)blocks, 256, 0, stream>>>((const T*)y, y_ld, (const T*)g, g_ld, (float)alpha, (T*)gx, gx_ld, accumulate,
+                                                 rows, (int)cols, vec);
+  };
+  if (vecs <= 2) launch(softmax_bwd_kernel<T, 2>);
+  else if (vecs <= 4) launch(softmax_bwd_kernel<T, 4>);
+  else launch(softmax_bwd_kernel<T, 0>);
+  count_launch(false);
+  return note_cuda_error(cudaGetLastError(), "softmax backward launch");
+}
+
 }  // namespace
 
 int layer_norm_forward(int dtype, int64_t rows, int64_t cols, const void* x, int64_t x_ld, const void* gamma, const void* beta,
@@ -423,6 +608,32 @@ int column_sum(int dtype, int64_t rows, int64_t cols, const void* g, int64_t ld,
     case B200_F32: return column_sum_t<float>(rows, cols, g, ld, out, stream);
     case B200_F16:
     case B200_AMP_F16: return column_sum_t<__half>(rows, cols, g, ld, out, stream);
+    default: return B200_ERR_UNSUPPORTED;
+  }
+}
+
+int softmax_forward(int dtype, int64_t rows, int64_t cols, const void* x, int64_t x_ld, double alpha, void* y, int64_t y_ld,
+                    cudaStream_t stream) {
+  if (rows == 0 || cols == 0) return B200_OK;
+  if (!device_state()) return note_cuda_error(cudaErrorInitializationError, "b200_init not called on this device");
+  if (cols > 0x7fffffffLL) return B200_ERR_LIMIT;
+  switch (dtype) {
+    case B200_F32: return softmax_forward_t<float>(rows, cols, x, x_ld, alpha, y, y_ld, stream);
+    case B200_F16:
+    case B200_AMP_F16: return softmax_forward_t<__half>(rows, cols, x, x_ld, alpha, y, y_ld, stream);
+    default: return B200_ERR_UNSUPPORTED;
+  }
+}
+
+int softmax_backward(int dtype, int64_t rows, int64_t cols, const void* y, int64_t y_ld, const void* g, int64_t g_ld,
+                     double alpha, void* gx, int64_t gx_ld, int accumulate, cudaStream_t stream) {
+  if (rows == 0 || cols == 0) return B200_OK;
+  if (!device_state()) return note_cuda_error(cudaErrorInitializationError, "b200_init not called on this device");
+  if (cols > 0x7fffffffLL) return B200_ERR_LIMIT;
+  switch (dtype) {
+    case B200_F32: return softmax_backward_t<float>(rows, cols, y, y_ld, g, g_ld, alpha, gx, gx_ld, accumulate, stream);
+    case B200_F16:
+    case B200_AMP_F16: return softmax_backward_t<__half>(rows, cols, y, y_ld, g, g_ld, alpha, gx, gx_ld, accumulate, stream);
     default: return B200_ERR_UNSUPPORTED;
   }
 }

@@ -302,6 +302,23 @@ class Cuda:
               "b200_layer_norm_backward")
         return gx
 
+    def softmax_forward(self, x, alpha: float = 1.0, out=None):
+        """`(x * alpha).softmax::<last axis>()` (softmax.rs:36-84) in one pass; x (..., cols) with a unit last stride."""
+        x2 = x.reshape(-1, x.shape[-1])
+        y = self._empty(x2.shape, x) if out is None else out.reshape(x2.shape)
+        check(self.lib.b200_softmax_forward(self._dtype(x), x2.shape[0], x2.shape[1], x2.data_ptr(), x2.stride(0), float(alpha),
+                                            y.data_ptr(), y.stride(0), self._stream()), "b200_softmax_forward")
+        return y.reshape(x.shape)
+
+    def softmax_backward(self, y, grad_out, alpha: float = 1.0, accumulate_into=None):
+        """grad_x (+)= alpha * y * (grad_out - sum(grad_out * y)) over the last axis."""
+        y2, g2 = y.reshape(-1, y.shape[-1]), grad_out.reshape(-1, y.shape[-1])
+        gx = self._empty(y2.shape, y) if accumulate_into is None else accumulate_into.reshape(y2.shape)
+        check(self.lib.b200_softmax_backward(self._dtype(y), y2.shape[0], y2.shape[1], y2.data_ptr(), y2.stride(0), g2.data_ptr(),
+                                             g2.stride(0), float(alpha), gx.data_ptr(), gx.stride(0),
+                                             0 if accumulate_into is None else 1, self._stream()), "b200_softmax_backward")
+        return gx.reshape(y.shape)
+
     def bias_grad(self, grad_out, grad_bias) -> None:
         """grad_bias (f32, `cols` elements) += column sums of the contiguous (..., cols) tensor grad_out."""
         cols = grad_out.shape[-1]

@@ -11,9 +11,9 @@ backward).  With `fused="attention"` the whole scores / softmax / weighted-sum s
 fused attention kernels.  With `fused=True` (default) the ops that directly follow a GEMM in the forward pass — Linear's
 bias add, the feed-forward ReLU, the 1/sqrt(d) scale of the scores — run in that GEMM's epilogue
 (`b200_linear_forward`, `b200_matmat_batch4_forward_scaled`); with `fused=False` they are separate torch
-ops, as they are separate kernels in dfdx; any fused mode also runs LayerNorm (forward and backward) and the bias
-gradient on this library's row-wise kernels.  Residual adds, softmax (unfused attention), the MSE loss and Adam are
-plain torch ops either way.
+ops, as they are separate kernels in dfdx; any fused mode also runs LayerNorm (forward and backward), the bias
+gradient and, where attention is not one fused kernel (f32, head sizes the fused kernel does not serve), the softmax
+on this library's row-wise kernels.  Residual adds, the MSE loss and Adam are plain torch ops either way.
 
 Parameters are f32 master weights; each step computes in f16 (`AMP<f16>`-like: f16 storage, f32
 accumulation inside the GEMMs) and Adam updates the f32 masters.  A `Trainer` keeps masters, f16 compute copies
@@ -91,6 +91,23 @@ class _FusedLinear(torch.autograd.Function):
         dev.bias_grad(g, grad_bias)                                # f32 column sums, one pass over g
         grad_bias = grad_bias.to(g.dtype)
         return None, dev.grad_view(gx, x), gw.view_as(weight), grad_bias, None
+
+
+class _Softmax(torch.autograd.Function):
+    """softmax over the last axis on this library's row-wise kernels (`b200_softmax_forward` / `_backward`): one pass
+    each way where dfdx's op sequence (softmax.rs:36-84) runs five kernels forward."""
+
+    @staticmethod
+    def forward(ctx, dev: Cuda, scores):
+        y = dev.softmax_forward(scores.contiguous())
+        ctx.dev = dev
+        ctx.save_for_backward(y)
+        return y
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        (y,) = ctx.saved_tensors
+        return None, ctx.dev.softmax_backward(y, grad_out.contiguous())
 
 
 class _ScaledMatMul(torch.autograd.Function):
@@ -257,9 +274,10 @@ class MultiHeadAttention(torch.nn.Module):
             return self.w_o(tokens.permute(0, 2, 1, 3).reshape(b, s, m))
         if self.fused:
             scores = _ScaledMatMul.apply(self.dev, q, k, 1.0 / math.sqrt(d))
+            weights = _Softmax.apply(self.dev, scores)
         else:
             scores = matmul(self.dev, q, k) * (1.0 / math.sqrt(d))
-        weights = torch.softmax(scores, dim=-1)
+            weights = torch.softmax(scores, dim=-1)
         tokens = matmul(self.dev, weights, v).permute(0, 2, 1, 3).reshape(b, s, m)
         return self.w_o(tokens)
 

@@ -361,6 +361,18 @@ int b200_layer_norm_backward(int dtype, size_t rows, size_t cols, const void* x,
 int b200_bias_grad(int dtype, size_t rows, size_t cols, const void* grad_out, size_t grad_out_ld,
                    float* grad_bias, void* stream);
 
+/* `softmax` over the last axis of a (rows, cols) matrix (dfdx-core/src/tensor_ops/softmax.rs:36-84: max, subtract,
+ * exp, sum, divide — five kernels and their tape entries in the reference, one pass here), with the scalar multiply
+ * that precedes it in MultiHeadAttention (multi_head_attention.rs:136-137) folded in:
+ *     y = softmax(alpha * x),     grad_x (+)= alpha * y * (grad_out - sum_j grad_out_j * y_j).
+ * f32 and f16 (f32 arithmetic); leading dimensions in elements, >= cols.  `accumulate` != 0 adds into grad_x
+ * (dfdx's `+=` into a gradient buffer), 0 writes it.  y may alias x; grad_x may alias grad_out. */
+int b200_softmax_forward(int dtype, size_t rows, size_t cols, const void* x, size_t x_ld, double alpha,
+                         void* y, size_t y_ld, void* stream);
+int b200_softmax_backward(int dtype, size_t rows, size_t cols, const void* y, size_t y_ld,
+                          const void* grad_out, size_t grad_out_ld, double alpha,
+                          void* grad_x, size_t grad_x_ld, int accumulate, void* stream);
+
 /* ---- conv2d (unfold + GEMM lowering) ---------------------------------------------------------- */
 
 /* Bytes of caller-provided scratch the conv2d entry points need; `backward` != 0 selects the

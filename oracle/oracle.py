@@ -380,6 +380,23 @@ def attention_backward(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, alpha:
     return g_q, g_k, g_v
 
 
+def softmax(x: torch.Tensor, alpha: float = 1.0):
+    """`softmax` over the last axis as dfdx-core/src/tensor_ops/softmax.rs:70-83 computes it (subtract the row maximum,
+    exp, divide by the row sum), applied to alpha * x (the scalar multiply MultiHeadAttention puts in front of it,
+    multi_head_attention.rs:136-137), in f64.  Returns (y, backward); backward(grad_out) -> grad_x is the chain of the
+    tape entries of div, sum, exp and the scalar multiply: alpha * y * (g - sum(g * y))."""
+    t = x.detach().cpu().to(torch.float64) * float(alpha)
+    t = t - t.max(dim=-1, keepdim=True).values
+    e = torch.exp(t)
+    y = e / e.sum(dim=-1, keepdim=True)
+
+    def backward(grad_out: torch.Tensor):
+        g = grad_out.detach().cpu().to(torch.float64)
+        return float(alpha) * y * (g - (g * y).sum(dim=-1, keepdim=True))
+
+    return y, backward
+
+
 def layer_norm(x: torch.Tensor, gamma: torch.Tensor = None, beta: torch.Tensor = None, eps: float = 1e-5):
     """`normalize::<last axis>(epsilon)` step by step as dfdx-core/src/tensor_ops/normalize.rs:33-50 writes it (mean,
     subtract, square, mean, + epsilon, sqrt, divide), then `* gamma + beta` (dfdx/src/nn/layers/layer_norm1d.rs:87-91),

@@ -14,6 +14,7 @@ Sources (dfdx v0.13.0):
     dfdx-core/src/tensor_ops/normalize.rs       (tests at :52-127; the normalisation inside LayerNorm1D)
     dfdx-core/src/tensor_ops/conv1d/tests.rs
     dfdx-core/src/tensor_ops/convtrans2d/tests.rs
+    dfdx-core/src/tensor_ops/softmax.rs         (tests at :90-222)
 """
 from __future__ import annotations
 
@@ -32,6 +33,7 @@ FILES = {
     "normalize": "dfdx-core/src/tensor_ops/normalize.rs",
     "conv1d": "dfdx-core/src/tensor_ops/conv1d/tests.rs",
     "convtrans2d": "dfdx-core/src/tensor_ops/convtrans2d/tests.rs",
+    "softmax": "dfdx-core/src/tensor_ops/softmax.rs",
 }
 
 

@@ -49,6 +49,9 @@ class OracleBackend:
         y, bwd = self.o.layer_norm(x, None, None, eps)
         return y, lambda go: bwd(go)[0]
 
+    def softmax(self, x):
+        return self.o.softmax(x)
+
     def linear(self, x, weight_view, bias, relu=False):
         return self.o.fused_matmul(x, weight_view, 1.0, bias, relu)
 
@@ -107,6 +110,12 @@ class CudaBackend:
         def backward(go):
             return bwd(go.to(self.dtype).to(self.dev.device))
         return out, backward
+
+    def softmax(self, x):
+        """softmax over the last axis through the row-wise kernels."""
+        xc = x.contiguous()
+        y = self.dev.softmax_forward(xc)
+        return y, lambda go: self.dev.softmax_backward(y, go.to(self.dtype).to(self.dev.device).contiguous())
 
     def host(self, t):
         return t.detach().cpu().to(torch.float64)

@@ -5,6 +5,7 @@ Each test body follows the dfdx test of the same name:
   matmul  — dfdx-core/src/tensor_ops/matmul/mod.rs:367-410, :529-702
   linear  — dfdx/src/nn/layers/linear.rs:97-204   (x.matmul(weight.permute()) + bias)
   conv2d  — dfdx-core/src/tensor_ops/conv2d/tests.rs:11-196, :252-402
+  softmax — dfdx-core/src/tensor_ops/softmax.rs:111-196
 and runs on the CPU oracle (pins the oracle; no GPU) and on the CUDA device (marked gpu) with the
 reference's absolute tolerances (1e-6 for f32/f64, 1e-2 for f16; dfdx-core/src/lib.rs:236-270).
 """
@@ -203,6 +204,23 @@ def test_normalize_last_axis(be, name):
     r, bwd = be.normalize(x, 1e-5)
     _check(be, r, a[0])
     _check(be, bwd(d_exp_mean(be.host(r))), a[1])
+
+
+# ------------------------------------------------------------------------------------------ softmax
+@pytest.mark.parametrize("name,axis", [("test_softmax_1d", -1), ("test_softmax_2d", 1), ("test_softmax_2d_0th_axis", 0)])
+def test_softmax(be, name, axis):
+    """dfdx-core/src/tensor_ops/softmax.rs:111-196: r = a.softmax::<Axis>(); l = r * mask; g = l.mean().backward().
+    The kernels reduce over the last axis; the 0th-axis test runs on the transposed matrix."""
+    if be.dtype == torch.float64 and be.name == "cuda":
+        pytest.skip("the row-wise kernels serve f32 and f16")
+    t, a = _split(golden("softmax")[name])
+    x, mask = be.tensor(t[0]), torch.tensor(t[1], dtype=torch.float64)
+    tr = (lambda v: v.t()) if axis == 0 else (lambda v: v)
+    r, bwd = be.softmax(tr(x))
+    _check(be, tr(be.host(r)), a[0])
+    _check(be, tr(be.host(r)) * mask, a[1])
+    g = bwd(tr(mask / mask.numel()).contiguous())
+    _check(be, tr(be.host(g)), a[2])
 
 
 # ------------------------------------------------------------------------------------------ conv2d

@@ -63,3 +63,47 @@ def test_bias_grad(cuda_dev, oracle, dtype, shape):
     cuda_dev.bias_grad(go, out)
     want = go.cpu().double().reshape(-1, shape[-1]).sum(0)
     assert oracle.rel_frobenius(out - 3.0, want) <= 1e-5
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+@pytest.mark.parametrize("shape", [(5, 3), (300, 512), (77, 520), (33, 1000), (64, 37), (4, 16, 128), (2050, 1024),
+                                   (9, 2048), (3, 5000)], ids=lambda s: "x".join(map(str, s)))
+def test_softmax_forward_backward(cuda_dev, oracle, dtype, shape):
+    """softmax over the last axis with the preceding scalar multiply folded in, forward and backward (written and
+    accumulated), against the f64 restatement of dfdx's op sequence; rows keep their sum of 1."""
+    g = gen(sum(shape) + 1)
+    alpha = 0.125
+    x = (torch.randn(*shape, generator=g, dtype=torch.float64) * 6).to(dtype).to(cuda_dev.device)
+    go = torch.randn(*shape, generator=g, dtype=torch.float64).to(dtype).to(cuda_dev.device)
+    y = cuda_dev.softmax_forward(x, alpha)
+    want, bwd = oracle.softmax(x, alpha)
+    assert oracle.rel_frobenius(y, want) <= FROB_TOL[dtype]
+    assert (y.double().sum(-1) - 1).abs().max().item() <= (2e-2 if dtype == torch.float16 else 1e-5)
+    # the backward reads the stored (rounded) y: the oracle is given the same y
+    wx = alpha * y.cpu().double() * (go.cpu().double() - (go.cpu().double() * y.cpu().double()).sum(-1, keepdim=True))
+    gx = cuda_dev.softmax_backward(y, go, alpha)
+    tol = FROB_TOL[dtype] * (2 if dtype == torch.float16 else 1)
+    assert oracle.rel_frobenius(gx, wx) <= tol
+    assert oracle.rel_frobenius(gx, bwd(go)) <= (8e-3 if dtype == torch.float16 else 1e-5)
+    acc = torch.ones_like(gx)
+    cuda_dev.softmax_backward(y, go, alpha, accumulate_into=acc)
+    assert oracle.rel_frobenius(acc, wx + 1.0) <= tol
+
+
+def test_softmax_extremes_and_strided_rows(cuda_dev, oracle):
+    """Large magnitudes do not overflow (the row maximum is subtracted first), and rows may be padded views."""
+    dev = cuda_dev
+    x = torch.tensor([[1e4, 1e4 - 1.0, -1e4, 0.0], [-3e4, -3e4, -3e4, -3e4]], device=dev.device)
+    y = dev.softmax_forward(x)
+    want, _ = oracle.softmax(x)
+    assert torch.isfinite(y).all()
+    assert oracle.rel_frobenius(y, want) <= 1e-5
+    base = torch.randn(40, 72, generator=gen(5)).to(dev.device)
+    view = base[:, :65]                                           # leading dimension 72, 65 columns: element-wise path
+    y = dev.softmax_forward(view)
+    want, _ = oracle.softmax(view)
+    assert oracle.rel_frobenius(y, want) <= 1e-5
+    x64 = torch.zeros(2, 8, dtype=torch.float64, device=dev.device)
+    with pytest.raises(dfdx_b200.B200Error) as e:
+        dev.softmax_forward(x64)
+    assert e.value.status == _lib.ERR_UNSUPPORTED
