@@ -61,6 +61,7 @@ SIGNATURES = {
     "b200_set_capture_split_k": (_i, [_i]),
     "b200_set_wait_limit": (_i, [C.c_longlong]),
     "b200_set_max_ctas": (_i, [_i]),
+    "b200_set_tail_split": (_i, [_i]),
     "b200_selftest_bounded_wait": (_i, [C.c_longlong, C.POINTER(C.c_longlong), _vp]),
     "b200_launch_count": (C.c_uint64, []),
     "b200_tensor_launch_count": (C.c_uint64, []),

@@ -37,6 +37,7 @@ void tc_set_split_mode(int mode);
 void tc_set_capture_split(int on);
 void tc_set_wait_limit(long long cycles);
 void tc_set_max_ctas(int n);
+void tc_set_tail_mode(int mode);
 int tc_wait_selftest(long long limit, long long* cycles, cudaStream_t stream);
 
 namespace {
@@ -237,6 +238,13 @@ int b200_set_capture_split_k(int on) {
 int b200_set_max_ctas(int n) {
   if (n < 0) return B200_ERR_UNSUPPORTED;
   tc_set_max_ctas(n);
+  return B200_OK;
+}
+
+/* Testing hook: 0 (default) the planner may cut the tiles of a last, partial wave along K; 1 never. */
+int b200_set_tail_split(int mode) {
+  if (mode != 0 && mode != 1) return B200_ERR_UNSUPPORTED;
+  tc_set_tail_mode(mode);
   return B200_OK;
 }
 

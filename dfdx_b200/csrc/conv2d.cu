@@ -366,27 +366,49 @@ std::atomic<size_t> g_conv_group_bytes{CONV_GROUP_BYTES_DEFAULT};
 // of the filters.
 
 // (B, C, H, W) through strides -> (B, H, W, G*cpad); channel c = g*cg + ci goes to g*cpad + ci, the rest is zero.
+// A block moves a tile of 32 output channels x 128 pixels through shared memory: coalesced 128-byte reads along the
+// pixels of each channel plane, 16-byte writes along the channels of each pixel.  The kernel is bound by instruction
+// issue before it is bound by DRAM, so the per-element work is a handful of instructions: the channel -> plane
+// offsets of the tile are worked out once per block, pixel offsets once per thread.
+constexpr int CL_PIX = 128, CL_CH = 32;
 __global__ void __launch_bounds__(256) to_channels_last_kernel(const float* __restrict__ in, const Strides4 st,
                                                                float* __restrict__ out, const int cg, const int cpad,
                                                                const int ctot, const int hw, const int w) {
-  __shared__ float tile[32][33];
-  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
-  const int64_t b = blockIdx.z;
-  const int p0 = blockIdx.x * 32, c0 = blockIdx.y * 32;
-  const int p = p0 + tx, y = p / w, x = p - y * w;
-#pragma unroll
-  for (int j = ty; j < 32; j += 8) {
-    const int cp = c0 + j, g = cp / cpad, ci = cp - g * cpad;
-    float v = 0.f;
-    if (cp < ctot && ci < cg && p < hw)
-      v = in[b * st.s[0] + (int64_t)(g * cg + ci) * st.s[1] + (int64_t)y * st.s[2] + (int64_t)x * st.s[3]];
-    tile[j][tx] = v;
+  __shared__ float tile[CL_CH][CL_PIX + 1];
+  __shared__ long long chan_off[CL_CH];                      // offset of the tile's channel planes; -1: padding
+  const int tid = threadIdx.x;
+  const long long b = blockIdx.z;
+  const int p0 = blockIdx.x * CL_PIX, c0 = blockIdx.y * CL_CH;
+  if (tid < CL_CH) {
+    const int cp = c0 + tid, g = cp / cpad, ci = cp - g * cpad;
+    chan_off[tid] = (cp < ctot && ci < cg) ? (long long)(g * cg + ci) * st.s[1] : -1;
+  }
+  // this thread's pixel (the same for all its loads) and its offset inside a plane
+  const int px = tid & (CL_PIX - 1), p = p0 + px;
+  long long poff = -1;
+  if (p < hw) {
+    const int y = p / w, x = p - y * w;
+    poff = b * st.s[0] + (long long)y * st.s[2] + (long long)x * st.s[3];
   }
   __syncthreads();
 #pragma unroll
-  for (int j = ty; j < 32; j += 8) {
-    const int pp = p0 + j, cp = c0 + tx;
-    if (pp < hw && cp < ctot) out[(b * hw + pp) * ctot + cp] = tile[tx][j];
+  for (int k = 0; k < CL_CH / 2; ++k) {
+    const int row = 2 * k + (tid >> 7);
+    const long long co = chan_off[row];
+    tile[row][px] = (co >= 0 && poff >= 0) ? __ldg(in + co + poff) : 0.f;
+  }
+  __syncthreads();
+  // 8 lanes cover the 32 channels of one pixel with 16-byte stores; a warp writes 4 pixels per instruction
+  const int c4 = (tid & 7) * 4, pl = (tid >> 3) & 3, wq = tid >> 5;
+  if (c0 + c4 < ctot) {
+#pragma unroll
+    for (int it = 0; it < CL_PIX / 32; ++it) {
+      const int q = wq * (CL_PIX / 8) + it * 4 + pl;
+      if (p0 + q < hw) {
+        const float4 v = make_float4(tile[c4][q], tile[c4 + 1][q], tile[c4 + 2][q], tile[c4 + 3][q]);
+        *reinterpret_cast<float4*>(out + ((b * hw + p0 + q) * ctot + c0 + c4)) = v;
+      }
+    }
   }
 }
 
@@ -434,7 +456,7 @@ int64_t round_up(int64_t x, int64_t to) { return (x + to - 1) / to * to; }
 int launch_to_channels_last(const float* in, const Strides4& st, float* out, int64_t batch, int64_t groups, int64_t cg,
                             int64_t cpad, int64_t h, int64_t w, cudaStream_t stream) {
   const int64_t ctot = groups * cpad, hw = h * w;
-  dim3 grid((unsigned)((hw + 31) / 32), (unsigned)((ctot + 31) / 32), (unsigned)batch);
+  dim3 grid((unsigned)((hw + CL_PIX - 1) / CL_PIX), (unsigned)((ctot + CL_CH - 1) / CL_CH), (unsigned)batch);
   to_channels_last_kernel<<<grid, 256, 0, stream>>>(in, st, out, (int)cg, (int)cpad, (int)ctot, (int)hw, (int)w);
   count_launch(false);
   return note_cuda_error(cudaGetLastError(), "to_channels_last launch");

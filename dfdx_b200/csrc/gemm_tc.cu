@@ -353,7 +353,6 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_const
   __shared__ __align__(8) uint64_t bar_tempty[2];
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
-  __shared__ int cv_tab[CV == 2 ? 3 * (BN / 32) : 1];      // CV 2: per 32-column chunk of the tile, its image box
 
   const uint32_t smem_base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -389,55 +388,105 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_const
 
   if (wg == 2) {
     setmaxnreg_dec_low();
-    if (warp == PRODUCER_WARP && lane == 0) {
+    if (warp == PRODUCER_WARP && (CV == 2 || lane == 0)) {
       // ---------------------------------------------------------------- TMA producer
-      uint32_t it = 0;
+      // One thread (CV 2: one warp).  Its instruction stream is a chain of dependent operations at some 15-20 clocks
+      // each, so everything a k-block needs beyond the loads themselves is kept out of the loop: ring position, tap
+      // and pixel counters advance by increments, divisions happen once per work unit.
+      uint32_t ring_s = 0, ring_ph = 0;                    // stage ring position and its phase bit
       bool ok = true;
       for (long long unit = blockIdx.x; ok && unit < g.total_units; unit += gridDim.x) {
         const Unit un = decode_unit(g, unit, total_kb);
         const TileCoord t = decode_tile(g, un.tile);
-        if constexpr (CV == 2) {
-          // the image box each 32-column chunk of this tile reads: (channel, column shift, row shift) of its tap
-          for (int j = 0; j < g.tile_cols / 32; ++j) {
-            const int n = t.nt * g.tile_cols + j * 32, tap = n / g.cv_cpad, k1 = tap / g.cv_kw;
-            cv_tab[3 * j] = n - tap * g.cv_cpad;
-            cv_tab[3 * j + 1] = g.cv_w0 + (tap - k1 * g.cv_kw) * g.cv_dw;
-            cv_tab[3 * j + 2] = tap < g.cv_taps ? g.cv_h0 + k1 * g.cv_dh : (1 << 28);   // past the last tap: zero fill
+        if constexpr (CV == 0) {
+          int r = un.kb_lo / g.k_blocks, kx = (un.kb_lo - r * g.k_blocks) * C::BK;
+          const int k_end = g.k_blocks * C::BK;
+          const int ax = g.a_x1 * t.ib1, ay = g.a_y0 * t.ib0, bx = g.b_x1 * t.ib1, by = g.b_y0 * t.ib0;
+          for (int i = un.kb_lo; i < un.kb_hi; ++i) {
+            const uint32_t s = ring_s, ph = ring_ph;
+            if (++ring_s == (uint32_t)STAGES) { ring_s = 0; ring_ph ^= 1u; }
+            if (!mbar_wait(smem_u32(&bar_empty[s]), ph ^ 1u, abortp, g.wait_limit)) { ok = false; break; }
+            const uint32_t full = smem_u32(&bar_full[s]);
+            const uint32_t a_dst = smem_base + s * C::STAGE_BYTES;
+            mbar_expect_tx(full, C::RAW_BYTES);
+            load_operand<BM, C::BK, C::CH, C::MN_LBO>(a_dst, &tma_a, full, g.a_ld, t.mt * BM, kx, ax + g.a_xr * r, ay);
+            load_operand<BN, C::BK, C::CH, C::MN_LBO>(a_dst + C::A_BYTES, &tma_b, full, g.b_ld, t.nt * BN, kx,
+                                                       bx + g.b_xr * r, by);
+            kx += C::BK;
+            if (kx == k_end) { kx = 0; ++r; }
           }
-        }
-        for (int i = un.kb_lo; i < un.kb_hi; ++i, ++it) {
-          const int r = i / g.k_blocks, kb = i - r * g.k_blocks;
-          const int s = it % STAGES;
-          const uint32_t ph = (it / STAGES) & 1u;
-          if (!mbar_wait(smem_u32(&bar_empty[s]), ph ^ 1u, abortp, g.wait_limit)) { ok = false; break; }
-          const uint32_t full = smem_u32(&bar_full[s]);
-          const uint32_t a_dst = smem_base + s * C::STAGE_BYTES;
-          if constexpr (CV == 1) {
-            // k-block = (tap, block of 16 channels): A = the re-laid-out filters (k = tap * channels + channel), B = one
-            // box of the channels-last image shifted by the tap; pixels outside the image arrive as zeros
-            mbar_expect_tx(full, C::A_BYTES + g.b_tx_bytes);
-            const int tap = kb / g.cv_cblocks, cb = kb - tap * g.cv_cblocks, k1 = tap / g.cv_kw, k2 = tap - k1 * g.cv_kw;
-            tma_load_4d(a_dst, &tma_a, full, kb * C::BK, t.mt * BM, t.ib1, 0);
-            tma_load_4d(a_dst + C::A_BYTES, &tma_b, full, t.ib1 * g.cv_cpad + cb * C::BK, g.cv_w0 + k2 * g.cv_dw,
-                        t.nt * g.cv_rows + g.cv_h0 + k1 * g.cv_dh, t.ib0);
-            continue;
+        } else if constexpr (CV == 1) {
+          // k-block = (tap, block of 16 channels): A = the re-laid-out filters (k = tap * channels + channel), B = one
+          // box of the channels-last image shifted by the tap; pixels outside the image arrive as zeros
+          int tap = un.kb_lo / g.cv_cblocks, cb = un.kb_lo - tap * g.cv_cblocks;
+          int k1 = tap / g.cv_kw, k2 = tap - k1 * g.cv_kw;
+          int kx = un.kb_lo * C::BK, bw = g.cv_w0 + k2 * g.cv_dw, bh = t.nt * g.cv_rows + g.cv_h0 + k1 * g.cv_dh;
+          int bc = t.ib1 * g.cv_cpad + cb * C::BK;
+          const int bc_end = (t.ib1 + 1) * g.cv_cpad, w_end = g.cv_w0 + g.cv_kw * g.cv_dw;
+          const uint32_t tx = (uint32_t)(C::A_BYTES + g.b_tx_bytes);
+          // The image rows of the NEXT tile of this CTA are asked into L2 now: a tile's first k-block touches all of
+          // its rows for the first time, and that miss would otherwise stall the pipeline at every tile start.
+          if (unit + gridDim.x < g.total_units) {
+            const TileCoord nx = decode_tile(g, decode_unit(g, unit + gridDim.x, total_kb).tile);
+            const int last = (g.cv_taps / g.cv_kw - 1) * g.cv_dh;
+            for (int c = nx.ib1 * g.cv_cpad; c < (nx.ib1 + 1) * g.cv_cpad; c += C::BK) {
+              tma_prefetch_4d(&tma_b, c, g.cv_w0, nx.nt * g.cv_rows + g.cv_h0, nx.ib0);
+              if (last) tma_prefetch_4d(&tma_b, c, g.cv_w0, nx.nt * g.cv_rows + g.cv_h0 + last, nx.ib0);
+            }
           }
-          if constexpr (CV == 2) {
-            // k-block = 16 pixels of output row `oh` of image r: A = that box of grad_out for 128 output channels,
-            // B = for each 32-column chunk the same pixels of the image, shifted by the chunk's tap
-            mbar_expect_tx(full, C::A_BYTES + g.b_tx_bytes);
-            const int oh = kb / g.cv_wblocks, w = (kb - oh * g.cv_wblocks) * C::BK;
-            tma_load_4d(a_dst, &tma_a, full, w, oh, t.mt * BM, r);
-            for (int j = 0; j < g.tile_cols / 32; ++j)
-              tma_load_4d(a_dst + C::A_BYTES + j * C::MN_LBO, &tma_b, full, cv_tab[3 * j], w + cv_tab[3 * j + 1],
-                          oh + cv_tab[3 * j + 2], r);
-            continue;
+          for (int i = un.kb_lo; i < un.kb_hi; ++i) {
+            const uint32_t s = ring_s, ph = ring_ph;
+            if (++ring_s == (uint32_t)STAGES) { ring_s = 0; ring_ph ^= 1u; }
+            if (!mbar_wait(smem_u32(&bar_empty[s]), ph ^ 1u, abortp, g.wait_limit)) { ok = false; break; }
+            const uint32_t full = smem_u32(&bar_full[s]);
+            const uint32_t a_dst = smem_base + s * C::STAGE_BYTES;
+            mbar_expect_tx(full, tx);
+            tma_load_4d(a_dst, &tma_a, full, kx, t.mt * BM, t.ib1, 0);
+            tma_load_4d(a_dst + C::A_BYTES, &tma_b, full, bc, bw, bh, t.ib0);
+            kx += C::BK; bc += C::BK;
+            if (bc == bc_end) {                              // next tap
+              bc -= g.cv_cpad; bw += g.cv_dw;
+              if (bw == w_end) { bw = g.cv_w0; bh += g.cv_dh; }
+            }
           }
-          mbar_expect_tx(full, C::RAW_BYTES);
-          load_operand<BM, C::BK, C::CH, C::MN_LBO>(a_dst, &tma_a, full, g.a_ld, t.mt * BM, kb * C::BK,
-                                                     g.a_x1 * t.ib1 + g.a_xr * r, g.a_y0 * t.ib0);
-          load_operand<BN, C::BK, C::CH, C::MN_LBO>(a_dst + C::A_BYTES, &tma_b, full, g.b_ld, t.nt * BN, kb * C::BK,
-                                                     g.b_x1 * t.ib1 + g.b_xr * r, g.b_y0 * t.ib0);
+        } else {
+          // CV 2.  k-block = 16 pixels of output row `oh` of image r: A = that box of grad_out for 128 output channels
+          // (lane 0), B = for each 32-column chunk of the tile the same pixels of the image shifted by the chunk's tap
+          // (lane j + 1 loads chunk j, all chunks in one instruction).
+          const int nch = g.tile_cols / 32;
+          const int n = t.nt * g.tile_cols + (lane - 1) * 32, tap = n / g.cv_cpad, tk1 = tap / g.cv_kw;
+          const bool loader = lane >= 1 && lane <= nch;
+          const int my_c = n - tap * g.cv_cpad, my_w = g.cv_w0 + (tap - tk1 * g.cv_kw) * g.cv_dw;
+          const int my_h = tap < g.cv_taps ? g.cv_h0 + tk1 * g.cv_dh : (1 << 20);   // past the last tap: zero fill
+          const uint32_t my_dst = C::A_BYTES + (uint32_t)(lane - 1) * C::MN_LBO;
+          int r = un.kb_lo / g.k_blocks, rem = un.kb_lo - r * g.k_blocks;
+          int oh = rem / g.cv_wblocks, w = (rem - oh * g.cv_wblocks) * C::BK;
+          const int w_end = g.cv_wblocks * C::BK;
+          const uint32_t tx = (uint32_t)(C::A_BYTES + g.b_tx_bytes);
+          for (int i = un.kb_lo; i < un.kb_hi; ++i) {
+            const uint32_t s = ring_s, ph = ring_ph;
+            if (++ring_s == (uint32_t)STAGES) { ring_s = 0; ring_ph ^= 1u; }
+            if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_empty[s]), ph ^ 1u, abortp, g.wait_limit))) { ok = false; break; }
+            const uint32_t full = smem_u32(&bar_full[s]);
+            const uint32_t a_dst = smem_base + s * C::STAGE_BYTES;
+            if (lane == 0) {
+              mbar_expect_tx(full, tx);
+              tma_load_4d(a_dst, &tma_a, full, w, oh, t.mt * BM, r);
+            }
+            if (loader) tma_load_4d(a_dst + my_dst, &tma_b, full, my_c, w + my_w, oh + my_h, r);
+            {
+              // the same boxes two image rows (8 or so k-blocks) ahead are asked into L2: every fourth k-block starts
+              // new 256-byte segments of 128 grad_out rows, too many misses at once for the ring of stages to cover
+              int pr = r, po = oh + 2;
+              if (po >= g.cv_rows) { po -= g.cv_rows; ++pr; }
+              if (pr < g.red) {
+                if (lane == 0) tma_prefetch_4d(&tma_a, w, po, t.mt * BM, pr);
+                if (loader) tma_prefetch_4d(&tma_b, my_c, w + my_w, po + my_h, pr);
+              }
+            }
+            w += C::BK;
+            if (w == w_end) { w = 0; if (++oh == g.cv_rows) { oh = 0; ++r; } }
+          }
         }
       }
     } else if (warp == MMA_WARP && lane == 0) {
@@ -526,7 +575,7 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_const
       if (!ok) break;
       if (un.kb_lo >= un.kb_hi) continue;               // an empty unit of the stream-K decomposition
       // partial sums (a K slice, or a stream-K range that does not span the tile's whole K) are added atomically
-      const bool partial = g.ksplit > 1 || (g.streamk && !(un.kb_lo == 0 && un.kb_hi == total_kb));
+      const bool partial = g.ksplit > 1 || ((g.streamk || g.tail_split > 1) && !(un.kb_lo == 0 && un.kb_hi == total_kb));
       const int row = t.mt * BM + quad * 32 + lane;
       // columns of this tile: [tile_col0, n_end).  An implicit-convolution tile holds tile_valid columns (whole image
       // rows) and the next tile starts tile_cols further on.
@@ -878,6 +927,7 @@ int build_launch(Launch& L, const Plan& pl, int esize, int tm, int tn, int bmc, 
   g.n_fast = g.n_tiles < g.m_tiles ? 1 : 0;
   g.total_tiles = (long long)g.m_tiles * g.n_tiles * p.b0 * p.b1;
   g.ksplit = 1; g.kb_per_slice = 0; g.total_units = g.total_tiles;   // launch_cfg fills the slice length
+  g.tail_from = 0; g.tail_split = 1; g.tail_kb = 0;
   g.streamk = 0; g.sk_per_cta = 0;
   g.red = (int)p.red;
   g.k_blocks = (int)((p.k + bk - 1) / bk);
@@ -910,6 +960,46 @@ int build_launch(Launch& L, const Plan& pl, int esize, int tm, int tn, int bmc, 
   const long long forced_limit = g_wait_limit.load();
   g.wait_limit = forced_limit > 0 ? forced_limit : 400000000LL + (long long)g.red * g.k_blocks * 40000LL;
   g.status = ds->status;
+  return B200_OK;
+}
+
+// Tail split (f32 kernel, see TcArgs): decides whether the tiles of the last, partial wave are cut along K, fills
+// the arguments and, for outputs that are written rather than added to, zeroes those tiles (they are then summed
+// atomically).  Only for row-major outputs without a fused epilogue; at most MAX_ZEROED tiles are zeroed.
+constexpr int TAIL_MAX_ZEROED = 8;
+std::atomic<int> g_tail_mode{0};   // 0 = choose, 1 = never (testing)
+
+int plan_tail_split(TcArgs& g, int sms, int total_kb, cudaStream_t stream) {
+  if (g_tail_mode.load() == 1 || g.ksplit != 1 || g.streamk || g.fused || g.c_col) return B200_OK;
+  const long long full = g.total_tiles / sms, rem = g.total_tiles % sms;
+  if (full < 1 || rem == 0) return B200_OK;
+  if (!g.beta && rem > TAIL_MAX_ZEROED) return B200_OK;
+  long long split = sms / rem;
+  if (split > total_kb / 4) split = total_kb / 4;          // slices of at least four k-blocks
+  if (split < 2) return B200_OK;
+  const int kb_per = (int)((total_kb + split - 1) / split);
+  split = (total_kb + kb_per - 1) / kb_per;
+  // cost in k-blocks per SM; a unit costs about 8 k-blocks beside its main loop (pipeline fill, epilogue)
+  const double fixed = 8.0, before = (double)(full + 1) * (total_kb + fixed), after = full * (total_kb + fixed) + kb_per + fixed;
+  if (split < 2 || after > 0.95 * before) return B200_OK;
+  g.tail_from = full * sms; g.tail_split = (int)split; g.tail_kb = kb_per;
+  g.total_units = g.tail_from + rem * split;
+  if (!g.beta) {
+    const long long per_batch = (long long)g.m_tiles * g.n_tiles;
+    for (long long tile = g.tail_from; tile < g.total_tiles; ++tile) {
+      const long long bt = tile / per_batch;
+      const int r = (int)(tile - bt * per_batch);
+      const int nt = g.n_fast ? r % g.n_tiles : r / g.m_tiles, mt = g.n_fast ? r / g.n_tiles : r % g.m_tiles;
+      const long long ib1 = bt % g.nb1, ib0 = bt / g.nb1;
+      const long long col0 = (long long)nt * g.tile_cols;
+      long long cols = g.n - col0 < g.tile_valid ? g.n - col0 : g.tile_valid;
+      long long rows = g.m - (long long)mt * BM < BM ? g.m - (long long)mt * BM : BM;
+      float* p = (float*)g.c + ib0 * g.c_b0 + ib1 * g.c_b1 + (long long)mt * BM * g.ldc + col0;
+      const int rc = note_cuda_error(cudaMemset2DAsync(p, (size_t)g.ldc * 4, 0, (size_t)cols * 4, (size_t)rows, stream),
+                                     "cudaMemset2DAsync(tail tiles)");
+      if (rc) return rc;
+    }
+  }
   return B200_OK;
 }
 
@@ -994,6 +1084,10 @@ int launch_cfg(const Plan& pl, cudaStream_t stream, Kernel kernel, int ksplit) {
         return note_cuda_error(cudaEventRecord(ds->split_event, stream), "cudaEventRecord(split-K)");
       }
     }
+  }
+  if constexpr (ESIZE == 4) {
+    const int rc = plan_tail_split(g, grid_sms(ds), total_kb, stream);
+    if (rc) return rc;
   }
   const long long grid = g.total_units < grid_sms(ds) ? g.total_units : grid_sms(ds);
   if (grid <= 0) return B200_OK;
@@ -1141,6 +1235,7 @@ int conv_rows_per_tile(const ConvImplicit& c, int sms) {
 void cv_common_args(TcArgs& g, DeviceState* ds) {
   g.nb1 = 1; g.n_fast = 0;
   g.ksplit = 1; g.streamk = 0; g.sk_per_cta = 0; g.split_out = nullptr; g.split_ld = 0;
+  g.tail_from = 0; g.tail_split = 1; g.tail_kb = 0;
   g.red = 1;
   g.a_mn = 0; g.b_mn = 0; g.a_ld = 0; g.b_ld = 0;
   g.a_x1 = g.a_xr = g.a_y0 = g.b_x1 = g.b_xr = g.b_y0 = 0;
@@ -1218,6 +1313,10 @@ int launch_conv_implicit(const ConvImplicit& c, cudaStream_t stream) {
   g.cv_rows = rows; g.cv_wout = (int)c.w_out;
   const long long forced_limit = g_wait_limit.load();
   g.wait_limit = forced_limit > 0 ? forced_limit : 400000000LL + (long long)g.k_blocks * 40000LL;
+  {
+    const int rc = plan_tail_split(g, sms, g.k_blocks, stream);
+    if (rc) return rc;
+  }
   const long long grid = g.total_units < sms ? g.total_units : sms;
   if (grid <= 0) return B200_OK;
   gemm_tf32x3_kernel<CV_BN, 1><<<(unsigned)grid, CvCfg::THREADS, CvCfg::SMEM_BYTES, stream>>>(L.ma, L.mb, L.mc, L.g);
@@ -1286,6 +1385,7 @@ int launch_conv_implicit_wgrad(const ConvImplicitWgrad& c, cudaStream_t stream) 
   g.total_tiles = (long long)g.m_tiles * g.n_tiles;
   g.red = (int)c.batch;
   g.cv_wblocks = (int)((c.w_out + CvCfg::BK - 1) / CvCfg::BK);
+  g.cv_rows = (int)c.h_out;
   g.k_blocks = (int)(c.h_out * g.cv_wblocks);
   const long long total_kb = (long long)g.red * g.k_blocks;
   // K slices: as many work units as SMs; the slices add into `out` atomically
@@ -1372,6 +1472,7 @@ void tc_set_pair_mode(int mode) { g_pair_mode = mode; }
 void tc_set_store_mode(int mode) { g_store_mode = mode; }
 void tc_set_split_mode(int mode) { g_split_mode = mode; }
 void tc_set_max_ctas(int n) { g_max_ctas = n; }
+void tc_set_tail_mode(int mode) { g_tail_mode = mode; }
 void tc_set_wait_limit(long long cycles) { g_wait_limit = cycles; }
 void tc_set_capture_split(int on) { g_capture_split = on ? 1 : 0; }
 

@@ -334,7 +334,8 @@ __global__ void __launch_bounds__(256) softmax_fwd_kernel(const T* __restrict__ 
   constexpr float LOG2E = 1.4426950408889634f;
   const int lane = threadIdx.x & 31;
   const long long warp0 = (long long)blockIdx.x * 8 + (threadIdx.x >> 5), nwarps = (long long)gridDim.x * 8;
-  const float a2 = alpha * LOG2E;                            // exp(alpha*x - m) = exp2(a2*x - m*log2e)
+  // t = alpha * x is rounded to f32 as the reference's scalar multiply rounds it; the maximum is subtracted before
+  // the change of base, so large inputs lose nothing: exp(t - m) = exp2((t - m) * log2e)
   for (long long r = warp0; r < rows; r += nwarps) {
     const T* xr = x + r * x_ld;
     T* yr = y + r * y_ld;
@@ -347,7 +348,7 @@ __global__ void __launch_bounds__(256) softmax_fwd_kernel(const T* __restrict__ 
         if (c < cols) load_vec(xr, c, cols, vec, f[v]);
 #pragma unroll
         for (int q = 0; q < N; ++q) {
-          f[v][q] = (c + q < cols) ? f[v][q] * a2 : -INFINITY;
+          f[v][q] = (c + q < cols) ? f[v][q] * alpha : -INFINITY;
           mx = fmaxf(mx, f[v][q]);
         }
       }
@@ -357,7 +358,7 @@ __global__ void __launch_bounds__(256) softmax_fwd_kernel(const T* __restrict__ 
 #pragma unroll
       for (int v = 0; v < MAXV; ++v)
 #pragma unroll
-        for (int q = 0; q < N; ++q) { f[v][q] = exp2f(f[v][q] - mx); s += f[v][q]; }
+        for (int q = 0; q < N; ++q) { f[v][q] = exp2f((f[v][q] - mx) * LOG2E); s += f[v][q]; }
       const float inv = 1.f / warp_sum(s);
 #pragma unroll
       for (int v = 0; v < MAXV; ++v) {
@@ -373,7 +374,7 @@ __global__ void __launch_bounds__(256) softmax_fwd_kernel(const T* __restrict__ 
         load_vec(xr, c, cols, vec, f);
 #pragma unroll
         for (int q = 0; q < N; ++q)
-          if (c + q < cols) mx = fmaxf(mx, f[q] * a2);
+          if (c + q < cols) mx = fmaxf(mx, f[q] * alpha);
       }
       mx = warp_max(mx);
       if (mx == -INFINITY) mx = 0.f;
@@ -383,14 +384,14 @@ __global__ void __launch_bounds__(256) softmax_fwd_kernel(const T* __restrict__ 
         load_vec(xr, c, cols, vec, f);
 #pragma unroll
         for (int q = 0; q < N; ++q)
-          if (c + q < cols) s += exp2f(f[q] * a2 - mx);
+          if (c + q < cols) s += exp2f((f[q] * alpha - mx) * LOG2E);
       }
       const float inv = 1.f / warp_sum(s);
       for (int c = lane * N; c < cols; c += 32 * N) {
         float f[N];
         load_vec(xr, c, cols, vec, f);
 #pragma unroll
-        for (int q = 0; q < N; ++q) f[q] = exp2f(f[q] * a2 - mx) * inv;
+        for (int q = 0; q < N; ++q) f[q] = exp2f((f[q] * alpha - mx) * LOG2E) * inv;
         store_vec(yr, c, cols, vec, f);
       }
     }

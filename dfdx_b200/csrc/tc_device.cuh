@@ -77,6 +77,11 @@ __device__ __forceinline__ void tma_load_5d(uint32_t dst, const CUtensorMap* map
       " [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
       ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4) : "memory");
 }
+// Tiled 4-D prefetch of a box into L2 (no shared-memory destination, nothing to wait for).
+__device__ __forceinline__ void tma_prefetch_4d(const CUtensorMap* map, int c0, int c1, int c2, int c3) {
+  asm volatile("cp.async.bulk.prefetch.tensor.4d.L2.global.tile [%0, {%1, %2, %3, %4}];"
+               ::"l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
+}
 // Tiled 4-D TMA store shared -> global (bulk async-group completion).  Rows / columns of the box that fall outside
 // the tensor are not written.
 __device__ __forceinline__ void tma_store_4d(const CUtensorMap* map, uint32_t src, int c0, int c1, int c2, int c3) {
@@ -276,6 +281,11 @@ struct TcArgs {
   long long total_tiles;
   int ksplit, kb_per_slice;       // f32 kernel: K is cut into ksplit slices of kb_per_slice k-blocks; a work unit is
   long long total_units;          // (tile, slice); slices of one tile add their partial results atomically
+  // f32 kernel, ksplit == 1: when the tiles do not fill a whole number of waves, the tiles of the last, partial wave
+  // (tile index >= tail_from) are cut into tail_split K slices of tail_kb k-blocks each, so that every SM gets a
+  // share of them; those slices add their partial results atomically like split-K slices.  tail_split == 1: off.
+  long long tail_from;
+  int tail_split, tail_kb;
   int streamk;                    // f32 kernel: the (tile, k-block) space is cut into one contiguous range per CTA
   long long sk_per_cta;           // k-blocks per CTA; a unit is the part of one tile inside the CTA's range (may be empty)
   float* split_out;               // f16 kernel with ksplit > 1: f32 scratch (m x split_ld, zeroed) that takes the
@@ -317,7 +327,7 @@ struct TcArgs {
   int cv_cpad;                    // padded channels per group in the channels-last image
   int cv_kw, cv_taps;             // filter taps per row, taps in all
   int cv_w0, cv_dw, cv_h0, cv_dh; // tap (k1, k2) reads the image at (row + cv_h0 + k1 * cv_dh, col + cv_w0 + k2 * cv_dw)
-  int cv_rows, cv_wout;           // CV 1: image rows and pixels per row of one N tile
+  int cv_rows, cv_wout;           // CV 1: image rows and pixels per row of one N tile; CV 2: cv_rows = output rows per image
   int cv_wblocks;                 // CV 2: k-blocks per image row (ceil(w_out / 16))
 };
 
@@ -528,6 +538,13 @@ __device__ __forceinline__ Unit decode_unit(const TcArgs& g, long long unit, int
     const long long lo = start > t0 ? start : t0, hi = end < t0 + total_kb ? end : t0 + total_kb;
     if (hi <= lo || u.tile >= g.total_tiles) { u.tile = 0; u.kb_lo = u.kb_hi = 0; }   // nothing of that tile in the range
     else { u.kb_lo = (int)(lo - t0); u.kb_hi = (int)(hi - t0); }
+    return u;
+  }
+  if (g.tail_split > 1 && unit >= g.tail_from) {
+    const long long v = unit - g.tail_from, q = v / g.tail_split;
+    u.tile = g.tail_from + q;
+    u.kb_lo = (int)(v - q * g.tail_split) * g.tail_kb;
+    u.kb_hi = u.kb_lo + g.tail_kb < total_kb ? u.kb_lo + g.tail_kb : total_kb;
     return u;
   }
   u.tile = unit / g.ksplit;

@@ -147,6 +147,12 @@ int b200_set_conv_lowering(int grad_img_mode, size_t group_bytes);
  * stream-K decomposition (the (tile, k-block) space cut into one equal contiguous range per SM; tiles cut by a
  * range boundary are summed atomically), which the planner never picks on its own. */
 int b200_set_split_k(int mode);
+/* Tail split of the f32 tensor-core kernel (testing / profiling).  The kernel is persistent: tiles are dealt round
+ * robin to one CTA per SM, so a tile count just above a multiple of the SM count leaves most SMs idle during the last
+ * round.  mode 0 (default): when that costs more than about 5 %, the tiles of the last, partial round are cut into K
+ * slices spread over all SMs; their partial results are added atomically (as with split-K, the last bits of those
+ * output tiles can then differ between runs; outputs with beta = 0 have those tiles zeroed first).  mode 1: never. */
+int b200_set_tail_split(int mode);
 /* The split-K of an f16 GEMM keeps its partial sums in the one f32 scratch the device owns; uses on different
  * streams are ordered by an event recorded when the GEMM is enqueued.  A stream capture cannot take part in that
  * ordering (a replay neither waits on nor records the event), so by default (0) a GEMM enqueued on a capturing

@@ -462,6 +462,30 @@ def test_config3_attention_matmuls_f16(cuda_dev, oracle):
     assert torch.equal(s2, s)
 
 
+@pytest.mark.parametrize("layout", ["rrr", "rcr", "crr"])
+def test_tail_split_f32(cuda_dev, oracle, layout):
+    """150 tiles on 148 SMs: the two tiles of the second round are cut along K over all SMs and summed atomically
+    (beta 0: those tiles are zeroed first, the output is NaN-poisoned; beta 1), ragged edges included; the same
+    problems with the tail split switched off give the same results within the tolerance."""
+    dev = cuda_dev
+    dev.set_path(dfdx_b200.PATH_TENSOR)
+    assert dev.lib.b200_set_tile_n(256) == 0
+    try:
+        for mode in (0, 1):
+            assert dev.lib.b200_set_tail_split(mode) == 0
+            for i, (m, k, n) in enumerate([(640, 1024, 7680), (5 * 128 - 24, 520, 30 * 256 - 40)]):
+                for beta in (0, 1):
+                    l0 = dev.lib.b200_launch_count()
+                    check_gemm(dev, oracle, m, k, n, layout[0], layout[1], layout[2], beta, torch.float32, pad=8,
+                               seed=700 + i)
+                    assert dev.lib.b200_launch_count() - l0 == 1
+    finally:
+        dev.lib.b200_set_tail_split(0)
+        dev.lib.b200_set_tile_n(0)
+        dev.set_path(dfdx_b200.PATH_AUTO)
+    assert dev.lib.b200_set_tail_split(2) == dfdx_b200._lib.ERR_UNSUPPORTED
+
+
 # --------------------------------------------------------------------------------- streams, capture, bounded waits
 @pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
 def test_backward_on_two_streams(cuda_dev, oracle, dtype):
