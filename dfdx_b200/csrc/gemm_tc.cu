@@ -424,16 +424,6 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_const
           int bc = t.ib1 * g.cv_cpad + cb * C::BK;
           const int bc_end = (t.ib1 + 1) * g.cv_cpad, w_end = g.cv_w0 + g.cv_kw * g.cv_dw;
           const uint32_t tx = (uint32_t)(C::A_BYTES + g.b_tx_bytes);
-          // The image rows of the NEXT tile of this CTA are asked into L2 now: a tile's first k-block touches all of
-          // its rows for the first time, and that miss would otherwise stall the pipeline at every tile start.
-          if (unit + gridDim.x < g.total_units) {
-            const TileCoord nx = decode_tile(g, decode_unit(g, unit + gridDim.x, total_kb).tile);
-            const int last = (g.cv_taps / g.cv_kw - 1) * g.cv_dh;
-            for (int c = nx.ib1 * g.cv_cpad; c < (nx.ib1 + 1) * g.cv_cpad; c += C::BK) {
-              tma_prefetch_4d(&tma_b, c, g.cv_w0, nx.nt * g.cv_rows + g.cv_h0, nx.ib0);
-              if (last) tma_prefetch_4d(&tma_b, c, g.cv_w0, nx.nt * g.cv_rows + g.cv_h0 + last, nx.ib0);
-            }
-          }
           for (int i = un.kb_lo; i < un.kb_hi; ++i) {
             const uint32_t s = ring_s, ph = ring_ph;
             if (++ring_s == (uint32_t)STAGES) { ring_s = 0; ring_ph ^= 1u; }
@@ -459,9 +449,11 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_const
           const int my_c = n - tap * g.cv_cpad, my_w = g.cv_w0 + (tap - tk1 * g.cv_kw) * g.cv_dw;
           const int my_h = tap < g.cv_taps ? g.cv_h0 + tk1 * g.cv_dh : (1 << 20);   // past the last tap: zero fill
           const uint32_t my_dst = C::A_BYTES + (uint32_t)(lane - 1) * C::MN_LBO;
+          // k-block = a box of cv_bw x cv_bh = 16 output pixels (the shape that wastes least on the image's edges)
           int r = un.kb_lo / g.k_blocks, rem = un.kb_lo - r * g.k_blocks;
-          int oh = rem / g.cv_wblocks, w = (rem - oh * g.cv_wblocks) * C::BK;
-          const int w_end = g.cv_wblocks * C::BK;
+          int oh = rem / g.cv_wblocks, w = (rem - oh * g.cv_wblocks) * g.cv_bw;
+          oh *= g.cv_bh;
+          const int w_end = g.cv_wblocks * g.cv_bw, h_end = g.cv_rows * g.cv_bh;
           const uint32_t tx = (uint32_t)(C::A_BYTES + g.b_tx_bytes);
           for (int i = un.kb_lo; i < un.kb_hi; ++i) {
             const uint32_t s = ring_s, ph = ring_ph;
@@ -474,18 +466,8 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_const
               tma_load_4d(a_dst, &tma_a, full, w, oh, t.mt * BM, r);
             }
             if (loader) tma_load_4d(a_dst + my_dst, &tma_b, full, my_c, w + my_w, oh + my_h, r);
-            {
-              // the same boxes two image rows (8 or so k-blocks) ahead are asked into L2: every fourth k-block starts
-              // new 256-byte segments of 128 grad_out rows, too many misses at once for the ring of stages to cover
-              int pr = r, po = oh + 2;
-              if (po >= g.cv_rows) { po -= g.cv_rows; ++pr; }
-              if (pr < g.red) {
-                if (lane == 0) tma_prefetch_4d(&tma_a, w, po, t.mt * BM, pr);
-                if (loader) tma_prefetch_4d(&tma_b, my_c, w + my_w, po + my_h, pr);
-              }
-            }
-            w += C::BK;
-            if (w == w_end) { w = 0; if (++oh == g.cv_rows) { oh = 0; ++r; } }
+            w += g.cv_bw;
+            if (w == w_end) { w = 0; oh += g.cv_bh; if (oh == h_end) { oh = 0; ++r; } }
           }
         }
       }
@@ -956,7 +938,7 @@ int build_launch(Launch& L, const Plan& pl, int esize, int tm, int tn, int bmc, 
   g.xform_mode = g_xform_mode;
   g.tile_cols = tn; g.tile_valid = tn; g.mma_n = tn; g.b_tx_bytes = 0;
   g.cv_cblocks = 1; g.cv_cpad = 16; g.cv_kw = 1; g.cv_taps = 1; g.cv_w0 = g.cv_dw = g.cv_h0 = g.cv_dh = 0;
-  g.cv_rows = 1; g.cv_wout = 1; g.cv_wblocks = 1;
+  g.cv_rows = 1; g.cv_wout = 1; g.cv_wblocks = 1; g.cv_bw = 16; g.cv_bh = 1;
   const long long forced_limit = g_wait_limit.load();
   g.wait_limit = forced_limit > 0 ? forced_limit : 400000000LL + (long long)g.red * g.k_blocks * 40000LL;
   g.status = ds->status;
@@ -967,6 +949,17 @@ int build_launch(Launch& L, const Plan& pl, int esize, int tm, int tn, int bmc, 
 // the arguments and, for outputs that are written rather than added to, zeroes those tiles (they are then summed
 // atomically).  Only for row-major outputs without a fused epilogue; at most MAX_ZEROED tiles are zeroed.
 constexpr int TAIL_MAX_ZEROED = 8;
+struct TailTiles { float* p[TAIL_MAX_ZEROED]; int rows[TAIL_MAX_ZEROED], cols[TAIL_MAX_ZEROED]; };
+// Zeroes up to TAIL_MAX_ZEROED output tiles (blockIdx.x: tile, rows x cols floats, row pitch ldc; blockIdx.y: a
+// group of 8 of its rows) in one launch.
+__global__ void __launch_bounds__(256) zero_tiles_kernel(const TailTiles t, long long ldc) {
+  float* p = t.p[blockIdx.x];
+  const int rows = t.rows[blockIdx.x], cols = t.cols[blockIdx.x];
+  const int r = blockIdx.y * 8 + (threadIdx.x >> 5);
+  if (r >= rows) return;
+  float* row = p + (long long)r * ldc;
+  for (int c = threadIdx.x & 31; c < cols; c += 32) row[c] = 0.f;
+}
 std::atomic<int> g_tail_mode{0};   // 0 = choose, 1 = never (testing)
 
 int plan_tail_split(TcArgs& g, int sms, int total_kb, cudaStream_t stream) {
@@ -986,19 +979,21 @@ int plan_tail_split(TcArgs& g, int sms, int total_kb, cudaStream_t stream) {
   g.total_units = g.tail_from + rem * split;
   if (!g.beta) {
     const long long per_batch = (long long)g.m_tiles * g.n_tiles;
-    for (long long tile = g.tail_from; tile < g.total_tiles; ++tile) {
+    TailTiles tt;
+    int cnt = 0;
+    for (long long tile = g.tail_from; tile < g.total_tiles; ++tile, ++cnt) {
       const long long bt = tile / per_batch;
       const int r = (int)(tile - bt * per_batch);
       const int nt = g.n_fast ? r % g.n_tiles : r / g.m_tiles, mt = g.n_fast ? r / g.n_tiles : r % g.m_tiles;
       const long long ib1 = bt % g.nb1, ib0 = bt / g.nb1;
       const long long col0 = (long long)nt * g.tile_cols;
-      long long cols = g.n - col0 < g.tile_valid ? g.n - col0 : g.tile_valid;
-      long long rows = g.m - (long long)mt * BM < BM ? g.m - (long long)mt * BM : BM;
-      float* p = (float*)g.c + ib0 * g.c_b0 + ib1 * g.c_b1 + (long long)mt * BM * g.ldc + col0;
-      const int rc = note_cuda_error(cudaMemset2DAsync(p, (size_t)g.ldc * 4, 0, (size_t)cols * 4, (size_t)rows, stream),
-                                     "cudaMemset2DAsync(tail tiles)");
-      if (rc) return rc;
+      tt.cols[cnt] = (int)(g.n - col0 < g.tile_valid ? g.n - col0 : g.tile_valid);
+      tt.rows[cnt] = (int)(g.m - (long long)mt * BM < BM ? g.m - (long long)mt * BM : BM);
+      tt.p[cnt] = (float*)g.c + ib0 * g.c_b0 + ib1 * g.c_b1 + (long long)mt * BM * g.ldc + col0;
     }
+    zero_tiles_kernel<<<dim3((unsigned)cnt, BM / 8), 256, 0, stream>>>(tt, g.ldc);
+    const int rc = note_cuda_error(cudaGetLastError(), "zero_tiles launch");
+    if (rc) return rc;
   }
   return B200_OK;
 }
@@ -1244,7 +1239,7 @@ void cv_common_args(TcArgs& g, DeviceState* ds) {
   g.status = ds->status;
   g.fused = 0; g.alpha = 1.f; g.bias = nullptr; g.bias_row = 0; g.act = B200_ACT_NONE;
   g.cv_cblocks = 1; g.cv_cpad = 16; g.cv_kw = 1; g.cv_taps = 1; g.cv_w0 = g.cv_dw = g.cv_h0 = g.cv_dh = 0;
-  g.cv_rows = 1; g.cv_wout = 1; g.cv_wblocks = 1;
+  g.cv_rows = 1; g.cv_wout = 1; g.cv_wblocks = 1; g.cv_bw = 16; g.cv_bh = 1;
 }
 
 }  // namespace
@@ -1345,7 +1340,7 @@ bool conv_implicit_wgrad_ok(const ConvImplicitWgrad& c) {
   if (c.cpad < 32 || c.cpad % 32 || c.c_total % 4 || c.kh < 1 || c.kw < 1 || c.gout_bs % 4) return false;
   const int64_t lim = 0x7fffff00LL;
   if (c.batch > lim || c.c_total > lim || c.h_img > lim || c.w_img > lim || c.h_out * c.w_out > lim ||
-      (int64_t)c.kh * c.kw * c.cpad > lim || c.m > lim || c.h_out * ((c.w_out + 15) / 16) > lim / (c.batch > 0 ? c.batch : 1))
+      (int64_t)c.kh * c.kw * c.cpad > lim || c.m > lim || c.h_out * c.w_out > lim / (c.batch > 0 ? c.batch : 1))
     return false;
   if (((uintptr_t)c.img_cl | (uintptr_t)c.gout | (uintptr_t)c.out) & 15) return false;
   return true;
@@ -1358,12 +1353,22 @@ int launch_conv_implicit_wgrad(const ConvImplicitWgrad& c, cudaStream_t stream) 
   const int sms = grid_sms(ds);
   const int64_t taps = (int64_t)c.kh * c.kw, kr = taps * c.cpad, npos = c.h_out * c.w_out;
   const int tile_cols = wgrad_tile_cols(kr);
+  // the 16 output pixels of a k-block form a box of bw x bh pixels: the shape with the fewest boxes per image
+  int bw = 16, bh = 1;
+  {
+    long long best = -1;
+    const int shapes[3][2] = {{16, 1}, {8, 2}, {4, 4}};
+    for (auto& sh : shapes) {
+      const long long n = ((c.w_out + sh[0] - 1) / sh[0]) * ((c.h_out + sh[1] - 1) / sh[1]);
+      if (best < 0 || n < best) { best = n; bw = sh[0]; bh = sh[1]; }
+    }
+  }
   Launch L;
   // A: grad_out of this group as (x, y, channel, image); one box = 16 pixels of one row x 128 channels
   {
     const uint64_t dims[4] = {(uint64_t)c.w_out, (uint64_t)c.h_out, (uint64_t)c.m, (uint64_t)c.batch};
     const uint64_t st[3] = {(uint64_t)c.w_out * 4, (uint64_t)npos * 4, (uint64_t)c.gout_bs * 4};
-    const uint32_t box[4] = {(uint32_t)CvCfg::BK, 1, (uint32_t)BM, 1};
+    const uint32_t box[4] = {(uint32_t)bw, (uint32_t)bh, (uint32_t)BM, 1};
     const int rc = encode_map_f32(&L.ma, c.gout, dims, st, box, CU_TENSOR_MAP_SWIZZLE_64B);
     if (rc) return rc;
   }
@@ -1372,7 +1377,7 @@ int launch_conv_implicit_wgrad(const ConvImplicitWgrad& c, cudaStream_t stream) 
     const uint64_t dims[4] = {(uint64_t)c.cpad, (uint64_t)c.w_img, (uint64_t)c.h_img, (uint64_t)c.batch};
     const uint64_t st[3] = {(uint64_t)c.c_total * 4, (uint64_t)c.w_img * c.c_total * 4,
                             (uint64_t)c.h_img * c.w_img * c.c_total * 4};
-    const uint32_t box[4] = {(uint32_t)CvCfg::CH, (uint32_t)CvCfg::BK, 1, 1};
+    const uint32_t box[4] = {(uint32_t)CvCfg::CH, (uint32_t)bw, (uint32_t)bh, 1};
     const int rc = encode_map_f32(&L.mb, c.img_cl, dims, st, box, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
     if (rc) return rc;
   }
@@ -1384,9 +1389,10 @@ int launch_conv_implicit_wgrad(const ConvImplicitWgrad& c, cudaStream_t stream) 
   g.n_tiles = (int)((kr + tile_cols - 1) / tile_cols);
   g.total_tiles = (long long)g.m_tiles * g.n_tiles;
   g.red = (int)c.batch;
-  g.cv_wblocks = (int)((c.w_out + CvCfg::BK - 1) / CvCfg::BK);
-  g.cv_rows = (int)c.h_out;
-  g.k_blocks = (int)(c.h_out * g.cv_wblocks);
+  g.cv_bw = bw; g.cv_bh = bh;
+  g.cv_wblocks = (int)((c.w_out + bw - 1) / bw);
+  g.cv_rows = (int)((c.h_out + bh - 1) / bh);
+  g.k_blocks = g.cv_rows * g.cv_wblocks;
   const long long total_kb = (long long)g.red * g.k_blocks;
   // K slices: as many work units as SMs; the slices add into `out` atomically
   long long slices = sms / g.total_tiles;

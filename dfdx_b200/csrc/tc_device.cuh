@@ -77,11 +77,6 @@ __device__ __forceinline__ void tma_load_5d(uint32_t dst, const CUtensorMap* map
       " [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
       ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4) : "memory");
 }
-// Tiled 4-D prefetch of a box into L2 (no shared-memory destination, nothing to wait for).
-__device__ __forceinline__ void tma_prefetch_4d(const CUtensorMap* map, int c0, int c1, int c2, int c3) {
-  asm volatile("cp.async.bulk.prefetch.tensor.4d.L2.global.tile [%0, {%1, %2, %3, %4}];"
-               ::"l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
-}
 // Tiled 4-D TMA store shared -> global (bulk async-group completion).  Rows / columns of the box that fall outside
 // the tensor are not written.
 __device__ __forceinline__ void tma_store_4d(const CUtensorMap* map, uint32_t src, int c0, int c1, int c2, int c3) {
@@ -328,7 +323,8 @@ struct TcArgs {
   int cv_kw, cv_taps;             // filter taps per row, taps in all
   int cv_w0, cv_dw, cv_h0, cv_dh; // tap (k1, k2) reads the image at (row + cv_h0 + k1 * cv_dh, col + cv_w0 + k2 * cv_dw)
   int cv_rows, cv_wout;           // CV 1: image rows and pixels per row of one N tile; CV 2: cv_rows = output rows per image
-  int cv_wblocks;                 // CV 2: k-blocks per image row (ceil(w_out / 16))
+  int cv_wblocks;                 // CV 2: k-blocks per row of boxes (ceil(w_out / cv_bw)); cv_rows = rows of boxes per image
+  int cv_bw, cv_bh;               // CV 2: a k-block's 16 output pixels are a box of cv_bw x cv_bh pixels
 };
 
 // Fused epilogue on 32 consecutive accumulator columns [col0, col0+32) of output row `row` (row < m):
