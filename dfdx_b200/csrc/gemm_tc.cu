@@ -288,9 +288,13 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
 constexpr int SPLIT_WARPS = 8;
 constexpr int SPLIT_THREADS = SPLIT_WARPS * 32;
 
+// `skip_a_hi`: rows 64..127 of the A tile are not in use (an output with at most 64 rows): their vectors (the second
+// SPLIT_THREADS * 16 bytes of a stage) are left alone.
 template <typename C>
 __device__ __forceinline__ void split_role(const TcArgs& g, uint32_t smem_base, uint64_t* bar_full,
-                                           uint64_t* bar_xform, volatile int* abortp, int total_kb, int tt) {
+                                           uint64_t* bar_xform, volatile int* abortp, int total_kb, int tt,
+                                           bool skip_a_hi = false) {
+  static_assert(SPLIT_THREADS * 16 == C::A_BYTES / 2, "the A tile's upper half must be one vector per split thread");
   constexpr int STAGES = C::STAGES;
   constexpr int NVEC = C::RAW_BYTES / 16;
   static_assert(NVEC % SPLIT_THREADS == 0, "a stage must be a whole number of vectors per split thread");
@@ -307,12 +311,15 @@ __device__ __forceinline__ void split_role(const TcArgs& g, uint32_t smem_base, 
       {
         uint32_t x[PER][4];
 #pragma unroll
-        for (int u = 0; u < PER; ++u)
+        for (int u = 0; u < PER; ++u) {
+          if (u == 1 && skip_a_hi) continue;
           asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
                        : "=r"(x[u][0]), "=r"(x[u][1]), "=r"(x[u][2]), "=r"(x[u][3])
                        : "r"(raw + u * (SPLIT_THREADS * 16)));
+        }
 #pragma unroll
         for (int u = 0; u < PER; ++u) {
+          if (u == 1 && skip_a_hi) continue;
           uint32_t sm[4];
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
@@ -423,7 +430,7 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_const
           int kx = un.kb_lo * C::BK, bw = g.cv_w0 + k2 * g.cv_dw, bh = t.nt * g.cv_rows + g.cv_h0 + k1 * g.cv_dh;
           int bc = t.ib1 * g.cv_cpad + cb * C::BK;
           const int bc_end = (t.ib1 + 1) * g.cv_cpad, w_end = g.cv_w0 + g.cv_kw * g.cv_dw;
-          const uint32_t tx = (uint32_t)(C::A_BYTES + g.b_tx_bytes);
+          const uint32_t tx = (uint32_t)((g.m64 ? C::A_BYTES / 2 : C::A_BYTES) + g.b_tx_bytes);   // m64: the A box has 64 rows
           for (int i = un.kb_lo; i < un.kb_hi; ++i) {
             const uint32_t s = ring_s, ph = ring_ph;
             if (++ring_s == (uint32_t)STAGES) { ring_s = 0; ring_ph ^= 1u; }
@@ -476,7 +483,8 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_const
       // instruction descriptor: D = f32, A = B = tf32 (format 2), majors, N >> 3, M >> 4
       const uint32_t mma_n = CV ? (uint32_t)g.mma_n : (uint32_t)BN;
       const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(g.a_mn ? 1 : 0) << 15) |
-                             ((uint32_t)(g.b_mn ? 1 : 0) << 16) | ((mma_n >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+                             ((uint32_t)(g.b_mn ? 1 : 0) << 16) | ((mma_n >> 3) << 17) |
+                             ((uint32_t)(((CV == 1 && g.m64) ? 64 : BM) >> 4) << 24);
       const uint32_t a_lbo = g.a_mn ? C::MN_LBO : 16u, b_lbo = g.b_mn ? C::MN_LBO : 16u;
       const uint32_t a_sbo = g.a_mn ? C::MN_SBO : C::K_SBO, b_sbo = g.b_mn ? C::MN_SBO : C::K_SBO;
       const uint32_t a_lay = g.a_mn ? C::MN_LAYOUT : C::K_LAYOUT, b_lay = g.b_mn ? C::MN_LAYOUT : C::K_LAYOUT;
@@ -521,7 +529,7 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_const
   } else if (wg >= 3) {
     // ------------------------------------------------------------------ operand split (warps 12..19)
     setmaxnreg_dec_split();
-    split_role<C>(g, smem_base, bar_full, bar_xform, abortp, total_kb, threadIdx.x - 384);
+    split_role<C>(g, smem_base, bar_full, bar_xform, abortp, total_kb, threadIdx.x - 384, CV == 1 && g.m64);
   } else {
     // ------------------------------------------------------------------ epilogue (warpgroups 0 and 1)
     setmaxnreg_inc_epi();
@@ -558,7 +566,11 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_const
       if (un.kb_lo >= un.kb_hi) continue;               // an empty unit of the stream-K decomposition
       // partial sums (a K slice, or a stream-K range that does not span the tile's whole K) are added atomically
       const bool partial = g.ksplit > 1 || ((g.streamk || g.tail_split > 1) && !(un.kb_lo == 0 && un.kb_hi == total_kb));
-      const int row = t.mt * BM + quad * 32 + lane;
+      // An MMA with M = 64 (m64: outputs of at most 64 rows) keeps row r in TMEM lane (r / 16) * 32 + r % 16: each
+      // warp's lanes 0..15 hold 16 rows, its lanes 16..31 nothing.
+      const bool m64 = CV == 1 && g.m64;
+      const int r_in = m64 ? quad * 16 + (lane & 15) : quad * 32 + lane;
+      const int row = (m64 && lane >= 16) ? g.m : t.mt * BM + r_in;     // row >= g.m: this thread stores nothing
       // columns of this tile: [tile_col0, n_end).  An implicit-convolution tile holds tile_valid columns (whole image
       // rows) and the next tile starts tile_cols further on.
       const int tile_col0 = CV ? t.nt * g.tile_cols : t.nt * BN;
@@ -571,7 +583,6 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_const
         // reduce-add (beta = 1) of whole 128-byte lines.  Rows and columns past the output's extent are clipped
         // by the tensor map.
         const uint32_t stage = smem_base + C::OFF_OUT + (uint32_t)wg * C::OUT_BYTES;
-        const int r_in = quad * 32 + lane;
         const uint32_t sw = (uint32_t)(r_in & 7);
         const bool leader = (threadIdx.x & 127) == 0;
 #pragma unroll
@@ -587,11 +598,13 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_const
             }
             if (leader) bulk_wait_group_read<0>();       // the store that last used this buffer has read it
             named_barrier_sync(1 + wg, 128);
+            if (!m64 || lane < 16) {
 #pragma unroll
-            for (int q = 0; q < 8; ++q)
-              st_shared_v4_u32(stage + (uint32_t)r_in * 128u + ((((uint32_t)q) ^ sw) << 4),
-                               __float_as_uint(acc[c * 32 + q * 4]), __float_as_uint(acc[c * 32 + q * 4 + 1]),
-                               __float_as_uint(acc[c * 32 + q * 4 + 2]), __float_as_uint(acc[c * 32 + q * 4 + 3]));
+              for (int q = 0; q < 8; ++q)
+                st_shared_v4_u32(stage + (uint32_t)r_in * 128u + ((((uint32_t)q) ^ sw) << 4),
+                                 __float_as_uint(acc[c * 32 + q * 4]), __float_as_uint(acc[c * 32 + q * 4 + 1]),
+                                 __float_as_uint(acc[c * 32 + q * 4 + 2]), __float_as_uint(acc[c * 32 + q * 4 + 3]));
+            }
             fence_proxy_async_smem();
             named_barrier_sync(1 + wg, 128);
             if (leader) {
@@ -938,7 +951,7 @@ int build_launch(Launch& L, const Plan& pl, int esize, int tm, int tn, int bmc, 
   g.xform_mode = g_xform_mode;
   g.tile_cols = tn; g.tile_valid = tn; g.mma_n = tn; g.b_tx_bytes = 0;
   g.cv_cblocks = 1; g.cv_cpad = 16; g.cv_kw = 1; g.cv_taps = 1; g.cv_w0 = g.cv_dw = g.cv_h0 = g.cv_dh = 0;
-  g.cv_rows = 1; g.cv_wout = 1; g.cv_wblocks = 1; g.cv_bw = 16; g.cv_bh = 1;
+  g.cv_rows = 1; g.cv_wout = 1; g.cv_wblocks = 1; g.cv_bw = 16; g.cv_bh = 1; g.m64 = 0;
   const long long forced_limit = g_wait_limit.load();
   g.wait_limit = forced_limit > 0 ? forced_limit : 400000000LL + (long long)g.red * g.k_blocks * 40000LL;
   g.status = ds->status;
@@ -1239,7 +1252,7 @@ void cv_common_args(TcArgs& g, DeviceState* ds) {
   g.status = ds->status;
   g.fused = 0; g.alpha = 1.f; g.bias = nullptr; g.bias_row = 0; g.act = B200_ACT_NONE;
   g.cv_cblocks = 1; g.cv_cpad = 16; g.cv_kw = 1; g.cv_taps = 1; g.cv_w0 = g.cv_dw = g.cv_h0 = g.cv_dh = 0;
-  g.cv_rows = 1; g.cv_wout = 1; g.cv_wblocks = 1; g.cv_bw = 16; g.cv_bh = 1;
+  g.cv_rows = 1; g.cv_wout = 1; g.cv_wblocks = 1; g.cv_bw = 16; g.cv_bh = 1; g.m64 = 0;
 }
 
 }  // namespace
@@ -1270,7 +1283,7 @@ int launch_conv_implicit(const ConvImplicit& c, cudaStream_t stream) {
   {
     const uint64_t dims[4] = {(uint64_t)kr, (uint64_t)c.m, (uint64_t)c.groups, 1};
     const uint64_t st[3] = {(uint64_t)kr * 4, (uint64_t)c.m * kr * 4, (uint64_t)c.groups * c.m * kr * 4};
-    const uint32_t box[4] = {(uint32_t)CvCfg::BK, (uint32_t)BM, 1, 1};
+    const uint32_t box[4] = {(uint32_t)CvCfg::BK, (uint32_t)(c.m <= 64 ? 64 : BM), 1, 1};
     const int rc = encode_map_f32(&L.ma, c.filt, dims, st, box, CU_TENSOR_MAP_SWIZZLE_64B);
     if (rc) return rc;
   }
@@ -1306,6 +1319,7 @@ int launch_conv_implicit(const ConvImplicit& c, cudaStream_t stream) {
   g.cv_cblocks = (int)(c.cpad / CvCfg::BK); g.cv_cpad = (int)c.cpad; g.cv_kw = c.kw; g.cv_taps = (int)taps;
   g.cv_w0 = c.w0; g.cv_dw = c.dw; g.cv_h0 = c.h0; g.cv_dh = c.dh;
   g.cv_rows = rows; g.cv_wout = (int)c.w_out;
+  g.m64 = c.m <= 64 ? 1 : 0;
   const long long forced_limit = g_wait_limit.load();
   g.wait_limit = forced_limit > 0 ? forced_limit : 400000000LL + (long long)g.k_blocks * 40000LL;
   {
@@ -1353,16 +1367,9 @@ int launch_conv_implicit_wgrad(const ConvImplicitWgrad& c, cudaStream_t stream) 
   const int sms = grid_sms(ds);
   const int64_t taps = (int64_t)c.kh * c.kw, kr = taps * c.cpad, npos = c.h_out * c.w_out;
   const int tile_cols = wgrad_tile_cols(kr);
-  // the 16 output pixels of a k-block form a box of bw x bh pixels: the shape with the fewest boxes per image
-  int bw = 16, bh = 1;
-  {
-    long long best = -1;
-    const int shapes[3][2] = {{16, 1}, {8, 2}, {4, 4}};
-    for (auto& sh : shapes) {
-      const long long n = ((c.w_out + sh[0] - 1) / sh[0]) * ((c.h_out + sh[1] - 1) / sh[1]);
-      if (best < 0 || n < best) { best = n; bw = sh[0]; bh = sh[1]; }
-    }
-  }
+  // A k-block is 16 pixels of one output row.  (Boxes of 8 x 2 or 4 x 4 pixels would waste less on ragged rows, but a
+  // swizzled TMA box narrower than the swizzle span does not land in the dense layout the MMA descriptor expects.)
+  const int bw = CvCfg::BK, bh = 1;
   Launch L;
   // A: grad_out of this group as (x, y, channel, image); one box = 16 pixels of one row x 128 channels
   {

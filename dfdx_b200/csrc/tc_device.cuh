@@ -325,6 +325,7 @@ struct TcArgs {
   int cv_rows, cv_wout;           // CV 1: image rows and pixels per row of one N tile; CV 2: cv_rows = output rows per image
   int cv_wblocks;                 // CV 2: k-blocks per row of boxes (ceil(w_out / cv_bw)); cv_rows = rows of boxes per image
   int cv_bw, cv_bh;               // CV 2: a k-block's 16 output pixels are a box of cv_bw x cv_bh pixels
+  int m64;                        // CV 1: the output has at most 64 rows: A boxes of 64 rows, MMAs with M = 64
 };
 
 // Fused epilogue on 32 consecutive accumulator columns [col0, col0+32) of output row `row` (row < m):
