@@ -49,7 +49,7 @@ NCU_TRAFFIC_BYTES_PER_LAUNCH = 366.4e6
 WORKLOAD = f"config[1]: MatMatBr f32 X[{B},{S},{K}] x W^T, W stored [{N},{K}], fwd + grad_lhs + grad_rhs"
 MIB = 1024.0 * 1024.0
 # SMs left to the NCCL kernel that runs beside the grad_lhs GEMM, and that kernel's CTA bound
-OVERLAP_SMS = 4
+OVERLAP_SMS = 8
 
 
 def measured_peaks():
@@ -301,11 +301,11 @@ class Harness:
 
 
 # ------------------------------------------------------------------------------------------------ workloads
-def make_c2(h, items=B, overlap=None, group=None):
+def make_c2(h, items=B, overlap=True, group=None, overlap_sms=OVERLAP_SMS):
     """The headline workload on `items` batch items.  Returns (step, tensors)."""
     import torch
     import dfdx_b200
-    from dfdx_b200.parallel import OverlappedReducer
+    from dfdx_b200.parallel import OverlappedReducer, allreduce_shared_grads
     lib, device, st = h.lib, h.device, dfdx_b200._lib.strides
     g = torch.Generator(device="cpu").manual_seed(0xD0FD + 2 + 1000 * h.rank)
     x_h = torch.randn(items, S, K, generator=g, dtype=torch.float32).pin_memory()
@@ -316,7 +316,7 @@ def make_c2(h, items=B, overlap=None, group=None):
     y = torch.empty(items, S, N, device=device)
     gx = torch.zeros(items * S * K, device=device)
     gw = torch.zeros(N * K, device=device)
-    reducer = OverlappedReducer(device, group) if h.world > 1 else None
+    reducer = OverlappedReducer(device, group) if (h.world > 1 and overlap) else None
     sms = torch.cuda.get_device_properties(device).multi_processor_count
     F32, check = dfdx_b200.F32, dfdx_b200._lib.check
     xs, ws = st(x.stride()), st(w_view.stride())
@@ -332,11 +332,13 @@ def make_c2(h, items=B, overlap=None, group=None):
         if reducer is None:
             check(lib.b200_matmat_br_backward(F32, items, S, K, N, x.data_ptr(), xs, gx.data_ptr(), w_view.data_ptr(),
                                               ws, gw.data_ptr(), dy.data_ptr(), s, None), "backward")
+            if h.world > 1:
+                allreduce_shared_grads([gw])
             return
         check(lib.b200_matmat_br_backward(F32, items, S, K, N, x.data_ptr(), xs, None, w_view.data_ptr(), ws,
                                           gw.data_ptr(), dy.data_ptr(), s, None), "backward (grad_rhs)")
         reducer.start([gw])
-        lib.b200_set_max_ctas(sms - OVERLAP_SMS)
+        lib.b200_set_max_ctas(sms - overlap_sms)
         try:
             check(lib.b200_matmat_br_backward(F32, items, S, K, N, x.data_ptr(), xs, gx.data_ptr(), w_view.data_ptr(),
                                               ws, None, dy.data_ptr(), s, None), "backward (grad_lhs)")
@@ -688,6 +690,11 @@ def main():
                          "the fused attention kernels")
     ap.add_argument("--unfused-epilogues", action="store_true",
                     help="workload c5: bias / ReLU / score scale as separate ops after the GEMMs (the reference's op sequence)")
+    ap.add_argument("--allreduce", default="overlap", choices=["overlap", "inline"],
+                    help="N > 1: the weight gradient's all-reduce on a side stream under the grad_lhs GEMM (default), or "
+                         "in line on the compute stream after both gradient GEMMs")
+    ap.add_argument("--overlap-sms", type=int, default=OVERLAP_SMS,
+                    help="SMs the grad_lhs GEMM leaves to the overlapped all-reduce (and that collective's CTA bound)")
     ap.add_argument("--workload", default="c2", choices=["c1", "c2", "c3", "c4", "c5", "attn"],
                     help="c2 (default) is the benchmark line with every configuration inside; the others time one "
                          "configuration alone (device-resident; used for profiling)")
@@ -739,8 +746,9 @@ def main():
         return
 
     # ---- the headline workload -------------------------------------------------------------------------
-    side_group = nccl_group(OVERLAP_SMS) if world > 1 else None
-    step, t = make_c2(h, B, group=side_group)
+    overlap = args.allreduce == "overlap"
+    side_group = nccl_group(max(args.overlap_sms, 1)) if (world > 1 and overlap and args.overlap_sms > 0) else None
+    step, t = make_c2(h, B, overlap=overlap, group=side_group, overlap_sms=args.overlap_sms)
     if rank == 0:
         h.sampler.start()
         time.sleep(0.3)          # let nvidia-smi come up before the GPU work starts
@@ -764,7 +772,7 @@ def main():
     if world > 1 and not args.headline_only:
         # the same fixed problem (B = 64) partitioned over the ranks along the batch; config 1 along M
         per = B // world
-        sstep, _ = make_c2(h, per, group=side_group)
+        sstep, _ = make_c2(h, per, overlap=overlap, group=side_group, overlap_sms=args.overlap_sms)
         r_s = h.region(sstep, args.steps, warmup)
         rows = 1024 // world
         c1s = make_c1(h, rows=rows, strong=True)
@@ -815,8 +823,9 @@ def main():
                    "l2": "inputs+outputs per step 672 MiB > 126 MB L2 (no flush needed)",
                    "parallelism": "1 GPU" if world == 1 else
                                   f"weak scaling: each of the {world} ranks runs its own {B}-item batch; the shared weight's "
-                                  f"gradient (16 MiB) is all-reduced over NCCL on a side stream under the grad_lhs GEMM "
-                                  f"({OVERLAP_SMS} SMs left to it)"},
+                                  f"gradient (16 MiB) is all-reduced over NCCL " +
+                                  (f"on a side stream under the grad_lhs GEMM ({args.overlap_sms} SMs left to it)" if overlap
+                                   else "in line after the gradient GEMMs")},
         "gpu_launches": r["launches"], "tensor_core_launches": r["tc_launches"],
         "clocks": clocks,
         "e2e": {"value": round(e2e_tflops, 3), "unit": "TFLOP/s", "steps": e2e_steps,

@@ -565,7 +565,7 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_const
       if (!ok) break;
       if (un.kb_lo >= un.kb_hi) continue;               // an empty unit of the stream-K decomposition
       // partial sums (a K slice, or a stream-K range that does not span the tile's whole K) are added atomically
-      const bool partial = g.ksplit > 1 || ((g.streamk || g.tail_split > 1) && !(un.kb_lo == 0 && un.kb_hi == total_kb));
+      const bool partial = g.ksplit > 1 || ((g.streamk || g.tail_per > 0) && !(un.kb_lo == 0 && un.kb_hi == total_kb));
       // An MMA with M = 64 (m64: outputs of at most 64 rows) keeps row r in TMEM lane (r / 16) * 32 + r % 16: each
       // warp's lanes 0..15 hold 16 rows, its lanes 16..31 nothing.
       const bool m64 = CV == 1 && g.m64;
@@ -922,7 +922,7 @@ int build_launch(Launch& L, const Plan& pl, int esize, int tm, int tn, int bmc, 
   g.n_fast = g.n_tiles < g.m_tiles ? 1 : 0;
   g.total_tiles = (long long)g.m_tiles * g.n_tiles * p.b0 * p.b1;
   g.ksplit = 1; g.kb_per_slice = 0; g.total_units = g.total_tiles;   // launch_cfg fills the slice length
-  g.tail_from = 0; g.tail_split = 1; g.tail_kb = 0;
+  g.tail_from = 0; g.tail_per = 0; g.tail_parts = 0;
   g.streamk = 0; g.sk_per_cta = 0;
   g.red = (int)p.red;
   g.k_blocks = (int)((p.k + bk - 1) / bk);
@@ -980,16 +980,17 @@ int plan_tail_split(TcArgs& g, int sms, int total_kb, cudaStream_t stream) {
   const long long full = g.total_tiles / sms, rem = g.total_tiles % sms;
   if (full < 1 || rem == 0) return B200_OK;
   if (!g.beta && rem > TAIL_MAX_ZEROED) return B200_OK;
-  long long split = sms / rem;
-  if (split > total_kb / 4) split = total_kb / 4;          // slices of at least four k-blocks
-  if (split < 2) return B200_OK;
-  const int kb_per = (int)((total_kb + split - 1) / split);
-  split = (total_kb + kb_per - 1) / kb_per;
+  // one contiguous range of the tail's (tile, k-block) space per CTA; at least four k-blocks per range
+  long long per = (rem * total_kb + sms - 1) / sms;
+  if (per < 4) per = 4;
+  if (per >= total_kb) return B200_OK;
+  const int parts = 2;                                     // a range shorter than a tile touches at most two tiles
   // cost in k-blocks per SM; a unit costs about 8 k-blocks beside its main loop (pipeline fill, epilogue)
-  const double fixed = 8.0, before = (double)(full + 1) * (total_kb + fixed), after = full * (total_kb + fixed) + kb_per + fixed;
-  if (split < 2 || after > 0.95 * before) return B200_OK;
-  g.tail_from = full * sms; g.tail_split = (int)split; g.tail_kb = kb_per;
-  g.total_units = g.tail_from + rem * split;
+  const double fixed = 8.0, before = (double)(full + 1) * (total_kb + fixed),
+               after = full * (total_kb + fixed) + (double)per + 2 * fixed;
+  if (after > 0.95 * before) return B200_OK;
+  g.tail_from = full * sms; g.tail_per = (int)per; g.tail_parts = parts;
+  g.total_units = g.tail_from + (long long)sms * parts;
   if (!g.beta) {
     const long long per_batch = (long long)g.m_tiles * g.n_tiles;
     TailTiles tt;
@@ -1243,7 +1244,7 @@ int conv_rows_per_tile(const ConvImplicit& c, int sms) {
 void cv_common_args(TcArgs& g, DeviceState* ds) {
   g.nb1 = 1; g.n_fast = 0;
   g.ksplit = 1; g.streamk = 0; g.sk_per_cta = 0; g.split_out = nullptr; g.split_ld = 0;
-  g.tail_from = 0; g.tail_split = 1; g.tail_kb = 0;
+  g.tail_from = 0; g.tail_per = 0; g.tail_parts = 0;
   g.red = 1;
   g.a_mn = 0; g.b_mn = 0; g.a_ld = 0; g.b_ld = 0;
   g.a_x1 = g.a_xr = g.a_y0 = g.b_x1 = g.b_xr = g.b_y0 = 0;

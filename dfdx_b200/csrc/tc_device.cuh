@@ -276,11 +276,12 @@ struct TcArgs {
   long long total_tiles;
   int ksplit, kb_per_slice;       // f32 kernel: K is cut into ksplit slices of kb_per_slice k-blocks; a work unit is
   long long total_units;          // (tile, slice); slices of one tile add their partial results atomically
-  // f32 kernel, ksplit == 1: when the tiles do not fill a whole number of waves, the tiles of the last, partial wave
-  // (tile index >= tail_from) are cut into tail_split K slices of tail_kb k-blocks each, so that every SM gets a
-  // share of them; those slices add their partial results atomically like split-K slices.  tail_split == 1: off.
+  // f32 kernel, ksplit == 1: when the tiles do not fill a whole number of waves, the (tile, k-block) space of the
+  // last, partial wave (tiles >= tail_from) is dealt out as one contiguous range of tail_per k-blocks per CTA, so
+  // that every SM gets an equal share; a range touches at most tail_parts tiles, parts of tiles add their partial
+  // results atomically like split-K slices.  tail_per == 0: off.
   long long tail_from;
-  int tail_split, tail_kb;
+  int tail_per, tail_parts;
   int streamk;                    // f32 kernel: the (tile, k-block) space is cut into one contiguous range per CTA
   long long sk_per_cta;           // k-blocks per CTA; a unit is the part of one tile inside the CTA's range (may be empty)
   float* split_out;               // f16 kernel with ksplit > 1: f32 scratch (m x split_ld, zeroed) that takes the
@@ -537,11 +538,18 @@ __device__ __forceinline__ Unit decode_unit(const TcArgs& g, long long unit, int
     else { u.kb_lo = (int)(lo - t0); u.kb_hi = (int)(hi - t0); }
     return u;
   }
-  if (g.tail_split > 1 && unit >= g.tail_from) {
-    const long long v = unit - g.tail_from, q = v / g.tail_split;
-    u.tile = g.tail_from + q;
-    u.kb_lo = (int)(v - q * g.tail_split) * g.tail_kb;
-    u.kb_hi = u.kb_lo + g.tail_kb < total_kb ? u.kb_lo + g.tail_kb : total_kb;
+  if (g.tail_per > 0 && unit >= g.tail_from) {
+    // unit = tail_from + part * gridDim.x + cta: the part-th tile that CTA cta's range of the tail touches
+    const long long v = unit - g.tail_from, part = v / gridDim.x, cta = v - part * gridDim.x;
+    const long long all = (g.total_tiles - g.tail_from) * (long long)total_kb;
+    const long long start = cta * g.tail_per;
+    long long end = start + g.tail_per;
+    if (end > all) end = all;
+    const long long ti = start / total_kb + part, t0 = ti * (long long)total_kb;
+    const long long lo = start > t0 ? start : t0, hi = end < t0 + total_kb ? end : t0 + total_kb;
+    u.tile = g.tail_from + ti;
+    if (hi <= lo || u.tile >= g.total_tiles) { u.tile = g.tail_from; u.kb_lo = u.kb_hi = 0; }   // nothing of that tile
+    else { u.kb_lo = (int)(lo - t0); u.kb_hi = (int)(hi - t0); }
     return u;
   }
   u.tile = unit / g.ksplit;
