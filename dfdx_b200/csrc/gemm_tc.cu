@@ -57,6 +57,7 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
                 const __grid_constant__ CUtensorMap tma_c, const TcArgs g) {
   using C = CfgH<BN>;
   constexpr int STAGES = C::STAGES;
+  constexpr int PRODUCER_WARP = 8, MMA_WARP = 9;       // warps 0..7: epilogue
 
   extern __shared__ uint8_t smem_dyn[];
   __shared__ __align__(8) uint64_t bar_full[STAGES];
@@ -77,16 +78,16 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(smem_u32(&bar_tfull[b]), 1);
-      mbar_init(smem_u32(&bar_tempty[b]), 128);
+      mbar_init(smem_u32(&bar_tempty[b]), 256);
     }
     abort_flag = 0;
     fence_mbar_init();
   }
-  if (warp == 5) {
+  if (warp == MMA_WARP) {
     tmem_alloc(smem_u32(&tmem_slot), C::TMEM_COLS);
     tmem_relinquish();
   }
-  if (warp == 4 && lane == 0) {
+  if (warp == PRODUCER_WARP && lane == 0) {
     tma_prefetch_desc(&tma_a);
     tma_prefetch_desc(&tma_b);
   }
@@ -96,7 +97,7 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
   const uint32_t tmem_base = tmem_slot;
   const int total_kb = g.red * g.k_blocks;
 
-  if (warp == 4) {
+  if (warp == PRODUCER_WARP) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
       uint32_t it = 0;
@@ -120,7 +121,7 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
       }
     }
     __syncwarp();
-  } else if (warp == 5) {
+  } else if (warp == MMA_WARP) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       // instruction descriptor: D = f32, A = B = f16, majors, N >> 3, M >> 4
@@ -160,46 +161,52 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
     }
     __syncwarp();
   } else {
-    // ------------------------------------------------------------------ epilogue (warps 0..3)
-    uint32_t tcount = 0, store_count = 0;
+    // ------------------------------------------------------------------ epilogue (warps 0..7)
+    // Two groups of four warps (a warp reads the TMEM lanes 32 * (warp % 4) ...): group eg takes every other
+    // 64-column (staged) or 32-column (per-thread) piece of the tile, with its own staging buffer and named barrier,
+    // so that a short-K tile's epilogue does not outlast the next tile's main loop.
+    const int eg = warp >> 2, ew = warp & 3;
+    const int bar_id = 1 + eg;
+    const bool leader = (threadIdx.x & 127) == 0;
+    uint32_t tcount = 0;
     bool ok = true;
     for (long long unit = blockIdx.x; ok && unit < g.total_units; unit += gridDim.x, ++tcount) {
       const Unit un = decode_unit(g, unit, total_kb);
       const TileCoord t = decode_tile(g, un.tile);
       const uint32_t buf = tcount & 1u, tph = (tcount >> 1) & 1u;
-      const int row = t.mt * BM + warp * 32 + lane;
+      const int row = t.mt * BM + ew * 32 + lane;
       __half* cbase = (__half*)g.c + t.ib0 * g.c_b0 + t.ib1 * g.c_b1;
       // beta = 1 with row stores: the values the row already holds do not depend on the accumulator, so
       // they are fetched before waiting for it, four 32-column chunks ahead of their use.
-      constexpr int NCH = BN / 32, AHEAD = NCH < 4 ? NCH : 4;
+      constexpr int NCH = BN / 32, MINE = NCH / 2, AHEAD = MINE < 4 ? MINE : 4;   // this group: chunks 2 i + eg
       const bool rmw = g.beta && !g.c_col && row < g.m && g.ksplit == 1 && !g.c_tma;
       const __half* orow = cbase + (long long)row * g.ldc + t.nt * BN;
       uint32_t oldv[AHEAD][16];
       if (rmw) {
 #pragma unroll
         for (int pc = 0; pc < AHEAD; ++pc)
-          if (t.nt * BN + pc * 32 + 32 <= g.n) load_old_f16(orow + pc * 32, oldv[pc], g.c_wide);
+          if (t.nt * BN + (2 * pc + eg) * 32 + 32 <= g.n) load_old_f16(orow + (2 * pc + eg) * 32, oldv[pc], g.c_wide);
       }
       bool got = mbar_wait(smem_u32(&bar_tfull[buf]), tph, abortp, g.wait_limit);
       // the staged epilogue below synchronises the four epilogue warps with named barriers, which have no
       // time-out: all of them take this tile or none does
-      got = g.c_tma ? named_barrier_and(1, 128, got) : __all_sync(0xffffffffu, got);
+      got = g.c_tma ? named_barrier_and(bar_id, 128, got) : __all_sync(0xffffffffu, got);
       if (!got) { ok = false; break; }
       tc_fence_after();
-      const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16) + buf * BN;
+      const uint32_t taddr = tmem_base + ((uint32_t)(ew * 32) << 16) + buf * BN;
       if (g.c_tma) {
         // Output through shared memory and TMA: per-thread row stores hand the memory system 32 separate
         // 32-byte pieces per instruction (rows are ldc apart), which bounds GEMMs with a short K and a wide
         // output; a staged 128 x 64 group leaves as one bulk tensor store of whole 128-byte lines.
-        const int r_in = warp * 32 + lane;
+        const int r_in = ew * 32 + lane;
         const uint32_t sw = (uint32_t)(r_in & 7);
 #pragma unroll
         for (int c2 = 0; c2 < BN / 64; ++c2) {
           const int col0 = t.nt * BN + c2 * 64;
-          if (col0 < g.n) {                          // block-uniform
-            const uint32_t stage = smem_base + C::OFF_OUT + (store_count & 1u) * C::OUT_BYTES;
-            if (threadIdx.x == 0) bulk_wait_group_read<1>();   // the store that last used this buffer has read it
-            named_barrier_sync(1, 128);
+          if ((c2 & 1) == eg && col0 < g.n) {        // group-uniform
+            const uint32_t stage = smem_base + C::OFF_OUT + (uint32_t)eg * C::OUT_BYTES;
+            if (leader) bulk_wait_group_read<0>();   // the store that last used this buffer has read it
+            named_barrier_sync(bar_id, 128);
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
               uint32_t v[32];
@@ -224,13 +231,12 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
               }
             }
             fence_proxy_async_smem();
-            named_barrier_sync(1, 128);
-            if (threadIdx.x == 0) {
+            named_barrier_sync(bar_id, 128);
+            if (leader) {
               if (g.c_tma == 2) tma_reduce_add_4d(&tma_c, stage, col0, t.mt * BM, t.ib1, t.ib0);
               else tma_store_4d(&tma_c, stage, col0, t.mt * BM, t.ib1, t.ib0);
               bulk_commit_group();
             }
-            ++store_count;
           }
         }
         tc_fence_before();
@@ -238,7 +244,8 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
         continue;
       }
 #pragma unroll
-      for (int c = 0; c < NCH; ++c) {
+      for (int ci = 0; ci < MINE; ++ci) {
+        const int c = 2 * ci + eg;
         const int col0 = t.nt * BN + c * 32;
         if (col0 < g.n) {                            // warp-uniform
           uint32_t v[32];
@@ -255,26 +262,26 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
             } else if (g.c_col) {
               store_chunk_col(cbase + (long long)col0 * g.ldc + row, f, valid, g.ldc, g.beta);
             } else if (rmw && valid == 32) {
-              add_old_f16(f, oldv[c % AHEAD]);
+              add_old_f16(f, oldv[ci % AHEAD]);
               store_chunk(cbase + (long long)row * g.ldc + col0, f, 32, 0, g.c_wide);
             } else {
               store_chunk(cbase + (long long)row * g.ldc + col0, f, valid, g.beta, g.c_wide);
             }
           }
-          if (rmw && c + AHEAD < NCH && col0 + AHEAD * 32 + 32 <= g.n)
-            load_old_f16(orow + (c + AHEAD) * 32, oldv[c % AHEAD], g.c_wide);
+          if (rmw && ci + AHEAD < MINE && col0 + 2 * AHEAD * 32 + 32 <= g.n)
+            load_old_f16(orow + (c + 2 * AHEAD) * 32, oldv[ci % AHEAD], g.c_wide);
         }
       }
       tc_fence_before();
       mbar_arrive(smem_u32(&bar_tempty[buf]));
     }
-    if (threadIdx.x == 0) bulk_wait_group_read<0>();     // shared memory must outlive the last bulk stores' reads
+    if (leader) bulk_wait_group_read<0>();               // shared memory must outlive the last bulk stores' reads
   }
 
   tc_fence_before();
   __syncthreads();
   teardown(abort_flag, g.status);
-  if (warp == 5) {
+  if (warp == MMA_WARP) {
     tc_fence_after();
     tmem_dealloc(tmem_base, C::TMEM_COLS);
   }

@@ -227,7 +227,7 @@ struct CfgH {
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int STAGES_FIT = (192 * 1024) / STAGE_BYTES;
   static constexpr int STAGES = STAGES_FIT > 8 ? 8 : STAGES_FIT;
-  static constexpr int THREADS = 192;
+  static constexpr int THREADS = 320;                       // 8 epilogue warps, TMA producer warp, MMA warp
   static constexpr int TMEM_COLS = 2 * BN;
   static constexpr int OUT_BYTES = 128 * 128;               // one staged output group: 128 rows x 64 f16 (TMA-store epilogue)
   static constexpr int OFF_OUT = STAGES * STAGE_BYTES;
