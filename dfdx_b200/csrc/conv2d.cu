@@ -391,12 +391,16 @@ __global__ void __launch_bounds__(256) to_channels_last_kernel(const float* __re
     poff = b * st.s[0] + (long long)y * st.s[2] + (long long)x * st.s[3];
   }
   __syncthreads();
+  // all of the thread's loads are issued before the first is used (memory-level parallelism, not instruction count,
+  // is what this kernel runs on)
+  float v[CL_CH / 2];
 #pragma unroll
   for (int k = 0; k < CL_CH / 2; ++k) {
-    const int row = 2 * k + (tid >> 7);
-    const long long co = chan_off[row];
-    tile[row][px] = (co >= 0 && poff >= 0) ? __ldg(in + co + poff) : 0.f;
+    const long long co = chan_off[2 * k + (tid >> 7)];
+    v[k] = (co >= 0 && poff >= 0) ? __ldg(in + co + poff) : 0.f;
   }
+#pragma unroll
+  for (int k = 0; k < CL_CH / 2; ++k) tile[2 * k + (tid >> 7)][px] = v[k];
   __syncthreads();
   // 8 lanes cover the 32 channels of one pixel with 16-byte stores; a warp writes 4 pixels per instruction
   const int c4 = (tid & 7) * 4, pl = (tid >> 3) & 3, wq = tid >> 5;
