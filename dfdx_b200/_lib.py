@@ -65,6 +65,7 @@ SIGNATURES = {
     "b200_selftest_bounded_wait": (_i, [C.c_longlong, C.POINTER(C.c_longlong), _vp]),
     "b200_launch_count": (C.c_uint64, []),
     "b200_tensor_launch_count": (C.c_uint64, []),
+    "b200_conv_implicit_count": (C.c_uint64, []),
     "b200_gemm": (_i, [_i, _sz, _sz, _sz, _vp, _szp, _vp, _szp, _d, _vp, _szp, _vp]),
     "b200_gemm_batch": (_i, [_i, _sz, _sz, _sz, _sz, _vp, _szp, _vp, _szp, _d, _vp, _szp, _vp]),
     "b200_matmat_forward": (_i, [_i, _sz, _sz, _sz, _vp, _szp, _vp, _szp, _vp, _vp]),

@@ -27,6 +27,7 @@ int conv1d_backward(int dtype, const b200_conv1d_op* o, const void* img, void* g
 int conv2d_backward(int dtype, const b200_conv2d_op* o, const void* img, void* grad_img, const void* filters,
                     const size_t fs[4], void* grad_filters, const void* grad_out, void* ws, cudaStream_t stream);
 int conv_noalloc_setup_device();
+uint64_t conv_implicit_passes();
 void tc_set_xform_mode(int mode);
 void tc_set_tile_n(int bn);
 void tc_set_mn_box5(int on);
@@ -263,6 +264,7 @@ int b200_selftest_bounded_wait(long long limit_cycles, long long* waited_cycles,
 
 uint64_t b200_launch_count(void) { return g_launches.load(); }
 uint64_t b200_tensor_launch_count(void) { return g_tc_launches.load(); }
+uint64_t b200_conv_implicit_count(void) { return conv_implicit_passes(); }
 
 // ---- Cuda::gemm / Cuda::gemm_batch ---------------------------------------------------------------
 int b200_gemm(int dtype, size_t m, size_t k, size_t n, const void* lhs, const size_t ls[2], const void* rhs,

@@ -370,13 +370,53 @@ std::atomic<size_t> g_conv_group_bytes{CONV_GROUP_BYTES_DEFAULT};
 // pixels of each channel plane, 16-byte writes along the channels of each pixel.  The kernel is bound by instruction
 // issue before it is bound by DRAM, so the per-element work is a handful of instructions: the channel -> plane
 // offsets of the tile are worked out once per block, pixel offsets once per thread.
+// The small job that every pass needs beside the layout change rides in the same launch (a dependent launch costs
+// 3-4 us of an otherwise idle GPU): blocks with blockIdx.z == images write the re-laid-out filters,
+//   rows[g][i][tap][cp], zero padded:  transpose 0: i = output channel in the group, cp = input channel
+//                                      (forward: M = O/G, K = taps x C/G);
+//                                      transpose 1: i = input channel, cp = output channel in the group
+//                                      (data gradient: M = C/G, K = taps x O/G);
+// or, with f == nullptr, fill `rows` with zeros (the filter gradient accumulates into it).
+struct FilterJob {
+  const float* f;
+  Strides4 st;
+  float* rows;
+  int og, cg, kk, kw, cpad, transpose;
+  int64_t total;
+};
+__device__ __forceinline__ void filter_job(const FilterJob& j, int64_t first, int64_t step) {
+  const int m = j.transpose ? j.cg : j.og, inner = j.transpose ? j.og : j.cg;
+  for (int64_t i = first; i < j.total; i += step) {
+    float v = 0.f;
+    if (j.f) {
+      int64_t idx = i;
+      const int cp = (int)(idx % j.cpad); idx /= j.cpad;
+      const int tap = (int)(idx % j.kk); idx /= j.kk;
+      const int mi = (int)(idx % m);
+      const int64_t g = idx / m;
+      const int k1 = tap / j.kw, k2 = tap - k1 * j.kw;
+      if (cp < inner) {
+        const int64_t o = g * j.og + (j.transpose ? cp : mi), ci = j.transpose ? mi : cp;
+        v = j.f[o * j.st.s[0] + ci * j.st.s[1] + (int64_t)k1 * j.st.s[2] + (int64_t)k2 * j.st.s[3]];
+      }
+    }
+    j.rows[i] = v;
+  }
+}
+
 constexpr int CL_PIX = 128, CL_CH = 32;
 __global__ void __launch_bounds__(256) to_channels_last_kernel(const float* __restrict__ in, const Strides4 st,
                                                                float* __restrict__ out, const int cg, const int cpad,
-                                                               const int ctot, const int hw, const int w) {
+                                                               const int ctot, const int hw, const int w,
+                                                               const int images, const FilterJob job) {
   __shared__ float tile[CL_CH][CL_PIX + 1];
   __shared__ long long chan_off[CL_CH];                      // offset of the tile's channel planes; -1: padding
   const int tid = threadIdx.x;
+  if ((int)blockIdx.z >= images) {
+    const int64_t nb = (int64_t)gridDim.x * gridDim.y, bid = (int64_t)blockIdx.y * gridDim.x + blockIdx.x;
+    filter_job(job, bid * 256 + tid, nb * 256);
+    return;
+  }
   const long long b = blockIdx.z;
   const int p0 = blockIdx.x * CL_PIX, c0 = blockIdx.y * CL_CH;
   if (tid < CL_CH) {
@@ -416,30 +456,6 @@ __global__ void __launch_bounds__(256) to_channels_last_kernel(const float* __re
   }
 }
 
-// filters (O, C/G, kh, kw) through strides -> rows[g][i][tap][cp] with zero padding:
-//   transpose 0: i = output channel in the group, cp = input channel      (forward: M = O/G, K = taps x C/G)
-//   transpose 1: i = input channel, cp = output channel in the group      (data gradient: M = C/G, K = taps x O/G)
-__global__ void __launch_bounds__(NT) filters_to_rows_kernel(const float* __restrict__ f, const Strides4 st,
-                                                             float* __restrict__ rows, const int og, const int cg,
-                                                             const int kk, const int kw, const int cpad,
-                                                             const int transpose, const int64_t total) {
-  const int m = transpose ? cg : og, inner = transpose ? og : cg;
-  for (int64_t i = (int64_t)blockIdx.x * NT + threadIdx.x; i < total; i += (int64_t)gridDim.x * NT) {
-    int64_t idx = i;
-    const int cp = (int)(idx % cpad); idx /= cpad;
-    const int tap = (int)(idx % kk); idx /= kk;
-    const int mi = (int)(idx % m);
-    const int64_t g = idx / m;
-    const int k1 = tap / kw, k2 = tap - k1 * kw;
-    float v = 0.f;
-    if (cp < inner) {
-      const int64_t o = g * og + (transpose ? cp : mi), ci = transpose ? mi : cp;
-      v = f[o * st.s[0] + ci * st.s[1] + (int64_t)k1 * st.s[2] + (int64_t)k2 * st.s[3]];
-    }
-    rows[i] = v;
-  }
-}
-
 // grad_filters[g*og + o, c, k1, k2] (through strides) += rows[g][o][tap][c]
 __global__ void __launch_bounds__(NT) add_filter_rows_kernel(const float* __restrict__ rows, float* __restrict__ gf,
                                                              const Strides4 st, const int og, const int cg, const int kk,
@@ -458,13 +474,16 @@ __global__ void __launch_bounds__(NT) add_filter_rows_kernel(const float* __rest
 int64_t round_up(int64_t x, int64_t to) { return (x + to - 1) / to * to; }
 
 int launch_to_channels_last(const float* in, const Strides4& st, float* out, int64_t batch, int64_t groups, int64_t cg,
-                            int64_t cpad, int64_t h, int64_t w, cudaStream_t stream) {
+                            int64_t cpad, int64_t h, int64_t w, const FilterJob& job, cudaStream_t stream) {
   const int64_t ctot = groups * cpad, hw = h * w;
-  dim3 grid((unsigned)((hw + CL_PIX - 1) / CL_PIX), (unsigned)((ctot + CL_CH - 1) / CL_CH), (unsigned)batch);
-  to_channels_last_kernel<<<grid, 256, 0, stream>>>(in, st, out, (int)cg, (int)cpad, (int)ctot, (int)hw, (int)w);
+  dim3 grid((unsigned)((hw + CL_PIX - 1) / CL_PIX), (unsigned)((ctot + CL_CH - 1) / CL_CH), (unsigned)batch + 1);
+  to_channels_last_kernel<<<grid, 256, 0, stream>>>(in, st, out, (int)cg, (int)cpad, (int)ctot, (int)hw, (int)w,
+                                                    (int)batch, job);
   count_launch(false);
   return note_cuda_error(cudaGetLastError(), "to_channels_last launch");
 }
+
+std::atomic<uint64_t> g_implicit_passes{0};
 
 // Which passes of a geometry the implicit path serves (f32, unit stride, a tensor-core sized problem whose padded
 // channel counts at most double the work).
@@ -475,7 +494,7 @@ struct ImplicitPlan {
 ImplicitPlan implicit_plan(int dtype, const Op& o) {
   ImplicitPlan pl;
   if (dtype != B200_F32 || o.stride != 1 || current_path() == B200_PATH_SIMT || !fits_int(o)) return pl;
-  if (o.groups < 1 || o.batch < 1 || o.batch > 65535) return pl;
+  if (o.groups < 1 || o.batch < 1 || o.batch > 65534) return pl;   // images + 1 is a grid dimension
   const int64_t cg = o.chan_in / o.groups, og = o.chan_out / o.groups, kk = o.kh * o.kw;
   const int64_t npos = o.h_out * o.w_out, hw = o.h_in * o.w_in;
   if (cg < 8 || og < 8 || npos < 8 || hw < 8) return pl;
@@ -504,13 +523,10 @@ int forward_implicit(const Op& op, const ImplicitPlan& pl, const float* img, con
   c.h0 = -(int)op.ph; c.dh = (int)op.dilation; c.w0 = -(int)op.pw; c.dw = (int)op.dilation;
   c.out = out; c.h_out = op.h_out; c.w_out = op.w_out; c.beta = beta;
   if (!conv_implicit_ok(c)) return B200_ERR_UNSUPPORTED;
-  int rc = launch_to_channels_last(img, ist, img_cl, op.batch, G, cg, cpad, op.h_in, op.w_in, stream);
+  const FilterJob job{filters, fst, rows, (int)og, (int)cg, (int)kk, (int)op.kw, (int)cpad, 0, G * og * kk * cpad};
+  int rc = launch_to_channels_last(img, ist, img_cl, op.batch, G, cg, cpad, op.h_in, op.w_in, job, stream);
   if (rc) return rc;
-  const int64_t n_rows = G * og * kk * cpad;
-  filters_to_rows_kernel<<<grid_for(n_rows, sms), NT, 0, stream>>>(filters, fst, rows, (int)og, (int)cg, (int)kk,
-                                                                    (int)op.kw, (int)cpad, 0, n_rows);
-  count_launch(false);
-  if ((rc = note_cuda_error(cudaGetLastError(), "filters_to_rows launch"))) return rc;
+  g_implicit_passes.fetch_add(1, std::memory_order_relaxed);
   return launch_conv_implicit(c, stream);
 }
 
@@ -532,11 +548,10 @@ int wgrad_implicit(const Op& op, const ImplicitPlan& pl, const float* img, const
   c.out = rows;
   if (!conv_implicit_wgrad_ok(c)) return B200_ERR_UNSUPPORTED;
   const Strides4 ist{{op.chan_in * hw, hw, op.w_in, 1}};
-  int rc = launch_to_channels_last(img, ist, img_cl, op.batch, G, cg, cpad, op.h_in, op.w_in, stream);
+  const FilterJob job{nullptr, fst, rows, (int)og, (int)cg, (int)kk, (int)op.kw, (int)cpad, 0, G * og * kk * cpad};   // zero fill
+  int rc = launch_to_channels_last(img, ist, img_cl, op.batch, G, cg, cpad, op.h_in, op.w_in, job, stream);
   if (rc) return rc;
-  const int64_t n_rows = G * og * kk * cpad;
-  if ((rc = note_cuda_error(cudaMemsetAsync(rows, 0, (size_t)n_rows * 4, stream), "cudaMemsetAsync(filter gradient rows)")))
-    return rc;
+  g_implicit_passes.fetch_add(1, std::memory_order_relaxed);
   for (int64_t g = 0; g < G; ++g) {
     c.gout = grad_out + g * og * npos;
     c.img_cl = img_cl + g * cpad;
@@ -567,13 +582,10 @@ int dgrad_implicit(const Op& op, const ImplicitPlan& pl, float* grad_img, const 
   c.out = grad_img; c.h_out = op.h_in; c.w_out = op.w_in; c.beta = 1;
   if (!conv_implicit_ok(c)) return B200_ERR_UNSUPPORTED;
   const Strides4 gst{{op.chan_out * npos, npos, op.w_out, 1}};
-  int rc = launch_to_channels_last(grad_out, gst, gout_cl, op.batch, G, og, opad, op.h_out, op.w_out, stream);
+  const FilterJob job{filters, fst, rows, (int)og, (int)cg, (int)kk, (int)op.kw, (int)opad, 1, G * cg * kk * opad};
+  int rc = launch_to_channels_last(grad_out, gst, gout_cl, op.batch, G, og, opad, op.h_out, op.w_out, job, stream);
   if (rc) return rc;
-  const int64_t n_rows = G * cg * kk * opad;
-  filters_to_rows_kernel<<<grid_for(n_rows, sms), NT, 0, stream>>>(filters, fst, rows, (int)og, (int)cg, (int)kk,
-                                                                    (int)op.kw, (int)opad, 1, n_rows);
-  count_launch(false);
-  if ((rc = note_cuda_error(cudaGetLastError(), "filters_to_rows launch (data gradient)"))) return rc;
+  g_implicit_passes.fetch_add(1, std::memory_order_relaxed);
   return launch_conv_implicit(c, stream);
 }
 
@@ -882,6 +894,8 @@ int convtrans2d_backward(int dtype, const b200_convtrans2d_op* o, const void* im
   if (grad_filters) rc = backward_any(dtype, op, grad_out, nullptr, filters, fs, grad_filters, img, ws, stream);
   return rc;
 }
+
+uint64_t conv_implicit_passes() { return g_implicit_passes.load(); }
 
 void conv_set_lowering(int grad_img_mode, size_t group_bytes) {
   g_conv_grad_img_mode.store(grad_img_mode);

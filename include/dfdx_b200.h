@@ -183,6 +183,9 @@ int b200_selftest_bounded_wait(long long limit_cycles, long long* waited_cycles,
 uint64_t b200_launch_count(void);
 /* Of those, launches of tcgen05 tensor-core kernels. */
 uint64_t b200_tensor_launch_count(void);
+/* Convolution passes (a forward, a filter gradient or a data gradient) that the implicit-GEMM lowering has served
+ * since load (testing / profiling: tells which lowering a call took). */
+uint64_t b200_conv_implicit_count(void);
 
 /* ---- the two GEMM seams ---------------------------------------------------------------------- */
 

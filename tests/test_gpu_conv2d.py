@@ -198,13 +198,13 @@ def test_implicit_gemm_lowering(cuda_dev, oracle, case):
         assert lib.b200_set_conv_lowering(mode, 0) == 0
         try:
             y = torch.full(want.shape, float("nan"), device=dev.device)
-            l0, t0 = lib.b200_launch_count(), lib.b200_tensor_launch_count()
+            l0, t0, i0 = lib.b200_launch_count(), lib.b200_tensor_launch_count(), lib.b200_conv_implicit_count()
             dev.conv2d_forward(op, xd, wd, y)
-            fwd_launches = (lib.b200_launch_count() - l0, lib.b200_tensor_launch_count() - t0)
+            fwd = (lib.b200_launch_count() - l0, lib.b200_tensor_launch_count() - t0, lib.b200_conv_implicit_count() - i0)
             gx, gw = torch.ones_like(xd), torch.full_like(wd, 0.5)
-            l0, t0 = lib.b200_launch_count(), lib.b200_tensor_launch_count()
+            l0, i0 = lib.b200_launch_count(), lib.b200_conv_implicit_count()
             dev.conv2d_backward(op, xd, gx, wd, gw, god)
-            bwd_launches = (lib.b200_launch_count() - l0, lib.b200_tensor_launch_count() - t0)
+            bwd = (lib.b200_launch_count() - l0, lib.b200_conv_implicit_count() - i0)
             dev.synchronize()
         finally:
             lib.b200_set_conv_lowering(0, 0)
@@ -212,15 +212,15 @@ def test_implicit_gemm_lowering(cuda_dev, oracle, case):
         assert oracle.rel_frobenius(y, want) <= 1e-5, (case, mode)
         assert oracle.rel_frobenius(gx, wgx.double() + 1.0) <= 1e-5, (case, mode)
         assert oracle.rel_frobenius(gw, wgw.double() + 0.5) <= 1e-5, (case, mode)
+        groups = cfg["groups"]
         if mode == 0:
-            # implicit forward: layout change + filter rows + one tensor-core launch
-            assert fwd_launches == (3, 1), fwd_launches
-            # filter gradient: layout change + one launch per group + add; data gradient: 3 launches when implicit,
-            # else one GEMM + one fold
-            groups = cfg["groups"]
-            expect = 2 + groups + (3 if cfg["dgrad"] else 2)
-            assert bwd_launches[0] == expect, (bwd_launches, expect)
+            # implicit forward: one launch for the layout change and the filter rows, one tensor-core launch
+            assert fwd == (2, 1, 1), fwd
+            # filter gradient: layout change, one launch per group, add; data gradient: 2 launches when implicit, else
+            # one GEMM + one fold
+            assert bwd == (2 + groups + 2, 2 if cfg["dgrad"] else 1), bwd
         else:
-            assert fwd_launches == (2, 1), fwd_launches
+            assert fwd == (2, 1, 0), fwd                    # unfold + GEMM
+            assert bwd[1] == 0, bwd
     for a, b in zip(res[0], res[2]):
         assert oracle.rel_frobenius(a, b.double()) <= 2e-5
