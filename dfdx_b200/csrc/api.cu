@@ -186,7 +186,7 @@ int b200_set_tf32_split_mode(int mode) {
 
 /* Testing hook: force the N extent of the tensor-core tile (64, 128 or 256); 0 restores the heuristic. */
 int b200_set_tile_n(int bn) {
-  if (bn != 0 && bn != 64 && bn != 128 && bn != 256) return B200_ERR_UNSUPPORTED;
+  if (bn != 0 && bn != 64 && bn != 128 && bn != 256 && bn != 512) return B200_ERR_UNSUPPORTED;
   tc_set_tile_n(bn);
   return B200_OK;
 }

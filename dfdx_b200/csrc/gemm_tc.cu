@@ -287,6 +287,189 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// f16 kernel with a 256 x 256 tile per CTA (CfgHB): same roles as gemm_f16_kernel; each k-step issues two MMAs (rows
+// 0..127 and 128..255 of the A tile against the same B tile) into two accumulators; epilogue warp group eg drains
+// accumulator eg.  Row-major outputs through the staged TMA store / reduce-add only, whole-K tiles only.
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(CfgHB::THREADS, 1)
+gemm_f16_big_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+                    const __grid_constant__ CUtensorMap tma_c, const TcArgs g) {
+  using C = CfgHB;
+  constexpr int STAGES = C::STAGES, BN = C::BN;
+  constexpr int PRODUCER_WARP = 8, MMA_WARP = 9;
+
+  extern __shared__ uint8_t smem_dyn[];
+  __shared__ __align__(8) uint64_t bar_full[STAGES];
+  __shared__ __align__(8) uint64_t bar_empty[STAGES];
+  __shared__ __align__(8) uint64_t bar_tfull;
+  __shared__ __align__(8) uint64_t bar_tempty;
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_flag;
+
+  const uint32_t smem_base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  volatile int* abortp = &abort_flag;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(smem_u32(&bar_full[s]), 1);
+      mbar_init(smem_u32(&bar_empty[s]), 1);
+    }
+    mbar_init(smem_u32(&bar_tfull), 1);
+    mbar_init(smem_u32(&bar_tempty), 256);
+    abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == MMA_WARP) {
+    tmem_alloc(smem_u32(&tmem_slot), C::TMEM_COLS);
+    tmem_relinquish();
+  }
+  if (warp == PRODUCER_WARP && lane == 0) {
+    tma_prefetch_desc(&tma_a);
+    tma_prefetch_desc(&tma_b);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_slot;
+  const int total_kb = g.red * g.k_blocks;
+
+  if (warp == PRODUCER_WARP) {
+    if (lane == 0) {
+      uint32_t ring_s = 0, ring_ph = 0;
+      bool ok = true;
+      for (long long unit = blockIdx.x; ok && unit < g.total_units; unit += gridDim.x) {
+        const TileCoord t = decode_tile(g, unit);
+        int r = 0, kx = 0;
+        const int k_end = g.k_blocks * C::BK;
+        const int ax = g.a_x1 * t.ib1, ay = g.a_y0 * t.ib0, bx = g.b_x1 * t.ib1, by = g.b_y0 * t.ib0;
+        for (int i = 0; i < total_kb; ++i) {
+          const uint32_t s = ring_s, ph = ring_ph;
+          if (++ring_s == (uint32_t)STAGES) { ring_s = 0; ring_ph ^= 1u; }
+          if (!mbar_wait(smem_u32(&bar_empty[s]), ph ^ 1u, abortp, g.wait_limit)) { ok = false; break; }
+          const uint32_t full = smem_u32(&bar_full[s]);
+          mbar_expect_tx(full, C::STAGE_BYTES);
+          const uint32_t a_dst = smem_base + s * C::STAGE_BYTES;
+          load_operand<C::BMB, C::BK, C::CH, C::MN_LBO>(a_dst, &tma_a, full, g.a_ld, t.mt * C::BMB, kx, ax + g.a_xr * r, ay);
+          load_operand<BN, C::BK, C::CH, C::MN_LBO>(a_dst + C::A_BYTES, &tma_b, full, g.b_ld, t.nt * BN, kx,
+                                                     bx + g.b_xr * r, by);
+          kx += C::BK;
+          if (kx == k_end) { kx = 0; ++r; }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == MMA_WARP) {
+    if (lane == 0) {
+      const uint32_t idesc = (1u << 4) | ((uint32_t)(g.a_mn ? 1 : 0) << 15) | ((uint32_t)(g.b_mn ? 1 : 0) << 16) |
+                             ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+      const uint32_t a_lbo = g.a_mn ? C::MN_LBO : 16u, b_lbo = g.b_mn ? C::MN_LBO : 16u;
+      const uint32_t a_kadv = g.a_mn ? C::MN_KADV : C::K_KADV, b_kadv = g.b_mn ? C::MN_KADV : C::K_KADV;
+      const uint64_t da0 = make_smem_desc(smem_base, a_lbo, C::SBO, C::LAYOUT);
+      const uint64_t db0 = make_smem_desc(smem_base + C::A_BYTES, b_lbo, C::SBO, C::LAYOUT);
+      const uint32_t a_hi = (uint32_t)(da0 >> 32), b_hi = (uint32_t)(db0 >> 32);
+      const uint32_t a_lo0 = (uint32_t)da0, b_lo0 = (uint32_t)db0;
+      const uint32_t a_k16 = a_kadv >> 4, b_k16 = b_kadv >> 4;
+      constexpr uint32_t STAGE16 = C::STAGE_BYTES >> 4, HALF16 = C::A_HALF >> 4;
+      uint32_t ring_s = 0, ring_ph = 0, tcount = 0;
+      bool ok = true;
+      for (long long unit = blockIdx.x; ok && unit < g.total_units; unit += gridDim.x, ++tcount) {
+        // both accumulators are free once the epilogue has read the previous tile out of them
+        if (!mbar_wait(smem_u32(&bar_tempty), (tcount & 1u) ^ 1u, abortp, g.wait_limit)) { ok = false; break; }
+        tc_fence_after();
+        for (int i = 0; i < total_kb; ++i) {
+          const uint32_t s = ring_s, ph = ring_ph;
+          if (++ring_s == (uint32_t)STAGES) { ring_s = 0; ring_ph ^= 1u; }
+          if (!mbar_wait(smem_u32(&bar_full[s]), ph, abortp, g.wait_limit)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_lo = a_lo0 + (uint32_t)s * STAGE16, b_lo = b_lo0 + (uint32_t)s * STAGE16;
+#pragma unroll
+          for (int ks = 0; ks < C::KSTEPS; ++ks) {
+            const uint32_t acc = (i > 0 || ks > 0) ? 1u : 0u;
+            umma_lohi<2>(tmem_base, a_lo + ks * a_k16, a_hi, b_lo + ks * b_k16, b_hi, idesc, acc);
+            umma_lohi<2>(tmem_base + BN, a_lo + HALF16 + ks * a_k16, a_hi, b_lo + ks * b_k16, b_hi, idesc, acc);
+          }
+          umma_commit(smem_u32(&bar_empty[s]));
+        }
+        if (ok) umma_commit(smem_u32(&bar_tfull));
+      }
+    }
+    __syncwarp();
+  } else {
+    // epilogue: warp group eg (warps 4 eg .. 4 eg + 3) owns accumulator eg = rows 128 eg .. 128 eg + 127 of the tile
+    const int eg = warp >> 2, ew = warp & 3;
+    const int bar_id = 1 + eg;
+    const bool leader = (threadIdx.x & 127) == 0;
+    uint32_t tcount = 0;
+    bool ok = true;
+    for (long long unit = blockIdx.x; ok && unit < g.total_units; unit += gridDim.x, ++tcount) {
+      const TileCoord t = decode_tile(g, unit);
+      const int row0 = t.mt * C::BMB + eg * BM;              // first output row of this group's accumulator
+      const int row = row0 + ew * 32 + lane;
+      bool got = mbar_wait(smem_u32(&bar_tfull), tcount & 1u, abortp, g.wait_limit);
+      got = named_barrier_and(bar_id, 128, got);             // the staged stores use named barriers: all or none
+      if (!got) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + ((uint32_t)(ew * 32) << 16) + (uint32_t)eg * BN;
+      const int r_in = ew * 32 + lane;
+      const uint32_t sw = (uint32_t)(r_in & 7);
+      const uint32_t stage = smem_base + C::OFF_OUT + (uint32_t)eg * C::OUT_BYTES;
+      if (row0 < g.m) {                                      // group-uniform
+#pragma unroll
+        for (int c2 = 0; c2 < BN / 64; ++c2) {
+          const int col0 = t.nt * BN + c2 * 64;
+          if (col0 < g.n) {
+            if (leader) bulk_wait_group_read<0>();           // the store that last used this buffer has read it
+            named_barrier_sync(bar_id, 128);
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              uint32_t v[32];
+              tmem_ld_32x32(taddr + c2 * 64 + h * 32, v);
+              tmem_wait_ld();
+              float f[32];
+#pragma unroll
+              for (int q = 0; q < 32; ++q) f[q] = __uint_as_float(v[q]);
+              if (g.fused && row < g.m) {
+                const int valid = (g.n - col0 - h * 32) < 32 ? (g.n - col0 - h * 32) : 32;
+                if (valid > 0) fused_epilogue<__half>(f, g, row, col0 + h * 32, valid);
+              }
+#pragma unroll
+              for (int q4 = 0; q4 < 4; ++q4) {
+                uint32_t w[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  const __half2 hh = __floats2half2_rn(f[q4 * 8 + 2 * e], f[q4 * 8 + 2 * e + 1]);
+                  w[e] = *reinterpret_cast<const uint32_t*>(&hh);
+                }
+                st_shared_v4_u32(stage + (uint32_t)r_in * 128u + ((((uint32_t)(h * 4 + q4)) ^ sw) << 4), w[0], w[1], w[2], w[3]);
+              }
+            }
+            fence_proxy_async_smem();
+            named_barrier_sync(bar_id, 128);
+            if (leader) {
+              if (g.c_tma == 2) tma_reduce_add_4d(&tma_c, stage, col0, row0, t.ib1, t.ib0);
+              else tma_store_4d(&tma_c, stage, col0, row0, t.ib1, t.ib0);
+              bulk_commit_group();
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(smem_u32(&bar_tempty));
+    }
+    if (leader) bulk_wait_group_read<0>();
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  teardown(abort_flag, g.status);
+  if (warp == MMA_WARP) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, C::TMEM_COLS);
+  }
+}
+
 // 3xTF32 operand split of the stages, run by SPLIT_THREADS threads (tt = 0 .. SPLIT_THREADS-1).
 // Each raw f32 x stays in place as the `big` operand (the tensor core reads its top 19 bits) and
 // small = x - trunc_tf32(x) (exact; the tensor core again keeps its top 19 bits) is written RAW_BYTES
@@ -946,7 +1129,7 @@ int build_launch(Launch& L, const Plan& pl, int esize, int tm, int tn, int bmc, 
   }
   g.c_tma = 0;
   L.mc = L.ma;                                               // a valid descriptor even when it is not used
-  if (!pl.c_col && g_store_mode != 1 && tm == BM) {
+  if (!pl.c_col && g_store_mode != 1 && (tm == BM || tm == 2 * BM)) {
     // output map (n, m, b1, b0), box 128 bytes x 128 rows, 128B swizzle: the epilogue stages groups of 64 f16 or
     // 32 f32 columns
     if (encode_map(&L.mc, p.c, esize, p.n, p.m, pl.ldc, p.b1, p.c_b1, p.b0, p.c_b0, 128 / esize, 128,
@@ -1121,6 +1304,22 @@ int launch_pair_plan(const Plan& pl, int esize, cudaStream_t stream) {
   return launch_pair(esize, L.ma, L.mb, L.g, grid_sms(device_state()), stream);
 }
 
+// f16, 256 x 256 tiles (gemm_f16_big_kernel).  Returns B200_ERR_UNSUPPORTED when the output cannot leave through
+// the staged TMA store (the only epilogue that kernel has).
+int launch_big_f16(const Plan& pl, cudaStream_t stream) {
+  Launch L;
+  const int st = build_launch(L, pl, 2, CfgHB::BMB, CfgHB::BN, CfgHB::BMB, CfgHB::BN, CfgHB::BK, CfgHB::CH);
+  if (st) return st;
+  if (!L.g.c_tma) return B200_ERR_UNSUPPORTED;
+  DeviceState* ds = device_state();
+  L.g.kb_per_slice = L.g.red * L.g.k_blocks;
+  const long long grid = L.g.total_units < grid_sms(ds) ? L.g.total_units : grid_sms(ds);
+  if (grid <= 0) return B200_OK;
+  gemm_f16_big_kernel<<<(unsigned)grid, CfgHB::THREADS, CfgHB::SMEM_BYTES, stream>>>(L.ma, L.mb, L.mc, L.g);
+  count_launch(true);
+  return note_cuda_error(cudaGetLastError(), "tensor-core gemm launch (256 x 256 tiles)");
+}
+
 template <int ESIZE, int BN>
 int launch_bn(const Plan& pl, cudaStream_t stream, int ksplit) {
   if constexpr (ESIZE == 2) return launch_cfg<CfgH<BN>, 2, BN>(pl, stream, gemm_f16_kernel<BN>, ksplit);
@@ -1154,7 +1353,25 @@ int launch_es(const Plan& pl, cudaStream_t stream) {
   const double best = choose_tile(pl, ESIZE, &bn);
   const int g_force_bn = b200::g_force_bn.load(), g_pair_mode = b200::g_pair_mode.load(),
             g_split_mode = b200::g_split_mode.load();     // one read per launch
-  if (g_force_bn) bn = g_force_bn;
+  if (g_force_bn && g_force_bn != 512) bn = g_force_bn;
+  // f16: 256 x 256 tiles per CTA where a wave model says they win (their main loop keeps the tensor pipe busier, but
+  // nothing overlaps their epilogue): measured per 64-wide k-block 0.55 us for a 128 x 256 tile against 0.83 us for a
+  // 256 x 256 one, and per tile about 1 us against 3.7 us beside the main loop.
+  if constexpr (ESIZE == 2) {
+    if ((g_force_bn == 0 || g_force_bn == 512) && !pl.c_col && p.m > BM && p.n > 128 && b200::g_store_mode.load() != 1) {
+      const int64_t kb = p.red * ((p.k + 63) / 64);
+      const int64_t t_small = ((p.m + BM - 1) / BM) * ((p.n + 255) / 256) * p.b0 * p.b1;
+      const int64_t t_big = ((p.m + 255) / 256) * ((p.n + 255) / 256) * p.b0 * p.b1;
+      const double c_small = (double)((t_small + sms - 1) / sms) * ((double)kb * 0.55 + 1.0);
+      const double c_big = (double)((t_big + sms - 1) / sms) * ((double)kb * 0.83 + 3.7);
+      // below about two thirds of a wave of big tiles the K split of the small-tile kernel is the better tool
+      if (g_force_bn == 512 || (bn == 256 && 3 * t_big >= 2 * sms && c_big < 0.9 * c_small)) {
+        const int rc = launch_big_f16(pl, stream);
+        if (rc != B200_ERR_UNSUPPORTED) return rc;
+      }
+    }
+  }
+  if (g_force_bn == 512) bn = 256;
   // CTA pairs (256 x 256 tiles on two SMs) when the problem fills the machine with them.
   if (!g_force_bn && g_pair_mode != 1 && p.n > 128 && !p.fused()) {   // the pair kernels have no fused epilogue
     const int64_t tiles2 = ((p.m + 255) / 256) * ((p.n + 255) / 256) * p.b0 * p.b1;
@@ -1441,6 +1658,7 @@ int tc_setup_device() {
   if ((st = set_attr<CfgH<64>>(gemm_f16_kernel<64>))) return st;
   if ((st = set_attr<CfgH<128>>(gemm_f16_kernel<128>))) return st;
   if ((st = set_attr<CfgH<256>>(gemm_f16_kernel<256>))) return st;
+  if ((st = set_attr<CfgHB>(gemm_f16_big_kernel))) return st;
   if ((st = set_attr<CfgS<64>>(gemm_tf32x3_kernel<64>))) return st;
   if ((st = set_attr<CfgS<128>>(gemm_tf32x3_kernel<128>))) return st;
   if ((st = set_attr<CfgS<256>>(gemm_tf32x3_kernel<256>))) return st;

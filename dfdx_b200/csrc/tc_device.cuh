@@ -239,6 +239,30 @@ struct CfgH {
   static constexpr uint32_t K_KADV = 32;                    // 16 elements of K per MMA
 };
 
+// f16, 256 x 256 output tile per CTA (two 128-row accumulators that fill the 512 TMEM columns): per 64-wide k-block
+// 64 KB are staged and the MMAs read 96 KB for 1024 tensor clocks, 160 B/clock against the 192 B/clock of the
+// 128 x 256 tile, which is what lets the main loop run at the tensor pipe's pace.  No spare TMEM, so a tile's
+// epilogue does not overlap the next tile's main loop: for long K and outputs of many tiles.
+struct CfgHB {
+  static constexpr int BMB = 256, BN = 256;
+  static constexpr int BK = 64, CH = 64, KSTEPS = 4;
+  static constexpr int A_BYTES = BMB * 128;
+  static constexpr int B_BYTES = BN * 128;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES = 3;
+  static constexpr int THREADS = 320;                       // 8 epilogue warps, TMA producer warp, MMA warp
+  static constexpr int TMEM_COLS = 512;
+  static constexpr int OUT_BYTES = 128 * 128;               // one staged output group per epilogue warp group
+  static constexpr int OFF_OUT = STAGES * STAGE_BYTES;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 2 * OUT_BYTES + 1024;
+  static constexpr uint32_t LAYOUT = 2u;                    // SWIZZLE_128B
+  static constexpr uint32_t SBO = 1024;
+  static constexpr uint32_t MN_LBO = BK * 128;
+  static constexpr uint32_t MN_KADV = 2 * 1024;
+  static constexpr uint32_t K_KADV = 32;
+  static constexpr uint32_t A_HALF = 128 * 128;             // bytes from the first to the second 128-row block of A
+};
+
 // f32 (3xTF32): K-major tiles are 64-byte rows under the 64B swizzle; MN-major tiles are chunks of
 // 32 columns x BK k-rows of 128 bytes under the 128B swizzle with 32-byte atoms.
 template <int BN>

@@ -114,8 +114,9 @@ int b200_set_path(int path);
  * mode 1 (default) stores small as computed, 0 rounds it to tf32 first (cvt.rna).  Both stay inside the f32
  * tolerance; any other value returns B200_ERR_UNSUPPORTED. */
 int b200_set_tf32_split_mode(int mode);
-/* Tensor-core tile width override (testing / profiling): 64, 128 or 256 output columns per CTA tile;
- * 0 (default) picks the widest tile that still gives every SM work. */
+/* Tensor-core tile width override (testing / profiling): 64, 128 or 256 output columns per CTA tile (128 rows);
+ * 512 stands for the f16 kernel with 256 x 256 tiles (f32 problems then take 256 columns); 0 (default) lets a wave
+ * model choose. */
 int b200_set_tile_n(int bn);
 /* MN-major operand loading (testing / profiling): 1 (default) brings a tile's column chunks with one
  * 5-D TMA box where the extent is a whole number of chunks; 0 always issues one 4-D box per chunk. */

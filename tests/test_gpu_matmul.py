@@ -128,6 +128,34 @@ def test_tensor_core_layouts(cuda_dev, oracle, dtype, layout, tile_n, store):
         cuda_dev.set_path(dfdx_b200.PATH_AUTO)
 
 
+BIG_SHAPES = [(256, 64, 256), (512, 192, 512), (296, 136, 264), (264, 520, 392), (1000, 1032, 136 * 2), (384, 40, 520)]
+
+
+@pytest.mark.parametrize("layout", ["".join(p) for p in itertools.product("rc", repeat=3)])
+def test_f16_256x256_tile_kernel(cuda_dev, oracle, layout):
+    """The f16 kernel with 256 x 256 tiles per CTA (two accumulators filling TMEM), forced: K-major / MN-major A and B,
+    row-major / transposed C, ragged M, N and K, outputs whose second 128-row block is empty or partial, beta 0
+    (NaN-poisoned output) and beta 1; plus a batched problem with MultiHeadAttention-like batch strides."""
+    dev = cuda_dev
+    dev.set_path(dfdx_b200.PATH_TENSOR)
+    assert dev.lib.b200_set_tile_n(512) == 0
+    try:
+        before = dev.lib.b200_tensor_launch_count()
+        for i, (m, k, n) in enumerate(BIG_SHAPES):
+            check_gemm(dev, oracle, m, k, n, layout[0], layout[1], layout[2], i % 2, torch.float16, pad=8, seed=900 + i)
+        assert dev.lib.b200_tensor_launch_count() - before == len(BIG_SHAPES)
+        g = gen(77)
+        a = (torch.randn(3, 2, 296, 72, generator=g) * 0.3).half().to(dev.device)
+        b = (torch.randn(3, 2, 72, 264, generator=g) * 0.3).half().to(dev.device)
+        out = dev.matmat_batch4_forward(a, b)
+        dev.synchronize()
+        want, _ = oracle.matmul(a.cpu(), b.cpu())
+        assert frob(oracle, out, want) <= FROB_TOL[torch.float16]
+    finally:
+        dev.lib.b200_set_tile_n(0)
+        dev.set_path(dfdx_b200.PATH_AUTO)
+
+
 @pytest.mark.parametrize("dtype", [torch.float16, torch.float32])
 @pytest.mark.parametrize("layout", ["".join(p) for p in itertools.product("rc", repeat=3)])
 def test_cta_pair_kernels(cuda_dev, oracle, dtype, layout):
