@@ -390,7 +390,11 @@ def make_c1(h, rows=1024, strong=False, group=None):
     `rows` rows of A / C / dC (the M-partition); the shared B's gradient is all-reduced."""
     import torch
     from dfdx_b200.parallel import allreduce_shared_grads
-    dev, device = h.dev, h.device
+    import dfdx_b200
+    device = h.device
+    # dfdx's device carries a second stream on which the grad_lhs GEMM of every backward runs beside the grad_rhs GEMM
+    # (matmul/cuda_kernel.rs:282-310); with GEMMs this small the two share the machine
+    dev = dfdx_b200.Cuda(device.index, par_stream=True)
     g = torch.Generator(device="cpu").manual_seed(0xD0FD + 1 + 1000 * h.rank)
     a = (torch.rand(rows, 1024, generator=g) * 2 - 1).to(device)
     b = (torch.rand(1024, 1024, generator=g) * 2 - 1).to(device)
@@ -464,7 +468,8 @@ def make_c4(h, group=None):
 OTHER = {
     # name: (builder, flops per step per GPU, algorithmic bytes, bound, arithmetic, description)
     "c1": (make_c1, 6 * 1024 ** 3, 44 * MIB, "tensor", "f32",
-           "config[0]: MatMat f32 A[1024,1024] x B[1024,1024], fwd + grad_lhs + grad_rhs"),
+           "config[0]: MatMat f32 A[1024,1024] x B[1024,1024], fwd + grad_lhs + grad_rhs (the two gradient GEMMs on "
+           "dfdx's two streams)"),
     "c3": (make_c3, 2 * 6 * 256 * 512 * 512 * 64, 1136 * MIB, "hbm", "f16",
            "config[2]: MatMatBatch4 f16 Q,K,V[16,16,512,64]: QK^T and PV, forward + backward (6 GEMM groups; the "
            "score-sized tensors cross HBM, so the bound is memory)"),

@@ -766,7 +766,7 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_const
       const int tile_col0 = CV ? t.nt * g.tile_cols : t.nt * BN;
       const int n_end = (CV && tile_col0 + g.tile_valid < g.n) ? tile_col0 + g.tile_valid : g.n;
       float* cbase = (float*)g.c + t.ib0 * g.c_b0 + t.ib1 * g.c_b1;
-      if (g.c_tma && !partial) {
+      if (g.c_tma) {
         // Output through shared memory and TMA, as in the f16 kernel: per-thread row stores hand the memory
         // system 32 separate 16- or 32-byte pieces per instruction, which bounds GEMMs with a short K and a
         // wide output; a staged group of 128 rows x 32 columns leaves as one bulk tensor store (beta = 0) or
@@ -783,7 +783,10 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_const
             if (g.fused && row < g.m) fused_epilogue<float>(&acc[c * 32], g, row, col0, valid);
             if (CV && valid < 32 && n_end < g.n) {
               // the group's other columns belong to the next tile (the map clips only at the output's end)
-              if (row < g.m) store_chunk(cbase + (long long)row * g.ldc + col0, &acc[c * 32], valid, g.beta, 0);
+              if (row < g.m) {
+                if (partial) add_chunk_atomic(cbase + (long long)row * g.ldc + col0, &acc[c * 32], valid);
+                else store_chunk(cbase + (long long)row * g.ldc + col0, &acc[c * 32], valid, g.beta, 0);
+              }
               continue;
             }
             if (leader) bulk_wait_group_read<0>();       // the store that last used this buffer has read it
@@ -798,7 +801,10 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_const
             fence_proxy_async_smem();
             named_barrier_sync(1 + wg, 128);
             if (leader) {
-              if (g.c_tma == 2) tma_reduce_add_4d(&tma_c, stage, col0, t.mt * BM, t.ib1, t.ib0);
+              // a partial sum (K slice, tail range) is ADDED, whatever beta is: the output holds zeros or beta * C;
+              // the bulk reduce-add works on whole 128-byte lines, where per-thread red.global.add.v4 touches 32 lines
+              // per instruction
+              if (g.c_tma == 2 || partial) tma_reduce_add_4d(&tma_c, stage, col0, t.mt * BM, t.ib1, t.ib0);
               else tma_store_4d(&tma_c, stage, col0, t.mt * BM, t.ib1, t.ib0);
               bulk_commit_group();
             }
@@ -1614,6 +1620,7 @@ int launch_conv_implicit_wgrad(const ConvImplicitWgrad& c, cudaStream_t stream) 
     if (rc) return rc;
   }
   L.mc = L.ma;
+  const bool out_map = encode_map(&L.mc, c.out, 4, kr, c.m, kr, 1, 0, 1, 0, 32, 128, CU_TENSOR_MAP_SWIZZLE_128B) == B200_OK;
   TcArgs& g = L.g;
   cv_common_args(g, ds);
   g.m = (int)c.m; g.n = (int)kr;
@@ -1635,6 +1642,7 @@ int launch_conv_implicit_wgrad(const ConvImplicitWgrad& c, cudaStream_t stream) 
   g.kb_per_slice = (int)kb_per; g.ksplit = (int)slices;
   // a single slice still adds into `out` (which holds zeros or a running sum): ksplit > 1 selects the atomic path
   if (g.ksplit == 1) { g.beta = 1; }
+  if (out_map && g_store_mode.load() != 1) g.c_tma = 2;    // the slices' sums leave as bulk reduce-adds
   g.total_units = g.total_tiles * slices;
   g.b_mn = 1;
   g.c = c.out; g.ldc = kr;
