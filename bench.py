@@ -446,6 +446,20 @@ def make_attn(h):
     return step
 
 
+def make_f16(h):
+    """One f16 GEMM of 8192^3 (the shape the measured cuBLAS bf16 peak of this pool is quoted on)."""
+    import torch
+    dev, device = h.dev, h.device
+    g = torch.Generator(device="cpu").manual_seed(0xD0FD + 16 + 1000 * h.rank)
+    a = torch.randn(8192, 8192, generator=g).half().to(device)
+    b = torch.randn(8192, 8192, generator=g).half().to(device)
+    c = torch.empty(8192, 8192, dtype=torch.float16, device=device)
+
+    def step():
+        dev.gemm((8192, 8192, 8192), a, a.stride(), b, b.stride(), 0.0, c, c.stride())
+    return step
+
+
 def make_c4(h, group=None):
     import torch
     from dfdx_b200.parallel import allreduce_shared_grads
@@ -476,6 +490,8 @@ OTHER = {
     "attn": (make_attn, 2 * 6 * 256 * 512 * 512 * 64, 9 * 16 * MIB, "tensor", "f16",
              "config[2] shapes, fused: softmax(Q K^T / 8) V for f16 Q,K,V[16,16,512,64], forward + backward "
              "(b200_attention_forward / _backward; flops of the six GEMM groups, recomputation not counted)"),
+    "f16": (make_f16, 2 * 8192 ** 3, 3 * 128 * MIB, "tensor", "f16",
+            "one f16 GEMM 8192^3, f32 accumulate (not a BASELINE configuration: the shape the pool's cuBLAS peak is measured on)"),
     "c4": (make_c4, 3 * 2 * 32 * 128 * 576 * 3136, 246 * MIB, "tensor", "f32",
            "config[3]: conv2d f32 x[32,64,56,56] * w[128,64,3,3], stride 1, padding 1, fwd + both gradients"),
 }
@@ -700,7 +716,7 @@ def main():
                          "in line on the compute stream after both gradient GEMMs")
     ap.add_argument("--overlap-sms", type=int, default=OVERLAP_SMS,
                     help="SMs the grad_lhs GEMM leaves to the overlapped all-reduce (and that collective's CTA bound)")
-    ap.add_argument("--workload", default="c2", choices=["c1", "c2", "c3", "c4", "c5", "attn"],
+    ap.add_argument("--workload", default="c2", choices=["c1", "c2", "c3", "c4", "c5", "attn", "f16"],
                     help="c2 (default) is the benchmark line with every configuration inside; the others time one "
                          "configuration alone (device-resident; used for profiling)")
     args = ap.parse_args()
@@ -800,7 +816,7 @@ def main():
     configs = None
     if not args.headline_only:
         small = max(10, min(args.steps, 30))
-        configs = {name: run_other(h, name, small, warmup) for name in ("c1", "c3", "c4", "attn")}
+        configs = {name: run_other(h, name, small, warmup) for name in ("c1", "c3", "c4", "attn", "f16")}
         configs["c5"] = run_transformer(h, args, max(10, min(args.steps, 30)), warmup)
     h.sampler.stop()
 
