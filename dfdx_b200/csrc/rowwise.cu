@@ -174,6 +174,125 @@ __global__ void __launch_bounds__(256) layer_norm_fwd_reg_kernel(const T* __rest
   }
 }
 
+template <typename T>
+__device__ __forceinline__ void unpack_vec(const uint4& raw, float* f) {
+  const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+  for (int q = 0; q < Vec<T>::N; ++q) f[q] = to_f(e[q]);
+}
+
+// The register kernel for rows that allow 16-byte access, with fewer instructions per row (one warp per row is bound
+// by instruction issue): gamma and beta wait in shared memory as f32 (lane-major float4s), the next row's loads are
+// issued one row ahead, and a launch-resident grid walks the rows.
+constexpr int LN_FWD_VEC_BLOCKS_PER_SM = 3;
+template <typename T, int MAXV>
+__global__ void __launch_bounds__(256, LN_FWD_VEC_BLOCKS_PER_SM)
+    layer_norm_fwd_vec_kernel(const T* __restrict__ x, long long x_ld, const T* __restrict__ gamma, const T* __restrict__ beta,
+                              float eps, T* __restrict__ y, long long y_ld, float* __restrict__ stats, long long rows, int cols) {
+  constexpr int N = Vec<T>::N, J = N / 4;
+  __shared__ float4 gamma_s[MAXV * J][32], beta_s[MAXV * J][32];
+  const int lane = threadIdx.x & 31;
+  const long long warp0 = (long long)blockIdx.x * 8 + (threadIdx.x >> 5), nwarps = (long long)gridDim.x * 8;
+  const float inv_n = 1.f / (float)cols;
+  for (int i = threadIdx.x; i < MAXV * J * 32; i += 256) {
+    const int vj = i >> 5, ln = i & 31, col = ((vj / J) * 32 + ln) * N + (vj % J) * 4;
+    float4 gv = make_float4(1.f, 1.f, 1.f, 1.f), bv = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (col < cols) {
+      if (gamma) gv = make_float4(to_f(gamma[col]), to_f(gamma[col + 1]), to_f(gamma[col + 2]), to_f(gamma[col + 3]));
+      if (beta) bv = make_float4(to_f(beta[col]), to_f(beta[col + 1]), to_f(beta[col + 2]), to_f(beta[col + 3]));
+    }
+    gamma_s[vj][ln] = gv;
+    beta_s[vj][ln] = bv;
+  }
+  __syncthreads();
+  uint4 nx[MAXV];
+  auto fetch = [&](long long r) {
+#pragma unroll
+    for (int v = 0; v < MAXV; ++v)
+      if ((v * 32 + lane) * N < cols) nx[v] = *reinterpret_cast<const uint4*>(x + r * x_ld + (v * 32 + lane) * N);
+  };
+  if (warp0 < rows) fetch(warp0);
+  for (long long r = warp0; r < rows; r += nwarps) {
+    float f[MAXV][N];
+    float s = 0.f;
+#pragma unroll
+    for (int v = 0; v < MAXV; ++v) {
+      if ((v * 32 + lane) * N < cols) {
+        unpack_vec<T>(nx[v], f[v]);
+#pragma unroll
+        for (int q = 0; q < N; ++q) s += f[v][q];
+      }
+    }
+    if (r + nwarps < rows) fetch(r + nwarps);
+    const float mean = warp_sum(s) * inv_n;
+    float sq = 0.f;
+#pragma unroll
+    for (int v = 0; v < MAXV; ++v) {
+      if ((v * 32 + lane) * N < cols) {
+#pragma unroll
+        for (int q = 0; q < N; ++q) {
+          f[v][q] -= mean;
+          sq = fmaf(f[v][q], f[v][q], sq);
+        }
+      }
+    }
+    const float rstd = 1.f / sqrtf(warp_sum(sq) * inv_n + eps);
+    T* yr = y + r * y_ld;
+#pragma unroll
+    for (int v = 0; v < MAXV; ++v) {
+      const int c = (v * 32 + lane) * N;
+      if (c < cols) {
+#pragma unroll
+        for (int j = 0; j < J; ++j) {
+          const float4 gm = gamma_s[v * J + j][lane], bt = beta_s[v * J + j][lane];
+          const float* gmp = reinterpret_cast<const float*>(&gm);
+          const float* btp = reinterpret_cast<const float*>(&bt);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) f[v][j * 4 + e] = fmaf(f[v][j * 4 + e] * rstd, gmp[e], btp[e]);
+        }
+        store_vec(yr, c, cols, true, f[v]);
+      }
+    }
+    if (stats && lane == 0) { stats[2 * r] = mean; stats[2 * r + 1] = rstd; }
+  }
+}
+
+// Sums acc[v][q] (this lane's columns (v * 32 + lane) * N + q) over the block's eight warps and adds the result
+// into out[] with one vector atomic per four columns; out may be null.  All threads of the block call it.
+template <int N, int MAXV>
+__device__ __forceinline__ void block_column_sums(float (*red)[32 * N + 1], const float (*acc)[N], float* __restrict__ out,
+                                                  int cols, int warp, int lane) {
+#pragma unroll
+  for (int v = 0; v < MAXV; ++v) {
+    if (v * 32 * N >= cols) break;
+    __syncthreads();
+#pragma unroll
+    for (int q = 0; q < N; ++q) red[warp][lane * N + q] = acc[v][q];
+    __syncthreads();
+    if (out) {
+      for (int i = threadIdx.x * 4; i < 32 * N; i += 256 * 4) {
+        const int col = v * 32 * N + i;
+        if (col < cols) {
+          float t[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+          for (int w = 0; w < 8; ++w) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) t[e] += red[w][i + e];
+          }
+          if (col + 3 < cols && ((uintptr_t)(out + col) & 15) == 0) {
+            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(out + col), "f"(t[0]), "f"(t[1]), "f"(t[2]),
+                         "f"(t[3]) : "memory");
+          } else {
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+              if (col + e < cols) atomicAdd(out + col + e, t[e]);
+          }
+        }
+      }
+    }
+  }
+}
+
 // MAXV vectors per lane: cols <= 32 * N * MAXV.  Per-lane partial sums of dgamma / dbeta live in registers over all
 // rows of the warp, are combined across the block's warps in shared memory and added to global memory once per block.
 template <typename T, int MAXV>
@@ -240,37 +359,127 @@ __global__ void __launch_bounds__(256) layer_norm_bwd_kernel(const T* __restrict
       }
     }
   }
-  // block reduction of the column sums, one 32*N-column slab at a time
+  block_column_sums<N, MAXV>(red, dg, ggamma, cols, warp, lane);
+  block_column_sums<N, MAXV>(red, db, gbeta, cols, warp, lane);
+}
+
+// The same for rows that allow 16-byte access, arranged for few instructions per row (with one warp per row the
+// kernel is bound by instruction issue, not by DRAM): x and g are converted once, the row's result is two fused
+// multiply-adds per element, gamma as f32 and the running column sums for dgamma / dbeta live in shared memory
+// (lane-major float4s; the sums are touched only by their owner until the end), which frees the registers for the
+// next row's loads, issued one row ahead.  Two blocks per SM, one launch-resident wave.
+
+constexpr int LN_BWD_VEC_BLOCKS_PER_SM = 2;
+template <typename T, int MAXV>
+__global__ void __launch_bounds__(256, LN_BWD_VEC_BLOCKS_PER_SM)
+    layer_norm_bwd_vec_kernel(const T* __restrict__ x, long long x_ld, const T* __restrict__ gamma, const float* __restrict__ stats,
+                              const T* __restrict__ g, long long g_ld, T* __restrict__ gx, long long gx_ld, int accumulate_x,
+                              float* __restrict__ ggamma, float* __restrict__ gbeta, long long rows, int cols) {
+  constexpr int N = Vec<T>::N, J = N / 4;
+  __shared__ float4 acc[8][2][MAXV * J][32];                   // [warp][g * x-hat | g][vector, quarter][lane]
+  __shared__ float4 gamma_s[MAXV * J][32];                     // gamma (ones without it) in the same order
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const long long warp0 = (long long)blockIdx.x * 8 + warp, nwarps = (long long)gridDim.x * 8;
+  const float inv_n = 1.f / (float)cols;
 #pragma unroll
-  for (int v = 0; v < MAXV; ++v) {
-    if (v * 32 * N >= cols) break;
+  for (int i = 0; i < MAXV * J; ++i) acc[warp][0][i][lane] = acc[warp][1][i][lane] = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int i = threadIdx.x; i < MAXV * J * 32; i += 256) {
+    const int vj = i >> 5, ln = i & 31, col = ((vj / J) * 32 + ln) * N + (vj % J) * 4;
+    float4 gv = make_float4(1.f, 1.f, 1.f, 1.f);
+    if (gamma && col < cols) gv = make_float4(to_f(gamma[col]), to_f(gamma[col + 1]), to_f(gamma[col + 2]), to_f(gamma[col + 3]));
+    gamma_s[vj][ln] = gv;
+  }
+  __syncthreads();
+  uint4 nx[MAXV], ng[MAXV];
+  float nmean = 0.f, nrstd = 0.f;
+  auto fetch = [&](long long r) {
 #pragma unroll
-    for (int pass = 0; pass < 2; ++pass) {
-      float* out = pass == 0 ? ggamma : gbeta;
-      __syncthreads();
+    for (int v = 0; v < MAXV; ++v) {
+      const int c = (v * 32 + lane) * N;
+      if (c < cols) {
+        nx[v] = *reinterpret_cast<const uint4*>(x + r * x_ld + c);
+        ng[v] = *reinterpret_cast<const uint4*>(g + r * g_ld + c);
+      }
+    }
+    nmean = stats[2 * r]; nrstd = stats[2 * r + 1];
+  };
+  if (warp0 < rows) fetch(warp0);
+  for (long long r = warp0; r < rows; r += nwarps) {
+    // x-hat = x * rstd - mean * rstd; d = rstd * (gg - c1 - x-hat * c2) as two fused multiply-adds
+    const float rstd = nrstd, shift = -nmean * nrstd;
+    float xh[MAXV][N], gg[MAXV][N];
+    float s1 = 0.f, s2 = 0.f;
 #pragma unroll
-      for (int q = 0; q < N; ++q) red[warp][lane * N + q] = pass == 0 ? dg[v][q] : db[v][q];
-      __syncthreads();
-      if (out) {
-        // four columns per thread and one vector atomic (red.global.add.v4.f32) where the output allows it
-        for (int i = threadIdx.x * 4; i < 32 * N; i += 256 * 4) {
-          const int col = v * 32 * N + i;
-          if (col < cols) {
-            float t[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int v = 0; v < MAXV; ++v) {
+      if ((v * 32 + lane) * N < cols) {
+        float fg[N];
+        unpack_vec<T>(nx[v], xh[v]);
+        unpack_vec<T>(ng[v], fg);
 #pragma unroll
-            for (int w = 0; w < 8; ++w) {
+        for (int j = 0; j < J; ++j) {
+          float4 dg = acc[warp][0][v * J + j][lane], db = acc[warp][1][v * J + j][lane];
+          const float4 gm = gamma_s[v * J + j][lane];
+          float* dgp = reinterpret_cast<float*>(&dg);
+          float* dbp = reinterpret_cast<float*>(&db);
+          const float* gmp = reinterpret_cast<const float*>(&gm);
 #pragma unroll
-              for (int e = 0; e < 4; ++e) t[e] += red[w][i + e];
-            }
-            if (col + 3 < cols && ((uintptr_t)(out + col) & 15) == 0) {
-              asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(out + col), "f"(t[0]), "f"(t[1]), "f"(t[2]),
-                           "f"(t[3]) : "memory");
-            } else {
-#pragma unroll
-              for (int e = 0; e < 4; ++e)
-                if (col + e < cols) atomicAdd(out + col + e, t[e]);
-            }
+          for (int e = 0; e < 4; ++e) {
+            const int q = j * 4 + e;
+            xh[v][q] = fmaf(xh[v][q], rstd, shift);
+            gg[v][q] = fg[q] * gmp[e];
+            s1 += gg[v][q];
+            s2 = fmaf(gg[v][q], xh[v][q], s2);
+            dgp[e] = fmaf(fg[q], xh[v][q], dgp[e]);
+            dbp[e] += fg[q];
           }
+          acc[warp][0][v * J + j][lane] = dg;
+          acc[warp][1][v * J + j][lane] = db;
+        }
+      }
+    }
+    if (r + nwarps < rows) fetch(r + nwarps);                  // this row's packed copy is consumed: reuse its registers
+    const float c1 = warp_sum(s1) * inv_n, c2 = warp_sum(s2) * inv_n;
+    if (gx) {
+      T* or_ = gx + r * gx_ld;
+      const float k0 = -rstd * c1, k2 = -rstd * c2;
+#pragma unroll
+      for (int v = 0; v < MAXV; ++v) {
+        const int c = (v * 32 + lane) * N;
+        if (c < cols) {
+          float d[N];
+          if (accumulate_x) {
+            const uint4 ro = *reinterpret_cast<const uint4*>(or_ + c);
+            unpack_vec<T>(ro, d);
+          }
+#pragma unroll
+          for (int q = 0; q < N; ++q) {
+            const float t = fmaf(rstd, gg[v][q], fmaf(k2, xh[v][q], k0));
+            d[q] = accumulate_x ? d[q] + t : t;
+          }
+          store_vec(or_, c, cols, true, d);
+        }
+      }
+    }
+  }
+  __syncthreads();
+  // threads 0..127 add the eight warps' sums of g * x-hat into dgamma, threads 128..255 those of g into dbeta
+  const int kind = threadIdx.x >> 7;
+  float* out = kind ? gbeta : ggamma;
+  if (out) {
+    for (int i = threadIdx.x & 127; i < MAXV * J * 32; i += 128) {
+      const int vj = i >> 5, ln = i & 31, col = ((vj / J) * 32 + ln) * N + (vj % J) * 4;
+      if (col < cols) {                                        // cols is a multiple of N here: the four columns exist
+        float4 t = acc[0][kind][vj][ln];
+#pragma unroll
+        for (int w = 1; w < 8; ++w) {
+          const float4 u = acc[w][kind][vj][ln];
+          t.x += u.x; t.y += u.y; t.z += u.z; t.w += u.w;
+        }
+        if (((uintptr_t)(out + col) & 15) == 0) {
+          asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(out + col), "f"(t.x), "f"(t.y), "f"(t.z), "f"(t.w)
+                       : "memory");
+        } else {
+          atomicAdd(out + col, t.x); atomicAdd(out + col + 1, t.y); atomicAdd(out + col + 2, t.z); atomicAdd(out + col + 3, t.w);
         }
       }
     }
@@ -289,7 +498,16 @@ __global__ void __launch_bounds__(256) column_sum_kernel(const T* __restrict__ g
 #pragma unroll
   for (int q = 0; q < N; ++q) acc[q] = 0.f;
   if (c < cols) {
-    for (long long r = (long long)blockIdx.y * 8 + warp; r < rows; r += (long long)gridDim.y * 8) {
+    const long long step = (long long)gridDim.y * 8;
+    long long r = (long long)blockIdx.y * 8 + warp;
+    for (; r + 3 * step < rows; r += 4 * step) {             // four independent loads in flight per lane
+      float f[4][N];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) load_vec(g + (r + u * step) * ld, c, cols, vec, f[u]);
+#pragma unroll
+      for (int q = 0; q < N; ++q) acc[q] += (f[0][q] + f[1][q]) + (f[2][q] + f[3][q]);
+    }
+    for (; r < rows; r += step) {
       float f[N];
       load_vec(g + r * ld, c, cols, vec, f);
 #pragma unroll
@@ -478,15 +696,19 @@ int ln_forward_t(int64_t rows, int64_t cols, const void* x, int64_t x_ld, const 
                  void* y, int64_t y_ld, float* stats, cudaStream_t stream) {
   DeviceState* ds = device_state();
   const int vec = vec_ok(sizeof(T), cols, {x_ld, y_ld}, {x, y, gamma, beta}) ? 1 : 0;
-  long long blocks = (rows + 7) / 8;
-  const long long cap = (long long)ds->sm_count * 16;
-  if (blocks > cap) blocks = cap;
   const int64_t vecs = (cols + 32 * Vec<T>::N - 1) / (32 * Vec<T>::N);
+  const bool fast = vec && vecs <= 2;
+  long long blocks = (rows + 7) / 8;
+  const long long cap = (long long)ds->sm_count * (fast ? LN_FWD_VEC_BLOCKS_PER_SM : 16);
+  if (blocks > cap) blocks = cap;
   auto launch = [&](auto kernel) {
     kernel<<<(unsigned)blocks, 256, 0, stream>>>((const T*)x, x_ld, (const T*)gamma, (const T*)beta, (float)eps, (T*)y, y_ld,
                                                  stats, rows, (int)cols, vec);
   };
-  if (vecs <= 2) launch(layer_norm_fwd_reg_kernel<T, 2>);
+  if (fast) {
+    layer_norm_fwd_vec_kernel<T, 2><<<(unsigned)blocks, 256, 0, stream>>>((const T*)x, x_ld, (const T*)gamma, (const T*)beta,
+                                                                            (float)eps, (T*)y, y_ld, stats, rows, (int)cols);
+  } else if (vecs <= 2) launch(layer_norm_fwd_reg_kernel<T, 2>);
   else if (vecs <= 4) launch(layer_norm_fwd_reg_kernel<T, 4>);
   else if (vecs <= 8) launch(layer_norm_fwd_reg_kernel<T, 8>);
   else launch(layer_norm_fwd_kernel<T>);                     // long rows: three passes, re-reads hit L1 / L2
@@ -500,15 +722,21 @@ int ln_backward_t(int64_t rows, int64_t cols, const void* x, int64_t x_ld, const
   DeviceState* ds = device_state();
   constexpr int N = Vec<T>::N;
   const int vec = vec_ok(sizeof(T), cols, {x_ld, g_ld, gx ? gx_ld : 0}, {x, g, gx, gamma}) ? 1 : 0;
-  long long blocks = (rows + 7) / 8;
-  const long long cap = (long long)ds->sm_count * 4;        // few blocks: each ends with `cols` atomics per output
-  if (blocks > cap) blocks = cap;
   const int64_t vecs = (cols + 32 * N - 1) / (32 * N);
+  const bool fast = vec && vecs <= 2;
+  long long blocks = (rows + 7) / 8;
+  // few blocks: each ends with `cols` atomics per output; the fast kernel runs as one resident wave
+  const long long cap = (long long)ds->sm_count * (fast ? LN_BWD_VEC_BLOCKS_PER_SM : 4);
+  if (blocks > cap) blocks = cap;
   auto launch = [&](auto kernel) {
     kernel<<<(unsigned)blocks, 256, 0, stream>>>((const T*)x, x_ld, (const T*)gamma, stats, (const T*)g, g_ld, (T*)gx, gx_ld,
                                                  accumulate_x, ggamma, gbeta, rows, (int)cols, vec);
   };
-  if (vecs <= 2) launch(layer_norm_bwd_kernel<T, 2>);
+  if (fast) {
+    layer_norm_bwd_vec_kernel<T, 2><<<(unsigned)blocks, 256, 0, stream>>>((const T*)x, x_ld, (const T*)gamma, stats, (const T*)g,
+                                                                            g_ld, (T*)gx, gx_ld, accumulate_x, ggamma, gbeta,
+                                                                            rows, (int)cols);
+  } else if (vecs <= 2) launch(layer_norm_bwd_kernel<T, 2>);
   else if (vecs <= 4) launch(layer_norm_bwd_kernel<T, 4>);
   else if (vecs <= 8) launch(layer_norm_bwd_kernel<T, 8>);
   else return B200_ERR_LIMIT;
@@ -537,10 +765,11 @@ int softmax_forward_t(int64_t rows, int64_t cols, const void* x, int64_t x_ld, d
                       cudaStream_t stream) {
   DeviceState* ds = device_state();
   const int vec = vec_ok(sizeof(T), cols, {x_ld, y_ld}, {x, y}) ? 1 : 0;
-  long long blocks = (rows + 7) / 8;
-  const long long cap = (long long)ds->sm_count * 16;
-  if (blocks > cap) blocks = cap;
   const int64_t vecs = (cols + 32 * Vec<T>::N - 1) / (32 * Vec<T>::N);
+  const bool fast = vec && vecs <= 2;
+  long long blocks = (rows + 7) / 8;
+  const long long cap = (long long)ds->sm_count * (fast ? LN_FWD_VEC_BLOCKS_PER_SM : 16);
+  if (blocks > cap) blocks = cap;
   auto launch = [&](auto kernel) {
     kernel<<<(unsigned)blocks, 256, 0, stream>>>((const T*)x, x_ld, (float)alpha, (T*)y, y_ld, rows, (int)cols, vec);
   };
@@ -557,10 +786,11 @@ int softmax_backward_t(int64_t rows, int64_t cols, const void* y, int64_t y_ld, 
                        void* gx, int64_t gx_ld, int accumulate, cudaStream_t stream) {
   DeviceState* ds = device_state();
   const int vec = vec_ok(sizeof(T), cols, {y_ld, g_ld, gx_ld}, {y, g, gx}) ? 1 : 0;
-  long long blocks = (rows + 7) / 8;
-  const long long cap = (long long)ds->sm_count * 16;
-  if (blocks > cap) blocks = cap;
   const int64_t vecs = (cols + 32 * Vec<T>::N - 1) / (32 * Vec<T>::N);
+  const bool fast = vec && vecs <= 2;
+  long long blocks = (rows + 7) / 8;
+  const long long cap = (long long)ds->sm_count * (fast ? LN_FWD_VEC_BLOCKS_PER_SM : 16);
+  if (blocks > cap) blocks = cap;
   auto launch = [&](auto kernel) {
     kernel<<<(unsigned)blocks, 256, 0, stream>>>((const T*)y, y_ld, (const T*)g, g_ld, (float)alpha, (T*)gx, gx_ld, accumulate,
                                                  rows, (int)cols, vec);
