@@ -250,12 +250,25 @@ class Cuda:
                                               self._stream()), "b200_attention_forward")
         return out, lse
 
-    def attention_backward(self, q, k, v, alpha: float, out, lse, grad_out, accumulate_into=None):
+    def attention_backward(self, q, k, v, alpha: float, out, lse, grad_out, accumulate_into=None, write_into=None):
         """Gradients of `attention_forward`.  Returns (grad_q, grad_k, grad_v) viewed through q's, k's and v's
-        strides (zeroed buffers of the storages' physical length, as `Gradients::try_alloc_for` makes them), or
-        accumulates into the three given flat buffers."""
+        strides (zeroed buffers of the storages' physical length, as `Gradients::try_alloc_for` makes them),
+        accumulates into the three given flat buffers, or writes into three given views shaped like q, k and v
+        (`write_into`; their strides may differ from q's, k's and v's)."""
         b, h, s1, d = q.shape
         s2 = k.shape[3]
+        if write_into is not None:
+            gq, gk, gv = write_into
+            if (gq.shape, gk.shape, gv.shape) != (q.shape, k.shape, v.shape):
+                raise ValueError("write_into: views shaped like q, k and v are required")
+            go = grad_out if grad_out.stride(3) == 1 else grad_out.contiguous()
+            ws = self.get_workspace(self.lib.b200_attention_backward_workspace_bytes(b, h, s1))
+            check(self.lib.b200_attention_backward(
+                self._dtype(q), b, h, s1, s2, d, q.data_ptr(), _st(q.stride()), k.data_ptr(), _st(k.stride()),
+                v.data_ptr(), _st(v.stride()), float(alpha), out.data_ptr(), _st(out.stride()), lse.data_ptr(),
+                go.data_ptr(), _st(go.stride()), gq.data_ptr(), _st(gq.stride()), gk.data_ptr(), _st(gk.stride()),
+                gv.data_ptr(), _st(gv.stride()), 0, ws.data_ptr(), ws.numel(), self._stream()), "b200_attention_backward")
+            return gq, gk, gv
         # Fresh buffers are simply written (no zero fill, no read-modify-write) when every element of q, k and v
         # owns its storage element and the views cover their storages; a broadcast view (several elements aliasing
         # one storage element) or a partial view keeps dfdx's zero-then-accumulate.

@@ -152,6 +152,39 @@ class _FusedAttention(torch.autograd.Function):
         return None, gq, gk, gv, None
 
 
+def _split_qkv(qkv: torch.Tensor, heads: int):
+    """The q (b, h, s, d), k (b, h, d, s) and v (b, h, s, d) views of a (b, s, 3 * h * d) projection output."""
+    m = qkv.shape[-1] // 3
+    d = m // heads
+    q = qkv[..., :m].unflatten(-1, (heads, d)).permute(0, 2, 1, 3)
+    k = qkv[..., m:2 * m].unflatten(-1, (heads, d)).permute(0, 2, 3, 1)
+    v = qkv[..., 2 * m:].unflatten(-1, (heads, d)).permute(0, 2, 1, 3)
+    return q, k, v
+
+
+class _FusedAttentionQKV(torch.autograd.Function):
+    """`_FusedAttention` on the output of one (model -> 3 * model) projection, i.e. w_q, w_k and w_v applied as one
+    GEMM over their adjacent weights: q, k and v are strided views of that output, and the backward kernels write
+    their three gradients into the matching views of one buffer, so that the projection's backward is one data
+    gradient GEMM, one weight gradient GEMM and one bias column sum instead of three of each plus two adds."""
+
+    @staticmethod
+    def forward(ctx, dev: Cuda, qkv, heads: int, alpha: float):
+        q, k, v = _split_qkv(qkv, heads)
+        out, lse = dev.attention_forward(q, k, v, alpha, want_lse=True)
+        ctx.dev, ctx.alpha, ctx.heads = dev, alpha, heads
+        ctx.save_for_backward(qkv, out, lse)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        qkv, out, lse = ctx.saved_tensors
+        q, k, v = _split_qkv(qkv, ctx.heads)
+        gqkv = torch.empty_like(qkv)
+        ctx.dev.attention_backward(q, k, v, ctx.alpha, out, lse, grad_out, write_into=_split_qkv(gqkv, ctx.heads))
+        return None, gqkv, None, None
+
+
 class _LayerNorm(torch.autograd.Function):
     """`LayerNorm1D` as one forward and one backward kernel (`b200_layer_norm_forward` / `_backward`); gamma and beta
     are the f16 compute copies, their gradients come back as f32 column sums."""
@@ -262,10 +295,15 @@ class MultiHeadAttention(torch.nn.Module):
         self.dev, self.heads, self.fused = dev, heads, fused
         self.w_q, self.w_k = Linear(dev, model, model, gen, fused), Linear(dev, model, model, gen, fused)
         self.w_v, self.w_o = Linear(dev, model, model, gen, fused), Linear(dev, model, model, gen, fused)
+        self.qkv_slot = None        # set by a Trainer that stores w_q, w_k, w_v (and their biases) next to each other
 
     def forward(self, x):
         b, s, m = x.shape
         h, d = self.heads, m // self.heads
+        if self.qkv_slot is not None and self.fused == "attention" and x.dtype == torch.float16 and d % 8 == 0 and d <= 128:
+            qkv = _DirectLinear.apply(self.dev, x, self.qkv_slot, False)
+            tokens = _FusedAttentionQKV.apply(self.dev, qkv, h, 1.0 / math.sqrt(d))
+            return self.w_o(tokens.permute(0, 2, 1, 3).reshape(b, s, m))
         v = self.w_v(x).reshape(b, s, h, d).permute(0, 2, 1, 3)
         k = self.w_k(x).reshape(b, s, h, d).permute(0, 2, 3, 1)
         q = self.w_q(x).reshape(b, s, h, d).permute(0, 2, 1, 3)
@@ -365,6 +403,15 @@ class Trainer:
             for blk in self.model.blocks:
                 for ln in (blk.norm1, blk.norm2):
                     ln.slot = (v16(ln.weight), v16(ln.bias), ln.weight.grad, ln.bias.grad)
+                # w_q, w_k, w_v lie next to each other in the flat buffers (so do their biases): one (3 * model, model)
+                # weight whose rows are the three projections' outputs
+                a = blk.attn
+                ws = [spans[id(l.weight)] for l in (a.w_q, a.w_k, a.w_v)]
+                bs = [spans[id(l.bias)] for l in (a.w_q, a.w_k, a.w_v)]
+                if all(ws[i][1] == ws[i + 1][0] and bs[i][1] == bs[i + 1][0] for i in range(2)):
+                    o3, i_ = 3 * a.w_q.weight.shape[0], a.w_q.weight.shape[1]
+                    a.qkv_slot = (self.flat16[ws[0][0]:ws[2][1]].view(o3, i_), self.flat16[bs[0][0]:bs[2][1]],
+                                  self.flat_gw16[ws[0][0]:ws[2][1]].view(o3, i_), self.flat_grad[bs[0][0]:bs[2][1]])
             self.model.attach = True
         self.opt = torch.optim.Adam(params, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, fused=True, capturable=True)
         self.graph = None

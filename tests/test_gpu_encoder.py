@@ -68,8 +68,10 @@ def test_trainer_graph_replay_matches_eager(cuda_dev):
 
 def test_trainer_direct_gradients_match_autograd_route(cuda_dev):
     """Gradients written straight into the trainer's flat buffers equal the ones torch's autograd collects
-    (cast, add per parameter) for the same step; bias / LayerNorm gradients differ only by the f16 rounding the
-    autograd route puts on the f32 column sums."""
+    (cast, add per parameter) for the same step; bias / LayerNorm gradients differ by the f16 rounding the
+    autograd route puts on the f32 column sums, and everything upstream of an attention block by the rounding of
+    the two f16 adds with which autograd sums the q, k and v projections' data gradients (the direct route's single
+    (model -> 3 * model) projection sums them in f32 inside one GEMM)."""
     from dfdx_b200.encoder import Trainer
     gen = torch.Generator().manual_seed(5)
     x = torch.randn(4, 32, 64, generator=gen).half().to(cuda_dev.device)
@@ -84,6 +86,28 @@ def test_trainer_direct_gradients_match_autograd_route(cuda_dev):
                                  [(n, 0) for n in range(10 ** 6)]):
         ref = pb.grad.float()
         err = (pa.grad.float() - ref).norm() / max(float(ref.norm()), 1e-2 * float(b.flat_grad.norm()))
-        assert err <= 2e-3, f"parameter {name}: {float(err):.3e}"
+        assert err <= 5e-3, f"parameter {name}: {float(err):.3e}"
     # the step trained both the same way
     assert (a.flat_param - b.flat_param).abs().max() <= 2.1e-3    # one Adam step moves a weight by at most lr
+
+
+def test_fused_qkv_attention_matches_separate_projections(cuda_dev):
+    """Attention on the strided q, k, v views of one (b, s, 3 * model) projection output, with the three gradients
+    written into the views of one buffer, equals attention on three separate tensors: same kernels, other strides."""
+    from dfdx_b200 import encoder as enc
+    dev = cuda_dev
+    b, s, h, d = 2, 64, 4, 16
+    m = h * d
+    gen = torch.Generator().manual_seed(11)
+    qkv = torch.randn(b, s, 3 * m, generator=gen).half().to(dev.device).requires_grad_()
+    go = torch.randn(b, h, s, d, generator=gen).half().to(dev.device)
+    alpha = 1.0 / d ** 0.5
+    out = enc._FusedAttentionQKV.apply(dev, qkv, h, alpha)
+    out.backward(go)
+    parts = [qkv.detach()[..., i * m:(i + 1) * m].reshape(b, s, h, d).clone().requires_grad_() for i in range(3)]
+    q, k, v = parts[0].permute(0, 2, 1, 3), parts[1].permute(0, 2, 3, 1), parts[2].permute(0, 2, 1, 3)
+    ref = enc._FusedAttention.apply(dev, q, k, v, alpha)
+    ref.backward(go)
+    assert torch.equal(out, ref)
+    for i, p in enumerate(parts):
+        assert torch.equal(qkv.grad[..., i * m:(i + 1) * m].reshape(b, s, h, d), p.grad), "qkv"[i]
