@@ -66,6 +66,7 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
   __shared__ __align__(8) uint64_t bar_tempty[2];
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
+  __shared__ __align__(16) float bias_s[2][128];     // per epilogue group: the column bias of its part of the tile
 
   const uint32_t smem_base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -187,6 +188,15 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
         for (int pc = 0; pc < AHEAD; ++pc)
           if (t.nt * BN + (2 * pc + eg) * 32 + 32 <= g.n) load_old_f16(orow + (2 * pc + eg) * 32, oldv[pc], g.c_wide);
       }
+      // column bias of this group's 64-column pieces (2 i + eg), as f32, fetched before the accumulator is waited for;
+      // the group's barriers below order these writes before the reads and the reads before the next tile's writes
+      const bool bias_cols = g.fused && g.c_tma && !g.bias_row;
+      if (bias_cols) {
+        const int j = threadIdx.x & 127, c2j = (j >> 6) * 2 + eg, colj = t.nt * BN + c2j * 64 + (j & 63);
+        float bv = 0.f;
+        if (g.bias != nullptr && c2j < BN / 64 && colj < g.n) bv = __half2float(__ldg(reinterpret_cast<const __half*>(g.bias) + colj));
+        bias_s[eg][j] = bv;
+      }
       bool got = mbar_wait(smem_u32(&bar_tfull[buf]), tph, abortp, g.wait_limit);
       // the staged epilogue below synchronises the four epilogue warps with named barriers, which have no
       // time-out: all of them take this tile or none does
@@ -215,7 +225,9 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
               float f[32];
 #pragma unroll
               for (int q = 0; q < 32; ++q) f[q] = __uint_as_float(v[q]);
-              if (g.fused && row < g.m) {
+              if (bias_cols) {
+                fused_epilogue_cols(f, g, &bias_s[eg][(c2 >> 1) * 64 + h * 32]);
+              } else if (g.fused && row < g.m) {
                 const int valid = (g.n - col0 - h * 32) < 32 ? (g.n - col0 - h * 32) : 32;
                 if (valid > 0) fused_epilogue<__half>(f, g, row, col0 + h * 32, valid);
               }
@@ -290,7 +302,8 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant
 // ---------------------------------------------------------------------------------------------
 // f16 kernel with a 256 x 256 tile per CTA (CfgHB): same roles as gemm_f16_kernel; each k-step issues two MMAs (rows
 // 0..127 and 128..255 of the A tile against the same B tile) into two accumulators; epilogue warp group eg drains
-// accumulator eg.  Row-major outputs through the staged TMA store / reduce-add only, whole-K tiles only.
+// accumulator eg.  Row-major outputs through the staged TMA store / reduce-add; K slices (ksplit > 1) add their f32
+// partial sums into the device's scratch matrix the same way.
 // ---------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(CfgHB::THREADS, 1)
 gemm_f16_big_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
@@ -306,6 +319,8 @@ gemm_f16_big_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
   __shared__ __align__(8) uint64_t bar_tempty;
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
+  __shared__ __align__(16) __half bias_s[2][256];    // per epilogue group: the tile's column bias (f16: 3 stages and the
+                                                     // staging buffers leave 2 KB of static shared memory)
 
   const uint32_t smem_base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -340,11 +355,12 @@ gemm_f16_big_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
       uint32_t ring_s = 0, ring_ph = 0;
       bool ok = true;
       for (long long unit = blockIdx.x; ok && unit < g.total_units; unit += gridDim.x) {
-        const TileCoord t = decode_tile(g, unit);
-        int r = 0, kx = 0;
+        const Unit un = decode_unit(g, unit, total_kb);
+        const TileCoord t = decode_tile(g, un.tile);
+        int r = un.kb_lo / g.k_blocks, kx = (un.kb_lo - r * g.k_blocks) * C::BK;
         const int k_end = g.k_blocks * C::BK;
         const int ax = g.a_x1 * t.ib1, ay = g.a_y0 * t.ib0, bx = g.b_x1 * t.ib1, by = g.b_y0 * t.ib0;
-        for (int i = 0; i < total_kb; ++i) {
+        for (int i = un.kb_lo; i < un.kb_hi; ++i) {
           const uint32_t s = ring_s, ph = ring_ph;
           if (++ring_s == (uint32_t)STAGES) { ring_s = 0; ring_ph ^= 1u; }
           if (!mbar_wait(smem_u32(&bar_empty[s]), ph ^ 1u, abortp, g.wait_limit)) { ok = false; break; }
@@ -375,10 +391,11 @@ gemm_f16_big_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
       uint32_t ring_s = 0, ring_ph = 0, tcount = 0;
       bool ok = true;
       for (long long unit = blockIdx.x; ok && unit < g.total_units; unit += gridDim.x, ++tcount) {
+        const Unit un = decode_unit(g, unit, total_kb);
         // both accumulators are free once the epilogue has read the previous tile out of them
         if (!mbar_wait(smem_u32(&bar_tempty), (tcount & 1u) ^ 1u, abortp, g.wait_limit)) { ok = false; break; }
         tc_fence_after();
-        for (int i = 0; i < total_kb; ++i) {
+        for (int i = un.kb_lo; i < un.kb_hi; ++i) {
           const uint32_t s = ring_s, ph = ring_ph;
           if (++ring_s == (uint32_t)STAGES) { ring_s = 0; ring_ph ^= 1u; }
           if (!mbar_wait(smem_u32(&bar_full[s]), ph, abortp, g.wait_limit)) { ok = false; break; }
@@ -386,7 +403,7 @@ gemm_f16_big_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
           const uint32_t a_lo = a_lo0 + (uint32_t)s * STAGE16, b_lo = b_lo0 + (uint32_t)s * STAGE16;
 #pragma unroll
           for (int ks = 0; ks < C::KSTEPS; ++ks) {
-            const uint32_t acc = (i > 0 || ks > 0) ? 1u : 0u;
+            const uint32_t acc = (i > un.kb_lo || ks > 0) ? 1u : 0u;
             umma_lohi<2>(tmem_base, a_lo + ks * a_k16, a_hi, b_lo + ks * b_k16, b_hi, idesc, acc);
             umma_lohi<2>(tmem_base + BN, a_lo + HALF16 + ks * a_k16, a_hi, b_lo + ks * b_k16, b_hi, idesc, acc);
           }
@@ -404,9 +421,21 @@ gemm_f16_big_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
     uint32_t tcount = 0;
     bool ok = true;
     for (long long unit = blockIdx.x; ok && unit < g.total_units; unit += gridDim.x, ++tcount) {
-      const TileCoord t = decode_tile(g, unit);
+      const TileCoord t = decode_tile(g, decode_unit(g, unit, total_kb).tile);
       const int row0 = t.mt * C::BMB + eg * BM;              // first output row of this group's accumulator
       const int row = row0 + ew * 32 + lane;
+      // the tile's column bias, fetched before the accumulators are waited for; the group's barriers below order
+      // these writes before the reads and the reads before the next tile's writes
+      const bool bias_cols = g.fused && !g.bias_row && g.ksplit == 1;
+      if (bias_cols) {
+#pragma unroll
+        for (int jj = 0; jj < 2; ++jj) {
+          const int j = (threadIdx.x & 127) + jj * 128, colj = t.nt * BN + j;
+          __half bv = __float2half_rn(0.f);
+          if (g.bias != nullptr && colj < g.n) bv = __ldg(reinterpret_cast<const __half*>(g.bias) + colj);
+          bias_s[eg][j] = bv;
+        }
+      }
       bool got = mbar_wait(smem_u32(&bar_tfull), tcount & 1u, abortp, g.wait_limit);
       got = named_barrier_and(bar_id, 128, got);             // the staged stores use named barriers: all or none
       if (!got) { ok = false; break; }
@@ -415,7 +444,31 @@ gemm_f16_big_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
       const int r_in = ew * 32 + lane;
       const uint32_t sw = (uint32_t)(r_in & 7);
       const uint32_t stage = smem_base + C::OFF_OUT + (uint32_t)eg * C::OUT_BYTES;
-      if (row0 < g.m) {                                      // group-uniform
+      if (g.ksplit > 1 && row0 < g.m) {
+        // K slice: the f32 partial sums are added into the device's scratch matrix (tma_c maps it here), 32 columns
+        // = one 128-byte line per row at a time through the same staging buffer
+#pragma unroll 1
+        for (int c4 = 0; c4 < BN / 32; ++c4) {
+          const int col0 = t.nt * BN + c4 * 32;
+          if (col0 < g.n) {
+            if (leader) bulk_wait_group_read<0>();
+            named_barrier_sync(bar_id, 128);
+            uint32_t v[32];
+            tmem_ld_32x32(taddr + c4 * 32, v);
+            tmem_wait_ld();
+#pragma unroll
+            for (int q4 = 0; q4 < 8; ++q4)
+              st_shared_v4_u32(stage + (uint32_t)r_in * 128u + ((((uint32_t)q4) ^ sw) << 4), v[q4 * 4], v[q4 * 4 + 1],
+                               v[q4 * 4 + 2], v[q4 * 4 + 3]);
+            fence_proxy_async_smem();
+            named_barrier_sync(bar_id, 128);
+            if (leader) {
+              tma_reduce_add_4d(&tma_c, stage, col0, row0, 0, 0);
+              bulk_commit_group();
+            }
+          }
+        }
+      } else if (row0 < g.m) {                               // group-uniform
 #pragma unroll
         for (int c2 = 0; c2 < BN / 64; ++c2) {
           const int col0 = t.nt * BN + c2 * 64;
@@ -430,7 +483,9 @@ gemm_f16_big_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
               float f[32];
 #pragma unroll
               for (int q = 0; q < 32; ++q) f[q] = __uint_as_float(v[q]);
-              if (g.fused && row < g.m) {
+              if (bias_cols) {
+                fused_epilogue_cols(f, g, &bias_s[eg][c2 * 64 + h * 32]);
+              } else if (g.fused && row < g.m) {
                 const int valid = (g.n - col0 - h * 32) < 32 ? (g.n - col0 - h * 32) : 32;
                 if (valid > 0) fused_epilogue<__half>(f, g, row, col0 + h * 32, valid);
               }
@@ -1208,6 +1263,47 @@ int plan_tail_split(TcArgs& g, int sms, int total_kb, cudaStream_t stream) {
   return B200_OK;
 }
 
+// f16 split-K: `launch_main(scratch, lds)` launches a kernel whose K slices add f32 partial sums into the device's
+// zeroed scratch matrix (m rows of lds floats); a second kernel then folds the scratch into C.  *done stays false
+// (and nothing is enqueued) when the scratch cannot be used: too small, or the stream is capturing -- the one scratch
+// per device is ordered across streams by an event that is recorded eagerly, and a replayed graph would neither wait
+// on it nor record it.  A caller that orders every replay of its graphs against all other work of the library on
+// the device (one stream, say) may ask for split-K inside captures (b200_set_capture_split_k); the event is then left
+// alone.
+template <typename Fn>
+int run_f16_split(const Plan& pl, cudaStream_t stream, bool* done, Fn launch_main) {
+  const GemmProblem& p = pl.p;   // single batch item (checked by the caller)
+  DeviceState* ds = device_state();
+  *done = false;
+  const long long lds = (p.n + 3) / 4 * 4;
+  const size_t need = (size_t)p.m * (size_t)lds * sizeof(float);
+  cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(stream, &cap) != cudaSuccess) cap = cudaStreamCaptureStatusActive;
+  const bool capturing = cap != cudaStreamCaptureStatusNone;
+  if (need > ds->split_scratch_bytes || (capturing && !g_capture_split.load())) return B200_OK;
+  std::lock_guard<std::mutex> lock(g_split_mutex);
+  int rc;
+  // Order this use after the previous one when that ran on another stream.
+  if (!capturing && ds->split_used && ds->split_last_stream != stream &&
+      (rc = note_cuda_error(cudaStreamWaitEvent(stream, ds->split_event, 0), "cudaStreamWaitEvent(split-K)")))
+    return rc;
+  if ((rc = note_cuda_error(cudaMemsetAsync(ds->split_scratch, 0, need, stream), "cudaMemsetAsync(split-K)"))) return rc;
+  *done = true;
+  if ((rc = launch_main(ds->split_scratch, lds))) return rc;
+  const long long total = (long long)p.m * p.n;
+  long long blocks = (total + 255) / 256;
+  if (blocks > (long long)ds->sm_count * 8) blocks = (long long)ds->sm_count * 8;
+  const long long c_r = pl.c_col ? 1 : pl.ldc, c_c = pl.c_col ? pl.ldc : 1;
+  splitk_finalize_f16_kernel<<<(unsigned)blocks, 256, 0, stream>>>(ds->split_scratch, lds, (__half*)p.c, c_r, c_c,
+                                                                   (int)p.m, (int)p.n, p.beta);
+  count_launch(false);
+  if ((rc = note_cuda_error(cudaGetLastError(), "split-K finalize launch"))) return rc;
+  if (capturing) return B200_OK;
+  ds->split_used = true;
+  ds->split_last_stream = stream;
+  return note_cuda_error(cudaEventRecord(ds->split_event, stream), "cudaEventRecord(split-K)");
+}
+
 // C: CfgH<BN> or CfgS<BN>; KERNEL: the matching kernel.  ksplit > 1 (f32 kernel only): K is cut into that many
 // slices, each (tile, slice) is a work unit and the slices' partial results are added into C atomically; for
 // beta = 0 the output is zeroed first.
@@ -1250,44 +1346,17 @@ int launch_cfg(const Plan& pl, cudaStream_t stream, Kernel kernel, int ksplit) {
         if (rc) return rc;
       }
     } else if (ESIZE == 2 && slices > 1) {
-      // f16: partial sums are accumulated in the device's f32 scratch, then folded into C by a second kernel
-      const long long lds = (p.n + 3) / 4 * 4;
-      const size_t need = (size_t)p.m * (size_t)lds * sizeof(float);
-      // A GEMM enqueued on a capturing stream runs unsplit: the one scratch per device is ordered across streams
-      // by an event that is recorded eagerly, and a replayed graph would neither wait on it nor record it.  A
-      // caller that orders every replay of its graphs against all other work of the library on the device (one
-      // stream, say) may ask for split-K inside captures (b200_set_capture_split_k); the event is then left alone.
-      cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
-      if (cudaStreamIsCapturing(stream, &cap) != cudaSuccess) cap = cudaStreamCaptureStatusActive;
-      const bool capturing = cap != cudaStreamCaptureStatusNone;
-      if (need <= ds->split_scratch_bytes && (!capturing || g_capture_split.load())) {
-        std::lock_guard<std::mutex> lock(g_split_mutex);
-        int rc;
-        // Order this use after the previous one when that ran on another stream.
-        if (!capturing && ds->split_used && ds->split_last_stream != stream &&
-            (rc = note_cuda_error(cudaStreamWaitEvent(stream, ds->split_event, 0), "cudaStreamWaitEvent(split-K)")))
-          return rc;
-        if ((rc = note_cuda_error(cudaMemsetAsync(ds->split_scratch, 0, need, stream), "cudaMemsetAsync(split-K)"))) return rc;
+      bool done = false;
+      const int rc = run_f16_split(pl, stream, &done, [&](float* scratch, long long lds) {
         g.kb_per_slice = kb_per; g.ksplit = slices; g.total_units = g.total_tiles * slices;
-        g.split_out = ds->split_scratch; g.split_ld = lds;
+        g.split_out = scratch; g.split_ld = lds;
         const long long grid2 = g.total_units < grid_sms(ds) ? g.total_units : grid_sms(ds);
         L.g.c_tma = 0;                                       // partial sums go to the scratch, not to C
         kernel<<<(unsigned)grid2, C::THREADS, C::SMEM_BYTES, stream>>>(L.ma, L.mb, L.mc, L.g);
         count_launch(true);
-        if ((rc = note_cuda_error(cudaGetLastError(), "tensor-core gemm launch"))) return rc;
-        const long long total = (long long)p.m * p.n;
-        long long blocks = (total + 255) / 256;
-        if (blocks > (long long)ds->sm_count * 8) blocks = (long long)ds->sm_count * 8;
-        const long long c_r = pl.c_col ? 1 : pl.ldc, c_c = pl.c_col ? pl.ldc : 1;
-        splitk_finalize_f16_kernel<<<(unsigned)blocks, 256, 0, stream>>>(ds->split_scratch, lds, (__half*)p.c, c_r, c_c,
-                                                                         (int)p.m, (int)p.n, g.beta);
-        count_launch(false);
-        if ((rc = note_cuda_error(cudaGetLastError(), "split-K finalize launch"))) return rc;
-        if (capturing) return B200_OK;
-        ds->split_used = true;
-        ds->split_last_stream = stream;
-        return note_cuda_error(cudaEventRecord(ds->split_event, stream), "cudaEventRecord(split-K)");
-      }
+        return note_cuda_error(cudaGetLastError(), "tensor-core gemm launch");
+      });
+      if (rc || done) return rc;
     }
   }
   if constexpr (ESIZE == 4) {
@@ -1310,16 +1379,42 @@ int launch_pair_plan(const Plan& pl, int esize, cudaStream_t stream) {
   return launch_pair(esize, L.ma, L.mb, L.g, grid_sms(device_state()), stream);
 }
 
-// f16, 256 x 256 tiles (gemm_f16_big_kernel).  Returns B200_ERR_UNSUPPORTED when the output cannot leave through
-// the staged TMA store (the only epilogue that kernel has).
-int launch_big_f16(const Plan& pl, cudaStream_t stream) {
+// f16, 256 x 256 tiles (gemm_f16_big_kernel).  ksplit == 1: whole-K tiles; returns B200_ERR_UNSUPPORTED when the
+// output cannot leave through the staged TMA store (the only direct epilogue that kernel has).  ksplit > 1 (one batch
+// item, no fused epilogue): K slices through the f32 scratch (run_f16_split), any output layout; returns
+// B200_ERR_UNSUPPORTED when the scratch cannot be used.
+int encode_map_f32(CUtensorMap* map, const void* base, const uint64_t dims[4], const uint64_t strides_b[3],
+                   const uint32_t box[4], CUtensorMapSwizzle sw);
+int launch_big_f16(const Plan& pl, cudaStream_t stream, int ksplit) {
   Launch L;
   const int st = build_launch(L, pl, 2, CfgHB::BMB, CfgHB::BN, CfgHB::BMB, CfgHB::BN, CfgHB::BK, CfgHB::CH);
   if (st) return st;
-  if (!L.g.c_tma) return B200_ERR_UNSUPPORTED;
   DeviceState* ds = device_state();
-  L.g.kb_per_slice = L.g.red * L.g.k_blocks;
-  const long long grid = L.g.total_units < grid_sms(ds) ? L.g.total_units : grid_sms(ds);
+  TcArgs& g = L.g;
+  const int total_kb = g.red * g.k_blocks;
+  g.kb_per_slice = total_kb;
+  if (ksplit > 1 && total_kb >= 2 * ksplit) {
+    const int kb_per = (total_kb + ksplit - 1) / ksplit, slices = (total_kb + kb_per - 1) / kb_per;
+    bool done = false;
+    const int rc = run_f16_split(pl, stream, &done, [&](float* scratch, long long lds) {
+      // the scratch as a (columns, rows) f32 tensor: boxes of 32 columns (one swizzled 128-byte line) x 128 rows
+      const uint64_t dims[4] = {(uint64_t)lds, (uint64_t)pl.p.m, 1, 1};
+      const uint64_t strides[3] = {(uint64_t)lds * 4, (uint64_t)lds * 4 * (uint64_t)pl.p.m, (uint64_t)lds * 4 * (uint64_t)pl.p.m};
+      const uint32_t box[4] = {32, (uint32_t)BM, 1, 1};
+      const int er = encode_map_f32(&L.mc, scratch, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+      if (er) return er;
+      g.kb_per_slice = kb_per; g.ksplit = slices; g.total_units = g.total_tiles * slices;
+      g.split_out = scratch; g.split_ld = lds;
+      const long long grid2 = g.total_units < grid_sms(ds) ? g.total_units : grid_sms(ds);
+      gemm_f16_big_kernel<<<(unsigned)grid2, CfgHB::THREADS, CfgHB::SMEM_BYTES, stream>>>(L.ma, L.mb, L.mc, L.g);
+      count_launch(true);
+      return note_cuda_error(cudaGetLastError(), "tensor-core gemm launch (256 x 256 tiles, K slices)");
+    });
+    if (rc) return rc;
+    return done ? B200_OK : B200_ERR_UNSUPPORTED;
+  }
+  if (!g.c_tma) return B200_ERR_UNSUPPORTED;
+  const long long grid = g.total_units < grid_sms(ds) ? g.total_units : grid_sms(ds);
   if (grid <= 0) return B200_OK;
   gemm_f16_big_kernel<<<(unsigned)grid, CfgHB::THREADS, CfgHB::SMEM_BYTES, stream>>>(L.ma, L.mb, L.mc, L.g);
   count_launch(true);
@@ -1371,8 +1466,9 @@ int launch_es(const Plan& pl, cudaStream_t stream) {
       const double c_small = (double)((t_small + sms - 1) / sms) * ((double)kb * 0.55 + 1.0);
       const double c_big = (double)((t_big + sms - 1) / sms) * ((double)kb * 0.83 + 3.7);
       // below about two thirds of a wave of big tiles the K split of the small-tile kernel is the better tool
-      if (g_force_bn == 512 || (bn == 256 && 3 * t_big >= 2 * sms && c_big < 0.9 * c_small)) {
-        const int rc = launch_big_f16(pl, stream);
+      const bool forced_slices = g_force_bn == 512 && g_split_mode >= 2;   // testing: K slices of big tiles, below
+      if (!forced_slices && (g_force_bn == 512 || (bn == 256 && 3 * t_big >= 2 * sms && c_big < 0.9 * c_small))) {
+        const int rc = launch_big_f16(pl, stream, 1);
         if (rc != B200_ERR_UNSUPPORTED) return rc;
       }
     }
@@ -1407,6 +1503,29 @@ int launch_es(const Plan& pl, cudaStream_t stream) {
         if (total_kb / s_ < (ESIZE == 4 ? 16 : 8)) break;    // keep slices long enough to amortise their fixed cost
         const double t = model(bn_, s_);
         if (t < 0.85 * best_t) { best_t = t; bn = bn_; ksplit = s_; }
+      }
+    }
+    // f16: K slices of 256 x 256 tiles.  Per 64-wide k-block 0.6 us in a long main loop; per unit about 10 us beside it
+    // (pipeline fill and the 256 KB of f32 partial sums that leave through bulk reduce-adds, which nothing overlaps).
+    if constexpr (ESIZE == 2) {
+      const bool forced_slices = g_force_bn == 512 && g_split_mode >= 2;
+      if (forced_slices) {
+        const int rc = launch_big_f16(pl, stream, g_split_mode);
+        if (rc != B200_ERR_UNSUPPORTED) return rc;
+      } else if (g_force_bn == 0 && g_split_mode <= 0 && p.m > BM && p.n > 128 && b200::g_store_mode.load() != 1) {
+        const int64_t t_big = ((p.m + 255) / 256) * ((p.n + 255) / 256);
+        int s_best = 0;
+        double t_best = 0.85 * best_t;
+        for (int s_ = 2; s_ <= 64; ++s_) {
+          if (total_kb / s_ < 8) break;
+          const double waves = (double)((t_big * s_ + sms - 1) / sms);
+          const double t = waves * ((double)((total_kb + s_ - 1) / s_) * 0.6 + 10.0);
+          if (t < t_best) { t_best = t; s_best = s_; }
+        }
+        if (s_best) {
+          const int rc = launch_big_f16(pl, stream, s_best);
+          if (rc != B200_ERR_UNSUPPORTED) return rc;
+        }
       }
     }
     if (g_split_mode >= 2) ksplit = g_split_mode;           // testing: force this many slices

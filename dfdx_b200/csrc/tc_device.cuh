@@ -390,6 +390,46 @@ __device__ __forceinline__ void fused_epilogue(float* f, const TcArgs& g, int ro
   }
 }
 
+// The same with a column bias that waits in shared memory as f32 (`bs`: this chunk's 32 values, zeros where there is
+// no bias or no column): broadcast 16-byte reads instead of global loads in the accumulator's way.
+__device__ __forceinline__ void fused_epilogue_cols(float* f, const TcArgs& g, const float* bs) {
+  const float alpha = g.alpha;
+  const float4* b4 = reinterpret_cast<const float4*>(bs);
+#pragma unroll
+  for (int v = 0; v < 8; ++v) {
+    const float4 b = b4[v];
+    f[4 * v] = fmaf(f[4 * v], alpha, b.x);
+    f[4 * v + 1] = fmaf(f[4 * v + 1], alpha, b.y);
+    f[4 * v + 2] = fmaf(f[4 * v + 2], alpha, b.z);
+    f[4 * v + 3] = fmaf(f[4 * v + 3], alpha, b.w);
+  }
+  if (g.act == B200_ACT_RELU) {
+#pragma unroll
+    for (int q = 0; q < 32; ++q) f[q] = fmaxf(f[q], 0.f);
+  }
+}
+
+// The same with the bias kept as f16 in shared memory (where the f32 copy does not fit).
+__device__ __forceinline__ void fused_epilogue_cols(float* f, const TcArgs& g, const __half* bs) {
+  const float alpha = g.alpha;
+  const uint4* b4 = reinterpret_cast<const uint4*>(bs);
+#pragma unroll
+  for (int v = 0; v < 4; ++v) {
+    const uint4 raw = b4[v];
+    const __half2* h2 = reinterpret_cast<const __half2*>(&raw);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 b = __half22float2(h2[e]);
+      f[8 * v + 2 * e] = fmaf(f[8 * v + 2 * e], alpha, b.x);
+      f[8 * v + 2 * e + 1] = fmaf(f[8 * v + 2 * e + 1], alpha, b.y);
+    }
+  }
+  if (g.act == B200_ACT_RELU) {
+#pragma unroll
+    for (int q = 0; q < 32; ++q) f[q] = fmaxf(f[q], 0.f);
+  }
+}
+
 // 256-bit global accesses (sm_100): one 32-byte sector per thread and instruction.
 __device__ __forceinline__ void ld_global_v8(const void* p, uint32_t (&r)[8]) {
   asm volatile("ld.global.v8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"

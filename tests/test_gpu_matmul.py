@@ -156,6 +156,29 @@ def test_f16_256x256_tile_kernel(cuda_dev, oracle, layout):
         dev.set_path(dfdx_b200.PATH_AUTO)
 
 
+@pytest.mark.parametrize("slices", [2, 5])
+@pytest.mark.parametrize("layout", ["".join(p) for p in itertools.product("rc", repeat=3)])
+def test_f16_256x256_tile_kernel_k_slices(cuda_dev, oracle, layout, slices):
+    """K slices of 256 x 256 tiles (forced): every unit adds its f32 partial tile into the library's scratch through
+    bulk reduce-adds and the finalize kernel folds the scratch into the f16 output; every layout (the scratch keeps
+    the kernel's orientation whichever way C lies), ragged M, N and K, beta 0 (NaN-poisoned output) and beta 1."""
+    dev = cuda_dev
+    dev.set_path(dfdx_b200.PATH_TENSOR)
+    assert dev.lib.b200_set_tile_n(512) == 0
+    assert dev.lib.b200_set_split_k(slices) == 0
+    try:
+        before, before_all = dev.lib.b200_tensor_launch_count(), dev.lib.b200_launch_count()
+        shapes = [(512, 1032, 520), (296, 2056, 264), (264, 4104, 392)]
+        for i, (m, k, n) in enumerate(shapes):
+            check_gemm(dev, oracle, m, k, n, layout[0], layout[1], layout[2], i % 2, torch.float16, pad=8, seed=950 + i)
+        assert dev.lib.b200_tensor_launch_count() - before == len(shapes)
+        assert dev.lib.b200_launch_count() - before_all == 2 * len(shapes)      # GEMM + finalize
+    finally:
+        dev.lib.b200_set_split_k(0)
+        dev.lib.b200_set_tile_n(0)
+        dev.set_path(dfdx_b200.PATH_AUTO)
+
+
 @pytest.mark.parametrize("dtype", [torch.float16, torch.float32])
 @pytest.mark.parametrize("layout", ["".join(p) for p in itertools.product("rc", repeat=3)])
 def test_cta_pair_kernels(cuda_dev, oracle, dtype, layout):
