@@ -83,6 +83,9 @@ SIGNATURES = {
     "b200_attention_forward": (_i, [_i, _sz, _sz, _sz, _sz, _sz, _vp, _szp, _vp, _szp, _vp, _szp, _d, _vp, _szp, _vp, _vp]),
     "b200_layer_norm_forward": (_i, [_i, _sz, _sz, _vp, _sz, _vp, _vp, _d, _vp, _sz, _vp, _vp]),
     "b200_layer_norm_backward": (_i, [_i, _sz, _sz, _vp, _sz, _vp, _vp, _vp, _sz, _vp, _sz, _i, _vp, _vp, _vp]),
+    "b200_layer_norm_backward_sum": (_i, [_i, _sz, _sz, _vp, _sz, _vp, _vp, _vp, _sz, _vp, _sz, _vp, _vp, _vp, _vp]),
+    "b200_add_layer_norm_forward": (_i, [_i, _sz, _sz, _vp, _sz, _vp, _sz, _vp, _sz, _vp, _vp, C.c_double, _vp, _sz, _vp, _vp]),
+    "b200_relu_backward_bias_grad": (_i, [_i, _sz, _sz, _vp, _sz, _vp, _sz, _vp, _vp]),
     "b200_bias_grad": (_i, [_i, _sz, _sz, _vp, _sz, _vp, _vp]),
     "b200_softmax_forward": (_i, [_i, _sz, _sz, _vp, _sz, _d, _vp, _sz, _vp]),
     "b200_softmax_backward": (_i, [_i, _sz, _sz, _vp, _sz, _vp, _sz, _d, _vp, _sz, _i, _vp]),

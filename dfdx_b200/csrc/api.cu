@@ -135,6 +135,7 @@ int b200_init(int ordinal) {
   if ((rc = tc_setup_device())) return rc;
   if ((rc = attention_setup_device())) return rc;
   if ((rc = attention_bwd_setup_device())) return rc;
+  if ((rc = rowwise_setup_device())) return rc;
   if ((rc = conv_noalloc_setup_device())) return rc;
   d.ready = true;
   return B200_OK;
@@ -483,7 +484,36 @@ int b200_layer_norm_backward(int dtype, size_t rows, size_t cols, const void* x,
   if (rows && cols && (!x || !grad_out || !stats)) return B200_ERR_NULL;
   if (rows > 1 && (x_ld < cols || grad_out_ld < cols || (grad_x && grad_x_ld < cols))) return B200_ERR_STRIDE;
   return layer_norm_backward(dtype, (int64_t)rows, (int64_t)cols, x, (int64_t)x_ld, gamma, stats, grad_out, (int64_t)grad_out_ld,
-                             grad_x, (int64_t)grad_x_ld, accumulate_x, grad_gamma, grad_beta, (cudaStream_t)stream);
+                             grad_x, (int64_t)grad_x_ld, accumulate_x, grad_gamma, grad_beta, nullptr, (cudaStream_t)stream);
+}
+
+int b200_layer_norm_backward_sum(int dtype, size_t rows, size_t cols, const void* x, size_t x_ld, const void* gamma,
+                                 const float* stats, const void* grad_out, size_t grad_out_ld, void* grad_x, size_t grad_x_ld,
+                                 float* grad_gamma, float* grad_beta, float* grad_x_sum, void* stream) {
+  if (!valid_dtype(dtype)) return B200_ERR_DTYPE;
+  if (rows && cols && (!x || !grad_out || !stats || !grad_x || !grad_x_sum)) return B200_ERR_NULL;
+  if (rows > 1 && (x_ld < cols || grad_out_ld < cols || grad_x_ld < cols)) return B200_ERR_STRIDE;
+  return layer_norm_backward(dtype, (int64_t)rows, (int64_t)cols, x, (int64_t)x_ld, gamma, stats, grad_out, (int64_t)grad_out_ld,
+                             grad_x, (int64_t)grad_x_ld, 0, grad_gamma, grad_beta, grad_x_sum, (cudaStream_t)stream);
+}
+
+int b200_add_layer_norm_forward(int dtype, size_t rows, size_t cols, const void* a, size_t a_ld, const void* b, size_t b_ld,
+                                void* sum, size_t sum_ld, const void* gamma, const void* beta, double epsilon, void* y,
+                                size_t y_ld, float* stats, void* stream) {
+  if (!valid_dtype(dtype)) return B200_ERR_DTYPE;
+  if (rows && cols && (!a || !b || !sum || !y)) return B200_ERR_NULL;
+  if (rows > 1 && (a_ld < cols || b_ld < cols || sum_ld < cols || y_ld < cols)) return B200_ERR_STRIDE;
+  return add_layer_norm_forward(dtype, (int64_t)rows, (int64_t)cols, a, (int64_t)a_ld, b, (int64_t)b_ld, sum, (int64_t)sum_ld,
+                                gamma, beta, epsilon, y, (int64_t)y_ld, stats, (cudaStream_t)stream);
+}
+
+int b200_relu_backward_bias_grad(int dtype, size_t rows, size_t cols, const void* y, size_t y_ld, void* grad, size_t grad_ld,
+                                 float* grad_bias, void* stream) {
+  if (!valid_dtype(dtype)) return B200_ERR_DTYPE;
+  if (rows && cols && (!y || !grad)) return B200_ERR_NULL;
+  if (rows > 1 && (y_ld < cols || grad_ld < cols)) return B200_ERR_STRIDE;
+  return relu_backward_column_sum(dtype, (int64_t)rows, (int64_t)cols, y, (int64_t)y_ld, grad, (int64_t)grad_ld, grad_bias,
+                                  (cudaStream_t)stream);
 }
 
 int b200_bias_grad(int dtype, size_t rows, size_t cols, const void* grad_out, size_t grad_out_ld, float* grad_bias, void* stream) {

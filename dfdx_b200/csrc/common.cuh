@@ -89,7 +89,13 @@ int layer_norm_forward(int dtype, int64_t rows, int64_t cols, const void* x, int
                        double eps, void* y, int64_t y_ld, float* stats, cudaStream_t stream);
 int layer_norm_backward(int dtype, int64_t rows, int64_t cols, const void* x, int64_t x_ld, const void* gamma, const float* stats,
                         const void* g, int64_t g_ld, void* gx, int64_t gx_ld, int accumulate_x, float* ggamma, float* gbeta,
-                        cudaStream_t stream);
+                        float* gxsum, cudaStream_t stream);
+int add_layer_norm_forward(int dtype, int64_t rows, int64_t cols, const void* a, int64_t a_ld, const void* b, int64_t b_ld,
+                           void* sum, int64_t sum_ld, const void* gamma, const void* beta, double eps, void* y, int64_t y_ld,
+                           float* stats, cudaStream_t stream);
+int relu_backward_column_sum(int dtype, int64_t rows, int64_t cols, const void* y, int64_t y_ld, void* g, int64_t ld, float* out,
+                             cudaStream_t stream);
+int rowwise_setup_device();                  // opt-in shared memory of the row-wise kernels
 int softmax_forward(int dtype, int64_t rows, int64_t cols, const void* x, int64_t x_ld, double alpha, void* y, int64_t y_ld,
                     cudaStream_t stream);
 int softmax_backward(int dtype, int64_t rows, int64_t cols, const void* y, int64_t y_ld, const void* g, int64_t g_ld,

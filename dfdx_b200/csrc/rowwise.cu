@@ -185,9 +185,12 @@ __device__ __forceinline__ void unpack_vec(const uint4& raw, float* f) {
 // by instruction issue): gamma and beta wait in shared memory as f32 (lane-major float4s), the next row's loads are
 // issued one row ahead, and a launch-resident grid walks the rows.
 constexpr int LN_FWD_VEC_BLOCKS_PER_SM = 3;
-template <typename T, int MAXV>
+// ADD: the normalised row is x + res, rounded to T as a separate add would round it and also written to `sum` (the
+// residual connection in front of the LayerNorm, whose backward needs that sum).
+template <typename T, int MAXV, bool ADD>
 __global__ void __launch_bounds__(256, LN_FWD_VEC_BLOCKS_PER_SM)
-    layer_norm_fwd_vec_kernel(const T* __restrict__ x, long long x_ld, const T* __restrict__ gamma, const T* __restrict__ beta,
+    layer_norm_fwd_vec_kernel(const T* __restrict__ x, long long x_ld, const T* __restrict__ res, long long res_ld,
+                              T* __restrict__ sum, long long sum_ld, const T* __restrict__ gamma, const T* __restrict__ beta,
                               float eps, T* __restrict__ y, long long y_ld, float* __restrict__ stats, long long rows, int cols) {
   constexpr int N = Vec<T>::N, J = N / 4;
   __shared__ float4 gamma_s[MAXV * J][32], beta_s[MAXV * J][32];
@@ -205,11 +208,15 @@ __global__ void __launch_bounds__(256, LN_FWD_VEC_BLOCKS_PER_SM)
     beta_s[vj][ln] = bv;
   }
   __syncthreads();
-  uint4 nx[MAXV];
+  uint4 nx[MAXV], nr[ADD ? MAXV : 1];
   auto fetch = [&](long long r) {
 #pragma unroll
-    for (int v = 0; v < MAXV; ++v)
-      if ((v * 32 + lane) * N < cols) nx[v] = *reinterpret_cast<const uint4*>(x + r * x_ld + (v * 32 + lane) * N);
+    for (int v = 0; v < MAXV; ++v) {
+      if ((v * 32 + lane) * N < cols) {
+        nx[v] = *reinterpret_cast<const uint4*>(x + r * x_ld + (v * 32 + lane) * N);
+        if constexpr (ADD) nr[v] = *reinterpret_cast<const uint4*>(res + r * res_ld + (v * 32 + lane) * N);
+      }
+    }
   };
   if (warp0 < rows) fetch(warp0);
   for (long long r = warp0; r < rows; r += nwarps) {
@@ -219,6 +226,13 @@ __global__ void __launch_bounds__(256, LN_FWD_VEC_BLOCKS_PER_SM)
     for (int v = 0; v < MAXV; ++v) {
       if ((v * 32 + lane) * N < cols) {
         unpack_vec<T>(nx[v], f[v]);
+        if constexpr (ADD) {
+          float fr[N];
+          unpack_vec<T>(nr[v], fr);
+#pragma unroll
+          for (int q = 0; q < N; ++q) f[v][q] = to_f(from_f<T>(f[v][q] + fr[q]));
+          store_vec(sum + r * sum_ld, (v * 32 + lane) * N, cols, true, f[v]);
+        }
 #pragma unroll
         for (int q = 0; q < N; ++q) s += f[v][q];
       }
@@ -370,19 +384,32 @@ __global__ void __launch_bounds__(256) layer_norm_bwd_kernel(const T* __restrict
 // next row's loads, issued one row ahead.  Two blocks per SM, one launch-resident wave.
 
 constexpr int LN_BWD_VEC_BLOCKS_PER_SM = 2;
-template <typename T, int MAXV>
+// GSUM: a third running sum, of this op's grad_x as stored (rounded to T): the bias gradient of a Linear whose output
+// fed the LayerNorm (through a residual add, which passes the gradient on unchanged).
+template <typename T, int MAXV, bool GSUM>
+struct LnBwdVecSmem {
+  static constexpr int J = Vec<T>::N / 4, KINDS = GSUM ? 3 : 2;
+  float4 acc[8][KINDS][MAXV * J][32];                          // [warp][g * x-hat | g | grad_x][vector, quarter][lane]
+  float4 gamma[MAXV * J][32];                                  // gamma (ones without it) in the same order
+};
+template <typename T, int MAXV, bool GSUM>
 __global__ void __launch_bounds__(256, LN_BWD_VEC_BLOCKS_PER_SM)
     layer_norm_bwd_vec_kernel(const T* __restrict__ x, long long x_ld, const T* __restrict__ gamma, const float* __restrict__ stats,
                               const T* __restrict__ g, long long g_ld, T* __restrict__ gx, long long gx_ld, int accumulate_x,
-                              float* __restrict__ ggamma, float* __restrict__ gbeta, long long rows, int cols) {
-  constexpr int N = Vec<T>::N, J = N / 4;
-  __shared__ float4 acc[8][2][MAXV * J][32];                   // [warp][g * x-hat | g][vector, quarter][lane]
-  __shared__ float4 gamma_s[MAXV * J][32];                     // gamma (ones without it) in the same order
+                              float* __restrict__ ggamma, float* __restrict__ gbeta, float* __restrict__ gxsum, long long rows,
+                              int cols) {
+  constexpr int N = Vec<T>::N, J = N / 4, KINDS = GSUM ? 3 : 2;
+  extern __shared__ __align__(16) unsigned char ln_bwd_smem[];
+  LnBwdVecSmem<T, MAXV, GSUM>& sm = *reinterpret_cast<LnBwdVecSmem<T, MAXV, GSUM>*>(ln_bwd_smem);
+  auto& acc = sm.acc;
+  auto& gamma_s = sm.gamma;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const long long warp0 = (long long)blockIdx.x * 8 + warp, nwarps = (long long)gridDim.x * 8;
   const float inv_n = 1.f / (float)cols;
 #pragma unroll
-  for (int i = 0; i < MAXV * J; ++i) acc[warp][0][i][lane] = acc[warp][1][i][lane] = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int i = 0; i < MAXV * J; ++i)
+#pragma unroll
+    for (int kd = 0; kd < KINDS; ++kd) acc[warp][kd][i][lane] = make_float4(0.f, 0.f, 0.f, 0.f);
   for (int i = threadIdx.x; i < MAXV * J * 32; i += 256) {
     const int vj = i >> 5, ln = i & 31, col = ((vj / J) * 32 + ln) * N + (vj % J) * 4;
     float4 gv = make_float4(1.f, 1.f, 1.f, 1.f);
@@ -455,16 +482,29 @@ __global__ void __launch_bounds__(256, LN_BWD_VEC_BLOCKS_PER_SM)
           for (int q = 0; q < N; ++q) {
             const float t = fmaf(rstd, gg[v][q], fmaf(k2, xh[v][q], k0));
             d[q] = accumulate_x ? d[q] + t : t;
+            if constexpr (GSUM) xh[v][q] = to_f(from_f<T>(t));   // x-hat is no longer needed: keep what is stored
           }
           store_vec(or_, c, cols, true, d);
+          if constexpr (GSUM) {
+#pragma unroll
+            for (int j = 0; j < J; ++j) {
+              float4 a = acc[warp][2][v * J + j][lane];
+              a.x += xh[v][j * 4]; a.y += xh[v][j * 4 + 1]; a.z += xh[v][j * 4 + 2]; a.w += xh[v][j * 4 + 3];
+              acc[warp][2][v * J + j][lane] = a;
+            }
+          }
         }
       }
     }
   }
   __syncthreads();
-  // threads 0..127 add the eight warps' sums of g * x-hat into dgamma, threads 128..255 those of g into dbeta
-  const int kind = threadIdx.x >> 7;
-  float* out = kind ? gbeta : ggamma;
+  // threads 0..127 add the eight warps' sums of g * x-hat into dgamma, threads 128..255 those of g into dbeta; then
+  // (GSUM) threads 0..127 those of grad_x
+#pragma unroll 1
+  for (int pass = 0; pass < (GSUM ? 2 : 1); ++pass) {
+  const int kind = pass ? 2 : (threadIdx.x >> 7);
+  float* out = pass ? gxsum : (kind ? gbeta : ggamma);
+  if (pass && threadIdx.x >= 128) out = nullptr;
   if (out) {
     for (int i = threadIdx.x & 127; i < MAXV * J * 32; i += 128) {
       const int vj = i >> 5, ln = i & 31, col = ((vj / J) * 32 + ln) * N + (vj % J) * 4;
@@ -483,6 +523,7 @@ __global__ void __launch_bounds__(256, LN_BWD_VEC_BLOCKS_PER_SM)
         }
       }
     }
+  }
   }
 }
 
@@ -517,6 +558,89 @@ __global__ void __launch_bounds__(256) column_sum_kernel(const T* __restrict__ g
 #pragma unroll
   for (int q = 0; q < N; ++q) red[warp][lane * N + q] = acc[q];
   __syncthreads();
+  for (int i = threadIdx.x * 4; i < 32 * N; i += 256 * 4) {
+    const int col = blockIdx.x * 32 * N + i;
+    if (col < cols) {
+      float t[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int w = 0; w < 8; ++w) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) t[e] += red[w][i + e];
+      }
+      if (col + 3 < cols && ((uintptr_t)(out + col) & 15) == 0) {
+        asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(out + col), "f"(t[0]), "f"(t[1]), "f"(t[2]),
+                     "f"(t[3]) : "memory");
+      } else {
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+          if (col + e < cols) atomicAdd(out + col + e, t[e]);
+      }
+    }
+  }
+}
+
+// sum[r, :] = a[r, :] + b[r, :] (the fallback of the fused add + LayerNorm for rows the vector kernel does not take).
+template <typename T>
+__global__ void __launch_bounds__(256) add_rows_kernel(const T* __restrict__ a, long long a_ld, const T* __restrict__ b,
+                                                       long long b_ld, T* __restrict__ sum, long long sum_ld, long long rows,
+                                                       int cols) {
+  const long long total = rows * (long long)cols;
+  for (long long i = (long long)blockIdx.x * 256 + threadIdx.x; i < total; i += (long long)gridDim.x * 256) {
+    const long long r = i / cols;
+    const int c = (int)(i - r * cols);
+    sum[r * sum_ld + c] = from_f<T>(to_f(a[r * a_ld + c]) + to_f(b[r * b_ld + c]));
+  }
+}
+
+// ReLU's backward and the bias gradient behind it in one pass: g[i, j] = y[i, j] > 0 ? g[i, j] : 0 (in place) and
+// out[j] += sum_i g[i, j].  Same decomposition as column_sum_kernel.
+template <typename T>
+__global__ void __launch_bounds__(256) relu_bwd_column_sum_kernel(const T* __restrict__ y, long long y_ld, T* __restrict__ g,
+                                                                  long long ld, float* __restrict__ out, long long rows, int cols,
+                                                                  int vec) {
+  constexpr int N = Vec<T>::N;
+  __shared__ float red[8][32 * N + 1];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int c = (blockIdx.x * 32 + lane) * N;
+  float acc[N];
+#pragma unroll
+  for (int q = 0; q < N; ++q) acc[q] = 0.f;
+  if (c < cols) {
+    const long long step = (long long)gridDim.y * 8;
+    long long r = (long long)blockIdx.y * 8 + warp;
+    for (; r + step < rows; r += 2 * step) {                  // two rows (four loads) in flight per lane
+      float fg[2][N], fy[2][N];
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        load_vec(g + (r + u * step) * ld, c, cols, vec, fg[u]);
+        load_vec(y + (r + u * step) * y_ld, c, cols, vec, fy[u]);
+      }
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+#pragma unroll
+        for (int q = 0; q < N; ++q) {
+          fg[u][q] = fy[u][q] > 0.f ? fg[u][q] : 0.f;
+          acc[q] += fg[u][q];
+        }
+        store_vec(g + (r + u * step) * ld, c, cols, vec, fg[u]);
+      }
+    }
+    for (; r < rows; r += step) {
+      float fg[N], fy[N];
+      load_vec(g + r * ld, c, cols, vec, fg);
+      load_vec(y + r * y_ld, c, cols, vec, fy);
+#pragma unroll
+      for (int q = 0; q < N; ++q) {
+        fg[q] = fy[q] > 0.f ? fg[q] : 0.f;
+        acc[q] += fg[q];
+      }
+      store_vec(g + r * ld, c, cols, vec, fg);
+    }
+  }
+#pragma unroll
+  for (int q = 0; q < N; ++q) red[warp][lane * N + q] = acc[q];
+  __syncthreads();
+  if (out == nullptr) return;
   for (int i = threadIdx.x * 4; i < 32 * N; i += 256 * 4) {
     const int col = blockIdx.x * 32 * N + i;
     if (col < cols) {
@@ -706,8 +830,8 @@ int ln_forward_t(int64_t rows, int64_t cols, const void* x, int64_t x_ld, const 
                                                  stats, rows, (int)cols, vec);
   };
   if (fast) {
-    layer_norm_fwd_vec_kernel<T, 2><<<(unsigned)blocks, 256, 0, stream>>>((const T*)x, x_ld, (const T*)gamma, (const T*)beta,
-                                                                            (float)eps, (T*)y, y_ld, stats, rows, (int)cols);
+    layer_norm_fwd_vec_kernel<T, 2, false><<<(unsigned)blocks, 256, 0, stream>>>(
+        (const T*)x, x_ld, nullptr, 0, nullptr, 0, (const T*)gamma, (const T*)beta, (float)eps, (T*)y, y_ld, stats, rows, (int)cols);
   } else if (vecs <= 2) launch(layer_norm_fwd_reg_kernel<T, 2>);
   else if (vecs <= 4) launch(layer_norm_fwd_reg_kernel<T, 4>);
   else if (vecs <= 8) launch(layer_norm_fwd_reg_kernel<T, 8>);
@@ -716,9 +840,42 @@ int ln_forward_t(int64_t rows, int64_t cols, const void* x, int64_t x_ld, const 
   return note_cuda_error(cudaGetLastError(), "layer_norm forward launch");
 }
 
+// y = LayerNorm(a + b), sum = a + b: one kernel for rows the vector kernel takes, otherwise an add followed by the
+// plain LayerNorm.
+template <typename T>
+int add_ln_forward_t(int64_t rows, int64_t cols, const void* a, int64_t a_ld, const void* b, int64_t b_ld, void* sum,
+                     int64_t sum_ld, const void* gamma, const void* beta, double eps, void* y, int64_t y_ld, float* stats,
+                     cudaStream_t stream) {
+  DeviceState* ds = device_state();
+  const int64_t vecs = (cols + 32 * Vec<T>::N - 1) / (32 * Vec<T>::N);
+  if (vecs <= 2 && vec_ok(sizeof(T), cols, {a_ld, b_ld, sum_ld, y_ld}, {a, b, sum, y, gamma, beta})) {
+    long long blocks = (rows + 7) / 8;
+    const long long cap = (long long)ds->sm_count * LN_FWD_VEC_BLOCKS_PER_SM;
+    if (blocks > cap) blocks = cap;
+    layer_norm_fwd_vec_kernel<T, 2, true><<<(unsigned)blocks, 256, 0, stream>>>(
+        (const T*)a, a_ld, (const T*)b, b_ld, (T*)sum, sum_ld, (const T*)gamma, (const T*)beta, (float)eps, (T*)y, y_ld, stats,
+        rows, (int)cols);
+    count_launch(false);
+    return note_cuda_error(cudaGetLastError(), "add + layer_norm forward launch");
+  }
+  const long long total = rows * cols;
+  long long blocks = (total + 255) / 256;
+  if (blocks > (long long)ds->sm_count * 16) blocks = (long long)ds->sm_count * 16;
+  add_rows_kernel<T><<<(unsigned)blocks, 256, 0, stream>>>((const T*)a, a_ld, (const T*)b, b_ld, (T*)sum, sum_ld, rows, (int)cols);
+  count_launch(false);
+  const int rc = note_cuda_error(cudaGetLastError(), "row add launch");
+  if (rc) return rc;
+  return ln_forward_t<T>(rows, cols, sum, sum_ld, gamma, beta, eps, y, y_ld, stats, stream);
+}
+
+template <typename T>
+int column_sum_t(int64_t rows, int64_t cols, const void* g, int64_t ld, float* out, cudaStream_t stream);
+
+// gxsum (may be NULL): receives the column sums of grad_x; needs grad_x written (not accumulated).
 template <typename T>
 int ln_backward_t(int64_t rows, int64_t cols, const void* x, int64_t x_ld, const void* gamma, const float* stats, const void* g,
-                  int64_t g_ld, void* gx, int64_t gx_ld, int accumulate_x, float* ggamma, float* gbeta, cudaStream_t stream) {
+                  int64_t g_ld, void* gx, int64_t gx_ld, int accumulate_x, float* ggamma, float* gbeta, float* gxsum,
+                  cudaStream_t stream) {
   DeviceState* ds = device_state();
   constexpr int N = Vec<T>::N;
   const int vec = vec_ok(sizeof(T), cols, {x_ld, g_ld, gx ? gx_ld : 0}, {x, g, gx, gamma}) ? 1 : 0;
@@ -732,16 +889,25 @@ int ln_backward_t(int64_t rows, int64_t cols, const void* x, int64_t x_ld, const
     kernel<<<(unsigned)blocks, 256, 0, stream>>>((const T*)x, x_ld, (const T*)gamma, stats, (const T*)g, g_ld, (T*)gx, gx_ld,
                                                  accumulate_x, ggamma, gbeta, rows, (int)cols, vec);
   };
+  if (fast && gxsum) {
+    layer_norm_bwd_vec_kernel<T, 2, true><<<(unsigned)blocks, 256, sizeof(LnBwdVecSmem<T, 2, true>), stream>>>(
+        (const T*)x, x_ld, (const T*)gamma, stats, (const T*)g, g_ld, (T*)gx, gx_ld, accumulate_x, ggamma, gbeta, gxsum, rows,
+        (int)cols);
+    count_launch(false);
+    return note_cuda_error(cudaGetLastError(), "layer_norm backward launch");
+  }
   if (fast) {
-    layer_norm_bwd_vec_kernel<T, 2><<<(unsigned)blocks, 256, 0, stream>>>((const T*)x, x_ld, (const T*)gamma, stats, (const T*)g,
-                                                                            g_ld, (T*)gx, gx_ld, accumulate_x, ggamma, gbeta,
-                                                                            rows, (int)cols);
+    layer_norm_bwd_vec_kernel<T, 2, false><<<(unsigned)blocks, 256, sizeof(LnBwdVecSmem<T, 2, false>), stream>>>(
+        (const T*)x, x_ld, (const T*)gamma, stats, (const T*)g, g_ld, (T*)gx, gx_ld, accumulate_x, ggamma, gbeta, nullptr, rows,
+        (int)cols);
   } else if (vecs <= 2) launch(layer_norm_bwd_kernel<T, 2>);
   else if (vecs <= 4) launch(layer_norm_bwd_kernel<T, 4>);
   else if (vecs <= 8) launch(layer_norm_bwd_kernel<T, 8>);
   else return B200_ERR_LIMIT;
   count_launch(false);
-  return note_cuda_error(cudaGetLastError(), "layer_norm backward launch");
+  const int rc = note_cuda_error(cudaGetLastError(), "layer_norm backward launch");
+  if (rc || !gxsum) return rc;
+  return column_sum_t<T>(rows, cols, gx, gx_ld, gxsum, stream);   // the unfused route: one more pass over grad_x
 }
 
 template <typename T>
@@ -758,6 +924,24 @@ int column_sum_t(int64_t rows, int64_t cols, const void* g, int64_t ld, float* o
   column_sum_kernel<T><<<dim3((unsigned)gx, (unsigned)gy), 256, 0, stream>>>((const T*)g, ld, out, rows, (int)cols, vec);
   count_launch(false);
   return note_cuda_error(cudaGetLastError(), "column sum launch");
+}
+
+template <typename T>
+int relu_bwd_column_sum_t(int64_t rows, int64_t cols, const void* y, int64_t y_ld, void* g, int64_t ld, float* out,
+                          cudaStream_t stream) {
+  DeviceState* ds = device_state();
+  constexpr int N = Vec<T>::N;
+  const int vec = vec_ok(sizeof(T), cols, {ld, y_ld}, {g, y}) ? 1 : 0;
+  const long long gx = (cols + 32 * N - 1) / (32 * N);
+  long long gy = (rows + 63) / 64;                           // at least 8 rows per warp
+  const long long cap = ((long long)ds->sm_count * 8 + gx - 1) / gx;
+  if (gy > cap) gy = cap;
+  if (gy < 1) gy = 1;
+  if (gx > 0x7fffffffLL || gy > 65535) return B200_ERR_LIMIT;
+  relu_bwd_column_sum_kernel<T><<<dim3((unsigned)gx, (unsigned)gy), 256, 0, stream>>>((const T*)y, y_ld, (T*)g, ld, out, rows,
+                                                                                      (int)cols, vec);
+  count_launch(false);
+  return note_cuda_error(cudaGetLastError(), "relu backward + column sum launch");
 }
 
 template <typename T>
@@ -819,16 +1003,58 @@ int layer_norm_forward(int dtype, int64_t rows, int64_t cols, const void* x, int
 
 int layer_norm_backward(int dtype, int64_t rows, int64_t cols, const void* x, int64_t x_ld, const void* gamma, const float* stats,
                         const void* g, int64_t g_ld, void* gx, int64_t gx_ld, int accumulate_x, float* ggamma, float* gbeta,
-                        cudaStream_t stream) {
+                        float* gxsum, cudaStream_t stream) {
   if (rows == 0 || cols == 0) return B200_OK;
   if (!device_state()) return note_cuda_error(cudaErrorInitializationError, "b200_init not called on this device");
   switch (dtype) {
-    case B200_F32: return ln_backward_t<float>(rows, cols, x, x_ld, gamma, stats, g, g_ld, gx, gx_ld, accumulate_x, ggamma, gbeta, stream);
+    case B200_F32:
+      return ln_backward_t<float>(rows, cols, x, x_ld, gamma, stats, g, g_ld, gx, gx_ld, accumulate_x, ggamma, gbeta, gxsum, stream);
     case B200_F16:
     case B200_AMP_F16:
-      return ln_backward_t<__half>(rows, cols, x, x_ld, gamma, stats, g, g_ld, gx, gx_ld, accumulate_x, ggamma, gbeta, stream);
+      return ln_backward_t<__half>(rows, cols, x, x_ld, gamma, stats, g, g_ld, gx, gx_ld, accumulate_x, ggamma, gbeta, gxsum, stream);
     default: return B200_ERR_UNSUPPORTED;
   }
+}
+
+int add_layer_norm_forward(int dtype, int64_t rows, int64_t cols, const void* a, int64_t a_ld, const void* b, int64_t b_ld,
+                           void* sum, int64_t sum_ld, const void* gamma, const void* beta, double eps, void* y, int64_t y_ld,
+                           float* stats, cudaStream_t stream) {
+  if (rows == 0 || cols == 0) return B200_OK;
+  if (!device_state()) return note_cuda_error(cudaErrorInitializationError, "b200_init not called on this device");
+  if (cols > 0x7fffffffLL) return B200_ERR_LIMIT;
+  switch (dtype) {
+    case B200_F32:
+      return add_ln_forward_t<float>(rows, cols, a, a_ld, b, b_ld, sum, sum_ld, gamma, beta, eps, y, y_ld, stats, stream);
+    case B200_F16:
+    case B200_AMP_F16:
+      return add_ln_forward_t<__half>(rows, cols, a, a_ld, b, b_ld, sum, sum_ld, gamma, beta, eps, y, y_ld, stats, stream);
+    default: return B200_ERR_UNSUPPORTED;
+  }
+}
+
+int relu_backward_column_sum(int dtype, int64_t rows, int64_t cols, const void* y, int64_t y_ld, void* g, int64_t ld, float* out,
+                             cudaStream_t stream) {
+  if (rows == 0 || cols == 0) return B200_OK;
+  if (!device_state()) return note_cuda_error(cudaErrorInitializationError, "b200_init not called on this device");
+  if (cols > 0x7fffffffLL) return B200_ERR_LIMIT;
+  switch (dtype) {
+    case B200_F32: return relu_bwd_column_sum_t<float>(rows, cols, y, y_ld, g, ld, out, stream);
+    case B200_F16:
+    case B200_AMP_F16: return relu_bwd_column_sum_t<__half>(rows, cols, y, y_ld, g, ld, out, stream);
+    default: return B200_ERR_UNSUPPORTED;
+  }
+}
+
+int rowwise_setup_device() {
+  int rc;
+  auto opt_in = [&](auto kernel, size_t bytes) {
+    return note_cuda_error(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes),
+                           "cudaFuncSetAttribute(layer_norm backward)");
+  };
+  if ((rc = opt_in(layer_norm_bwd_vec_kernel<float, 2, false>, sizeof(LnBwdVecSmem<float, 2, false>)))) return rc;
+  if ((rc = opt_in(layer_norm_bwd_vec_kernel<float, 2, true>, sizeof(LnBwdVecSmem<float, 2, true>)))) return rc;
+  if ((rc = opt_in(layer_norm_bwd_vec_kernel<__half, 2, false>, sizeof(LnBwdVecSmem<__half, 2, false>)))) return rc;
+  return opt_in(layer_norm_bwd_vec_kernel<__half, 2, true>, sizeof(LnBwdVecSmem<__half, 2, true>));
 }
 
 int column_sum(int dtype, int64_t rows, int64_t cols, const void* g, int64_t ld, float* out, cudaStream_t stream) {

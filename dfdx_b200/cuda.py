@@ -315,6 +315,39 @@ class Cuda:
               "b200_layer_norm_backward")
         return gx
 
+    def layer_norm_backward_sum(self, x, gamma, stats, grad_out, grad_gamma, grad_beta, grad_x_sum):
+        """`layer_norm_backward` that also adds the column sums of the grad_x it returns into grad_x_sum (f32, `cols`
+        elements): the bias gradient of a Linear whose output reached this LayerNorm through a residual add."""
+        cols = x.shape[-1]
+        rows = x.numel() // max(cols, 1)
+        gx = self._empty(tuple(x.shape), x)
+        check(self.lib.b200_layer_norm_backward_sum(self._dtype(x), rows, cols, x.data_ptr(), cols, _ptr(gamma),
+                                                    stats.data_ptr(), grad_out.data_ptr(), cols, gx.data_ptr(), cols,
+                                                    _ptr(grad_gamma), _ptr(grad_beta), grad_x_sum.data_ptr(),
+                                                    self._stream()), "b200_layer_norm_backward_sum")
+        return gx
+
+    def add_layer_norm_forward(self, a, b, gamma=None, beta=None, eps: float = 1e-5):
+        """`LayerNorm1D(a + b)` (ResidualAdd followed by the norm) in one kernel.  Returns (y, a + b, stats)."""
+        cols = a.shape[-1]
+        rows = a.numel() // max(cols, 1)
+        _assert_eq(tuple(a.shape), tuple(b.shape))
+        total, y = self._empty(tuple(a.shape), a), self._empty(tuple(a.shape), a)
+        stats = torch.empty((rows, 2), dtype=torch.float32, device=a.device)
+        check(self.lib.b200_add_layer_norm_forward(self._dtype(a), rows, cols, a.data_ptr(), cols, b.data_ptr(), cols,
+                                                   total.data_ptr(), cols, _ptr(gamma), _ptr(beta), float(eps),
+                                                   y.data_ptr(), cols, stats.data_ptr(), self._stream()),
+              "b200_add_layer_norm_forward")
+        return y, total, stats
+
+    def relu_backward_bias_grad(self, y, grad, grad_bias=None) -> None:
+        """In place: grad = grad where y > 0 else 0 (ReLU's backward); grad_bias (f32) += column sums of the result."""
+        cols = y.shape[-1]
+        rows = y.numel() // max(cols, 1)
+        _assert_eq(tuple(y.shape), tuple(grad.shape))
+        check(self.lib.b200_relu_backward_bias_grad(self._dtype(y), rows, cols, y.data_ptr(), cols, grad.data_ptr(), cols,
+                                                    _ptr(grad_bias), self._stream()), "b200_relu_backward_bias_grad")
+
     def softmax_forward(self, x, alpha: float = 1.0, out=None):
         """`(x * alpha).softmax::<last axis>()` (softmax.rs:36-84) in one pass; x (..., cols) with a unit last stride."""
         x2 = x.reshape(-1, x.shape[-1])

@@ -413,7 +413,12 @@ class Trainer:
                     a.qkv_slot = (self.flat16[ws[0][0]:ws[2][1]].view(o3, i_), self.flat16[bs[0][0]:bs[2][1]],
                                   self.flat_gw16[ws[0][0]:ws[2][1]].view(o3, i_), self.flat_grad[bs[0][0]:bs[2][1]])
             self.model.attach = True
-        self.opt = torch.optim.Adam(params, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, fused=True, capturable=True)
+        # Adam is element-wise, so it runs on the one flat buffer (a single fused kernel per step) instead of on the
+        # hundred parameter views into it; `params` keeps the views for inspection
+        self.params = params
+        self.flat_p = torch.nn.Parameter(self.flat_param, requires_grad=False)
+        self.flat_p.grad = self.flat_grad
+        self.opt = torch.optim.Adam([self.flat_p], lr=1e-3, betas=(0.9, 0.999), eps=1e-8, fused=True, capturable=True)
         self.graph = None
 
     def _step(self, x: torch.Tensor, target: torch.Tensor) -> torch.Tensor:

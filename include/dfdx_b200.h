@@ -366,6 +366,34 @@ int b200_layer_norm_backward(int dtype, size_t rows, size_t cols, const void* x,
                              void* grad_x, size_t grad_x_ld, int accumulate_x,
                              float* grad_gamma, float* grad_beta, void* stream);
 
+/* b200_layer_norm_backward (grad_x written) that also returns the column sums of grad_x as it stores it (rounded to
+ * dtype): grad_x_sum[j] += sum_r grad_x[r, j] in f32.  For `LayerNorm(x + Linear(h))`, where the residual add passes
+ * the gradient on unchanged, that is the Linear's bias gradient (bias1d.rs:66-79), which otherwise costs a pass of
+ * its own over grad_x.  One kernel where the rows allow 16-byte access and cols <= 512 (f16) / 256 (f32), otherwise the
+ * plain backward followed by the column sum. */
+int b200_layer_norm_backward_sum(int dtype, size_t rows, size_t cols, const void* x, size_t x_ld, const void* gamma,
+                                 const float* stats, const void* grad_out, size_t grad_out_ld,
+                                 void* grad_x, size_t grad_x_ld, float* grad_gamma, float* grad_beta,
+                                 float* grad_x_sum, void* stream);
+
+/* The residual add in front of a LayerNorm and the LayerNorm in one kernel (dfdx's transformer block computes
+ * `norm(x + sublayer(x))`: ResidualAdd, dfdx/src/nn/layers/residual_add.rs, then LayerNorm1D,
+ * dfdx/src/nn/layers/transformer.rs:27-30):
+ *     sum[r, :] = a[r, :] + b[r, :]   (rounded to dtype, as the separate add stores it)
+ *     y[r, :]   = LayerNorm(sum[r, :])
+ * `sum` is kept because the LayerNorm's backward reads it.  Same limits and `stats` as b200_layer_norm_forward; rows
+ * the one-kernel path does not take (cols > 512 (f16) / 256 (f32), or no 16-byte access) run as an add kernel followed
+ * by the plain LayerNorm. */
+int b200_add_layer_norm_forward(int dtype, size_t rows, size_t cols, const void* a, size_t a_ld, const void* b, size_t b_ld,
+                                void* sum, size_t sum_ld, const void* gamma, const void* beta, double epsilon,
+                                void* y, size_t y_ld, float* stats, void* stream);
+
+/* ReLU's backward (dfdx-core/src/tensor_ops/relu/cpu_kernel.rs:11, grad * (y > 0)) and the bias gradient of the Linear in front of it in
+ * one pass: grad[r, j] = y[r, j] > 0 ? grad[r, j] : 0, in place, and grad_bias[j] += sum_r grad[r, j] in f32
+ * (grad_bias may be NULL: mask only). */
+int b200_relu_backward_bias_grad(int dtype, size_t rows, size_t cols, const void* y, size_t y_ld,
+                                 void* grad, size_t grad_ld, float* grad_bias, void* stream);
+
 /* Backward of `bias.broadcast_like(&x) + x` (dfdx/src/nn/layers/bias1d.rs:66-79; the `sum` over the
  * broadcast axes): grad_bias[j] += sum_r grad_out[r, j] in f32, one pass over grad_out. */
 int b200_bias_grad(int dtype, size_t rows, size_t cols, const void* grad_out, size_t grad_out_ld,

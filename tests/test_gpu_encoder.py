@@ -82,8 +82,7 @@ def test_trainer_direct_gradients_match_autograd_route(cuda_dev):
     assert torch.equal(a.flat_param, b.flat_param)
     la, lb = a._step(x, t), b._step(x, t)
     assert abs(la.item() - lb.item()) <= 1e-6 * abs(lb.item())
-    for pa, pb, (name, _) in zip(a.opt.param_groups[0]["params"], b.opt.param_groups[0]["params"],
-                                 [(n, 0) for n in range(10 ** 6)]):
+    for pa, pb, (name, _) in zip(a.params, b.params, [(n, 0) for n in range(10 ** 6)]):
         ref = pb.grad.float()
         err = (pa.grad.float() - ref).norm() / max(float(ref.norm()), 1e-2 * float(b.flat_grad.norm()))
         assert err <= 5e-3, f"parameter {name}: {float(err):.3e}"

@@ -66,6 +66,63 @@ def test_bias_grad(cuda_dev, oracle, dtype, shape):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+@pytest.mark.parametrize("shape", [(5, 3), (300, 512), (77, 520), (4, 16, 128), (2050, 256), (64, 37), (9, 2048)],
+                         ids=lambda s: "x".join(map(str, s)))
+def test_add_layer_norm_and_backward_with_sum(cuda_dev, oracle, dtype, shape):
+    """`LayerNorm(a + b)` in one call (the sum comes back rounded as a separate add rounds it, the norm is taken of
+    that rounded sum) and the backward that also returns the column sums of the grad_x it stores; shapes on both
+    sides of the one-kernel path's limits."""
+    dev = cuda_dev
+    cols = shape[-1]
+    if dtype == torch.float32 and cols > 1024:
+        pytest.skip("backward limit for f32 is 1024 columns")
+    g = gen(sum(shape) + 7)
+    a = (torch.randn(*shape, generator=g, dtype=torch.float64) * 2 + 0.5).to(dtype).to(dev.device)
+    b = torch.randn(*shape, generator=g, dtype=torch.float64).to(dtype).to(dev.device)
+    gamma = (1 + 0.3 * torch.randn(cols, generator=g, dtype=torch.float64)).to(dtype).to(dev.device)
+    beta = torch.randn(cols, generator=g, dtype=torch.float64).to(dtype).to(dev.device)
+    go = torch.randn(*shape, generator=g, dtype=torch.float64).to(dtype).to(dev.device)
+    y, total, stats = dev.add_layer_norm_forward(a, b, gamma, beta, 1e-5)
+    want_sum = (a.cpu().double() + b.cpu().double()).to(dtype)
+    assert torch.equal(total.cpu(), want_sum)                                    # one rounding, like the add op
+    want, bwd = oracle.layer_norm(want_sum, gamma, beta, 1e-5)
+    assert oracle.rel_frobenius(y, want) <= FROB_TOL[dtype]
+    y2, stats2 = dev.layer_norm_forward(total, gamma, beta, 1e-5, want_stats=True)
+    assert torch.equal(y, y2) and torch.equal(stats, stats2)                     # same arithmetic as the two-step route
+    gg = torch.full((cols,), 1.0, dtype=torch.float32, device=dev.device)
+    gb = torch.full((cols,), -2.0, dtype=torch.float32, device=dev.device)
+    gs = torch.full((cols,), 0.5, dtype=torch.float32, device=dev.device)
+    gx = dev.layer_norm_backward_sum(total, gamma, stats, go, gg, gb, gs)
+    wx, wg, wb = bwd(go)
+    tol = FROB_TOL[dtype] * (4 if dtype == torch.float16 else 1)
+    assert oracle.rel_frobenius(gx, wx) <= tol
+    assert oracle.rel_frobenius(gg - 1.0, wg) <= 1e-4
+    assert oracle.rel_frobenius(gb + 2.0, wb) <= 1e-4
+    # the sums are those of the stored (rounded) gradient
+    assert oracle.rel_frobenius(gs - 0.5, gx.cpu().double().reshape(-1, cols).sum(0)) <= 1e-5
+    assert torch.equal(gx, dev.layer_norm_backward(total, gamma, stats, go))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+@pytest.mark.parametrize("shape", [(7, 5), (1000, 37), (4096, 2048), (3, 700, 520), (129, 264)], ids=str)
+def test_relu_backward_bias_grad(cuda_dev, oracle, dtype, shape):
+    """ReLU's backward in place plus the bias gradient: bit-exact mask (zeros where y <= 0, NaN-free), f32 sums."""
+    dev = cuda_dev
+    g = gen(sum(shape) + 3)
+    y = torch.relu(torch.randn(*shape, generator=g, dtype=torch.float64)).to(dtype).to(dev.device)
+    go = torch.randn(*shape, generator=g, dtype=torch.float64).to(dtype).to(dev.device)
+    want = torch.where(y > 0, go, torch.zeros_like(go))
+    out = torch.full((shape[-1],), 3.0, dtype=torch.float32, device=dev.device)
+    got = go.clone()
+    dev.relu_backward_bias_grad(y, got, out)
+    assert torch.equal(got, want)
+    assert oracle.rel_frobenius(out - 3.0, want.cpu().double().reshape(-1, shape[-1]).sum(0)) <= 1e-5
+    got2 = go.clone()
+    dev.relu_backward_bias_grad(y, got2, None)                                   # mask only
+    assert torch.equal(got2, want)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
 @pytest.mark.parametrize("shape", [(5, 3), (300, 512), (77, 520), (33, 1000), (64, 37), (4, 16, 128), (2050, 1024),
                                    (9, 2048), (3, 5000)], ids=lambda s: "x".join(map(str, s)))
 def test_softmax_forward_backward(cuda_dev, oracle, dtype, shape):
