@@ -254,6 +254,79 @@ class _DirectLayerNorm(torch.autograd.Function):
         return None, ctx.dev.layer_norm_backward(x, g16, stats, grad_out.contiguous(), gg32, gb32), None, None
 
 
+class _DirectAttentionBlock(torch.autograd.Function):
+    """`norm1(x + w_o(attention(w_q x, w_k x, w_v x)))` (dfdx/src/nn/layers/transformer.rs:27-28: ResidualAdd around
+    MultiHeadAttention, then LayerNorm1D) with the backward written out by hand, as dfdx's tape would replay it, so
+    that the gradients that meet at x and at the residual add are summed inside kernels that run anyway:
+    the residual add rides in the LayerNorm's forward kernel, the LayerNorm's backward also produces w_o's bias
+    gradient (the column sums of its grad_x), and the q/k/v projection's data gradient is accumulated onto the
+    residual branch's gradient by the GEMM (beta = 1) instead of by an add kernel.
+    Slots as in `_DirectLinear` / `_DirectLayerNorm`; `qkv` is the merged (3 * model, model) projection."""
+
+    @staticmethod
+    def forward(ctx, dev: Cuda, x, qkv, o, ln, heads: int, eps: float):
+        if x.storage_offset() or not _dense(x) or not x.is_contiguous():
+            x = x.contiguous()
+        b, s, m = x.shape
+        alpha = 1.0 / math.sqrt(m // heads)
+        p = dev.linear_forward(x, qkv[0].permute(1, 0), qkv[1], False)             # (b, s, 3 m)
+        q, k, v = _split_qkv(p, heads)
+        out, lse = dev.attention_forward(q, k, v, alpha, want_lse=True)            # (b, h, s, d) view of a (b, s, m) buffer
+        tokens = out.permute(0, 2, 1, 3).reshape(b, s, m)
+        y = dev.linear_forward(tokens, o[0].permute(1, 0), o[1], False)
+        z, total, stats = dev.add_layer_norm_forward(x, y, ln[0], ln[1], eps)
+        ctx.dev, ctx.slots, ctx.heads, ctx.alpha = dev, (qkv, o, ln), heads, alpha
+        ctx.save_for_backward(x, p, out, lse, tokens, total, stats)
+        return z
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        x, p, out, lse, tokens, total, stats = ctx.saved_tensors
+        dev, (qkv, o, ln), heads = ctx.dev, ctx.slots, ctx.heads
+        b, s, m = x.shape
+        # LayerNorm: gs is the gradient of x + y, i.e. of both; its column sums are w_o's bias gradient
+        gs = dev.layer_norm_backward_sum(total, ln[0], stats, grad_out.contiguous(), ln[2], ln[3], o[3])
+        g_tokens = torch.empty_like(tokens)
+        dev.matmat_br_backward_overwrite(tokens, g_tokens, o[0].permute(1, 0), o[2], gs)
+        gp = torch.empty_like(p)
+        q, k, v = _split_qkv(p, heads)
+        dev.attention_backward(q, k, v, ctx.alpha, out, lse, g_tokens.view(b, s, heads, m // heads).permute(0, 2, 1, 3),
+                               write_into=_split_qkv(gp, heads))
+        dev.matmat_br_backward_overwrite(x, None, qkv[0].permute(1, 0), qkv[2], gp)      # weight gradient, written
+        dev.matmat_br_backward(x, gs, qkv[0].permute(1, 0), None, gp)                    # gs += gp . W_qkv
+        dev.bias_grad(gp, qkv[3])
+        return None, gs, None, None, None, None, None
+
+
+class _DirectFeedForwardBlock(torch.autograd.Function):
+    """`norm2(x + l2(relu(l1 x)))` (transformer.rs:29-30) with the backward written out by hand, see
+    `_DirectAttentionBlock`: l2's bias gradient comes out of the LayerNorm's backward, ReLU's backward and l1's bias
+    gradient are one pass, and l1's data gradient is accumulated onto the residual branch's gradient by the GEMM."""
+
+    @staticmethod
+    def forward(ctx, dev: Cuda, x, l1, l2, ln, eps: float):
+        if x.storage_offset() or not _dense(x) or not x.is_contiguous():
+            x = x.contiguous()
+        h = dev.linear_forward(x, l1[0].permute(1, 0), l1[1], True)
+        y = dev.linear_forward(h, l2[0].permute(1, 0), l2[1], False)
+        z, total, stats = dev.add_layer_norm_forward(x, y, ln[0], ln[1], eps)
+        ctx.dev, ctx.slots = dev, (l1, l2, ln)
+        ctx.save_for_backward(x, h, total, stats)
+        return z
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        x, h, total, stats = ctx.saved_tensors
+        dev, (l1, l2, ln) = ctx.dev, ctx.slots
+        gs = dev.layer_norm_backward_sum(total, ln[0], stats, grad_out.contiguous(), ln[2], ln[3], l2[3])
+        gh = torch.empty_like(h)
+        dev.matmat_br_backward_overwrite(h, gh, l2[0].permute(1, 0), l2[2], gs)
+        dev.relu_backward_bias_grad(h, gh, l1[3])
+        dev.matmat_br_backward_overwrite(x, None, l1[0].permute(1, 0), l1[2], gh)
+        dev.matmat_br_backward(x, gs, l1[0].permute(1, 0), None, gh)                    # gs += gh . W_1
+        return None, gs, None, None, None, None
+
+
 class _Attach(torch.autograd.Function):
     """Puts a tensor that needs no gradient on the tape (the ops above take their parameters outside autograd, so
     the first layer's input is what makes their backward run); nothing flows back through it."""
@@ -336,6 +409,12 @@ class EncoderBlock(torch.nn.Module):
         return F.layer_norm(x, ln.normalized_shape, ln.weight.half(), ln.bias.half(), ln.eps)
 
     def forward(self, x):
+        a = self.attn
+        d = x.shape[-1] // a.heads
+        if (a.qkv_slot is not None and a.fused == "attention" and x.dtype == torch.float16 and d % 8 == 0 and d <= 128
+                and getattr(self.norm1, "slot", None) is not None):
+            x = _DirectAttentionBlock.apply(a.dev, x, a.qkv_slot, a.w_o.slot, self.norm1.slot, a.heads, self.norm1.eps)
+            return _DirectFeedForwardBlock.apply(a.dev, x, self.l1.slot, self.l2.slot, self.norm2.slot, self.norm2.eps)
         x = self._norm(self.norm1, x + self.attn(x))
         return self._norm(self.norm2, x + self.l2(self.l1(x, relu=True)))
 
