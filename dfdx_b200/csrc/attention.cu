@@ -6,7 +6,9 @@
 // .matmul(v)), which on the unfused path costs two batched GEMMs plus three elementwise passes over the
 // (batch, heads, S1, S2) score tensor.
 //
-// One CTA per (batch, head, 256 queries): two query tiles of 128 rows, each owned by one softmax warpgroup,
+// One work item per (batch, head, 256 queries), walked by a grid of at most one CTA per SM (item = blockIdx.x,
+// + gridDim.x, ...: every barrier keeps counting across items, so the next item's loads and first S = Q K^T run
+// under the current item's last exponentials and output): two query tiles of 128 rows, each owned by one softmax warpgroup,
 // share the key/value tiles (128 rows each) that stream through TMA rings.
 //   warpgroup 2  warp 8: TMA producer (both Q tiles once, then K_j and V_j); warps 9, 10, 11: MMA issuers (one
 //                thread each: all S_t = Q_t K_j^T (kind::f16, M=128, N=128); PV_0 = P_0 V_j; PV_1 = P_1 V_j with
@@ -32,7 +34,8 @@ using namespace attn;
 
 struct AttnArgs {
   int s1, s2, d;
-  int heads, q_pairs, kv_tiles;    // q_pairs: CTAs per (batch, head), each 256 queries
+  int heads, q_pairs, kv_tiles;    // q_pairs: work items per (batch, head), each 256 queries
+  long long items;                // batch * heads * q_pairs; CTA c takes items c, c + gridDim.x, ...
   float scale_log2;               // alpha * log2(e)
   __half* out;
   long long o_b, o_h, o_s;        // element strides of the (batch, head, query) axes; d has unit stride
@@ -75,7 +78,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
   constexpr bool TWO_PASS = DP == 128;
 
   extern __shared__ uint8_t smem_dyn[];
-  __shared__ __align__(8) uint64_t bar_q;
+  __shared__ __align__(8) uint64_t bar_q, bar_q_empty;
   __shared__ __align__(8) uint64_t bar_k_full[ST], bar_k_empty[ST], bar_v_full[ST], bar_v_empty[ST];
   // per query tile, one completion per key tile
   __shared__ __align__(8) uint64_t bar_s_full[2], bar_s_empty[2];
@@ -88,9 +91,12 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, wg = warp >> 2;
   volatile int* abortp = &abort_flag;
 
+  // query tiles that hold rows: the same for every item of this CTA (a grid smaller than the item count is only
+  // launched when all items have two)
   const int ntile0 = (((int)(blockIdx.x % g.q_pairs) * 2 + 1) * 128 < g.s1) ? 2 : 1;
   if (threadIdx.x == 0) {
     mbar_init(smem_u32(&bar_q), 1);
+    mbar_init(smem_u32(&bar_q_empty), 1);
     for (int s = 0; s < ST; ++s) {
       mbar_init(smem_u32(&bar_k_full[s]), 1);
       mbar_init(smem_u32(&bar_k_empty[s]), 1);
@@ -126,9 +132,6 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
   const uint32_t tmem_base = tmem_slot;
 
   // CTA -> (batch, head, pair of query tiles); the pairs of one head are neighbours so they share K / V in L2
-  const int qp = blockIdx.x % g.q_pairs;
-  const int bh = blockIdx.x / g.q_pairs;
-  const int ih = bh % g.heads, ib = bh / g.heads;
   const int T = g.kv_tiles;
   const int ntile = ntile0;                                 // query tiles of this CTA that hold rows
   const int ksteps_qk = (g.d + 15) / 16;                    // k-steps that hold data (the rest of DP is zero fill)
@@ -139,14 +142,22 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
       // ---------------------------------------------------------------- TMA producer
       if (lane == 0) {
         const uint32_t bq = smem_u32(&bar_q);
+        bool ok = true;
+        int it = 0;
+        for (long long item = blockIdx.x; ok && item < g.items; item += gridDim.x, ++it) {
+        const int qp = (int)(item % g.q_pairs);
+        const long long bh = item / g.q_pairs;
+        const int ih = (int)(bh % g.heads), ib = (int)(bh / g.heads);
+        // the Q tiles are free once the previous item's last S = Q K^T has been computed
+        if (it > 0 && !mbar_wait(smem_u32(&bar_q_empty), (uint32_t)(it - 1) & 1u, abortp, g.wait_limit)) break;
         mbar_expect_tx(bq, ntile * C::Q_BYTES);
         for (int t = 0; t < ntile; ++t)
           for (int c = 0; c < DCH; ++c)
             tma_load_4d(smem_base + t * C::Q_BYTES + c * 16384, &tma_q, bq, c * 64, (qp * 2 + t) * 128, ih, ib);
-        bool ok = true;
         for (int j = 0; ok && j < T; ++j) {
-          const int s = j % ST;
-          const uint32_t ph = (j / ST) & 1u;
+          const int jg = it * T + j;                           // tiles this CTA has streamed so far: ring position
+          const int s = jg % ST;
+          const uint32_t ph = (jg / ST) & 1u;
           if (!mbar_wait(smem_u32(&bar_k_empty[s]), ph ^ 1u, abortp, g.wait_limit)) { ok = false; break; }
           const uint32_t fk = smem_u32(&bar_k_full[s]);
           mbar_expect_tx(fk, C::KV_BYTES);
@@ -157,6 +168,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
           mbar_expect_tx(fv, C::KV_BYTES);
           for (int c = 0; c < DCH; ++c)
             tma_load_4d(smem_base + C::OFF_V + s * C::KV_BYTES + c * 16384, &tma_v, fv, c * 64, j * 128, ih, ib);
+        }
         }
       }
       __syncwarp();
@@ -174,14 +186,19 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
           // S = Q K^T: A and B K-major, N = 128
           const uint32_t idesc_qk = (1u << 4) | ((uint32_t)(128 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
           const uint32_t q_lo = (uint32_t)dk, k_lo = (uint32_t)dk + (uint32_t)(C::OFF_K >> 4);
-          bool ok = mbar_wait(smem_u32(&bar_q), 0, abortp, g.wait_limit);
-          // S_t(j): needs K_j and, for j > 0, the softmax warps of tile t to have read S_t(j-1)
+          bool ok = true;
+          int it = 0;
+          for (long long item = blockIdx.x; ok && item < g.items; item += gridDim.x, ++it) {
+          ok = mbar_wait(smem_u32(&bar_q), (uint32_t)it & 1u, abortp, g.wait_limit);
+          // S_t(j): needs K_j and the softmax warps of tile t to have read the S_t before it (the previous item's last
+          // one for j = 0)
           for (int j = 0; ok && j < T; ++j) {
-            const int s = j % ST;
-            if (!mbar_wait(smem_u32(&bar_k_full[s]), (j / ST) & 1u, abortp, g.wait_limit)) break;
+            const int jg = it * T + j;
+            const int s = jg % ST;
+            if (!mbar_wait(smem_u32(&bar_k_full[s]), (jg / ST) & 1u, abortp, g.wait_limit)) { ok = false; break; }
             const uint32_t klo = k_lo + (uint32_t)(s * (C::KV_BYTES >> 4));
             for (int t = 0; t < ntile; ++t) {
-              if (j > 0 && !mbar_wait(smem_u32(&bar_s_empty[t]), (uint32_t)(j - 1) & 1u, abortp, g.wait_limit)) { ok = false; break; }
+              if (jg > 0 && !mbar_wait(smem_u32(&bar_s_empty[t]), (uint32_t)(jg - 1) & 1u, abortp, g.wait_limit)) { ok = false; break; }
               tc_fence_after();
               const uint32_t alo = q_lo + (uint32_t)(t * C::Q_BYTES >> 4);
               if (ksteps_qk == DP / 16) {
@@ -200,20 +217,27 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
             }
             if (ok) umma_commit(smem_u32(&bar_k_empty[s]));
           }
+          if (ok) umma_commit(smem_u32(&bar_q_empty));       // all of this item's S MMAs have read Q
+          }
         } else if (warp - 10 < ntile) {
           // PV = P V: A K-major, B MN-major (V rows are keys), N = DP
           const int t = warp - 10;
           const uint32_t idesc_pv = (1u << 4) | (1u << 16) | ((uint32_t)(DP >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
           const uint32_t p_lo = (uint32_t)dk + (uint32_t)((C::OFF_P + t * P_STRIDE) >> 4);
           const uint32_t v_lo = (uint32_t)dv + (uint32_t)(C::OFF_V >> 4);
+          bool ok = true;
+          int it = 0;
+          for (long long item = blockIdx.x; ok && item < g.items; item += gridDim.x, ++it)
           for (int j = 0; j < T; ++j) {
-            const int s = j % ST;
-            // PV_t(j): needs V_j, P_t(j) and the softmax warps to have taken PV_t(j-1) out of tensor memory
-            if (!mbar_wait(smem_u32(&bar_v_full[s]), (j / ST) & 1u, abortp, g.wait_limit)) break;
-            const int b = j % NB;
-            const uint32_t bph = (uint32_t)(j / NB) & 1u;
-            if (j >= NB && !mbar_wait(smem_u32(&bar_o_empty[t][b]), bph ^ 1u, abortp, g.wait_limit)) break;
-            if (!mbar_wait(smem_u32(&bar_p_full[t][b]), bph, abortp, g.wait_limit)) break;
+            const int jg = it * T + j;
+            const int s = jg % ST;
+            // PV_t(j): needs V_j, P_t(j) and the softmax warps to have taken the PV_t that last used the buffer out of
+            // tensor memory
+            if (!mbar_wait(smem_u32(&bar_v_full[s]), (jg / ST) & 1u, abortp, g.wait_limit)) { ok = false; break; }
+            const int b = jg % NB;
+            const uint32_t bph = (uint32_t)(jg / NB) & 1u;
+            if (jg >= NB && !mbar_wait(smem_u32(&bar_o_empty[t][b]), bph ^ 1u, abortp, g.wait_limit)) { ok = false; break; }
+            if (!mbar_wait(smem_u32(&bar_p_full[t][b]), bph, abortp, g.wait_limit)) { ok = false; break; }
             const uint32_t plo = p_lo + (uint32_t)(b * (C::P_BYTES >> 4));
             tc_fence_after();
             const uint32_t vlo = v_lo + (uint32_t)(s * (C::KV_BYTES >> 4));
@@ -241,16 +265,22 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
       const uint32_t pb0 = smem_base + C::OFF_P + t * P_STRIDE + p_row;
       const float scale = g.scale_log2;
       const bool pos = scale >= 0.f;
+      bool ok = true;
+      int it = 0;
+      for (long long item = blockIdx.x; ok && item < g.items; item += gridDim.x, ++it) {
+      const int qp = (int)(item % g.q_pairs);
+      const long long bh = item / g.q_pairs;
+      const int ih = (int)(bh % g.heads), ib = (int)(bh / g.heads);
+      const int jg0 = it * T;                                // tiles this CTA has worked through before this item
       float acc[DP];
 #pragma unroll
       for (int q = 0; q < DP; ++q) acc[q] = 0.f;
       float m = -INFINITY, l = 0.f;                          // m in the scaled base-2 domain
-      bool ok = true;
 
       float corr = 1.f;                                      // factor that moves acc to the current maximum
-      auto add_pv = [&](int j) -> bool {                     // acc = acc * corr + PV_t(j)
-        const int b = j % NB;
-        if (!mbar_wait_warp(smem_u32(&bar_o_full[t][b]), (uint32_t)(j / NB) & 1u, abortp, g.wait_limit)) return false;
+      auto add_pv = [&](int jg) -> bool {                    // acc = acc * corr + PV_t(jg)
+        const int b = jg % NB;
+        if (!mbar_wait_warp(smem_u32(&bar_o_full[t][b]), (uint32_t)(jg / NB) & 1u, abortp, g.wait_limit)) return false;
         tc_fence_after();
 #pragma unroll
         for (int c = 0; c < DP / 32; ++c) {
@@ -266,7 +296,8 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
       };
 
       for (int j = 0; j < T; ++j) {
-        if (!mbar_wait_warp(smem_u32(&bar_s_full[t]), (uint32_t)j & 1u, abortp, g.wait_limit)) { ok = false; break; }
+        const int jg = jg0 + j;
+        if (!mbar_wait_warp(smem_u32(&bar_s_full[t]), (uint32_t)jg & 1u, abortp, g.wait_limit)) { ok = false; break; }
         tc_fence_after();
         const int valid = g.s2 - j * 128;                    // keys of this tile that exist
         const float gone = pos ? -INFINITY : INFINITY;       // a masked score: scaled it is -inf, probability 0
@@ -313,15 +344,15 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
         const float m_new = fmaxf(m, ext * scale);
         const float corr_new = ex2_approx(m - m_new);        // first tile: exp2(-inf) = 0, acc and l are 0
         // the P tile is free once PV(j-1) has been read by the tensor core
-        const int pbuf = j % NB;
-        if (j >= NB && !mbar_wait_warp(smem_u32(&bar_p_empty[t][pbuf]), ((uint32_t)(j / NB) & 1u) ^ 1u, abortp, g.wait_limit)) { ok = false; break; }
+        const int pbuf = jg % NB;
+        if (jg >= NB && !mbar_wait_warp(smem_u32(&bar_p_empty[t][pbuf]), ((uint32_t)(jg / NB) & 1u) ^ 1u, abortp, g.wait_limit)) { ok = false; break; }
         const uint32_t pb = pb0 + pbuf * C::P_BYTES;
         // (With single P / PV buffers, DP = 128, the turns would add to the tensor-core round trip instead.)
         // The two warpgroups take turns in the exponential phase: it saturates the SFU pipe, and in lockstep that
         // pipe would idle while both read scores / fold PV in.  Tile 0 goes first; tile 1 follows in the same j.
         if (NB == 2 && ntile == 2) {
-          const bool go = t == 0 ? (j == 0 || mbar_wait_warp(smem_u32(&bar_turn[1]), (uint32_t)(j - 1) & 1u, abortp, g.wait_limit))
-                                 : mbar_wait_warp(smem_u32(&bar_turn[0]), (uint32_t)j & 1u, abortp, g.wait_limit);
+          const bool go = t == 0 ? (jg == 0 || mbar_wait_warp(smem_u32(&bar_turn[1]), (uint32_t)(jg - 1) & 1u, abortp, g.wait_limit))
+                                 : mbar_wait_warp(smem_u32(&bar_turn[0]), (uint32_t)jg & 1u, abortp, g.wait_limit);
           if (!go) { ok = false; break; }
         }
         float s4[4] = {0.f, 0.f, 0.f, 0.f};
@@ -361,10 +392,10 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
         m = m_new;
         // PV(j-1) was issued a whole iteration ago: taking it out here (rather than before the exponentials)
         // keeps the tensor core's latency off this warpgroup's critical path
-        if (j > 0 && !add_pv(j - 1)) { ok = false; break; }
+        if (j > 0 && !add_pv(jg - 1)) { ok = false; break; }
         corr = corr_new;
       }
-      if (ok && T > 0) ok = add_pv(T - 1);
+      if (ok && T > 0) ok = add_pv(jg0 + T - 1);
       const int row = (qp * 2 + t) * 128 + r;
       if (ok && row < g.s1) {
         const float inv = 1.f / l;
@@ -381,6 +412,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tma_q, const __grid_con
           }
         }
         if (g.lse) g.lse[((long long)ib * g.heads + ih) * g.s1 + row] = (m + log2f(l)) * 0.6931471805599453f;
+      }
       }
     }
   }
@@ -433,8 +465,12 @@ int attention_forward(int dtype, int64_t B, int64_t H, int64_t s1, int64_t s2, i
     return B200_ERR_UNSUPPORTED;
   if (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)out) & 15) return B200_ERR_UNSUPPORTED;
   if (s1 > 0x7fffff00LL || s2 > 0x7fffff00LL || B * H > 0x7fffffffLL) return B200_ERR_LIMIT;
-  const int64_t q_pairs = (s1 + 255) / 256, ctas = q_pairs * H * B;
-  if (ctas > 0x7fffffffLL) return B200_ERR_LIMIT;
+  const int64_t q_pairs = (s1 + 255) / 256, items = q_pairs * H * B;
+  if (items > 0x7fffffffLL) return B200_ERR_LIMIT;
+  // One CTA per SM walks the items when every item has both of its query tiles (the barriers' arrival counts are set
+  // once per CTA); otherwise one CTA per item.
+  const bool uniform = s1 % 256 == 0 || s1 % 256 > 128;
+  const int64_t ctas = (uniform && items > ds->sm_count) ? ds->sm_count : items;
 
   alignas(64) CUtensorMap mq, mk, mv;
   int rc;
@@ -444,6 +480,7 @@ int attention_forward(int dtype, int64_t B, int64_t H, int64_t s1, int64_t s2, i
   AttnArgs g;
   g.s1 = (int)s1; g.s2 = (int)s2; g.d = (int)d;
   g.heads = (int)H; g.q_pairs = (int)q_pairs; g.kv_tiles = (int)((s2 + 127) / 128);
+  g.items = items;
   g.scale_log2 = (float)(alpha * 1.4426950408889634);
   if (g.scale_log2 == 0.f) g.scale_log2 = 1e-30f;           // keeps (masked score = -inf) * scale = -inf
   g.out = (__half*)out; g.o_b = os[0]; g.o_h = os[1]; g.o_s = os[2];
