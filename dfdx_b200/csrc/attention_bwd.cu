@@ -11,6 +11,10 @@
 //                                 of 64 rows with (+inf, 0): a padded row then has P = exp2(x - inf) = 0.
 //   attention_bwd_kernel<DP, 0>   dQ: one CTA per (b, h, 128 queries), streams key / value tiles of 64 rows.
 //   attention_bwd_kernel<DP, 1>   dK, dV: one CTA per (b, h, 128 keys), streams query / dO tiles of 64 rows.
+// Each is launched as at most one CTA per SM that walks its work items (item = blockIdx.x, + gridDim.x, ...): every
+// barrier keeps counting across items, so the next item's loads and first S' / dP' run under the current item's last
+// steps, and (DP = 64) its accumulators are written into the other half of tensor memory while the row threads still
+// turn the finished ones into gradients.
 // Both use one template: "rows" (128, resident in shared memory: R1, R2) against "columns" (64 per step, TMA
 // ring: C1, C2):
 //   mode 0: R1 = Q, R2 = dO, C1 = K_j, C2 = V_j      S' = R1 C1^T = S,    dP' = R2 C2^T = dP
@@ -32,6 +36,7 @@ using namespace attn;
 struct BwdArgs {
   int n_rows, n_cols, d;            // extent of the row / column axis (mode 0: s1, s2; mode 1: s2, s1)
   int heads, row_tiles, col_tiles;
+  long long items;                  // batch * heads * row_tiles; CTA c takes items c, c + gridDim.x, ...
   int aux_pad;                      // rows of aux per (b, h)
   float scale_log2, alpha;
   const float2* aux;
@@ -53,7 +58,8 @@ struct BwdCfg {
   static constexpr int SMEM_BYTES = OFF_A + (MODE == 1 ? 4 : 2) * A_BYTES + 1024;
   static constexpr int THREADS = 384;                      // 8 row warps, TMA warp, two MMA issuers, one idle warp
   static constexpr int TMEM_COLS = 512;
-  static constexpr uint32_t TM_S = 0, TM_DP = 128, TM_ACC1 = 256, TM_ACC2 = 256 + DP;
+  static constexpr int NACC = DP == 64 ? 2 : 1;            // accumulator sets (acc1, acc2) in tensor memory
+  static constexpr uint32_t TM_S = 0, TM_DP = 128, TM_ACC1 = 256, TM_ACC2 = 256 + DP, TM_ACC_STRIDE = 2 * DP;
 };
 
 // aux[(b*H + h) * pad + i] = (lse * log2 e, sum_d dO * O) for i < s1, (+inf, 0) for the padding rows.
@@ -104,7 +110,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tma_r1, const __grid_co
   constexpr int DCH = DP / 64;
 
   extern __shared__ uint8_t smem_dyn[];
-  __shared__ __align__(8) uint64_t bar_r, bar_acc;
+  __shared__ __align__(8) uint64_t bar_r, bar_r_empty, bar_acc_full[C::NACC], bar_acc_empty[C::NACC];
   __shared__ __align__(8) uint64_t bar_c_full[ST], bar_c_empty[ST];
   __shared__ __align__(8) uint64_t bar_sdp_full[2], bar_sdp_empty[2], bar_a_full[2], bar_a_empty[2];
   __shared__ uint32_t tmem_slot;
@@ -116,7 +122,11 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tma_r1, const __grid_co
 
   if (threadIdx.x == 0) {
     mbar_init(smem_u32(&bar_r), 1);
-    mbar_init(smem_u32(&bar_acc), 1);
+    mbar_init(smem_u32(&bar_r_empty), 2);                   // the S' and the dP' issuer
+    for (int a = 0; a < C::NACC; ++a) {
+      mbar_init(smem_u32(&bar_acc_full[a]), 1);
+      mbar_init(smem_u32(&bar_acc_empty[a]), 8);            // one arrival per row warp
+    }
     for (int s = 0; s < ST; ++s) {
       mbar_init(smem_u32(&bar_c_full[s]), 1);
       mbar_init(smem_u32(&bar_c_empty[s]), 1);
@@ -145,9 +155,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tma_r1, const __grid_co
   tc_fence_after();
   const uint32_t tmem_base = tmem_slot;
 
-  const int rt = blockIdx.x % g.row_tiles;
-  const int bh = blockIdx.x / g.row_tiles;
-  const int ih = bh % g.heads, ib = bh / g.heads;
+  constexpr int NACC = C::NACC;
   const int T = g.col_tiles;
   const int ksteps = (g.d + 15) / 16;                       // k-steps of S' / dP' that hold data
 
@@ -155,14 +163,23 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tma_r1, const __grid_co
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
       const uint32_t br = smem_u32(&bar_r);
+      bool ok = true;
+      int it = 0;
+      for (long long item = blockIdx.x; ok && item < g.items; item += gridDim.x, ++it) {
+      const int rt = (int)(item % g.row_tiles);
+      const long long bh = item / g.row_tiles;
+      const int ih = (int)(bh % g.heads), ib = (int)(bh / g.heads);
+      // the row operands are free once the previous item's last S' and dP' have been computed
+      if (it > 0 && !mbar_wait(smem_u32(&bar_r_empty), (uint32_t)(it - 1) & 1u, abortp, g.wait_limit)) break;
       mbar_expect_tx(br, 2 * C::R_BYTES);
       for (int c = 0; c < DCH; ++c) {
         tma_load_4d(smem_base + c * 16384, &tma_r1, br, c * 64, rt * 128, ih, ib);
         tma_load_4d(smem_base + C::R_BYTES + c * 16384, &tma_r2, br, c * 64, rt * 128, ih, ib);
       }
       for (int j = 0; j < T; ++j) {
-        const int s = j % ST;
-        if (!mbar_wait(smem_u32(&bar_c_empty[s]), (((uint32_t)(j / ST)) & 1u) ^ 1u, abortp, g.wait_limit)) break;
+        const int jg = it * T + j;                             // column tiles this CTA has streamed so far
+        const int s = jg % ST;
+        if (!mbar_wait(smem_u32(&bar_c_empty[s]), (((uint32_t)(jg / ST)) & 1u) ^ 1u, abortp, g.wait_limit)) { ok = false; break; }
         const uint32_t f = smem_u32(&bar_c_full[s]);
         mbar_expect_tx(f, 2 * C::C_BYTES);
         const uint32_t dst = smem_base + C::OFF_C + s * 2 * C::C_BYTES;
@@ -170,6 +187,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tma_r1, const __grid_co
           tma_load_4d(dst + c * 8192, &tma_c1, f, c * 64, j * 64, ih, ib);
           tma_load_4d(dst + C::C_BYTES + c * 8192, &tma_c2, f, c * 64, j * 64, ih, ib);
         }
+      }
       }
     }
     __syncwarp();
@@ -188,12 +206,16 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tma_r1, const __grid_co
         const bool second = warp == 11;                      // false: S' = R1 C1^T, true: dP' = R2 C2^T
         const uint32_t r_off = second ? (uint32_t)C::R_BYTES : 0u, c_off = second ? (uint32_t)C::C_BYTES : 0u;
         const uint32_t d_off = second ? C::TM_DP : C::TM_S;
-        bool ok = mbar_wait(smem_u32(&bar_r), 0, abortp, g.wait_limit);
-        // (j): needs column tile j and, for j >= 2, the row threads to have read buffer j & 1
+        bool ok = true;
+        int it = 0;
+        for (long long item = blockIdx.x; ok && item < g.items; item += gridDim.x, ++it) {
+        ok = mbar_wait(smem_u32(&bar_r), (uint32_t)it & 1u, abortp, g.wait_limit);
+        // (j): needs column tile j and the row threads to have read what buffer j & 1 held two steps before
         for (int j = 0; ok && j < T; ++j) {
-          const int s = j % ST, b = j & 1;
-          if (!mbar_wait(smem_u32(&bar_c_full[s]), ((uint32_t)(j / ST)) & 1u, abortp, g.wait_limit)) break;
-          if (j >= 2 && !mbar_wait(smem_u32(&bar_sdp_empty[b]), (((uint32_t)(j >> 1)) & 1u) ^ 1u, abortp, g.wait_limit)) break;
+          const int jg = it * T + j;
+          const int s = jg % ST, b = jg & 1;
+          if (!mbar_wait(smem_u32(&bar_c_full[s]), ((uint32_t)(jg / ST)) & 1u, abortp, g.wait_limit)) { ok = false; break; }
+          if (jg >= 2 && !mbar_wait(smem_u32(&bar_sdp_empty[b]), (((uint32_t)(jg >> 1)) & 1u) ^ 1u, abortp, g.wait_limit)) { ok = false; break; }
           tc_fence_after();
           const uint32_t c_lo = lo_k + (uint32_t)((C::OFF_C + s * 2 * C::C_BYTES) >> 4);
           for (int ks = 0; ks < ksteps; ++ks) {
@@ -203,29 +225,39 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tma_r1, const __grid_co
           }
           umma_commit(smem_u32(&bar_sdp_full[b]));
         }
+        if (ok) umma_commit(smem_u32(&bar_r_empty));         // this issuer's MMAs of the item have read the row operands
+        }
       } else {
         bool ok = true;
+        int it = 0;
+        for (long long item = blockIdx.x; ok && item < g.items; item += gridDim.x, ++it) {
+        const int ab = it % NACC;                            // accumulator set of this item
+        const uint32_t acc_off = (uint32_t)ab * C::TM_ACC_STRIDE;
+        // the set is free once the row threads have turned the item that last used it into gradients
+        if (it >= NACC && !mbar_wait(smem_u32(&bar_acc_empty[ab]), (((uint32_t)(it / NACC)) & 1u) ^ 1u, abortp, g.wait_limit)) { ok = false; break; }
         for (int j = 0; j < T; ++j) {
-          const int s = j % ST, b = j & 1;
-          if (!mbar_wait(smem_u32(&bar_c_full[s]), ((uint32_t)(j / ST)) & 1u, abortp, g.wait_limit)) { ok = false; break; }
-          if (!mbar_wait(smem_u32(&bar_a_full[b]), ((uint32_t)(j >> 1)) & 1u, abortp, g.wait_limit)) { ok = false; break; }
+          const int jg = it * T + j;
+          const int s = jg % ST, b = jg & 1;
+          if (!mbar_wait(smem_u32(&bar_c_full[s]), ((uint32_t)(jg / ST)) & 1u, abortp, g.wait_limit)) { ok = false; break; }
+          if (!mbar_wait(smem_u32(&bar_a_full[b]), ((uint32_t)(jg >> 1)) & 1u, abortp, g.wait_limit)) { ok = false; break; }
           tc_fence_after();
           const uint32_t a_lo = lo_k + (uint32_t)((C::OFF_A + b * C::A_BYTES) >> 4);
           const uint32_t c_lo = lo_m + (uint32_t)((C::OFF_C + s * 2 * C::C_BYTES) >> 4);
 #pragma unroll
           for (int ks = 0; ks < 4; ++ks)                      // 64 columns of S', 16 per MMA
-            umma_lohi<2>(tmem_base + C::TM_ACC1, a_lo + (uint32_t)(ks * 32 >> 4), hi_k, c_lo + (uint32_t)(ks * 2048 >> 4), hi_m,
+            umma_lohi<2>(tmem_base + C::TM_ACC1 + acc_off, a_lo + (uint32_t)(ks * 32 >> 4), hi_k, c_lo + (uint32_t)(ks * 2048 >> 4), hi_m,
                          idesc_acc, (j > 0 || ks > 0) ? 1u : 0u);
           if (MODE == 1) {
 #pragma unroll
             for (int ks = 0; ks < 4; ++ks)
-              umma_lohi<2>(tmem_base + C::TM_ACC2, a_lo + (uint32_t)((2 * C::A_BYTES + ks * 32) >> 4), hi_k,
+              umma_lohi<2>(tmem_base + C::TM_ACC2 + acc_off, a_lo + (uint32_t)((2 * C::A_BYTES + ks * 32) >> 4), hi_k,
                            c_lo + (uint32_t)((C::C_BYTES + ks * 2048) >> 4), hi_m, idesc_acc, (j > 0 || ks > 0) ? 1u : 0u);
           }
           umma_commit(smem_u32(&bar_a_empty[b]));
           umma_commit(smem_u32(&bar_c_empty[s]));
         }
-        if (ok) umma_commit(smem_u32(&bar_acc));
+        if (ok) umma_commit(smem_u32(&bar_acc_full[ab]));
+        }
       }
     }
     __syncwarp();
@@ -234,21 +266,27 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tma_r1, const __grid_co
     // warps w and w + 4 share the rows of TMEM lane quadrant w & 3 and split each step's 64 columns in halves
     const int quad = warp & 3, half = warp >> 2;
     const int r = quad * 32 + lane;                          // row inside the tile = TMEM lane
-    const int row = rt * 128 + r;
     const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
     const uint32_t a_row = (uint32_t)(r >> 3) * 1024 + (uint32_t)(r & 7) * 128;
     const uint32_t sw = (uint32_t)(r & 7);
     const float scale = g.scale_log2;
-    const float2* aux = g.aux + (long long)bh * g.aux_pad;
+    bool ok = true;
+    int it = 0;
+    for (long long item = blockIdx.x; ok && item < g.items; item += gridDim.x, ++it) {
+    const int rt = (int)(item % g.row_tiles);
+    const long long bh = item / g.row_tiles;
+    const int ih = (int)(bh % g.heads), ib = (int)(bh / g.heads);
+    const int row = rt * 128 + r;
+    const float2* aux = g.aux + bh * g.aux_pad;
     float row_l = 0.f, row_d = 0.f;
     if (MODE == 0) {                                         // per-row constants; rows beyond the extent are never stored
       const float2 a = aux[row < g.aux_pad ? row : g.aux_pad - 1];
       row_l = a.x; row_d = a.y;
     }
-    bool ok = true;
     for (int j = 0; j < T; ++j) {
-      const int b = j & 1;
-      const uint32_t ph = ((uint32_t)(j >> 1)) & 1u;
+      const int jg = it * T + j;
+      const int b = jg & 1;
+      const uint32_t ph = ((uint32_t)(jg >> 1)) & 1u;
       if (!mbar_wait_warp(smem_u32(&bar_sdp_full[b]), ph, abortp, g.wait_limit)) { ok = false; break; }
       tc_fence_after();
       uint32_t sv[32], dv[32];
@@ -258,7 +296,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tma_r1, const __grid_co
       tc_fence_before();
       warp_arrive(smem_u32(&bar_sdp_empty[b]), lane);
       // the operand buffers of this parity are free once the accumulator MMAs of step j-2 have read them
-      if (j >= 2 && !mbar_wait_warp(smem_u32(&bar_a_empty[b]), ph ^ 1u, abortp, g.wait_limit)) { ok = false; break; }
+      if (jg >= 2 && !mbar_wait_warp(smem_u32(&bar_a_empty[b]), ph ^ 1u, abortp, g.wait_limit)) { ok = false; break; }
       const uint32_t ds_dst = smem_base + C::OFF_A + b * C::A_BYTES + a_row;
       const int valid = g.n_cols - j * 64 - half * 32;       // columns of this thread's half that exist
       const float2* caux = aux + j * 64 + half * 32;         // mode 1: per-column constants (padded to 64)
@@ -295,7 +333,8 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tma_r1, const __grid_co
       warp_arrive(smem_u32(&bar_a_full[b]), lane);
     }
     // ---- accumulators -> gradients
-    if (ok) ok = mbar_wait_warp(smem_u32(&bar_acc), 0, abortp, g.wait_limit);
+    const int ab = it % NACC;
+    if (ok) ok = mbar_wait_warp(smem_u32(&bar_acc_full[ab]), ((uint32_t)(it / NACC)) & 1u, abortp, g.wait_limit);
     if (ok) {
       tc_fence_after();
       const bool store = row < g.n_rows;                     // only the global accesses are per-lane
@@ -304,7 +343,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tma_r1, const __grid_co
         __half* dst = which == 0 ? g.out1 + ib * g.o1_b + ih * g.o1_h + (long long)row * g.o1_r
                                  : g.out2 + ib * g.o2_b + ih * g.o2_h + (long long)row * g.o2_r;
         const float mul = which == 0 ? g.alpha : 1.f;         // dQ and dK carry the score scale, dV does not
-        const uint32_t tm = which == 0 ? C::TM_ACC1 : C::TM_ACC2;
+        const uint32_t tm = (which == 0 ? C::TM_ACC1 : C::TM_ACC2) + (uint32_t)ab * C::TM_ACC_STRIDE;
         constexpr int CPH = DP / 64;                          // 32-column chunks per half
 #pragma unroll
         for (int cc = 0; cc < CPH; ++cc) {                    // each half stores half of the columns
@@ -344,6 +383,9 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tma_r1, const __grid_co
           }
         }
       }
+      tc_fence_before();
+      warp_arrive(smem_u32(&bar_acc_empty[ab]), lane);       // this warp has read its part of the accumulator set
+    }
     }
   }
 
@@ -448,8 +490,9 @@ int attention_backward(int dtype, int64_t B, int64_t H, int64_t s1, int64_t s2, 
     g.out1 = (__half*)gq; g.o1_b = gqs[0]; g.o1_h = gqs[1]; g.o1_r = gqs[2];
     g.out2 = nullptr; g.o2_b = g.o2_h = g.o2_r = 0;
     g.wait_limit = 400000000LL + (long long)g.col_tiles * 400000LL;
-    rc = d <= 64 ? launch_bwd<64, 0>(mq128, mg128, mk64, mv64, g, q_tiles * H * B, stream)
-                 : launch_bwd<128, 0>(mq128, mg128, mk64, mv64, g, q_tiles * H * B, stream);
+    g.items = q_tiles * H * B;
+    rc = d <= 64 ? launch_bwd<64, 0>(mq128, mg128, mk64, mv64, g, g.items < ds->sm_count ? g.items : ds->sm_count, stream)
+                 : launch_bwd<128, 0>(mq128, mg128, mk64, mv64, g, g.items < ds->sm_count ? g.items : ds->sm_count, stream);
     if (rc) return rc;
   }
   // 3. dK, dV: rows = keys, columns = queries
@@ -459,8 +502,9 @@ int attention_backward(int dtype, int64_t B, int64_t H, int64_t s1, int64_t s2, 
     g.out1 = (__half*)gk; g.o1_b = gks[0]; g.o1_h = gks[1]; g.o1_r = gks[3];
     g.out2 = (__half*)gv; g.o2_b = gvs[0]; g.o2_h = gvs[1]; g.o2_r = gvs[2];
     g.wait_limit = 400000000LL + (long long)g.col_tiles * 400000LL;
-    rc = d <= 64 ? launch_bwd<64, 1>(mk128, mv128, mq64, mg64, g, k_tiles * H * B, stream)
-                 : launch_bwd<128, 1>(mk128, mv128, mq64, mg64, g, k_tiles * H * B, stream);
+    g.items = k_tiles * H * B;
+    rc = d <= 64 ? launch_bwd<64, 1>(mk128, mv128, mq64, mg64, g, g.items < ds->sm_count ? g.items : ds->sm_count, stream)
+                 : launch_bwd<128, 1>(mk128, mv128, mq64, mg64, g, g.items < ds->sm_count ? g.items : ds->sm_count, stream);
     if (rc) return rc;
   }
   return B200_OK;
