@@ -19,9 +19,11 @@
 // ring: C1, C2):
 //   mode 0: R1 = Q, R2 = dO, C1 = K_j, C2 = V_j      S' = R1 C1^T = S,    dP' = R2 C2^T = dP
 //   mode 1: R1 = K, R2 = V,  C1 = Q_i, C2 = dO_i     S' = R1 C1^T = S^T,  dP' = R2 C2^T = dP^T
-// Warp 8 = TMA producer, warps 9 and 10 = MMA issuers (S', dP' into double-buffered TMEM; accumulators acc1 += dS' C1
-// and, mode 1, acc2 += P' C2 stay in TMEM over the whole loop), warps 0..7 = two threads per row (each takes half of
-// a step's 64 columns; no reduction across a row is needed in the backward pass): read S' and dP' from TMEM, P' = exp2(s * scale - L), dS' = P' (dP' - Dl), write dS' (and P') as f16 MMA operands into shared memory.
+// Warps 0..15 = four threads per row (each takes a quarter of a step's 64 columns; no reduction across a row is needed
+// in the backward pass): read S' and dP' from TMEM, P' = exp2(s * scale - L), dS' = P' (dP' - Dl), write dS' (and P') as
+// f16 MMA operands into shared memory.  Warp 16 = TMA producer, warps 17, 18, 19 = MMA issuers (S', the accumulators,
+// dP'; S' and dP' into double-buffered TMEM; accumulators acc1 += dS' C1 and, mode 1, acc2 += P' C2 stay in TMEM over
+// an item's loop).
 // The same shared-memory image of a column tile serves as the K-major B operand of S' / dP' and as the MN-major
 // B operand of the accumulator MMAs.  Every wait is bounded (abort flag, device status word).
 #include "attention_common.cuh"
@@ -56,7 +58,10 @@ struct BwdCfg {
   static constexpr int OFF_C = 2 * R_BYTES;
   static constexpr int OFF_A = OFF_C + ST * 2 * C_BYTES;   // dS'[0], dS'[1], then (mode 1) P'[0], P'[1]
   static constexpr int SMEM_BYTES = OFF_A + (MODE == 1 ? 4 : 2) * A_BYTES + 1024;
-  static constexpr int THREADS = 384;                      // 8 row warps, TMA warp, two MMA issuers, one idle warp
+  static constexpr int ROW_WARPS = 16;                     // four threads per row: the row threads' chains of waits, tensor-memory
+                                                           // loads and exponentials are latency-bound, so warps per scheduler count
+  static constexpr int W_TMA = ROW_WARPS, W_S = ROW_WARPS + 1, W_ACC = ROW_WARPS + 2, W_DP = ROW_WARPS + 3;
+  static constexpr int THREADS = (ROW_WARPS + 4) * 32;     // row warps, TMA warp, three MMA issuers
   static constexpr int TMEM_COLS = 512;
   static constexpr int NACC = DP == 64 ? 2 : 1;            // accumulator sets (acc1, acc2) in tensor memory
   static constexpr uint32_t TM_S = 0, TM_DP = 128, TM_ACC1 = 256, TM_ACC2 = 256 + DP, TM_ACC_STRIDE = 2 * DP;
@@ -125,7 +130,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tma_r1, const __grid_co
     mbar_init(smem_u32(&bar_r_empty), 2);                   // the S' and the dP' issuer
     for (int a = 0; a < C::NACC; ++a) {
       mbar_init(smem_u32(&bar_acc_full[a]), 1);
-      mbar_init(smem_u32(&bar_acc_empty[a]), 8);            // one arrival per row warp
+      mbar_init(smem_u32(&bar_acc_empty[a]), C::ROW_WARPS); // one arrival per row warp
     }
     for (int s = 0; s < ST; ++s) {
       mbar_init(smem_u32(&bar_c_full[s]), 1);
@@ -133,18 +138,18 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tma_r1, const __grid_co
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(smem_u32(&bar_sdp_full[b]), 2);             // S' and dP' are committed by different issuers
-      mbar_init(smem_u32(&bar_sdp_empty[b]), 8);            // one arrival per row warp
-      mbar_init(smem_u32(&bar_a_full[b]), 8);
+      mbar_init(smem_u32(&bar_sdp_empty[b]), C::ROW_WARPS); // one arrival per row warp
+      mbar_init(smem_u32(&bar_a_full[b]), C::ROW_WARPS);
       mbar_init(smem_u32(&bar_a_empty[b]), 1);
     }
     abort_flag = 0;
     fence_mbar_init();
   }
-  if (warp == 9) {
+  if (warp == C::W_S) {
     tmem_alloc(smem_u32(&tmem_slot), C::TMEM_COLS);
     tmem_relinquish();
   }
-  if (warp == 8 && lane == 0) {
+  if (warp == C::W_TMA && lane == 0) {
     tma_prefetch_desc(&tma_r1);
     tma_prefetch_desc(&tma_r2);
     tma_prefetch_desc(&tma_c1);
@@ -159,7 +164,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tma_r1, const __grid_co
   const int T = g.col_tiles;
   const int ksteps = (g.d + 15) / 16;                       // k-steps of S' / dP' that hold data
 
-  if (warp == 8) {
+  if (warp == C::W_TMA) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
       const uint32_t br = smem_u32(&bar_r);
@@ -191,9 +196,9 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tma_r1, const __grid_co
       }
     }
     __syncwarp();
-  } else if (warp >= 9) {
+  } else if (warp > C::W_TMA) {
     // ------------------------------------------------------------------ MMA issuers
-    // warp 9 issues S', warp 11 dP', warp 10 the accumulator MMAs: three short instruction streams instead of one
+    // one warp issues S', one dP', one the accumulator MMAs: three short instruction streams instead of one
     // long one (each wait, MMA and commit of the issuing thread is a serial, long-latency step).
     if (lane == 0) {
       const uint32_t idesc_s = (1u << 4) | ((uint32_t)(64 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);             // N = 64
@@ -202,8 +207,8 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tma_r1, const __grid_co
       const uint64_t dm = make_smem_desc(smem_base, 8192, 1024, 2);            // MN-major column tile (d-chunk stride 8192)
       const uint32_t hi_k = (uint32_t)(dk >> 32), hi_m = (uint32_t)(dm >> 32);
       const uint32_t lo_k = (uint32_t)dk, lo_m = (uint32_t)dm;
-      if (warp == 9 || warp == 11) {
-        const bool second = warp == 11;                      // false: S' = R1 C1^T, true: dP' = R2 C2^T
+      if (warp == C::W_S || warp == C::W_DP) {
+        const bool second = warp == C::W_DP;                      // false: S' = R1 C1^T, true: dP' = R2 C2^T
         const uint32_t r_off = second ? (uint32_t)C::R_BYTES : 0u, c_off = second ? (uint32_t)C::C_BYTES : 0u;
         const uint32_t d_off = second ? C::TM_DP : C::TM_S;
         bool ok = true;
@@ -261,10 +266,12 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tma_r1, const __grid_co
       }
     }
     __syncwarp();
-  } else if (warp < 8) {
-    // ------------------------------------------------------------------ row threads (warps 0..7)
-    // warps w and w + 4 share the rows of TMEM lane quadrant w & 3 and split each step's 64 columns in halves
-    const int quad = warp & 3, half = warp >> 2;
+  } else {
+    // ------------------------------------------------------------------ row threads (warps 0..15)
+    // warps w, w + 4, w + 8, w + 12 share the rows of TMEM lane quadrant w & 3 and split each step's 64 columns in
+    // quarters
+    constexpr int CW = 64 / (C::ROW_WARPS / 4);              // columns of a step per thread: 16
+    const int quad = warp & 3, part = warp >> 2;
     const int r = quad * 32 + lane;                          // row inside the tile = TMEM lane
     const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
     const uint32_t a_row = (uint32_t)(r >> 3) * 1024 + (uint32_t)(r & 7) * 128;
@@ -287,27 +294,33 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tma_r1, const __grid_co
       const int jg = it * T + j;
       const int b = jg & 1;
       const uint32_t ph = ((uint32_t)(jg >> 1)) & 1u;
+      // mode 1: per-column constants (padded to 64), requested before the wait so that they are there after it
+      float4 cl[CW / 2];
+      if (MODE == 1) {
+        const float2* caux = aux + j * 64 + part * CW;
+#pragma unroll
+        for (int e = 0; e < CW / 2; ++e) cl[e] = __ldg(reinterpret_cast<const float4*>(caux + 2 * e));
+      }
       if (!mbar_wait_warp(smem_u32(&bar_sdp_full[b]), ph, abortp, g.wait_limit)) { ok = false; break; }
       tc_fence_after();
-      uint32_t sv[32], dv[32];
-      tmem_ld_32x32(lane_addr + C::TM_S + b * 64 + half * 32, sv);
-      tmem_ld_32x32(lane_addr + C::TM_DP + b * 64 + half * 32, dv);
+      uint32_t sv[CW], dv[CW];
+      tmem_ld_32x16(lane_addr + C::TM_S + b * 64 + part * CW, sv);
+      tmem_ld_32x16(lane_addr + C::TM_DP + b * 64 + part * CW, dv);
       tmem_wait_ld();
       tc_fence_before();
       warp_arrive(smem_u32(&bar_sdp_empty[b]), lane);
       // the operand buffers of this parity are free once the accumulator MMAs of step j-2 have read them
       if (jg >= 2 && !mbar_wait_warp(smem_u32(&bar_a_empty[b]), ph ^ 1u, abortp, g.wait_limit)) { ok = false; break; }
       const uint32_t ds_dst = smem_base + C::OFF_A + b * C::A_BYTES + a_row;
-      const int valid = g.n_cols - j * 64 - half * 32;       // columns of this thread's half that exist
-      const float2* caux = aux + j * 64 + half * 32;         // mode 1: per-column constants (padded to 64)
+      const int valid = g.n_cols - j * 64 - part * CW;       // columns of this thread's part that exist
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {                          // 16-byte chunks of 8 columns
+      for (int c = 0; c < CW / 8; ++c) {                     // 16-byte chunks of 8 columns
         float pv[8], dsv[8];
 #pragma unroll
         for (int e = 0; e < 8; e += 2) {
           float l0, d0, l1, d1;
           if (MODE == 1) {
-            const float4 a = __ldg(reinterpret_cast<const float4*>(caux + c * 8 + e));
+            const float4 a = cl[(c * 8 + e) / 2];
             l0 = a.x; d0 = a.y; l1 = a.z; d1 = a.w;
           } else {
             l0 = l1 = row_l; d0 = d1 = row_d;
@@ -322,7 +335,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tma_r1, const __grid_co
           dsv[e] = p0 * (__uint_as_float(dv[c * 8 + e]) - d0);
           dsv[e + 1] = p1 * (__uint_as_float(dv[c * 8 + e + 1]) - d1);
         }
-        const uint32_t off = (((uint32_t)(half * 4 + c) ^ sw) << 4);
+        const uint32_t off = (((uint32_t)(part * (CW / 8) + c) ^ sw) << 4);
         st_shared_v4(ds_dst + off, pack_half2(dsv[0], dsv[1]), pack_half2(dsv[2], dsv[3]), pack_half2(dsv[4], dsv[5]),
                      pack_half2(dsv[6], dsv[7]));
         if (MODE == 1)
@@ -332,54 +345,52 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tma_r1, const __grid_co
       fence_proxy_async_smem();
       warp_arrive(smem_u32(&bar_a_full[b]), lane);
     }
-    // ---- accumulators -> gradients
+    // ---- accumulators -> gradients: each of a row's four threads stores a quarter of the columns
     const int ab = it % NACC;
     if (ok) ok = mbar_wait_warp(smem_u32(&bar_acc_full[ab]), ((uint32_t)(it / NACC)) & 1u, abortp, g.wait_limit);
     if (ok) {
       tc_fence_after();
       const bool store = row < g.n_rows;                     // only the global accesses are per-lane
+      constexpr int CP = DP / (C::ROW_WARPS / 4);            // columns per thread: 16 (DP = 64) or 32
 #pragma unroll
       for (int which = 0; which < (MODE == 1 ? 2 : 1); ++which) {
         __half* dst = which == 0 ? g.out1 + ib * g.o1_b + ih * g.o1_h + (long long)row * g.o1_r
                                  : g.out2 + ib * g.o2_b + ih * g.o2_h + (long long)row * g.o2_r;
         const float mul = which == 0 ? g.alpha : 1.f;         // dQ and dK carry the score scale, dV does not
         const uint32_t tm = (which == 0 ? C::TM_ACC1 : C::TM_ACC2) + (uint32_t)ab * C::TM_ACC_STRIDE;
-        constexpr int CPH = DP / 64;                          // 32-column chunks per half
+        const int c0 = part * CP;
+        uint32_t v[CP];
+        if constexpr (CP == 16) tmem_ld_32x16(lane_addr + tm + c0, v);
+        else tmem_ld_32x32(lane_addr + tm + c0, v);
+        // what the gradient buffer holds: all 16-byte pieces are requested before any is used, so the row-strided
+        // (uncoalesced) reads overlap instead of costing one memory round trip each
+        uint4 old[CP / 8];
+        if (g.accumulate) {
 #pragma unroll
-        for (int cc = 0; cc < CPH; ++cc) {                    // each half stores half of the columns
-          const int c = half * CPH + cc;
-          uint32_t v[32];
-          tmem_ld_32x32(lane_addr + tm + c * 32, v);
-          // what the gradient buffer holds: all four 16-byte pieces are requested before any is used, so the
-          // row-strided (uncoalesced) reads overlap instead of costing one memory round trip each
-          uint4 old[4];
-          if (g.accumulate) {
+          for (int q8 = 0; q8 < CP / 8; ++q8)
+            old[q8] = (store && c0 + q8 * 8 < g.d) ? *reinterpret_cast<const uint4*>(dst + c0 + q8 * 8)
+                                                   : make_uint4(0u, 0u, 0u, 0u);
+        }
+        tmem_wait_ld();
 #pragma unroll
-            for (int q8 = 0; q8 < 4; ++q8)
-              old[q8] = (store && c * 32 + q8 * 8 < g.d) ? *reinterpret_cast<const uint4*>(dst + c * 32 + q8 * 8)
-                                                         : make_uint4(0u, 0u, 0u, 0u);
-          }
-          tmem_wait_ld();
+        for (int q8 = 0; q8 < CP / 8; ++q8) {
+          const int col = c0 + q8 * 8;
+          if (store && col < g.d) {                          // d is a multiple of 8
+            float f[8];
 #pragma unroll
-          for (int q8 = 0; q8 < 4; ++q8) {
-            const int col = c * 32 + q8 * 8;
-            if (store && col < g.d) {                        // d is a multiple of 8
-              float f[8];
+            for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(v[q8 * 8 + e]) * mul;
+            if (g.accumulate) {
+              const __half2* ho = reinterpret_cast<const __half2*>(&old[q8]);
 #pragma unroll
-              for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(v[q8 * 8 + e]) * mul;
-              if (g.accumulate) {
-                const __half2* ho = reinterpret_cast<const __half2*>(&old[q8]);
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                  const float2 fo = __half22float2(ho[e]);
-                  f[2 * e] += fo.x; f[2 * e + 1] += fo.y;
-                }
+              for (int e = 0; e < 4; ++e) {
+                const float2 fo = __half22float2(ho[e]);
+                f[2 * e] += fo.x; f[2 * e + 1] += fo.y;
               }
-              uint4 o;
-              o.x = pack_half2(f[0], f[1]); o.y = pack_half2(f[2], f[3]);
-              o.z = pack_half2(f[4], f[5]); o.w = pack_half2(f[6], f[7]);
-              *reinterpret_cast<uint4*>(dst + col) = o;
             }
+            uint4 o;
+            o.x = pack_half2(f[0], f[1]); o.y = pack_half2(f[2], f[3]);
+            o.z = pack_half2(f[4], f[5]); o.w = pack_half2(f[6], f[7]);
+            *reinterpret_cast<uint4*>(dst + col) = o;
           }
         }
       }
@@ -392,7 +403,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tma_r1, const __grid_co
   tc_fence_before();
   __syncthreads();
   teardown(abort_flag, g.status);
-  if (warp == 9) {
+  if (warp == C::W_S) {
     tc_fence_after();
     tmem_dealloc(tmem_base, C::TMEM_COLS);
   }
