@@ -119,6 +119,40 @@ def test_attention_backward(cuda_dev, oracle, shape):
     assert cuda_dev.device_status() == 0
 
 
+@pytest.mark.parametrize("shape", [(40, 8, 256, 256, 64), (20, 8, 200, 264, 128), (30, 6, 300, 136, 64)],
+                         ids=lambda s: "x".join(map(str, s)))
+def test_attention_many_work_items_per_cta(cuda_dev, oracle, shape):
+    """More work items than SMs: each CTA of the forward and of both backward kernels walks several (batch, head,
+    row tile) items, its barriers, shared-memory rings and tensor-memory buffers counting on across them (d <= 64:
+    the backward's double-buffered accumulator sets; d = 128: one set; s1 = 300: the forward's one-CTA-per-item
+    launch, because the last pair of query tiles of a head holds one tile only)."""
+    b, h, s1, s2, d = shape
+    dev = cuda_dev
+    sms = torch.cuda.get_device_properties(dev.device).multi_processor_count
+    assert b * h * ((s2 + 127) // 128) > sms and b * h * ((s1 + 127) // 128) > sms
+    g = gen(2000 + sum(shape))
+    q, k, v = mha_views(b, h, s1, s2, d, g, dev.device)
+    alpha = 1.0 / math.sqrt(d)
+    out, lse = dev.attention_forward(q, k, v, alpha, want_lse=True)
+    go = torch.randn(b, s1, h, d, generator=g, dtype=torch.float64).half().to(dev.device).permute(0, 2, 1, 3)
+    gq, gk, gv = dev.attention_backward(q, k, v, alpha, out, lse, go)
+    dev.synchronize()
+    want, want_lse = oracle.attention(q.cpu(), k.cpu(), v.cpu(), alpha)
+    assert oracle.rel_frobenius(out, want) <= FROB_TOL[torch.float16]
+    assert float((lse.cpu().double() - want_lse).abs().max()) <= 2e-3
+    wq, wk, wv = oracle.attention_backward(q.cpu(), k.cpu(), v.cpu(), alpha, go.cpu())
+    for name, got, ref in (("dQ", gq, wq), ("dK", gk, wk), ("dV", gv, wv)):
+        err = oracle.rel_frobenius(got, ref)
+        assert err <= 2 * FROB_TOL[torch.float16], f"{name}: rel frobenius {err:.3e}"
+    # every item separately: the per-(batch, head) errors, not only the norm over all of them
+    per_item = (out.float().cpu() - want.float()).flatten(2).norm(dim=2) / want.float().flatten(2).norm(dim=2)
+    assert float(per_item.max()) <= 2 * FROB_TOL[torch.float16]
+    per_item = (gk.float().cpu() - wk.float()).permute(0, 1, 3, 2).flatten(2).norm(dim=2) / \
+        wk.float().permute(0, 1, 3, 2).flatten(2).norm(dim=2)
+    assert float(per_item.max()) <= 4 * FROB_TOL[torch.float16]
+    assert dev.device_status() == 0
+
+
 def test_attention_backward_accumulates(cuda_dev, oracle):
     """accumulate = 1 adds to what the gradient buffers hold (two calls give twice the gradient)."""
     g = gen(77)
