@@ -548,7 +548,8 @@ def run_transformer(h, args, steps, warmup):
         "parameters": sum(p.numel() for p in trainer.model.parameters()),
         "parallelism": f"dp{h.world}: one NCCL all-reduce of the flat f32 gradient buffer per step, inside the step's CUDA graph",
         "matmuls": "all on libdfdx_b200 (MatMatBr + MatMatBatch4, forward and backward); w_q, w_k and w_v, stored next "
-                   "to each other, run as one (model -> 3 * model) MatMatBr each way; residual adds, casts, "
+                   "to each other, run as one (model -> 3 * model) MatMatBr each way; weight gradients are added in f32 "
+                   "into the f32 gradient buffer (b200_matmat_br_grad_rhs_f32); casts, "
                    "loss and Adam are torch ops (separate non-matmul kernels in dfdx too)",
         "rowwise": "torch LayerNorm / sum" if args.unfused_epilogues else
                    "LayerNorm forward + backward and the bias gradients on libdfdx_b200",

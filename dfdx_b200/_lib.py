@@ -73,6 +73,7 @@ SIGNATURES = {
     "b200_matmat_br_forward": (_i, [_i, _sz, _sz, _sz, _sz, _vp, _szp, _vp, _szp, _vp, _vp]),
     "b200_matmat_br_backward": (_i, [_i, _sz, _sz, _sz, _sz, _vp, _szp, _vp, _vp, _szp, _vp, _vp, _vp, _vp]),
     "b200_matmat_br_backward_overwrite": (_i, [_i, _sz, _sz, _sz, _sz, _vp, _szp, _vp, _vp, _szp, _vp, _vp, _vp]),
+    "b200_matmat_br_grad_rhs_f32": (_i, [_i, _sz, _sz, _sz, _sz, _vp, _szp, _vp, _vp, _szp, _vp]),
     "b200_matmat_batch3_forward": (_i, [_i, _sz, _sz, _sz, _sz, _vp, _szp, _vp, _szp, _vp, _vp]),
     "b200_matmat_batch3_backward": (_i, [_i, _sz, _sz, _sz, _sz, _vp, _szp, _vp, _vp, _szp, _vp, _vp, _vp, _vp]),
     "b200_matmat_batch4_forward": (_i, [_i, _sz, _sz, _sz, _sz, _sz, _vp, _szp, _vp, _szp, _vp, _vp]),

@@ -370,6 +370,24 @@ int b200_matmat_br_backward(int dtype, size_t batch, size_t m, size_t k, size_t 
                                  lhs_stream_of(stream, par_stream), 1);
 }
 
+int b200_matmat_br_grad_rhs_f32(int dtype, size_t batch, size_t m, size_t k, size_t n, const void* lhs, const size_t ls[3],
+                                const void* grad_out, float* grad_rhs, const size_t gs[2], void* stream) {
+  if (!valid_dtype(dtype)) return B200_ERR_DTYPE;
+  if (dtype != B200_F16 && dtype != B200_AMP_F16) return B200_ERR_UNSUPPORTED;
+  if (!ls || !gs) return B200_ERR_NULL;
+  if (!matrix_strides_ok(ls + 1) || !matrix_strides_ok(gs)) return B200_ERR_STRIDE;
+  if (batch == 0 || m == 0 || k == 0 || n == 0) return B200_OK;
+  if (!lhs || !grad_out || !grad_rhs) return B200_ERR_NULL;
+  if ((k > 1 && gs[0] == 0) || (n > 1 && gs[1] == 0)) return B200_ERR_STRIDE;   // every element owns its storage
+  if (!device_state()) return note_cuda_error(cudaErrorInitializationError, "b200_init not called on this device");
+  GemmProblem p;
+  p.dtype = dtype; p.beta = 1; p.acc32 = true; p.red = batch; p.m = k; p.k = m; p.n = n;
+  p.a = lhs; p.a_red = ls[0]; p.a_r = ls[2]; p.a_c = ls[1];
+  p.b = grad_out; p.b_red = m * n; p.b_r = n; p.b_c = 1;
+  p.c = grad_rhs; p.c_r = gs[0]; p.c_c = gs[1];
+  return launch_gemm_tc_acc32(p, (cudaStream_t)stream);
+}
+
 int b200_matmat_br_backward_overwrite(int dtype, size_t batch, size_t m, size_t k, size_t n, const void* lhs,
                                       const size_t ls[3], void* grad_lhs, const void* rhs, const size_t rs[2],
                                       void* grad_rhs, const void* grad_out, void* stream) {

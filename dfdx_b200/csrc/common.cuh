@@ -32,6 +32,9 @@ struct GemmProblem {
   int bias_dim = 0;
   int act = B200_ACT_NONE;
   bool fused() const { return alpha != 1.0 || bias != nullptr || act != B200_ACT_NONE; }
+  // f16 problems only: `c` is an f32 matrix (strides in f32 elements) that the f32 accumulator is ADDED to, without a
+  // rounding to f16 in between (a mixed-precision trainer's f32 gradient of an f16 weight).  Tensor-core path only.
+  bool acc32 = false;
 };
 
 static inline size_t dtype_size(int dtype) {
@@ -66,6 +69,8 @@ void count_launch(bool tensor);
 int launch_gemm_simt(const GemmProblem& p, cudaStream_t stream);
 // Returns B200_ERR_UNSUPPORTED (without launching) when the operands are not TMA-addressable.
 int launch_gemm_tc(const GemmProblem& p, cudaStream_t stream);
+// GemmProblem::acc32 (f16 operands added in f32 to an f32 C); B200_ERR_UNSUPPORTED without a launch otherwise.
+int launch_gemm_tc_acc32(const GemmProblem& p, cudaStream_t stream);
 bool tc_eligible(const GemmProblem& p);
 int tc_setup_device();                       // cudaFuncSetAttribute for every tensor-core kernel
 

@@ -426,7 +426,7 @@ gemm_f16_big_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
       const int row = row0 + ew * 32 + lane;
       // the tile's column bias, fetched before the accumulators are waited for; the group's barriers below order
       // these writes before the reads and the reads before the next tile's writes
-      const bool bias_cols = g.fused && !g.bias_row && g.ksplit == 1;
+      const bool bias_cols = g.fused && !g.bias_row && g.ksplit == 1 && !g.acc32;
       if (bias_cols) {
 #pragma unroll
         for (int jj = 0; jj < 2; ++jj) {
@@ -444,8 +444,9 @@ gemm_f16_big_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_cons
       const int r_in = ew * 32 + lane;
       const uint32_t sw = (uint32_t)(r_in & 7);
       const uint32_t stage = smem_base + C::OFF_OUT + (uint32_t)eg * C::OUT_BYTES;
-      if (g.ksplit > 1 && row0 < g.m) {
-        // K slice: the f32 partial sums are added into the device's scratch matrix (tma_c maps it here), 32 columns
+      if ((g.ksplit > 1 || g.acc32) && row0 < g.m) {
+        // K slice, or an f32 destination: the f32 sums are added into the device's scratch matrix / into C (tma_c maps
+        // it here), 32 columns
         // = one 128-byte line per row at a time through the same staging buffer
 #pragma unroll 1
         for (int c4 = 0; c4 < BN / 32; ++c4) {
@@ -1199,6 +1200,7 @@ int build_launch(Launch& L, const Plan& pl, int esize, int tm, int tn, int bmc, 
   }
   g.beta = p.beta;
   g.fused = p.fused() ? 1 : 0; g.alpha = (float)p.alpha; g.bias = p.bias; g.bias_row = p.bias_dim ? 1 : 0; g.act = p.act;
+  g.acc32 = 0;
   g.xform_mode = g_xform_mode;
   g.tile_cols = tn; g.tile_valid = tn; g.mma_n = tn; g.b_tx_bytes = 0;
   g.cv_cblocks = 1; g.cv_cpad = 16; g.cv_kw = 1; g.cv_taps = 1; g.cv_w0 = g.cv_dw = g.cv_h0 = g.cv_dh = 0;
@@ -1421,6 +1423,46 @@ int launch_big_f16(const Plan& pl, cudaStream_t stream, int ksplit) {
   return note_cuda_error(cudaGetLastError(), "tensor-core gemm launch (256 x 256 tiles)");
 }
 
+// f16 operands, f32 destination that is added to (GemmProblem::acc32): 256 x 256 tiles whose accumulators leave as
+// bulk reduce-adds into C itself, whole-K tiles or K slices alike -- no scratch, no zero fill, no second kernel.
+int launch_big_f16_acc32(const Plan& pl, cudaStream_t stream) {
+  const GemmProblem& p = pl.p;
+  if (pl.c_col || p.b0 != 1 || p.b1 != 1 || p.fused() || (pl.ldc % 4) || ((uintptr_t)p.c & 15)) return B200_ERR_UNSUPPORTED;
+  Launch L;
+  const int st = build_launch(L, pl, 2, CfgHB::BMB, CfgHB::BN, CfgHB::BMB, CfgHB::BN, CfgHB::BK, CfgHB::CH);
+  if (st) return st;
+  DeviceState* ds = device_state();
+  const int sms = grid_sms(ds);
+  TcArgs& g = L.g;
+  const int total_kb = g.red * g.k_blocks;
+  // K slices by the same model as the scratch route: per 64-wide k-block 0.6 us, per unit about 10 us beside it
+  int slices = 1;
+  {
+    double t_best = (double)((g.total_tiles + sms - 1) / sms) * ((double)total_kb * 0.6 + 10.0);
+    for (int s_ = 2; s_ <= 64; ++s_) {
+      if (total_kb / s_ < 8) break;
+      const double waves = (double)((g.total_tiles * s_ + sms - 1) / sms);
+      const double t = waves * ((double)((total_kb + s_ - 1) / s_) * 0.6 + 10.0);
+      if (t < 0.85 * t_best) { t_best = t; slices = s_; }
+    }
+  }
+  const int kb_per = (total_kb + slices - 1) / slices;
+  slices = (total_kb + kb_per - 1) / kb_per;
+  const uint64_t dims[4] = {(uint64_t)p.n, (uint64_t)p.m, 1, 1};
+  const uint64_t strides[3] = {(uint64_t)pl.ldc * 4, (uint64_t)pl.ldc * 4 * (uint64_t)p.m, (uint64_t)pl.ldc * 4 * (uint64_t)p.m};
+  const uint32_t box[4] = {32, (uint32_t)BM, 1, 1};
+  const int er = encode_map_f32(&L.mc, p.c, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (er) return er;
+  g.acc32 = 1; g.c_tma = 0; g.beta = 1;
+  g.kb_per_slice = kb_per; g.ksplit = slices; g.total_units = g.total_tiles * slices;
+  g.split_out = nullptr; g.split_ld = 0;
+  const long long grid = g.total_units < sms ? g.total_units : sms;
+  if (grid <= 0) return B200_OK;
+  gemm_f16_big_kernel<<<(unsigned)grid, CfgHB::THREADS, CfgHB::SMEM_BYTES, stream>>>(L.ma, L.mb, L.mc, L.g);
+  count_launch(true);
+  return note_cuda_error(cudaGetLastError(), "tensor-core gemm launch (f32 destination)");
+}
+
 template <int ESIZE, int BN>
 int launch_bn(const Plan& pl, cudaStream_t stream, int ksplit) {
   if constexpr (ESIZE == 2) return launch_cfg<CfgH<BN>, 2, BN>(pl, stream, gemm_f16_kernel<BN>, ksplit);
@@ -1600,7 +1642,7 @@ void cv_common_args(TcArgs& g, DeviceState* ds) {
   g.c_b0 = g.c_b1 = 0; g.c_col = 0; g.c_wide = 0; g.c_tma = 0; g.beta = 0;
   g.xform_mode = g_xform_mode.load();
   g.status = ds->status;
-  g.fused = 0; g.alpha = 1.f; g.bias = nullptr; g.bias_row = 0; g.act = B200_ACT_NONE;
+  g.fused = 0; g.alpha = 1.f; g.bias = nullptr; g.bias_row = 0; g.act = B200_ACT_NONE; g.acc32 = 0;
   g.cv_cblocks = 1; g.cv_cpad = 16; g.cv_kw = 1; g.cv_taps = 1; g.cv_w0 = g.cv_dw = g.cv_h0 = g.cv_dh = 0;
   g.cv_rows = 1; g.cv_wout = 1; g.cv_wblocks = 1; g.cv_bw = 16; g.cv_bh = 1; g.m64 = 0;
 }
@@ -1815,6 +1857,15 @@ int launch_gemm_tc(const GemmProblem& p, cudaStream_t stream) {
   }
   if (p.dtype == B200_F32) return launch_es<4>(*pl, stream);
   return launch_es<2>(*pl, stream);
+}
+
+// GemmProblem::acc32: f16 operands, f32 destination.  Only the row-store orientation (the kernel's N along C's unit
+// stride); B200_ERR_UNSUPPORTED without a launch where the operands are not TMA-addressable.
+int launch_gemm_tc_acc32(const GemmProblem& p, cudaStream_t stream) {
+  if (!p.acc32 || (p.dtype != B200_F16 && p.dtype != B200_AMP_F16)) return B200_ERR_UNSUPPORTED;
+  const Plan row = make_plan(p, false);
+  if (!row.ok) return B200_ERR_UNSUPPORTED;
+  return launch_big_f16_acc32(row, stream);
 }
 
 int tc_wait_selftest(long long limit, long long* cycles, cudaStream_t stream) {

@@ -331,6 +331,7 @@ struct TcArgs {
   float alpha;
   const void* bias;               // C's element type, 16-byte aligned; indexed by the kernel's column, or
   int bias_row;                   // (bias_row) by the kernel's row
+  int acc32;                      // f16 kernels: the f32 accumulator is added to an f32 C through bulk reduce-adds
   int act;                        // B200_ACT_*
   // Implicit convolution (f32 kernel, template parameter CV != 0): the im2col happens in the TMA loads.
   //   CV 1 (forward / data gradient): the B tile of k-block (tap, channel block) is ONE box of a channels-last

@@ -161,6 +161,18 @@ class Cuda:
                                                          _st(rhs.stride()), _ptr(grad_rhs), grad_out.data_ptr(),
                                                          self._stream()), "b200_matmat_br_backward_overwrite")
 
+    def matmat_br_grad_rhs_f32(self, lhs, grad_out, grad_rhs32) -> None:
+        """grad_rhs32 (an f32 (K, N) view, any of the two orientations) += sum_b lhs_b^T . grad_out_b for f16 lhs
+        (B, M, K) and a contiguous f16 grad_out (B, M, N): the weight gradient of a broadcast-rhs matmul added in f32
+        to an f32 gradient buffer, one launch (`b200_matmat_br_grad_rhs_f32`)."""
+        (b, m, k), n = lhs.shape, grad_out.shape[-1]
+        _assert_eq(tuple(grad_rhs32.shape), (k, n))
+        if grad_rhs32.dtype != torch.float32:
+            raise TypeError("grad_rhs32 must be an f32 tensor")
+        check(self.lib.b200_matmat_br_grad_rhs_f32(self._dtype(lhs), b, m, k, n, lhs.data_ptr(), _st(lhs.stride()),
+                                                   grad_out.data_ptr(), grad_rhs32.data_ptr(), _st(grad_rhs32.stride()),
+                                                   self._stream()), "b200_matmat_br_grad_rhs_f32")
+
     def matmat_batch3_forward(self, lhs, rhs):
         (b, m, k), n = lhs.shape, rhs.shape[2]
         out = self._empty((b, m, n), lhs)

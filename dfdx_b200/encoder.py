@@ -225,7 +225,7 @@ class _DirectLinear(torch.autograd.Function):
     @staticmethod
     def backward(ctx, grad_out):
         x, y = ctx.saved_tensors
-        dev, (w16, _, gw16, gb32) = ctx.dev, ctx.slot
+        dev, (w16, _, gw16, gb32) = ctx.dev, ctx.slot[:4]
         g = grad_out.contiguous()
         if ctx.relu:
             g = torch.ops.aten.threshold_backward(g, y, 0.0)
@@ -252,6 +252,19 @@ class _DirectLayerNorm(torch.autograd.Function):
         x, stats = ctx.saved_tensors
         g16, _, gg32, gb32 = ctx.slot
         return None, ctx.dev.layer_norm_backward(x, g16, stats, grad_out.contiguous(), gg32, gb32), None, None
+
+
+def _weight_grad(dev: Cuda, x, slot, g) -> None:
+    """The weight gradient of `Linear(x)` given the gradient g of its output: added in f32 straight into the f32
+    gradient of the master weight where the slot carries it and the blocks are told to (one launch, no f16 copy of the
+    gradient, no cast at the end of the step), else written as f16 into the slot's f16 gradient."""
+    if _ACC32[0] and len(slot) > 4 and slot[4] is not None:
+        dev.matmat_br_grad_rhs_f32(x, g, slot[4].permute(1, 0))
+    else:
+        dev.matmat_br_backward_overwrite(x, None, slot[0].permute(1, 0), slot[2], g)
+
+
+_ACC32 = [False]        # set by the Trainer that owns f32 gradients and skips the f16 -> f32 copy in exchange
 
 
 class _DirectAttentionBlock(torch.autograd.Function):
@@ -287,12 +300,13 @@ class _DirectAttentionBlock(torch.autograd.Function):
         # LayerNorm: gs is the gradient of x + y, i.e. of both; its column sums are w_o's bias gradient
         gs = dev.layer_norm_backward_sum(total, ln[0], stats, grad_out.contiguous(), ln[2], ln[3], o[3])
         g_tokens = torch.empty_like(tokens)
-        dev.matmat_br_backward_overwrite(tokens, g_tokens, o[0].permute(1, 0), o[2], gs)
+        dev.matmat_br_backward_overwrite(tokens, g_tokens, o[0].permute(1, 0), None, gs)
+        _weight_grad(dev, tokens, o, gs)
         gp = torch.empty_like(p)
         q, k, v = _split_qkv(p, heads)
         dev.attention_backward(q, k, v, ctx.alpha, out, lse, g_tokens.view(b, s, heads, m // heads).permute(0, 2, 1, 3),
                                write_into=_split_qkv(gp, heads))
-        dev.matmat_br_backward_overwrite(x, None, qkv[0].permute(1, 0), qkv[2], gp)      # weight gradient, written
+        _weight_grad(dev, x, qkv, gp)
         dev.matmat_br_backward(x, gs, qkv[0].permute(1, 0), None, gp)                    # gs += gp . W_qkv
         dev.bias_grad(gp, qkv[3])
         return None, gs, None, None, None, None, None
@@ -320,9 +334,10 @@ class _DirectFeedForwardBlock(torch.autograd.Function):
         dev, (l1, l2, ln) = ctx.dev, ctx.slots
         gs = dev.layer_norm_backward_sum(total, ln[0], stats, grad_out.contiguous(), ln[2], ln[3], l2[3])
         gh = torch.empty_like(h)
-        dev.matmat_br_backward_overwrite(h, gh, l2[0].permute(1, 0), l2[2], gs)
+        dev.matmat_br_backward_overwrite(h, gh, l2[0].permute(1, 0), None, gs)
+        _weight_grad(dev, h, l2, gs)
         dev.relu_backward_bias_grad(h, gh, l1[3])
-        dev.matmat_br_backward_overwrite(x, None, l1[0].permute(1, 0), l1[2], gh)
+        _weight_grad(dev, x, l1, gh)
         dev.matmat_br_backward(x, gs, l1[0].permute(1, 0), None, gh)                    # gs += gh . W_1
         return None, gs, None, None, None, None
 
@@ -478,7 +493,7 @@ class Trainer:
                 return self.flat16[lo:hi].view_as(p)
             for m in linears:
                 lo, hi = spans[id(m.weight)]
-                m.slot = (v16(m.weight), v16(m.bias), self.flat_gw16[lo:hi].view_as(m.weight), m.bias.grad)
+                m.slot = (v16(m.weight), v16(m.bias), self.flat_gw16[lo:hi].view_as(m.weight), m.bias.grad, m.weight.grad)
             for blk in self.model.blocks:
                 for ln in (blk.norm1, blk.norm2):
                     ln.slot = (v16(ln.weight), v16(ln.bias), ln.weight.grad, ln.bias.grad)
@@ -490,8 +505,17 @@ class Trainer:
                 if all(ws[i][1] == ws[i + 1][0] and bs[i][1] == bs[i + 1][0] for i in range(2)):
                     o3, i_ = 3 * a.w_q.weight.shape[0], a.w_q.weight.shape[1]
                     a.qkv_slot = (self.flat16[ws[0][0]:ws[2][1]].view(o3, i_), self.flat16[bs[0][0]:bs[2][1]],
-                                  self.flat_gw16[ws[0][0]:ws[2][1]].view(o3, i_), self.flat_grad[bs[0][0]:bs[2][1]])
+                                  self.flat_gw16[ws[0][0]:ws[2][1]].view(o3, i_), self.flat_grad[bs[0][0]:bs[2][1]],
+                                  self.flat_grad[ws[0][0]:ws[2][1]].view(o3, i_))
             self.model.attach = True
+        # With every Linear inside the hand-written blocks (f16 input, fused attention, head size the kernel takes) the
+        # weight gradients are added in f32 straight into flat_grad; the f16 gradient buffer and its cast are not used.
+        blocks = list(self.model.blocks)
+        a0 = blocks[0].attn if blocks else None
+        self.acc32 = bool(self.direct and a0 is not None and a0.fused == "attention" and len(linears) == 6 * len(blocks)
+                          and all(b.attn.qkv_slot is not None for b in blocks)
+                          and (a0.w_q.weight.shape[0] // a0.heads) % 8 == 0 and a0.w_q.weight.shape[0] // a0.heads <= 128
+                          and all(d % 8 == 0 for m in linears for d in m.weight.shape))
         # Adam is element-wise, so it runs on the one flat buffer (a single fused kernel per step) instead of on the
         # hundred parameter views into it; `params` keeps the views for inspection
         self.params = params
@@ -502,11 +526,14 @@ class Trainer:
 
     def _step(self, x: torch.Tensor, target: torch.Tensor) -> torch.Tensor:
         self.flat_grad.zero_()
+        _ACC32[0] = self.acc32
+        if self.acc32 and x.dtype != torch.float16:
+            raise TypeError("this trainer's blocks take f16 inputs")
         if self.direct:
             self.flat16.copy_(self.flat_param)
         loss = F.mse_loss(self.model(x).float(), target.float())
         loss.backward()
-        if self.direct:
+        if self.direct and not self.acc32:
             self.flat_grad[:self.n_weights].copy_(self.flat_gw16)
         if self.world > 1:
             import torch.distributed as dist

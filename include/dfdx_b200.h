@@ -265,6 +265,19 @@ int b200_matmat_batch4_backward(int dtype, size_t batch, size_t seq, size_t m, s
 
 /* ---- GEMMs with a fused epilogue (API additions: no single counterpart in the reference) -------- */
 
+/* Mixed-precision form of the broadcast-rhs weight gradient (the grad_rhs half of MatMatBrKernel::backward,
+ * dfdx-core/src/tensor_ops/matmul/cuda_kernel.rs:358-371): f16 lhs and grad_out, and a gradient buffer that holds f32:
+ *     grad_rhs[k x n, strides grad_rhs_strides in f32 elements] += sum_b lhs_b^T * grad_out_b
+ * added in f32 without an f16 rounding in between -- what a trainer that keeps f32 master weights and f32 gradients
+ * (dfdx's AMP dtype) otherwise gets from an f16 gradient buffer plus a cast, and one launch (the K slices add into
+ * grad_rhs itself through bulk reduce-adds: no scratch, no zero fill, no second kernel).  dtype B200_F16 or
+ * B200_AMP_F16; tensor cores only: B200_ERR_UNSUPPORTED without a launch where the operands are not TMA-addressable
+ * (16-byte aligned bases, a unit stride per operand, other strides multiples of 8 elements; grad_rhs: a unit stride
+ * and the other a multiple of 8). */
+int b200_matmat_br_grad_rhs_f32(int dtype, size_t batch, size_t m, size_t k, size_t n,
+                                const void* lhs, const size_t lhs_strides[3], const void* grad_out,
+                                float* grad_rhs, const size_t grad_rhs_strides[2], void* stream);
+
 /* `b200_matmat_br_backward` for the FIRST accumulation into freshly allocated gradient buffers: grad_lhs and grad_rhs
  * are written, not added to, so they need not be zero-filled and are not read (dfdx zero-fills every gradient buffer
  * in `Gradients::try_alloc_for` and the first backward op then adds into the zeros: two extra passes over each

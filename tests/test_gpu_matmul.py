@@ -179,6 +179,41 @@ def test_f16_256x256_tile_kernel_k_slices(cuda_dev, oracle, layout, slices):
         dev.set_path(dfdx_b200.PATH_AUTO)
 
 
+@pytest.mark.parametrize("stored", ["kn", "nk"])
+@pytest.mark.parametrize("shape", [(4, 256, 264, 520), (3, 136, 1032, 264), (64, 256, 512, 2048), (2, 72, 24, 16)], ids=str)
+def test_weight_gradient_added_in_f32(cuda_dev, oracle, shape, stored):
+    """`b200_matmat_br_grad_rhs_f32`: the broadcast-rhs weight gradient of f16 operands added in f32 to an f32 buffer
+    that already holds values, in both storage orders of the (K, N) gradient (dfdx's Linear keeps (N, K)), whole-K
+    tiles and K slices, ragged extents; against the f64 oracle at f32 accuracy (an f16 gradient buffer would be at 5e-4),
+    and twice in a row (it accumulates)."""
+    dev = cuda_dev
+    b, m, k, n = shape
+    g = gen(4000 + sum(shape))
+    lhs = (torch.randn(b, m, k, generator=g) * 0.5).half().to(dev.device)
+    go = (torch.randn(b, m, n, generator=g) * 0.5).half().to(dev.device)
+    start = torch.randn(k, n, generator=g)
+    buf = (start if stored == "kn" else start.t().contiguous()).to(dev.device)
+    view = buf if stored == "kn" else buf.t()
+    want = lhs.cpu().double().reshape(-1, k).t() @ go.cpu().double().reshape(-1, n)
+    before = dev.lib.b200_launch_count()
+    dev.matmat_br_grad_rhs_f32(lhs, go, view)
+    dev.synchronize()
+    assert dev.lib.b200_launch_count() - before == 1
+    # f32 accumulation of b * m products per element (up to 16384 here) and one f32 rounding of start + sum
+    err = oracle.rel_frobenius(view.cpu().double() - start.double(), want)
+    assert err <= 2e-5, f"rel frobenius {err:.3e}"
+    dev.matmat_br_grad_rhs_f32(lhs, go, view)
+    dev.synchronize()
+    err = oracle.rel_frobenius(view.cpu().double() - start.double(), 2 * want)
+    assert err <= 2e-5, f"rel frobenius {err:.3e} after the second call"
+    # operands the tensor-core path cannot address are refused before any launch (the caller keeps its f16 route)
+    before = dev.lib.b200_launch_count()
+    with pytest.raises(dfdx_b200.B200Error) as e:
+        dev.matmat_br_grad_rhs_f32(lhs[:, :, 1:], go, view[1:, :])
+    assert e.value.status == dfdx_b200._lib.ERR_UNSUPPORTED
+    assert dev.lib.b200_launch_count() == before
+
+
 @pytest.mark.parametrize("dtype", [torch.float16, torch.float32])
 @pytest.mark.parametrize("layout", ["".join(p) for p in itertools.product("rc", repeat=3)])
 def test_cta_pair_kernels(cuda_dev, oracle, dtype, layout):
