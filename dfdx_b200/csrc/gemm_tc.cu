@@ -811,7 +811,7 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_const
       if (!ok) break;
       if (un.kb_lo >= un.kb_hi) continue;               // an empty unit of the stream-K decomposition
       // partial sums (a K slice, or a stream-K range that does not span the tile's whole K) are added atomically
-      const bool partial = g.ksplit > 1 || ((g.streamk || g.tail_per > 0) && !(un.kb_lo == 0 && un.kb_hi == total_kb));
+      const bool partial = g.ksplit > 1 || ((g.streamk || g.tail_per > 0 || g.kt_cut > 0) && !(un.kb_lo == 0 && un.kb_hi == total_kb));
       // An MMA with M = 64 (m64: outputs of at most 64 rows) keeps row r in TMEM lane (r / 16) * 32 + r % 16: each
       // warp's lanes 0..15 hold 16 rows, its lanes 16..31 nothing.
       const bool m64 = CV == 1 && g.m64;
@@ -1174,7 +1174,7 @@ int build_launch(Launch& L, const Plan& pl, int esize, int tm, int tn, int bmc, 
   g.n_fast = g.n_tiles < g.m_tiles ? 1 : 0;
   g.total_tiles = (long long)g.m_tiles * g.n_tiles * p.b0 * p.b1;
   g.ksplit = 1; g.kb_per_slice = 0; g.total_units = g.total_tiles;   // launch_cfg fills the slice length
-  g.tail_from = 0; g.tail_per = 0; g.tail_parts = 0;
+  g.tail_from = 0; g.tail_per = 0; g.tail_parts = 0; g.kt_cut = 0; g.kt_per = 0;
   g.streamk = 0; g.sk_per_cta = 0;
   g.red = (int)p.red;
   g.k_blocks = (int)((p.k + bk - 1) / bk);
@@ -1231,7 +1231,24 @@ std::atomic<int> g_tail_mode{0};   // 0 = choose, 1 = never (testing)
 int plan_tail_split(TcArgs& g, int sms, int total_kb, cudaStream_t stream) {
   if (g_tail_mode.load() == 1 || g.ksplit != 1 || g.streamk || g.fused || g.c_col) return B200_OK;
   const long long full = g.total_tiles / sms, rem = g.total_tiles % sms;
-  if (full < 1 || rem == 0) return B200_OK;
+  if (rem == 0) return B200_OK;
+  if (full < 1) {
+    // Less than one round of tiles (and more than half of one: fewer take the K split), an output that is added to (a
+    // gradient: no tile needs a zero fill first).  CTA c < tiles computes k-blocks [0, cut) of tile c; the CTAs that
+    // would idle share out the tiles' last total - cut k-blocks, `per` tiles each, and add their sums to the same
+    // output.  (Dealing out one contiguous range of the whole (tile, k-block) space per CTA, as for a tail, puts every
+    // CTA at a different K position at any time: no two of them share an operand panel in L2 any more and the launch
+    // becomes DRAM-bound -- measured: no gain at all.)
+    if (!g.beta || 2 * rem < sms) return B200_OK;
+    const long long extra = sms - rem, per = (rem + extra - 1) / extra;
+    const double fixed = 8.0;                              // k-blocks a unit costs beside its main loop (4 .. 16 measure alike)
+    const long long cut = (long long)((per * (double)total_kb + fixed * per) / (1.0 + per)) + 1;   // cut ~ per * (total - cut + fixed)
+    if (cut >= total_kb || total_kb - cut < 4) return B200_OK;
+    if ((double)cut + fixed > 0.95 * ((double)total_kb + fixed)) return B200_OK;
+    g.kt_cut = (int)cut; g.kt_per = (int)per;
+    g.total_units = (long long)sms * per;
+    return B200_OK;
+  }
   if (!g.beta && rem > TAIL_MAX_ZEROED) return B200_OK;
   // one contiguous range of the tail's (tile, k-block) space per CTA; at least four k-blocks per range
   long long per = (rem * total_kb + sms - 1) / sms;
@@ -1635,7 +1652,7 @@ int conv_rows_per_tile(const ConvImplicit& c, int sms) {
 void cv_common_args(TcArgs& g, DeviceState* ds) {
   g.nb1 = 1; g.n_fast = 0;
   g.ksplit = 1; g.streamk = 0; g.sk_per_cta = 0; g.split_out = nullptr; g.split_ld = 0;
-  g.tail_from = 0; g.tail_per = 0; g.tail_parts = 0;
+  g.tail_from = 0; g.tail_per = 0; g.tail_parts = 0; g.kt_cut = 0; g.kt_per = 0;
   g.red = 1;
   g.a_mn = 0; g.b_mn = 0; g.a_ld = 0; g.b_ld = 0;
   g.a_x1 = g.a_xr = g.a_y0 = g.b_x1 = g.b_xr = g.b_y0 = 0;

@@ -306,6 +306,9 @@ struct TcArgs {
   // results atomically like split-K slices.  tail_per == 0: off.
   long long tail_from;
   int tail_per, tail_parts;
+  // fewer tiles than CTAs (beta = 1): k-blocks [0, kt_cut) of tile c on CTA c, the rest on the other CTAs, kt_per
+  // tiles each (decode_unit).  kt_cut == 0: off.
+  int kt_cut, kt_per;
   int streamk;                    // f32 kernel: the (tile, k-block) space is cut into one contiguous range per CTA
   long long sk_per_cta;           // k-blocks per CTA; a unit is the part of one tile inside the CTA's range (may be empty)
   float* split_out;               // f16 kernel with ksplit > 1: f32 scratch (m x split_ld, zeroed) that takes the
@@ -601,6 +604,21 @@ __device__ __forceinline__ Unit decode_unit(const TcArgs& g, long long unit, int
     const long long lo = start > t0 ? start : t0, hi = end < t0 + total_kb ? end : t0 + total_kb;
     if (hi <= lo || u.tile >= g.total_tiles) { u.tile = 0; u.kb_lo = u.kb_hi = 0; }   // nothing of that tile in the range
     else { u.kb_lo = (int)(lo - t0); u.kb_hi = (int)(hi - t0); }
+    return u;
+  }
+  if (g.kt_cut > 0) {
+    // Fewer tiles than CTAs, an output that is added to: CTA c < tiles takes k-blocks [0, kt_cut) of tile c -- all of
+    // them at the same K position at the same time, so that the CTAs of a row / column of tiles share their operand
+    // panels in L2 as in the unsplit launch -- and the remaining CTAs take the tiles' last k-blocks [kt_cut, total),
+    // kt_per tiles each.
+    const long long part = unit / gridDim.x, cta = unit - part * gridDim.x;
+    u.tile = 0; u.kb_lo = u.kb_hi = 0;
+    if (cta < g.total_tiles) {
+      if (part == 0) { u.tile = cta; u.kb_hi = g.kt_cut; }
+    } else {
+      const long long seg = (cta - g.total_tiles) * g.kt_per + part;
+      if (part < g.kt_per && seg < g.total_tiles) { u.tile = seg; u.kb_lo = g.kt_cut; u.kb_hi = total_kb; }
+    }
     return u;
   }
   if (g.tail_per > 0 && unit >= g.tail_from) {

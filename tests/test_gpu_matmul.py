@@ -564,8 +564,9 @@ def test_config3_attention_matmuls_f16(cuda_dev, oracle):
 @pytest.mark.parametrize("layout", ["rrr", "rcr", "crr"])
 def test_tail_split_f32(cuda_dev, oracle, layout):
     """150 tiles on 148 SMs: the two tiles of the second round are cut along K over all SMs and summed atomically
-    (beta 0: those tiles are zeroed first, the output is NaN-poisoned; beta 1), ragged edges included; the same
-    problems with the tail split switched off give the same results within the tolerance."""
+    (beta 0: those tiles are zeroed first, the output is NaN-poisoned; beta 1), ragged edges included; problems with
+    less than one round of tiles and beta 1; the same problems with the tail split switched off give the same results
+    within the tolerance."""
     dev = cuda_dev
     dev.set_path(dfdx_b200.PATH_TENSOR)
     assert dev.lib.b200_set_tile_n(256) == 0
@@ -578,6 +579,12 @@ def test_tail_split_f32(cuda_dev, oracle, layout):
                     check_gemm(dev, oracle, m, k, n, layout[0], layout[1], layout[2], beta, torch.float32, pad=8,
                                seed=700 + i)
                     assert dev.lib.b200_launch_count() - l0 == 1
+            # less than one round of tiles (100 and 96 on 148 SMs), long K, an output that is added to: the whole
+            # (tile, k-block) space is dealt out over the SMs
+            for i, (m, k, n) in enumerate([(640, 1024, 5120), (3 * 128 - 24, 1032, 32 * 256 - 40)]):
+                l0 = dev.lib.b200_launch_count()
+                check_gemm(dev, oracle, m, k, n, layout[0], layout[1], layout[2], 1, torch.float32, pad=8, seed=720 + i)
+                assert dev.lib.b200_launch_count() - l0 == 1
     finally:
         dev.lib.b200_set_tail_split(0)
         dev.lib.b200_set_tile_n(0)
