@@ -590,11 +590,13 @@ __device__ __forceinline__ void add_chunk_atomic_col(float* dst, const float* v,
 
 struct TileCoord { int mt, nt, ib0, ib1; };
 struct Unit { long long tile; int kb_lo, kb_hi; };
-__device__ __forceinline__ Unit decode_unit(const TcArgs& g, long long unit, int total_kb) {
+// Work unit -> (tile, k-block range) for a launch of `grid` CTAs; CTA c takes units c, c + grid, ...  A pure function of
+// its arguments (the host-side test of the schedules calls it as it is).
+__host__ __device__ __forceinline__ Unit decode_unit_on(const TcArgs& g, long long unit, int total_kb, long long grid) {
   Unit u;
   if (g.streamk) {
-    // unit = blockIdx.x + i * gridDim.x is the i-th tile that CTA blockIdx.x's k-block range touches
-    const long long cta = unit % gridDim.x, i = unit / gridDim.x;
+    // unit = blockIdx.x + i * grid is the i-th tile that CTA blockIdx.x's k-block range touches
+    const long long cta = unit % grid, i = unit / grid;
     const long long start = cta * g.sk_per_cta;
     long long end = start + g.sk_per_cta;
     const long long all = g.total_tiles * (long long)total_kb;
@@ -611,7 +613,7 @@ __device__ __forceinline__ Unit decode_unit(const TcArgs& g, long long unit, int
     // them at the same K position at the same time, so that the CTAs of a row / column of tiles share their operand
     // panels in L2 as in the unsplit launch -- and the remaining CTAs take the tiles' last k-blocks [kt_cut, total),
     // kt_per tiles each.
-    const long long part = unit / gridDim.x, cta = unit - part * gridDim.x;
+    const long long part = unit / grid, cta = unit - part * grid;
     u.tile = 0; u.kb_lo = u.kb_hi = 0;
     if (cta < g.total_tiles) {
       if (part == 0) { u.tile = cta; u.kb_hi = g.kt_cut; }
@@ -622,8 +624,8 @@ __device__ __forceinline__ Unit decode_unit(const TcArgs& g, long long unit, int
     return u;
   }
   if (g.tail_per > 0 && unit >= g.tail_from) {
-    // unit = tail_from + part * gridDim.x + cta: the part-th tile that CTA cta's range of the tail touches
-    const long long v = unit - g.tail_from, part = v / gridDim.x, cta = v - part * gridDim.x;
+    // unit = tail_from + part * grid + cta: the part-th tile that CTA cta's range of the tail touches
+    const long long v = unit - g.tail_from, part = v / grid, cta = v - part * grid;
     const long long all = (g.total_tiles - g.tail_from) * (long long)total_kb;
     const long long start = cta * g.tail_per;
     long long end = start + g.tail_per;
@@ -640,6 +642,9 @@ __device__ __forceinline__ Unit decode_unit(const TcArgs& g, long long unit, int
   u.kb_lo = slice * g.kb_per_slice;
   u.kb_hi = u.kb_lo + g.kb_per_slice < total_kb ? u.kb_lo + g.kb_per_slice : total_kb;
   return u;
+}
+__device__ __forceinline__ Unit decode_unit(const TcArgs& g, long long unit, int total_kb) {
+  return decode_unit_on(g, unit, total_kb, (long long)gridDim.x);
 }
 __device__ __forceinline__ TileCoord decode_tile(const TcArgs& g, long long tile) {
   const long long per_batch = (long long)g.m_tiles * g.n_tiles;
